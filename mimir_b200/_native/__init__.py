@@ -1,0 +1,74 @@
+"""ctypes binding of ``libmimir_b200.so`` (plain C ABI, see ``csrc/*.cu``).
+
+The library is built in-tree by :mod:`mimir_b200._native.build`.  On a machine
+with a GPU a missing library is an error, never a silent fallback: callers use
+:func:`lib` and get an exception that names the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libmimir_b200.so"
+_lib = None
+
+
+class NativeUnavailable(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    """Returns the loaded native library, building nothing: raises if absent."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise NativeUnavailable(
+                f"{LIB_PATH} is missing; run `python -m mimir_b200._native.build`")
+        _lib = ctypes.CDLL(str(LIB_PATH), mode=os.RTLD_LOCAL | os.RTLD_NOW)
+        _declare(_lib)
+    return _lib
+
+
+def available() -> bool:
+    try:
+        lib()
+        return True
+    except (NativeUnavailable, OSError):
+        return False
+
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_ll = ctypes.c_longlong
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    def sig(name, res, *args):
+        fn = getattr(l, name, None)
+        if fn is not None:
+            fn.restype = res
+            fn.argtypes = list(args)
+
+    sig("mimir_version", c_int)
+    sig("mimir_set_device", c_int, c_int)
+    sig("mimir_error_word", ctypes.c_uint, c_int)
+    sig("mimir_launch_count", c_ll)
+    sig("mimir_launch_count_add", None, c_ll)
+    sig("mimir_last_error", ctypes.c_char_p)
+    sig("mimir_sm_count", c_int)
+    sig("mimir_gemm_workspace_bytes", c_ll, c_int, c_int)
+    sig("mimir_gemm_bf16", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_ll,
+        c_int, c_int, c_void_p)
+
+
+def last_error() -> str:
+    return lib().mimir_last_error().decode()
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what}: {last_error()}")

@@ -1,0 +1,108 @@
+"""Builds the native library in-tree: every ``csrc/*.cu`` / ``*.cpp`` is compiled
+for sm_100a and linked into ``mimir_b200/_native/libmimir_b200.so``.
+
+The library has a plain C ABI (no Python or torch headers), so it compiles in
+seconds, loads through ``ctypes`` here and through ``purego`` from Go, and the
+same symbols serve both.  Run ``python -m mimir_b200._native.build``.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CSRC = HERE.parent / "csrc"
+OBJ = HERE / "build"
+LIB = HERE / "libmimir_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3",
+    "-Xptxas", "-v",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _digest(src: Path) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(src.read_bytes())
+    for hdr in sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")):
+        h.update(hdr.read_bytes())
+    return h.hexdigest()
+
+
+def _compile(src: Path, verbose: bool) -> Path:
+    obj = OBJ / (src.name + ".o")
+    stamp = OBJ / (src.name + ".sha")
+    dig = _digest(src)
+    if obj.exists() and stamp.exists() and stamp.read_text() == dig:
+        return obj
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    if src.suffix == ".cpp":
+        cmd.insert(1, "-x")
+        cmd.insert(2, "cu")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    log = OBJ / (src.name + ".log")
+    log.write_text(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        sys.stderr.write(f"[build] {src.name}\n")
+    stamp.write_text(dig)
+    return obj
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compiles what changed and links the shared library; returns its path."""
+    OBJ.mkdir(exist_ok=True)
+    if force:
+        for f in OBJ.glob("*.sha"):
+            f.unlink()
+    srcs = sources()
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
+    newest = max(o.stat().st_mtime for o in objs)
+    if LIB.exists() and LIB.stat().st_mtime >= newest and not force:
+        return LIB
+    tmp = LIB.with_suffix(".so.tmp")
+    cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs),
+           "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-lpthread", "-ldl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, LIB)
+    if verbose:
+        sys.stderr.write(f"[build] linked {LIB}\n")
+    return LIB
+
+
+def ptxas_report() -> str:
+    """Concatenates the registers / spills / shared-memory lines of the last build."""
+    out = []
+    for log in sorted(OBJ.glob("*.log")):
+        out.append(f"== {log.name}\n{log.read_text()}")
+    return "\n".join(out)
+
+
+if __name__ == "__main__":
+    build(verbose=True, force="--force" in sys.argv)
+    if "--report" in sys.argv:
+        print(ptxas_report())

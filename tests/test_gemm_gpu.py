@@ -1,0 +1,75 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch product of the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A @ B
+
+
+def _check(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < 2e-2, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 128, 64, 128), (256, 256, 128, 256), (384, 512, 320, 0), (1000, 776, 136, 0),
+    (4096, 768, 768, 0), (200, 64, 72, 64), (130, 264, 1024, 128),
+])
+def test_gemm_layouts(M, N, K, bn, a_mn, b_mn):
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte row pitch")
+    torch.manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    assert check_error_word() == 0
+    _check(out, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_gemm_epilogues():
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    torch.manual_seed(1)
+    M, N, K = 512, 384, 256
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    z = a.float() @ w.float().t() + bias.float()
+    pre = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, w, bias=bias, gelu=True, aux_out=pre)
+    _check(pre, z, K)
+    _check(out, torch.nn.functional.gelu(z, approximate="tanh"), K)
+    out = gemm(a, w, bias=bias, residual=True, aux=res)
+    _check(out, z + res.float(), K)
+    # d/dz gelu(z) via autograd
+    zz = res.float().clone().requires_grad_(True)
+    torch.nn.functional.gelu(zz, approximate="tanh").sum().backward()
+    out = gemm(a, w, mul_dgelu=True, aux=res)
+    _check(out, (a.float() @ w.float().t()) * zz.grad, K)
+    out32 = torch.ones(M, N, device="cuda")
+    gemm(a, w, out=out32, accumulate=True, alpha=0.5)
+    _check(out32, 1 + 0.5 * (a.float() @ w.float().t()), K)
+    assert check_error_word() == 0
+
+
+@pytest.mark.parametrize("splits", [2, 4, 7])
+def test_gemm_split_k(splits):
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    torch.manual_seed(2)
+    M, N, K = 256, 256, 2048
+    a = torch.randn(K, M, device="cuda").bfloat16()
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    out = gemm(a, b, a_mn=True, b_mn=True, splits=splits)
+    assert check_error_word() == 0
+    _check(out, _ref(a, b, True, True), K)
