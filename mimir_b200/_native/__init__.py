@@ -63,6 +63,30 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("mimir_gemm_bf16", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_ll,
         c_int, c_int, c_void_p)
+    P, I, F, L = c_void_p, c_int, c_float, c_ll
+    sig("mimir_layernorm_fwd", I, P, P, P, P, P, P, I, I, F, P)
+    sig("mimir_rmsnorm_fwd", I, P, P, P, P, I, I, F, P)
+    sig("mimir_norm_bwd_blocks", I)
+    sig("mimir_layernorm_bwd", I, P, P, P, P, P, P, P, P, P, P, I, I, I, P)
+    sig("mimir_rmsnorm_bwd", I, P, P, P, P, P, P, P, P, I, I, I, P)
+    sig("mimir_colsum", I, P, I, I, I, P, P, I, P)
+    sig("mimir_cross_entropy", I, P, P, P, P, P, I, I, I, F, F, P)
+    sig("mimir_softmax_rows", I, P, P, I, I, I, P)
+    sig("mimir_embedding_fwd", I, P, P, P, P, I, I, I, I, P)
+    sig("mimir_embedding_bwd", I, P, P, P, P, I, I, I, I, I, P)
+    sig("mimir_act_fwd", I, P, P, L, I, P)
+    sig("mimir_act_bwd", I, P, P, P, L, I, P)
+    sig("mimir_swiglu_fwd", I, P, P, I, I, P)
+    sig("mimir_swiglu_bwd", I, P, P, P, I, I, P)
+    sig("mimir_rope", I, P, P, P, I, I, I, I, I, I, I, P)
+    sig("mimir_cast_f32_bf16", I, P, P, L, F, P)
+    sig("mimir_cast_bf16_f32", I, P, P, L, F, P)
+    sig("mimir_axpby", I, P, P, P, L, F, F, P)
+    sig("mimir_sumsq", I, P, L, I, P, P)
+    sig("mimir_attention_fwd", I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, P)
+    sig("mimir_attention_bwd", I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
+        I, I, I, F, P)
+    sig("mimir_adamw_flat", I, P, P, P, I, P, P, L, L, F, F, F, F, F, I, F, P, F, P, P)
 
 
 def last_error() -> str:

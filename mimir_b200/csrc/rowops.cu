@@ -1,0 +1,461 @@
+// Row kernels: LayerNorm / RMSNorm forward+backward, softmax, fused
+// softmax-cross-entropy (loss + gradient in place).  One warp (norms) or one
+// block (vocabulary rows) per row, 128-bit loads, fp32 math, bf16 storage.
+//
+// Reference semantics: nn/layers.go:139 (LayerNorm), nn/transformer.go:28-61
+// (RMSNorm: normalise in fp32, round to the input dtype, then scale),
+// tensor/reduce.go:199-218 (softmax / log-softmax), nn/loss/loss.go:35-96
+// (cross entropy over class indices).
+#include "common.cuh"
+#include "runtime.h"
+
+namespace mimir {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm / RMSNorm forward.  Lane owns columns lane*8 + i*256.
+// ---------------------------------------------------------------------------
+template <int NCHUNK, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                const __nv_bfloat16* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * C;
+  float v[NCHUNK][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = lane * 8 + i * 256;
+    if (c < C) {
+      load8(xr + c, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += RMS ? v[i][j] * v[i][j] : v[i][j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+    }
+  }
+  s = warp_sum(s);
+  float mean = 0.f, rstd;
+  if (RMS) {
+    rstd = rsqrtf(s / C + eps);
+  } else {
+    mean = s / C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < C) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; q += d * d; }
+      }
+    }
+    q = warp_sum(q);
+    rstd = rsqrtf(q / C + eps);
+  }
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * C;
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = lane * 8 + i * 256;
+    if (c < C) {
+      float g[8], b[8], o[8];
+      load8(gamma + c, g);
+      if (!RMS && beta) load8(beta + c, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float n = (v[i][j] - mean) * rstd;
+        if (RMS) n = __bfloat162float(__float2bfloat16_rn(n));  // round before the scale
+        o[j] = n * g[j] + ((!RMS && beta) ? b[j] : 0.f);
+      }
+      store8(yr + c, o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm / RMSNorm backward.  dx (+= residual gradient), and per-block
+// partial sums of dgamma / dbeta in `partial` [gridDim.x][2][C] (fp32).
+// ---------------------------------------------------------------------------
+template <int NCHUNK, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C) {
+  extern __shared__ float red[];  // [warps][2][C] would be large: reduce through rounds instead
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  float dg[NCHUNK][8], db[NCHUNK][8], g[NCHUNK][8];
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    const int c = lane * 8 + i * 256;
+    if (c < C) load8(gamma + c, g[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; if (c >= C) g[i][j] = 0.f; }
+  }
+  for (int row = blockIdx.x * nwarp + warp; row < rows; row += gridDim.x * nwarp) {
+    const size_t off = static_cast<size_t>(row) * C;
+    const float mean = RMS ? 0.f : mean_in[row], rstd = rstd_in[row];
+    float xh[NCHUNK][8], d[NCHUNK][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < C) {
+        load8(x + off + c, xh[i]);
+        load8(dy + off + c, d[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          dg[i][j] += d[i][j] * xh[i][j];
+          db[i][j] += d[i][j];
+          d[i][j] *= g[i][j];
+          s1 += d[i][j];
+          s2 += d[i][j] * xh[i][j];
+        }
+      }
+    }
+    s1 = RMS ? 0.f : warp_sum(s1) / C;
+    s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < NCHUNK; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < C) {
+        float o[8];
+        if (dres) load8(dres + off + c, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float t = rstd * (d[i][j] - s1 - xh[i][j] * s2);
+          o[j] = dres ? o[j] + t : t;
+        }
+        store8(dx + off + c, o);
+      }
+    }
+  }
+  // Block reduce of dg / db over warps, one chunk at a time through shared memory.
+  float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * C;
+#pragma unroll
+  for (int i = 0; i < NCHUNK; ++i) {
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      red[(warp * 2 + 0) * 256 + lane * 8 + j] = dg[i][j];
+      red[(warp * 2 + 1) * 256 + lane * 8 + j] = db[i][j];
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < 512; t += blockDim.x) {
+      const int which = t >> 8, col = t & 255;
+      float s = 0.f;
+      for (int w = 0; w < nwarp; ++w) s += red[(w * 2 + which) * 256 + col];
+      const int c = col + i * 256;
+      if (c < C) out[which * C + c] = s;
+    }
+  }
+}
+
+// Sums `nparts` partial rows [nparts][width] into bf16 (optionally accumulating).
+// `out_f32` may be row 0 of `partial` itself (each thread reads column c of
+// every row before it writes column c).
+__global__ void reduce_partials_kernel(const float* partial, int nparts, int width,
+                                       __nv_bfloat16* out, float* out_f32, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * width + c];
+  if (out_f32) {
+    out_f32[c] = accumulate ? out_f32[c] + s : s;
+  } else {
+    if (accumulate) s += __bfloat162float(out[c]);
+    out[c] = __float2bfloat16_rn(s);
+  }
+}
+
+// Column sums of a bf16 matrix [rows, N] (row pitch ld) into partial[gridDim.y][N].
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ x, int rows, int N, int ld,
+                      float* __restrict__ partial) {
+  __shared__ float red[8][256];
+  const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + cg * 8;
+  const int rows_per = (rows + gridDim.y - 1) / gridDim.y;
+  const int r0 = blockIdx.y * rows_per, r1 = min(rows, r0 + rows_per);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < N) {
+    for (int r = r0 + rl; r < r1; r += 8) {
+      float v[8];
+      load8(x + static_cast<size_t>(r) * ld + col, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[rl][cg * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;
+  float s = 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) s += red[r][c];
+  if (blockIdx.x * 256 + c < N) partial[static_cast<size_t>(blockIdx.y) * N + blockIdx.x * 256 + c] = s;
+}
+
+// ---------------------------------------------------------------------------
+// Fused softmax cross-entropy over a padded vocabulary.  One block per row.
+// logits [rows, ld] bf16 (columns >= V are padding).  Writes loss[row] and, if
+// dlogits != nullptr, (softmax - onehot) * gscale in bf16 (may alias logits).
+// target < 0 means "ignore this row".
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ target,
+                     float* __restrict__ loss, __nv_bfloat16* __restrict__ dlogits, int V, int ld,
+                     float gscale, unsigned* err) {
+  __shared__ float smax[16], ssum[16];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  const int64_t tgt = target[row];
+  if (tgt >= V) { if (tid == 0) raise_error(err, kErrIndex); }
+  // read before anyone may overwrite the row in place
+  const float tgt_logit = (tid == 0 && tgt >= 0 && tgt < V) ? __bfloat162float(lr[tgt]) : 0.f;
+  float m = -INFINITY, s = 0.f;
+  for (int c = tid * 8; c < V; c += 512 * 8) {
+    float v[8];
+    load8(lr + c, v);
+    float cm = m;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (c + j < V) cm = fmaxf(cm, v[j]);
+    float add = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (c + j < V) add += __expf(v[j] - cm);
+    s = s * __expf(m - cm) + add;
+    m = cm;
+  }
+  // combine (m, s) pairs across the block
+  // a thread or warp that saw no column has m = -inf: its weight is zero
+  float wm = warp_max(m);
+  s = warp_sum(m == -INFINITY ? 0.f : s * __expf(m - wm));
+  if (lane == 0) { smax[warp] = wm; ssum[warp] = s; }
+  __syncthreads();
+  float bm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 16; ++w) bm = fmaxf(bm, smax[w]);
+  float bs = 0.f;
+#pragma unroll
+  for (int w = 0; w < 16; ++w) bs += smax[w] == -INFINITY ? 0.f : ssum[w] * __expf(smax[w] - bm);
+  const float lse = bm + __logf(bs);
+  const bool ignore = tgt < 0 || tgt >= V;
+  if (tid == 0) loss[row] = ignore ? 0.f : lse - tgt_logit;
+  if (dlogits) {
+    __nv_bfloat16* dr = dlogits + static_cast<size_t>(row) * ld;
+    const float gs = ignore ? 0.f : gscale;
+    for (int c = tid * 8; c < ld; c += 512 * 8) {
+      float v[8], o[8];
+      load8(lr + c, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float p = (c + j < V) ? __expf(v[j] - lse) : 0.f;
+        if (c + j == tgt) p -= 1.f;
+        o[j] = p * gs;
+      }
+      store8(dr + c, o);
+    }
+  }
+}
+
+// out[0] = scale * sum(x[0..n)); single block.
+__global__ void __launch_bounds__(1024) sum_scale_kernel(const float* __restrict__ x, int n, float scale,
+                                                        float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) out[0] = s * scale;
+  }
+}
+
+// Row softmax (bf16 in/out), one warp per row for short rows, used by generic
+// attention / classifier heads.  log != 0 writes log-softmax.
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int rows,
+                    int C, int log) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * C;
+  float m = -INFINITY;
+  for (int c = lane; c < C; c += 32) m = fmaxf(m, __bfloat162float(xr[c]));
+  m = warp_max(m);
+  float s = 0.f;
+  for (int c = lane; c < C; c += 32) s += __expf(__bfloat162float(xr[c]) - m);
+  s = warp_sum(s);
+  const float inv = 1.f / s, ls = __logf(s);
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * C;
+  for (int c = lane; c < C; c += 32) {
+    float v = __bfloat162float(xr[c]) - m;
+    yr[c] = __float2bfloat16_rn(log ? v - ls : __expf(v) * inv);
+  }
+}
+
+template <bool RMS>
+static int norm_fwd_dispatch(const void* x, const void* g, const void* b, void* y, float* mean,
+                             float* rstd, int rows, int C, float eps, cudaStream_t st) {
+  const int wpb = 8, grid = ceil_div(rows, wpb);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto G = static_cast<const __nv_bfloat16*>(g);
+  auto B = static_cast<const __nv_bfloat16*>(b);
+  auto Y = static_cast<__nv_bfloat16*>(y);
+#define CASE(NC) norm_fwd_kernel<NC, RMS><<<grid, wpb * 32, 0, st>>>(X, G, B, Y, mean, rstd, rows, C, eps)
+  if (C <= 256) CASE(1); else if (C <= 512) CASE(2); else if (C <= 768) CASE(3);
+  else if (C <= 1024) CASE(4); else if (C <= 2048) CASE(8); else if (C <= 4096) CASE(16);
+  else if (C <= 8192) CASE(32); else return refuse("norm: C=%d exceeds 8192", C);
+#undef CASE
+  count_launch();
+  return 0;
+}
+
+template <bool RMS>
+static int norm_bwd_dispatch(const void* dy, const void* x, const void* g, const float* mean,
+                             const float* rstd, const void* dres, void* dx, float* partial,
+                             int nblocks, int rows, int C, cudaStream_t st) {
+  const int wpb = 8;
+  const size_t smem = static_cast<size_t>(wpb) * 2 * 256 * sizeof(float);
+  auto DY = static_cast<const __nv_bfloat16*>(dy);
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto G = static_cast<const __nv_bfloat16*>(g);
+  auto DR = static_cast<const __nv_bfloat16*>(dres);
+  auto DX = static_cast<__nv_bfloat16*>(dx);
+#define CASE(NC) norm_bwd_kernel<NC, RMS><<<nblocks, wpb * 32, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partial, rows, C)
+  if (C <= 256) CASE(1); else if (C <= 512) CASE(2); else if (C <= 768) CASE(3);
+  else if (C <= 1024) CASE(4); else if (C <= 2048) CASE(8); else if (C <= 4096) CASE(16);
+  else return refuse("norm backward: C=%d exceeds 4096", C);
+#undef CASE
+  count_launch();
+  return 0;
+}
+
+}  // namespace mimir
+
+using namespace mimir;
+
+// y = LayerNorm(x) * gamma + beta over the last dim C (C % 8 == 0); saves mean / rstd (fp32).
+MIMIR_API int mimir_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y,
+                                  float* mean, float* rstd, int rows, int C, float eps,
+                                  cudaStream_t st) {
+  if (C % 8) return refuse("layernorm: C must be a multiple of 8");
+  return norm_fwd_dispatch<false>(x, gamma, beta, y, mean, rstd, rows, C, eps, st);
+}
+MIMIR_API int mimir_rmsnorm_fwd(const void* x, const void* gamma, void* y, float* rstd, int rows,
+                                int C, float eps, cudaStream_t st) {
+  if (C % 8) return refuse("rmsnorm: C must be a multiple of 8");
+  return norm_fwd_dispatch<true>(x, gamma, nullptr, y, nullptr, rstd, rows, C, eps, st);
+}
+
+// Number of blocks (and rows of `partial`) the backward kernels use.
+MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 2; }
+
+// dx = dres + LN'(dy); dgamma/dbeta (bf16) written, or accumulated when accumulate != 0.
+// partial: fp32 scratch of mimir_norm_bwd_blocks() * 2 * C floats.
+MIMIR_API int mimir_layernorm_bwd(const void* dy, const void* x, const void* gamma,
+                                  const float* mean, const float* rstd, const void* dres, void* dx,
+                                  void* dgamma, void* dbeta, float* partial, int rows, int C,
+                                  int accumulate, cudaStream_t st) {
+  if (C % 8) return refuse("layernorm: C must be a multiple of 8");
+  const int nb = mimir_norm_bwd_blocks();
+  if (norm_bwd_dispatch<false>(dy, x, gamma, mean, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
+  // partial rows are [2][C]: view as width 2C, then split
+  reduce_partials_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, nb, 2 * C, nullptr, partial,
+                                                                0);
+  // partial[0 .. 2C) now holds the totals (row 0 overwritten in place by its own sum)
+  reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, 1, C,
+                                                           static_cast<__nv_bfloat16*>(dgamma),
+                                                           nullptr, accumulate);
+  if (dbeta)
+    reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial + C, 1, C,
+                                                             static_cast<__nv_bfloat16*>(dbeta),
+                                                             nullptr, accumulate);
+  count_launch(dbeta ? 3 : 2);
+  return 0;
+}
+MIMIR_API int mimir_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd,
+                                const void* dres, void* dx, void* dgamma, float* partial, int rows,
+                                int C, int accumulate, cudaStream_t st) {
+  if (C % 8) return refuse("rmsnorm: C must be a multiple of 8");
+  const int nb = mimir_norm_bwd_blocks();
+  if (norm_bwd_dispatch<true>(dy, x, gamma, nullptr, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
+  reduce_partials_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, nb, 2 * C, nullptr, partial,
+                                                                0);
+  reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, 1, C,
+                                                           static_cast<__nv_bfloat16*>(dgamma),
+                                                           nullptr, accumulate);
+  count_launch(2);
+  return 0;
+}
+
+// out[N] (bf16) = column sums of x[rows, N]; partial: fp32 scratch of 64 * N floats.
+MIMIR_API int mimir_colsum(const void* x, int rows, int N, int ld, void* out, float* partial,
+                           int accumulate, cudaStream_t st) {
+  if (N % 8 || ld % 8) return refuse("colsum: N and ld must be multiples of 8");
+  const int parts = rows >= 64 * 8 ? 64 : 1;
+  dim3 grid(ceil_div(N, 256), parts);
+  colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld,
+                                              partial);
+  reduce_partials_kernel<<<ceil_div(N, 256), 256, 0, st>>>(partial, parts, N,
+                                                           static_cast<__nv_bfloat16*>(out), nullptr,
+                                                           accumulate);
+  count_launch(2);
+  return 0;
+}
+
+// Per-row loss and (optionally) in-place gradient; then mean_loss[0] = sum(loss) * loss_scale.
+MIMIR_API int mimir_cross_entropy(const void* logits, const void* target, float* loss_rows,
+                                  void* dlogits, float* mean_loss, int rows, int V, int ld,
+                                  float gscale, float loss_scale, cudaStream_t st) {
+  if (ld % 8) return refuse("cross entropy: row pitch must be a multiple of 8");
+  cross_entropy_kernel<<<rows, 512, 0, st>>>(static_cast<const __nv_bfloat16*>(logits),
+                                             static_cast<const int64_t*>(target), loss_rows,
+                                             static_cast<__nv_bfloat16*>(dlogits), V, ld, gscale,
+                                             error_word_dev());
+  count_launch();
+  if (mean_loss) {
+    sum_scale_kernel<<<1, 1024, 0, st>>>(loss_rows, rows, loss_scale, mean_loss);
+    count_launch();
+  }
+  return 0;
+}
+
+MIMIR_API int mimir_softmax_rows(const void* x, void* y, int rows, int C, int log, cudaStream_t st) {
+  softmax_rows_kernel<<<ceil_div(rows, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                                        static_cast<__nv_bfloat16*>(y), rows, C, log);
+  count_launch();
+  return 0;
+}
