@@ -86,6 +86,16 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("mimir_attention_fwd", I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, P)
     sig("mimir_attention_bwd", I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
         I, I, I, F, P)
+    PP = ctypes.POINTER(c_void_p)
+    sig("mimir_peer_alloc", I, L, PP)
+    sig("mimir_peer_free", I, P)
+    sig("mimir_ipc_export", I, P, ctypes.c_char_p)
+    sig("mimir_ipc_open", I, ctypes.c_char_p, PP)
+    sig("mimir_ipc_close", I, P)
+    sig("mimir_set_peer_wait_ms", None, L)
+    sig("mimir_dp_bucket", I, PP, PP, PP, P, P, P, P, P, P, L, L, L, L, F, F, F, F, I, I, I, I, I, P)
+    sig("mimir_dp_step_begin", I, P, P, I, P, I, P)
+    sig("mimir_peer_wait_probe", I, P, ctypes.c_uint, L, P, P)
     sig("mimir_adamw_flat", I, P, P, P, I, P, P, L, L, F, F, F, F, F, I, F, P, F, P, P)
 
 

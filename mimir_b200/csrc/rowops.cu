@@ -181,19 +181,27 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 }
 
 // Sums `nparts` partial rows [nparts][width] into bf16 (optionally accumulating).
-// `out_f32` may be row 0 of `partial` itself (each thread reads column c of
-// every row before it writes column c).
-__global__ void reduce_partials_kernel(const float* partial, int nparts, int width,
-                                       __nv_bfloat16* out, float* out_f32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= width) return;
+// Sums `nparts` partial rows [nparts][width] (fp32) column-wise.  Block = 32
+// columns x 8 row lanes.  Columns [0, split) go to out0, [split, width) to out1
+// (bf16, optionally accumulating), which finishes dgamma and dbeta in one launch.
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, int nparts, int width, int split,
+                       __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1, int accumulate) {
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * width + c];
-  if (out_f32) {
-    out_f32[c] = accumulate ? out_f32[c] + s : s;
-  } else {
-    if (accumulate) s += __bfloat162float(out[c]);
-    out[c] = __float2bfloat16_rn(s);
+  if (c < width)
+    for (int p = rl; p < nparts; p += 8) s += partial[static_cast<size_t>(p) * width + c];
+  red[rl][cl] = s;
+  __syncthreads();
+  if (rl == 0 && c < width) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r) s += red[r][cl];
+    __nv_bfloat16* o = c < split ? out0 + c : out1 + (c - split);
+    if (c >= split && !out1) return;
+    if (accumulate) s += __bfloat162float(*o);
+    *o = __float2bfloat16_rn(s);
   }
 }
 
@@ -381,7 +389,7 @@ MIMIR_API int mimir_rmsnorm_fwd(const void* x, const void* gamma, void* y, float
 }
 
 // Number of blocks (and rows of `partial`) the backward kernels use.
-MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 2; }
+MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 4; }
 
 // dx = dres + LN'(dy); dgamma/dbeta (bf16) written, or accumulated when accumulate != 0.
 // partial: fp32 scratch of mimir_norm_bwd_blocks() * 2 * C floats.
@@ -392,18 +400,11 @@ MIMIR_API int mimir_layernorm_bwd(const void* dy, const void* x, const void* gam
   if (C % 8) return refuse("layernorm: C must be a multiple of 8");
   const int nb = mimir_norm_bwd_blocks();
   if (norm_bwd_dispatch<false>(dy, x, gamma, mean, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
-  // partial rows are [2][C]: view as width 2C, then split
-  reduce_partials_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, nb, 2 * C, nullptr, partial,
-                                                                0);
-  // partial[0 .. 2C) now holds the totals (row 0 overwritten in place by its own sum)
-  reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, 1, C,
-                                                           static_cast<__nv_bfloat16*>(dgamma),
-                                                           nullptr, accumulate);
-  if (dbeta)
-    reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial + C, 1, C,
-                                                             static_cast<__nv_bfloat16*>(dbeta),
-                                                             nullptr, accumulate);
-  count_launch(dbeta ? 3 : 2);
+  // partial rows are [dgamma (C) | dbeta (C)]
+  reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
+                                                               static_cast<__nv_bfloat16*>(dgamma),
+                                                               static_cast<__nv_bfloat16*>(dbeta), accumulate);
+  count_launch();
   return 0;
 }
 MIMIR_API int mimir_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rstd,
@@ -412,12 +413,10 @@ MIMIR_API int mimir_rmsnorm_bwd(const void* dy, const void* x, const void* gamma
   if (C % 8) return refuse("rmsnorm: C must be a multiple of 8");
   const int nb = mimir_norm_bwd_blocks();
   if (norm_bwd_dispatch<true>(dy, x, gamma, nullptr, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
-  reduce_partials_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(partial, nb, 2 * C, nullptr, partial,
-                                                                0);
-  reduce_partials_kernel<<<ceil_div(C, 256), 256, 0, st>>>(partial, 1, C,
-                                                           static_cast<__nv_bfloat16*>(dgamma),
-                                                           nullptr, accumulate);
-  count_launch(2);
+  reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
+                                                               static_cast<__nv_bfloat16*>(dgamma), nullptr,
+                                                               accumulate);
+  count_launch();
   return 0;
 }
 
@@ -429,9 +428,9 @@ MIMIR_API int mimir_colsum(const void* x, int rows, int N, int ld, void* out, fl
   dim3 grid(ceil_div(N, 256), parts);
   colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld,
                                               partial);
-  reduce_partials_kernel<<<ceil_div(N, 256), 256, 0, st>>>(partial, parts, N,
-                                                           static_cast<__nv_bfloat16*>(out), nullptr,
-                                                           accumulate);
+  reduce_partials_kernel<<<ceil_div(N, 32), 256, 0, st>>>(partial, parts, N, N,
+                                                          static_cast<__nv_bfloat16*>(out), nullptr,
+                                                          accumulate);
   count_launch(2);
   return 0;
 }

@@ -37,6 +37,8 @@ class FusedTrainer:
     # The device work of one step, launched on the current stream.
     def _device_step(self) -> None:
         e = self.engine
+        if self.dp is not None:
+            self.dp.begin_step()
         e.forward()
         e.loss_and_dlogits()
         if self.dp is not None:

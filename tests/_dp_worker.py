@@ -1,0 +1,59 @@
+"""Worker for the multi-GPU data-parallel test (launched by torch.distributed.run)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    use_graph = os.environ.get("MIMIR_TEST_GRAPH", "1") == "1"
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from mimir_b200 import _native
+    from mimir_b200.models.gpt2 import GPT2Config, GPT2Engine
+    from mimir_b200.ops._util import check_error_word
+    from mimir_b200.parallel.dp import FusedDataParallel
+    from mimir_b200.train import FusedTrainer
+    _native.lib().mimir_set_device(local)
+    cfg = GPT2Config(n_layer=2, n_head=2, d_model=128, vocab=512, ctx=128)
+    Bl, T, steps = 2, 128, 6
+    gen = torch.Generator().manual_seed(7)
+    tok = torch.randint(0, cfg.vocab, (Bl * world, T), generator=gen)
+    tgt = torch.roll(tok, -1, 1)
+    dp = FusedDataParallel(rank, world, local)
+    eng = GPT2Engine(cfg, Bl, T, device=f"cuda:{local}", seed=5, flat_alloc=dp.alloc_shared)
+    dp.attach(eng)
+    tr = FusedTrainer(eng, lr=2e-3, dp=dp, use_graph=use_graph)
+    my = slice(rank * Bl, (rank + 1) * Bl)
+    losses = [tr.step(tok[my], tgt[my]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    err = check_error_word()
+    # replicas must be bit-identical
+    mine = eng.params.clone().view(torch.uint8).clone()
+    ref = mine.clone()
+    dist.broadcast(ref, 0)
+    identical = bool((mine == ref).all().item())
+    lt = torch.tensor(losses, device="cuda")
+    dist.all_reduce(lt)
+    mean_losses = (lt / world).tolist()
+    result = {"rank": rank, "err": err, "identical": identical, "losses": mean_losses}
+    if rank == 0:
+        # the same training on one device with the whole batch
+        e1 = GPT2Engine(cfg, Bl * world, T, device=f"cuda:{local}", seed=5)
+        t1 = FusedTrainer(e1, lr=2e-3, use_graph=False)
+        result["single"] = [t1.step(tok, tgt) for _ in range(steps)]
+        diff = (e1.params.float() - eng.params.float()).abs().max().item()
+        result["max_param_diff"] = diff
+    dp.close()
+    dist.destroy_process_group()
+    print("RESULT " + json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()
