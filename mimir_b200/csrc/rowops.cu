@@ -458,3 +458,63 @@ MIMIR_API int mimir_softmax_rows(const void* x, void* y, int rows, int C, int lo
   count_launch();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free column sums (declared in mimir_noalloc.h).
+// ---------------------------------------------------------------------------
+#include "mimir_noalloc.h"
+
+#include <mutex>
+
+namespace mimir {
+namespace {
+// Partial sums of one call: [64 row groups][MIMIR_COLSUM_NOALLOC_MAX_N] floats.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer
+// to pass to a kernel.
+static __device__ __align__(256) float g_colsum_scratch[64 * MIMIR_COLSUM_NOALLOC_MAX_N];
+
+constexpr int kNoAllocMaxDevices = 64;
+float* g_colsum_scratch_addr[kNoAllocMaxDevices] = {};
+std::mutex g_colsum_scratch_mu;
+
+// Device address of the scratch array on the current device (looked up once per device).
+float* colsum_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) {
+    refuse("colsum_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_colsum_scratch_mu);
+  if (!g_colsum_scratch_addr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_scratch);
+    if (e != cudaSuccess || !p) {
+      refuse("colsum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_colsum_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  return g_colsum_scratch_addr[dev];
+}
+}  // namespace
+}  // namespace mimir
+
+MIMIR_API int mimir_colsum_noalloc(const void* x, int rows, int N, int ld, void* out, int accumulate,
+                                   cudaStream_t st) {
+  if (rows <= 0 || N <= 0) return refuse("colsum_noalloc: empty input (%d x %d)", rows, N);
+  if (N % 8 || ld % 8) return refuse("colsum_noalloc: N and ld must be multiples of 8");
+  if (N > MIMIR_COLSUM_NOALLOC_MAX_N)
+    return refuse("colsum_noalloc: N = %d exceeds the built-in scratch (at most %d columns); "
+                  "use mimir_colsum with your own buffer",
+                  N, MIMIR_COLSUM_NOALLOC_MAX_N);
+  float* scratch = mimir::colsum_scratch_for_current_device();
+  if (!scratch) return -1;
+  const int parts = rows >= 64 * 8 ? 64 : 1;  // same split as mimir_colsum, so results agree bit for bit
+  dim3 grid(ceil_div(N, 256), parts);
+  colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld, scratch);
+  reduce_partials_kernel<<<ceil_div(N, 32), 256, 0, st>>>(scratch, parts, N, N,
+                                                          static_cast<__nv_bfloat16*>(out), nullptr,
+                                                          accumulate);
+  count_launch(2);
+  return cudaGetLastError() == cudaSuccess ? 0 : refuse("colsum_noalloc: launch failed");
+}
