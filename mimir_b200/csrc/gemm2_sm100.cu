@@ -1,0 +1,294 @@
+// bf16 GEMM with CTA pairs: tcgen05.mma.cta_group::2 computes a 256 x BN tile on
+// two SMs.  Each CTA of the pair stages its own 128 rows of A and its own half
+// (BN/2 columns) of B with plain TMA loads, so every byte of B is fetched once
+// per pair instead of once per SM; the accumulator (128 lanes x BN columns per
+// CTA) stays double buffered in TMEM.  The leader CTA (cluster rank 0) issues
+// the MMAs for both; its commits arrive on the barriers of both CTAs.
+//
+// Protocol (barriers live at the same shared-memory offset in both CTAs):
+//   full[s]    used in the leader only.  The leader's producer posts the byte
+//              count of BOTH CTAs' loads; each CTA's loads complete on it
+//              (the peer addresses it through its cluster-mapped address).
+//   empty[s]   in each CTA; the leader's tcgen05.commit arrives on both.
+//   tfull[a]   in each CTA; the leader's commit arrives on both, each CTA's
+//              epilogue warps then drain their own 128 accumulator rows.
+//   tempty[a]  in the leader; the 4 epilogue warps of each CTA arrive on it.
+// All waits are bounded; both CTAs meet at a cluster barrier before TMEM is freed.
+//
+// Same C ABI and epilogues as the 1-CTA kernel (gemm_sm100.cu), which remains
+// the path for small problems.
+#include "gemm_common.cuh"
+
+namespace mimir {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t nclusters_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a pair: data lands in this CTA, completion bytes go to `bar_cluster_addr`
+// (a cluster-mapped mbarrier address, the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* tm, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in every CTA of `cta_mask`
+// once all MMAs issued so far have finished.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+
+template <int BN, bool A_MN, bool B_MN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpi ep,
+                  int M, int N, int K, int splits, unsigned* err) {
+  constexpr int BNH = BN / 2;  // columns of B staged by each CTA
+  constexpr int A_BYTES = kBM * kBK * 2;
+  constexpr int B_BYTES = BNH * kBK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr uint32_t IDESC = make_idesc_bf16(2 * kBM, BN, A_MN, B_MN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int pair = static_cast<int>(cluster_id_x()), npairs = static_cast<int>(nclusters_x());
+  const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + BN - 1) / BN;
+  const int kb_total = (K + kBK - 1) / kBK;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  const int units = m_tiles * n_tiles * splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);  // 4 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers and TMEM exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = pair; u < units && ok; u += npairs) {
+        const int split = u % splits, tile = u / splits;
+        const int n_idx = tile % n_tiles, m_idx = tile / n_tiles;
+        const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+        const int m0 = m_idx * 2 * kBM + static_cast<int>(cta) * kBM;  // this CTA's A rows
+        const int n0 = n_idx * BN + static_cast<int>(cta) * BNH;       // this CTA's B columns
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
+          uint8_t* sA = smem + s * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          const uint32_t bar = map_to_cta(smem_u32(&full[s]), 0);  // the leader's barrier
+          if (cta == 0) mbar_arrive_expect_tx(&full[s], 2 * STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_2d_pair(sA + c * (kBK * 128), &tmA, bar, m0 + c * 64, kb * kBK);
+          } else {
+            tma_load_2d_pair(sA, &tmA, bar, kb * kBK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BNH / 64; ++c)
+              tma_load_2d_pair(sB + c * (kBK * 128), &tmB, bar, n0 + c * 64, kb * kBK);
+          } else {
+            tma_load_2d_pair(sB, &tmB, bar, kb * kBK, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta == 0) {
+      uint32_t it = 0, ti = 0;
+      bool ok = true;
+      for (int u = pair; u < units && ok; u += npairs, ++ti) {
+        const int split = u % splits;
+        const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+        const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, err)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          const uint64_t adesc = A_MN ? make_smem_desc_sw128(sA, kBK * 128, 1024)
+                                      : make_smem_desc_sw128(sA, 16, 1024);
+          const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sB, kBK * 128, 1024)
+                                      : make_smem_desc_sw128(sB, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t ad = adesc + (A_MN ? k * 128 : k * 2);
+            const uint64_t bd = bdesc + (B_MN ? k * 128 : k * 2);
+            umma_ss_pair(d_tmem, ad, bd, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s], 3);  // frees the stage in both CTAs
+        }
+        if (ok) umma_commit_pair(&tfull[acc], 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty[0]), 0);
+    const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty[1]), 0);
+    uint32_t ti = 0;
+    for (int u = pair; u < units; u += npairs, ++ti) {
+      const int split = u % splits, tile = u / splits;
+      const int n_idx = tile % n_tiles, m_idx = tile / n_tiles;
+      const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, err)) break;
+      tc_fence_after();
+      const int row = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      drain_accumulator<BN>(ep, taddr, row, n_idx * BN, M, N, split);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody frees TMEM or exits while the peer may still signal it
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int STAGES>
+static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpi& ep, int M, int N, int K,
+                        int splits, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 1024 + 256;
+  auto kern = gemm2_bf16_kernel<BN, A_MN, B_MN, STAGES>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return refuse("cannot reserve %d bytes of shared memory", SMEM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = SMEM;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  const int units = ceil_div(M, 2 * kBM) * ceil_div(N, BN) * splits;
+  const int pairs = units < max_pairs ? units : max_pairs;
+  kern<<<2 * pairs, kGemmThreads, SMEM, stream>>>(tmA, tmB, ep, M, N, K, splits, error_word_dev());
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : refuse("gemm2 launch failed");
+}
+
+// Launches the CTA-pair kernel; called by mimir_gemm_bf16 when the problem is large enough.
+int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn, int b_mn,
+                     const GemmEpi& ep, int bn, int splits, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  uint64_t dims[2], strides[1];
+  uint32_t box[2];
+  if (a_mn) { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = kBK; }
+  else      { dims[0] = K; dims[1] = M; box[0] = kBK; box[1] = kBM; }
+  strides[0] = static_cast<uint64_t>(lda) * 2;
+  if (encode_tmap(&tmA, A, 2, 2, dims, strides, box, 3)) return -1;
+  if (b_mn) { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = kBK; }
+  else      { dims[0] = K; dims[1] = N; box[0] = kBK; box[1] = static_cast<uint32_t>(bn / 2); }
+  strides[0] = static_cast<uint64_t>(ldb) * 2;
+  if (encode_tmap(&tmB, B, 2, 2, dims, strides, box, 3)) return -1;
+#define MIMIR_GEMM2_CASE(BN_, ST_)                                                                       \
+  if (!a_mn && !b_mn) return launch_gemm2<BN_, false, false, ST_>(tmA, tmB, ep, M, N, K, splits, stream); \
+  if (!a_mn && b_mn) return launch_gemm2<BN_, false, true, ST_>(tmA, tmB, ep, M, N, K, splits, stream);   \
+  if (a_mn && b_mn) return launch_gemm2<BN_, true, true, ST_>(tmA, tmB, ep, M, N, K, splits, stream);     \
+  return launch_gemm2<BN_, true, false, ST_>(tmA, tmB, ep, M, N, K, splits, stream);
+  if (bn == 256) { MIMIR_GEMM2_CASE(256, 6) }
+  MIMIR_GEMM2_CASE(128, 8)
+#undef MIMIR_GEMM2_CASE
+}
+
+}  // namespace mimir

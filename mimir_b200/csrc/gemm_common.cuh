@@ -1,0 +1,130 @@
+// Pieces shared by the 1-CTA and the 2-CTA (cta_group::2) GEMM kernels: tile
+// constants, epilogue flags, the fused epilogue applied to 8 columns of a row.
+#pragma once
+#include "common.cuh"
+#include "runtime.h"
+
+namespace mimir {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kGemmThreads = 192;
+
+enum GemmFlags : int {
+  kOutF32 = 1,      // C is fp32 (default bf16)
+  kAccumulate = 2,  // C += result
+  kGelu = 4,        // C = gelu_tanh(acc + bias)
+  kResidual = 8,    // C = acc + bias + aux
+  kMulDGelu = 16,   // C = (acc) * gelu_tanh'(aux)
+  kWritePre = 32,   // aux_out = acc + bias (pre-activation), with kGelu
+};
+
+struct GemmEpi {
+  void* C;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;
+  __nv_bfloat16* aux_out;
+  float* partial;  // split-K workspace [splits][M][N] (fp32) or nullptr
+  int ldc, ldaux;
+  int flags;
+  float alpha;
+};
+
+// Applies the fused epilogue to 8 consecutive columns of one row and stores them.
+__device__ __forceinline__ void epilogue_store8(const GemmEpi& ep, float (&v)[8], int row, int col) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
+  if (ep.bias) {
+    uint4 b = *reinterpret_cast<const uint4*>(ep.bias + col);
+    float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
+           b3 = unpack_bf16x2(b.w);
+    v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
+    v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
+  }
+  if (ep.flags & (kResidual | kMulDGelu)) {
+    uint4 a = *reinterpret_cast<const uint4*>(ep.aux + static_cast<size_t>(row) * ep.ldaux + col);
+    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z),
+           a3 = unpack_bf16x2(a.w);
+    float x[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
+    if (ep.flags & kMulDGelu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= gelu_tanh_grad(x[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += x[j];
+    }
+  }
+  if (ep.flags & kGelu) {
+    if (ep.flags & kWritePre) {
+      uint4 o;
+      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+      o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ldaux + col) = o;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+  }
+  if (ep.flags & kOutF32) {
+    float* c = reinterpret_cast<float*>(ep.C) + static_cast<size_t>(row) * ep.ldc + col;
+    float4 lo = make_float4(v[0], v[1], v[2], v[3]), hi = make_float4(v[4], v[5], v[6], v[7]);
+    if (ep.flags & kAccumulate) {
+      float4 plo = *reinterpret_cast<float4*>(c), phi = *reinterpret_cast<float4*>(c + 4);
+      lo.x += plo.x; lo.y += plo.y; lo.z += plo.z; lo.w += plo.w;
+      hi.x += phi.x; hi.y += phi.y; hi.z += phi.z; hi.w += phi.w;
+    }
+    *reinterpret_cast<float4*>(c) = lo;
+    *reinterpret_cast<float4*>(c + 4) = hi;
+  } else {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(ep.C) + static_cast<size_t>(row) * ep.ldc + col;
+    if (ep.flags & kAccumulate) {
+      uint4 p = *reinterpret_cast<uint4*>(c);
+      float2 p0 = unpack_bf16x2(p.x), p1 = unpack_bf16x2(p.y), p2 = unpack_bf16x2(p.z),
+             p3 = unpack_bf16x2(p.w);
+      v[0] += p0.x; v[1] += p0.y; v[2] += p1.x; v[3] += p1.y;
+      v[4] += p2.x; v[5] += p2.y; v[6] += p3.x; v[7] += p3.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(c) = o;
+  }
+}
+
+
+// Drains one accumulator buffer (128 lanes x BN columns of fp32 in TMEM) through
+// the fused epilogue.  `row` is this thread's output row, taddr its TMEM address
+// (lane quadrant included), col_base the first output column of the tile.
+template <int BN>
+__device__ __forceinline__ void drain_accumulator(const GemmEpi& ep, uint32_t taddr, int row, int col_base,
+                                                  int M, int N, int split) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = col_base + c * 32;
+    if (row < M) {
+      if (ep.partial) {
+        float* dst = ep.partial + (static_cast<size_t>(split) * M + row) * N + col0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          if (col0 + j < N)
+            *reinterpret_cast<float4*>(dst + j) =
+                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                            __uint_as_float(r[j + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          if (col0 + j < N) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+            epilogue_store8(ep, v, row, col0 + j);
+          }
+        }
+      }
+    }
+  }
+}
+
+}  // namespace mimir

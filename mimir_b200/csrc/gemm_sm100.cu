@@ -15,94 +15,9 @@
 // epilogue kernel (backend/internal/gen/gen.go:973-1037, gemm.go:55-128,
 // internal/sched/fuse.go:312-325: bias / activation / residual epilogues, and
 // :293-302: transposed and batch-summed products).
-#include "common.cuh"
-#include "runtime.h"
+#include "gemm_common.cuh"
 
 namespace mimir {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;  // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kGemmThreads = 192;
-
-enum GemmFlags : int {
-  kOutF32 = 1,      // C is fp32 (default bf16)
-  kAccumulate = 2,  // C += result
-  kGelu = 4,        // C = gelu_tanh(acc + bias)
-  kResidual = 8,    // C = acc + bias + aux
-  kMulDGelu = 16,   // C = (acc) * gelu_tanh'(aux)
-  kWritePre = 32,   // aux_out = acc + bias (pre-activation), with kGelu
-};
-
-struct GemmEpi {
-  void* C;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* aux;
-  __nv_bfloat16* aux_out;
-  float* partial;  // split-K workspace [splits][M][N] (fp32) or nullptr
-  int ldc, ldaux;
-  int flags;
-  float alpha;
-};
-
-// Applies the fused epilogue to 8 consecutive columns of one row and stores them.
-__device__ __forceinline__ void epilogue_store8(const GemmEpi& ep, float (&v)[8], int row, int col) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
-  if (ep.bias) {
-    uint4 b = *reinterpret_cast<const uint4*>(ep.bias + col);
-    float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
-           b3 = unpack_bf16x2(b.w);
-    v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
-    v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
-  }
-  if (ep.flags & (kResidual | kMulDGelu)) {
-    uint4 a = *reinterpret_cast<const uint4*>(ep.aux + static_cast<size_t>(row) * ep.ldaux + col);
-    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z),
-           a3 = unpack_bf16x2(a.w);
-    float x[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
-    if (ep.flags & kMulDGelu) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] *= gelu_tanh_grad(x[j]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] += x[j];
-    }
-  }
-  if (ep.flags & kGelu) {
-    if (ep.flags & kWritePre) {
-      uint4 o;
-      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-      o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ldaux + col) = o;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-  }
-  if (ep.flags & kOutF32) {
-    float* c = reinterpret_cast<float*>(ep.C) + static_cast<size_t>(row) * ep.ldc + col;
-    float4 lo = make_float4(v[0], v[1], v[2], v[3]), hi = make_float4(v[4], v[5], v[6], v[7]);
-    if (ep.flags & kAccumulate) {
-      float4 plo = *reinterpret_cast<float4*>(c), phi = *reinterpret_cast<float4*>(c + 4);
-      lo.x += plo.x; lo.y += plo.y; lo.z += plo.z; lo.w += plo.w;
-      hi.x += phi.x; hi.y += phi.y; hi.z += phi.z; hi.w += phi.w;
-    }
-    *reinterpret_cast<float4*>(c) = lo;
-    *reinterpret_cast<float4*>(c + 4) = hi;
-  } else {
-    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(ep.C) + static_cast<size_t>(row) * ep.ldc + col;
-    if (ep.flags & kAccumulate) {
-      uint4 p = *reinterpret_cast<uint4*>(c);
-      float2 p0 = unpack_bf16x2(p.x), p1 = unpack_bf16x2(p.y), p2 = unpack_bf16x2(p.z),
-             p3 = unpack_bf16x2(p.w);
-      v[0] += p0.x; v[1] += p0.y; v[2] += p1.x; v[3] += p1.y;
-      v[4] += p2.x; v[5] += p2.y; v[6] += p3.x; v[7] += p3.y;
-    }
-    uint4 o;
-    o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-    o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-    *reinterpret_cast<uint4*>(c) = o;
-  }
-}
 
 template <int BN, bool A_MN, bool B_MN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -231,34 +146,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = m_idx * kBM + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n_idx * BN + c * 32;
-        if (row < M) {
-          if (ep.partial) {
-            float* dst = ep.partial + (static_cast<size_t>(split) * M + row) * N + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (col0 + j < N)
-                *reinterpret_cast<float4*>(dst + j) =
-                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j < N) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                epilogue_store8(ep, v, row, col0 + j);
-              }
-            }
-          }
-        }
-      }
+      drain_accumulator<BN>(ep, taddr, row, n_idx * BN, M, N, split);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -308,6 +196,9 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("gemm launch failed");
 }
 
+int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn, int b_mn,
+                     const GemmEpi& ep, int bn, int splits, cudaStream_t stream);
+
 }  // namespace mimir
 
 using namespace mimir;
@@ -340,6 +231,9 @@ MIMIR_API int mimir_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if ((flags & kWritePre) && !aux_out) return refuse("gemm: aux_out missing");
 
   const int nsm = sm_count();
+  // bn_hint + 1000 forces the CTA-pair kernel, + 2000 forces the single-CTA kernel
+  int pair_mode = bn_hint >= 2000 ? 2 : bn_hint >= 1000 ? 1 : 0;
+  bn_hint %= 1000;
   int bn = bn_hint;
   if (bn != 64 && bn != 128 && bn != 256) {
     // Prefer the wide tile unless its wave quantisation is clearly worse.
@@ -370,6 +264,33 @@ MIMIR_API int mimir_gemm_bf16(const void* A, const void* B, void* C, int M, int 
                      workspace_bytes < static_cast<long long>(splits) * M * N * 4))
     splits = 1;
 
+  GemmEpi ep;
+  ep.C = C;
+  ep.bias = static_cast<const __nv_bfloat16*>(bias);
+  ep.aux = static_cast<const __nv_bfloat16*>(aux);
+  ep.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  ep.partial = splits > 1 ? static_cast<float*>(workspace) : nullptr;
+  ep.ldc = ldc;
+  ep.ldaux = ldaux;
+  ep.flags = flags;
+  ep.alpha = alpha;
+
+  bool use_pair = pair_mode == 1;
+  if (pair_mode == 0) {
+    // pairs pay off once there are enough 256-row tiles to fill the machine
+    const long long pair_units = static_cast<long long>(ceil_div(M, 2 * kBM)) * ceil_div(N, bn < 128 ? 128 : bn) * splits;
+    use_pair = bn >= 128 && M >= 2 * kBM && pair_units >= nsm / 4;
+  }
+  if (use_pair && bn >= 128) {
+    if (launch_gemm_pair(A, B, M, N, K, lda, ldb, a_mn, b_mn, ep, bn, splits, stream)) return -1;
+    if (splits > 1) {
+      const size_t n = static_cast<size_t>(M) * (N / 8);
+      gemm_splitk_reduce_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(ep, M, N, splits);
+      count_launch();
+    }
+    return 0;
+  }
+
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[2], strides[1];
@@ -383,17 +304,6 @@ MIMIR_API int mimir_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     strides[0] = static_cast<uint64_t>(ldb) * 2;
     if (encode_tmap(&tmB, B, 2, 2, dims, strides, box, 3)) return -1;
   }
-  GemmEpi ep;
-  ep.C = C;
-  ep.bias = static_cast<const __nv_bfloat16*>(bias);
-  ep.aux = static_cast<const __nv_bfloat16*>(aux);
-  ep.aux_out = static_cast<__nv_bfloat16*>(aux_out);
-  ep.partial = splits > 1 ? static_cast<float*>(workspace) : nullptr;
-  ep.ldc = ldc;
-  ep.ldaux = ldaux;
-  ep.flags = flags;
-  ep.alpha = alpha;
-
   int rc;
 #define MIMIR_GEMM_CASE(BN_, ST_)                                                             \
   if (!a_mn && !b_mn) rc = launch_gemm<BN_, false, false, ST_>(tmA, tmB, ep, M, N, K, splits, stream); \

@@ -1,0 +1,130 @@
+"""Micro-benchmarks of the hand-written kernels against the library baselines.
+
+    python -m mimir_b200.utils.kernel_bench gemm --m 8192 --n 2304 --k 768
+    python -m mimir_b200.utils.kernel_bench attention --b 8 --t 1024 --h 12 --d 64
+
+Times with CUDA events after warm-up; between timed iterations an L2-sized
+buffer is overwritten so that no operand is served from a warm L2.  Prints one
+JSON line per case with achieved TFLOP/s and the fraction of the measured cuBLAS
+bf16 peak recorded in ``MEASURED_PEAKS.json`` (if present).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+def time_ms(fn, iters: int, flush: torch.Tensor | None) -> float:
+    """Mean device time of ``fn``; all iterations are queued before the one sync, so
+    host launch latency never shows up as idle time between the two events."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        evs.append((e0, e1))
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs) / iters
+
+
+def bench_gemm(a):
+    from ..ops.gemm import gemm
+    M, N, K = a.m, a.n, a.k
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if a.flush else None
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    dx = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    dw = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+    peak = _peaks().get("bf16_tflops")
+    cases = {
+        "nt_forward": (lambda: gemm(x, w, out=out, bn=a.bn), lambda: torch.matmul(x, w.t(), out=out)),
+        "nn_dgrad": (lambda: gemm(dy, w, b_mn=True, out=dx, bn=a.bn), lambda: torch.matmul(dy, w, out=dx)),
+        "tn_wgrad": (lambda: gemm(dy, x, a_mn=True, b_mn=True, out=dw, bn=a.bn),
+                     lambda: torch.matmul(dy.t(), x, out=dw)),
+    }
+    for name, (ours, lib) in cases.items():
+        if a.only and a.only != name:
+            continue
+        t = time_ms(ours, a.iters, flush)
+        rec = {"kernel": "gemm_bf16", "case": name, "M": M, "N": N, "K": K, "ms": t,
+               "tflops": 2.0 * M * N * K / t / 1e9}
+        if peak:
+            rec["frac_of_measured_cublas_peak"] = rec["tflops"] / peak
+        if not a.no_baseline:
+            tl = time_ms(lib, a.iters, flush)
+            rec["cublas_ms"] = tl
+            rec["cublas_tflops"] = 2.0 * M * N * K / tl / 1e9
+        print(json.dumps(rec), flush=True)
+
+
+def bench_attention(a):
+    from ..ops.attention import attention_bwd, attention_fwd
+    B, T, H, D = a.b, a.t, a.h, a.d
+    qkv = torch.randn(B, T, 3, H, D, device="cuda").bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    out = torch.empty(B, T, H, D, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn_like(out)
+    lse = torch.empty(B, H, T, device="cuda")
+    dsum = torch.empty(B, H, T, device="cuda")
+    dqkv = torch.empty_like(qkv)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if a.flush else None
+    flops_fwd = 4.0 * B * H * T * T * D / 2  # causal
+    t = time_ms(lambda: attention_fwd(q, k, v, out, lse, causal=True), a.iters, flush)
+    print(json.dumps({"kernel": "attention_fwd", "B": B, "T": T, "H": H, "D": D, "ms": t,
+                      "tflops": flops_fwd / t / 1e9}), flush=True)
+    t = time_ms(lambda: attention_bwd(q, k, v, out, do, lse, dsum, dqkv[:, :, 0], dqkv[:, :, 1],
+                                      dqkv[:, :, 2], causal=True), a.iters, flush)
+    print(json.dumps({"kernel": "attention_bwd", "B": B, "T": T, "H": H, "D": D, "ms": t,
+                      "tflops": 2.5 * flops_fwd / t / 1e9}), flush=True)
+    if not a.no_baseline:
+        qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
+        t = time_ms(lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True),
+                    a.iters, flush)
+        print(json.dumps({"kernel": "torch_sdpa_fwd", "ms": t, "tflops": flops_fwd / t / 1e9}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=8192)
+    g.add_argument("--n", type=int, default=2304)
+    g.add_argument("--k", type=int, default=768)
+    g.add_argument("--bn", type=int, default=0)
+    g.add_argument("--only", default="")
+    t = sub.add_parser("attention")
+    t.add_argument("--b", type=int, default=8)
+    t.add_argument("--t", type=int, default=1024)
+    t.add_argument("--h", type=int, default=12)
+    t.add_argument("--d", type=int, default=64)
+    for p in (g, t):
+        p.add_argument("--iters", type=int, default=10)
+        p.add_argument("--flush", action="store_true")
+        p.add_argument("--no-baseline", action="store_true")
+    a = ap.parse_args()
+    {"gemm": bench_gemm, "attention": bench_attention}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    main()

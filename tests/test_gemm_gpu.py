@@ -73,3 +73,40 @@ def test_gemm_split_k(splits):
     out = gemm(a, b, a_mn=True, b_mn=True, splits=splits)
     assert check_error_word() == 0
     _check(out, _ref(a, b, True, True), K)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [
+    (256, 256, 64, 1256), (512, 384, 192, 1128), (1000, 776, 136, 1256), (4096, 768, 768, 1256),
+    (392, 520, 72, 1128), (2048, 2304, 768, 1256),
+])
+def test_gemm_cta_pair_layouts(M, N, K, bn, a_mn, b_mn):
+    """The cta_group::2 kernel (forced with bn + 1000) against the fp32 product."""
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte row pitch")
+    torch.manual_seed(M + N + K)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    assert check_error_word() == 0
+    _check(out, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_gemm_cta_pair_split_k_and_epilogue():
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    torch.manual_seed(5)
+    M, N, K = 512, 256, 2048
+    a = torch.randn(K, M, device="cuda").bfloat16()
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    out = gemm(a, b, a_mn=True, b_mn=True, splits=4, bn=1256)
+    _check(out, _ref(a, b, True, True), K)
+    x = torch.randn(M, 256, device="cuda").bfloat16()
+    w = (torch.randn(N, 256, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    out = gemm(x, w, bias=bias, residual=True, aux=res, bn=1128)
+    _check(out, x.float() @ w.float().t() + bias.float() + res.float(), 256)
+    assert check_error_word() == 0
