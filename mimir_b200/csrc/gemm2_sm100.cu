@@ -91,8 +91,9 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
 
 template <int BN, bool A_MN, bool B_MN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpi ep,
-                  int M, int N, int K, int splits, unsigned* err) {
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, GemmEpi ep,
+                  int M, int N, int K, int splits, int tma_out, unsigned* err) {
   constexpr int BNH = BN / 2;  // columns of B staged by each CTA
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BNH * kBK * 2;
@@ -103,7 +104,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* out_ring = smem + STAGES * STAGE_BYTES;  // 4 warps x 2 x 4 KiB, for TMA stores
+  uint64_t* full = reinterpret_cast<uint64_t*>(out_ring + 4 * 2 * 4096);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -214,20 +216,26 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int q = warp & 3;
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty[0]), 0);
     const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty[1]), 0);
-    uint32_t ti = 0;
+    uint32_t ti = 0, ring = 0;
+    uint8_t* wbuf = out_ring + (warp - 2) * 2 * 4096;
     for (int u = pair; u < units; u += npairs, ++ti) {
       const int split = u % splits, tile = u / splits;
       const int n_idx = tile % n_tiles, m_idx = tile / n_tiles;
       const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, err)) break;
       tc_fence_after();
-      const int row = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32 + lane;
+      const int row0 = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32;
+      const int row = row0 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      drain_accumulator<BN>(ep, taddr, row, n_idx * BN, M, N, split);
+      if (tma_out)
+        drain_accumulator_tma<BN>(ep, &tmC, &tmPre, taddr, row, row0, n_idx * BN, M, N, wbuf, ring, lane);
+      else
+        drain_accumulator<BN>(ep, taddr, row, n_idx * BN, M, N, split);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
     }
+    if (lane == 0) bulk_wait_group_read<0>();  // the ring must outlive its last store's reads
   }
 
   tc_fence_before();
@@ -241,9 +249,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 template <int BN, bool A_MN, bool B_MN, int STAGES>
-static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpi& ep, int M, int N, int K,
+static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                        const CUtensorMap& tmPre, int tma_out, const GemmEpi& ep, int M, int N, int K,
                         int splits, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 1024 + 256;
+  constexpr int SMEM = STAGES * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 4 * 2 * 4096 + 1024 + 256;
   auto kern = gemm2_bf16_kernel<BN, A_MN, B_MN, STAGES>;
   static int max_pairs = 0;
   if (max_pairs == 0) {
@@ -262,7 +271,8 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
   }
   const int units = ceil_div(M, 2 * kBM) * ceil_div(N, BN) * splits;
   const int pairs = units < max_pairs ? units : max_pairs;
-  kern<<<2 * pairs, kGemmThreads, SMEM, stream>>>(tmA, tmB, ep, M, N, K, splits, error_word_dev());
+  kern<<<2 * pairs, kGemmThreads, SMEM, stream>>>(tmA, tmB, tmC, tmPre, ep, M, N, K, splits, tma_out,
+                                                  error_word_dev());
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("gemm2 launch failed");
 }
@@ -281,13 +291,25 @@ int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda,
   else      { dims[0] = K; dims[1] = N; box[0] = kBK; box[1] = static_cast<uint32_t>(bn / 2); }
   strides[0] = static_cast<uint64_t>(ldb) * 2;
   if (encode_tmap(&tmB, B, 2, 2, dims, strides, box, 3)) return -1;
+  // bf16 outputs without accumulation leave through TMA stores of 32 x 64 sub-tiles
+  CUtensorMap tmC = tmA, tmPre = tmA;
+  const int tma_out = !(ep.flags & (kOutF32 | kAccumulate)) && !ep.partial;
+  if (tma_out) {
+    dims[0] = N; dims[1] = M; box[0] = 64; box[1] = 32;
+    strides[0] = static_cast<uint64_t>(ep.ldc) * 2;
+    if (encode_tmap(&tmC, ep.C, 2, 2, dims, strides, box, 3)) return -1;
+    if ((ep.flags & kGelu) && (ep.flags & kWritePre)) {
+      strides[0] = static_cast<uint64_t>(ep.ldaux) * 2;
+      if (encode_tmap(&tmPre, ep.aux_out, 2, 2, dims, strides, box, 3)) return -1;
+    }
+  }
 #define MIMIR_GEMM2_CASE(BN_, ST_)                                                                       \
-  if (!a_mn && !b_mn) return launch_gemm2<BN_, false, false, ST_>(tmA, tmB, ep, M, N, K, splits, stream); \
-  if (!a_mn && b_mn) return launch_gemm2<BN_, false, true, ST_>(tmA, tmB, ep, M, N, K, splits, stream);   \
-  if (a_mn && b_mn) return launch_gemm2<BN_, true, true, ST_>(tmA, tmB, ep, M, N, K, splits, stream);     \
-  return launch_gemm2<BN_, true, false, ST_>(tmA, tmB, ep, M, N, K, splits, stream);
-  if (bn == 256) { MIMIR_GEMM2_CASE(256, 6) }
-  MIMIR_GEMM2_CASE(128, 8)
+  if (!a_mn && !b_mn) return launch_gemm2<BN_, false, false, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream); \
+  if (!a_mn && b_mn) return launch_gemm2<BN_, false, true, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream);   \
+  if (a_mn && b_mn) return launch_gemm2<BN_, true, true, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream);     \
+  return launch_gemm2<BN_, true, false, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream);
+  if (bn == 256) { MIMIR_GEMM2_CASE(256, 5) }
+  MIMIR_GEMM2_CASE(128, 7)
 #undef MIMIR_GEMM2_CASE
 }
 

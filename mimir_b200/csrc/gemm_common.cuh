@@ -91,6 +91,93 @@ __device__ __forceinline__ void epilogue_store8(const GemmEpi& ep, float (&v)[8]
 }
 
 
+// Epilogue arithmetic on 8 consecutive columns of one row, without the store:
+// v becomes the output values; pre (if the GELU side output is on) the pre-activation.
+__device__ __forceinline__ void epilogue_math8(const GemmEpi& ep, float (&v)[8], float (&pre)[8], int row,
+                                               int col) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] *= ep.alpha;
+  if (ep.bias) {
+    uint4 b = *reinterpret_cast<const uint4*>(ep.bias + col);
+    float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+    v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
+    v[4] += b2.x; v[5] += b2.y; v[6] += b3.x; v[7] += b3.y;
+  }
+  if (ep.flags & (kResidual | kMulDGelu)) {
+    uint4 a = *reinterpret_cast<const uint4*>(ep.aux + static_cast<size_t>(row) * ep.ldaux + col);
+    float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    float x[8] = {a0.x, a0.y, a1.x, a1.y, a2.x, a2.y, a3.x, a3.y};
+    if (ep.flags & kMulDGelu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= gelu_tanh_grad(x[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += x[j];
+    }
+  }
+  if (ep.flags & kGelu) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { pre[j] = v[j]; v[j] = gelu_tanh(v[j]); }
+  }
+}
+
+// Stages a [32 rows x 64 columns] bf16 sub-tile (one row per lane, 8 x 16-byte units
+// in pk) into a 128-byte-swizzled shared buffer and stores it with TMA.  Lane 0
+// owns the bulk groups; at most one earlier store may still be reading the ring.
+__device__ __forceinline__ void stage_and_store(const CUtensorMap* tm, uint8_t* wbuf, uint32_t& ring,
+                                                const uint32_t (&pk)[32], int lane, int c0, int c1) {
+  uint8_t* buf = wbuf + (ring & 1) * 4096;
+  if (lane == 0) bulk_wait_group_read<1>();
+  __syncwarp();
+  const uint32_t base = smem_u32(buf) + lane * 128;
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+    st_shared_v4(base + ((u ^ (lane & 7)) << 4), pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tm, buf, c0, c1);
+    bulk_commit_group();
+  }
+  ++ring;
+}
+
+// Drains an accumulator through the fused epilogue into TMA stores (bf16 outputs,
+// no accumulate).  row = this lane's output row, row0 = the warp's first row.
+template <int BN>
+__device__ __forceinline__ void drain_accumulator_tma(const GemmEpi& ep, const CUtensorMap* tmC,
+                                                      const CUtensorMap* tmPre, uint32_t taddr, int row,
+                                                      int row0, int col_base, int M, int N, uint8_t* wbuf,
+                                                      uint32_t& ring, int lane) {
+  const bool write_pre = (ep.flags & kGelu) && (ep.flags & kWritePre);
+#pragma unroll 1
+  for (int c = 0; c < BN / 64; ++c) {
+    uint32_t r0[32], r1[32];
+    tmem_ld32(taddr + c * 64, r0);
+    tmem_ld32(taddr + c * 64 + 32, r1);
+    tmem_ld_wait();
+    const int col0 = col_base + c * 64;
+    if (col0 >= N || row0 >= M) continue;  // uniform over the warp
+    uint32_t pk[32], pp[32];
+    const bool live = row < M;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float v[8], pre[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
+      if (live && col0 + g * 8 < N) epilogue_math8(ep, v, pre, row, col0 + g * 8);
+      pk[4 * g] = pack_bf16x2(v[0], v[1]); pk[4 * g + 1] = pack_bf16x2(v[2], v[3]);
+      pk[4 * g + 2] = pack_bf16x2(v[4], v[5]); pk[4 * g + 3] = pack_bf16x2(v[6], v[7]);
+      if (write_pre) {
+        pp[4 * g] = pack_bf16x2(pre[0], pre[1]); pp[4 * g + 1] = pack_bf16x2(pre[2], pre[3]);
+        pp[4 * g + 2] = pack_bf16x2(pre[4], pre[5]); pp[4 * g + 3] = pack_bf16x2(pre[6], pre[7]);
+      }
+    }
+    if (write_pre) stage_and_store(tmPre, wbuf, ring, pp, lane, col0, row0);
+    stage_and_store(tmC, wbuf, ring, pk, lane, col0, row0);
+  }
+}
+
 // Drains one accumulator buffer (128 lanes x BN columns of fp32 in TMEM) through
 // the fused epilogue.  `row` is this thread's output row, taddr its TMEM address
 // (lane quadrant included), col_base the first output column of the tile.

@@ -110,3 +110,33 @@ def test_gemm_cta_pair_split_k_and_epilogue():
     out = gemm(x, w, bias=bias, residual=True, aux=res, bn=1128)
     _check(out, x.float() @ w.float().t() + bias.float() + res.float(), 256)
     assert check_error_word() == 0
+
+
+@pytest.mark.parametrize("bn", [1256, 1128])
+def test_gemm_cta_pair_tma_store_epilogues(bn):
+    """bf16 outputs of the pair kernel leave through TMA stores, with every fused epilogue."""
+    from mimir_b200.ops import gemm
+    from mimir_b200.ops._util import check_error_word
+    torch.manual_seed(9)
+    M, N, K = 1000, 712, 256  # ragged in both directions
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    z = a.float() @ w.float().t() + bias.float()
+    pre = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, w, bias=bias, gelu=True, aux_out=pre, bn=bn)
+    _check(pre, z, K)
+    _check(out, torch.nn.functional.gelu(z, approximate="tanh"), K)
+    out = gemm(a, w, bias=bias, residual=True, aux=res, bn=bn)
+    _check(out, z + res.float(), K)
+    zz = res.float().clone().requires_grad_(True)
+    torch.nn.functional.gelu(zz, approximate="tanh").sum().backward()
+    out = gemm(a, w, mul_dgelu=True, aux=res, bn=bn)
+    _check(out, (a.float() @ w.float().t()) * zz.grad, K)
+    # a strided output (columns of a wider matrix) must leave its neighbours alone
+    wide = torch.full((M, 2 * N), 3.0, device="cuda", dtype=torch.bfloat16)
+    gemm(a, w, out=wide[:, :N], bn=bn)
+    _check(wide[:, :N], a.float() @ w.float().t(), K)
+    assert (wide[:, N:] == 3.0).all()
+    assert check_error_word() == 0
