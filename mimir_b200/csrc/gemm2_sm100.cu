@@ -89,11 +89,16 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
       : "memory");
 }
 
+// warp 0 TMA, warp 1 MMA, warps 2..9 epilogue: two warps per TMEM lane quadrant, each
+// draining half of the tile's columns, so that every scheduler holds two epilogue warps.
+constexpr int kGemm2Threads = 320;
+constexpr int kEpiWarps = 8;
+
 template <int BN, bool A_MN, bool B_MN, int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, GemmEpi ep,
-                  int M, int N, int K, int splits, int tma_out, unsigned* err) {
+                  int M, int N, int K, int splits, int tma_out, unsigned long long* prof, unsigned* err) {
   constexpr int BNH = BN / 2;  // columns of B staged by each CTA
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BNH * kBK * 2;
@@ -104,8 +109,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* out_ring = smem + STAGES * STAGE_BYTES;  // 4 warps x 2 x 4 KiB, for TMA stores
-  uint64_t* full = reinterpret_cast<uint64_t*>(out_ring + 4 * 2 * 4096);
+  uint8_t* out_ring = smem + STAGES * STAGE_BYTES;  // 8 warps x 2 x 4 KiB, for TMA stores
+  uint64_t* full = reinterpret_cast<uint64_t*>(out_ring + kEpiWarps * 2 * 4096);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -127,7 +132,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 8);  // 4 epilogue warps of each CTA
+      mbar_init(&tempty[a], 2 * kEpiWarps);  // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -183,17 +188,23 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0 && cta == 0) {
       uint32_t it = 0, ti = 0;
       bool ok = true;
+      // optional diagnostics of pair 0: cycles the MMA thread spent waiting
+      long long t_begin = clock64(), w_acc = 0, w_full = 0;
       for (int u = pair; u < units && ok; u += npairs, ++ti) {
         const int split = u % splits;
         const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
         const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
+        long long t0 = clock64();
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, err)) break;
+        w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
+          t0 = clock64();
           if (!mbar_wait(&full[s], ph, abort_flag, err)) { ok = false; break; }
+          w_full += clock64() - t0;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sB = sA + A_BYTES;
@@ -211,29 +222,45 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         if (ok) umma_commit_pair(&tfull[acc], 3);
       }
+      if (prof && pair == 0) {
+        prof[0] = clock64() - t_begin;  // MMA thread: first wait to last issue
+        prof[1] = w_acc;                // ... waiting for a free accumulator
+        prof[2] = w_full;               // ... waiting for operands
+        prof[3] = ti;
+      }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;           // TMEM lane quadrant
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty[0]), 0);
     const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty[1]), 0);
     uint32_t ti = 0, ring = 0;
     uint8_t* wbuf = out_ring + (warp - 2) * 2 * 4096;
+    long long e_wait = 0, e_work = 0;
     for (int u = pair; u < units; u += npairs, ++ti) {
       const int split = u % splits, tile = u / splits;
       const int n_idx = tile % n_tiles, m_idx = tile / n_tiles;
       const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
+      const long long t0 = clock64();
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, err)) break;
+      const long long t1 = clock64();
+      e_wait += t1 - t0;
       tc_fence_after();
       const int row0 = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32;
-      const int row = row0 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * BN + half * (BN / 2) + (static_cast<uint32_t>(q * 32) << 16);
+      const int col_base = n_idx * BN + half * (BN / 2);
       if (tma_out)
-        drain_accumulator_tma<BN>(ep, &tmC, &tmPre, taddr, row, row0, n_idx * BN, M, N, wbuf, ring, lane);
+        drain_accumulator_tma<BN / 128>(ep, &tmC, &tmPre, taddr, row0, col_base, M, N, wbuf, ring, lane);
       else
-        drain_accumulator<BN>(ep, taddr, row, n_idx * BN, M, N, split);
+        drain_accumulator<BN / 2>(ep, taddr, row0 + lane, col_base, M, N, split);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
+      e_work += clock64() - t1;
+    }
+    if (prof && pair == 0 && cta == 0 && warp == 2 && lane == 0) {
+      prof[4] = e_wait;  // epilogue warp: waiting for a finished accumulator
+      prof[5] = e_work;  // ... draining its share of it
     }
     if (lane == 0) bulk_wait_group_read<0>();  // the ring must outlive its last store's reads
   }
@@ -248,11 +275,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
+// Device buffer of 8 counters that pair 0 fills when set (see mimir_gemm_set_profile_buffer).
+static unsigned long long* g_gemm_prof = nullptr;
+
 template <int BN, bool A_MN, bool B_MN, int STAGES>
 static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                         const CUtensorMap& tmPre, int tma_out, const GemmEpi& ep, int M, int N, int K,
                         int splits, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + 4 * 2 * 4096 + 1024 + 256;
+  constexpr int SMEM = STAGES * (kBM * kBK * 2 + (BN / 2) * kBK * 2) + kEpiWarps * 2 * 4096 + 1024 + 256;
   auto kern = gemm2_bf16_kernel<BN, A_MN, B_MN, STAGES>;
   static int max_pairs = 0;
   if (max_pairs == 0) {
@@ -260,7 +290,7 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
       return refuse("cannot reserve %d bytes of shared memory", SMEM);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (sm_count() / 2));
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(kGemm2Threads);
     cfg.dynamicSmemBytes = SMEM;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
@@ -271,8 +301,8 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   }
   const int units = ceil_div(M, 2 * kBM) * ceil_div(N, BN) * splits;
   const int pairs = units < max_pairs ? units : max_pairs;
-  kern<<<2 * pairs, kGemmThreads, SMEM, stream>>>(tmA, tmB, tmC, tmPre, ep, M, N, K, splits, tma_out,
-                                                  error_word_dev());
+  kern<<<2 * pairs, kGemm2Threads, SMEM, stream>>>(tmA, tmB, tmC, tmPre, ep, M, N, K, splits, tma_out,
+                                                  g_gemm_prof, error_word_dev());
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("gemm2 launch failed");
 }
@@ -309,8 +339,16 @@ int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda,
   if (a_mn && b_mn) return launch_gemm2<BN_, true, true, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream);     \
   return launch_gemm2<BN_, true, false, ST_>(tmA, tmB, tmC, tmPre, tma_out, ep, M, N, K, splits, stream);
   if (bn == 256) { MIMIR_GEMM2_CASE(256, 5) }
-  MIMIR_GEMM2_CASE(128, 7)
+  MIMIR_GEMM2_CASE(128, 6)
 #undef MIMIR_GEMM2_CASE
 }
 
 }  // namespace mimir
+
+// Diagnostics: when `buf` (device memory, 8 x uint64) is non-null the CTA-pair
+// kernel's first pair records, in SM cycles: [0] MMA-thread span, [1] its wait for a
+// free accumulator, [2] its wait for operands, [3] tiles, [4] an epilogue warp's wait for
+// a finished accumulator, [5] its drain time.  Pass null to switch off.
+MIMIR_API void mimir_gemm_set_profile_buffer(void* buf) {
+  mimir::g_gemm_prof = static_cast<unsigned long long*>(buf);
+}

@@ -142,16 +142,75 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tm, uint8_t* 
   ++ring;
 }
 
-// Drains an accumulator through the fused epilogue into TMA stores (bf16 outputs,
-// no accumulate).  row = this lane's output row, row0 = the warp's first row.
-template <int BN>
-__device__ __forceinline__ void drain_accumulator_tma(const GemmEpi& ep, const CUtensorMap* tmC,
-                                                      const CUtensorMap* tmPre, uint32_t taddr, int row,
-                                                      int row0, int col_base, int M, int N, uint8_t* wbuf,
-                                                      uint32_t& ring, int lane) {
-  const bool write_pre = (ep.flags & kGelu) && (ep.flags & kWritePre);
+// Epilogue modes of the straight-line (branch-free) chunk code below.
+enum EpiMode : int { kEpiPlain = 0, kEpiGelu = 1, kEpiResidual = 2, kEpiDGelu = 3 };
+
+__device__ __forceinline__ int epi_mode_of(int flags) {
+  return (flags & kGelu) ? kEpiGelu : (flags & kResidual) ? kEpiResidual : (flags & kMulDGelu) ? kEpiDGelu : kEpiPlain;
+}
+
+// 64 columns of one row: accumulator bits in r0 | r1 -> packed bf16 output (pk) and,
+// in GELU mode, packed pre-activation (pp).  No branches: loads for columns past N
+// or rows past M are redirected to valid addresses and their results are clipped by
+// the TMA store, so the whole chunk is one block of independent instructions and a
+// lone warp per scheduler still keeps its pipelines busy.
+template <int MODE, bool BIAS>
+__device__ __forceinline__ void epilogue_chunk64(const GemmEpi& ep, const uint32_t (&r0)[32],
+                                                 const uint32_t (&r1)[32], uint32_t (&pk)[32],
+                                                 uint32_t (&pp)[32], int row_c, int col0, int N) {
+  const float alpha = ep.alpha;
+  uint4 bv[8], av[8];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const int cg = min(col0 + g * 8, N - 8);
+    if (BIAS) bv[g] = *reinterpret_cast<const uint4*>(ep.bias + cg);
+    if (MODE == kEpiResidual || MODE == kEpiDGelu)
+      av[g] = *reinterpret_cast<const uint4*>(ep.aux + static_cast<size_t>(row_c) * ep.ldaux + cg);
+  }
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = alpha * __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
+    if (BIAS) {
+      const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { float2 t = unpack_bf16x2(bw[e]); v[2 * e] += t.x; v[2 * e + 1] += t.y; }
+    }
+    if (MODE == kEpiResidual || MODE == kEpiDGelu) {
+      const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 t = unpack_bf16x2(aw[e]);
+        if (MODE == kEpiResidual) { v[2 * e] += t.x; v[2 * e + 1] += t.y; }
+        else { v[2 * e] *= gelu_tanh_grad(t.x); v[2 * e + 1] *= gelu_tanh_grad(t.y); }
+      }
+    }
+    if (MODE == kEpiGelu) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        pp[4 * g + e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+        v[2 * e] = gelu_tanh(v[2 * e]);
+        v[2 * e + 1] = gelu_tanh(v[2 * e + 1]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pk[4 * g + e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+  }
+}
+
+// Drains NCH 64-column chunks of an accumulator through the fused epilogue into TMA
+// stores (bf16 outputs, no accumulate).  row0 = the warp's first row, lane's row =
+// row0 + lane.  taddr / col_base point at the first chunk this warp owns.
+template <int NCH, int MODE, bool BIAS>
+__device__ __forceinline__ void drain_chunks_tma(const GemmEpi& ep, const CUtensorMap* tmC,
+                                                 const CUtensorMap* tmPre, uint32_t taddr, int row0,
+                                                 int col_base, int M, int N, uint8_t* wbuf, uint32_t& ring,
+                                                 int lane) {
+  const int row_c = min(row0 + lane, M - 1);
+  const bool write_pre = MODE == kEpiGelu && (ep.flags & kWritePre);
 #pragma unroll 1
-  for (int c = 0; c < BN / 64; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     uint32_t r0[32], r1[32];
     tmem_ld32(taddr + c * 64, r0);
     tmem_ld32(taddr + c * 64 + 32, r1);
@@ -159,23 +218,27 @@ __device__ __forceinline__ void drain_accumulator_tma(const GemmEpi& ep, const C
     const int col0 = col_base + c * 64;
     if (col0 >= N || row0 >= M) continue;  // uniform over the warp
     uint32_t pk[32], pp[32];
-    const bool live = row < M;
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-      float v[8], pre[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e]);
-      if (live && col0 + g * 8 < N) epilogue_math8(ep, v, pre, row, col0 + g * 8);
-      pk[4 * g] = pack_bf16x2(v[0], v[1]); pk[4 * g + 1] = pack_bf16x2(v[2], v[3]);
-      pk[4 * g + 2] = pack_bf16x2(v[4], v[5]); pk[4 * g + 3] = pack_bf16x2(v[6], v[7]);
-      if (write_pre) {
-        pp[4 * g] = pack_bf16x2(pre[0], pre[1]); pp[4 * g + 1] = pack_bf16x2(pre[2], pre[3]);
-        pp[4 * g + 2] = pack_bf16x2(pre[4], pre[5]); pp[4 * g + 3] = pack_bf16x2(pre[6], pre[7]);
-      }
-    }
+    epilogue_chunk64<MODE, BIAS>(ep, r0, r1, pk, pp, row_c, col0, N);
     if (write_pre) stage_and_store(tmPre, wbuf, ring, pp, lane, col0, row0);
     stage_and_store(tmC, wbuf, ring, pk, lane, col0, row0);
   }
+}
+
+template <int NCH>
+__device__ __forceinline__ void drain_accumulator_tma(const GemmEpi& ep, const CUtensorMap* tmC,
+                                                      const CUtensorMap* tmPre, uint32_t taddr, int row0,
+                                                      int col_base, int M, int N, uint8_t* wbuf, uint32_t& ring,
+                                                      int lane) {
+  const int mode = epi_mode_of(ep.flags);
+  const bool bias = ep.bias != nullptr;
+#define MIMIR_DRAIN(MODE_)                                                                                   \
+  if (bias) drain_chunks_tma<NCH, MODE_, true>(ep, tmC, tmPre, taddr, row0, col_base, M, N, wbuf, ring, lane); \
+  else drain_chunks_tma<NCH, MODE_, false>(ep, tmC, tmPre, taddr, row0, col_base, M, N, wbuf, ring, lane);
+  if (mode == kEpiPlain) { MIMIR_DRAIN(kEpiPlain) }
+  else if (mode == kEpiGelu) { MIMIR_DRAIN(kEpiGelu) }
+  else if (mode == kEpiResidual) { MIMIR_DRAIN(kEpiResidual) }
+  else { MIMIR_DRAIN(kEpiDGelu) }
+#undef MIMIR_DRAIN
 }
 
 // Drains one accumulator buffer (128 lanes x BN columns of fp32 in TMEM) through
