@@ -249,8 +249,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row0 = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32;
       const uint32_t taddr = tmem_base + acc * BN + half * (BN / 2) + (static_cast<uint32_t>(q * 32) << 16);
       const int col_base = n_idx * BN + half * (BN / 2);
-      if (tma_out)
+      if (tma_out == 1)
         drain_accumulator_tma<BN / 128>(ep, &tmC, &tmPre, taddr, row0, col_base, M, N, wbuf, ring, lane);
+      else if (tma_out == 2)
+        drain_partial_tma<BN / 64>(&tmC, taddr, row0, col_base, M, N, split, wbuf, ring, lane);
       else
         drain_accumulator<BN / 2>(ep, taddr, row0 + lane, col_base, M, N, split);
       tc_fence_before();
@@ -323,8 +325,14 @@ int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda,
   if (encode_tmap(&tmB, B, 2, 2, dims, strides, box, 3)) return -1;
   // bf16 outputs without accumulation leave through TMA stores of 32 x 64 sub-tiles
   CUtensorMap tmC = tmA, tmPre = tmA;
-  const int tma_out = !(ep.flags & (kOutF32 | kAccumulate)) && !ep.partial;
-  if (tma_out) {
+  int tma_out = !(ep.flags & (kOutF32 | kAccumulate)) && !ep.partial;
+  if (ep.partial) {
+    // fp32 partial sums [splits][M][N]: 32-column (128-byte) boxes, clipped per split
+    uint64_t d3[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(splits)};
+    uint64_t s3[2] = {static_cast<uint64_t>(N) * 4, static_cast<uint64_t>(M) * N * 4};
+    uint32_t b3[3] = {32, 32, 1};
+    if (N % 4 == 0 && encode_tmap(&tmC, ep.partial, 4, 3, d3, s3, b3, 3) == 0) tma_out = 2;
+  } else if (tma_out) {
     dims[0] = N; dims[1] = M; box[0] = 64; box[1] = 32;
     strides[0] = static_cast<uint64_t>(ep.ldc) * 2;
     if (encode_tmap(&tmC, ep.C, 2, 2, dims, strides, box, 3)) return -1;

@@ -142,6 +142,36 @@ __device__ __forceinline__ void stage_and_store(const CUtensorMap* tm, uint8_t* 
   ++ring;
 }
 
+// Split-K partial sums: NCH32 chunks of 32 fp32 columns leave through TMA stores into
+// the workspace viewed as [splits][M][N] (3-D map, so rows past M are clipped per split).
+template <int NCH32>
+__device__ __forceinline__ void drain_partial_tma(const CUtensorMap* tmP, uint32_t taddr, int row0, int col_base,
+                                                  int M, int N, int split, uint8_t* wbuf, uint32_t& ring,
+                                                  int lane) {
+#pragma unroll 1
+  for (int c = 0; c < NCH32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = col_base + c * 32;
+    if (col0 >= N || row0 >= M) continue;  // uniform over the warp
+    uint8_t* buf = wbuf + (ring & 1) * 4096;
+    if (lane == 0) bulk_wait_group_read<1>();
+    __syncwarp();
+    const uint32_t base = smem_u32(buf) + lane * 128;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      st_shared_v4(base + ((u ^ (lane & 7)) << 4), r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tmP, buf, col0, row0, split);
+      bulk_commit_group();
+    }
+    ++ring;
+  }
+}
+
 // Epilogue modes of the straight-line (branch-free) chunk code below.
 enum EpiMode : int { kEpiPlain = 0, kEpiGelu = 1, kEpiResidual = 2, kEpiDGelu = 3 };
 

@@ -235,26 +235,52 @@ MIMIR_API int mimir_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   int pair_mode = bn_hint >= 2000 ? 2 : bn_hint >= 1000 ? 1 : 0;
   bn_hint %= 1000;
   int bn = bn_hint;
-  if (bn != 64 && bn != 128 && bn != 256) {
-    // Prefer the wide tile unless its wave quantisation is clearly worse.
-    auto eff = [&](int b) {
-      long long t = static_cast<long long>(ceil_div(M, kBM)) * ceil_div(N, b);
-      long long w = (t + nsm - 1) / nsm;
-      return static_cast<double>(t) / static_cast<double>(w * nsm);
-    };
-    bn = (N >= 256 && eff(256) >= eff(128) - 0.08) ? 256 : 128;
-    if (N <= 64) bn = 64;
-  }
-  const int tiles = ceil_div(M, kBM) * ceil_div(N, bn);
   const int kb_total = ceil_div(K, kBK);
   int splits = splits_hint;
-  if (splits <= 0) {
-    splits = 1;
-    if (workspace && tiles * 2 <= nsm && kb_total >= 8) {
-      splits = nsm / tiles;
-      if (splits > 16) splits = 16;
-      if (splits > kb_total / 4) splits = kb_total / 4;
-      if (splits < 1) splits = 1;
+  // Plan for the CTA-pair kernel.
+  bool plan_pair = pair_mode != 2 && M >= 2 * kBM && N >= 128;
+  if (plan_pair && (bn != 128 && bn != 256 || splits <= 0)) {
+    // Measured on B200 (sweep over tile width x split-K for the GPT-2 shapes): the
+    // 256-wide tile wins whenever N allows it; split-K only pays when the tiles
+    // would leave more than half of the CTA pairs idle.
+    const int npairs = nsm / 2;
+    if (bn != 128 && bn != 256) bn = N >= 256 ? 256 : 128;
+    if (splits <= 0) {
+      const long long tiles2 = static_cast<long long>(ceil_div(M, 2 * kBM)) * ceil_div(N, bn);
+      splits = 1;
+      if (workspace && tiles2 * 2 <= npairs && kb_total >= 32) {
+        splits = static_cast<int>(npairs / tiles2);
+        if (splits > 8) splits = 8;
+        if (splits > kb_total / 16) splits = kb_total / 16;
+        while (splits > 1 && workspace_bytes < static_cast<long long>(splits) * M * N * 4) --splits;
+        if (splits < 1) splits = 1;
+      }
+    }
+    // tiny problems run better on the single-CTA kernel (no cluster launch, finer tiles)
+    if (pair_mode == 0 && static_cast<long long>(ceil_div(M, 2 * kBM)) * ceil_div(N, bn) * splits < nsm / 8)
+      plan_pair = false;
+  }
+  if (!plan_pair || pair_mode == 2) {
+    plan_pair = pair_mode == 1;
+    if (bn != 64 && bn != 128 && bn != 256) {
+      // Prefer the wide tile unless its wave quantisation is clearly worse.
+      auto eff = [&](int b) {
+        long long t = static_cast<long long>(ceil_div(M, kBM)) * ceil_div(N, b);
+        long long w = (t + nsm - 1) / nsm;
+        return static_cast<double>(t) / static_cast<double>(w * nsm);
+      };
+      bn = (N >= 256 && eff(256) >= eff(128) - 0.08) ? 256 : 128;
+      if (N <= 64) bn = 64;
+    }
+    const int tiles = ceil_div(M, kBM) * ceil_div(N, bn);
+    if (splits <= 0) {
+      splits = 1;
+      if (workspace && tiles * 2 <= nsm && kb_total >= 8) {
+        splits = nsm / tiles;
+        if (splits > 16) splits = 16;
+        if (splits > kb_total / 4) splits = kb_total / 4;
+        if (splits < 1) splits = 1;
+      }
     }
   }
   if (splits > kb_total) splits = kb_total;
@@ -275,12 +301,7 @@ MIMIR_API int mimir_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   ep.flags = flags;
   ep.alpha = alpha;
 
-  bool use_pair = pair_mode == 1;
-  if (pair_mode == 0) {
-    // pairs pay off once there are enough 256-row tiles to fill the machine
-    const long long pair_units = static_cast<long long>(ceil_div(M, 2 * kBM)) * ceil_div(N, bn < 128 ? 128 : bn) * splits;
-    use_pair = bn >= 128 && M >= 2 * kBM && pair_units >= nsm / 4;
-  }
+  const bool use_pair = plan_pair;
   if (use_pair && bn >= 128) {
     if (launch_gemm_pair(A, B, M, N, K, lda, ldb, a_mn, b_mn, ep, bn, splits, stream)) return -1;
     if (splits > 1) {

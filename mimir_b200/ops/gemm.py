@@ -22,7 +22,7 @@ GEMM_FLAGS = {
 _workspaces: dict = {}
 
 
-def workspace(device, nbytes: int = 64 << 20) -> torch.Tensor:
+def workspace(device, nbytes: int = 128 << 20) -> torch.Tensor:
     """Per-device split-K scratch buffer (grown on demand, never shrunk)."""
     key = (device.index if device.index is not None else torch.cuda.current_device())
     ws = _workspaces.get(key)
