@@ -105,6 +105,12 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
 
+    # Libraries (NCCL's version banner among them) may write to stdout; the contract is
+    # ONE JSON line there, so everything else goes to stderr until the result is printed.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -114,6 +120,7 @@ def main() -> int:
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             # re-launch under torchrun so that there is one process per GPU
+            os.dup2(real_stdout, 1)
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                    f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port",
                    os.environ.get("MASTER_PORT", "29517"), os.path.abspath(__file__)] + sys.argv[1:]
@@ -215,7 +222,8 @@ def main() -> int:
             "error_word": err,
             "impl": "ours",
         }
-        print(json.dumps(out))
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(out) + "\n").encode())
     if world > 1:
         if dp is not None:
             dp.close()

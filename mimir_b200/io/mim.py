@@ -1,0 +1,276 @@
+"""``.mim`` model / checkpoint files (reference: io/mim/mim.go:193-226,
+weights.go:50-201, write.go:54-167).
+
+``open(path)`` maps the file read-only through the native library and returns a
+:class:`Model` whose tensors are zero-copy views over the mapping;
+``write_tensors`` / ``save`` produce files byte-compatible with the reference
+writer (verified by rewriting every sample file of the reference bit for bit).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import numpy as np
+import torch
+
+from .. import _native
+from . import metadata as _md
+
+# dtype codes of the container (io/mim/dtype.go:32-35,118-123)
+F32, F16, BF16, U8, I32, I64 = 1, 2, 3, 6, 9, 11
+Q8_0, Q4_0, Q4_K, Q6_K = 64, 65, 66, 67
+_TORCH = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16, U8: torch.uint8,
+          I32: torch.int32, I64: torch.int64}
+_CODE = {v: k for k, v in _TORCH.items()}
+# quantized block layouts: (values per block, bytes per block)
+QUANT_BLOCK = {Q8_0: (32, 34), Q4_0: (32, 18), Q4_K: (256, 144), Q6_K: (256, 210)}
+SECTION_WEIGHTS, SECTION_METADATA, SECTION_GRAPH, SECTION_TRAINING = 1, 2, 3, 4
+
+
+class MimError(RuntimeError):
+    pass
+
+
+class QuantizedTensor:
+    """A block-quantized tensor kept in its file encoding (ggml layouts)."""
+
+    def __init__(self, code: int, shape, raw: torch.Tensor):
+        self.code, self.shape, self.raw = code, tuple(shape), raw
+
+    @property
+    def kind(self) -> str:
+        return {Q8_0: "q8_0", Q4_0: "q4_0", Q4_K: "q4_k", Q6_K: "q6_k"}[self.code]
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        from ..ops.quant import dequantize
+        return dequantize(self, dtype)
+
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+def _lib():
+    lib = _native.lib()
+    if not getattr(lib, "_mim_declared", False):
+        vp, c = ctypes.c_void_p, ctypes
+        lib.mimir_mim_last_error.restype = c.c_char_p
+        lib.mimir_mim_open.argtypes = [c.c_char_p, c.POINTER(vp)]
+        lib.mimir_mim_parse.argtypes = [vp, c.c_uint64, c.POINTER(vp)]
+        lib.mimir_mim_close.argtypes = [vp]
+        lib.mimir_mim_close.restype = None
+        lib.mimir_mim_info.argtypes = [vp] + [c.POINTER(c.c_int)] * 6
+        lib.mimir_mim_base.argtypes = [vp]
+        lib.mimir_mim_base.restype = vp
+        lib.mimir_mim_size.argtypes = [vp]
+        lib.mimir_mim_size.restype = c.c_uint64
+        lib.mimir_mim_tensor.argtypes = [vp, c.c_int, c.POINTER(c.c_char_p), c.POINTER(c.c_int),
+                                         c.POINTER(c.c_int), c.POINTER(c.c_int), c.POINTER(c.c_uint64),
+                                         c.POINTER(c.c_uint64), c.POINTER(c.c_uint64)]
+        lib.mimir_mim_section.argtypes = [vp, c.c_int, c.POINTER(c.c_int), c.POINTER(c.c_int),
+                                          c.POINTER(c.c_uint64), c.POINTER(c.c_uint64), c.c_char_p]
+        lib.mimir_mim_verify.argtypes = [vp]
+        lib.mimir_mim_writer_new.argtypes = [c.c_int, c.c_int, c.c_int]
+        lib.mimir_mim_writer_new.restype = vp
+        lib.mimir_mim_writer_free.argtypes = [vp]
+        lib.mimir_mim_writer_free.restype = None
+        lib.mimir_mim_writer_add_tensor.argtypes = [vp, c.c_char_p, c.c_int, c.c_int, c.c_int,
+                                                    c.POINTER(c.c_uint64), vp, c.c_uint64]
+        lib.mimir_mim_writer_set_section.argtypes = [vp, c.c_int, c.c_int, vp, c.c_uint64]
+        lib.mimir_mim_writer_write.argtypes = [vp, c.c_char_p]
+        lib.mimir_mim_writer_serialize.argtypes = [vp, c.POINTER(c.POINTER(c.c_uint8)), c.POINTER(c.c_uint64)]
+        lib.mimir_mim_free_buffer.argtypes = [c.POINTER(c.c_uint8)]
+        lib.mimir_mim_free_buffer.restype = None
+        lib._mim_declared = True
+    return lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise MimError(_lib().mimir_mim_last_error().decode())
+
+
+class Model:
+    """An open ``.mim`` file.  Tensors are views over the read-only mapping."""
+
+    def __init__(self, handle, keepalive=None):
+        lib = _lib()
+        self._h, self._keep = handle, keepalive
+        vals = [ctypes.c_int() for _ in range(6)]
+        lib.mimir_mim_info(handle, *[ctypes.byref(v) for v in vals])
+        self.major, self.minor, self.alignment, nt, ns, mmf = (v.value for v in vals)
+        self.legacy_magic = bool(mmf)
+        size = lib.mimir_mim_size(handle)
+        base = lib.mimir_mim_base(handle)
+        self._buf = (ctypes.c_uint8 * size).from_address(base)
+        self._np = np.frombuffer(self._buf, dtype=np.uint8)
+        self._index = {}
+        name, nl, dt, rank = ctypes.c_char_p(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        dims = (ctypes.c_uint64 * 8)()
+        off, nb = ctypes.c_uint64(), ctypes.c_uint64()
+        for i in range(nt):
+            _check(lib.mimir_mim_tensor(handle, i, ctypes.byref(name), ctypes.byref(nl), ctypes.byref(dt),
+                                        ctypes.byref(rank), dims, ctypes.byref(off), ctypes.byref(nb)))
+            nm = ctypes.string_at(name, nl.value).decode("utf-8")
+            self._index[nm] = (dt.value, tuple(dims[d] for d in range(rank.value)), off.value, nb.value)
+        self.sections = []
+        kind, flags = ctypes.c_int(), ctypes.c_int()
+        h32 = ctypes.create_string_buffer(32)
+        for i in range(ns):
+            _check(lib.mimir_mim_section(handle, i, ctypes.byref(kind), ctypes.byref(flags),
+                                         ctypes.byref(off), ctypes.byref(nb), h32))
+            self.sections.append(dict(kind=kind.value, flags=flags.value, offset=off.value,
+                                      length=nb.value, sha256=bytes(h32.raw)))
+        self._metadata = None
+
+    # -- inspection
+    def names(self):
+        return sorted(self._index)
+
+    def __contains__(self, name):
+        return name in self._index
+
+    def info(self, name):
+        dt, shape, _, nb = self._index[name]
+        return dt, shape, nb
+
+    def section_bytes(self, kind: int):
+        for s in self.sections:
+            if s["kind"] == kind:
+                return bytes(self._np[s["offset"]: s["offset"] + s["length"]])
+        return None
+
+    @property
+    def metadata(self) -> dict:
+        if self._metadata is None:
+            raw = self.section_bytes(SECTION_METADATA)
+            self._metadata = _md.decode(raw) if raw else {}
+        return self._metadata
+
+    def training(self):
+        """Training section (counters, hyper-parameters, extras) or None."""
+        raw = self.section_bytes(SECTION_TRAINING)
+        return _md.decode(raw) if raw else None
+
+    def verify(self) -> bool:
+        """Re-hashes every section against the SHA-256 in the index."""
+        return _lib().mimir_mim_verify(self._h) == 0
+
+    # -- tensors
+    def tensor(self, name: str):
+        """Zero-copy tensor over the mapping (clone before writing to it)."""
+        if name not in self._index:
+            raise KeyError(name)
+        dt, shape, off, nb = self._index[name]
+        raw = torch.from_numpy(self._np[off: off + nb])
+        if dt in _TORCH:
+            return raw.view(_TORCH[dt]).view(shape)
+        if dt in QUANT_BLOCK:
+            return QuantizedTensor(dt, shape, raw)
+        raise MimError(f"tensor {name!r}: unknown dtype code {dt}")
+
+    def load(self, device="cpu", prefix: str = "", dequantize: bool = False) -> dict:
+        """All tensors under ``prefix`` as a name -> tensor dict on ``device``."""
+        out = {}
+        for n in self.names():
+            if not n.startswith(prefix):
+                continue
+            t = self.tensor(n)
+            if isinstance(t, QuantizedTensor):
+                t = t.dequantize() if dequantize else QuantizedTensor(t.code, t.shape, t.raw.to(device))
+            else:
+                t = t.to(device) if str(device) != "cpu" else t.clone()
+            if dequantize and not isinstance(t, QuantizedTensor):
+                t = t.to(device)
+            out[n[len(prefix):]] = t
+        return out
+
+    def close(self):
+        if self._h:
+            self._np = self._buf = None
+            _lib().mimir_mim_close(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+
+def open(path) -> Model:  # noqa: A001 - mirrors mim.Open
+    h = ctypes.c_void_p()
+    _check(_lib().mimir_mim_open(os.fspath(path).encode(), ctypes.byref(h)))
+    return Model(h)
+
+
+def parse(data: bytes) -> Model:
+    buf = ctypes.create_string_buffer(data, len(data))
+    h = ctypes.c_void_p()
+    _check(_lib().mimir_mim_parse(ctypes.cast(buf, ctypes.c_void_p), len(data), ctypes.byref(h)))
+    return Model(h, keepalive=buf)
+
+
+def _writer(tensors: dict, metadata=None, graph=None, training=None, alignment=4096, minor=2,
+            legacy_magic=False, extra_sections=None):
+    lib = _lib()
+    w = lib.mimir_mim_writer_new(alignment, minor, int(legacy_magic))
+    keep = []
+    for name, t in tensors.items():
+        if isinstance(t, QuantizedTensor):
+            code, shape, raw = t.code, t.shape, t.raw.detach().cpu().contiguous()
+        else:
+            t = t.detach().cpu().contiguous()
+            if t.dtype not in _CODE:
+                raise MimError(f"tensor {name!r}: dtype {t.dtype} has no .mim code")
+            code, shape, raw = _CODE[t.dtype], tuple(t.shape), t.reshape(-1).view(torch.uint8)
+        raw = raw.reshape(-1)
+        keep.append(raw)
+        dims = (ctypes.c_uint64 * 8)(*shape, *([0] * (8 - len(shape))))
+        nm = name.encode("utf-8")
+        _check(lib.mimir_mim_writer_add_tensor(w, nm, len(nm), code, len(shape), dims,
+                                               raw.data_ptr() if raw.numel() else None, raw.numel()))
+    def put(kind, flags, data):
+        b = ctypes.create_string_buffer(data, len(data))
+        _check(lib.mimir_mim_writer_set_section(w, kind, flags, ctypes.cast(b, ctypes.c_void_p), len(data)))
+    if metadata is not None:
+        put(SECTION_METADATA, 0, metadata if isinstance(metadata, bytes)
+            else _md.encode(metadata, b"MMFM" if legacy_magic else b"MIMM"))
+    if graph is not None:
+        put(SECTION_GRAPH, 1, graph)
+    if training is not None:
+        put(SECTION_TRAINING, 0, training if isinstance(training, bytes) else _md.encode(training))
+    for kind, (flags, data) in (extra_sections or {}).items():
+        put(kind, flags, data)
+    return w, keep
+
+
+def write_tensors(path, tensors: dict, metadata=None, training=None, graph=None, alignment=4096,
+                  minor=2, legacy_magic=False) -> None:
+    """Writes ``tensors`` (name -> tensor) atomically: temp file, fsync, rename."""
+    w, keep = _writer(tensors, metadata, graph, training, alignment, minor, legacy_magic)
+    try:
+        _check(_lib().mimir_mim_writer_write(w, os.fspath(path).encode()))
+    finally:
+        _lib().mimir_mim_writer_free(w)
+
+
+def serialize(tensors: dict, metadata=None, training=None, graph=None, alignment=4096, minor=2,
+              legacy_magic=False) -> bytes:
+    w, keep = _writer(tensors, metadata, graph, training, alignment, minor, legacy_magic)
+    try:
+        out, n = ctypes.POINTER(ctypes.c_uint8)(), ctypes.c_uint64()
+        _check(_lib().mimir_mim_writer_serialize(w, ctypes.byref(out), ctypes.byref(n)))
+        data = ctypes.string_at(out, n.value)
+        _lib().mimir_mim_free_buffer(out)
+        return data
+    finally:
+        _lib().mimir_mim_writer_free(w)
+
+
+def save(path, module_or_state, metadata=None, training=None) -> None:
+    """Saves a module's named parameters/buffers (or a state dict) as ``.mim``."""
+    state = module_or_state.state_dict() if hasattr(module_or_state, "state_dict") else module_or_state
+    write_tensors(path, {k: v for k, v in state.items() if torch.is_tensor(v) or isinstance(v, QuantizedTensor)},
+                  metadata=metadata, training=training)
