@@ -1,0 +1,288 @@
+"""Parameters, reverse-mode differentiation and function transforms.
+
+``Param`` is the only mutable object (tensor/autograd.go:830-1020): optimizers
+write new values in place, after which tensors obtained from ``value()`` before
+the write are stale (``ErrOverwritten``).  ``backward(loss)`` evaluates the loss
+and all gradients in ONE pass and accumulates into existing gradients
+(tensor/autograd.go:322-345); the differentiation itself is PyTorch autograd
+over the executed graph.  ``grad / vjp / jvp / jacobian / hessian / vmap`` wrap
+``torch.func`` around functions written against the lazy ``Tensor`` API
+(tensor/transform.go, tensor/vmap.go).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import core as C
+from . import errors as E
+
+
+class Param:
+    """A trainable (or frozen) tensor with an accumulated gradient."""
+
+    def __init__(self, value, name: str = "", trainable: bool = True):
+        v = value.data() if isinstance(value, C.Tensor) else torch.as_tensor(value)
+        self._data = v.detach().clone()
+        self._grad = None
+        self._version = 0
+        self.name = name
+        self._trainable = trainable
+        self._sharding = None
+
+    # -- value access
+    def value(self) -> C.Tensor:
+        t = C.from_torch(self._data)
+        t._stale = (self, self._version)
+        t._fn = None
+        _LEAF_PARAM[id(t)] = self
+        return t
+
+    def grad(self):
+        return None if self._grad is None else C.from_torch(self._grad)
+
+    def zero_grad(self) -> None:
+        self._grad = None
+
+    def set(self, value) -> None:
+        v = value.data() if isinstance(value, C.Tensor) else torch.as_tensor(value)
+        if tuple(v.shape) != tuple(self._data.shape):
+            raise E.ErrShape(f"Param.set: shape {tuple(v.shape)} != {tuple(self._data.shape)}")
+        self._data.copy_(v.to(self._data.dtype))
+        self._version += 1
+
+    def to(self, device: C.Device) -> "Param":
+        self._data = self._data.to(device.torch)
+        if self._grad is not None:
+            self._grad = self._grad.to(device.torch)
+        self._version += 1
+        return self
+
+    def cast(self, dtype) -> "Param":
+        self._data = self._data.to(dtype)
+        self._grad = None
+        self._version += 1
+        return self
+
+    def freeze(self) -> "Param":
+        self._trainable = False
+        return self
+
+    def unfreeze(self) -> "Param":
+        self._trainable = True
+        return self
+
+    @property
+    def frozen(self) -> bool:
+        return not self._trainable
+
+    @property
+    def trainable(self) -> bool:
+        return self._trainable
+
+    @property
+    def shape(self):
+        return tuple(self._data.shape)
+
+    @property
+    def dtype(self):
+        return self._data.dtype
+
+    @property
+    def device(self) -> C.Device:
+        return C._dev_of(self._data)
+
+    def shard(self, mesh, spec) -> "Param":
+        self._sharding = (mesh, spec)
+        return self
+
+    def numel(self) -> int:
+        return self._data.numel()
+
+
+class Buffer(Param):
+    """Non-trainable state (running statistics, caches): ``NewBuffer`` in the reference."""
+
+    def __init__(self, value, name: str = ""):
+        super().__init__(value, name, trainable=False)
+
+
+import weakref
+
+_LEAF_PARAM = weakref.WeakValueDictionary()
+
+
+def _collect_params(root: C.Tensor) -> dict:
+    """Leaf tensors below ``root`` that view parameter storage: id(leaf) -> Param."""
+    out, seen, stack = {}, set(), [root]
+    while stack:
+        t = stack.pop()
+        if id(t) in seen:
+            continue
+        seen.add(id(t))
+        if t._stale is not None:
+            out[id(t)] = (t, t._stale[0])
+        stack.extend(a for a in C._flatten(t._args) if isinstance(a, C.Tensor))
+    return out
+
+
+def backward(loss: C.Tensor, effects=()) -> None:
+    """Loss and all parameter gradients in one pass; gradients accumulate in place."""
+    if loss._err is not None:
+        raise loss._err
+    if loss.numel() != 1:
+        raise E.ErrShape(f"backward needs a scalar loss, got shape {loss.shape}")
+    if loss._fn is None:
+        raise E.ErrNoGrad("the loss does not depend on any recorded operation")
+    leaves = _collect_params(loss)
+    trainable = {k: (t, p) for k, (t, p) in leaves.items() if p._trainable}
+    if not trainable:
+        raise E.ErrNoGrad("the loss depends on no trainable parameter")
+    from .memory import reserve
+    reserve([loss])
+    memo, inputs = {}, {}
+    for k, (t, p) in leaves.items():
+        C._check_leaf(t)
+        v = p._data.detach()
+        if p._trainable:
+            if not v.dtype.is_floating_point:
+                raise E.ErrNotDifferentiable(f"parameter {p.name!r} has dtype {v.dtype}")
+            v = inputs.setdefault(id(p), v.requires_grad_(True))
+        memo[k] = v
+    with torch.enable_grad():
+        (out,) = C.evaluate([loss], memo, reuse_cached=False)
+        if not out.requires_grad:
+            raise E.ErrNoGrad("the loss is not differentiable with respect to the parameters")
+        params = [p for _, (t, p) in trainable.items()]
+        uniq = list({id(p): p for p in params}.values())
+        grads = torch.autograd.grad(out, [inputs[id(p)] for p in uniq], allow_unused=True)
+    for p, g in zip(uniq, grads):
+        if g is None:
+            continue
+        p._grad = g.detach() if p._grad is None else p._grad + g.detach()
+        p._data.requires_grad_(False)
+    for p in uniq:
+        p._data.requires_grad_(False)
+    loss._val = out.detach()
+    loss._fn, loss._args, loss._kw = None, (), {}
+    for e in effects:
+        e()
+
+
+def gradients(loss: C.Tensor, wrt) -> list:
+    """Gradients of a scalar with respect to arbitrary tensors of its graph (not accumulated)."""
+    wrt = list(wrt)
+    memo = {}
+    leaves = []
+    for w in wrt:
+        v = w.data().detach().clone().requires_grad_(True)
+        memo[id(w)] = v
+        leaves.append(v)
+    with torch.enable_grad():
+        (out,) = C.evaluate([loss], memo, reuse_cached=False)
+        gs = torch.autograd.grad(out, leaves, allow_unused=True)
+    return [C.from_torch(torch.zeros_like(l) if g is None else g) for g, l in zip(gs, leaves)]
+
+
+def _wrap_fn(f):
+    """Lifts a function over lazy Tensors to one over torch tensors (for torch.func)."""
+    def g(*xs):
+        outs = f(*[_Traced(x) for x in xs])
+        if isinstance(outs, (tuple, list)):
+            return tuple(_untrace(o) for o in outs)
+        return _untrace(outs)
+    return g
+
+
+class _Traced(C.Tensor):
+    """A leaf whose value is a torch.func tracer (kept out of the realized cache)."""
+
+    def __init__(self, v):
+        super().__init__(val=v, shape=v.shape, dtype=v.dtype, device=C._dev_of(v))
+
+
+def _untrace(t: C.Tensor):
+    if t._err is not None:
+        raise t._err
+    (v,) = C.evaluate([t], {}, reuse_cached=True)
+    return v
+
+
+def grad(f, argnums=0):
+    """``grad(f)(x...)`` = gradient of the scalar ``f`` (tensor.Grad)."""
+    def run(*xs):
+        vals = [x.data() for x in xs]
+        out = torch.func.grad(_wrap_fn(f), argnums=argnums)(*vals)
+        return tuple(C.from_torch(o) for o in out) if isinstance(out, tuple) else C.from_torch(out)
+    return run
+
+
+def vjp(f, *xs):
+    out, pull = torch.func.vjp(_wrap_fn(f), *[x.data() for x in xs])
+
+    def pullback(ct):
+        res = pull(ct.data())
+        return tuple(C.from_torch(r) for r in res)
+    return C.from_torch(out), pullback
+
+
+def jvp(f, xs, tangents):
+    out, tan = torch.func.jvp(_wrap_fn(f), tuple(x.data() for x in xs), tuple(t.data() for t in tangents))
+    return C.from_torch(out), C.from_torch(tan)
+
+
+def jacobian(f, x):
+    return C.from_torch(torch.func.jacrev(_wrap_fn(f))(x.data()))
+
+
+def hessian(f, x):
+    return C.from_torch(torch.func.hessian(_wrap_fn(f))(x.data()))
+
+
+def vmap(f, in_axes=0, out_axes=0):
+    """Vectorises ``f`` over an axis (tensor.VMap with InAxes / OutAxes)."""
+    def run(*xs):
+        try:
+            out = torch.func.vmap(_wrap_fn(f), in_dims=in_axes, out_dims=out_axes)(*[x.data() for x in xs])
+        except RuntimeError as exc:
+            raise E.ErrNotBatchable(str(exc)) from exc
+        return tuple(C.from_torch(o) for o in out) if isinstance(out, tuple) else C.from_torch(out)
+    return run
+
+
+def func(forward, backward_fn):
+    """Custom differentiable operation (tensor.Func, tensor/autograd.go:785-802):
+    ``forward(*torch tensors) -> torch tensor`` and ``backward_fn(inputs, output, grad) -> grads``."""
+    class _F(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, *xs):
+            out = forward(*xs)
+            ctx.save_for_backward(*xs, out)
+            return out
+
+        @staticmethod
+        def backward(ctx, g):
+            *xs, out = ctx.saved_tensors
+            res = backward_fn(xs, out, g)
+            return tuple(res) if isinstance(res, (tuple, list)) else (res,)
+
+    def op(*ts):
+        return C._node(lambda *vs: forward(*vs) if vs and vs[0].device.type == "meta" else _F.apply(*vs), ts, {}, "func")
+    return op
+
+
+def checkpoint(f):
+    """Recomputes ``f``'s intermediates during backward instead of keeping them
+    (tensor.Checkpoint, tensor/checkpoint.go:30-68)."""
+    def run(*ts):
+        def ev(*vs):
+            if vs and vs[0].device.type == "meta":
+                return _wrap_fn(f)(*vs)
+            if torch.is_grad_enabled() and any(v.requires_grad for v in vs):
+                import torch.utils.checkpoint as cp
+                return cp.checkpoint(_wrap_fn(f), *vs, use_reentrant=False)
+            return _wrap_fn(f)(*vs)
+        out = C._node(ev, ts, {}, "checkpoint")
+        if isinstance(out, C.Tensor) and out._err is not None:
+            out._err = E.ErrCheckpoint(str(out._err)) if not isinstance(out._err, E.MimirError) else out._err
+        return out
+    return run

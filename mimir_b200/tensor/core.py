@@ -1,0 +1,823 @@
+"""Lazy, immutable tensors with sticky errors over PyTorch.
+
+Reference semantics (tensor/tensor.go:17-30,126-157): every operation checks
+shapes and dtypes when it is *recorded* and returns a new ``Tensor`` node;
+nothing runs until ``realize`` / ``data`` / ``item`` / ``backward``.  A bad
+operation does not raise: it returns a tensor that carries the error, and every
+tensor computed from it carries it too.  ``MIMIR_EAGER=1`` realizes each
+operation as it is recorded (tensor/tensor.go:149).
+
+Shape inference runs the recorded function on ``meta`` tensors, so the check
+costs no compute; execution maps the graph onto eager PyTorch kernels (and the
+native sm_100a kernels for the fused operations) in one pass with memoisation.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Any, Callable, Sequence
+
+import torch
+
+from . import errors as E
+
+float32, float16, bfloat16, int32, int64, bool_ = (torch.float32, torch.float16, torch.bfloat16,
+                                                    torch.int32, torch.int64, torch.bool)
+_HALF = (torch.float16, torch.bfloat16)
+_FLOAT = (torch.float32, torch.float16, torch.bfloat16, torch.float64)
+_EAGER = os.environ.get("MIMIR_EAGER", "") == "1"
+
+
+class Device:
+    """A compute device: ``Device("cpu")`` or ``Device("gpu", index)``."""
+
+    def __init__(self, kind: str = "cpu", index: int = 0):
+        kind = {"cuda": "gpu"}.get(kind, kind)
+        if kind not in ("cpu", "gpu"):
+            raise E.ErrDevice(f"unknown device kind {kind!r}")
+        self.kind, self.index = kind, index
+
+    @property
+    def torch(self) -> torch.device:
+        return torch.device("cpu") if self.kind == "cpu" else torch.device("cuda", self.index)
+
+    def __eq__(self, o):
+        return isinstance(o, Device) and (self.kind, self.index) == (o.kind, o.index)
+
+    def __hash__(self):
+        return hash((self.kind, self.index))
+
+    def __repr__(self):
+        return "cpu" if self.kind == "cpu" else f"gpu:{self.index}"
+
+
+def CPU() -> Device:
+    return Device("cpu")
+
+
+def GPU(index: int = 0) -> Device:
+    if not torch.cuda.is_available() or index >= torch.cuda.device_count():
+        raise E.ErrDevice(f"gpu:{index} is not available")
+    return Device("gpu", index)
+
+
+def devices() -> list:
+    out = [Device("cpu")]
+    if torch.cuda.is_available():
+        out += [Device("gpu", i) for i in range(torch.cuda.device_count())]
+    return out
+
+
+def auto() -> Device:
+    """The device ``MIMIR_DEVICE`` names (cpu | gpu | cuda | auto), else the first GPU, else CPU
+    (tensor/device.go:173-187)."""
+    want = os.environ.get("MIMIR_DEVICE", "auto").lower()
+    if want in ("gpu", "cuda"):
+        return GPU(0)
+    if want == "cpu":
+        return CPU()
+    return Device("gpu", 0) if torch.cuda.is_available() else Device("cpu")
+
+
+_default_device = None
+
+
+def default_device() -> Device:
+    global _default_device
+    if _default_device is None:
+        _default_device = auto()
+    return _default_device
+
+
+def set_default_device(d: Device) -> None:
+    global _default_device
+    _default_device = d
+
+
+def _dev_of(t: torch.Tensor) -> Device:
+    return Device("cpu") if t.device.type == "cpu" else Device("gpu", t.device.index or 0)
+
+
+class Tensor:
+    """One node of the lazy graph (or a realized leaf)."""
+
+    __slots__ = ("_fn", "_args", "_kw", "_val", "_err", "shape", "dtype", "device", "_stale", "_donated",
+                 "_sharding", "_opname", "__weakref__")
+
+    def __init__(self, fn=None, args=(), kw=None, val=None, err=None, shape=(), dtype=float32, device=None,
+                 opname=""):
+        self._fn, self._args, self._kw = fn, args, kw or {}
+        self._val, self._err = val, err
+        self.shape, self.dtype = tuple(shape), dtype
+        self.device = device or default_device()
+        self._stale = None      # (param, version) for views of parameter storage
+        self._donated = False
+        self._sharding = None
+        self._opname = opname
+
+    # ------------------------------------------------------------- properties
+    @property
+    def err(self):
+        return self._err
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+    def __repr__(self):
+        if self._err is not None:
+            return f"Tensor(error={type(self._err).__name__}: {self._err})"
+        state = "realized" if self._val is not None else "lazy"
+        return f"Tensor(shape={self.shape}, dtype={str(self.dtype).replace('torch.', '')}, device={self.device}, {state})"
+
+    # --------------------------------------------------------------- realize
+    def realize(self) -> "Tensor":
+        realize(self)
+        return self
+
+    def data(self) -> torch.Tensor:
+        """The realized value as a (detached) torch tensor."""
+        realize(self)
+        return self._val.detach()
+
+    def numpy(self):
+        return self.data().float().cpu().numpy() if self.dtype in _HALF else self.data().cpu().numpy()
+
+    def item(self):
+        if self.numel() != 1 and self._err is None:
+            raise E.ErrShape(f"item() needs one element, tensor has shape {self.shape}")
+        return self.data().reshape(()).item()
+
+    def tolist(self):
+        return self.data().cpu().tolist()
+
+    def donate(self) -> "Tensor":
+        """Marks a realized leaf whose memory the next schedule may reuse
+        (internal/sched/donate.go:49); using it afterwards is ErrDonated."""
+        self._donated = True
+        return self
+
+    def to(self, device: Device) -> "Tensor":
+        if self._err is not None or device == self.device:
+            return self
+        src = self
+        return _node(lambda v: v.to(device.torch), (src,), {}, "to", device=device)
+
+    def backward(self) -> None:
+        from .autograd import backward
+        backward(self)
+
+    # ------------------------------------------------------------- operators
+    def __add__(self, o): return add(self, o)
+    def __radd__(self, o): return add(o, self)
+    def __sub__(self, o): return sub(self, o)
+    def __rsub__(self, o): return sub(o, self)
+    def __mul__(self, o): return mul(self, o)
+    def __rmul__(self, o): return mul(o, self)
+    def __truediv__(self, o): return div(self, o)
+    def __rtruediv__(self, o): return div(o, self)
+    def __neg__(self): return neg(self)
+    def __matmul__(self, o): return matmul(self, o)
+    def __pow__(self, o): return pow_(self, o)
+    def __getitem__(self, idx): return getitem(self, idx)
+    def __lt__(self, o): return less(self, o)
+    def __gt__(self, o): return less(o, self)
+    def __le__(self, o): return logical_not(less(o, self))
+    def __ge__(self, o): return logical_not(less(self, o))
+
+
+def _error_tensor(err, like: Tensor | None = None) -> Tensor:
+    return Tensor(err=err, shape=like.shape if like is not None else (), dtype=like.dtype if like is not None else float32,
+                  device=like.device if like is not None else None)
+
+
+def from_torch(t: torch.Tensor) -> Tensor:
+    return Tensor(val=t, shape=t.shape, dtype=t.dtype, device=_dev_of(t))
+
+
+def tensor(data, dtype=None, device: Device | None = None) -> Tensor:
+    """Creates a realized leaf from Python data, a NumPy array or a torch tensor."""
+    device = device or default_device()
+    try:
+        if torch.is_tensor(data):
+            t = data.detach().to(device.torch)
+            if dtype is not None:
+                t = t.to(dtype)
+        else:
+            t = torch.as_tensor(data)
+            if dtype is None:
+                dtype = float32 if t.dtype.is_floating_point else (int32 if t.dtype != torch.bool else torch.bool)
+            t = t.to(dtype).to(device.torch)
+        return from_torch(t)
+    except Exception as exc:  # noqa: BLE001 - errors are values here
+        return _error_tensor(E.classify(exc))
+
+
+def _first_error(args) -> Any:
+    for a in args:
+        if isinstance(a, Tensor):
+            if a._err is not None:
+                return a._err
+        elif isinstance(a, (list, tuple)):
+            e = _first_error(a)
+            if e is not None:
+                return e
+    return None
+
+
+def _map_args(args, f):
+    out = []
+    for a in args:
+        if isinstance(a, Tensor):
+            out.append(f(a))
+        elif isinstance(a, (list, tuple)):
+            out.append(type(a)(_map_args(a, f)))
+        else:
+            out.append(a)
+    return out
+
+
+def _meta_of(t: Tensor) -> torch.Tensor:
+    return torch.empty(t.shape, dtype=t.dtype, device="meta")
+
+
+def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None) -> Tensor:
+    """Records ``fn(*args, **kw)``: propagates errors, infers shape/dtype on meta tensors."""
+    err = _first_error(args)
+    if err is not None:
+        return _error_tensor(err)
+    tensors = [a for a in _flatten(args) if isinstance(a, Tensor)]
+    if device is None:
+        device = tensors[0].device if tensors else default_device()
+        for t in tensors:
+            if t.device != device:
+                return _error_tensor(E.ErrDevice(f"{opname}: operands on {device} and {t.device}"))
+    try:
+        meta = fn(*_map_args(args, _meta_of), **kw)
+    except Exception as exc:  # noqa: BLE001
+        return _error_tensor(E.classify(exc))
+    if isinstance(meta, (tuple, list)):
+        outs = tuple(Tensor(fn=_pick(fn, i), args=tuple(args), kw=kw, shape=m.shape, dtype=m.dtype, device=device,
+                            opname=opname) for i, m in enumerate(meta))
+        if _EAGER:
+            for o in outs:
+                realize(o)
+        return outs
+    out = Tensor(fn=fn, args=tuple(args), kw=kw, shape=meta.shape, dtype=meta.dtype, device=device, opname=opname)
+    if _EAGER:
+        realize(out)
+    return out
+
+
+def _pick(fn, i):
+    def g(*a, **k):
+        return fn(*a, **k)[i]
+    return g
+
+
+def _flatten(args):
+    for a in args:
+        if isinstance(a, (list, tuple)):
+            yield from _flatten(a)
+        else:
+            yield a
+
+
+def _check_leaf(t: Tensor):
+    if t._donated:
+        raise E.ErrDonated("tensor was donated to an earlier schedule")
+    if t._stale is not None:
+        p, version = t._stale
+        if p._version != version:
+            raise E.ErrOverwritten("parameter value was overwritten by a later in-place step")
+
+
+def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bool = True) -> list:
+    """Evaluates the graph below ``roots`` (iteratively, memoised); returns torch tensors."""
+    memo = {} if memo is None else memo
+    for root in roots:
+        if root._err is not None:
+            raise root._err
+        stack = [root]
+        while stack:
+            t = stack[-1]
+            if id(t) in memo:
+                stack.pop()
+                continue
+            if t._fn is None or (reuse_cached and t._val is not None):
+                if t._val is None:
+                    raise E.ErrNilTensor("tensor has neither a value nor a producer")
+                _check_leaf(t)
+                memo[id(t)] = t._val
+                stack.pop()
+                continue
+            pending = [a for a in _flatten(t._args) if isinstance(a, Tensor) and id(a) not in memo]
+            if pending:
+                stack.extend(pending)
+                continue
+            vals = _map_args(t._args, lambda a: memo[id(a)])
+            try:
+                memo[id(t)] = t._fn(*vals, **t._kw)
+            except E.MimirError:
+                raise
+            except Exception as exc:  # noqa: BLE001
+                err = E.classify(exc)
+                t._err = err
+                raise err from exc
+            stack.pop()
+    return [memo[id(r)] for r in roots]
+
+
+def realize(*tensors: Tensor) -> None:
+    """Computes the given tensors in one pass (sched.Realize, internal/sched/sched.go:102-166)."""
+    todo = [t for t in tensors if t._val is None]
+    for t in tensors:
+        if t._err is not None:
+            raise t._err
+    if not todo:
+        for t in tensors:
+            if t._fn is None:
+                _check_leaf(t)
+        return
+    from .memory import reserve
+    reserve(todo)
+    with torch.no_grad():
+        vals = evaluate(todo)
+    for t, v in zip(todo, vals):
+        t._val = v.detach() if torch.is_tensor(v) else v
+        t._fn, t._args, t._kw = None, (), {}
+
+
+# ---------------------------------------------------------------------------
+# creators
+# ---------------------------------------------------------------------------
+def _creator(fn, shape, dtype, device, opname):
+    device = device or default_device()
+    shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
+    if any(s < 0 for s in shape):
+        return _error_tensor(E.ErrShape(f"{opname}: negative dimension in {shape}"))
+    return Tensor(fn=lambda: fn(shape, dtype, device.torch), shape=shape, dtype=dtype, device=device, opname=opname)
+
+
+def zeros(shape, dtype=float32, device=None):
+    return _creator(lambda s, d, dev: torch.zeros(s, dtype=d, device=dev), shape, dtype, device, "zeros")
+
+
+def ones(shape, dtype=float32, device=None):
+    return _creator(lambda s, d, dev: torch.ones(s, dtype=d, device=dev), shape, dtype, device, "ones")
+
+
+def full(shape, value, dtype=float32, device=None):
+    return _creator(lambda s, d, dev: torch.full(s, value, dtype=d, device=dev), shape, dtype, device, "full")
+
+
+def arange(n, dtype=int32, device=None):
+    return _creator(lambda s, d, dev: torch.arange(s[0], dtype=d, device=dev), (n,), dtype, device, "arange")
+
+
+def eye(n, dtype=float32, device=None):
+    return _creator(lambda s, d, dev: torch.eye(s[0], dtype=d, device=dev), (n, n), dtype, device, "eye")
+
+
+def rand(shape, seed: int = 0, dtype=float32, device=None):
+    """Uniform [0,1) from the Philox4x32-10 stream of ``seed`` (same values on every device)."""
+    from .random import philox_uniform
+    return _creator(lambda s, d, dev: philox_uniform(s, seed, dev).to(d), shape, dtype, device, "rand")
+
+
+def randn(shape, seed: int = 0, dtype=float32, device=None):
+    from .random import philox_normal
+    return _creator(lambda s, d, dev: philox_normal(s, seed, dev).to(d), shape, dtype, device, "randn")
+
+
+# ---------------------------------------------------------------------------
+# elementwise
+# ---------------------------------------------------------------------------
+def _lift(x, like: Tensor) -> Tensor:
+    """Python scalars take the dtype of the tensor operand (no promotion)."""
+    if isinstance(x, Tensor):
+        return x
+    if isinstance(x, (int, float, bool)):
+        dt = like.dtype
+        if isinstance(x, float) and not dt.is_floating_point:
+            dt = float32
+        return Tensor(val=torch.tensor(x, dtype=dt, device=like.device.torch), shape=(), dtype=dt, device=like.device)
+    return tensor(x, device=like.device)
+
+
+def _binary_dtype(a: Tensor, b: Tensor, opname: str):
+    """No implicit promotion except half (+) float32 -> float32 (tensor/tensor.go:48-76)."""
+    if a.dtype == b.dtype:
+        return a.dtype, None
+    pair = {a.dtype, b.dtype}
+    if float32 in pair and (pair - {float32}).issubset(set(_HALF)):
+        return float32, None
+    return None, E.ErrDType(f"{opname}: dtypes {a.dtype} and {b.dtype} do not mix (cast explicitly)")
+
+
+def _binary(opname, fn, out_bool=False):
+    def op(a, b):
+        like = a if isinstance(a, Tensor) else b
+        a, b = _lift(a, like), _lift(b, like)
+        if a._err is not None or b._err is not None:
+            return _error_tensor(a._err or b._err)
+        dt, err = _binary_dtype(a, b, opname)
+        if err is not None:
+            return _error_tensor(err)
+
+        def run(x, y):
+            if x.dtype != y.dtype:
+                x, y = x.to(dt), y.to(dt)
+            return fn(x, y)
+        return _node(run, (a, b), {}, opname)
+    op.__name__ = opname
+    return op
+
+
+def _int_div(x, y):
+    if not x.dtype.is_floating_point:
+        if y.device.type != "meta" and bool((y == 0).any()):
+            raise E.ErrDivideByZero("integer division by zero")
+        return torch.div(x, y, rounding_mode="trunc")
+    return x / y
+
+
+add = _binary("add", torch.add)
+sub = _binary("sub", torch.sub)
+mul = _binary("mul", torch.mul)
+div = _binary("div", _int_div)
+maximum = _binary("maximum", torch.maximum)
+minimum = _binary("minimum", torch.minimum)
+pow_ = _binary("pow", torch.pow)
+less = _binary("less", torch.lt)
+equal = _binary("equal", torch.eq)
+mod = _binary("mod", torch.remainder)
+
+
+def _unary(opname, fn):
+    def op(x: Tensor, *args, **kw):
+        return _node(lambda v: fn(v, *args, **kw), (x,), {}, opname)
+    op.__name__ = opname
+    return op
+
+
+neg = _unary("neg", torch.neg)
+exp = _unary("exp", torch.exp)
+log = _unary("log", torch.log)
+sqrt = _unary("sqrt", torch.sqrt)
+rsqrt = _unary("rsqrt", torch.rsqrt)
+sin = _unary("sin", torch.sin)
+cos = _unary("cos", torch.cos)
+tanh = _unary("tanh", torch.tanh)
+sigmoid = _unary("sigmoid", torch.sigmoid)
+relu = _unary("relu", torch.relu)
+abs_ = _unary("abs", torch.abs)
+sign = _unary("sign", torch.sign)
+floor = _unary("floor", torch.floor)
+ceil = _unary("ceil", torch.ceil)
+recip = _unary("recip", torch.reciprocal)
+erf = _unary("erf", torch.erf)
+erfinv = _unary("erfinv", torch.erfinv)
+log1p = _unary("log1p", torch.log1p)
+expm1 = _unary("expm1", torch.expm1)
+lgamma = _unary("lgamma", torch.lgamma)
+digamma = _unary("digamma", torch.digamma)
+logical_not = _unary("logical_not", torch.logical_not)
+silu = _unary("silu", torch.nn.functional.silu)
+softplus = _unary("softplus", torch.nn.functional.softplus)
+
+
+def trigamma(x):
+    return _node(lambda v: torch.polygamma(1, v), (x,), {}, "trigamma")
+
+
+def gelu(x, approximate: str = "tanh"):
+    """GELU; the tanh form is the default like the reference (tensor/elementwise.go:556-594)."""
+    return _node(lambda v: torch.nn.functional.gelu(v, approximate=approximate), (x,), {}, "gelu")
+
+
+def leaky_relu(x, slope=0.01):
+    return _node(lambda v: torch.nn.functional.leaky_relu(v, slope), (x,), {}, "leaky_relu")
+
+
+def clamp(x, lo=None, hi=None):
+    return _node(lambda v: torch.clamp(v, lo, hi), (x,), {}, "clamp")
+
+
+def where(cond, a, b):
+    like = a if isinstance(a, Tensor) else b if isinstance(b, Tensor) else cond
+    a, b = _lift(a, like), _lift(b, like)
+    return _node(lambda c, x, y: torch.where(c.bool(), x, y.to(x.dtype)), (cond, a, b), {}, "where")
+
+
+def cast(x, dtype):
+    return _node(lambda v: v.to(dtype), (x,), {}, "cast")
+
+
+def swiglu(gate, up):
+    return mul(silu(gate), up)
+
+
+# ---------------------------------------------------------------------------
+# movement
+# ---------------------------------------------------------------------------
+def reshape(x, shape):
+    return _node(lambda v: v.reshape(shape), (x,), {}, "reshape")
+
+
+def permute(x, dims):
+    return _node(lambda v: v.permute(dims), (x,), {}, "permute")
+
+
+def transpose(x, a=-1, b=-2):
+    return _node(lambda v: v.transpose(a, b), (x,), {}, "transpose")
+
+
+def expand(x, shape):
+    return _node(lambda v: v.expand(shape), (x,), {}, "expand")
+
+
+def squeeze(x, dim=None):
+    return _node(lambda v: v.squeeze() if dim is None else v.squeeze(dim), (x,), {}, "squeeze")
+
+
+def unsqueeze(x, dim):
+    return _node(lambda v: v.unsqueeze(dim), (x,), {}, "unsqueeze")
+
+
+def flip(x, dims):
+    return _node(lambda v: v.flip(dims), (x,), {}, "flip")
+
+
+def pad(x, pads, value=0.0):
+    """``pads`` = (before, after) per axis, first axis first."""
+    flat = []
+    for before, after in reversed(list(pads)):
+        flat += [before, after]
+    return _node(lambda v: torch.nn.functional.pad(v, flat, value=value), (x,), {}, "pad")
+
+
+def shrink(x, ranges):
+    """Keeps ``[lo, hi)`` of every axis (reference primitive ``Shrink``)."""
+    def run(v):
+        for ax, (lo, hi) in enumerate(ranges):
+            if lo < 0 or hi > v.shape[ax] or lo > hi:
+                raise E.ErrIndex(f"shrink: range [{lo},{hi}) outside axis {ax} of size {v.shape[ax]}")
+            v = v.narrow(ax, lo, hi - lo)
+        return v
+    return _node(run, (x,), {}, "shrink")
+
+
+def getitem(x, idx):
+    if isinstance(idx, Tensor):
+        return gather_rows(x, idx)
+    return _node(lambda v: v[idx], (x,), {}, "getitem")
+
+
+def cat(xs, dim=0):
+    return _node(lambda vs: torch.cat(list(vs), dim), (list(xs),), {}, "cat")
+
+
+def stack(xs, dim=0):
+    return _node(lambda vs: torch.stack(list(vs), dim), (list(xs),), {}, "stack")
+
+
+def split(x, sizes, dim=0):
+    return _node(lambda v: tuple(torch.split(v, sizes, dim)), (x,), {}, "split")
+
+
+def contiguous(x):
+    return _node(lambda v: v.contiguous(), (x,), {}, "contiguous")
+
+
+def _check_index(i, n, opname):
+    if i.device.type != "meta" and i.numel() and (int(i.min()) < 0 or int(i.max()) >= n):
+        raise E.ErrIndex(f"{opname}: index outside [0, {n})")
+
+
+def gather_rows(x, index):
+    """``x[index]`` along axis 0 (embedding lookup); out-of-range indices are ErrIndex."""
+    def run(v, i):
+        _check_index(i, v.shape[0], "gather")
+        return v[i.long()]
+    return _node(run, (x, index), {}, "gather")
+
+
+def gather(x, dim, index):
+    def run(v, i):
+        _check_index(i, v.shape[dim], "gather")
+        return torch.gather(v, dim, i.long())
+    return _node(run, (x, index), {}, "gather")
+
+
+def scatter_add(x, dim, index, src):
+    def run(v, i, s):
+        _check_index(i, v.shape[dim], "scatter_add")
+        return v.scatter_add(dim, i.long(), s)
+    return _node(run, (x, index, src), {}, "scatter_add")
+
+
+def scatter(x, dim, index, src):
+    def run(v, i, s):
+        _check_index(i, v.shape[dim], "scatter")
+        return v.scatter(dim, i.long(), s)
+    return _node(run, (x, index, src), {}, "scatter")
+
+
+def slice_scatter(x, src, dim, start, end):
+    return _node(lambda v, s: torch.slice_scatter(v, s, dim, start, end), (x, src), {}, "slice_scatter")
+
+
+def unfold(x, kernel, stride=1, padding=0, dilation=1):
+    return _node(lambda v: torch.nn.functional.unfold(v, kernel, dilation, padding, stride), (x,), {}, "unfold")
+
+
+def fold(x, output_size, kernel, stride=1, padding=0, dilation=1):
+    return _node(lambda v: torch.nn.functional.fold(v, output_size, kernel, dilation, padding, stride), (x,), {}, "fold")
+
+
+def one_hot(index, classes, dtype=float32):
+    def run(i):
+        _check_index(i, classes, "one_hot")
+        return torch.nn.functional.one_hot(i.long(), classes).to(dtype)
+    return _node(run, (index,), {}, "one_hot")
+
+
+# ---------------------------------------------------------------------------
+# reductions: half inputs accumulate in fp32 and return float32 (tensor/tensor.go:68-69)
+# ---------------------------------------------------------------------------
+def _reduce(opname, fn):
+    def op(x, dim=None, keepdim=False):
+        def run(v):
+            if v.dtype in _HALF:
+                v = v.float()
+            return fn(v, dim, keepdim)
+        return _node(run, (x,), {}, opname)
+    op.__name__ = opname
+    return op
+
+
+sum_ = _reduce("sum", lambda v, d, k: v.sum() if d is None else v.sum(d, keepdim=k))
+mean = _reduce("mean", lambda v, d, k: v.mean() if d is None else v.mean(d, keepdim=k))
+max_ = _reduce("max", lambda v, d, k: v.max() if d is None else v.amax(d, keepdim=k))
+min_ = _reduce("min", lambda v, d, k: v.min() if d is None else v.amin(d, keepdim=k))
+var = _reduce("var", lambda v, d, k: v.var(unbiased=False) if d is None else v.var(d, unbiased=False, keepdim=k))
+logsumexp = _reduce("logsumexp", lambda v, d, k: torch.logsumexp(v, tuple(range(v.ndim)) if d is None else d, keepdim=k))
+
+
+def argmax(x, dim=-1):
+    return _node(lambda v: v.argmax(dim).to(int32), (x,), {}, "argmax")
+
+
+def softmax(x, dim=-1):
+    return _node(lambda v: torch.softmax(v.float(), dim).to(v.dtype), (x,), {}, "softmax")
+
+
+def log_softmax(x, dim=-1):
+    return _node(lambda v: torch.log_softmax(v.float(), dim).to(v.dtype), (x,), {}, "log_softmax")
+
+
+def cumsum(x, dim=-1):
+    return _node(lambda v: torch.cumsum(v, dim), (x,), {}, "cumsum")
+
+
+def cummax(x, dim=-1):
+    return _node(lambda v: torch.cummax(v, dim).values, (x,), {}, "cummax")
+
+
+def logcumsumexp(x, dim=-1):
+    return _node(lambda v: torch.logcumsumexp(v, dim), (x,), {}, "logcumsumexp")
+
+
+def sort(x, dim=-1, descending=False):
+    return _node(lambda v: tuple(torch.sort(v, dim, descending)), (x,), {}, "sort")
+
+
+def argsort(x, dim=-1, descending=False):
+    return _node(lambda v: torch.argsort(v, dim, descending).to(int32), (x,), {}, "argsort")
+
+
+def topk(x, k, dim=-1):
+    return _node(lambda v: tuple(torch.topk(v, k, dim)), (x,), {}, "topk")
+
+
+# ---------------------------------------------------------------------------
+# products
+# ---------------------------------------------------------------------------
+def _use_native(*vals) -> bool:
+    return all(v.is_cuda and v.dtype == bfloat16 for v in vals)
+
+
+def matmul(a, b):
+    """``a @ b`` with batch broadcasting; bf16 CUDA operands run on the tcgen05 GEMM."""
+    def run(x, y):
+        if x.dtype != y.dtype:
+            raise E.ErrDType(f"matmul: dtypes {x.dtype} and {y.dtype} differ")
+        if _use_native(x, y) and x.dim() == 2 and y.dim() == 2 and x.shape[0] >= 128 and y.shape[1] % 8 == 0 \
+                and x.shape[1] % 8 == 0:
+            from ..ops.gemm import gemm
+            return gemm(x.contiguous(), y.contiguous(), b_mn=True)
+        return x @ y
+    return _node(run, (a, b), {}, "matmul")
+
+
+def matmul_t(x, w, bias=None):
+    """``x @ w^T (+ bias)``: the Linear product with the weight stored [out, in]
+    (nn/layers.go:49-55).  ``w`` may be a quantized buffer."""
+    from ..io.mim import QuantizedTensor
+    if isinstance(w, QuantizedTensor):
+        from ..ops.quant import qmatmul_t
+        return _node(lambda v: qmatmul_t(v, w), (x,), {}, "qmatmul")
+
+    def run(v, wt, *b):
+        if v.dtype != wt.dtype:
+            raise E.ErrDType(f"linear: input {v.dtype} and weight {wt.dtype} differ")
+        lead = v.shape[:-1]
+        if _use_native(v, wt) and v.numel() // v.shape[-1] >= 128 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0:
+            from ..ops.gemm import gemm
+            out = gemm(v.reshape(-1, v.shape[-1]).contiguous(), wt.contiguous(), bias=b[0] if b else None)
+            return out.view(*lead, wt.shape[0])
+        return torch.nn.functional.linear(v, wt, b[0] if b else None)
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(run, args, {}, "linear")
+
+
+def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
+    """Fused attention over ``[B, H, T, D]`` tensors (tensor/attention.go:81-253): grouped-query
+    heads when ``k``/``v`` have fewer heads, optional causal mask with offset, additive or
+    boolean mask; never materialises the score matrix on the CUDA bf16 path."""
+    args = (q, k, v) + ((mask,) if mask is not None else ())
+
+    def run(qv, kv, vv, *m):
+        B, Hq, Tq, D = qv.shape
+        Hk, Tk = kv.shape[1], kv.shape[2]
+        if Hq % Hk:
+            raise E.ErrShape(f"attention: {Hq} query heads are not a multiple of {Hk} key heads")
+        off = Tk - Tq if causal_offset is None else causal_offset
+        if not m and _use_native(qv, kv, vv) and D in (64, 128) and qv.device.type == "cuda" \
+                and not torch.is_grad_enabled():
+            from ..ops.attention import attention_fwd
+            out = torch.empty(B, Tq, Hq, D, dtype=qv.dtype, device=qv.device)
+            attention_fwd(qv.transpose(1, 2).contiguous(), kv.transpose(1, 2).contiguous(),
+                          vv.transpose(1, 2).contiguous(), out, None, causal=causal, offset=off, scale=scale)
+            return out.transpose(1, 2)
+        if Hk != Hq:
+            kv = kv.repeat_interleave(Hq // Hk, 1)
+            vv = vv.repeat_interleave(Hq // Hk, 1)
+        am = None
+        if causal:
+            i = torch.arange(Tq, device=qv.device)[:, None]
+            j = torch.arange(Tk, device=qv.device)[None]
+            am = torch.zeros(Tq, Tk, device=qv.device, dtype=qv.dtype).masked_fill(j > i + off, float("-inf"))
+        if m:
+            mm = m[0]
+            if mm.dtype == torch.bool:
+                mm = torch.zeros_like(mm, dtype=qv.dtype).masked_fill(~mm, float("-inf"))
+            am = mm if am is None else am + mm
+        return torch.nn.functional.scaled_dot_product_attention(qv, kv, vv, attn_mask=am, scale=scale)
+    return _node(run, args, {}, "attention")
+
+
+def conv2d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(lambda v, wt, *b: torch.nn.functional.conv2d(v, wt, b[0] if b else None, stride, padding, dilation, groups),
+                 args, {}, "conv2d")
+
+
+def conv1d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(lambda v, wt, *b: torch.nn.functional.conv1d(v, wt, b[0] if b else None, stride, padding, dilation, groups),
+                 args, {}, "conv1d")
+
+
+def conv3d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(lambda v, wt, *b: torch.nn.functional.conv3d(v, wt, b[0] if b else None, stride, padding, dilation, groups),
+                 args, {}, "conv3d")
+
+
+def conv_transpose2d(x, w, bias=None, stride=1, padding=0, output_padding=0):
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(lambda v, wt, *b: torch.nn.functional.conv_transpose2d(v, wt, b[0] if b else None, stride, padding, output_padding),
+                 args, {}, "conv_transpose2d")
+
+
+def conv_transpose1d(x, w, bias=None, stride=1, padding=0, output_padding=0):
+    args = (x, w) + ((bias,) if bias is not None else ())
+    return _node(lambda v, wt, *b: torch.nn.functional.conv_transpose1d(v, wt, b[0] if b else None, stride, padding, output_padding),
+                 args, {}, "conv_transpose1d")
+
+
+def max_pool2d(x, kernel, stride=None, padding=0):
+    return _node(lambda v: torch.nn.functional.max_pool2d(v, kernel, stride, padding), (x,), {}, "max_pool2d")
+
+
+def avg_pool2d(x, kernel, stride=None, padding=0):
+    return _node(lambda v: torch.nn.functional.avg_pool2d(v, kernel, stride, padding), (x,), {}, "avg_pool2d")
+
+
+def upsample_nearest(x, scale):
+    return _node(lambda v: torch.nn.functional.interpolate(v, scale_factor=scale, mode="nearest"), (x,), {}, "upsample")
