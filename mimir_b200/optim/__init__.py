@@ -251,11 +251,16 @@ def Polynomial(lr, epochs, power): return lambda e: lr * (1 - min(e, epochs) / m
 
 
 def OneCycle(peak, epochs, warm=0.3):
-    up = max(1, int(epochs * warm))
+    """Cosine ramp from peak/25 to the peak over ``warm * epochs - 1`` epochs, then cosine down
+    to peak / 25e4 at the last epoch."""
+    start, end = peak / 25, peak / 25 / 1e4
+    up = warm * epochs - 1
+
+    def cos(a, b, f):
+        return b + (a - b) * (1 + math.cos(math.pi * f)) / 2
 
     def f(e):
-        if e < up:
-            return peak / 25 + (peak - peak / 25) * e / up
-        frac = (e - up) / max(1, epochs - up)
-        return peak / 25e3 + 0.5 * (peak - peak / 25e3) * (1 + math.cos(math.pi * min(frac, 1.0)))
+        if e <= up:
+            return cos(start, peak, e / up)
+        return cos(peak, end, (e - up) / (epochs - 1 - up))
     return f

@@ -664,7 +664,7 @@ sum_ = _reduce("sum", lambda v, d, k: v.sum() if d is None else v.sum(d, keepdim
 mean = _reduce("mean", lambda v, d, k: v.mean() if d is None else v.mean(d, keepdim=k))
 max_ = _reduce("max", lambda v, d, k: v.max() if d is None else v.amax(d, keepdim=k))
 min_ = _reduce("min", lambda v, d, k: v.min() if d is None else v.amin(d, keepdim=k))
-var = _reduce("var", lambda v, d, k: v.var(unbiased=False) if d is None else v.var(d, unbiased=False, keepdim=k))
+var = _reduce("var", lambda v, d, k: v.var(unbiased=True) if d is None else v.var(d, unbiased=True, keepdim=k))  # sample variance, like the reference
 logsumexp = _reduce("logsumexp", lambda v, d, k: torch.logsumexp(v, tuple(range(v.ndim)) if d is None else d, keepdim=k))
 
 
