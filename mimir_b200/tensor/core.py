@@ -324,6 +324,8 @@ def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bo
             except E.MimirError:
                 raise
             except Exception as exc:  # noqa: BLE001
+                if type(exc).__module__.startswith("torch.utils.checkpoint"):
+                    raise  # control flow of activation recomputation, not a failure
                 err = E.classify(exc)
                 t._err = err
                 raise err from exc
