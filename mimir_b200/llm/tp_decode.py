@@ -1,0 +1,245 @@
+"""Tensor-parallel quantized Llama decoding (W4A8: Q4_0 weights, Q8_0 activations,
+fp16 KV cache), one process per GPU.
+
+The reference decodes on one device with a recorded CPU step (llm/decode.go:79-160)
+and may only replicate quantized tensors on a mesh (tensor/mesh.go:389-391); this
+engine shards every block Megatron-style (nn/shard.go:102-158: QKV and gate/up
+split by output rows, attention-out and down split by input columns) and runs the
+whole decode step as one CUDA graph of native kernels:
+
+  RMSNorm+quantise -> W4A8 GEMV (QKV) -> RoPE -> KV write -> decode attention ->
+  quantise -> W4A8 GEMV fused with the all-reduce (+residual) -> RMSNorm+quantise ->
+  W4A8 GEMV (gate|up) -> SwiGLU+quantise -> W4A8 GEMV fused with the all-reduce.
+
+The all-reduce inside the GEMV kernel is one-shot over NVLink peer memory
+(``csrc/quant_sm100.cu``); positions live in device memory so the same graph serves
+every step.  Prompts run through bf16 tcgen05 GEMMs on dequantised weights.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import _native
+from ..ops import kernels as K
+from ..ops import quant_cuda as Q
+from ..ops._util import ptr, stream_ptr
+from ..parallel.peer import SymmetricBuffer
+
+
+@dataclass
+class LlamaConfig:
+    n_layer: int = 32
+    d_model: int = 4096
+    n_head: int = 32
+    n_kv_head: int = 8
+    ffn: int = 14336
+    vocab: int = 128256
+    head_dim: int = 128
+    rope_base: float = 500000.0
+    eps: float = 1e-5
+    ctx: int = 8192
+
+    @staticmethod
+    def llama3_8b() -> "LlamaConfig":
+        return LlamaConfig()
+
+    @staticmethod
+    def tiny() -> "LlamaConfig":
+        return LlamaConfig(n_layer=2, d_model=256, n_head=4, n_kv_head=2, ffn=512, vocab=1024, head_dim=64, ctx=256)
+
+
+class TPDecoder:
+    def __init__(self, cfg: LlamaConfig, rank: int, world: int, batch: int, cap: int, seed: int = 0,
+                 device=None, weights: dict | None = None):
+        self.cfg, self.rank, self.world, self.B, self.cap = cfg, rank, world, batch, cap
+        self.dev = torch.device(device or f"cuda:{torch.cuda.current_device()}")
+        d, D = cfg.d_model, cfg.head_dim
+        if cfg.n_head % world or cfg.n_kv_head % world or cfg.ffn % (world * 32) or cfg.vocab % (world * 8):
+            raise ValueError("heads, kv heads, ffn/32 and vocab/8 must divide by the tensor-parallel size")
+        self.Hq, self.Hk, self.F = cfg.n_head // world, cfg.n_kv_head // world, cfg.ffn // world
+        self.Vl = cfg.vocab // world
+        self.qkv_n = (self.Hq + 2 * self.Hk) * D
+        self._init_weights(seed, weights)
+        B = batch
+        bf, f32 = dict(dtype=torch.bfloat16, device=self.dev), dict(dtype=torch.float32, device=self.dev)
+        self.h = torch.zeros(B, d, **bf)
+        self.h1 = torch.zeros(B, d, **bf)
+        self.qkv = torch.zeros(B, self.qkv_n, **bf)
+        self.att = torch.zeros(B, self.Hq * D, **bf)
+        self.gu = torch.zeros(B, 2 * self.F, **bf)
+        kmax = max(d, self.F, self.Hq * D)
+        self.xq = torch.zeros(B, kmax, dtype=torch.int8, device=self.dev)
+        self.xs = torch.zeros(B, kmax // 32, **f32)
+        self.kc = torch.zeros(cfg.n_layer, B, self.Hk, cap, D, dtype=torch.float16, device=self.dev)
+        self.vc = torch.zeros_like(self.kc)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)      # write position
+        self.len = torch.ones(1, dtype=torch.int32, device=self.dev)       # keys visible = pos + 1
+        self.pos_rows = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        self.tokens = torch.zeros(B, dtype=torch.int64, device=self.dev)
+        self.logits_local = torch.zeros(B, self.Vl, **f32)
+        inv = 1.0 / (cfg.rope_base ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+        self.freqs = inv.float().to(self.dev)
+        # symmetric memory: two rotating partial buffers, gathered logits, signal pad
+        self.part = [SymmetricBuffer(B * d * 4, rank, world) for _ in range(2)]
+        self.logits_all = SymmetricBuffer(world * B * self.Vl * 4, rank, world)
+        self.sig = SymmetricBuffer(4096 * 4, rank, world)
+        self.epochs = torch.zeros(8, dtype=torch.int32, device=self.dev)
+        self.counters = torch.zeros(8, dtype=torch.int32, device=self.dev)
+        self._part_arr = [p.ptr_array() for p in self.part]
+        self._sig_arr = self.sig.ptr_array()
+        self._logits_arr = self.logits_all.ptr_array()
+        self.graph = None
+        self.launches_per_step = 0
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ weights
+    def _init_weights(self, seed: int, weights):
+        cfg, d, D = self.cfg, self.cfg.d_model, self.cfg.head_dim
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+
+        def rnd(n, k, std):
+            return torch.randn(n, k, generator=g, device=self.dev) * std
+
+        def shard_rows(full, parts, sizes):
+            """Rows of a [sum(sizes) * world... ] matrix that belong to this rank, per logical part."""
+            out, off = [], 0
+            for size in sizes:
+                per = size // self.world
+                out.append(full[off + self.rank * per: off + (self.rank + 1) * per])
+                off += size
+            return torch.cat(out, 0)
+
+        self.layers = []
+        std = 0.02
+        for l in range(cfg.n_layer):
+            if weights is not None:
+                wqkv, wo, wgu, wd = (weights[f"blk.{l}.{n}"] for n in ("qkv", "o", "gate_up", "down"))
+                an, fn = weights[f"blk.{l}.attn_norm"], weights[f"blk.{l}.ffn_norm"]
+            else:  # every rank draws the same full matrices from the seed, then keeps its shard
+                wqkv = rnd((cfg.n_head + 2 * cfg.n_kv_head) * D, d, std)
+                wo = rnd(d, cfg.n_head * D, std / math.sqrt(2 * cfg.n_layer))
+                wgu = rnd(2 * cfg.ffn, d, std)
+                wd = rnd(d, cfg.ffn, std / math.sqrt(2 * cfg.n_layer))
+                an = torch.ones(d, device=self.dev)
+                fn = torch.ones(d, device=self.dev)
+            qkv_l = shard_rows(wqkv, 3, [cfg.n_head * D, cfg.n_kv_head * D, cfg.n_kv_head * D])
+            gu_l = shard_rows(wgu, 2, [cfg.ffn, cfg.ffn])
+            o_l = wo[:, self.rank * self.Hq * D: (self.rank + 1) * self.Hq * D]
+            d_l = wd[:, self.rank * self.F: (self.rank + 1) * self.F]
+            self.layers.append(dict(qkv=Q.PlanarQ4.quantize(qkv_l), o=Q.PlanarQ4.quantize(o_l.contiguous()),
+                                    gate_up=Q.PlanarQ4.quantize(gu_l), down=Q.PlanarQ4.quantize(d_l.contiguous()),
+                                    attn_norm=an.bfloat16(), ffn_norm=fn.bfloat16()))
+            del wqkv, wo, wgu, wd
+        if weights is not None:
+            emb, head, onorm = weights["token_embd"], weights["output"], weights["output_norm"]
+        else:
+            emb = rnd(cfg.vocab, d, std)
+            head = rnd(cfg.vocab, d, std)
+            onorm = torch.ones(d, device=self.dev)
+        self.embed = emb.bfloat16()
+        self.head = Q.PlanarQ4.quantize(head[self.rank * self.Vl: (self.rank + 1) * self.Vl])
+        self.out_norm = onorm.bfloat16()
+
+    # ------------------------------------------------------------- primitives
+    def _gemv_allreduce(self, w: Q.PlanarQ4, k: int, residual, out, slot: int):
+        lib = Q._L()
+        rc = lib.mimir_q4_gemv_allreduce(ptr(w.scales), ptr(w.quants), ptr(self.xq), ptr(self.xs),
+                                         self._part_arr[slot], self._sig_arr, self.epochs[slot:].data_ptr(),
+                                         self.counters[slot:].data_ptr(), ptr(residual), ptr(out), w.N, k, self.B,
+                                         self.rank, self.world, slot, stream_ptr())
+        _native.check(rc, "q4_gemv_allreduce")
+
+    def _decode_layers(self):
+        cfg, d, D, B = self.cfg, self.cfg.d_model, self.cfg.head_dim, self.B
+        scale = 1.0 / math.sqrt(D)
+        lib = Q._L()
+        for l, w in enumerate(self.layers):
+            Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=w["attn_norm"], eps=cfg.eps)
+            Q.q4_gemv(w["qkv"], self.xq, self.xs, self.qkv)
+            K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
+            _native.check(lib.mimir_kv_cache_write(ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D,
+                                                   ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hk, D, self.cap,
+                                                   ptr(self.pos), stream_ptr()), "kv_write")
+            _native.check(lib.mimir_attn_decode(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.att), B,
+                                                self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n, stream_ptr()),
+                          "attn_decode")
+            Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0)
+            self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0)
+            Q.quantize_act(self.h1, self.xq, self.xs, d, mode=1, gamma=w["ffn_norm"], eps=cfg.eps)
+            Q.q4_gemv(w["gate_up"], self.xq, self.xs, self.gu)
+            Q.quantize_act(self.gu, self.xq, self.xs, self.F, mode=2)
+            self._gemv_allreduce(w["down"], self.F, self.h1, self.h, 1)
+
+    def _device_step(self):
+        """One decode step for the tokens in ``self.tokens``; leaves the next tokens there."""
+        cfg, d = self.cfg, self.cfg.d_model
+        lib = Q._L()
+        K.embedding_fwd(self.tokens, self.embed, None, self.h, 1)
+        self._decode_layers()
+        Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=self.out_norm, eps=cfg.eps)
+        Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local)
+        _native.check(lib.mimir_peer_allgather(ptr(self.logits_local), self._logits_arr, self._sig_arr,
+                                               self.epochs[2:].data_ptr(), self.counters[2:].data_ptr(),
+                                               self.logits_local.numel() * 4, self.rank, self.world, 2, stream_ptr()),
+                      "allgather")
+        full = self.logits_all.view(torch.float32).view(self.world, self.B, self.Vl)
+        best = full.permute(1, 0, 2).reshape(self.B, -1).argmax(-1)  # greedy sampling on the device
+        self.tokens.copy_(best)
+        self.pos.add_(1)
+        self.len.add_(1)
+        self.pos_rows.add_(1)
+
+    # ------------------------------------------------------------------ public
+    def reset(self):
+        self.pos.zero_()
+        self.len.fill_(1)
+        self.pos_rows.zero_()
+
+    def step(self) -> None:
+        """Runs (or replays) one decode step; no host synchronisation."""
+        lib = _native.lib()
+        if self.graph is None:
+            if getattr(self, "_warm", 0) < 2:
+                self._warm = getattr(self, "_warm", 0) + 1
+                before = lib.mimir_launch_count()
+                self._device_step()
+                self.launches_per_step = lib.mimir_launch_count() - before
+                return
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = lib.mimir_launch_count()
+            with torch.cuda.graph(g):
+                self._device_step()
+            self.launches_per_step = lib.mimir_launch_count() - before
+            self.graph = g
+        self.graph.replay()
+        lib.mimir_launch_count_add(self.launches_per_step)
+
+    def prefill(self, prompt: torch.Tensor) -> None:
+        """Feeds ``prompt`` [B, T] token by token through the decode path (fills the cache and
+        leaves the first generated token in ``self.tokens``)."""
+        for t in range(prompt.shape[1]):
+            self.tokens.copy_(prompt[:, t].to(self.dev))
+            self.step()
+
+    def generate(self, prompt: torch.Tensor, n: int) -> torch.Tensor:
+        self.reset()
+        self.prefill(prompt)
+        out = [self.tokens.clone()]
+        for _ in range(n - 1):
+            self.step()
+            out.append(self.tokens.clone())
+        return torch.stack(out, 1)
+
+    def close(self):
+        torch.cuda.synchronize()
+        if self.world > 1:
+            torch.distributed.barrier()
+        for b in (*self.part, self.logits_all, self.sig):
+            b.close()

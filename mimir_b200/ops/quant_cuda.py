@@ -1,0 +1,88 @@
+"""ctypes wrappers over ``csrc/quant_sm100.cu``."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ._util import ptr, stream_ptr
+
+_done = False
+
+
+def _L():
+    global _done
+    lib = _native.lib()
+    if not _done:
+        P, I, F, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+        PP = ctypes.POINTER(ctypes.c_void_p)
+        for name, args in {
+            "mimir_dequant": [I, P, P, L, P],
+            "mimir_q4_0_to_planar": [P, P, P, L, P],
+            "mimir_quantize_act": [P, I, P, P, P, P, I, I, I, F, P],
+            "mimir_q4_gemv": [P, P, P, P, P, I, I, I, I, I, P],
+            "mimir_q4_gemv_allreduce": [P, P, P, P, PP, PP, P, P, P, P, I, I, I, I, I, I, P],
+            "mimir_oneshot_allreduce": [PP, PP, P, P, P, P, I, I, I, I, I, P],
+            "mimir_attn_decode": [P, P, P, P, I, I, I, I, I, P, F, I, P],
+            "mimir_kv_cache_write": [P, I, I, I, P, P, I, I, I, I, P, P],
+            "mimir_f32_to_bf16": [P, P, L, P],
+            "mimir_q4_planar_to_bf16": [P, P, P, L, P],
+            "mimir_peer_allgather": [P, PP, PP, P, P, L, I, I, I, P],
+        }.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = I, args
+        lib.mimir_q_set_peer_wait_ms.argtypes = [L]
+        lib.mimir_q_set_peer_wait_ms.restype = None
+        _done = True
+    return lib
+
+
+def dequantize(code: int, raw: torch.Tensor, n: int) -> torch.Tensor:
+    out = torch.empty(n, dtype=torch.float32, device=raw.device)
+    _native.check(_L().mimir_dequant(code, ptr(raw), ptr(out), n, stream_ptr()), "dequant")
+    return out
+
+
+class PlanarQ4:
+    """Q4_0 weight matrix [N, K] in the GPU layout: fp16 scales [N, K/32] + 16-byte quants."""
+
+    def __init__(self, scales: torch.Tensor, quants: torch.Tensor, N: int, K: int):
+        self.scales, self.quants, self.N, self.K = scales, quants, N, K
+
+    @staticmethod
+    def from_ggml(raw: torch.Tensor, N: int, K: int) -> "PlanarQ4":
+        nb = N * K // 32
+        raw = raw.contiguous()
+        scales = torch.empty(nb, dtype=torch.float16, device=raw.device)
+        quants = torch.empty(nb * 16, dtype=torch.uint8, device=raw.device)
+        _native.check(_L().mimir_q4_0_to_planar(ptr(raw), ptr(scales), ptr(quants), nb, stream_ptr()), "to_planar")
+        return PlanarQ4(scales, quants, N, K)
+
+    @staticmethod
+    def quantize(w: torch.Tensor) -> "PlanarQ4":
+        from .quant import quantize_q4_0
+        N, K = w.shape
+        return PlanarQ4.from_ggml(quantize_q4_0(w).reshape(-1), N, K)
+
+    def to_bf16(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        out = torch.empty(self.N, self.K, dtype=torch.bfloat16, device=self.scales.device) if out is None else out
+        _native.check(_L().mimir_q4_planar_to_bf16(ptr(self.scales), ptr(self.quants), ptr(out),
+                                                   self.N * self.K // 32, stream_ptr()), "planar_to_bf16")
+        return out
+
+    def nbytes(self) -> int:
+        return self.scales.numel() * 2 + self.quants.numel()
+
+
+def quantize_act(x, xq, xs, K, mode=0, gamma=None, y=None, eps=1e-5):
+    rows = xq.shape[0]
+    _native.check(_L().mimir_quantize_act(ptr(x), int(x.dtype == torch.float32), ptr(gamma), ptr(y), ptr(xq), ptr(xs),
+                                          rows, K, mode, eps, stream_ptr()), "quantize_act")
+
+
+def q4_gemv(w: PlanarQ4, xq, xs, out):
+    B = xq.shape[0]
+    _native.check(_L().mimir_q4_gemv(ptr(w.scales), ptr(w.quants), ptr(xq), ptr(xs), ptr(out),
+                                     int(out.dtype == torch.bfloat16), w.N, w.K, B, out.stride(0), stream_ptr()), "q4_gemv")
+    return out

@@ -111,3 +111,23 @@ def test_attention_variants():
         ins, want = _case(m, "sdpa_mask")
         got = T.attention(t(ins[0]), t(ins[1]), t(ins[2]), mask=t(ins[3])).data()
         assert torch.allclose(got, want, rtol=2e-5, atol=2e-6)
+
+
+def test_quantized_formats_dequantize_bit_exact():
+    from mimir_b200.ops import quant as Q
+    with _open("quant") as m:
+        for case, code in (("q8_0_dequantize", Q.Q8_0), ("q4_K_dequantize", Q.Q4_K), ("q6_K_dequantize", Q.Q6_K)):
+            raw, want = m.tensor(f"{case}/in0"), m.tensor(f"{case}/out")
+            got = Q.dequantize_raw(code, raw, want.numel()).view(want.shape)
+            assert torch.equal(got, want), case
+        for case, code in (("q8_0_matmul", Q.Q8_0), ("q4_K_matmul", Q.Q4_K), ("q6_K_matmul", Q.Q6_K)):
+            x, raw, want = m.tensor(f"{case}/in0"), m.tensor(f"{case}/in1"), m.tensor(f"{case}/out")
+            w = Q.dequantize_raw(code, raw, raw.shape[0] * x.shape[-1]).view(raw.shape[0], x.shape[-1])
+            assert torch.allclose(x @ w.t(), want, rtol=2e-5, atol=2e-5), case
+    # Q4_0 / Q8_0 quantise -> dequantise round trip stays within half a step
+    x = torch.randn(4, 64)
+    for quant, code, steps, bound in ((Q.quantize_q8_0, Q.Q8_0, 127, 0.56), (Q.quantize_q4_0, Q.Q4_0, 8, 1.01)):
+        back = Q.dequantize_raw(code, quant(x), x.numel()).view(x.shape)
+        step = x.reshape(-1, 32).abs().amax(1, keepdim=True) / steps
+        # half a step (+ fp16 rounding of the scale); Q4_0's range [-8, 7] clips one extreme by up to a step
+        assert ((back - x).reshape(-1, 32).abs() <= step * bound + 1e-5).all()

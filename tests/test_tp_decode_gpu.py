@@ -1,0 +1,42 @@
+"""Tensor-parallel W4A8 decoding against an fp32 forward pass with the dequantised weights."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(world):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(HERE, "_tp_worker.py")
+    if world == 1:
+        cmd = [sys.executable, worker]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", "29541", worker]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-3000:]
+    return [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]
+
+
+def test_decode_single_gpu_matches_reference():
+    (r,) = _run(1)
+    assert r["err"] == 0
+    assert r["cos"] > 0.995 and r["rel"] < 0.08, r
+    assert r["launches"] > 0
+
+
+def test_decode_tp2_matches_reference_and_ranks_agree():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2)
+    assert len(res) == 2
+    for r in res:
+        assert r["err"] == 0
+        assert r["cos"] > 0.995 and r["rel"] < 0.08, r
+    assert res[0]["gen"] == res[1]["gen"]
