@@ -540,9 +540,16 @@ MIMIR_API int mimir_q4_gemv_allreduce(const void* ws, const void* wq, const void
   a.residual = static_cast<const __nv_bfloat16*>(residual);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.rank = rank; a.world = world; a.slot = slot; a.wait_ns = g_q_wait_ns;
-  // every block must be resident at once (blocks wait on each other's flags)
+  // every block must be resident at once (blocks wait on flags that the last block of the
+  // grid sets): size the grid from the occupancy the kernel really gets
+  static int blocks_per_sm = 0;
+  if (blocks_per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, q4_gemv_allreduce_kernel, 256, 0) != cudaSuccess || n < 1) n = 1;
+    blocks_per_sm = n;
+  }
   int grid = ceil_div(N, 8);
-  const int cap = sm_count() * 4;
+  const int cap = sm_count() * blocks_per_sm;
   if (grid > cap) grid = cap;
   q4_gemv_allreduce_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(ws), static_cast<const uint4*>(wq),
                                                  static_cast<const int8_t*>(xq), xs, a, N, K, B, error_word_dev());
@@ -563,7 +570,7 @@ MIMIR_API int mimir_oneshot_allreduce(void* const* partial, void* const* sig, vo
   a.residual = static_cast<const __nv_bfloat16*>(residual);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.rank = rank; a.world = world; a.slot = slot; a.wait_ns = g_q_wait_ns;
-  oneshot_allreduce_kernel<<<sm_count() * 2, 256, 0, st>>>(a, B, N, error_word_dev());
+  oneshot_allreduce_kernel<<<sm_count(), 256, 0, st>>>(a, B, N, error_word_dev());  // one resident block per SM
   count_launch();
   return 0;
 }

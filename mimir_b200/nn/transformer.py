@@ -91,6 +91,9 @@ class SelfAttention(Module):
         self.head_dim = head_dim or dim // heads
         self.causal, self.rope = causal, rope
         self.qkv = Linear(dim, (self.heads + 2 * self.kv_heads) * self.head_dim, bias, dtype)
+        # rows are [all Q heads | all K heads | all V heads]: a tensor-parallel split cuts each section
+        self.qkv._qkv_sections = (self.heads * self.head_dim, self.kv_heads * self.head_dim,
+                                  self.kv_heads * self.head_dim)
         self.out = Linear(self.heads * self.head_dim, dim, bias, dtype)
 
     def forward(self, x, cache: KVCache | None = None, mask=None):

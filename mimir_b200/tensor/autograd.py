@@ -35,6 +35,11 @@ class Param:
         t._stale = (self, self._version)
         t._fn = None
         _LEAF_PARAM[id(t)] = self
+        gather = getattr(self, "_gather", None)
+        if gather is not None:
+            # a fully sharded parameter is all-gathered where it is used; the gradient of the
+            # gathered value is reduce-scattered back onto the shard (nn/shard.go:74-89)
+            return gather(t)
         return t
 
     def grad(self):

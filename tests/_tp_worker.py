@@ -83,8 +83,8 @@ def main():
     dec.close()
     if world > 1:
         dist.destroy_process_group()
-    print("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen,
-                                  "launches": int(dec.launches_per_step)}), flush=True)
+    os.write(1, ("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen,
+                                  "launches": int(dec.launches_per_step)}) + "\n").encode())  # one write: lines of different ranks never interleave
 
 
 if __name__ == "__main__":
