@@ -6,3 +6,5 @@ from .autograd import Param, Buffer, backward, gradients, grad, vjp, jvp, jacobi
 from .loop import scan, record, Recording, trace, TracedGraph  # noqa: F401
 from .memory import set_memory_budget, memory_budget, memory_of  # noqa: F401
 from .random import philox_uniform, philox_normal, splitmix64  # noqa: F401
+from . import group  # noqa: F401,E402
+from .group import Group, cpus  # noqa: F401,E402

@@ -823,3 +823,21 @@ def avg_pool2d(x, kernel, stride=None, padding=0):
 
 def upsample_nearest(x, scale):
     return _node(lambda v: torch.nn.functional.interpolate(v, scale_factor=scale, mode="nearest"), (x,), {}, "upsample")
+
+
+def _bind_methods():
+    """Method forms of the functional ops (``x.sum(0)`` = ``sum_(x, 0)``), bound once; a name the
+    class already defines is left alone."""
+    g = globals()
+    names = {"sum": "sum_", "max": "max_", "min": "min_", "abs": "abs_", "pow": "pow_"}
+    for n in ("mean var logsumexp argmax softmax log_softmax cumsum exp log sqrt rsqrt sin cos tanh sigmoid relu "
+              "neg sign floor ceil erf silu softplus gelu clamp cast reshape permute transpose expand squeeze "
+              "unsqueeze flip pad cat contiguous gather scatter_add sort argsort topk matmul maximum minimum "
+              "where one_hot").split():
+        names[n] = n
+    for meth, fn in names.items():
+        if fn in g and not hasattr(Tensor, meth):
+            setattr(Tensor, meth, g[fn])
+
+
+_bind_methods()

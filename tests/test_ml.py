@@ -1,0 +1,95 @@
+"""Classical ML on small synthetic problems (reference: tree/*_test.go, linear/*_test.go, ...)."""
+import torch
+
+from mimir_b200 import distributions as D
+from mimir_b200 import ml
+import mimir_b200.tensor as T
+
+
+def _reg():
+    torch.manual_seed(0)
+    X = torch.randn(400, 4)
+    w = torch.tensor([1.0, -2.0, 0.0, 0.5])
+    return X, X @ w + 3 + 0.01 * torch.randn(400), w
+
+
+def test_linear_family():
+    X, y, w = _reg()
+    m = ml.ridge(X, y)
+    assert torch.allclose(m.w, w, atol=5e-3) and abs(float(m.b) - 3) < 5e-3
+    l = ml.lasso(X, y, 0.05)
+    assert l.w[2] == 0 and l.w[0] > 0.8
+    yc = (X @ w > 0).long()
+    assert (ml.logistic(X, yc).classify(X) == yc).float().mean() > 0.97
+    y3 = torch.bucketize(X @ w, torch.tensor([-1.0, 1.0]))
+    assert (ml.logistic(X, y3, 3).classify(X) == y3).float().mean() > 0.97
+    assert (ml.linear_svm(X, yc).classify(X) == yc).float().mean() > 0.9
+
+
+def test_trees():
+    X, y, _ = _reg()
+    y = y + X[:, 1] ** 2
+    m = ml.gradient_boosting(X, y, trees=40, max_depth=4)
+    assert ((m.predict(X) - y) ** 2).mean().sqrt() < 0.4
+    assert m.importance()[2] < 0.05
+    m2 = ml.tree.Model.from_json(m.to_json())
+    assert torch.allclose(m2.predict(X), m.predict(X))
+    yc = (X[:, 0] + X[:, 3] > 0).long()
+    assert (ml.gradient_boosting(X, yc, trees=30, max_depth=3, classes=2).classify(X) == yc).float().mean() > 0.95
+    y3 = torch.bucketize(X[:, 0], torch.tensor([-0.5, 0.5]))
+    assert (ml.gradient_boosting(X, y3, trees=15, max_depth=2, classes=3).classify(X) == y3).float().mean() > 0.95
+    assert (ml.decision_tree(X, yc, max_depth=6, classes=2).classify(X) == yc).float().mean() > 0.9
+    rf = ml.random_forest(X, y, trees=20, max_depth=6)
+    assert ((rf.predict(X) - y) ** 2).mean() < y.var()
+    pts = torch.cat([torch.randn(200, 2), torch.tensor([[8.0, 8.0]])])
+    s = ml.isolation_forest(pts, trees=50).score(pts)
+    assert s.argmax() == 200
+
+
+def test_neighbors_cluster_decomp():
+    X, y, w = _reg()
+    yc = (X @ w > 0).long()
+    assert (ml.KNN(X, yc, 5, 2).classify(X) == yc).float().mean() > 0.9
+    assert (ml.GaussianNB(X, yc, 2).classify(X) == yc).float().mean() > 0.85
+    C = torch.cat([torch.randn(100, 2) + 5, torch.randn(100, 2) - 5])
+    km = ml.kmeans(C, 2)
+    assert sorted(km.centers[:, 0].round().tolist()) == [-5.0, 5.0]
+    assert ml.dbscan(C, 1.5, 4).max() == 1
+    p = ml.pca(X, 2)
+    assert p.transform(X).shape == (400, 2) and p.variance[0] >= p.variance[1]
+
+
+def test_forecast_recommend_rules_automl():
+    hw = ml.HoltWinters(period=4).fit([1, 2, 3, 4] * 6)
+    assert torch.allclose(hw.forecast(4), torch.tensor([1.0, 2, 3, 4]), atol=1e-4)
+    assert torch.allclose(ml.autoregressive(torch.arange(20.0), 2)(3), torch.tensor([20.0, 21, 22]), atol=1e-3)
+    als = ml.ALS(5, 6, factors=2, l2=0.01, iters=20).fit([0, 0, 1, 2, 3, 4], [0, 1, 1, 2, 3, 4], [5, 3, 4, 1, 2, 5.0])
+    assert abs(float(als.predict(torch.tensor([0]), torch.tensor([0]))) - 5) < 0.1
+    _, rules = ml.apriori([["a", "b"], ["a", "b", "c"], ["a"], ["b", "c"]], 0.4, 0.6)
+    assert rules[0][0] == {"c"} and rules[0][1] == {"b"} and rules[0][3] == 1.0
+    X, y, _ = _reg()
+    name, model, board = ml.automl(X[:200], y[:200], folds=2)
+    assert name == "ridge" and board["ridge"] > 0.99
+    tr, te = ml.split(ml.Data(X, y), 0.25)
+    assert len(tr) == 300 and len(te) == 100
+    sc = ml.fit_scaler(X)
+    assert torch.allclose(sc.inverse(sc.transform(X)), X, atol=1e-5)
+
+
+def test_distributions():
+    mu = T.Param(torch.tensor([0.5]))
+    d = D.Normal(mu.value(), T.tensor([2.0]))
+    lp = d.log_prob(T.tensor([1.0]))
+    T.backward(lp.sum())
+    g = mu.grad()
+    assert abs(float(g.data()) - 0.125) < 1e-6
+    k = D.kl(D.Normal(T.tensor([0.0]), T.tensor([1.0])), D.Normal(T.tensor([1.0]), T.tensor([2.0])))
+    assert abs(float(k.data()) - 0.4431) < 1e-3
+    assert D.Normal(T.tensor([0.0]), T.tensor([1.0])).rsample((3,), seed=1).shape == (3, 1)
+    try:
+        D.kl(D.Poisson(T.tensor([1.0])), D.Dirichlet(T.tensor([1.0, 1.0])))
+        raise AssertionError("expected ErrNoKL")
+    except D.ErrNoKL:
+        pass
+    c = D.Categorical(probs=T.tensor([0.2, 0.8]))
+    assert abs(float(c.entropy().data()) - 0.5004) < 1e-3
