@@ -14,24 +14,10 @@
 // GPU weight layout ("planar Q4_0"): the 18-byte ggml blocks of a [N, K] matrix
 // are split at load time into scales[N][K/32] (fp16) and quants[N][K/32][16 bytes]
 // so that a lane reads one aligned 16-byte vector per block.
-#include "common.cuh"
-#include "runtime.h"
+#include "quant_common.cuh"
 
 namespace mimir {
 
-constexpr int kQMaxRanks = 8;
-constexpr int kQMaxBatch = 32;
-
-__device__ __forceinline__ float warp_sum_f(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max_f(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
 __device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 // ---------------------------------------------------------------------------
@@ -235,46 +221,6 @@ __global__ void q4_planar_to_bf16_kernel(const __half* __restrict__ ws, const ui
 // ---------------------------------------------------------------------------
 // GEMV fused with the tensor-parallel all-reduce.
 // ---------------------------------------------------------------------------
-struct QArArgs {
-  float* partial[kQMaxRanks];  // every rank's partial buffer [B][N] for this call (symmetric memory)
-  unsigned* sig[kQMaxRanks];   // every rank's signal pad
-  unsigned* epoch;             // device counter, advanced by this kernel
-  unsigned* block_counter;     // device word, zero between launches
-  const __nv_bfloat16* residual;  // [B][N] or nullptr
-  __nv_bfloat16* out;             // [B][N] bf16
-  int rank, world, slot;
-  unsigned long long wait_ns;
-};
-
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
-  float4 v;
-  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ bool wait_flag_ge(const unsigned* flag, unsigned want, unsigned long long limit_ns,
-                                             unsigned* err) {
-  if (static_cast<int>(ld_acquire_sys_u32(flag) - want) >= 0) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    for (int i = 0; i < 32; ++i) {
-      if (static_cast<int>(ld_acquire_sys_u32(flag) - want) >= 0) return true;
-      __nanosleep(100);
-    }
-    if (global_timer_ns() - t0 > limit_ns) { raise_error(err, kErrPeerTimeout); return false; }
-  }
-}
-
 // All-gather by peer stores: this rank's slice [n bytes] goes to offset rank * n of
 // every rank's destination buffer; then flags, then a bounded wait for all ranks.
 struct AgArgs {
@@ -395,64 +341,165 @@ __global__ void __launch_bounds__(256) oneshot_allreduce_kernel(QArArgs a, int B
 }
 
 // ---------------------------------------------------------------------------
-// Single-query attention over an fp16 KV cache (decode step).  The number of valid
-// keys and the write position come from device memory, so one captured CUDA graph
+// Single-query attention over an fp16 KV cache (decode step), split over the keys.
+// The number of valid keys comes from device memory, so one captured CUDA graph
 // serves every decode step.
 // q [B][Hq][D] bf16 with row pitch ldq, cache K/V [B][Hkv][cap][D] fp16, out [B][Hq][D] bf16.
-// One block per (batch, query head); each warp walks a strided subset of keys
-// with an online softmax, warps are merged through shared memory.
+// Grid (Hkv, B, S): a block owns one KV head (all G = Hq/Hkv query heads that share it,
+// so each key and value row is read once) and the z-th of S equal key ranges.  A warp
+// takes four keys per iteration, so four independent row loads are in flight per lane.
+// Each block leaves an unnormalised partial (o, max, sum) in `ws`; the block that
+// arrives last at the (batch, kv head) counter merges the S partials and resets the
+// counter for the next launch.  With S == 1 the block writes the result directly.
 // ---------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(128)
+constexpr int kDecWarps = 8;
+constexpr int kDecKeys = 4;
+
+template <int D, int G>
+__global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc,
                    __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int cap, const int* __restrict__ len_ptr, float scale,
-                   int ldq) {
-  const int len = min(*len_ptr, cap);
+                   int ldq, float* __restrict__ ws, unsigned* __restrict__ counters, int S) {
   constexpr int PER = D / 32;  // elements of the head dimension per lane
-  __shared__ float sm[4], sl[4], so[4][D];
+  const int len = min(*len_ptr, cap);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int h = blockIdx.x, b = blockIdx.y, hk = h / (Hq / Hkv);
-  float qv[PER], o[PER];
+  const int hk = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
+  const int chunk = (len + S - 1) / S;
+  const int t_begin = z * chunk, t_end = min(len, t_begin + chunk);
+  __shared__ float sm[kDecWarps][G], sl[kDecWarps][G];
+  __shared__ float so[kDecWarps][G][D];
+  __shared__ int s_last;
+
+  float qv[G][PER], o[G][PER], m[G], l[G];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    qv[i] = __bfloat162float(q[static_cast<size_t>(b) * ldq + h * D + lane * PER + i]) * scale;
-    o[i] = 0.f;
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      qv[g][i] = __bfloat162float(q[static_cast<size_t>(b) * ldq + (hk * G + g) * D + lane * PER + i]) * scale;
+      o[g][i] = 0.f;
+    }
   }
-  const __half* kb = kc + (static_cast<size_t>(b) * Hkv + hk) * cap * D;
-  const __half* vb = vc + (static_cast<size_t>(b) * Hkv + hk) * cap * D;
-  float m = -INFINITY, l = 0.f;
-  for (int t = warp; t < len; t += 4) {
-    float s = 0.f;
+  const __half* kb = kc + (static_cast<size_t>(b) * Hkv + hk) * cap * D + lane * PER;
+  const __half* vb = vc + (static_cast<size_t>(b) * Hkv + hk) * cap * D + lane * PER;
+  for (int t0 = t_begin + warp * kDecKeys; t0 < t_end; t0 += kDecWarps * kDecKeys) {
+    float kf[kDecKeys][PER], vf[kDecKeys][PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) s += qv[i] * __half2float(kb[static_cast<size_t>(t) * D + lane * PER + i]);
-    s = warp_sum_f(s);
-    const float mn = fmaxf(m, s), alpha = __expf(m - mn), p = __expf(s - mn);
-    l = l * alpha + p;
+    for (int u = 0; u < kDecKeys; ++u) {
+      const int t = min(t0 + u, t_end - 1);  // a clamped row is read but its weight is zero
+      if constexpr (PER == 4) {
+        const uint2 kr = *reinterpret_cast<const uint2*>(kb + static_cast<size_t>(t) * D);
+        const uint2 vr = *reinterpret_cast<const uint2*>(vb + static_cast<size_t>(t) * D);
+        const __half2 k0 = *reinterpret_cast<const __half2*>(&kr.x), k1 = *reinterpret_cast<const __half2*>(&kr.y);
+        const __half2 v0 = *reinterpret_cast<const __half2*>(&vr.x), v1 = *reinterpret_cast<const __half2*>(&vr.y);
+        kf[u][0] = __low2float(k0); kf[u][1] = __high2float(k0); kf[u][2] = __low2float(k1); kf[u][3] = __high2float(k1);
+        vf[u][0] = __low2float(v0); vf[u][1] = __high2float(v0); vf[u][2] = __low2float(v1); vf[u][3] = __high2float(v1);
+      } else {
+        const __half2 k0 = *reinterpret_cast<const __half2*>(kb + static_cast<size_t>(t) * D);
+        const __half2 v0 = *reinterpret_cast<const __half2*>(vb + static_cast<size_t>(t) * D);
+        kf[u][0] = __low2float(k0); kf[u][1] = __high2float(k0);
+        vf[u][0] = __low2float(v0); vf[u][1] = __high2float(v0);
+      }
+    }
 #pragma unroll
-    for (int i = 0; i < PER; ++i) o[i] = o[i] * alpha + p * __half2float(vb[static_cast<size_t>(t) * D + lane * PER + i]);
-    m = mn;
+    for (int g = 0; g < G; ++g) {
+      float sc[kDecKeys];
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) d += qv[g][i] * kf[u][i];
+        sc[u] = d;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int u = 0; u < kDecKeys; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], off);
+      float mn = m[g];
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u)
+        if (t0 + u < t_end) mn = fmaxf(mn, sc[u]);
+      const float alpha = m[g] == -INFINITY ? 0.f : __expf(m[g] - mn);
+      float pw[kDecKeys], psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) {
+        pw[u] = t0 + u < t_end ? __expf(sc[u] - mn) : 0.f;
+        psum += pw[u];
+      }
+      l[g] = l[g] * alpha + psum;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        float acc = o[g][i] * alpha;
+#pragma unroll
+        for (int u = 0; u < kDecKeys; ++u) acc += pw[u] * vf[u][i];
+        o[g][i] = acc;
+      }
+      m[g] = mn;
+    }
   }
-  if (lane == 0) { sm[warp] = m; sl[warp] = l; }
 #pragma unroll
-  for (int i = 0; i < PER; ++i) so[warp][lane * PER + i] = o[i];
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) { sm[warp][g] = m[g]; sl[warp][g] = l[g]; }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) so[warp][g][lane * PER + i] = o[g][i];
+  }
   __syncthreads();
-  if (warp == 0) {
-    float M = fmaxf(fmaxf(sm[0], sm[1]), fmaxf(sm[2], sm[3]));
-    float L = 0.f;
-    float acc[PER];
+  // warp g merges the block's warps for query head g
+  float M = -INFINITY, L = 0.f, acc[PER];
+  if (warp < G) {
+    const int g = warp;
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm[w][g]);
 #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      const float f = sm[w] == -INFINITY ? 0.f : __expf(sm[w] - M);
-      L += sl[w] * f;
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float f = sm[w][g] == -INFINITY ? 0.f : __expf(sm[w][g] - M);
+      L += sl[w][g] * f;
 #pragma unroll
-      for (int i = 0; i < PER; ++i) acc[i] += so[w][lane * PER + i] * f;
+      for (int i = 0; i < PER; ++i) acc[i] += so[w][g][lane * PER + i] * f;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    const int h = hk * G + g;
+    if (S == 1) {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i)
-      out[(static_cast<size_t>(b) * Hq + h) * D + lane * PER + i] = __float2bfloat16_rn(acc[i] * inv);
+      for (int i = 0; i < PER; ++i)
+        out[(static_cast<size_t>(b) * Hq + h) * D + lane * PER + i] = __float2bfloat16_rn(acc[i] * inv);
+    } else {
+      float* part = ws + ((static_cast<size_t>(b) * Hq + h) * S + z) * (D + 2);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) part[lane * PER + i] = acc[i];
+      if (lane == 0) { part[D] = M; part[D + 1] = L; }
+    }
   }
+  if (S == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&counters[b * Hkv + hk], 1u);
+    s_last = prev == static_cast<unsigned>(S - 1);
+    if (s_last) counters[b * Hkv + hk] = 0u;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (!s_last || warp >= G) return;
+  __threadfence();
+  const int h = hk * G + warp;
+  const float* parts = ws + (static_cast<size_t>(b) * Hq + h) * S * (D + 2);
+  float Mt = -INFINITY;
+  for (int j = 0; j < S; ++j) Mt = fmaxf(Mt, __ldcg(parts + static_cast<size_t>(j) * (D + 2) + D));
+  float Lt = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+  for (int j = 0; j < S; ++j) {
+    const float* pj = parts + static_cast<size_t>(j) * (D + 2);
+    const float mj = __ldcg(pj + D);
+    const float f = mj == -INFINITY ? 0.f : __expf(mj - Mt);
+    Lt += __ldcg(pj + D + 1) * f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] += __ldcg(pj + lane * PER + i) * f;
+  }
+  const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i)
+    out[(static_cast<size_t>(b) * Hq + h) * D + lane * PER + i] = __float2bfloat16_rn(acc[i] * inv);
 }
 
 // k, v [B][Hkv][D] bf16 (row pitch ld, column offsets kcol / vcol) -> fp16 cache at position pos
@@ -476,6 +523,7 @@ __global__ void f32_to_bf16_rows_kernel(const float* __restrict__ x, __nv_bfloat
 }
 
 static unsigned long long g_q_wait_ns = 10000000000ull;
+unsigned long long q_peer_wait_ns() { return g_q_wait_ns; }
 
 }  // namespace mimir
 
@@ -574,21 +622,35 @@ MIMIR_API int mimir_oneshot_allreduce(void* const* partial, void* const* sig, vo
   count_launch();
   return 0;
 }
-MIMIR_API int mimir_attn_decode(const void* q, const void* kc, const void* vc, void* out, int B, int Hq, int Hkv,
-                                int D, int cap, const int* len_dev, float scale, int ldq, cudaStream_t st) {
-  dim3 grid(Hq, B);
-  if (D == 128)
-    attn_decode_kernel<128><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __half*>(kc),
-                                                  static_cast<const __half*>(vc), static_cast<__nv_bfloat16*>(out), Hq,
-                                                  Hkv, cap, len_dev, scale, ldq);
-  else if (D == 64)
-    attn_decode_kernel<64><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __half*>(kc),
-                                                 static_cast<const __half*>(vc), static_cast<__nv_bfloat16*>(out), Hq,
-                                                 Hkv, cap, len_dev, scale, ldq);
-  else
-    return refuse("decode attention: head dim %d not supported (64 or 128)", D);
+template <int D>
+static int launch_attn_decode(const void* q, const void* kc, const void* vc, void* out, int B, int Hq, int Hkv, int cap,
+                              const int* len_dev, float scale, int ldq, float* ws, unsigned* counters, int S,
+                              cudaStream_t st) {
+  dim3 grid(Hkv, B, S);
+#define MIMIR_DEC(G)                                                                                                 \
+  attn_decode_kernel<D, G><<<grid, kDecWarps * 32, 0, st>>>(                                                         \
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __half*>(kc), static_cast<const __half*>(vc),          \
+      static_cast<__nv_bfloat16*>(out), Hq, Hkv, cap, len_dev, scale, ldq, ws, counters, S)
+  switch (Hq / Hkv) {
+    case 1: MIMIR_DEC(1); break;
+    case 2: MIMIR_DEC(2); break;
+    case 4: MIMIR_DEC(4); break;
+    case 8: MIMIR_DEC(8); break;
+    default: return refuse("decode attention: %d query heads per KV head not supported (1, 2, 4 or 8)", Hq / Hkv);
+  }
+#undef MIMIR_DEC
   count_launch();
   return 0;
+}
+// ws: B * Hq * splits * (D + 2) floats and counters: B * Hkv zeroed words, both needed only when splits > 1.
+MIMIR_API int mimir_attn_decode(const void* q, const void* kc, const void* vc, void* out, int B, int Hq, int Hkv,
+                                int D, int cap, const int* len_dev, float scale, int ldq, float* ws,
+                                unsigned* counters, int splits, cudaStream_t st) {
+  if (Hkv <= 0 || Hq % Hkv) return refuse("decode attention: %d query heads do not divide over %d KV heads", Hq, Hkv);
+  if (splits < 1 || (splits > 1 && (!ws || !counters))) return refuse("decode attention: %d splits need a workspace", splits);
+  if (D == 128) return launch_attn_decode<128>(q, kc, vc, out, B, Hq, Hkv, cap, len_dev, scale, ldq, ws, counters, splits, st);
+  if (D == 64) return launch_attn_decode<64>(q, kc, vc, out, B, Hq, Hkv, cap, len_dev, scale, ldq, ws, counters, splits, st);
+  return refuse("decode attention: head dim %d not supported (64 or 128)", D);
 }
 MIMIR_API int mimir_kv_cache_write(const void* kv, int ld, int kcol, int vcol, void* kc, void* vc, int B, int Hkv,
                                    int D, int cap, const int* pos_dev, cudaStream_t st) {

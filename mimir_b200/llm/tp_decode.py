@@ -76,6 +76,11 @@ class TPDecoder:
         self.xs = torch.zeros(B, kmax // 32, **f32)
         self.kc = torch.zeros(cfg.n_layer, B, self.Hk, cap, D, dtype=torch.float16, device=self.dev)
         self.vc = torch.zeros_like(self.kc)
+        # decode attention splits the keys over enough blocks to fill the GPU (about 4 per SM)
+        sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        self.attn_splits = max(1, min((cap + 63) // 64, (4 * sms) // max(1, B * self.Hk), 64))
+        self.attn_ws = torch.zeros(B * self.Hq * self.attn_splits * (D + 2), **f32)
+        self.attn_cnt = torch.zeros(B * self.Hk, dtype=torch.int32, device=self.dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)      # write position
         self.len = torch.ones(1, dtype=torch.int32, device=self.dev)       # keys visible = pos + 1
         self.pos_rows = torch.zeros(B, dtype=torch.int32, device=self.dev)
@@ -167,7 +172,8 @@ class TPDecoder:
                                                    ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hk, D, self.cap,
                                                    ptr(self.pos), stream_ptr()), "kv_write")
             _native.check(lib.mimir_attn_decode(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.att), B,
-                                                self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n, stream_ptr()),
+                                                self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n,
+                                                ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits, stream_ptr()),
                           "attn_decode")
             Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0)
             self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0)
@@ -228,14 +234,131 @@ class TPDecoder:
             self.tokens.copy_(prompt[:, t].to(self.dev))
             self.step()
 
-    def generate(self, prompt: torch.Tensor, n: int) -> torch.Tensor:
+    def prefill_batched(self, prompt: torch.Tensor, rows_per_chunk: int = 16384) -> None:
+        """Prompt processing as GEMMs: all but the last prompt token go through the layers as
+        one [B*(T-1), d] bf16 activation matrix (tcgen05 GEMMs on weights expanded from Q4_0 to
+        bf16 one matrix at a time, the causal flash-attention kernel, one NCCL all-reduce per
+        row-parallel projection), filling the fp16 KV cache; the last token then takes the
+        ordinary decode step, which leaves the first generated token in ``self.tokens``.
+        Activations stay bf16 here (the decode step rounds them to Q8_0)."""
+        from ..ops.attention import attention_fwd
+        from ..ops.gemm import gemm
+        cfg, d, D, B = self.cfg, self.cfg.d_model, self.cfg.head_dim, self.B
+        T = prompt.shape[1]
+        if prompt.shape[0] != B:
+            raise ValueError(f"prompt batch {prompt.shape[0]} != decoder batch {B}")
+        if T + 1 > self.cap:
+            raise ValueError(f"prompt of {T} tokens does not fit a cache of {self.cap}")
+        Tm = T - 1
+        if Tm >= 1:
+            bf, f32 = dict(dtype=torch.bfloat16, device=self.dev), dict(dtype=torch.float32, device=self.dev)
+            M = B * Tm
+            tok = prompt[:, :Tm].reshape(-1).to(self.dev, torch.int64)
+            h = torch.empty(M, d, **bf)
+            K.embedding_fwd(tok, self.embed, None, h, Tm)
+            pos = torch.arange(Tm, dtype=torch.int32, device=self.dev).repeat(B)
+            x, rstd = torch.empty(M, d, **bf), torch.empty(M, **f32)
+            qkv, att = torch.empty(M, self.qkv_n, **bf), torch.empty(M, self.Hq * D, **bf)
+            lse = torch.empty(B * self.Hq * Tm, **f32)
+            part = torch.empty(M, d, **bf)
+            chunk = max(128, min(M, rows_per_chunk))
+            gu = torch.empty(chunk, 2 * self.F, **bf)
+            act = torch.empty(chunk, self.F, **bf)
+            wmax = max(self.qkv_n * d, d * self.Hq * D, 3 * self.F * d)
+            wbuf = torch.empty(wmax, **bf)
+
+            def expand(w):
+                return w.to_bf16(wbuf[: w.N * w.K].view(w.N, w.K))
+
+            def allreduce_residual(partial, resid):
+                if self.world > 1:
+                    torch.distributed.all_reduce(partial)
+                resid.add_(partial)
+
+            q4 = qkv.view(B, Tm, self.qkv_n)
+            qv = q4[:, :, : self.Hq * D].unflatten(2, (self.Hq, D))
+            kv = q4[:, :, self.Hq * D: (self.Hq + self.Hk) * D].unflatten(2, (self.Hk, D))
+            vv = q4[:, :, (self.Hq + self.Hk) * D:].unflatten(2, (self.Hk, D))
+            for l, w in enumerate(self.layers):
+                K.rmsnorm_fwd(h, w["attn_norm"], x, rstd, cfg.eps)
+                gemm(x, expand(w["qkv"]), out=qkv)
+                K.rope_(qkv, pos, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
+                self.kc[l][:, :, :Tm].copy_(kv.permute(0, 2, 1, 3))
+                self.vc[l][:, :, :Tm].copy_(vv.permute(0, 2, 1, 3))
+                attention_fwd(qv, kv, vv, att.view(B, Tm, self.Hq, D), lse, causal=True)
+                gemm(att, expand(w["o"]), out=part)
+                allreduce_residual(part, h)
+                K.rmsnorm_fwd(h, w["ffn_norm"], x, rstd, cfg.eps)
+                wgu = expand(w["gate_up"])
+                wd = w["down"].to_bf16(wbuf[wgu.numel(): wgu.numel() + d * self.F].view(d, self.F))
+                for r0 in range(0, M, chunk):
+                    r1 = min(M, r0 + chunk)
+                    gemm(x[r0:r1], wgu, out=gu[: r1 - r0])
+                    K.swiglu_fwd(gu[: r1 - r0], act[: r1 - r0])
+                    gemm(act[: r1 - r0], wd, out=part[r0:r1])
+                allreduce_residual(part, h)
+            self.pos.fill_(Tm)
+            self.len.fill_(Tm + 1)
+            self.pos_rows.fill_(Tm)
+        self.tokens.copy_(prompt[:, T - 1].to(self.dev))
+        self.step()
+
+    def generate(self, prompt: torch.Tensor, n: int, batched_prefill: bool = True) -> torch.Tensor:
         self.reset()
-        self.prefill(prompt)
+        (self.prefill_batched if batched_prefill else self.prefill)(prompt)
         out = [self.tokens.clone()]
         for _ in range(n - 1):
             self.step()
             out.append(self.tokens.clone())
         return torch.stack(out, 1)
+
+    def primitive_times(self, iters: int = 50) -> dict:
+        """Device time in microseconds of each kernel of a decode step, measured by queueing
+        ``iters`` back-to-back calls of it (layer 0's weights) between two CUDA events.  Every
+        rank makes the same calls, so the collective kernels meet their peers."""
+        cfg, d, D, B = self.cfg, self.cfg.d_model, self.cfg.head_dim, self.B
+        lib, w = Q._L(), self.layers[0]
+        scale = 1.0 / math.sqrt(D)
+        full = self.logits_all.view(torch.float32).view(self.world, self.B, self.Vl)
+        cases = {
+            "embedding": lambda: K.embedding_fwd(self.tokens, self.embed, None, self.h, 1),
+            "rmsnorm_quantize": lambda: Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=w["attn_norm"], eps=cfg.eps),
+            "gemv_qkv": lambda: Q.q4_gemv(w["qkv"], self.xq, self.xs, self.qkv),
+            "rope": lambda: K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True),
+            "kv_write": lambda: _native.check(lib.mimir_kv_cache_write(
+                ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D, ptr(self.kc[0]), ptr(self.vc[0]), B,
+                self.Hk, D, self.cap, ptr(self.pos), stream_ptr()), "kv_write"),
+            "attn_decode": lambda: _native.check(lib.mimir_attn_decode(
+                ptr(self.qkv), ptr(self.kc[0]), ptr(self.vc[0]), ptr(self.att), B, self.Hq, self.Hk, D, self.cap,
+                ptr(self.len), scale, self.qkv_n, ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits,
+                stream_ptr()), "attn_decode"),
+            "quantize_att": lambda: Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0),
+            "gemv_o_allreduce": lambda: self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0),
+            "gemv_gate_up": lambda: Q.q4_gemv(w["gate_up"], self.xq, self.xs, self.gu),
+            "swiglu_quantize": lambda: Q.quantize_act(self.gu, self.xq, self.xs, self.F, mode=2),
+            "gemv_down_allreduce": lambda: self._gemv_allreduce(w["down"], self.F, self.h1, self.h, 1),
+            "gemv_head": lambda: Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local),
+            "logits_allgather": lambda: _native.check(lib.mimir_peer_allgather(
+                ptr(self.logits_local), self._logits_arr, self._sig_arr, self.epochs[2:].data_ptr(),
+                self.counters[2:].data_ptr(), self.logits_local.numel() * 4, self.rank, self.world, 2, stream_ptr()),
+                "allgather"),
+            "argmax": lambda: full.permute(1, 0, 2).reshape(self.B, -1).argmax(-1),
+        }
+        out = {}
+        for name, fn in cases.items():
+            for _ in range(3):
+                fn()
+            if self.world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            out[name] = round(e0.elapsed_time(e1) * 1e3 / iters, 2)
+        return out
 
     def close(self):
         torch.cuda.synchronize()

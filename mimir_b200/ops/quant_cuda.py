@@ -24,7 +24,7 @@ def _L():
             "mimir_q4_gemv": [P, P, P, P, P, I, I, I, I, I, P],
             "mimir_q4_gemv_allreduce": [P, P, P, P, PP, PP, P, P, P, P, I, I, I, I, I, I, P],
             "mimir_oneshot_allreduce": [PP, PP, P, P, P, P, I, I, I, I, I, P],
-            "mimir_attn_decode": [P, P, P, P, I, I, I, I, I, P, F, I, P],
+            "mimir_attn_decode": [P, P, P, P, I, I, I, I, I, P, F, I, P, P, I, P],
             "mimir_kv_cache_write": [P, I, I, I, P, P, I, I, I, I, P, P],
             "mimir_f32_to_bf16": [P, P, L, P],
             "mimir_q4_planar_to_bf16": [P, P, P, L, P],
@@ -85,4 +85,22 @@ def q4_gemv(w: PlanarQ4, xq, xs, out):
     B = xq.shape[0]
     _native.check(_L().mimir_q4_gemv(ptr(w.scales), ptr(w.quants), ptr(xq), ptr(xs), ptr(out),
                                      int(out.dtype == torch.bfloat16), w.N, w.K, B, out.stride(0), stream_ptr()), "q4_gemv")
+    return out
+
+
+def attn_decode(q, kc, vc, length, scale=None, splits=0, out=None):
+    """Single-query attention of ``q`` [B, Hq, D] bf16 over the fp16 cache ``kc``/``vc``
+    [B, Hkv, cap, D]; ``length`` is a 1-element int32 device tensor with the number of valid keys.
+    ``splits`` = 0 picks enough key ranges to fill the GPU."""
+    B, Hq, D = q.shape
+    Hkv, cap = kc.shape[1], kc.shape[2]
+    if splits <= 0:
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        splits = max(1, min((cap + 63) // 64, (4 * sms) // max(1, B * Hkv), 64))
+    ws = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)
+    cnt = torch.zeros(B * Hkv, dtype=torch.int32, device=q.device)
+    out = torch.empty(B, Hq, D, dtype=torch.bfloat16, device=q.device) if out is None else out
+    _native.check(_L().mimir_attn_decode(ptr(q), ptr(kc), ptr(vc), ptr(out), B, Hq, Hkv, D, cap, ptr(length),
+                                         float(scale if scale is not None else D ** -0.5), q.stride(0), ptr(ws),
+                                         ptr(cnt), splits, stream_ptr()), "attn_decode")
     return out

@@ -24,6 +24,9 @@ def main():
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the model's)")
+    ap.add_argument("--sequential-prefill", action="store_true", help="feed the prompt token by token")
+    ap.add_argument("--primitives", action="store_true",
+                    help="also time each kernel of the step on its own (at the final cache length)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -57,11 +60,14 @@ def main():
     dec.reset()
     for _ in range(4):  # warm-up and graph capture
         dec.step()
+    if not a.sequential_prefill:   # untimed pass: buffers and kernels of the GEMM path are warm afterwards
+        dec.prefill_batched(prompt)
     dec.reset()
-    ms_prompt = timed(lambda: dec.prefill(prompt))
+    ms_prompt = timed(lambda: (dec.prefill if a.sequential_prefill else dec.prefill_batched)(prompt))
     launches0 = _native.lib().mimir_launch_count()
     ms_gen = timed(lambda: [dec.step() for _ in range(a.gen)])
     launches = _native.lib().mimir_launch_count() - launches0
+    prim = dec.primitive_times() if a.primitives else None
     err = check_error_word()
     if rank == 0:
         print(json.dumps({
@@ -70,7 +76,7 @@ def main():
             "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "gen": a.gen,
             "config": {"model": a.model, "layers": cfg.n_layer, "weights": "Q4_0", "activations": "Q8_0",
                        "kv_cache": "fp16", "parallelism": f"tp{world}"},
-            "gpu_launches": int(launches), "launches_per_token": int(dec.launches_per_step), "error_word": err}))
+            "gpu_launches": int(launches), "launches_per_token": int(dec.launches_per_step), "primitive_us": prim, "error_word": err}))
     dec.close()
     if world > 1:
         dist.destroy_process_group()

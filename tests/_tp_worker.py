@@ -78,12 +78,17 @@ def main():
     want = reference_logits(cfg, weights, prompt.cuda())
     cos = torch.nn.functional.cosine_similarity(got.flatten(1), want.flatten(1), dim=1).min().item()
     rel = ((got - want).norm() / want.norm()).item()
+    dec.reset()
+    dec.prefill_batched(prompt)          # GEMM path over the first T-1 tokens + one decode step
+    torch.cuda.synchronize()
+    last = dec.logits_all.view(torch.float32).view(world, B, dec.Vl).permute(1, 0, 2).reshape(B, -1)
+    cos_prefill = torch.nn.functional.cosine_similarity(last, want[:, -1], dim=1).min().item()
     gen = dec.generate(prompt, 6).cpu().tolist()
     err = check_error_word()
     dec.close()
     if world > 1:
         dist.destroy_process_group()
-    os.write(1, ("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen,
+    os.write(1, ("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen, "cos_prefill": cos_prefill,
                                   "launches": int(dec.launches_per_step)}) + "\n").encode())  # one write: lines of different ranks never interleave
 
 

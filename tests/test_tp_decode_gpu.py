@@ -28,6 +28,7 @@ def test_decode_single_gpu_matches_reference():
     (r,) = _run(1)
     assert r["err"] == 0
     assert r["cos"] > 0.995 and r["rel"] < 0.08, r
+    assert r["cos_prefill"] > 0.995, r
     assert r["launches"] > 0
 
 
@@ -39,4 +40,5 @@ def test_decode_tp2_matches_reference_and_ranks_agree():
     for r in res:
         assert r["err"] == 0
         assert r["cos"] > 0.995 and r["rel"] < 0.08, r
+        assert r["cos_prefill"] > 0.995, r
     assert res[0]["gen"] == res[1]["gen"]
