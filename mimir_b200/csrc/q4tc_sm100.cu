@@ -6,12 +6,14 @@
 // and the kernel stays bound by the 4.5-bit weight stream, not by arithmetic:
 //
 //   warp 0       bulk-copies raw weight tiles (4608 bytes: 2 x 128 x 16-byte quants +
-//                2 x 128 fp16 scales) into a deep shared-memory ring
-//   warp 2       TMA-loads the activation tile [batch x 64] of the same k-block
-//   warps 4..7   expand a raw tile to bf16 in the 128-byte-swizzled K-major layout the
-//                tensor core reads (nibble -> 128 + n via a byte permute, -136, x scale)
+//                2 x 128 fp16 scales) and TMA-loads the activation tile [batch x 64] of the
+//                same k-block into a deep shared-memory ring (loads run 8 k-blocks ahead)
+//   warps 4..15  expand a raw tile to bf16 in the 128-byte-swizzled K-major layout the
+//                tensor core reads (nibble -> 128 + n via a byte permute, -136, x scale);
+//                three groups of four warps take k-blocks in turn, because one tile's
+//                expansion is a latency chain (shared load, convert, store, proxy fence)
 //   warp 1       issues tcgen05.mma (accumulator 128 x batch in TMEM, double-buffered)
-//   warps 8..11  read the accumulator and write fp32 partials [split][b][n]
+//   warps 16..19 read the accumulator and write fp32 partials [split][b][n]
 //
 // Work is split over (row tile, k range) so that every SM streams weights; after the
 // main loop all blocks meet (they are co-resident: the grid never exceeds the SM
@@ -31,9 +33,10 @@ namespace mimir {
 constexpr int kTcRows = 128;
 constexpr int kTcBK = 64;
 constexpr int kTcRawBytes = 2 * kTcRows * 16 + 2 * kTcRows * 2;  // 4608
-constexpr int kTcRawStages = 10;
-constexpr int kTcAStages = 4;
-constexpr int kTcThreads = 384;
+constexpr int kTcRawStages = 8;
+constexpr int kTcAStages = 6;
+constexpr int kTcGroups = 3;  // groups of four expanding warps; group g owns the k-blocks it % kTcGroups == g
+constexpr int kTcThreads = (4 + 4 * kTcGroups + 4) * 32;
 
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -76,16 +79,16 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
              int splits, unsigned* err) {
   constexpr int A_BYTES = kTcRows * kTcBK * 2;  // 16 KB
   constexpr int X_BYTES = BNB * kTcBK * 2;
-  constexpr int ASTAGE = A_BYTES + 4096;        // activation tile slot padded to keep 1024-byte alignment
+  constexpr int RSTAGE = 4096 + 5120;           // activation tile (1024-byte aligned) + raw weight tile
   constexpr uint32_t TMEM_COLS = 2 * BNB < 32 ? 32 : 2 * BNB;
   constexpr uint32_t IDESC = make_idesc_bf16(kTcRows, BNB, false, false);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* a_ring = smem;                                    // kTcAStages x (A tile + x tile)
-  uint8_t* raw_ring = smem + kTcAStages * ASTAGE;            // kTcRawStages x 4608
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * kTcRawBytes);
+  uint8_t* a_ring = smem;                                    // kTcAStages x expanded bf16 weight tile
+  uint8_t* raw_ring = smem + kTcAStages * A_BYTES;           // kTcRawStages x (x tile | raw weight tile)
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * RSTAGE);
   uint64_t* raw_empty = raw_full + kTcRawStages;
   uint64_t* a_full = raw_empty + kTcRawStages;
   uint64_t* a_empty = a_full + kTcAStages;
@@ -103,10 +106,10 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 128);
+      mbar_init(&raw_empty[s], 129);  // 128 expanding threads + the MMAs that read the activation tile
     }
     for (int s = 0; s < kTcAStages; ++s) {
-      mbar_init(&a_full[s], 129);  // 128 expanding threads + the activation load
+      mbar_init(&a_full[s], 128);
       mbar_init(&a_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -126,7 +129,8 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {  // raw weight tiles
+    if (lane == 0) {  // raw weight tiles and activation tiles
+      tma_prefetch_desc(&tmX);
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -136,26 +140,10 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
           const int s = it % kTcRawStages;
           const uint32_t ph = (it / kTcRawStages) & 1;
           if (!mbar_wait(&raw_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
-          mbar_arrive_expect_tx(&raw_full[s], kTcRawBytes);
-          bulk_load_1d(raw_ring + s * kTcRawBytes,
+          mbar_arrive_expect_tx(&raw_full[s], kTcRawBytes + X_BYTES);
+          tma_load_2d(raw_ring + s * RSTAGE, &tmX, &raw_full[s], kb * kTcBK, 0);  // rows >= B read zeros
+          bulk_load_1d(raw_ring + s * RSTAGE + 4096,
                        wt + (static_cast<size_t>(tile) * kb_total + kb) * kTcRawBytes, kTcRawBytes, &raw_full[s]);
-        }
-      }
-    }
-  } else if (warp == 2) {
-    if (lane == 0) {  // activation tiles
-      tma_prefetch_desc(&tmX);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const int split = u % splits;
-        const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcAStages;
-          const uint32_t ph = (it / kTcAStages) & 1;
-          if (!mbar_wait(&a_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
-          mbar_arrive_expect_tx(&a_full[s], X_BYTES);
-          tma_load_2d(a_ring + s * ASTAGE + A_BYTES, &tmX, &a_full[s], kb * kTcBK, 0);  // rows >= B read zeros
         }
       }
     }
@@ -171,36 +159,39 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BNB;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcAStages;
+          const int s = it % kTcAStages, sr = it % kTcRawStages;
           const uint32_t ph = (it / kTcAStages) & 1;
+          // the expanding threads arrive here only after the stage's loads (activation tile included) landed
           if (!mbar_wait(&a_full[s], ph, abort_flag, err)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_u32(a_ring + s * ASTAGE);
-          const uint64_t adesc = make_smem_desc_sw128(sA, 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sA + A_BYTES, 16, 1024);
+          const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + s * A_BYTES), 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(raw_ring + sr * RSTAGE), 16, 1024);
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)
             umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
+          umma_commit(&raw_empty[sr]);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else if (warp >= 4 && warp < 8) {
-    // expand raw Q4_0 tiles to bf16; thread t owns row t of the tile
-    const int t = threadIdx.x - 128;
+  } else if (warp >= 4 && warp < 4 + 4 * kTcGroups) {
+    // expand raw Q4_0 tiles to bf16; thread t of the group owns row t of the tile
+    const int group = (warp - 4) >> 2;
+    const int t = ((warp - 4) & 3) * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int split = u % splits;
       const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (static_cast<int>(it % kTcGroups) != group) continue;
         const int sr = it % kTcRawStages, sa = it % kTcAStages;
         const uint32_t phr = (it / kTcRawStages) & 1, pha = (it / kTcAStages) & 1;
         if (!mbar_wait(&raw_full[sr], phr, abort_flag, err)) { ok = false; break; }
         if (!mbar_wait(&a_empty[sa], pha ^ 1, abort_flag, err)) { ok = false; break; }
-        const uint8_t* raw = raw_ring + sr * kTcRawBytes;
-        uint8_t* arow = a_ring + sa * ASTAGE + t * 128;
+        const uint8_t* raw = raw_ring + sr * RSTAGE + 4096;
+        uint8_t* arow = a_ring + sa * A_BYTES + t * 128;
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
           const uint4 q = *reinterpret_cast<const uint4*>(raw + (blk * kTcRows + t) * 16);
@@ -222,7 +213,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         mbar_arrive(&raw_empty[sr]);
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 4 + 4 * kTcGroups) {
     const int q = warp & 3;
     uint32_t ti = 0;
     float* mine = tail.partial[tail.rank];
@@ -322,7 +313,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
 // One block per (row, 2048-column slab); 8 values per thread, a Q8_0 block is 4 lanes.
 __global__ void __launch_bounds__(256)
 round_act_q8_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                    __nv_bfloat16* __restrict__ y, int K, int mode, float eps) {
+                    __nv_bfloat16* __restrict__ y, int ldy, int K, int mode, float eps) {
   const int row = blockIdx.y;
   const int ld = mode == 2 ? 2 * K : K;
   const __nv_bfloat16* xr = x + static_cast<size_t>(row) * ld;
@@ -378,13 +369,13 @@ round_act_q8_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   o.y = pack_bf16x2(rintf(v[2] * inv) * d, rintf(v[3] * inv) * d);
   o.z = pack_bf16x2(rintf(v[4] * inv) * d, rintf(v[5] * inv) * d);
   o.w = pack_bf16x2(rintf(v[6] * inv) * d, rintf(v[7] * inv) * d);
-  *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * K + c) = o;
+  *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy + c) = o;
 }
 
 template <int BNB>
 static int launch_q4_tc(const CUtensorMap& tmX, const uint8_t* wt, const TcTail& tail, int N, int K, int B, int splits,
                         cudaStream_t st) {
-  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2 + 4096) + kTcRawStages * kTcRawBytes + 1024 + 512;
+  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2) + kTcRawStages * (4096 + 5120) + 1024 + 512;
   auto kern = q4_tc_kernel<BNB>;
   static bool configured = false;
   if (!configured) {
@@ -438,15 +429,15 @@ MIMIR_API int mimir_q4_planar_to_tiled(const void* ws, const void* wq, void* out
   return 0;
 }
 
-// y[rows][K] bf16 = Q8_0-rounded activation (mode 0), of RMSNorm(x) * gamma (mode 1), or of
-// silu(gate) * up for x = [rows][2K] (mode 2).
-MIMIR_API int mimir_round_act_q8(const void* x, const void* gamma, void* y, int rows, int K, int mode, float eps,
+// y[rows][K] bf16 (row pitch ldy) = Q8_0-rounded activation (mode 0), of RMSNorm(x) * gamma (mode 1), or of
+// silu(gate) * up for x = [rows][2K] (mode 2).  x rows are contiguous.
+MIMIR_API int mimir_round_act_q8(const void* x, const void* gamma, void* y, int ldy, int rows, int K, int mode, float eps,
                                  cudaStream_t st) {
-  if (K % 32) return refuse("activation rounding: K must be a multiple of 32");
+  if (K % 32 || ldy % 8) return refuse("activation rounding: K %% 32 == 0 and ldy %% 8 == 0 required");
   if (mode == 1 && !gamma) return refuse("activation rounding: RMSNorm needs gamma");
   dim3 grid(ceil_div(K, 2048), rows);
   round_act_q8_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),
-                                            static_cast<__nv_bfloat16*>(y), K, mode, eps);
+                                            static_cast<__nv_bfloat16*>(y), ldy, K, mode, eps);
   count_launch();
   return 0;
 }
@@ -464,8 +455,17 @@ MIMIR_API int mimir_q4_tc(const void* wt, const void* x, int ldx, void* const* p
   if (world < 1 || world > kQMaxRanks) return refuse("q4 tensor-core product: world %d outside 1..%d", world, kQMaxRanks);
   const int n_tiles = ceil_div(N, kTcRows), kb_total = K / kTcBK;
   if (splits <= 0) {
-    splits = sm_count() / n_tiles;
-    if (splits > kb_total / 4) splits = kb_total / 4;  // at least four k-blocks per unit
+    // the makespan of a persistent grid is ceil(units / SMs) units of 1/splits of a row tile each;
+    // a split costs one more partial to write and to sum
+    const int sms = sm_count();
+    int lim = kb_total / 4 < max_splits ? kb_total / 4 : max_splits;  // at least four k-blocks per unit
+    if (lim < 1) lim = 1;
+    double best = 1e30;
+    splits = 1;
+    for (int sp = 1; sp <= lim; ++sp) {
+      const double cost = static_cast<double>(ceil_div(n_tiles * sp, sms)) / sp + (0.01 + 0.002 * B) * sp;
+      if (cost < best - 1e-9) { best = cost; splits = sp; }
+    }
   }
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;

@@ -54,7 +54,15 @@ class LlamaConfig:
 
 class TPDecoder:
     def __init__(self, cfg: LlamaConfig, rank: int, world: int, batch: int, cap: int, seed: int = 0,
-                 device=None, weights: dict | None = None):
+                 device=None, weights: dict | None = None, engine: str = "tc"):
+        """``engine``: "tc" runs every projection on the tensor cores (Q4_0 tiles expanded to bf16 in
+        shared memory, activations rounded to Q8_0 and kept as bf16); "dp4a" is the integer
+        dot-product path (one warp per weight row)."""
+        if engine not in ("tc", "dp4a"):
+            raise ValueError(f"unknown decode engine {engine!r}")
+        if engine == "tc" and (batch > 32 or cfg.d_model % 64 or (cfg.ffn // world) % 64 or (cfg.n_head // world * cfg.head_dim) % 64):
+            engine = "dp4a"
+        self.engine = engine
         self.cfg, self.rank, self.world, self.B, self.cap = cfg, rank, world, batch, cap
         self.dev = torch.device(device or f"cuda:{torch.cuda.current_device()}")
         d, D = cfg.d_model, cfg.head_dim
@@ -89,7 +97,10 @@ class TPDecoder:
         inv = 1.0 / (cfg.rope_base ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
         self.freqs = inv.float().to(self.dev)
         # symmetric memory: two rotating partial buffers, gathered logits, signal pad
-        self.part = [SymmetricBuffer(B * d * 4, rank, world) for _ in range(2)]
+        self.ar_splits = 4 if B <= 8 else 2   # k-splits of the row-parallel products (their partials cross NVLink)
+        self.part = [SymmetricBuffer(self.ar_splits * B * d * 4, rank, world) for _ in range(2)]
+        self.xdq = torch.zeros(B, kmax, **bf)  # activations rounded to Q8_0, as bf16 (tensor-core engine)
+        self.tc_scratch = Q.TcScratch(B * max(self.qkv_n, 2 * self.F, self.Vl), self.dev) if engine == "tc" else None
         self.logits_all = SymmetricBuffer(world * B * self.Vl * 4, rank, world)
         self.sig = SymmetricBuffer(4096 * 4, rank, world)
         self.epochs = torch.zeros(8, dtype=torch.int32, device=self.dev)
@@ -149,6 +160,11 @@ class TPDecoder:
             onorm = torch.ones(d, device=self.dev)
         self.embed = emb.bfloat16()
         self.head = Q.PlanarQ4.quantize(head[self.rank * self.Vl: (self.rank + 1) * self.Vl])
+        if self.engine == "tc":
+            for w in self.layers:
+                for k in ("qkv", "o", "gate_up", "down"):
+                    w[k + "_t"] = Q.TiledQ4.from_planar(w[k])
+            self.head_t = Q.TiledQ4.from_planar(self.head)
         self.out_norm = onorm.bfloat16()
 
     # ------------------------------------------------------------- primitives
@@ -160,7 +176,43 @@ class TPDecoder:
                                          self.rank, self.world, slot, stream_ptr())
         _native.check(rc, "q4_gemv_allreduce")
 
+    def _tc_allreduce(self, w: Q.TiledQ4, x, residual, out, slot: int):
+        lib = Q._L()
+        rc = lib.mimir_q4_tc(ptr(w.blob), ptr(x), x.stride(0), self._part_arr[slot], self._sig_arr,
+                             self.epochs[slot:].data_ptr(), self.counters[slot:].data_ptr(), ptr(residual), ptr(out), 0,
+                             out.stride(0), w.N, w.K, self.B, 0, self.ar_splits, self.rank, self.world, slot, stream_ptr())
+        _native.check(rc, "q4_tc(all-reduce)")
+
+    def _attention_step(self, l: int, scale: float):
+        cfg, D, B = self.cfg, self.cfg.head_dim, self.B
+        lib = Q._L()
+        K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
+        _native.check(lib.mimir_kv_cache_write(ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D,
+                                               ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hk, D, self.cap,
+                                               ptr(self.pos), stream_ptr()), "kv_write")
+        _native.check(lib.mimir_attn_decode(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.att), B,
+                                            self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n,
+                                            ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits, stream_ptr()),
+                      "attn_decode")
+
+    def _decode_layers_tc(self):
+        cfg, d, D, B = self.cfg, self.cfg.d_model, self.cfg.head_dim, self.B
+        scale = 1.0 / math.sqrt(D)
+        xd, xa, xf = self.xdq[:, :d], self.xdq[:, : self.Hq * D], self.xdq[:, : self.F]
+        for l, w in enumerate(self.layers):
+            Q.round_act_q8(self.h, xd, d, 1, w["attn_norm"], cfg.eps)
+            Q.q4_tc(w["qkv_t"], xd, self.qkv, self.tc_scratch)
+            self._attention_step(l, scale)
+            Q.round_act_q8(self.att, xa, self.Hq * D, 0)
+            self._tc_allreduce(w["o_t"], xa, self.h, self.h1, 0)
+            Q.round_act_q8(self.h1, xd, d, 1, w["ffn_norm"], cfg.eps)
+            Q.q4_tc(w["gate_up_t"], xd, self.gu, self.tc_scratch)
+            Q.round_act_q8(self.gu, xf, self.F, 2)
+            self._tc_allreduce(w["down_t"], xf, self.h1, self.h, 1)
+
     def _decode_layers(self):
+        if self.engine == "tc":
+            return self._decode_layers_tc()
         cfg, d, D, B = self.cfg, self.cfg.d_model, self.cfg.head_dim, self.B
         scale = 1.0 / math.sqrt(D)
         lib = Q._L()
@@ -188,8 +240,12 @@ class TPDecoder:
         lib = Q._L()
         K.embedding_fwd(self.tokens, self.embed, None, self.h, 1)
         self._decode_layers()
-        Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=self.out_norm, eps=cfg.eps)
-        Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local)
+        if self.engine == "tc":
+            Q.round_act_q8(self.h, self.xdq[:, :d], d, 1, self.out_norm, cfg.eps)
+            Q.q4_tc(self.head_t, self.xdq[:, :d], self.logits_local, self.tc_scratch)
+        else:
+            Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=self.out_norm, eps=cfg.eps)
+            Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local)
         _native.check(lib.mimir_peer_allgather(ptr(self.logits_local), self._logits_arr, self._sig_arr,
                                                self.epochs[2:].data_ptr(), self.counters[2:].data_ptr(),
                                                self.logits_local.numel() * 4, self.rank, self.world, 2, stream_ptr()),
@@ -320,10 +376,8 @@ class TPDecoder:
         lib, w = Q._L(), self.layers[0]
         scale = 1.0 / math.sqrt(D)
         full = self.logits_all.view(torch.float32).view(self.world, self.B, self.Vl)
-        cases = {
+        common = {
             "embedding": lambda: K.embedding_fwd(self.tokens, self.embed, None, self.h, 1),
-            "rmsnorm_quantize": lambda: Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=w["attn_norm"], eps=cfg.eps),
-            "gemv_qkv": lambda: Q.q4_gemv(w["qkv"], self.xq, self.xs, self.qkv),
             "rope": lambda: K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True),
             "kv_write": lambda: _native.check(lib.mimir_kv_cache_write(
                 ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D, ptr(self.kc[0]), ptr(self.vc[0]), B,
@@ -332,18 +386,35 @@ class TPDecoder:
                 ptr(self.qkv), ptr(self.kc[0]), ptr(self.vc[0]), ptr(self.att), B, self.Hq, self.Hk, D, self.cap,
                 ptr(self.len), scale, self.qkv_n, ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits,
                 stream_ptr()), "attn_decode"),
-            "quantize_att": lambda: Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0),
-            "gemv_o_allreduce": lambda: self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0),
-            "gemv_gate_up": lambda: Q.q4_gemv(w["gate_up"], self.xq, self.xs, self.gu),
-            "swiglu_quantize": lambda: Q.quantize_act(self.gu, self.xq, self.xs, self.F, mode=2),
-            "gemv_down_allreduce": lambda: self._gemv_allreduce(w["down"], self.F, self.h1, self.h, 1),
-            "gemv_head": lambda: Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local),
             "logits_allgather": lambda: _native.check(lib.mimir_peer_allgather(
                 ptr(self.logits_local), self._logits_arr, self._sig_arr, self.epochs[2:].data_ptr(),
                 self.counters[2:].data_ptr(), self.logits_local.numel() * 4, self.rank, self.world, 2, stream_ptr()),
                 "allgather"),
             "argmax": lambda: full.permute(1, 0, 2).reshape(self.B, -1).argmax(-1),
         }
+        if self.engine == "tc":
+            xd, xa, xf = self.xdq[:, :d], self.xdq[:, : self.Hq * D], self.xdq[:, : self.F]
+            cases = dict(common, **{
+                "rmsnorm_round": lambda: Q.round_act_q8(self.h, xd, d, 1, w["attn_norm"], cfg.eps),
+                "tc_qkv": lambda: Q.q4_tc(w["qkv_t"], xd, self.qkv, self.tc_scratch),
+                "round_att": lambda: Q.round_act_q8(self.att, xa, self.Hq * D, 0),
+                "tc_o_allreduce": lambda: self._tc_allreduce(w["o_t"], xa, self.h, self.h1, 0),
+                "tc_gate_up": lambda: Q.q4_tc(w["gate_up_t"], xd, self.gu, self.tc_scratch),
+                "swiglu_round": lambda: Q.round_act_q8(self.gu, xf, self.F, 2),
+                "tc_down_allreduce": lambda: self._tc_allreduce(w["down_t"], xf, self.h1, self.h, 1),
+                "tc_head": lambda: Q.q4_tc(self.head_t, xd, self.logits_local, self.tc_scratch),
+            })
+        else:
+            cases = dict(common, **{
+                "rmsnorm_quantize": lambda: Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=w["attn_norm"], eps=cfg.eps),
+                "gemv_qkv": lambda: Q.q4_gemv(w["qkv"], self.xq, self.xs, self.qkv),
+                "quantize_att": lambda: Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0),
+                "gemv_o_allreduce": lambda: self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0),
+                "gemv_gate_up": lambda: Q.q4_gemv(w["gate_up"], self.xq, self.xs, self.gu),
+                "swiglu_quantize": lambda: Q.quantize_act(self.gu, self.xq, self.xs, self.F, mode=2),
+                "gemv_down_allreduce": lambda: self._gemv_allreduce(w["down"], self.F, self.h1, self.h, 1),
+                "gemv_head": lambda: Q.q4_gemv(self.head, self.xq, self.xs, self.logits_local),
+            })
         out = {}
         for name, fn in cases.items():
             for _ in range(3):

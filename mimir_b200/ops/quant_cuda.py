@@ -29,9 +29,13 @@ def _L():
             "mimir_f32_to_bf16": [P, P, L, P],
             "mimir_q4_planar_to_bf16": [P, P, P, L, P],
             "mimir_peer_allgather": [P, PP, PP, P, P, L, I, I, I, P],
+            "mimir_q4_planar_to_tiled": [P, P, P, I, I, P],
+            "mimir_round_act_q8": [P, P, P, I, I, I, I, F, P],
+            "mimir_q4_tc": [P, P, I, PP, PP, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         }.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = I, args
+        lib.mimir_q4_tiled_bytes.argtypes, lib.mimir_q4_tiled_bytes.restype = [I, I], L
         lib.mimir_q_set_peer_wait_ms.argtypes = [L]
         lib.mimir_q_set_peer_wait_ms.restype = None
         _done = True
@@ -103,4 +107,58 @@ def attn_decode(q, kc, vc, length, scale=None, splits=0, out=None):
     _native.check(_L().mimir_attn_decode(ptr(q), ptr(kc), ptr(vc), ptr(out), B, Hq, Hkv, D, cap, ptr(length),
                                          float(scale if scale is not None else D ** -0.5), q.stride(0), ptr(ws),
                                          ptr(cnt), splits, stream_ptr()), "attn_decode")
+    return out
+
+
+class TiledQ4:
+    """Q4_0 weight matrix [N, K] in the tensor-core kernel's layout: per (128-row tile, 64-column
+    k-block) 4608 contiguous bytes (quants [2][128][16], then fp16 scales [2][128])."""
+
+    def __init__(self, blob: torch.Tensor, N: int, K: int):
+        self.blob, self.N, self.K = blob, N, K
+
+    @staticmethod
+    def from_planar(w: PlanarQ4) -> "TiledQ4":
+        if w.K % 64:
+            raise ValueError("tiled Q4_0 needs K % 64 == 0")
+        blob = torch.empty(_L().mimir_q4_tiled_bytes(w.N, w.K), dtype=torch.uint8, device=w.scales.device)
+        _native.check(_L().mimir_q4_planar_to_tiled(ptr(w.scales), ptr(w.quants), ptr(blob), w.N, w.K, stream_ptr()),
+                      "planar_to_tiled")
+        return TiledQ4(blob, w.N, w.K)
+
+    @staticmethod
+    def quantize(w: torch.Tensor) -> "TiledQ4":
+        return TiledQ4.from_planar(PlanarQ4.quantize(w))
+
+    def nbytes(self) -> int:
+        return self.blob.numel()
+
+
+def round_act_q8(x, y, K, mode=0, gamma=None, eps=1e-5):
+    """y [rows, K] bf16 = the Q8_0 rounding (32-value blocks) of x (mode 0), of RMSNorm(x) * gamma
+    (mode 1) or of silu(gate) * up for x = [rows, 2K] (mode 2)."""
+    _native.check(_L().mimir_round_act_q8(ptr(x), ptr(gamma), ptr(y), y.stride(0), x.shape[0], K, mode, eps, stream_ptr()),
+                  "round_act_q8")
+    return y
+
+
+class TcScratch:
+    """Single-GPU scratch of ``q4_tc``: split-K partials, flag pad, epoch and arrival counter."""
+
+    def __init__(self, max_elems: int, device, max_splits: int = 8):
+        self.max_splits = max_splits
+        self.partial = torch.zeros(max_splits * max_elems, dtype=torch.float32, device=device)
+        self.sig = torch.zeros(64, dtype=torch.int32, device=device)
+        self.words = torch.zeros(2, dtype=torch.int32, device=device)
+        self.partial_arr = (ctypes.c_void_p * 1)(self.partial.data_ptr())
+        self.sig_arr = (ctypes.c_void_p * 1)(self.sig.data_ptr())
+
+
+def q4_tc(w: TiledQ4, x, out, scratch: TcScratch, residual=None, splits=0):
+    """out[b, n] = residual[b, n] + sum_k W[n, k] x[b, k] on the tensor cores (one GPU); x bf16 [B, K]."""
+    B = x.shape[0]
+    _native.check(_L().mimir_q4_tc(ptr(w.blob), ptr(x), x.stride(0), scratch.partial_arr, scratch.sig_arr,
+                                   scratch.words.data_ptr(), scratch.words[1:].data_ptr(), ptr(residual), ptr(out),
+                                   int(out.dtype == torch.float32), out.stride(0), w.N, w.K, B, splits,
+                                   scratch.max_splits, 0, 1, 0, stream_ptr()), "q4_tc")
     return out

@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the model's)")
+    ap.add_argument("--engine", default="tc", choices=["tc", "dp4a"])
     ap.add_argument("--sequential-prefill", action="store_true", help="feed the prompt token by token")
     ap.add_argument("--primitives", action="store_true",
                     help="also time each kernel of the step on its own (at the final cache length)")
@@ -40,7 +41,7 @@ def main():
     cfg = LlamaConfig.llama3_8b() if a.model == "llama3-8b" else LlamaConfig.tiny()
     if a.layers:
         cfg.n_layer = a.layers
-    dec = TPDecoder(cfg, rank, world, batch=a.batch, cap=a.prompt + a.gen + 8, seed=0)
+    dec = TPDecoder(cfg, rank, world, batch=a.batch, cap=a.prompt + a.gen + 8, seed=0, engine=a.engine)
     prompt = torch.randint(0, cfg.vocab, (a.batch, a.prompt), generator=torch.Generator().manual_seed(1))
 
     def timed(fn):
@@ -74,7 +75,7 @@ def main():
             "metric": "decode_tokens_per_s", "value": a.batch * a.gen / (ms_gen / 1e3), "unit": "tokens/s",
             "ms_per_token": ms_gen / a.gen, "prompt_tokens_per_s": a.batch * a.prompt / (ms_prompt / 1e3),
             "n_gpus": world, "batch": a.batch, "prompt": a.prompt, "gen": a.gen,
-            "config": {"model": a.model, "layers": cfg.n_layer, "weights": "Q4_0", "activations": "Q8_0",
+            "config": {"model": a.model, "layers": cfg.n_layer, "weights": "Q4_0", "activations": "Q8_0", "engine": dec.engine,
                        "kv_cache": "fp16", "parallelism": f"tp{world}"},
             "gpu_launches": int(launches), "launches_per_token": int(dec.launches_per_step), "primitive_us": prim, "error_word": err}))
     dec.close()

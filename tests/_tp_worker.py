@@ -65,7 +65,8 @@ def main():
         weights[f"blk.{l}.attn_norm"] = 1 + rnd(d)
         weights[f"blk.{l}.ffn_norm"] = 1 + rnd(d)
     B, T = 3, 9
-    dec = TPDecoder(cfg, rank, world, batch=B, cap=32, weights=weights)
+    dec = TPDecoder(cfg, rank, world, batch=B, cap=32, weights=weights, engine=os.environ.get("DECODE_ENGINE", "tc"))
+    assert dec.engine == os.environ.get("DECODE_ENGINE", "tc")
     prompt = torch.randint(0, cfg.vocab, (B, T), generator=torch.Generator().manual_seed(5))
     dec.reset()
     logits = []

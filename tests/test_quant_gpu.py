@@ -27,3 +27,50 @@ def test_decode_attention_split_kv(B, Hq, Hkv, D, cap, length, splits):
     assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
     assert torch.equal(out, out2)
     assert check_error_word() == 0
+
+
+@pytest.mark.parametrize("B,N,K,splits", [(1, 768, 4096, 0), (32, 4096, 512, 0), (5, 1000, 1792, 3),
+                                          (17, 256, 14336, 0), (32, 3584, 4096, 1), (8, 132, 128, 0)])
+def test_q4_tensor_core_product(B, N, K, splits):
+    from mimir_b200.ops import quant_cuda as Q
+    from mimir_b200.ops.quant import Q4_0, dequantize_raw, quantize_q4_0
+    from mimir_b200.ops._util import check_error_word
+    torch.manual_seed(B + N)
+    dev = "cuda"
+    w = torch.randn(N, K) * 0.05
+    raw = quantize_q4_0(w)
+    wd = dequantize_raw(Q4_0, raw, w.numel()).view(N, K).to(dev)
+    wt = Q.TiledQ4.from_planar(Q.PlanarQ4.from_ggml(raw.reshape(-1).to(dev), N, K))
+    x = torch.randn(B, K, device=dev).bfloat16()
+    res = torch.randn(B, N, device=dev).bfloat16()
+    scratch = Q.TcScratch(B * N, dev)
+    ref = x.float() @ wd.t()
+    out = Q.q4_tc(wt, x, torch.empty(B, N, device=dev), scratch, splits=splits)
+    tol = 2e-2 * ref.abs().max().item()
+    assert (out - ref).abs().max().item() < tol, ((out - ref).abs().max().item(), tol)
+    out2 = Q.q4_tc(wt, x, torch.empty(B, N, device=dev, dtype=torch.bfloat16), scratch, residual=res, splits=splits)
+    assert (out2.float() - (ref + res.float())).abs().max().item() < tol + 2e-2 * res.abs().max().item()
+    assert check_error_word() == 0
+
+
+@pytest.mark.parametrize("mode,rows,K", [(0, 3, 512), (1, 2, 4096), (2, 5, 1792), (1, 32, 4096), (2, 1, 14336)])
+def test_round_act_q8(mode, rows, K):
+    from mimir_b200.ops import quant_cuda as Q
+    torch.manual_seed(mode + K)
+    x = torch.randn(rows, 2 * K if mode == 2 else K, device="cuda").bfloat16()
+    gamma = (1 + 0.1 * torch.randn(K, device="cuda")).bfloat16()
+    y = Q.round_act_q8(x, torch.empty(rows, K, device="cuda", dtype=torch.bfloat16), K, mode, gamma)
+    xf = x.float()
+    if mode == 1:
+        t = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).bfloat16().float() * gamma.float()
+        t = t.bfloat16().float()
+    elif mode == 2:
+        t = torch.nn.functional.silu(xf[:, :K]) * xf[:, K:]
+    else:
+        t = xf
+    blocks = t.view(rows, K // 32, 32)
+    d = blocks.abs().amax(-1, keepdim=True) / 127
+    ref = (torch.round(blocks / d.clamp_min(1e-30)) * d).view(rows, K)
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 1.01 * d.max().item() + 1e-3, (err, d.max().item())     # at most one quantisation step
+    assert (y.float() - ref).abs().mean().item() < 0.02 * ref.abs().mean().item() + 1e-4

@@ -11,8 +11,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(world):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run(world, engine="tc"):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", DECODE_ENGINE=engine)
     worker = os.path.join(HERE, "_tp_worker.py")
     if world == 1:
         cmd = [sys.executable, worker]
@@ -24,18 +24,20 @@ def _run(world):
     return [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]
 
 
-def test_decode_single_gpu_matches_reference():
-    (r,) = _run(1)
+@pytest.mark.parametrize("engine", ["tc", "dp4a"])
+def test_decode_single_gpu_matches_reference(engine):
+    (r,) = _run(1, engine)
     assert r["err"] == 0
     assert r["cos"] > 0.995 and r["rel"] < 0.08, r
     assert r["cos_prefill"] > 0.995, r
     assert r["launches"] > 0
 
 
-def test_decode_tp2_matches_reference_and_ranks_agree():
+@pytest.mark.parametrize("engine", ["tc", "dp4a"])
+def test_decode_tp2_matches_reference_and_ranks_agree(engine):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    res = _run(2)
+    res = _run(2, engine)
     assert len(res) == 2
     for r in res:
         assert r["err"] == 0
