@@ -6,14 +6,15 @@
 // and the kernel stays bound by the 4.5-bit weight stream, not by arithmetic:
 //
 //   warp 0       bulk-copies raw weight tiles (4608 bytes: 2 x 128 x 16-byte quants +
-//                2 x 128 fp16 scales) and TMA-loads the activation tile [batch x 64] of the
-//                same k-block into a deep shared-memory ring (loads run 8 k-blocks ahead)
-//   warps 4..15  expand a raw tile to bf16 in the 128-byte-swizzled K-major layout the
+//                2 x 128 fp16 scales) into a 24-deep shared-memory ring: the weight stream
+//                is the only HBM traffic, and a slot is recycled as soon as it is expanded
+//   warp 2       TMA-loads the activation tile [batch x 64] of each k-block (L2 resident)
+//   warps 4..11  expand a raw tile to bf16 in the 128-byte-swizzled K-major layout the
 //                tensor core reads (nibble -> 128 + n via a byte permute, -136, x scale);
-//                three groups of four warps take k-blocks in turn, because one tile's
+//                two groups of four warps take k-blocks in turn, because one tile's
 //                expansion is a latency chain (shared load, convert, store, proxy fence)
 //   warp 1       issues tcgen05.mma (accumulator 128 x batch in TMEM, double-buffered)
-//   warps 16..19 read the accumulator and write fp32 partials [split][b][n]
+//   warps 12..15 read the accumulator and write fp32 partials [split][b][n]
 //
 // Work is split over (row tile, k range) so that every SM streams weights; after the
 // main loop all blocks meet (they are co-resident: the grid never exceeds the SM
@@ -33,9 +34,10 @@ namespace mimir {
 constexpr int kTcRows = 128;
 constexpr int kTcBK = 64;
 constexpr int kTcRawBytes = 2 * kTcRows * 16 + 2 * kTcRows * 2;  // 4608
-constexpr int kTcRawStages = 8;
-constexpr int kTcAStages = 6;
-constexpr int kTcGroups = 3;  // groups of four expanding warps; group g owns the k-blocks it % kTcGroups == g
+constexpr int kTcRawStages = 24;  // raw weight tiles in flight: ~110 KB per SM covers HBM latency at full bandwidth
+constexpr int kTcXStages = 8;
+constexpr int kTcAStages = 4;
+constexpr int kTcGroups = 2;  // groups of four expanding warps; group g owns the k-blocks it % kTcGroups == g
 constexpr int kTcThreads = (4 + 4 * kTcGroups + 4) * 32;
 
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -79,7 +81,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
              int splits, unsigned* err) {
   constexpr int A_BYTES = kTcRows * kTcBK * 2;  // 16 KB
   constexpr int X_BYTES = BNB * kTcBK * 2;
-  constexpr int RSTAGE = 4096 + 5120;           // activation tile (1024-byte aligned) + raw weight tile
+  constexpr int XSTAGE = 4096;                  // activation tile slot (1024-byte aligned)
   constexpr uint32_t TMEM_COLS = 2 * BNB < 32 ? 32 : 2 * BNB;
   constexpr uint32_t IDESC = make_idesc_bf16(kTcRows, BNB, false, false);
 
@@ -87,10 +89,13 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* a_ring = smem;                                    // kTcAStages x expanded bf16 weight tile
-  uint8_t* raw_ring = smem + kTcAStages * A_BYTES;           // kTcRawStages x (x tile | raw weight tile)
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * RSTAGE);
+  uint8_t* x_ring = smem + kTcAStages * A_BYTES;             // kTcXStages x activation tile
+  uint8_t* raw_ring = x_ring + kTcXStages * XSTAGE;          // kTcRawStages x raw weight tile
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * kTcRawBytes);
   uint64_t* raw_empty = raw_full + kTcRawStages;
-  uint64_t* a_full = raw_empty + kTcRawStages;
+  uint64_t* x_full = raw_empty + kTcRawStages;
+  uint64_t* x_empty = x_full + kTcXStages;
+  uint64_t* a_full = x_empty + kTcXStages;
   uint64_t* a_empty = a_full + kTcAStages;
   uint64_t* tfull = a_empty + kTcAStages;
   uint64_t* tempty = tfull + 2;
@@ -106,7 +111,11 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 129);  // 128 expanding threads + the MMAs that read the activation tile
+      mbar_init(&raw_empty[s], 128);
+    }
+    for (int s = 0; s < kTcXStages; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], 1);
     }
     for (int s = 0; s < kTcAStages; ++s) {
       mbar_init(&a_full[s], 128);
@@ -129,8 +138,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {  // raw weight tiles and activation tiles
-      tma_prefetch_desc(&tmX);
+    if (lane == 0) {  // raw weight tiles
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -140,10 +148,26 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
           const int s = it % kTcRawStages;
           const uint32_t ph = (it / kTcRawStages) & 1;
           if (!mbar_wait(&raw_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
-          mbar_arrive_expect_tx(&raw_full[s], kTcRawBytes + X_BYTES);
-          tma_load_2d(raw_ring + s * RSTAGE, &tmX, &raw_full[s], kb * kTcBK, 0);  // rows >= B read zeros
-          bulk_load_1d(raw_ring + s * RSTAGE + 4096,
+          mbar_arrive_expect_tx(&raw_full[s], kTcRawBytes);
+          bulk_load_1d(raw_ring + s * kTcRawBytes,
                        wt + (static_cast<size_t>(tile) * kb_total + kb) * kTcRawBytes, kTcRawBytes, &raw_full[s]);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {  // activation tiles
+      tma_prefetch_desc(&tmX);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int split = u % splits;
+        const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % kTcXStages;
+          const uint32_t ph = (it / kTcXStages) & 1;
+          if (!mbar_wait(&x_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
+          mbar_arrive_expect_tx(&x_full[s], X_BYTES);
+          tma_load_2d(x_ring + s * XSTAGE, &tmX, &x_full[s], kb * kTcBK, 0);  // rows >= B read zeros
         }
       }
     }
@@ -159,18 +183,18 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BNB;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcAStages, sr = it % kTcRawStages;
-          const uint32_t ph = (it / kTcAStages) & 1;
-          // the expanding threads arrive here only after the stage's loads (activation tile included) landed
+          const int s = it % kTcAStages, sx = it % kTcXStages;
+          const uint32_t ph = (it / kTcAStages) & 1, phx = (it / kTcXStages) & 1;
+          if (!mbar_wait(&x_full[sx], phx, abort_flag, err)) { ok = false; break; }
           if (!mbar_wait(&a_full[s], ph, abort_flag, err)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + s * A_BYTES), 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(raw_ring + sr * RSTAGE), 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(x_ring + sx * XSTAGE), 16, 1024);
 #pragma unroll
           for (int k = 0; k < kTcBK / 16; ++k)
             umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
-          umma_commit(&raw_empty[sr]);
+          umma_commit(&x_empty[sx]);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
@@ -190,7 +214,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         const uint32_t phr = (it / kTcRawStages) & 1, pha = (it / kTcAStages) & 1;
         if (!mbar_wait(&raw_full[sr], phr, abort_flag, err)) { ok = false; break; }
         if (!mbar_wait(&a_empty[sa], pha ^ 1, abort_flag, err)) { ok = false; break; }
-        const uint8_t* raw = raw_ring + sr * RSTAGE + 4096;
+        const uint8_t* raw = raw_ring + sr * kTcRawBytes;
         uint8_t* arow = a_ring + sa * A_BYTES + t * 128;
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
@@ -375,7 +399,7 @@ round_act_q8_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 template <int BNB>
 static int launch_q4_tc(const CUtensorMap& tmX, const uint8_t* wt, const TcTail& tail, int N, int K, int B, int splits,
                         cudaStream_t st) {
-  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2) + kTcRawStages * (4096 + 5120) + 1024 + 512;
+  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2) + kTcXStages * 4096 + kTcRawStages * kTcRawBytes + 1024 + 1024;
   auto kern = q4_tc_kernel<BNB>;
   static bool configured = false;
   if (!configured) {

@@ -28,6 +28,7 @@ class ErrNotBatchable(MimirError): pass
 class ErrCheckpoint(MimirError): pass
 class ErrFrozen(MimirError): pass
 class ErrNilTensor(MimirError): pass
+class ErrUnsupported(MimirError): pass
 
 
 def classify(exc: BaseException) -> MimirError:

@@ -1,0 +1,62 @@
+"""Dataset readers and the Parquet reader (reference: data/datasets/*_test.go, io/parquet/*_test.go)."""
+import os
+
+import torch
+
+from mimir_b200.data import datasets
+from mimir_b200.io import mim, parquet
+
+
+def test_mnist_idx_round_trip(tmp_path):
+    img = torch.randint(0, 256, (10, 28, 28), dtype=torch.uint8)
+    lab = torch.arange(10, dtype=torch.uint8)
+    datasets.write_idx(os.path.join(tmp_path, "train-images-idx3-ubyte"), img)
+    datasets.write_idx(os.path.join(tmp_path, "train-labels-idx1-ubyte"), lab)
+    ds = datasets.mnist(str(tmp_path), batch_size=4, shuffle=False, normalize=False)
+    batches = list(ds)
+    assert [b.x.shape[0] for b in batches] == [4, 4, 2]
+    assert torch.equal((batches[0].x.data() * 255).round().to(torch.uint8)[:, 0], img[:4])
+    assert batches[2].y.data().tolist() == [8, 9]
+
+
+def test_csv_and_shards(tmp_path):
+    for k in range(2):
+        with open(os.path.join(tmp_path, f"s{k}.csv"), "w") as f:
+            f.write("a,b,y\n")
+            for i in range(5):
+                f.write(f"{i + 10 * k},{2 * i},{i % 2}\n")
+    X, y, names = datasets.read_csv(os.path.join(tmp_path, "s0.csv"), "y")
+    assert names == ["a", "b"] and X.shape == (5, 2) and y.tolist() == [0, 1, 0, 1, 0]
+    st = datasets.csv_shards(os.path.join(tmp_path, "s*.csv"), "y", batch_size=4)
+    rows = torch.cat([b.x.data() for b in st])
+    assert rows.shape == (10, 2) and rows[:, 0].tolist() == [0, 1, 2, 3, 4, 10, 11, 12, 13, 14]
+
+
+def test_parquet_reader_and_shards(tmp_path):
+    p = os.path.join(tmp_path, "d.parquet")
+    cols = {"f0": torch.arange(100).float(), "f1": torch.arange(100).double() * 2, "label": torch.arange(100) % 3,
+            "name": [f"r{i}" for i in range(100)]}
+    for comp in ("snappy", "gzip", "zstd"):
+        parquet.write(p, cols, compression=comp, row_group_size=40)
+        f = parquet.File(p)
+        assert f.rows == 100 and f.row_groups == 3 and f.columns == ["f0", "f1", "label", "name"]
+        got = f.read()
+        assert torch.equal(got["f0"], cols["f0"]) and got["name"][7] == "r7" and got["label"].dtype == torch.int64
+        X, y = f.matrix(["f0", "f1"], "label", row_group=1)
+        assert X.shape == (40, 2) and X[0].tolist() == [40.0, 80.0] and y[0] == 40 % 3
+    st = datasets.parquet_shards(p, ["f0", "f1"], "label", batch_size=32)
+    assert sum(b.x.shape[0] for b in st) == 100
+
+
+def test_mapped_and_synthetic(tmp_path):
+    p = os.path.join(tmp_path, "d.mim")
+    mim.write_tensors(p, {"x": torch.arange(24.0).view(6, 4), "y": torch.arange(6)})
+    ds = datasets.mapped(p, batch_size=4, shuffle=False)
+    b = list(ds)
+    assert b[0].x.data()[1].tolist() == [4.0, 5, 6, 7] and b[1].y.data().tolist() == [4, 5]
+    c = datasets.synthetic_classification(rows=64, classes=3, batch_size=16)
+    assert len(list(c)) == 4
+    t = datasets.synthetic_tokens(rows=8, seq=16, vocab=32, batch_size=4)
+    b0 = next(iter(t))
+    assert b0.x.shape == (4, 16) and b0.y.shape == (4, 16)
+    assert datasets.synthetic_regression(rows=10, batch_size=5).rows() == 10
