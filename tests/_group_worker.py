@@ -26,3 +26,31 @@ def grads(g):
     g.all_reduce_grads(ps)
     return {"p0": same[0].sum().item(), "g": [p.grad().data().flatten()[0].item() for p in ps],
             "calls": g.traffic["all_reduce"]}
+
+
+def dp_fit(g, mode):
+    """Trains a small MLP data-parallel; returns the losses and a parameter checksum."""
+    from mimir_b200 import nn, optim, train
+    from mimir_b200.data import Tensors
+    nn.manual_seed(g.rank + 5)          # different initial weights per rank: the broadcast must fix that
+    model = nn.Sequential(nn.Linear(6, 16), nn.Tanh(), nn.Linear(16, 3))
+    gen = torch.Generator().manual_seed(0)
+    x, y = torch.randn(40, 6, generator=gen), torch.randint(0, 3, (40,), generator=gen)
+    ds = Tensors(x, y, batch_size=10, shuffle=True, seed=1)
+    opt = optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    from mimir_b200.parallel.replicas import fit_data_parallel
+    reps = fit_data_parallel(model, opt, ds, nn.loss.cross_entropy, 3, g, mode=mode)
+    return {"loss": [r.loss for r in reps], "w": [float(p._data.double().sum()) for p in model.parameters()]}
+
+
+def single_fit():
+    from mimir_b200 import nn, optim, train
+    from mimir_b200.data import Tensors
+    nn.manual_seed(5)
+    model = nn.Sequential(nn.Linear(6, 16), nn.Tanh(), nn.Linear(16, 3))
+    gen = torch.Generator().manual_seed(0)
+    x, y = torch.randn(40, 6, generator=gen), torch.randint(0, 3, (40,), generator=gen)
+    ds = Tensors(x, y, batch_size=10, shuffle=True, seed=1)
+    opt = optim.SGD(model.parameters(), lr=0.1, momentum=0.9)
+    reps = train.fit(model, opt, ds, loss=nn.loss.cross_entropy, epochs=3)
+    return {"loss": [r.loss for r in reps], "w": [float(p._data.double().sum()) for p in model.parameters()]}
