@@ -83,6 +83,8 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("mimir_cast_bf16_f32", I, P, P, L, F, P)
     sig("mimir_axpby", I, P, P, P, L, F, F, P)
     sig("mimir_sumsq", I, P, L, I, P, P)
+    sig("mimir_philox_uniform", I, P, L, ctypes.c_ulonglong, P)
+    sig("mimir_philox_dropout", I, P, P, L, ctypes.c_ulonglong, F, P)
     sig("mimir_attention_fwd", I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, P)
     sig("mimir_attention_bwd", I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I,
         I, I, I, F, P)

@@ -311,6 +311,54 @@ static inline unsigned blocks_for(size_t n, int per_block) {
 
 }  // namespace mimir
 
+
+// ---------------------------------------------------------------------------
+// Philox4x32-10 (counter = block index, key = the 64-bit seed).  Element i of a
+// stream is word i % 4 of block i / 4; a thread produces one block.  Uniforms are
+// the top 24 bits / 2^24, exactly as the host generator computes them, so a
+// dropout mask drawn here matches the CPU's bit for bit
+// (reference: backend/internal/gen/gen.go:577-610, backend/cpu/rand.go).
+// ---------------------------------------------------------------------------
+namespace mimir {
+__device__ __forceinline__ uint4 philox4x32_10(uint64_t ctr, uint64_t seed) {
+  uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32), c2 = 0, c3 = 0;
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0; c1 = lo1; c2 = hi0 ^ c3 ^ k1; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+__global__ void philox_uniform_kernel(float* __restrict__ out, size_t n, uint64_t seed) {
+  const size_t blk = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (blk * 4 >= n) return;
+  const uint4 w = philox4x32_10(blk, seed);
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (blk * 4 + j < n) out[blk * 4 + j] = static_cast<float>(v[j] >> 8) * (1.0f / 16777216.0f);
+}
+// y = x * keep / (1 - p) with keep = uniform >= p (bf16, 4 values per thread)
+__global__ void philox_dropout_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n,
+                                      uint64_t seed, float p, float scale) {
+  const size_t blk = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (blk * 4 >= n) return;
+  const uint4 w = philox4x32_10(blk, seed);
+  const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const size_t i = blk * 4 + j;
+    if (i < n) {
+      const float u = static_cast<float>(v[j] >> 8) * (1.0f / 16777216.0f);
+      y[i] = u >= p ? __float2bfloat16_rn(__bfloat162float(x[i]) * scale) : __float2bfloat16_rn(0.f);
+    }
+  }
+}
+}  // namespace mimir
+
 using namespace mimir;
 typedef __nv_bfloat16 bf16;
 
@@ -432,6 +480,25 @@ MIMIR_API int mimir_adamw_flat(float* master, void* param, const void* grad, int
     adamw_flat_kernel<bf16><<<blocks_for(n / 8, 256), 256, 0, st>>>(master, static_cast<bf16*>(param),
                                                                    static_cast<const bf16*>(grad), m, v,
                                                                    n / 8, decay_n / 8, a, gnorm_sq, hyper);
+  count_launch();
+  return 0;
+}
+
+MIMIR_API int mimir_philox_uniform(float* out, long long n, unsigned long long seed, cudaStream_t st) {
+  if (n <= 0) return 0;
+  const size_t blocks = (static_cast<size_t>(n) + 3) / 4;
+  philox_uniform_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, st>>>(out, static_cast<size_t>(n), seed);
+  count_launch();
+  return 0;
+}
+// Inverted dropout with drop probability p; the same seed reproduces the mask (backward pass, other devices).
+MIMIR_API int mimir_philox_dropout(const void* x, void* y, long long n, unsigned long long seed, float p,
+                                   cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!(p >= 0.f && p < 1.f)) return refuse("dropout: probability %f outside [0, 1)", p);
+  const size_t blocks = (static_cast<size_t>(n) + 3) / 4;
+  philox_dropout_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, st>>>(
+      static_cast<const bf16*>(x), static_cast<bf16*>(y), static_cast<size_t>(n), seed, p, 1.f / (1.f - p));
   count_launch();
   return 0;
 }

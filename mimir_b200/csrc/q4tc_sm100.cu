@@ -28,6 +28,7 @@
 //
 // Replaces the reference's SIMT qmatmul (backend/internal/gen/quant.go:163-209).
 #include "quant_common.cuh"
+#include <cstdlib>
 
 namespace mimir {
 
@@ -78,7 +79,7 @@ __device__ __forceinline__ void expand8(uint32_t w, int shift, __nv_bfloat162 d2
 template <int BNB>
 __global__ void __launch_bounds__(kTcThreads, 1)
 q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ wt, TcTail tail, int N, int K, int B,
-             int splits, unsigned* err) {
+             int splits, unsigned* err, int dbg) {
   constexpr int A_BYTES = kTcRows * kTcBK * 2;  // 16 KB
   constexpr int X_BYTES = BNB * kTcBK * 2;
   constexpr int XSTAGE = 4096;                  // activation tile slot (1024-byte aligned)
@@ -190,9 +191,11 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
           tc_fence_after();
           const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + s * A_BYTES), 16, 1024);
           const uint64_t bdesc = make_smem_desc_sw128(smem_u32(x_ring + sx * XSTAGE), 16, 1024);
+          if (!(dbg & 4)) {
 #pragma unroll
-          for (int k = 0; k < kTcBK / 16; ++k)
-            umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kTcBK / 16; ++k)
+              umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(&a_empty[s]);
           umma_commit(&x_empty[sx]);
         }
@@ -217,7 +220,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         const uint8_t* raw = raw_ring + sr * kTcRawBytes;
         uint8_t* arow = a_ring + sa * A_BYTES + t * 128;
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
+        for (int blk = 0; blk < 2 && !(dbg & 1); ++blk) {
           const uint4 q = *reinterpret_cast<const uint4*>(raw + (blk * kTcRows + t) * 16);
           const __half dh = *reinterpret_cast<const __half*>(raw + 2 * kTcRows * 16 + (blk * kTcRows + t) * 2);
           const __nv_bfloat162 d2 = __float2bfloat162_rn(__half2float(dh));
@@ -232,7 +235,7 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
             *reinterpret_cast<uint4*>(arow + chunk * 16) = make_uint4(lo[0], lo[1], hi[0], hi[1]);
           }
         }
-        fence_proxy_async_smem();  // the tensor core reads this tile through the async proxy
+        if (!(dbg & 2)) fence_proxy_async_smem();  // the tensor core reads this tile through the async proxy
         mbar_arrive(&a_full[sa]);
         mbar_arrive(&raw_empty[sr]);
       }
@@ -409,7 +412,8 @@ static int launch_q4_tc(const CUtensorMap& tmX, const uint8_t* wt, const TcTail&
   }
   const int units = ceil_div(N, kTcRows) * splits;
   const int grid = units < sm_count() ? units : sm_count();  // one block per SM: all blocks are resident
-  kern<<<grid, kTcThreads, SMEM, st>>>(tmX, wt, tail, N, K, B, splits, error_word_dev());
+  static int dbg = getenv("MIMIR_Q4TC_DEBUG") ? atoi(getenv("MIMIR_Q4TC_DEBUG")) : 0;
+  kern<<<grid, kTcThreads, SMEM, st>>>(tmX, wt, tail, N, K, B, splits, error_word_dev(), dbg);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("q4 tensor-core product: launch failed");
 }

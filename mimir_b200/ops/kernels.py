@@ -149,3 +149,18 @@ def adamw_flat(master, param, grad, m, v, *, decay_n=None, lr, beta1=0.9, beta2=
                                         int(grad.dtype == torch.float32), ptr(m), ptr(v), n, decay_n,
                                         lr, beta1, beta2, eps, wd, step, gscale, ptr(gnorm_sq), clip,
                                         ptr(hyper), stream_ptr()), "adamw")
+
+
+def philox_uniform(n: int, seed: int, device="cuda") -> torch.Tensor:
+    """``n`` uniforms in [0, 1) of the Philox stream ``seed``; bit-identical to ``tensor.random.philox_uniform``."""
+    out = torch.empty(n, dtype=torch.float32, device=device)
+    _native.check(_L().mimir_philox_uniform(ptr(out), n, seed & 0xFFFFFFFFFFFFFFFF, stream_ptr()), "philox_uniform")
+    return out
+
+
+def dropout(x, p: float, seed: int, out=None):
+    """Inverted dropout of a bf16 tensor with the Philox mask of ``seed`` (same seed = same mask)."""
+    out = torch.empty_like(x) if out is None else out
+    _native.check(_L().mimir_philox_dropout(ptr(x), ptr(out), x.numel(), seed & 0xFFFFFFFFFFFFFFFF, p, stream_ptr()),
+                  "dropout")
+    return out

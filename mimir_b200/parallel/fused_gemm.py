@@ -44,20 +44,27 @@ class ShardedWeight:
     """A weight [N, K] sharded by rows: every rank holds a full-size symmetric buffer and
     keeps its own rows current in it; the other rows are scratch the fused GEMM fills."""
 
-    def __init__(self, N: int, K: int, rank: int, world: int, group=None):
+    def __init__(self, N: int, K: int, rank: int, world: int, group=None, arena: SymmetricBuffer | None = None,
+                 offset: int = 0):
+        """``arena`` / ``offset`` place the matrix inside an existing symmetric buffer (one allocation and
+        one handle exchange for a whole model) instead of a buffer of its own."""
         if N % world:
             raise ValueError("rows must divide by the number of ranks")
+        if offset % 16:
+            raise ValueError("the matrix must start on a 16-byte boundary of the arena")
         self.N, self.K, self.rank, self.world = N, K, rank, world
-        self.buf = SymmetricBuffer(N * K * 2, rank, world, group)
-        self.full = self.buf.view(torch.bfloat16, 0, N * K).view(N, K)
+        self._own_buf = arena is None
+        self.buf = SymmetricBuffer(N * K * 2, rank, world, group) if arena is None else arena
+        self.full = self.buf.view(torch.bfloat16, offset, N * K).view(N, K)
         self.rows = N // world
         self.shard = self.full[rank * self.rows: (rank + 1) * self.rows]
         dev = self.full.device
         self.state = torch.zeros(world + 2, dtype=torch.int32, device=dev)  # shard counters, epoch, done
-        self._arr = self.buf.ptr_array()
+        self._arr = self.buf.ptr_array(offset)
 
     def close(self):
-        self.buf.close()
+        if self._own_buf:
+            self.buf.close()
 
 
 def gemm_allgather(x: torch.Tensor, w: ShardedWeight, out=None, bias=None, gelu=False, residual=False, aux=None):

@@ -104,6 +104,33 @@ def bench_attention(a):
         print(json.dumps({"kernel": "torch_sdpa_fwd", "ms": t, "tflops": flops_fwd / t / 1e9}), flush=True)
 
 
+def bench_q4(a):
+    """Q4_0 weight x activation products of a decode step: the tensor-core kernel and the dp4a GEMV."""
+    from ..ops import quant_cuda as Q
+    N, K, B = a.n, a.k, a.b
+    dev = "cuda"
+    nb = N * K // 32
+    planar = Q.PlanarQ4((torch.rand(nb, device=dev) * 0.01).half(), torch.randint(0, 256, (nb * 16,), device=dev, dtype=torch.uint8), N, K)
+    tiled = Q.TiledQ4.from_planar(planar)
+    x = torch.randn(B, K, device=dev).bfloat16()
+    out = torch.empty(B, N, device=dev, dtype=torch.bfloat16)
+    scratch = Q.TcScratch(B * N, dev)
+    xq = torch.randint(-127, 127, (B, K), device=dev, dtype=torch.int8)
+    xs = torch.rand(B, K // 32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
+    nbytes = N * K * 0.5625
+    peak = _peaks().get("hbm_gbs")
+    for name, fn in (("q4_tc", lambda: Q.q4_tc(tiled, x, out, scratch, splits=a.splits)),
+                     ("q4_gemv_dp4a", lambda: Q.q4_gemv(planar, xq, xs, out))):
+        if a.only and a.only != name:
+            continue
+        t = time_ms(fn, a.iters, flush)
+        rec = {"kernel": name, "N": N, "K": K, "B": B, "us": t * 1e3, "weight_gbs": nbytes / t / 1e6}
+        if peak:
+            rec["frac_of_measured_hbm_copy"] = rec["weight_gbs"] / peak
+        print(json.dumps(rec), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -118,12 +145,18 @@ def main():
     t.add_argument("--t", type=int, default=1024)
     t.add_argument("--h", type=int, default=12)
     t.add_argument("--d", type=int, default=64)
-    for p in (g, t):
+    q = sub.add_parser("q4")
+    q.add_argument("--n", type=int, default=28672)
+    q.add_argument("--k", type=int, default=4096)
+    q.add_argument("--b", type=int, default=1)
+    q.add_argument("--splits", type=int, default=0)
+    q.add_argument("--only", default="")
+    for p in (g, t, q):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention}[a.cmd](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "q4": bench_q4}[a.cmd](a)
 
 
 if __name__ == "__main__":

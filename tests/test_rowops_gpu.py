@@ -159,3 +159,18 @@ def test_swiglu_rope_act():
     close(x, ref)
     K.rope_(x, pos, freqs, 0, H, D, interleaved=False, inverse=True)
     close(x, x0.float(), 3e-2)
+
+
+def test_philox_kernel_matches_host_stream_bit_for_bit():
+    from mimir_b200.ops import kernels as K
+    from mimir_b200.tensor.random import philox_uniform
+    for n, seed in ((1, 0), (1027, 42), (65536, 0x1234567890ABCDEF)):
+        got = K.philox_uniform(n, seed).cpu()
+        want = philox_uniform((n,), seed, "cpu")
+        assert torch.equal(got, want)
+    x = torch.randn(4099, device="cuda").bfloat16()
+    y = K.dropout(x, 0.25, 7)
+    keep = philox_uniform((4099,), 7, "cpu") >= 0.25
+    ref = torch.where(keep.cuda(), (x.float() / 0.75).bfloat16(), torch.zeros_like(x))
+    assert torch.equal(y, ref)
+    assert torch.equal(K.dropout(x, 0.25, 7), y)
