@@ -28,17 +28,22 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 METRIC = "train_tokens_per_s"
 MODEL = "gpt2-small(12L,d768,12h,vocab50257,ctx1024)"
 
-SMI_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+SMI_QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    """Samples nvidia-smi clocks and throttle reasons of one GPU.  The process starts early (its
+    start-up takes about a second) and keeps running; ``window(t0, t1)`` summarises the samples
+    whose time stamps fall inside a timed region."""
+
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
+        self.rows = []
 
     def start(self):
         try:
@@ -49,37 +54,42 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def stop(self) -> dict:
+    def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        self.proc = None
+        import datetime
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
+            if len(f) < 10:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-                power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                self.rows.append((ts, float(f[2]), float(f[3]), float(f[4]), [v.lower().startswith("active") for v in f[6:10]]))
             except ValueError:
                 continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # under load = the upper half of the samples (the sampler starts slightly early)
-        sm_sorted = sorted(sm)
-        load = sm_sorted[len(sm_sorted) // 4:]
-        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "power_w_max": max(power), "samples": len(sm)}
+
+    def window(self, t0: float, t1: float) -> dict:
+        """Median SM clock, maximum clock, power and active throttle reasons between two ``time.time()`` stamps."""
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable or no samples"]}
+        inside = [r for r in self.rows if t0 - 0.05 <= r[0] <= t1 + 0.05]
+        note = None
+        if not inside:      # region shorter than the sampling period: take the nearest sample
+            inside = [min(self.rows, key=lambda r: abs(r[0] - (t0 + t1) / 2))]
+            note = "nearest sample (timed region shorter than the 100 ms sampling period)"
+        reasons = sorted({n for r in inside for n, on in zip(self.NAMES, r[4]) if on})
+        out = {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": max(r[2] for r in inside),
+               "reasons": reasons, "power_w_max": max(r[3] for r in inside), "samples": len(inside)}
+        if note:
+            out["note"] = note
+        return out
 
 
 def reference_arm(args) -> int:
@@ -164,38 +174,41 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     # warm-up through the public call (also captures the graph)
     for i in range(warmup):
         loss = tr.step(toks[i % nbatch], tgts[i % nbatch])
 
     def timed(fn):
-        sampler = ClockSampler(local_rank)
         barrier()
-        sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = lib.mimir_launch_count()
-        w0 = time.perf_counter()
+        w0, t0 = time.perf_counter(), time.time()
         e0.record()
         for i in range(args.steps):
             fn(i)
         e1.record()
         barrier()
-        wall = time.perf_counter() - w0
-        clocks = sampler.stop()
+        wall, t1 = time.perf_counter() - w0, time.time()
         ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item(), lib.mimir_launch_count() - l0, clocks, wall
+        return t.item(), lib.mimir_launch_count() - l0, (t0, t1), wall
 
     # device-timed loop: batch already resident, no host round trip per step
     eng.tokens.copy_(toks[0].view(-1))
     eng.targets.copy_(tgts[0].view(-1))
-    ms_dev, launches, clocks, _ = timed(lambda i: tr.run_device_step())
+    ms_dev, launches, win_dev, _ = timed(lambda i: tr.run_device_step())
     # end to end: H2D of the batch and D2H of the loss every step
     losses = []
-    ms_e2e, _, clocks_e2e, wall_e2e = timed(lambda i: losses.append(tr.step(toks[i % nbatch], tgts[i % nbatch])))
+    ms_e2e, _, win_e2e, wall_e2e = timed(lambda i: losses.append(tr.step(toks[i % nbatch], tgts[i % nbatch])))
     err = check_error_word()
+    time.sleep(0.25)      # let the sampler print the last samples of the region
+    sampler.stop()
+    clocks, clocks_e2e = sampler.window(*win_dev), sampler.window(*win_e2e)
 
     tokens_per_step = B * T * world
     value = tokens_per_step * args.steps / (ms_dev / 1e3)

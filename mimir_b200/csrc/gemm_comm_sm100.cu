@@ -464,7 +464,7 @@ MIMIR_API int mimir_gemm_reduce_scatter(const void* A, const void* B, int M, int
                                         cudaStream_t stream) {
   if (M % world || (M / world) % 32 || N % 8 || lda % 8 || ldb % 8)
     return refuse("gemm_reduce_scatter: M / world must be a multiple of 32, sizes multiples of 8");
-  if (a_mn != b_mn) return refuse("gemm_reduce_scatter: NT and TN products only");
+  if (a_mn && !b_mn) return refuse("gemm_reduce_scatter: NT, NN and TN products only");
   CUtensorMap tmA, tmB, tmC;
   TmArr tmS = {};
   if (encode2d(&tmA, A, M, K, lda, a_mn, kBM)) return -1;
@@ -486,6 +486,7 @@ MIMIR_API int mimir_gemm_reduce_scatter(const void* A, const void* B, int M, int
   cm.epoch = static_cast<unsigned*>(epoch);
   cm.done_count = static_cast<unsigned*>(done_count);
   cm.rank = rank; cm.world = world; cm.rows_per_rank = rpr; cm.slot = slot; cm.wait_ns = g_comm_wait_ns;
-  if (!a_mn) return launch_comm<256, false, false, 5, 2>(tmA, tmB, tmC, tmS, ep, cm, M, N, K, stream);
+  if (!a_mn && !b_mn) return launch_comm<256, false, false, 5, 2>(tmA, tmB, tmC, tmS, ep, cm, M, N, K, stream);
+  if (!a_mn) return launch_comm<256, false, true, 5, 2>(tmA, tmB, tmC, tmS, ep, cm, M, N, K, stream);
   return launch_comm<256, true, true, 5, 2>(tmA, tmB, tmC, tmS, ep, cm, M, N, K, stream);
 }

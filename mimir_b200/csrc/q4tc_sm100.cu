@@ -5,12 +5,12 @@
 // (16 or 32 columns), so a single instruction stream covers every row of the batch
 // and the kernel stays bound by the 4.5-bit weight stream, not by arithmetic:
 //
-//   warp 0       bulk-copies raw weight tiles (4608 bytes: 2 x 128 x 16-byte quants +
-//                2 x 128 fp16 scales) into a 24-deep shared-memory ring: the weight stream
-//                is the only HBM traffic, and a slot is recycled as soon as it is expanded
-//   warp 2       TMA-loads the activation tile [batch x 64] of each k-block (L2 resident)
+//   warp 0       bulk-copies raw weight tiles (4608 bytes per k-block: 2 x 128 x 16-byte quants +
+//                2 x 128 fp16 scales), four k-blocks per copy, into a 6-deep shared-memory ring:
+//                the weight stream is the only HBM traffic
 //   warps 4..11  expand a raw tile to bf16 in the 128-byte-swizzled K-major layout the
-//                tensor core reads (nibble -> 128 + n via a byte permute, -136, x scale);
+//                tensor core reads (nibble -> 128 + n via a byte permute, -136, x scale) and
+//                copy the k-block's activation tile [batch x 64] (L2 resident) beside it;
 //                two groups of four warps take k-blocks in turn, because one tile's
 //                expansion is a latency chain (shared load, convert, store, proxy fence)
 //   warp 1       issues tcgen05.mma (accumulator 128 x batch in TMEM, double-buffered)
@@ -28,15 +28,14 @@
 //
 // Replaces the reference's SIMT qmatmul (backend/internal/gen/quant.go:163-209).
 #include "quant_common.cuh"
-#include <cstdlib>
 
 namespace mimir {
 
 constexpr int kTcRows = 128;
 constexpr int kTcBK = 64;
 constexpr int kTcRawBytes = 2 * kTcRows * 16 + 2 * kTcRows * 2;  // 4608
-constexpr int kTcRawStages = 24;  // raw weight tiles in flight: ~110 KB per SM covers HBM latency at full bandwidth
-constexpr int kTcXStages = 8;
+constexpr int kTcSub = 4;         // k-blocks per bulk copy (18 KB)
+constexpr int kTcRawStages = 6;   // bulk copies in flight: ~110 KB per SM covers HBM latency at full bandwidth
 constexpr int kTcAStages = 4;
 constexpr int kTcGroups = 2;  // groups of four expanding warps; group g owns the k-blocks it % kTcGroups == g
 constexpr int kTcThreads = (4 + 4 * kTcGroups + 4) * 32;
@@ -78,25 +77,22 @@ __device__ __forceinline__ void expand8(uint32_t w, int shift, __nv_bfloat162 d2
 
 template <int BNB>
 __global__ void __launch_bounds__(kTcThreads, 1)
-q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict__ wt, TcTail tail, int N, int K, int B,
-             int splits, unsigned* err, int dbg) {
-  constexpr int A_BYTES = kTcRows * kTcBK * 2;  // 16 KB
-  constexpr int X_BYTES = BNB * kTcBK * 2;
-  constexpr int XSTAGE = 4096;                  // activation tile slot (1024-byte aligned)
+q4_tc_kernel(const uint8_t* __restrict__ wt, const __nv_bfloat16* __restrict__ x, int ldx, TcTail tail, int N, int K,
+             int B, int splits, unsigned* err) {
+  constexpr int A_BYTES = kTcRows * kTcBK * 2;  // 16 KB expanded weight tile
+  constexpr int ASTAGE = A_BYTES + 4096;        // + activation tile [BNB x 64] bf16 (1024-byte aligned slot)
+  constexpr int BIG = kTcSub * kTcRawBytes;     // one bulk copy: the raw tiles of kTcSub consecutive k-blocks
   constexpr uint32_t TMEM_COLS = 2 * BNB < 32 ? 32 : 2 * BNB;
   constexpr uint32_t IDESC = make_idesc_bf16(kTcRows, BNB, false, false);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* a_ring = smem;                                    // kTcAStages x expanded bf16 weight tile
-  uint8_t* x_ring = smem + kTcAStages * A_BYTES;             // kTcXStages x activation tile
-  uint8_t* raw_ring = x_ring + kTcXStages * XSTAGE;          // kTcRawStages x raw weight tile
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * kTcRawBytes);
+  uint8_t* a_ring = smem;                                    // kTcAStages x (weight tile | activation tile)
+  uint8_t* raw_ring = smem + kTcAStages * ASTAGE;            // kTcRawStages x BIG
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(raw_ring + kTcRawStages * BIG);
   uint64_t* raw_empty = raw_full + kTcRawStages;
-  uint64_t* x_full = raw_empty + kTcRawStages;
-  uint64_t* x_empty = x_full + kTcXStages;
-  uint64_t* a_full = x_empty + kTcXStages;
+  uint64_t* a_full = raw_empty + kTcRawStages;
   uint64_t* a_empty = a_full + kTcAStages;
   uint64_t* tfull = a_empty + kTcAStages;
   uint64_t* tempty = tfull + 2;
@@ -112,14 +108,10 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], 128);
-    }
-    for (int s = 0; s < kTcXStages; ++s) {
-      mbar_init(&x_full[s], 1);
-      mbar_init(&x_empty[s], 1);
+      mbar_init(&raw_empty[s], 4 * kTcGroups);  // every expanding warp arrives once per bulk stage
     }
     for (int s = 0; s < kTcAStages; ++s) {
-      mbar_init(&a_full[s], 128);
+      mbar_init(&a_full[s], 4);                 // the four warps of the group that filled the stage
       mbar_init(&a_empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -139,36 +131,21 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {  // raw weight tiles
-      uint32_t it = 0;
+    if (lane == 0) {  // raw weight tiles: one bulk copy per kTcSub k-blocks (the copy engine takes a fixed
+                      // time per request, so small requests cap the bandwidth of an SM)
+      uint32_t bit = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int split = u % splits, tile = u / splits;
         const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcRawStages;
-          const uint32_t ph = (it / kTcRawStages) & 1;
+        for (int kb = kb0; kb < kb1; kb += kTcSub, ++bit) {
+          const int nsub = min(kTcSub, kb1 - kb);
+          const int s = bit % kTcRawStages;
+          const uint32_t ph = (bit / kTcRawStages) & 1;
           if (!mbar_wait(&raw_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
-          mbar_arrive_expect_tx(&raw_full[s], kTcRawBytes);
-          bulk_load_1d(raw_ring + s * kTcRawBytes,
-                       wt + (static_cast<size_t>(tile) * kb_total + kb) * kTcRawBytes, kTcRawBytes, &raw_full[s]);
-        }
-      }
-    }
-  } else if (warp == 2) {
-    if (lane == 0) {  // activation tiles
-      tma_prefetch_desc(&tmX);
-      uint32_t it = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        const int split = u % splits;
-        const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcXStages;
-          const uint32_t ph = (it / kTcXStages) & 1;
-          if (!mbar_wait(&x_empty[s], ph ^ 1, abort_flag, err)) { ok = false; break; }
-          mbar_arrive_expect_tx(&x_full[s], X_BYTES);
-          tma_load_2d(x_ring + s * XSTAGE, &tmX, &x_full[s], kb * kTcBK, 0);  // rows >= B read zeros
+          mbar_arrive_expect_tx(&raw_full[s], nsub * kTcRawBytes);
+          bulk_load_1d(raw_ring + s * BIG, wt + (static_cast<size_t>(tile) * kb_total + kb) * kTcRawBytes,
+                       nsub * kTcRawBytes, &raw_full[s]);
         }
       }
     }
@@ -184,60 +161,85 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BNB;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % kTcAStages, sx = it % kTcXStages;
-          const uint32_t ph = (it / kTcAStages) & 1, phx = (it / kTcXStages) & 1;
-          if (!mbar_wait(&x_full[sx], phx, abort_flag, err)) { ok = false; break; }
+          const int s = it % kTcAStages;
+          const uint32_t ph = (it / kTcAStages) & 1;
           if (!mbar_wait(&a_full[s], ph, abort_flag, err)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t adesc = make_smem_desc_sw128(smem_u32(a_ring + s * A_BYTES), 16, 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(smem_u32(x_ring + sx * XSTAGE), 16, 1024);
-          if (!(dbg & 4)) {
+          const uint32_t sA = smem_u32(a_ring + s * ASTAGE);
+          const uint64_t adesc = make_smem_desc_sw128(sA, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sA + A_BYTES, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < kTcBK / 16; ++k)
-              umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < kTcBK / 16; ++k)
+            umma_ss(d_tmem, adesc + k * 2, bdesc + k * 2, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
-          umma_commit(&x_empty[sx]);
         }
         if (ok) umma_commit(&tfull[acc]);
       }
     }
   } else if (warp >= 4 && warp < 4 + 4 * kTcGroups) {
-    // expand raw Q4_0 tiles to bf16; thread t of the group owns row t of the tile
+    // expand raw Q4_0 tiles to bf16 and stage the activation tile; thread t of the group owns row t
     const int group = (warp - 4) >> 2;
     const int t = ((warp - 4) & 3) * 32 + lane;
-    uint32_t it = 0;
+    uint32_t it = 0, bit = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int split = u % splits;
       const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        if (static_cast<int>(it % kTcGroups) != group) continue;
-        const int sr = it % kTcRawStages, sa = it % kTcAStages;
-        const uint32_t phr = (it / kTcRawStages) & 1, pha = (it / kTcAStages) & 1;
-        if (!mbar_wait(&raw_full[sr], phr, abort_flag, err)) { ok = false; break; }
-        if (!mbar_wait(&a_empty[sa], pha ^ 1, abort_flag, err)) { ok = false; break; }
-        const uint8_t* raw = raw_ring + sr * kTcRawBytes;
-        uint8_t* arow = a_ring + sa * A_BYTES + t * 128;
+      for (int kbb = kb0; kbb < kb1 && ok; kbb += kTcSub, ++bit) {
+        const int nsub = min(kTcSub, kb1 - kbb);
+        const int sb = bit % kTcRawStages;
+        const uint32_t phb = (bit / kTcRawStages) & 1;
+        bool waited = false;
+        for (int j = 0; j < nsub; ++j) {
+          const uint32_t itc = it + j;
+          if (static_cast<int>(itc % kTcGroups) != group) continue;
+          const int kb = kbb + j;
+          // activation chunks (16 bytes = 8 values) this thread stages: chunk c = row * 8 + column chunk
+          uint4 xv[BNB / 16];
 #pragma unroll
-        for (int blk = 0; blk < 2 && !(dbg & 1); ++blk) {
-          const uint4 q = *reinterpret_cast<const uint4*>(raw + (blk * kTcRows + t) * 16);
-          const __half dh = *reinterpret_cast<const __half*>(raw + 2 * kTcRows * 16 + (blk * kTcRows + t) * 2);
-          const __nv_bfloat162 d2 = __float2bfloat162_rn(__half2float(dh));
-          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-          // values 0..7 | 8..15 from the low nibbles of words 0,1 | 2,3; 16..23 | 24..31 from the high ones
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t lo[2], hi[2];
-            expand8(w[(c & 1) * 2], (c >> 1) * 4, d2, lo);
-            expand8(w[(c & 1) * 2 + 1], (c >> 1) * 4, d2, hi);
-            const int chunk = (blk * 4 + c) ^ (t & 7);  // 128-byte swizzle of the 16-byte chunks
-            *reinterpret_cast<uint4*>(arow + chunk * 16) = make_uint4(lo[0], lo[1], hi[0], hi[1]);
+          for (int c2 = 0; c2 < BNB / 16; ++c2) {
+            const int c = t + c2 * 128, row = c >> 3;
+            xv[c2] = row < B ? *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx + kb * kTcBK + (c & 7) * 8)
+                             : make_uint4(0u, 0u, 0u, 0u);
           }
+          if (!waited) {
+            if (!mbar_wait(&raw_full[sb], phb, abort_flag, err)) { ok = false; break; }
+            waited = true;
+          }
+          const int sa = itc % kTcAStages;
+          const uint32_t pha = (itc / kTcAStages) & 1;
+          if (!mbar_wait(&a_empty[sa], pha ^ 1, abort_flag, err)) { ok = false; break; }
+          const uint8_t* raw = raw_ring + sb * BIG + j * kTcRawBytes;
+          uint8_t* stage = a_ring + sa * ASTAGE;
+          uint8_t* arow = stage + t * 128;
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            const uint4 q = *reinterpret_cast<const uint4*>(raw + (blk * kTcRows + t) * 16);
+            const __half dh = *reinterpret_cast<const __half*>(raw + 2 * kTcRows * 16 + (blk * kTcRows + t) * 2);
+            const __nv_bfloat162 d2 = __float2bfloat162_rn(__half2float(dh));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            // values 0..7 | 8..15 from the low nibbles of words 0,1 | 2,3; 16..23 | 24..31 from the high ones
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t lo[2], hi[2];
+              expand8(w[(c & 1) * 2], (c >> 1) * 4, d2, lo);
+              expand8(w[(c & 1) * 2 + 1], (c >> 1) * 4, d2, hi);
+              const int chunk = (blk * 4 + c) ^ (t & 7);  // 128-byte swizzle of the 16-byte chunks
+              *reinterpret_cast<uint4*>(arow + chunk * 16) = make_uint4(lo[0], lo[1], hi[0], hi[1]);
+            }
+          }
+#pragma unroll
+          for (int c2 = 0; c2 < BNB / 16; ++c2) {
+            const int c = t + c2 * 128, row = c >> 3;
+            *reinterpret_cast<uint4*>(stage + A_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = xv[c2];
+          }
+          fence_proxy_async_smem();  // the tensor core reads both tiles through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[sa]);
         }
-        if (!(dbg & 2)) fence_proxy_async_smem();  // the tensor core reads this tile through the async proxy
-        mbar_arrive(&a_full[sa]);
-        mbar_arrive(&raw_empty[sr]);
+        it += nsub;
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(&raw_empty[sb]);
       }
     }
   } else if (warp >= 4 + 4 * kTcGroups) {
@@ -340,7 +342,8 @@ q4_tc_kernel(const __grid_constant__ CUtensorMap tmX, const uint8_t* __restrict_
 // One block per (row, 2048-column slab); 8 values per thread, a Q8_0 block is 4 lanes.
 __global__ void __launch_bounds__(256)
 round_act_q8_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                    __nv_bfloat16* __restrict__ y, int ldy, int K, int mode, float eps) {
+                    __nv_bfloat16* __restrict__ y, int ldy, int8_t* __restrict__ xq, float* __restrict__ xs, int K,
+                    int mode, float eps) {
   const int row = blockIdx.y;
   const int ld = mode == 2 ? 2 * K : K;
   const __nv_bfloat16* xr = x + static_cast<size_t>(row) * ld;
@@ -391,18 +394,30 @@ round_act_q8_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   const float d = amax / 127.f, inv = d > 0.f ? 1.f / d : 0.f;
-  uint4 o;
-  o.x = pack_bf16x2(rintf(v[0] * inv) * d, rintf(v[1] * inv) * d);
-  o.y = pack_bf16x2(rintf(v[2] * inv) * d, rintf(v[3] * inv) * d);
-  o.z = pack_bf16x2(rintf(v[4] * inv) * d, rintf(v[5] * inv) * d);
-  o.w = pack_bf16x2(rintf(v[6] * inv) * d, rintf(v[7] * inv) * d);
-  *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy + c) = o;
+  if (y) {
+    uint4 o;
+    o.x = pack_bf16x2(rintf(v[0] * inv) * d, rintf(v[1] * inv) * d);
+    o.y = pack_bf16x2(rintf(v[2] * inv) * d, rintf(v[3] * inv) * d);
+    o.z = pack_bf16x2(rintf(v[4] * inv) * d, rintf(v[5] * inv) * d);
+    o.w = pack_bf16x2(rintf(v[6] * inv) * d, rintf(v[7] * inv) * d);
+    *reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy + c) = o;
+  }
+  if (xq) {   // planar Q8_0 for the integer dot-product path: int8 values and one fp32 scale per 32
+    int q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = __float2int_rn(v[j] * inv);
+    uint2 pk;
+    pk.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((q[3] & 0xff) << 24);
+    pk.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2*>(xq + static_cast<size_t>(row) * K + c) = pk;
+    if ((threadIdx.x & 3) == 0) xs[static_cast<size_t>(row) * (K / 32) + c / 32] = d;
+  }
 }
 
 template <int BNB>
-static int launch_q4_tc(const CUtensorMap& tmX, const uint8_t* wt, const TcTail& tail, int N, int K, int B, int splits,
-                        cudaStream_t st) {
-  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2) + kTcXStages * 4096 + kTcRawStages * kTcRawBytes + 1024 + 1024;
+static int launch_q4_tc(const uint8_t* wt, const __nv_bfloat16* x, int ldx, const TcTail& tail, int N, int K, int B,
+                        int splits, cudaStream_t st) {
+  constexpr int SMEM = kTcAStages * (kTcRows * kTcBK * 2 + 4096) + kTcRawStages * kTcSub * kTcRawBytes + 1024 + 1024;
   auto kern = q4_tc_kernel<BNB>;
   static bool configured = false;
   if (!configured) {
@@ -412,8 +427,7 @@ static int launch_q4_tc(const CUtensorMap& tmX, const uint8_t* wt, const TcTail&
   }
   const int units = ceil_div(N, kTcRows) * splits;
   const int grid = units < sm_count() ? units : sm_count();  // one block per SM: all blocks are resident
-  static int dbg = getenv("MIMIR_Q4TC_DEBUG") ? atoi(getenv("MIMIR_Q4TC_DEBUG")) : 0;
-  kern<<<grid, kTcThreads, SMEM, st>>>(tmX, wt, tail, N, K, B, splits, error_word_dev(), dbg);
+  kern<<<grid, kTcThreads, SMEM, st>>>(wt, x, ldx, tail, N, K, B, splits, error_word_dev());
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("q4 tensor-core product: launch failed");
 }
@@ -459,13 +473,15 @@ MIMIR_API int mimir_q4_planar_to_tiled(const void* ws, const void* wq, void* out
 
 // y[rows][K] bf16 (row pitch ldy) = Q8_0-rounded activation (mode 0), of RMSNorm(x) * gamma (mode 1), or of
 // silu(gate) * up for x = [rows][2K] (mode 2).  x rows are contiguous.
-MIMIR_API int mimir_round_act_q8(const void* x, const void* gamma, void* y, int ldy, int rows, int K, int mode, float eps,
-                                 cudaStream_t st) {
+// xq / xs (both or neither): also the planar Q8_0 form, int8 [rows][K] and fp32 scales [rows][K/32]; y may be null then.
+MIMIR_API int mimir_round_act_q8(const void* x, const void* gamma, void* y, int ldy, void* xq, float* xs, int rows, int K,
+                                 int mode, float eps, cudaStream_t st) {
+  if ((xq == nullptr) != (xs == nullptr) || (!y && !xq)) return refuse("activation rounding: no output given");
   if (K % 32 || ldy % 8) return refuse("activation rounding: K %% 32 == 0 and ldy %% 8 == 0 required");
   if (mode == 1 && !gamma) return refuse("activation rounding: RMSNorm needs gamma");
   dim3 grid(ceil_div(K, 2048), rows);
   round_act_q8_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),
-                                            static_cast<__nv_bfloat16*>(y), ldy, K, mode, eps);
+                                            static_cast<__nv_bfloat16*>(y), ldy, static_cast<int8_t*>(xq), xs, K, mode, eps);
   count_launch();
   return 0;
 }
@@ -498,14 +514,7 @@ MIMIR_API int mimir_q4_tc(const void* wt, const void* x, int ldx, void* const* p
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
   while (splits > 1 && ceil_div(kb_total, splits) * (splits - 1) >= kb_total) --splits;
-  CUtensorMap tmX;
   const int bnb = B <= 16 ? 16 : 32;
-  {
-    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(B)};
-    uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
-    uint32_t box[2] = {kTcBK, static_cast<uint32_t>(bnb)};
-    if (encode_tmap(&tmX, x, 2, 2, dims, strides, box, 3)) return -1;
-  }
   TcTail t;
   for (int r = 0; r < kQMaxRanks; ++r) {
     t.partial[r] = r < world ? static_cast<float*>(partial[r]) : nullptr;
@@ -518,6 +527,7 @@ MIMIR_API int mimir_q4_tc(const void* wt, const void* x, int ldx, void* const* p
   t.out_f32 = out_is_f32 ? static_cast<float*>(out) : nullptr;
   t.ldo = ldo;
   t.rank = rank; t.world = world; t.slot = slot; t.wait_ns = q_peer_wait_ns();
-  return bnb == 16 ? launch_q4_tc<16>(tmX, static_cast<const uint8_t*>(wt), t, N, K, B, splits, st)
-                   : launch_q4_tc<32>(tmX, static_cast<const uint8_t*>(wt), t, N, K, B, splits, st);
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  return bnb == 16 ? launch_q4_tc<16>(static_cast<const uint8_t*>(wt), xb, ldx, t, N, K, B, splits, st)
+                   : launch_q4_tc<32>(static_cast<const uint8_t*>(wt), xb, ldx, t, N, K, B, splits, st);
 }

@@ -686,7 +686,11 @@ MIMIR_API int mimir_peer_allgather(const void* src, void* const* dst, void* cons
   a.epoch = static_cast<unsigned*>(epoch);
   a.block_counter = static_cast<unsigned*>(block_counter);
   a.rank = rank; a.world = world; a.slot = slot; a.wait_ns = g_q_wait_ns;
-  peer_allgather_kernel<<<32, 256, 0, st>>>(static_cast<const uint4*>(src), a, static_cast<size_t>(nbytes / 16),
+  // small messages: 32 blocks keep the arrival counter cheap; large ones use every SM for link bandwidth
+  int blocks = static_cast<int>(nbytes / 65536);
+  if (blocks < 32) blocks = 32;
+  if (blocks > sm_count()) blocks = sm_count();
+  peer_allgather_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(src), a, static_cast<size_t>(nbytes / 16),
                                             error_word_dev());
   count_launch();
   return 0;

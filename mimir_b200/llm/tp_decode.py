@@ -54,12 +54,15 @@ class LlamaConfig:
 
 class TPDecoder:
     def __init__(self, cfg: LlamaConfig, rank: int, world: int, batch: int, cap: int, seed: int = 0,
-                 device=None, weights: dict | None = None, engine: str = "tc"):
+                 device=None, weights: dict | None = None, engine: str = "auto"):
         """``engine``: "tc" runs every projection on the tensor cores (Q4_0 tiles expanded to bf16 in
         shared memory, activations rounded to Q8_0 and kept as bf16); "dp4a" is the integer
-        dot-product path (one warp per weight row)."""
-        if engine not in ("tc", "dp4a"):
+        dot-product path (one warp per weight row), whose time grows with the batch; "auto" takes
+        dp4a up to 4 rows and the tensor cores above (the measured crossover)."""
+        if engine not in ("auto", "tc", "dp4a"):
             raise ValueError(f"unknown decode engine {engine!r}")
+        if engine == "auto":
+            engine = "tc" if batch > 4 else "dp4a"
         if engine == "tc" and (batch > 32 or cfg.d_model % 64 or (cfg.ffn // world) % 64 or (cfg.n_head // world * cfg.head_dim) % 64):
             engine = "dp4a"
         self.engine = engine

@@ -16,6 +16,15 @@ captures into one CUDA graph).  Two placements of the parameters:
     from the GEMM epilogue (GEMM -> reduce-scatter), so each rank ends up with the summed
     gradient of its rows.  Norm gains are replicated and their gradients all-reduced once per
     step.  Every rank works on its own micro-batch (data parallel).
+
+``mode="tp"``       Megatron tensor parallelism over the ranks of ``group`` (reference:
+    nn.TensorParallel, nn/shard.go:102-158): QKV and gate|up are split by output rows (heads and
+    hidden features), the attention output and down projections by input columns; attention runs
+    on the local heads.  A row-parallel product is the fused GEMM -> reduce-scatter kernel (each
+    rank receives its rows of the sum while the rest is still being computed), the residual is
+    added on those rows, and a peer all-gather rebuilds the full activation: together one
+    all-reduce per row-parallel layer, forward and backward.  ``dp_group`` adds data parallelism
+    across tensor-parallel groups (gradients all-reduced once per step).
 """
 from __future__ import annotations
 
@@ -69,26 +78,33 @@ class LlamaTrainConfig:
 
 class LlamaEngine:
     def __init__(self, cfg: LlamaTrainConfig, batch: int, seq: int, device="cuda", seed: int = 0, mode: str = "single",
-                 rank: int = 0, world: int = 1, group=None):
-        if mode not in ("single", "fsdp"):
+                 rank: int = 0, world: int = 1, group=None, dp_group=None, dp_world: int = 1):
+        if mode not in ("single", "fsdp", "tp"):
             raise ValueError(f"unknown mode {mode!r}")
         if mode == "single":
             rank, world = 0, 1
         self.cfg, self.B, self.T, self.M = cfg, batch, seq, batch * seq
         self.mode, self.rank, self.world, self.group = mode, rank, world, group
+        self.dp_group, self.dp_world = dp_group, dp_world
         self.device = torch.device(device)
         C, D = cfg.d_model, cfg.head_dim
-        self.qkv_n = (cfg.n_head + 2 * cfg.n_kv_head) * D
-        # 2-D weights [rows, cols] in the order backward finishes their gradients
+        tp = world if mode == "tp" else 1
+        if cfg.n_head % tp or cfg.n_kv_head % tp or cfg.ffn % (tp * 8):
+            raise ValueError("heads, KV heads and ffn / 8 must divide by the tensor-parallel size")
+        # local (per tensor-parallel rank) head and feature counts
+        self.Hq, self.Hk, self.F = cfg.n_head // tp, cfg.n_kv_head // tp, cfg.ffn // tp
+        self.qkv_n = (self.Hq + 2 * self.Hk) * D
+        # 2-D weights [rows, cols] as this rank multiplies with them, in the order backward finishes their gradients
         self.shapes = {"lm_head": (cfg.padded_vocab, C)}
         for l in reversed(range(cfg.n_layer)):
-            self.shapes[f"h.{l}.wd"] = (C, cfg.ffn)
-            self.shapes[f"h.{l}.wgu"] = (2 * cfg.ffn, C)
-            self.shapes[f"h.{l}.wo"] = (C, cfg.n_head * D)
+            self.shapes[f"h.{l}.wd"] = (C, self.F)
+            self.shapes[f"h.{l}.wgu"] = (2 * self.F, C)
+            self.shapes[f"h.{l}.wo"] = (C, self.Hq * D)
             self.shapes[f"h.{l}.wqkv"] = (self.qkv_n, C)
         self.shapes["wte"] = (cfg.padded_vocab, C)
+        self.shard_rows = world if mode == "fsdp" else 1     # fsdp keeps 1 / world of the rows of every matrix
         for name, (r, _) in self.shapes.items():
-            if r % world:
+            if r % self.shard_rows:
                 raise ValueError(f"{name}: {r} rows do not divide over {world} ranks")
         self.gain_names = [f"h.{l}.{n}" for l in range(cfg.n_layer) for n in ("attn_norm", "ffn_norm")] + ["out_norm"]
         self._alloc_params(seed)
@@ -99,7 +115,7 @@ class LlamaEngine:
 
     # ------------------------------------------------------------------ parameters
     def _alloc_params(self, seed: int) -> None:
-        cfg, dev, W = self.cfg, self.device, self.world
+        cfg, dev, W = self.cfg, self.device, self.shard_rows
         bf, f32 = dict(dtype=torch.bfloat16, device=dev), dict(dtype=torch.float32, device=dev)
         align = 1024
         # local (owned) elements: this rank's rows of every matrix, then the gains (replicated)
@@ -152,15 +168,37 @@ class LlamaEngine:
         for name, (r, c) in self.shapes.items():
             leaf = name.split(".")[-1]
             std = 0.02 / math.sqrt(2 * cfg.n_layer) if leaf in ("wo", "wd") else 0.02
-            full = torch.randn(r, c, generator=gen, device=dev) * std
+            if self.mode == "tp":
+                full = self._tp_slice(leaf, gen, std)
+            else:
+                full = torch.randn(r, c, generator=gen, device=dev) * std
             if leaf in ("wte", "lm_head"):
                 full[cfg.vocab:] = 0
             rows = r // W
-            self.mv[name].copy_(full[self.rank * rows: (self.rank + 1) * rows])
+            own_rank = self.rank if self.mode == "fsdp" else 0
+            self.mv[name].copy_(full[own_rank * rows: (own_rank + 1) * rows])
             del full
         for n in self.gain_names:
             self.mv[n].fill_(1.0)
         self._publish_params()
+
+    def _tp_slice(self, leaf: str, gen, std: float) -> torch.Tensor:
+        """Draws the full matrix (so that every tensor-parallel size sees the same model) and cuts this rank's part."""
+        cfg, dev, r, tp = self.cfg, self.device, self.rank, self.world
+        C, D = cfg.d_model, cfg.head_dim
+        if leaf == "wqkv":
+            full = torch.randn((cfg.n_head + 2 * cfg.n_kv_head) * D, C, generator=gen, device=dev) * std
+            q, k, v = full.split([cfg.n_head * D, cfg.n_kv_head * D, cfg.n_kv_head * D], 0)
+            cut = lambda t, n: t[r * n * D: (r + 1) * n * D]  # noqa: E731
+            return torch.cat([cut(q, self.Hq), cut(k, self.Hk), cut(v, self.Hk)], 0)
+        if leaf == "wo":
+            return (torch.randn(C, cfg.n_head * D, generator=gen, device=dev) * std)[:, r * self.Hq * D: (r + 1) * self.Hq * D].contiguous()
+        if leaf == "wgu":
+            full = torch.randn(2 * cfg.ffn, C, generator=gen, device=dev) * std
+            return torch.cat([full[r * self.F: (r + 1) * self.F], full[cfg.ffn + r * self.F: cfg.ffn + (r + 1) * self.F]], 0)
+        if leaf == "wd":
+            return (torch.randn(C, cfg.ffn, generator=gen, device=dev) * std)[:, r * self.F: (r + 1) * self.F].contiguous()
+        return torch.randn(cfg.padded_vocab, C, generator=gen, device=dev) * std
 
     def _publish_params(self) -> None:
         """bf16 working copies from the fp32 masters (the optimizer kernel keeps them in step afterwards)."""
@@ -169,19 +207,35 @@ class LlamaEngine:
 
     def _alloc_activations(self) -> None:
         cfg, M, dev, L = self.cfg, self.M, self.device, self.cfg.n_layer
-        C, F, D = cfg.d_model, cfg.ffn, cfg.head_dim
+        C, F, D = cfg.d_model, self.F, cfg.head_dim
         bf, f32 = dict(dtype=torch.bfloat16, device=dev), dict(dtype=torch.float32, device=dev)
         self.tokens = torch.zeros(M, dtype=torch.int64, device=dev)
         self.targets = torch.zeros(M, dtype=torch.int64, device=dev)
         self.pos = torch.arange(self.T, dtype=torch.int32, device=dev).repeat(self.B)
         inv = 1.0 / (cfg.rope_base ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
         self.freqs = inv.float().to(dev)
-        self.x = torch.empty(L + 1, M, C, **bf)
+        if self.mode == "tp":
+            # activations that an all-gather writes into on every rank live in symmetric memory
+            from ..parallel.fused_gemm import ReduceScatterGemm
+            from ..parallel.peer import SymmetricBuffer
+            n = M * C
+            self.act_arena = SymmetricBuffer((2 * L + 2) * n * 2, self.rank, self.world, self.group)
+            flat = self.act_arena.view(torch.bfloat16, 0, (2 * L + 2) * n)
+            self.x = flat[: (L + 1) * n].view(L + 1, M, C)
+            self.xmid = flat[(L + 1) * n: (2 * L + 1) * n].view(L, M, C)
+            self.dtmp = flat[(2 * L + 1) * n:].view(M, C)
+            self.rs_act = ReduceScatterGemm(M, C, self.rank, self.world, self.group)
+            self.shard = torch.empty(M // self.world, C, **bf)
+            self.ag_sig = SymmetricBuffer(1024 * 4, self.rank, self.world, self.group)
+            self.ag_state = torch.zeros(4, dtype=torch.int32, device=dev)
+        else:
+            self.x = torch.empty(L + 1, M, C, **bf)
+            self.xmid = torch.empty(L, M, C, **bf)
+            self.dtmp = torch.empty(M, C, **bf)
         self.h1 = torch.empty(L, M, C, **bf)
         self.qkv = torch.empty(L, M, self.qkv_n, **bf)
-        self.att = torch.empty(L, M, cfg.n_head * D, **bf)
-        self.lse = torch.empty(L, self.B * cfg.n_head * self.T, **f32)
-        self.xmid = torch.empty(L, M, C, **bf)
+        self.att = torch.empty(L, M, self.Hq * D, **bf)
+        self.lse = torch.empty(L, self.B * self.Hq * self.T, **f32)
         self.h2 = torch.empty(L, M, C, **bf)
         self.gu = torch.empty(L, M, 2 * F, **bf)
         self.act = torch.empty(L, M, F, **bf)
@@ -192,12 +246,11 @@ class LlamaEngine:
         self.loss = torch.zeros(1, **f32)
         self.dx = torch.empty(M, C, **bf)
         self.dx2 = torch.empty(M, C, **bf)
-        self.dtmp = torch.empty(M, C, **bf)
-        self.datt = torch.empty(M, cfg.n_head * D, **bf)
+        self.datt = torch.empty(M, self.Hq * D, **bf)
         self.dqkv = torch.empty(M, self.qkv_n, **bf)
         self.dgu = torch.empty(M, 2 * F, **bf)
         self.dact = torch.empty(M, F, **bf)
-        self.dsum = torch.empty(self.B * cfg.n_head * self.T, **f32)
+        self.dsum = torch.empty(self.B * self.Hq * self.T, **f32)
         self.norm_scratch = K.norm_bwd_scratch(C, dev)
         if self.mode == "fsdp":
             self.dwte_full = torch.zeros(cfg.padded_vocab, C, **bf)
@@ -213,6 +266,37 @@ class LlamaEngine:
         # fsdp: the forward pass of this step left every rank's rows in the local full-size copy
         return gemm(dy, self.full[name], b_mn=True, out=out)
 
+    # tensor parallel: products whose contraction is split over the ranks
+    def _allgather_rows(self, shard, out) -> None:
+        """Pushes ``shard`` [M / tp, C] into rows ``rank * M / tp`` of ``out`` on every rank (``out`` lives in
+        the symmetric activation arena) and waits, bounded, until every rank's rows have arrived."""
+        from .. import _native
+        from ..ops._util import ptr, stream_ptr
+        from ..ops.quant_cuda import _L
+        off = out.data_ptr() - self.act_arena.local_ptr
+        rc = _L().mimir_peer_allgather(ptr(shard), self.act_arena.ptr_array(off), self.ag_sig.ptr_array(),
+                                       self.ag_state.data_ptr(), self.ag_state[1:].data_ptr(), shard.numel() * 2,
+                                       self.rank, self.world, 0, stream_ptr())
+        _native.check(rc, "allgather_rows")
+
+    def _row_parallel_fwd(self, a, name, resid, out) -> None:
+        """out = resid + sum over ranks of a_local @ w_local^T."""
+        if self.mode != "tp":
+            self._fwd(a, name, out, residual=True, aux=resid)
+            return
+        rows = self.M // self.world
+        self.rs_act(a, self.p[name], out=self.shard)
+        K.axpby(self.shard, resid[self.rank * rows: (self.rank + 1) * rows], self.shard)
+        self._allgather_rows(self.shard, out)
+
+    def _col_parallel_dgrad(self, dy, name, out) -> None:
+        """out = sum over ranks of dy_local @ w_local (input gradient of a column-parallel layer)."""
+        if self.mode != "tp":
+            self._dgrad(dy, name, out)
+            return
+        self.rs_act(dy, self.p[name], b_mn=True, out=self.shard)
+        self._allgather_rows(self.shard, out)
+
     def _wgrad(self, dy, x, name):
         if self.mode == "fsdp":
             self.rs[self.shapes[name]](dy, x, transposed=True, out=self.g[name])
@@ -222,7 +306,7 @@ class LlamaEngine:
     # --------------------------------------------------------------------- forward
     def forward(self) -> None:
         cfg, p, L = self.cfg, self.p, self.cfg.n_layer
-        Hq, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        Hq, Hk, D = self.Hq, self.Hk, cfg.head_dim
         if self.mode == "fsdp":
             self._gather_rows("wte")     # also the step's barrier: every rank's optimizer has finished
         K.embedding_fwd(self.tokens, self.full["wte"], None, self.x[0], self.T)
@@ -232,11 +316,11 @@ class LlamaEngine:
             self._fwd(self.h1[l], n + "wqkv", self.qkv[l])
             K.rope_(self.qkv[l], self.pos, self.freqs, 0, Hq + Hk, D, interleaved=True)
             attention_fwd_packed(self.qkv[l], self.att[l], self.lse[l], self.B, self.T, Hq, Hk, D, causal=True)
-            self._fwd(self.att[l], n + "wo", self.xmid[l], residual=True, aux=self.x[l])
+            self._row_parallel_fwd(self.att[l], n + "wo", self.x[l], self.xmid[l])
             K.rmsnorm_fwd(self.xmid[l], p[n + "ffn_norm"], self.h2[l], self.rstd[2 * l + 1], cfg.eps)
             self._fwd(self.h2[l], n + "wgu", self.gu[l])
             K.swiglu_fwd(self.gu[l], self.act[l])
-            self._fwd(self.act[l], n + "wd", self.x[l + 1], residual=True, aux=self.xmid[l])
+            self._row_parallel_fwd(self.act[l], n + "wd", self.xmid[l], self.x[l + 1])
         K.rmsnorm_fwd(self.x[L], p["out_norm"], self.hf, self.rstd[2 * L], cfg.eps)
         self._fwd(self.hf, "lm_head", self.logits)
 
@@ -244,12 +328,12 @@ class LlamaEngine:
         """Mean cross-entropy of this rank's tokens into ``self.loss``; logits become the gradient in
         place, scaled by 1 / (tokens on all ranks) so that the summed gradients are the global mean's."""
         K.cross_entropy(self.logits, self.targets, self.loss_rows, self.logits, self.loss, self.cfg.vocab,
-                        grad_scale / (self.M * self.world), 1.0 / self.M)
+                        grad_scale / (self.M * (self.world if self.mode == "fsdp" else 1) * self.dp_world), 1.0 / self.M)
 
     # -------------------------------------------------------------------- backward
     def backward(self, on_bucket_ready=None) -> None:
         cfg, p, g, L = self.cfg, self.p, self.g, self.cfg.n_layer
-        Hq, Hk, D = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+        Hq, Hk, D = self.Hq, self.Hk, cfg.head_dim
         dlogits = self.logits
         self._wgrad(dlogits, self.hf, "lm_head")
         self._dgrad(dlogits, "lm_head", self.dtmp)
@@ -260,7 +344,7 @@ class LlamaEngine:
             self._dgrad(dx, n + "wd", self.dact)
             self._wgrad(dx, self.act[l], n + "wd")
             K.swiglu_bwd(self.gu[l], self.dact, self.dgu)
-            self._dgrad(self.dgu, n + "wgu", self.dtmp)
+            self._col_parallel_dgrad(self.dgu, n + "wgu", self.dtmp)
             self._wgrad(self.dgu, self.h2[l], n + "wgu")
             K.rmsnorm_bwd(self.dtmp, self.xmid[l], p[n + "ffn_norm"], self.rstd[2 * l + 1], dx, dx2, g[n + "ffn_norm"],
                           self.norm_scratch)
@@ -270,7 +354,7 @@ class LlamaEngine:
             attention_bwd_packed(self.qkv[l], self.att[l], self.datt, self.lse[l], self.dsum, self.dqkv, self.B, self.T,
                                  Hq, Hk, D, causal=True)
             K.rope_(self.dqkv, self.pos, self.freqs, 0, Hq + Hk, D, interleaved=True, inverse=True)
-            self._dgrad(self.dqkv, n + "wqkv", self.dtmp)
+            self._col_parallel_dgrad(self.dqkv, n + "wqkv", self.dtmp)
             self._wgrad(self.dqkv, self.h1[l], n + "wqkv")
             K.rmsnorm_bwd(self.dtmp, self.x[l], p[n + "attn_norm"], self.rstd[2 * l], dx, dx2, g[n + "attn_norm"],
                           self.norm_scratch)
@@ -284,6 +368,8 @@ class LlamaEngine:
         else:
             g["wte"].zero_()
             K.embedding_bwd(self.tokens, dx, g["wte"], None, self.B, self.T)
+        if self.dp_group is not None and self.dp_world > 1:
+            torch.distributed.all_reduce(self.grads, group=self.dp_group)     # replicas of this shard see other data
 
     def _gather_rows(self, name: str) -> None:
         """Pushes this rank's rows of a sharded matrix into every rank's full-size copy and waits
@@ -322,6 +408,11 @@ class LlamaEngine:
                          step=1, hyper=self.hyper)
 
     def close(self) -> None:
+        if self.mode == "tp":
+            torch.cuda.synchronize()
+            self.rs_act.close()
+            self.ag_sig.close()
+            self.act_arena.close()
         if self.mode == "fsdp":
             torch.cuda.synchronize()
             for r in self.rs.values():

@@ -30,7 +30,7 @@ def _L():
             "mimir_q4_planar_to_bf16": [P, P, P, L, P],
             "mimir_peer_allgather": [P, PP, PP, P, P, L, I, I, I, P],
             "mimir_q4_planar_to_tiled": [P, P, P, I, I, P],
-            "mimir_round_act_q8": [P, P, P, I, I, I, I, F, P],
+            "mimir_round_act_q8": [P, P, P, I, P, P, I, I, I, F, P],
             "mimir_q4_tc": [P, P, I, PP, PP, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
         }.items():
             fn = getattr(lib, name)
@@ -80,6 +80,11 @@ class PlanarQ4:
 
 
 def quantize_act(x, xq, xs, K, mode=0, gamma=None, y=None, eps=1e-5):
+    """Planar Q8_0 of the activation rows (int8 ``xq`` with row pitch K, scales ``xs``); bf16 inputs take
+    the kernel that spreads a row over many blocks, fp32 inputs the warp-per-row one."""
+    if x.dtype == torch.bfloat16 and y is None:
+        round_act_q8(x, None, K, mode, gamma, eps, xq, xs)
+        return
     rows = xq.shape[0]
     _native.check(_L().mimir_quantize_act(ptr(x), int(x.dtype == torch.float32), ptr(gamma), ptr(y), ptr(xq), ptr(xs),
                                           rows, K, mode, eps, stream_ptr()), "quantize_act")
@@ -134,11 +139,12 @@ class TiledQ4:
         return self.blob.numel()
 
 
-def round_act_q8(x, y, K, mode=0, gamma=None, eps=1e-5):
+def round_act_q8(x, y, K, mode=0, gamma=None, eps=1e-5, xq=None, xs=None):
     """y [rows, K] bf16 = the Q8_0 rounding (32-value blocks) of x (mode 0), of RMSNorm(x) * gamma
-    (mode 1) or of silu(gate) * up for x = [rows, 2K] (mode 2)."""
-    _native.check(_L().mimir_round_act_q8(ptr(x), ptr(gamma), ptr(y), y.stride(0), x.shape[0], K, mode, eps, stream_ptr()),
-                  "round_act_q8")
+    (mode 1) or of silu(gate) * up for x = [rows, 2K] (mode 2).  With ``xq`` / ``xs`` the planar
+    Q8_0 form (int8 values, fp32 scale per 32) is written too; ``y`` may then be None."""
+    _native.check(_L().mimir_round_act_q8(ptr(x), ptr(gamma), ptr(y), y.stride(0) if y is not None else 0, ptr(xq),
+                                          ptr(xs), x.shape[0], K, mode, eps, stream_ptr()), "round_act_q8")
     return y
 
 

@@ -102,17 +102,19 @@ class ReduceScatterGemm:
         self.state = torch.zeros(2, dtype=torch.int32, device=dev)
         self._stage_arr, self._sig_arr = self.stage.ptr_array(), self.sig.ptr_array()
 
-    def __call__(self, a: torch.Tensor, b: torch.Tensor, transposed: bool = False, out=None):
-        """``a [M,K] @ b[N,K]^T`` (or, ``transposed``, a stored [K,M] and b stored [K,N]):
-        returns this rank's rows ``[M/world, N]`` of the sum over ranks."""
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, transposed: bool = False, out=None, b_mn: bool | None = None):
+        """``a [M,K] @ b[N,K]^T`` (or, ``transposed``, a stored [K,M] and b stored [K,N]; or, with
+        ``b_mn`` alone, a [M,K] and b stored [K,N]): returns this rank's rows ``[M/world, N]`` of the
+        sum over ranks."""
         if transposed:
             K, M = a.shape
         else:
             M, K = a.shape
+        b_mn = transposed if b_mn is None else b_mn
         if out is None:
             out = torch.empty(M // self.world, self.N, dtype=torch.bfloat16, device=a.device)
         rc = _L().mimir_gemm_reduce_scatter(ptr(a), ptr(b), M, self.N, K, a.stride(0), b.stride(0), int(transposed),
-                                            int(transposed), self._stage_arr, self._sig_arr, ptr(out),
+                                            int(b_mn), self._stage_arr, self._sig_arr, ptr(out),
                                             self.state.data_ptr(), self.state[1:].data_ptr(), self.rank, self.world,
                                             self.slot, stream_ptr())
         _native.check(rc, "gemm_reduce_scatter")

@@ -24,7 +24,7 @@ def main():
     ap.add_argument("--gen", type=int, default=256)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the model's)")
-    ap.add_argument("--engine", default="tc", choices=["tc", "dp4a"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "tc", "dp4a"])
     ap.add_argument("--sequential-prefill", action="store_true", help="feed the prompt token by token")
     ap.add_argument("--primitives", action="store_true",
                     help="also time each kernel of the step on its own (at the final cache length)")

@@ -51,10 +51,11 @@ def test_llama_engine_trains_with_fused_trainer():
     assert tr.graph is not None
 
 
-def test_llama_fsdp_two_ranks_match_single_device():
+@pytest.mark.parametrize("mode", ["fsdp", "tp"])
+def test_llama_sharded_two_ranks_match_single_device(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", LLAMA_MODE=mode)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29547", os.path.join(HERE, "_llama_fsdp_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
