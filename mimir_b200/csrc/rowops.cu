@@ -351,22 +351,108 @@ static int norm_fwd_dispatch(const void* x, const void* g, const void* b, void* 
   return 0;
 }
 
+// LayerNorm / RMSNorm backward, second form: a block spans the row (one thread per 8 columns),
+// so every thread owns the same columns for all rows and keeps their dgamma / dbeta sums in 16
+// registers whatever C is; the two row sums (sum d*g, sum d*g*xhat) go through one shared-memory
+// exchange per kRowsPerIter rows.  Register use does not grow with C (the warp-per-row form
+// above spills beyond C = 1024).  partial: [gridDim.x][2][C].
+constexpr int kRowsPerIter = 4;
+template <bool RMS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C) {
+  __shared__ float red[2][32][2 * kRowsPerIter];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int c = threadIdx.x * 8;
+  const bool active = c < C;
+  float g[8], dg[8], db[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { g[j] = 0.f; dg[j] = 0.f; db[j] = 0.f; }
+  if (active) load8(gamma + c, g);
+  const float invC = 1.f / C;
+  int parity = 0;
+  for (int row0 = blockIdx.x * kRowsPerIter; row0 < rows; row0 += gridDim.x * kRowsPerIter, parity ^= 1) {
+    float xh[kRowsPerIter][8], d[kRowsPerIter][8], sums[2 * kRowsPerIter], rs[kRowsPerIter];
+#pragma unroll
+    for (int r = 0; r < kRowsPerIter; ++r) {
+      const int row = row0 + r;
+      sums[2 * r] = 0.f; sums[2 * r + 1] = 0.f; rs[r] = 0.f;
+      if (row < rows && active) {
+        const size_t off = static_cast<size_t>(row) * C + c;
+        const float mean = RMS ? 0.f : mean_in[row];
+        rs[r] = rstd_in[row];
+        load8(x + off, xh[r]);
+        load8(dy + off, d[r]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[r][j] = (xh[r][j] - mean) * rs[r];
+          dg[j] += d[r][j] * xh[r][j];
+          db[j] += d[r][j];
+          d[r][j] *= g[j];
+          sums[2 * r] += d[r][j];
+          sums[2 * r + 1] += d[r][j] * xh[r][j];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2 * kRowsPerIter; ++k) sums[k] = warp_sum(sums[k]);
+    if (lane == 0) {
+#pragma unroll
+      for (int k = 0; k < 2 * kRowsPerIter; ++k) red[parity][warp][k] = sums[k];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2 * kRowsPerIter; ++k) {
+      float t = 0.f;
+      for (int w = 0; w < nwarp; ++w) t += red[parity][w][k];
+      sums[k] = t * invC;
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerIter; ++r) {
+      const int row = row0 + r;
+      if (row < rows && active) {
+        const size_t off = static_cast<size_t>(row) * C + c;
+        const float s1 = RMS ? 0.f : sums[2 * r], s2 = sums[2 * r + 1];
+        float o[8];
+        if (dres) load8(dres + off, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float t = rs[r] * (d[r][j] - s1 - xh[r][j] * s2);
+          o[j] = dres ? o[j] + t : t;
+        }
+        store8(dx + off, o);
+      }
+    }
+  }
+  if (active) {
+    float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * C + c;
+#pragma unroll
+    for (int j = 0; j < 8; j += 4) {
+      *reinterpret_cast<float4*>(out + j) = make_float4(dg[j], dg[j + 1], dg[j + 2], dg[j + 3]);
+      *reinterpret_cast<float4*>(out + C + j) = make_float4(db[j], db[j + 1], db[j + 2], db[j + 3]);
+    }
+  }
+}
+
+// Returns the number of partial rows written (blocks launched) in *used.
 template <bool RMS>
 static int norm_bwd_dispatch(const void* dy, const void* x, const void* g, const float* mean,
                              const float* rstd, const void* dres, void* dx, float* partial,
-                             int nblocks, int rows, int C, cudaStream_t st) {
-  const int wpb = 8;
-  const size_t smem = static_cast<size_t>(wpb) * 2 * 256 * sizeof(float);
-  auto DY = static_cast<const __nv_bfloat16*>(dy);
-  auto X = static_cast<const __nv_bfloat16*>(x);
-  auto G = static_cast<const __nv_bfloat16*>(g);
-  auto DR = static_cast<const __nv_bfloat16*>(dres);
-  auto DX = static_cast<__nv_bfloat16*>(dx);
-#define CASE(NC) norm_bwd_kernel<NC, RMS><<<nblocks, wpb * 32, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partial, rows, C)
-  if (C <= 256) CASE(1); else if (C <= 512) CASE(2); else if (C <= 768) CASE(3);
-  else if (C <= 1024) CASE(4); else if (C <= 2048) CASE(8); else if (C <= 4096) CASE(16);
-  else return refuse("norm backward: C=%d exceeds 4096", C);
-#undef CASE
+                             int nblocks, int rows, int C, int* used, cudaStream_t st) {
+  if (C > 8192) return refuse("norm backward: C=%d exceeds 8192", C);
+  int threads = (C / 8 + 31) / 32 * 32;
+  int blocks = ceil_div(rows, kRowsPerIter);
+  if (blocks > nblocks) blocks = nblocks;
+  *used = blocks;
+#define NB_CASE(MAXT)                                                                                                   \
+  norm_bwd_rows_kernel<RMS, MAXT><<<blocks, threads, 0, st>>>(                                                           \
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(g), \
+      mean, rstd, static_cast<const __nv_bfloat16*>(dres), static_cast<__nv_bfloat16*>(dx), partial, rows, C)
+  if (threads <= 128) NB_CASE(128); else if (threads <= 256) NB_CASE(256); else if (threads <= 512) NB_CASE(512);
+  else NB_CASE(1024);
+#undef NB_CASE
   count_launch();
   return 0;
 }
@@ -389,7 +475,7 @@ MIMIR_API int mimir_rmsnorm_fwd(const void* x, const void* gamma, void* y, float
 }
 
 // Number of blocks (and rows of `partial`) the backward kernels use.
-MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 4; }
+MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 8; }
 
 // dx = dres + LN'(dy); dgamma/dbeta (bf16) written, or accumulated when accumulate != 0.
 // partial: fp32 scratch of mimir_norm_bwd_blocks() * 2 * C floats.
@@ -398,8 +484,8 @@ MIMIR_API int mimir_layernorm_bwd(const void* dy, const void* x, const void* gam
                                   void* dgamma, void* dbeta, float* partial, int rows, int C,
                                   int accumulate, cudaStream_t st) {
   if (C % 8) return refuse("layernorm: C must be a multiple of 8");
-  const int nb = mimir_norm_bwd_blocks();
-  if (norm_bwd_dispatch<false>(dy, x, gamma, mean, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
+  int nb = mimir_norm_bwd_blocks();
+  if (norm_bwd_dispatch<false>(dy, x, gamma, mean, rstd, dres, dx, partial, nb, rows, C, &nb, st)) return -1;
   // partial rows are [dgamma (C) | dbeta (C)]
   reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
                                                                static_cast<__nv_bfloat16*>(dgamma),
@@ -411,8 +497,8 @@ MIMIR_API int mimir_rmsnorm_bwd(const void* dy, const void* x, const void* gamma
                                 const void* dres, void* dx, void* dgamma, float* partial, int rows,
                                 int C, int accumulate, cudaStream_t st) {
   if (C % 8) return refuse("rmsnorm: C must be a multiple of 8");
-  const int nb = mimir_norm_bwd_blocks();
-  if (norm_bwd_dispatch<true>(dy, x, gamma, nullptr, rstd, dres, dx, partial, nb, rows, C, st)) return -1;
+  int nb = mimir_norm_bwd_blocks();
+  if (norm_bwd_dispatch<true>(dy, x, gamma, nullptr, rstd, dres, dx, partial, nb, rows, C, &nb, st)) return -1;
   reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
                                                                static_cast<__nv_bfloat16*>(dgamma), nullptr,
                                                                accumulate);

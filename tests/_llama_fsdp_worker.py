@@ -42,6 +42,7 @@ def main():
     loss = fs.loss.clone()
     dist.all_reduce(loss)
     loss_fsdp = loss.item() / world
+    loss_single = single.loss.item()      # before the optimizer steps below move it
     rows = single.g["h.0.wgu"].shape[0] // world
     a, b = fs.g["h.0.wgu"].float().flatten(), single.g["h.0.wgu"][rank * rows:(rank + 1) * rows].float().flatten()
     grad_cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
@@ -61,7 +62,7 @@ def main():
     dist.barrier()
     fs.close()
     dist.destroy_process_group()
-    os.write(1, ("RESULT " + json.dumps({"rank": rank, "loss_fsdp": loss_fsdp, "loss_single": single.loss.item(),
+    os.write(1, ("RESULT " + json.dumps({"rank": rank, "loss_fsdp": loss_fsdp, "loss_single": loss_single,
                                          "grad_cos": grad_cos, "param_cos": param_cos, "losses": losses, "err": err}) + "\n").encode())
 
 
