@@ -250,18 +250,47 @@ cross_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const int64_t* __
   if (tgt >= V) { if (tid == 0) raise_error(err, kErrIndex); }
   // read before anyone may overwrite the row in place
   const float tgt_logit = (tid == 0 && tgt >= 0 && tgt < V) ? __bfloat162float(lr[tgt]) : 0.f;
-  float m = -INFINITY, s = 0.f;
-  for (int c = tid * 8; c < V; c += 512 * 8) {
-    float v[8];
+  // two independent online-softmax chains over alternate chunks: two row loads in flight per
+  // thread and half the dependent rescale chain
+  float m = -INFINITY, s = 0.f, m2 = -INFINITY, s2 = 0.f;
+  const int vfull = V & ~7;   // chunks below this bound lie entirely inside the row
+  for (int c = tid * 8; c < V; c += 2 * 512 * 8) {
+    const int c2 = c + 512 * 8;
+    float v[8], w[8];
     load8(lr + c, v);
+    const bool have2 = c2 < V;
+    if (have2) load8(lr + c2, w);
+    if (c + 8 > vfull) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (c + j >= V) v[j] = -INFINITY;
+    }
     float cm = m;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) if (c + j < V) cm = fmaxf(cm, v[j]);
+    for (int j = 0; j < 8; ++j) cm = fmaxf(cm, v[j]);
     float add = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) if (c + j < V) add += __expf(v[j] - cm);
+    for (int j = 0; j < 8; ++j) add += __expf(v[j] - cm);
     s = s * __expf(m - cm) + add;
     m = cm;
+    if (have2) {
+      if (c2 + 8 > vfull) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (c2 + j >= V) w[j] = -INFINITY;
+      }
+      float dm = m2;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dm = fmaxf(dm, w[j]);
+      float add2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) add2 += __expf(w[j] - dm);
+      s2 = s2 * __expf(m2 - dm) + add2;
+      m2 = dm;
+    }
+  }
+  {
+    const float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+    m = mm;
   }
   // combine (m, s) pairs across the block
   // a thread or warp that saw no column has m = -inf: its weight is zero

@@ -103,3 +103,78 @@ def linear_svm(X, y, c: float = 1.0, iters: int = 100) -> SVMModel:
         return loss
     opt.step(closure)
     return SVMModel(w.detach(), b.detach())
+
+
+def fista_lasso(X, y, l1: float, iters: int = 500, tol: float = 1e-8) -> LinearModel:
+    """Lasso by the accelerated proximal gradient method (FISTA) on centred data."""
+    X, y = torch.as_tensor(X).double(), torch.as_tensor(y).double()
+    n = X.shape[0]
+    mu, ym = X.mean(0), y.mean()
+    Xc, yc = X - mu, y - ym
+    L = float(torch.linalg.matrix_norm(Xc, 2) ** 2 / n)          # Lipschitz constant of the smooth part
+    w = torch.zeros(X.shape[1], dtype=X.dtype)
+    z, t = w.clone(), 1.0
+    for _ in range(iters):
+        grad = Xc.t() @ (Xc @ z - yc) / n
+        u = z - grad / L
+        new = torch.sign(u) * torch.clamp(u.abs() - l1 / L, min=0)
+        t_new = (1 + (1 + 4 * t * t) ** 0.5) / 2
+        z = new + (t - 1) / t_new * (new - w)
+        done = float((new - w).abs().max()) < tol
+        w, t = new, t_new
+        if done:
+            break
+    return LinearModel(w.float(), (ym - mu @ w).float())
+
+
+class KernelSVM:
+    """C-SVM with an RBF or linear kernel trained by sequential minimal optimisation (Platt's
+    simplified SMO with the maximal-violating-pair choice); labels in {0, 1}."""
+
+    def __init__(self, c: float = 1.0, kernel: str = "rbf", gamma: float | None = None, tol: float = 1e-3, max_iter: int = 20000):
+        self.c, self.kernel, self.gamma, self.tol, self.max_iter = c, kernel, gamma, tol, max_iter
+
+    def _k(self, A, B):
+        if self.kernel == "linear":
+            return A @ B.t()
+        d = (A * A).sum(1, keepdim=True) - 2 * A @ B.t() + (B * B).sum(1)[None]
+        return torch.exp(-self.gamma * d.clamp_min(0))
+
+    def fit(self, X, y):
+        X = torch.as_tensor(X).double()
+        t = torch.as_tensor(y).double() * 2 - 1
+        n = X.shape[0]
+        if self.gamma is None:
+            self.gamma = 1.0 / (X.shape[1] * float(X.var()) + 1e-12)
+        Kmat = self._k(X, X)
+        alpha = torch.zeros(n, dtype=torch.double)
+        g = -torch.ones(n, dtype=torch.double)           # gradient of the dual objective
+        for _ in range(self.max_iter):
+            up = ((t > 0) & (alpha < self.c)) | ((t < 0) & (alpha > 0))
+            low = ((t > 0) & (alpha > 0)) | ((t < 0) & (alpha < self.c))
+            score = -t * g
+            i = int(torch.where(up, score, torch.full_like(score, -float("inf"))).argmax())
+            j = int(torch.where(low, score, torch.full_like(score, float("inf"))).argmin())
+            if score[i] - score[j] < self.tol:
+                break
+            eta = Kmat[i, i] + Kmat[j, j] - 2 * Kmat[i, j]
+            step = (score[i] - score[j]) / max(float(eta), 1e-12)
+            # keep both multipliers inside [0, C] along the feasible direction (t_i, -t_j)
+            hi_i = (self.c - alpha[i]) if t[i] > 0 else alpha[i]
+            hi_j = alpha[j] if t[j] > 0 else (self.c - alpha[j])
+            step = min(float(step), float(hi_i), float(hi_j))
+            alpha[i] += t[i] * step
+            alpha[j] -= t[j] * step
+            g += step * (Kmat[:, i] - Kmat[:, j]) * t
+        sv = alpha > 1e-8
+        self.sv, self.coef = X[sv], (alpha * t)[sv]
+        free = sv & (alpha < self.c - 1e-8)
+        idx = free if free.any() else sv
+        self.b = float((t[idx] - (Kmat[idx][:, sv] @ self.coef)).mean()) if idx.any() else 0.0
+        return self
+
+    def decision(self, X):
+        return (self._k(torch.as_tensor(X).double(), self.sv) @ self.coef + self.b).float()
+
+    def classify(self, X):
+        return (self.decision(X) > 0).long()

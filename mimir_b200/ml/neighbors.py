@@ -125,3 +125,79 @@ def pca(X, k) -> PCAModel:
     mu = X.mean(0)
     _, S, Vt = torch.linalg.svd(X - mu, full_matrices=False)
     return PCAModel(mu, Vt[:k], (S[:k] ** 2) / (len(X) - 1))
+
+
+class GMMModel:
+    def __init__(self, weights, means, covs):
+        self.weights, self.means, self.covs = weights, means, covs
+
+    def log_prob(self, X):
+        """[n, k] log of weight_k * N(x | mean_k, cov_k)."""
+        X = torch.as_tensor(X).float()
+        d = torch.distributions.MultivariateNormal(self.means, covariance_matrix=self.covs)
+        return d.log_prob(X[:, None, :]) + self.weights.log()
+
+    def predict(self, X):
+        return torch.softmax(self.log_prob(X), 1)
+
+    def assign(self, X):
+        return self.log_prob(X).argmax(1)
+
+    def score(self, X):
+        return float(torch.logsumexp(self.log_prob(X), 1).mean())
+
+
+def gmm(X, k, iters=100, seed=0, tol=1e-5, reg=1e-6) -> GMMModel:
+    """Full-covariance Gaussian mixture by expectation-maximisation, seeded with k-means."""
+    X = torch.as_tensor(X).float()
+    n, d = X.shape
+    km = kmeans(X, k, seed=seed)
+    a = km.assign(X)
+    means = km.centers.clone()
+    weights = torch.bincount(a, minlength=k).float().clamp_min(1) / n
+    covs = torch.stack([torch.cov(X[a == j].t()) + reg * torch.eye(d) if (a == j).sum() > d else torch.eye(d) for j in range(k)])
+    last = -float("inf")
+    for _ in range(iters):
+        model = GMMModel(weights, means, covs)
+        lp = model.log_prob(X)
+        ll = float(torch.logsumexp(lp, 1).mean())
+        r = torch.softmax(lp, 1)                                  # responsibilities
+        nk = r.sum(0).clamp_min(1e-8)
+        weights = nk / n
+        means = (r.t() @ X) / nk[:, None]
+        diff = X[:, None, :] - means[None]
+        covs = torch.einsum("nk,nki,nkj->kij", r, diff, diff) / nk[:, None, None] + reg * torch.eye(d)
+        if abs(ll - last) < tol:
+            break
+        last = ll
+    return GMMModel(weights, means, covs)
+
+
+def ward(X, k):
+    """Agglomerative clustering with Ward's minimum-variance linkage (Lance-Williams update); labels [n]."""
+    X = torch.as_tensor(X).double()
+    n = X.shape[0]
+    D = pairwise_sq(X, X).clamp_min(0)      # squared Euclidean = Ward distance between singletons (times 1/2)
+    D.fill_diagonal_(float("inf"))
+    size = torch.ones(n, dtype=torch.double)
+    alive = torch.ones(n, dtype=torch.bool)
+    label = torch.arange(n)
+    for _ in range(n - k):
+        flat = int(D.argmin())
+        i, j = flat // n, flat % n
+        if i > j:
+            i, j = j, i
+        ni, nj = size[i], size[j]
+        others = alive.clone()
+        others[i] = others[j] = False
+        nk = size[others]
+        new = ((ni + nk) * D[i, others] + (nj + nk) * D[j, others] - nk * D[i, j]) / (ni + nj + nk)
+        D[i, others] = new
+        D[others, i] = new
+        D[j, :] = float("inf")
+        D[:, j] = float("inf")
+        alive[j] = False
+        size[i] = ni + nj
+        label[label == label[j]] = label[i]
+    _, out = torch.unique(label, return_inverse=True)
+    return out

@@ -93,3 +93,29 @@ def test_distributions():
         pass
     c = D.Categorical(probs=T.tensor([0.2, 0.8]))
     assert abs(float(c.entropy().data()) - 0.5004) < 1e-3
+
+
+def test_gmm_ward_fista_kernel_svm():
+    torch.manual_seed(1)
+    C = torch.cat([torch.randn(80, 2) * 0.5 + torch.tensor([4.0, 0.0]), torch.randn(80, 2) * 0.5 - torch.tensor([4.0, 0.0]),
+                   torch.randn(80, 2) * 0.5 + torch.tensor([0.0, 5.0])])
+    truth = torch.arange(3).repeat_interleave(80)
+    m = ml.gmm(C, 3)
+    a = m.assign(C)
+    assert all(len(set(a[truth == k].tolist())) == 1 for k in range(3)) and len(set(a.tolist())) == 3
+    assert abs(float(m.weights.sum()) - 1) < 1e-5 and m.score(C) > -3.5
+    w = ml.ward(C, 3)
+    assert all(len(set(w[truth == k].tolist())) == 1 for k in range(3)) and len(set(w.tolist())) == 3
+    X, y, wt = _reg()
+    f = ml.fista_lasso(X, y, 0.05)
+    c = ml.lasso(X, y, 0.05)
+    assert torch.allclose(f.w, c.w, atol=2e-3) and f.w[2] == 0
+    # a ring inside a ring: not linearly separable
+    r = torch.cat([torch.rand(100) * 1.0, 2.5 + torch.rand(100) * 1.0])
+    th = torch.rand(200) * 6.283
+    P = torch.stack([r * th.cos(), r * th.sin()], 1)
+    lab = (torch.arange(200) >= 100).long()
+    svm = ml.KernelSVM(c=10.0, kernel="rbf", gamma=1.0).fit(P, lab)
+    assert (svm.classify(P) == lab).float().mean() > 0.98
+    lin = ml.KernelSVM(c=1.0, kernel="linear").fit(X[:150], (X[:150] @ wt > 0).long())
+    assert (lin.classify(X[:150]) == (X[:150] @ wt > 0).long()).float().mean() > 0.95
