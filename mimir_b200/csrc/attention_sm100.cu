@@ -24,7 +24,8 @@
 
 namespace mimir {
 
-constexpr int kAttThreads = 192;
+constexpr int kAttThreads = 192;      // backward kernels: TMA warp, MMA warp, 4 softmax warps
+constexpr int kAttFwdThreads = 320;   // forward: TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quadrant)
 constexpr int kTile = 128;            // query rows and key rows per tile
 constexpr int kChunkBytes = 128 * 128;  // 128 rows x 64 bf16
 
@@ -80,11 +81,41 @@ __device__ __forceinline__ void mma_from_tmem(uint32_t d_tmem, uint32_t p_tmem, 
     umma_ts(d_tmem, p_tmem + ks * 8, mndesc(b_addr, ks), idesc, (accumulate || ks > 0) ? 1u : 0u);
 }
 
+// Bounded rendezvous of the two warps that share a TMEM lane quadrant: publishes `seq` in *mine,
+// waits until *theirs has reached it.  Returns false (and raises the abort flag) after two seconds,
+// so a lost partner can never leave a warp spinning.
+__device__ __forceinline__ bool pair_sync(volatile int* mine, volatile int* theirs, int seq, int lane,
+                                          volatile int* abort_flag, unsigned* err) {
+  __syncwarp();
+  bool ok = true;
+  if (lane == 0) {
+    __threadfence_block();
+    *mine = seq;
+    uint64_t t0 = 0;
+    for (uint32_t it = 1; *theirs < seq; ++it) {
+      if ((it & 0xff) == 0) {
+        if (*abort_flag) { ok = false; break; }
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) {
+          *abort_flag = 1;
+          raise_error(err, kErrWaitTimeout);
+          ok = false;
+          break;
+        }
+      }
+    }
+    __threadfence_block();
+  }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  return ok;
+}
+
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(kAttThreads, 1)
+__global__ void __launch_bounds__(kAttFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ O,
                 float* __restrict__ LSE, AttnParams p, unsigned* err) {
@@ -107,6 +138,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* pv_full = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float xmax[2][2][kTile];   // [score buffer][half][row]: row maxima exchanged between partner warps
+  __shared__ int xseq[2][4];            // [half][quadrant]: how many exchanges that warp has published
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.Tq + kTile - 1) / kTile;
@@ -127,8 +160,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4); mbar_init(&pv_full[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); mbar_init(&pv_full[i], 1);
     }
+    for (int i = 0; i < 8; ++i) (&xseq[0][0])[i] = 0;
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -184,59 +218,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    const int quad = warp & 3;
+    // Two warps share each 32-row TMEM lane quadrant: `half` 0 owns keys 0..63 of a score tile and
+    // output columns 0..D/2, `half` 1 the rest.  Each keeps its 64 scores in registers (one pass
+    // over TMEM), the pair exchanges the running row maximum through shared memory once per tile
+    // (a 64-thread named barrier), and the two partial row sums are added at the very end.  One
+    // warp per scheduler was latency-bound; this puts two on each.
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int q_pos = q0 + r;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
+    constexpr int DH = D / 2;
     float m = -INFINITY, l = 0.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    for (int d = 0; d < DH; ++d) o[d] = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int bi = j & 1;
       if (!(ok = mbar_wait(&s_full[bi], (j >> 1) & 1, abort_flag, err))) break;
       tc_fence_after();
-      const int kv0 = j * kTile;
-      const bool need_mask = (p.causal && kv0 + kTile - 1 > q0 + p.offset) || (kv0 + kTile > p.Tk);
+      const int kv0 = j * kTile + half * 64;
+      const bool need_mask = (p.causal && kv0 + 63 > q0 + p.offset) || (kv0 + 64 > p.Tk);
       const int limit = p.causal ? min(p.Tk - 1, q_pos + p.offset) : p.Tk - 1;  // last visible key
       const uint32_t ts = tS + bi * 128 + lane_base;
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(ts + c * 32, rr);
-        tmem_ld_wait();
+      uint32_t s0[32], s1[32];
+      tmem_ld32(ts + half * 64, s0);
+      tmem_ld32(ts + half * 64 + 32, s1);
+      tmem_ld_wait();
+      float mx = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float s = __uint_as_float(rr[e]);
-          if (need_mask && kv0 + c * 32 + e > limit) s = -INFINITY;
-          mx = fmaxf(mx, s);
+      for (int e = 0; e < 32; ++e) {
+        float a = __uint_as_float(s0[e]), c = __uint_as_float(s1[e]);
+        if (need_mask) {
+          if (kv0 + e > limit) a = -INFINITY;
+          if (kv0 + 32 + e > limit) c = -INFINITY;
+          s0[e] = __float_as_uint(a);
+          s1[e] = __float_as_uint(c);
         }
+        mx = fmaxf(mx, fmaxf(a, c));
       }
+      xmax[bi][half][r] = mx;
+      if (!(ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], j + 1, lane, abort_flag, err))) break;
+      mx = fmaxf(m, fmaxf(mx, xmax[bi][half ^ 1][r]));
       const float m_use = mx == -INFINITY ? 0.f : mx;
       const float alpha = ex2((m - m_use) * sl2);
       const float msl = m_use * sl2;
       float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32], pk[16];
-        tmem_ld32(ts + c * 32, rr);
-        tmem_ld_wait();
+      uint32_t pk[32];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = ex2(__uint_as_float(rr[e]) * sl2 - msl);
-          float p1 = ex2(__uint_as_float(rr[e + 1]) * sl2 - msl);
-          if (need_mask) {
-            if (kv0 + c * 32 + e > limit) p0 = 0.f;
-            if (kv0 + c * 32 + e + 1 > limit) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st16(ts + c * 16, pk);  // P (bf16 pairs) over the consumed part of S
+      for (int e = 0; e < 32; e += 2) {
+        const float p0 = ex2(__uint_as_float(s0[e]) * sl2 - msl), p1 = ex2(__uint_as_float(s0[e + 1]) * sl2 - msl);
+        const float p2 = ex2(__uint_as_float(s1[e]) * sl2 - msl), p3 = ex2(__uint_as_float(s1[e + 1]) * sl2 - msl);
+        rowsum += (p0 + p1) + (p2 + p3);
+        pk[e >> 1] = pack_bf16x2(p0, p1);
+        pk[16 + (e >> 1)] = pack_bf16x2(p2, p3);
       }
+      // P (bf16 pairs) goes over columns 0..63 of the score buffer; both warps hold their scores in
+      // registers since before the barrier, so nothing unread is overwritten
+      tmem_st32(ts + half * 32, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -248,36 +288,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!(ok = mbar_wait(&pv_full[pb], ((j - 1) >> 1) & 1, abort_flag, err))) break;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < DH / 32; ++c) {
           uint32_t rr[32];
-          tmem_ld32(tPV + pb * D + lane_base + c * 32, rr);
+          tmem_ld32(tPV + pb * D + lane_base + half * DH + c * 32, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[c * 32 + e] += __uint_as_float(rr[e]);
         }
       }
 #pragma unroll
-      for (int d = 0; d < D; ++d) o[d] *= alpha;
+      for (int d = 0; d < DH; ++d) o[d] *= alpha;
     }
     if (ok && n_kv > 0) {
       const int pb = (n_kv - 1) & 1;
       if (mbar_wait(&pv_full[pb], ((n_kv - 1) >> 1) & 1, abort_flag, err)) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < DH / 32; ++c) {
           uint32_t rr[32];
-          tmem_ld32(tPV + pb * D + lane_base + c * 32, rr);
+          tmem_ld32(tPV + pb * D + lane_base + half * DH + c * 32, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[c * 32 + e] += __uint_as_float(rr[e]);
         }
       }
     }
-    if (q_pos < p.Tq) {
+    // the row sum is the sum of the two halves' partial sums (same running maximum in both); the
+    // buffer the last tile did not use carries it
+    const int fb = n_kv & 1;
+    xmax[fb][half][r] = l;
+    if (ok) ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], n_kv + 1, lane, abort_flag, err);
+    l += xmax[fb][half ^ 1][r];
+    if (ok && q_pos < p.Tq) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = O + (static_cast<size_t>(b) * p.Tq + q_pos) * p.ldo + h * D;
+      __nv_bfloat16* dst = O + (static_cast<size_t>(b) * p.Tq + q_pos) * p.ldo + h * D + half * DH;
 #pragma unroll
-      for (int d = 0; d < D; d += 8) {
+      for (int d = 0; d < DH; d += 8) {
         uint4 u;
         u.x = pack_bf16x2(o[d] * inv, o[d + 1] * inv);
         u.y = pack_bf16x2(o[d + 2] * inv, o[d + 3] * inv);
@@ -285,7 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         u.w = pack_bf16x2(o[d + 6] * inv, o[d + 7] * inv);
         *reinterpret_cast<uint4*>(dst + d) = u;
       }
-      if (LSE)
+      if (LSE && half == 0)
         LSE[(static_cast<size_t>(b) * p.Hq + h) * p.Tq + q_pos] =
             l > 0.f ? (m * sl2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
@@ -339,7 +385,7 @@ __global__ void attn_dsum_kernel(const __nv_bfloat16* __restrict__ O, const __nv
 //   S'  = X0 * Y0^T,  dP' = X1 * Y1^T
 // ---------------------------------------------------------------------------
 template <int D, int MODE>
-__global__ void __launch_bounds__(kAttThreads, 1)
+__global__ void __launch_bounds__(kAttFwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmX1,
                 const __grid_constant__ CUtensorMap tmY0, const __grid_constant__ CUtensorMap tmY1,
                 const float* __restrict__ LSE, const float* __restrict__ Dsum,
@@ -353,9 +399,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
   uint8_t* sX0 = smem;
   uint8_t* sX1 = sX0 + TB;
   uint8_t* sY = sX1 + TB;  // NST x (Y0, Y1)
-  // per softmax warp, double buffered: [2][4 warps][lse*log2e (128) | dsum (128)]
+  // per softmax warp, double buffered: [2][8 warps][lse*log2e (128) | dsum (128)]
   float* vec = reinterpret_cast<float*>(sY + NST * 2 * TB);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(vec + 2 * 4 * 256);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(vec + 2 * 8 * 256);
   uint64_t* x_full = bars;
   uint64_t* y_full = x_full + 1;
   uint64_t* y_empty = y_full + NST;
@@ -364,6 +410,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
   uint64_t* acc_full = p_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ int xseq[2][4];   // [half][quadrant]: rendezvous counters of the two warps sharing a lane quadrant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = p.Hq / p.Hkv;
@@ -397,8 +444,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
     mbar_init(x_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&y_full[s], 1); mbar_init(&y_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 4);
+    mbar_init(p_ready, 8);
     mbar_init(acc_full, 1);
+    for (int i = 0; i < 8; ++i) (&xseq[0][0])[i] = 0;
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -450,7 +498,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
       if (ok) umma_commit(acc_full);
     }
   } else {
-    const int quad = warp & 3;
+    // Two warps per TMEM lane quadrant: `half` 0 handles columns 0..63 of the score / dP tiles and
+    // the first half of the accumulator columns in the epilogue, `half` 1 the rest.  Both read their
+    // columns into registers, meet (bounded), and only then write P / dS over the score buffers,
+    // whose bf16 columns overlap the partner's unread fp32 columns.
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row inside the owned tile
     const int x_pos = x0 + r;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
@@ -467,7 +519,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
     for (int it = 0; it < n_iter && ok; ++it) {
       const int g = it / n_inner, yt = y_begin + it % n_inner;
       const int y0 = yt * kTile;
-      float* vbuf = vec + ((it & 1) * 4 + quad) * 256;
+      float* vbuf = vec + ((it & 1) * 8 + (warp - 2)) * 256;
       if (MODE == 0) {
         // each warp stages its own copy of this query tile's logsumexp and Dsum vectors
         const int hq = hx * group + g;
@@ -496,12 +548,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
         if (p.causal) c_hi = min(c_hi, x_pos + p.offset - y0 + 1);
       }
       if (!row_live) c_hi = 0;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rd[32], pk[16], dk[16];
-        tmem_ld32(tS + lane_base + c * 32, rs);
-        tmem_ld32(tDP + lane_base + c * 32, rd);
-        tmem_ld_wait();
+      uint32_t rs[2][32], rd[2][32];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld32(tS + lane_base + (half * 2 + cc) * 32, rs[cc]);
+        tmem_ld32(tDP + lane_base + (half * 2 + cc) * 32, rd[cc]);
+      }
+      tmem_ld_wait();
+      if (!(ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], it + 1, lane, abort_flag, err))) break;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        uint32_t pk[16], dk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float pv[2], dv[2];
@@ -510,10 +568,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
             const int col = c * 32 + e + u;
             const float lse2 = MODE == 0 ? vbuf[col] : my_lse2;
             const float ds = MODE == 0 ? vbuf[128 + col] : my_dsum;
-            float pr = ex2(__uint_as_float(rs[e + u]) * sl2 - lse2);
+            float pr = ex2(__uint_as_float(rs[cc][e + u]) * sl2 - lse2);
             if (col < c_lo || col >= c_hi) pr = 0.f;
             pv[u] = pr;
-            dv[u] = pr * (__uint_as_float(rd[e + u]) - ds);
+            dv[u] = pr * (__uint_as_float(rd[cc][e + u]) - ds);
           }
           pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
           dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
@@ -540,6 +598,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
         const uint32_t ta = (a == 0 ? tA0 : tA1) + lane_base;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
+          if ((c & 1) != half) continue;   // the two warps of a quadrant take alternate 32-column chunks
           uint32_t rr[32];
           tmem_ld32(ta + c * 32, rr);
           tmem_ld_wait();
@@ -559,7 +618,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
     } else if (n_iter == 0) {
       // nothing attends here (possible only with a negative causal offset): zero gradients
       const bool live = MODE == 0 ? x_pos < p.Tk : x_pos < p.Tq;
-      if (live) {
+      if (live && half == 0) {
         const int T = MODE == 0 ? p.Tk : p.Tq;
         const int ld = MODE == 0 ? p.ldkv : p.ldo;
         for (int a = 0; a < (MODE == 0 ? 2 : 1); ++a) {
@@ -622,13 +681,13 @@ MIMIR_API int mimir_attention_fwd(const void* Q, const void* K, const void* V, v
     constexpr int SM = (1 + 2 * 3) * kChunkBytes + 1024 + 256;
     static bool cfg = false;
     if (!cfg) { if (set_smem(attn_fwd_kernel<64>, SM)) return -1; cfg = true; }
-    attn_fwd_kernel<64><<<grid, kAttThreads, SM, st>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(O), LSE, p,
+    attn_fwd_kernel<64><<<grid, kAttFwdThreads, SM, st>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(O), LSE, p,
                                                        error_word_dev());
   } else {
     constexpr int SM = (1 + 2 * 2) * 2 * kChunkBytes + 1024 + 256;
     static bool cfg = false;
     if (!cfg) { if (set_smem(attn_fwd_kernel<128>, SM)) return -1; cfg = true; }
-    attn_fwd_kernel<128><<<grid, kAttThreads, SM, st>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(O), LSE, p,
+    attn_fwd_kernel<128><<<grid, kAttFwdThreads, SM, st>>>(tq, tk, tv, static_cast<__nv_bfloat16*>(O), LSE, p,
                                                         error_word_dev());
   }
   count_launch();
@@ -659,26 +718,26 @@ MIMIR_API int mimir_attention_bwd(const void* Q, const void* K, const void* V, c
   auto dk = static_cast<__nv_bfloat16*>(dK);
   auto dv = static_cast<__nv_bfloat16*>(dV);
   if (D == 64) {
-    constexpr int SM = (2 + 2 * 2) * kChunkBytes + 8192 + 1024 + 256;
+    constexpr int SM = (2 + 2 * 2) * kChunkBytes + 16384 + 1024 + 256;
     static bool cfg = false;
     if (!cfg) {
       if (set_smem(attn_bwd_kernel<64, 0>, SM) || set_smem(attn_bwd_kernel<64, 1>, SM)) return -1;
       cfg = true;
     }
-    attn_bwd_kernel<64, 0><<<grid_kv, kAttThreads, SM, st>>>(tk, tv, tq, tdo, LSE, dsum, dv, dk, p,
+    attn_bwd_kernel<64, 0><<<grid_kv, kAttFwdThreads, SM, st>>>(tk, tv, tq, tdo, LSE, dsum, dv, dk, p,
                                                              error_word_dev());
-    attn_bwd_kernel<64, 1><<<grid_q, kAttThreads, SM, st>>>(tq, tdo, tk, tv, LSE, dsum, dq, nullptr, p,
+    attn_bwd_kernel<64, 1><<<grid_q, kAttFwdThreads, SM, st>>>(tq, tdo, tk, tv, LSE, dsum, dq, nullptr, p,
                                                             error_word_dev());
   } else {
-    constexpr int SM = (2 + 2 * 2) * 2 * kChunkBytes + 8192 + 1024 + 256;
+    constexpr int SM = (2 + 2 * 2) * 2 * kChunkBytes + 16384 + 1024 + 256;
     static bool cfg = false;
     if (!cfg) {
       if (set_smem(attn_bwd_kernel<128, 0>, SM) || set_smem(attn_bwd_kernel<128, 1>, SM)) return -1;
       cfg = true;
     }
-    attn_bwd_kernel<128, 0><<<grid_kv, kAttThreads, SM, st>>>(tk, tv, tq, tdo, LSE, dsum, dv, dk, p,
+    attn_bwd_kernel<128, 0><<<grid_kv, kAttFwdThreads, SM, st>>>(tk, tv, tq, tdo, LSE, dsum, dv, dk, p,
                                                               error_word_dev());
-    attn_bwd_kernel<128, 1><<<grid_q, kAttThreads, SM, st>>>(tq, tdo, tk, tv, LSE, dsum, dq, nullptr, p,
+    attn_bwd_kernel<128, 1><<<grid_q, kAttFwdThreads, SM, st>>>(tq, tdo, tk, tv, LSE, dsum, dq, nullptr, p,
                                                              error_word_dev());
   }
   count_launch(3);

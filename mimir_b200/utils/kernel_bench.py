@@ -131,6 +131,36 @@ def bench_q4(a):
         print(json.dumps(rec), flush=True)
 
 
+def bench_conv(a):
+    """Implicit-GEMM convolution (forward, input gradient, weight gradient) against cuDNN through PyTorch."""
+    from ..ops import conv as C
+    N, Ci, Co, H, W, Kk = a.n, a.ci, a.co, a.h, a.w, a.ksize
+    pad = Kk // 2
+    x = torch.randn(N, Ci, H, W, device="cuda").bfloat16()
+    w = (torch.randn(Co, Ci, Kk, Kk, device="cuda") * 0.05).bfloat16()
+    xn, wp, wd = C.to_nhwc(x), C.pack_filter(w), C.pack_filter_dgrad(w)
+    y = C.conv2d_fwd(xn, wp, Kk, Kk, pad)
+    dy = torch.randn_like(y)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if a.flush else None
+    flops = 2.0 * N * H * W * Co * Ci * Kk * Kk
+    peak = _peaks().get("bf16_tflops")
+    cases = {"conv_fwd": lambda: C.conv2d_fwd(xn, wp, Kk, Kk, pad, out=y),
+             "conv_dgrad": lambda: C.conv2d_dgrad(dy, wd, Kk, Kk, pad),
+             "conv_wgrad": lambda: C.conv2d_wgrad(dy, xn, Co, Kk, Kk, pad)}
+    for name, fn in cases.items():
+        if a.only and a.only != name:
+            continue
+        t = time_ms(fn, a.iters, flush)
+        rec = {"kernel": name, "N": N, "Ci": Ci, "Co": Co, "H": H, "W": W, "k": Kk, "ms": t, "tflops": flops / t / 1e9}
+        if peak:
+            rec["frac_of_measured_cublas_peak"] = rec["tflops"] / peak
+        print(json.dumps(rec), flush=True)
+    if not a.no_baseline:
+        xc, wc = x.contiguous(memory_format=torch.channels_last), w.contiguous(memory_format=torch.channels_last)
+        t = time_ms(lambda: torch.nn.functional.conv2d(xc, wc, padding=pad), a.iters, flush)
+        print(json.dumps({"kernel": "cudnn_conv_fwd(torch)", "ms": t, "tflops": flops / t / 1e9}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -151,12 +181,20 @@ def main():
     q.add_argument("--b", type=int, default=1)
     q.add_argument("--splits", type=int, default=0)
     q.add_argument("--only", default="")
-    for p in (g, t, q):
+    c = sub.add_parser("conv")
+    c.add_argument("--n", type=int, default=32)
+    c.add_argument("--ci", type=int, default=128)
+    c.add_argument("--co", type=int, default=128)
+    c.add_argument("--h", type=int, default=56)
+    c.add_argument("--w", type=int, default=56)
+    c.add_argument("--ksize", type=int, default=3)
+    c.add_argument("--only", default="")
+    for p in (g, t, q, c):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "q4": bench_q4}[a.cmd](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "q4": bench_q4, "conv": bench_conv}[a.cmd](a)
 
 
 if __name__ == "__main__":
