@@ -61,3 +61,20 @@ def test_watchdog_and_error_word_decoding():
     assert fired == [1]
     e = health.DeviceFault(8 | 4)
     assert "another GPU" in str(e) and "barrier" in str(e) and e.word == 12
+
+
+def test_phase_timer_on_host():
+    from mimir_b200.utils.phases import PhaseTimer
+    t = PhaseTimer()
+    for _ in range(3):
+        with t.phase("forward"):
+            time.sleep(0.01)
+        with t.phase("backward"):
+            time.sleep(0.02)
+    rep = t.report()
+    assert rep["forward"]["calls"] == 3 and 25 < rep["forward"]["ms"] < 200
+    assert rep["backward"]["ms"] > rep["forward"]["ms"]
+    off = PhaseTimer(enabled=False)
+    with off.phase("x"):
+        pass
+    assert off.report() == {}
