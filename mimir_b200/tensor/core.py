@@ -244,8 +244,35 @@ def _meta_of(t: Tensor) -> torch.Tensor:
     return torch.empty(t.shape, dtype=t.dtype, device="meta")
 
 
+_META_CACHE: dict = {}
+
+
+def _meta_key(fn, args, kw):
+    """Structural key of a shape inference: the op's code, the constants it closes over, the operand
+    shapes / dtypes and the plain arguments.  None when something in there cannot be hashed (a tensor
+    captured by the closure, a list argument): that inference is simply not cached."""
+    try:
+        cells = tuple(c.cell_contents for c in (fn.__closure__ or ()))
+        for c in cells:
+            if isinstance(c, (torch.Tensor, Tensor, list, dict)):
+                return None
+
+        def sig(a):
+            if isinstance(a, Tensor):
+                return ("T", tuple(a.shape), a.dtype)
+            if isinstance(a, (list, tuple)):
+                return tuple(sig(x) for x in a)
+            return a
+        key = (fn.__code__, cells, getattr(fn, "__defaults__", None), tuple(sig(a) for a in args), tuple(sorted(kw.items())))
+        hash(key)
+        return key
+    except Exception:  # noqa: BLE001 - unhashable or exotic argument
+        return None
+
+
 def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None) -> Tensor:
-    """Records ``fn(*args, **kw)``: propagates errors, infers shape/dtype on meta tensors."""
+    """Records ``fn(*args, **kw)``: propagates errors, infers shape/dtype on meta tensors (the result
+    of an inference is cached by structure, so a training loop pays for it once)."""
     err = _first_error(args)
     if err is not None:
         return _error_tensor(err)
@@ -255,10 +282,17 @@ def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | 
         for t in tensors:
             if t.device != device:
                 return _error_tensor(E.ErrDevice(f"{opname}: operands on {device} and {t.device}"))
-    try:
-        meta = fn(*_map_args(args, _meta_of), **kw)
-    except Exception as exc:  # noqa: BLE001
-        return _error_tensor(E.classify(exc))
+    key = _meta_key(fn, args, kw)
+    meta = _META_CACHE.get(key) if key is not None else None
+    if meta is None:
+        try:
+            meta = fn(*_map_args(args, _meta_of), **kw)
+        except Exception as exc:  # noqa: BLE001
+            return _error_tensor(E.classify(exc))
+        if key is not None:
+            if len(_META_CACHE) > 8192:
+                _META_CACHE.clear()
+            _META_CACHE[key] = meta
     if isinstance(meta, (tuple, list)):
         outs = tuple(Tensor(fn=_pick(fn, i), args=tuple(args), kw=kw, shape=m.shape, dtype=m.dtype, device=device,
                             opname=opname) for i, m in enumerate(meta))
