@@ -274,3 +274,52 @@ def save(path, module_or_state, metadata=None, training=None) -> None:
     state = module_or_state.state_dict() if hasattr(module_or_state, "state_dict") else module_or_state
     write_tensors(path, {k: v for k, v in state.items() if torch.is_tensor(v) or isinstance(v, QuantizedTensor)},
                   metadata=metadata, training=training)
+
+
+def lora_info(model: "Model"):
+    """``{"rank", "alpha", "base", "targets"}`` of a LoRA adapter file, None for other files
+    (mim.Model.LoRA in the reference)."""
+    md = model.metadata
+    if md.get("adapter.type") != "lora":
+        return None
+    targets = sorted({n.rsplit(".", 1)[0] for n in model.names() if n.endswith(".lora_a")})
+    return {"rank": int(md.get("adapter.lora.rank", 0)), "alpha": float(md.get("adapter.lora.alpha", 0.0)),
+            "base": md.get("adapter.base", ""), "targets": targets}
+
+
+def apply_lora(module, adapter: "Model") -> int:
+    """Wraps the ``nn.Linear`` layers an adapter file names (``<path>.lora_a`` / ``<path>.lora_b``, paths as
+    in ``module.named_params()`` without the ``.weight`` suffix) in ``LoRALinear`` and loads the factors;
+    returns how many layers were adapted (mim.Model.ApplyLoRA)."""
+    from ..nn.module import Linear, LoRALinear
+    info = lora_info(adapter)
+    if info is None:
+        raise MimError("not a LoRA adapter file")
+    done = 0
+    for path in info["targets"]:
+        owner, attr = module, None
+        parts = path.split(".")
+        for i, part in enumerate(parts):
+            last = i == len(parts) - 1
+            holder = owner
+            owner = owner[int(part)] if isinstance(owner, (list, tuple)) else (owner[part] if isinstance(owner, dict) else getattr(owner, part))
+            if last:
+                attr = (holder, part)
+        holder, part = attr
+        lin = owner
+        if isinstance(lin, LoRALinear):
+            wrapped = lin
+        elif isinstance(lin, Linear):
+            wrapped = LoRALinear(lin, info["rank"], info["alpha"])
+            if isinstance(holder, list):
+                holder[int(part)] = wrapped
+            elif isinstance(holder, dict):
+                holder[part] = wrapped
+            else:
+                setattr(holder, part, wrapped)
+        else:
+            raise MimError(f"{path}: not a Linear layer")
+        wrapped.lora_a.set(adapter.tensor(path + ".lora_a").clone().to(wrapped.lora_a.dtype))
+        wrapped.lora_b.set(adapter.tensor(path + ".lora_b").clone().to(wrapped.lora_b.dtype))
+        done += 1
+    return done

@@ -83,6 +83,21 @@ class KVCache:
     def buffers(self):
         return self.k, self.v
 
+    def write(self, k: torch.Tensor, v: torch.Tensor, at: int | None = None) -> None:
+        """Stores keys / values at position ``at`` (default: the current length) without moving the
+        length: a recorded decode step writes first and calls ``advance`` afterwards."""
+        at = self.len if at is None else at
+        t = k.shape[2]
+        if at + t > self.cap:
+            raise T.ErrShape(f"KV cache overflow: {at} + {t} > {self.cap}")
+        self.k[:, :, at: at + t] = k.to(self.k.dtype)
+        self.v[:, :, at: at + t] = v.to(self.v.dtype)
+
+    def advance(self, t: int = 1) -> None:
+        if self.len + t > self.cap:
+            raise T.ErrShape(f"KV cache overflow: {self.len} + {t} > {self.cap}")
+        self.len += t
+
 
 class SelfAttention(Module):
     def __init__(self, dim: int, heads: int, kv_heads: int | None = None, bias: bool = True, causal: bool = True,

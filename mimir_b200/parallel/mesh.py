@@ -458,3 +458,50 @@ def sharded_step(model, opt, mesh: Mesh, loss_fn, x, y, data_axis: str = "data")
     if dp > 1:
         total = mesh.all_reduce(total, data_axis)
     return float(total[0])
+
+
+# ---------------------------------------------------------------------------
+# tensors with a sharding (tensor.Shard / WithSharding / Tensor.Sharding, tensor/mesh.go:218-314)
+# ---------------------------------------------------------------------------
+def shard(x: T.Tensor, mesh: Mesh, spec: PartitionSpec) -> T.Tensor:
+    """This rank's block of a replicated tensor under ``spec``; the result remembers its sharding."""
+    out = T.from_torch(mesh.local_slice(x.data(), spec))
+    out._sharding = (mesh, spec)
+    return out
+
+
+def sharding_of(x: T.Tensor):
+    """``(mesh, spec)`` of a tensor made by ``shard`` / ``with_sharding``, else None (replicated)."""
+    return getattr(x, "_sharding", None)
+
+
+def unshard(x: T.Tensor) -> T.Tensor:
+    """The whole tensor on every rank: one all-gather per split dimension (sections regrouped)."""
+    sh = sharding_of(x)
+    if sh is None:
+        return x
+    mesh, spec = sh
+    v = x.data()
+    for d, ax in enumerate(spec):
+        if ax is None or mesh.axis_size(ax) == 1:
+            continue
+        n = mesh.axis_size(ax)
+        full = mesh.all_gather(v, ax, d)
+        sec = spec.sections
+        if sec is not None and sec[0] == d:
+            # gathered order is [rank][section]; the tensor's own order is [section][rank]
+            per = [s // n for s in sec[1]]
+            blocks = full.split([p for _ in range(n) for p in per], d)
+            order = [blocks[r * len(per) + s] for s in range(len(per)) for r in range(n)]
+            full = torch.cat(order, d)
+        v = full
+    return T.from_torch(v)
+
+
+def with_sharding(x: T.Tensor, mesh: Mesh, spec: PartitionSpec) -> T.Tensor:
+    """Converts ``x`` to the layout ``spec``.  There is no all-to-all: a split that moves from one axis
+    to another is gathered and cut again, as in the reference."""
+    cur = sharding_of(x)
+    if cur is not None and cur[0] is mesh and tuple(cur[1]) == tuple(spec) and cur[1].sections == spec.sections:
+        return x
+    return shard(unshard(x), mesh, spec)

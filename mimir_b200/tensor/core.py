@@ -154,6 +154,22 @@ class Tensor:
     def tolist(self):
         return self.data().cpu().tolist()
 
+    def bytes(self) -> bytes:
+        """The realized value as raw little-endian bytes in row-major order (tensor.Bytes)."""
+        v = self.data().contiguous().cpu()
+        return v.view(torch.uint8).numpy().tobytes() if v.numel() else b""
+
+    def read_bytes(self, out) -> int:
+        """Copies the value's bytes into a writable buffer (bytearray, memoryview, numpy); returns the count."""
+        raw = self.bytes()
+        memoryview(out).cast("B")[: len(raw)] = raw
+        return len(raw)
+
+    @property
+    def sharding(self):
+        """``(mesh, spec)`` when the tensor is one rank's block of a sharded value, else None."""
+        return getattr(self, "_sharding", None)
+
     def donate(self) -> "Tensor":
         """Marks a realized leaf whose memory the next schedule may reuse
         (internal/sched/donate.go:49); using it afterwards is ErrDonated."""
@@ -857,6 +873,39 @@ def avg_pool2d(x, kernel, stride=None, padding=0):
 
 def upsample_nearest(x, scale):
     return _node(lambda v: torch.nn.functional.interpolate(v, scale_factor=scale, mode="nearest"), (x,), {}, "upsample")
+
+
+def from_bytes(data, shape, dtype=torch.float32, device: Device | None = None) -> Tensor:
+    """A tensor over raw little-endian bytes (bytes, bytearray, memoryview, mmap) without copying when
+    the buffer is writable or the target is another device (tensor.FromBytes, tensor/bytes.go)."""
+    shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
+    need = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+    mv = memoryview(data).cast("B")
+    if len(mv) < need:
+        return _error_tensor(E.ErrShape(f"from_bytes: {len(mv)} bytes for shape {shape} of {dtype} ({need} needed)"))
+    import numpy as np
+    arr = np.frombuffer(mv, dtype=np.uint8, count=need)
+    t = torch.from_numpy(arr if arr.flags.writeable else arr.copy()).view(dtype).view(shape)
+    return from_torch(t if device is None else t.to(device.torch))
+
+
+def from_bytes_func(fill, shape, dtype=torch.float32, device: Device | None = None) -> Tensor:
+    """Like ``from_bytes`` but ``fill(buffer)`` writes the bytes into storage this call owns (one copy
+    fewer when the source is a stream)."""
+    shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list)) else (shape,)))
+    t = torch.empty(shape, dtype=dtype)
+    fill(memoryview(t.view(torch.uint8).numpy()).cast("B"))
+    return from_torch(t if device is None else t.to(device.torch))
+
+
+def realize_into(dst: Tensor, src: Tensor) -> Tensor:
+    """Computes ``src`` and writes it over the storage of the realized tensor ``dst`` (same shape and
+    dtype), so that holders of ``dst`` see the new value (sched.RealizeInto)."""
+    if tuple(dst.shape) != tuple(src.shape) or dst.dtype != src.dtype:
+        raise E.ErrShape(f"realize_into: {tuple(src.shape)} {src.dtype} does not fit {tuple(dst.shape)} {dst.dtype}")
+    realize(dst, src)
+    dst._val.copy_(src._val)
+    return dst
 
 
 def _bind_methods():

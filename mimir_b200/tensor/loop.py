@@ -81,8 +81,32 @@ class Recording:
         return (outs[0] if self._single else outs), True
 
 
+    def replay_into(self, dests, *inputs) -> bool:
+        """Replays and writes the results over the realized tensors ``dests``; False (nothing written)
+        when the inputs or the destinations do not fit (tensor.ReplayInto)."""
+        outs, ok = self.replay(*inputs)
+        if not ok:
+            return False
+        outs = [outs] if self._single else list(outs)
+        dests = [dests] if isinstance(dests, C.Tensor) else list(dests)
+        if len(dests) != len(outs) or any(tuple(d.shape) != tuple(o.shape) or d.dtype != o.dtype for d, o in zip(dests, outs)):
+            return False
+        for d, o in zip(dests, outs):
+            C.realize_into(d, o)
+        return True
+
+
 def record(f, *inputs) -> Recording:
     return Recording(f, inputs)
+
+
+def record_into(dests, f, *inputs) -> Recording:
+    """``record`` whose first run already lands in ``dests`` (tensor.RecordInto)."""
+    r = Recording(f, inputs)
+    dests = [dests] if isinstance(dests, C.Tensor) else list(dests)
+    for d, o in zip(dests, r.outputs):
+        C.realize_into(d, o)
+    return r
 
 
 class TracedGraph:

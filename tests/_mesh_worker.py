@@ -23,10 +23,35 @@ def build():
     return Net()
 
 
+def sharded_tensor_layouts(rank, world):
+    """shard / unshard / with_sharding of plain tensors, with a sectioned split."""
+    import torch
+    import mimir_b200.tensor as T
+    from mimir_b200.parallel import mesh as M
+    mesh = M.Mesh((2, 2), ("data", "model"))
+    full = torch.arange(8 * 6, dtype=torch.float32).view(8, 6)
+    x = M.shard(T.from_torch(full), mesh, M.P("data", "model"))
+    ok = tuple(x.shape) == (4, 3) and x.sharding[1] == M.P("data", "model")
+    ok = ok and torch.equal(M.unshard(x).data(), full)
+    y = M.with_sharding(x, mesh, M.P("model", None))               # the split moves to the other axis
+    ok = ok and tuple(y.shape) == (4, 6) and torch.equal(M.unshard(y).data(), full)
+    spec = M.P("model", None).with_sections(0, 4, 2, 2)            # [Q | K | V]-style rows
+    z = M.shard(T.from_torch(full), mesh, spec)
+    ok = ok and tuple(z.shape) == (4, 6) and torch.equal(M.unshard(z).data(), full)
+    i = mesh.axis_index("model")
+    ok = ok and torch.equal(z.data()[:2], full[2 * i: 2 * i + 2]) and torch.equal(z.data()[2:3], full[4 + i: 5 + i])
+    return {"ok": bool(ok)}
+
+
 def main():
     strategy = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
+    if strategy == "layouts":
+        out = sharded_tensor_layouts(rank, world)
+        os.write(1, ("RESULT " + json.dumps(dict(out, rank=rank)) + "\n").encode())
+        dist.destroy_process_group()
+        return
     import mimir_b200.tensor as T
     from mimir_b200 import optim
     from mimir_b200.nn import loss as L

@@ -37,3 +37,8 @@ def test_sharded_matches_one_device(strategy, port):
     if strategy == "fsdp":
         assert r["fwd"]["ar"] == 0 and r["fwd"]["ag"] > 0 and r["fwd"]["rs"] == 0
         assert r["step"]["ag"] == r["step"]["rs"]  # gathered once, gradient scattered once per sharded tensor
+
+
+def test_tensor_shard_unshard_and_relayout():
+    res = _run("layouts", 4, 29566)
+    assert all(r["ok"] for r in res), res

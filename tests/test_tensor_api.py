@@ -86,3 +86,61 @@ def test_custom_func_and_checkpoint_gradients():
     T.sum_(T.checkpoint(lambda t: T.exp(t) * t)(q.value())).backward()
     want = q._data.exp() * (1 + q._data)
     assert torch.allclose(q.grad().data(), want)
+
+
+def test_bytes_round_trip_realize_into_and_record_into():
+    import mimir_b200.tensor as T
+    x = T.tensor([[1.0, 2.0], [3.0, 4.0]])
+    raw = x.bytes()
+    assert len(raw) == 16
+    y = T.from_bytes(raw, (2, 2))
+    assert y.data().tolist() == [[1.0, 2.0], [3.0, 4.0]]
+    buf = bytearray(16)
+    assert x.read_bytes(buf) == 16 and bytes(buf) == raw
+    assert T.from_bytes(raw[:8], (2, 2)).err is not None                 # too few bytes: a sticky error, no exception
+    z = T.from_bytes_func(lambda mv: mv.__setitem__(slice(0, 16), raw), (2, 2))
+    assert z.data().tolist() == y.data().tolist()
+    dst = T.tensor([[0.0, 0.0], [0.0, 0.0]])
+    held = dst.data()
+    T.realize_into(dst, x * 2.0)
+    assert held.tolist() == [[2.0, 4.0], [6.0, 8.0]]                      # same storage, new value
+    out = T.tensor([0.0, 0.0])
+    rec = T.record_into(out, lambda a: a + 1.0, T.tensor([1.0, 2.0]))
+    assert out.data().tolist() == [2.0, 3.0]
+    assert rec.replay_into(out, T.tensor([5.0, 6.0])) and out.data().tolist() == [6.0, 7.0]
+    assert not rec.replay_into(out, T.tensor([5.0, 6.0, 7.0]))            # other shape: refused, nothing written
+    assert out.data().tolist() == [6.0, 7.0]
+    assert isinstance(T.gpus(), list)
+
+
+def test_kv_cache_write_then_advance():
+    import torch
+    from mimir_b200 import nn
+    c = nn.KVCache(1, 2, 4, 3)
+    k = torch.ones(1, 2, 1, 3)
+    c.write(k, 2 * k)
+    assert c.len == 0 and c.k[0, 0, 0, 0] == 1 and c.v[0, 1, 0, 2] == 2
+    c.advance()
+    assert c.len == 1 and c.positions(1).tolist() == [1]
+
+
+def test_apply_lora_to_a_module(tmp_path):
+    import os
+    import torch
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.io import mim
+    nn.manual_seed(0)
+    net = nn.Sequential(nn.Linear(4, 6), nn.ReLU(), nn.Linear(6, 2))
+    x = T.from_torch(torch.randn(3, 4))
+    base = net(x).data().clone()
+    a, b = torch.randn(2, 4) * 0.1, torch.randn(6, 2) * 0.1
+    p = os.path.join(tmp_path, "ad.mim")
+    mim.write_tensors(p, {"layers.0.lora_a": a, "layers.0.lora_b": b},
+                      metadata={"adapter.type": "lora", "adapter.lora.rank": 2, "adapter.lora.alpha": 4.0, "adapter.base": "net"})
+    ad = mim.open(p)
+    assert mim.lora_info(ad) == {"rank": 2, "alpha": 4.0, "base": "net", "targets": ["layers.0"]}
+    assert mim.apply_lora(net, ad) == 1
+    w = net.layers[0].base.weight._data
+    want = torch.relu(x.data() @ (w + 2.0 * b @ a).t() + net.layers[0].base.bias._data) @ net.layers[2].weight._data.t() + net.layers[2].bias._data
+    assert torch.allclose(net(x).data(), want, atol=1e-5) and not torch.allclose(want, base)
