@@ -24,8 +24,7 @@
 
 namespace mimir {
 
-constexpr int kAttThreads = 192;      // backward kernels: TMA warp, MMA warp, 4 softmax warps
-constexpr int kAttFwdThreads = 320;   // forward: TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quadrant)
+constexpr int kAttFwdThreads = 320;   // every kernel here: TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quadrant)
 constexpr int kTile = 128;            // query rows and key rows per tile
 constexpr int kChunkBytes = 128 * 128;  // 128 rows x 64 bf16
 
@@ -109,6 +108,28 @@ __device__ __forceinline__ bool pair_sync(volatile int* mine, volatile int* thei
   }
   ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
   return ok;
+}
+
+// Half-tile forms used by the backward kernels: `hh` selects rows [64 hh, 64 hh + 64) of the B tile.
+// S_half[128 x 64] = A[128 x D] * B_half[64 x D]^T
+template <int D>
+__device__ __forceinline__ void mma_scores_half(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, int hh) {
+  constexpr uint32_t idesc = make_idesc_bf16(128, 64, false, false);
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int chunk = ks / 4, kk = ks % 4;
+    umma_ss(d_tmem, kdesc(a_addr + chunk * kChunkBytes, kk), kdesc(b_addr + chunk * kChunkBytes + hh * 8192, kk), idesc,
+            ks > 0 ? 1u : 0u);
+  }
+}
+// Acc[128 x D] (+)= P_half[128 x 64] (bf16 in TMEM) * Bmn_half[64 x D]
+template <int D>
+__device__ __forceinline__ void mma_from_tmem_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t b_addr, int hh,
+                                                   bool accumulate) {
+  constexpr uint32_t idesc = make_idesc_bf16(128, D, false, true);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks)
+    umma_ts(d_tmem, p_tmem + ks * 8, mndesc(b_addr, hh * 4 + ks), idesc, (accumulate || ks > 0) ? 1u : 0u);
 }
 
 // ---------------------------------------------------------------------------
@@ -405,9 +426,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
   uint64_t* x_full = bars;
   uint64_t* y_full = x_full + 1;
   uint64_t* y_empty = y_full + NST;
-  uint64_t* s_full = y_empty + NST;
-  uint64_t* p_ready = s_full + 1;
-  uint64_t* acc_full = p_ready + 1;
+  uint64_t* s_full = y_empty + NST;   // [2]: one per score / dP half-tile buffer
+  uint64_t* p_ready = s_full + 2;     // [2]
+  uint64_t* acc_full = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ int xseq[2][4];   // [half][quadrant]: rendezvous counters of the two warps sharing a lane quadrant
@@ -443,8 +464,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&y_full[s], 1); mbar_init(&y_empty[s], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_ready, 8);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); }
     mbar_init(acc_full, 1);
     for (int i = 0; i < 8; ++i) (&xseq[0][0])[i] = 0;
     *abort_flag = 0;
@@ -455,7 +475,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tA0 = tmem + 256, tA1 = tmem + 256 + D;
+  // two half-tile buffers (64 score columns + 64 dP columns each) at 0 and 128, accumulators above:
+  // the MMAs of half-tile j+1 run while the softmax warps work on half-tile j
+  const uint32_t tBuf = tmem, tA0 = tmem + 256, tA1 = tmem + 256 + D;
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
@@ -477,31 +499,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
     if (lane == 0 && n_iter > 0) {
       bool ok = mbar_wait(x_full, 0, abort_flag, err);
       const uint32_t aX0 = smem_u32(sX0), aX1 = smem_u32(sX1);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int s = it % NST;
+      const int n_half = 2 * n_iter;
+      auto issue_scores = [&](int j) -> bool {
+        const int it = j >> 1, hh = j & 1, s = it % NST;
         const uint32_t aY0 = smem_u32(sY + (s * 2) * TB), aY1 = aY0 + TB;
-        if (!(ok = mbar_wait(&y_full[s], (it / NST) & 1, abort_flag, err))) break;
+        if (hh == 0 && !mbar_wait(&y_full[s], (it / NST) & 1, abort_flag, err)) return false;
         tc_fence_after();
-        mma_scores<D>(tS, aX0, aY0);
-        mma_scores<D>(tDP, aX1, aY1);
-        umma_commit(s_full);
-        if (!(ok = mbar_wait(p_ready, it & 1, abort_flag, err))) break;
+        const uint32_t tb = tBuf + (j & 1) * 128;
+        mma_scores_half<D>(tb, aX0, aY0, hh);
+        mma_scores_half<D>(tb + 64, aX1, aY1, hh);
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok && n_half > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_half && ok; ++j) {
+        if (j + 1 < n_half && !(ok = issue_scores(j + 1))) break;   // overlaps the softmax of half-tile j
+        const int it = j >> 1, hh = j & 1, s = it % NST;
+        const uint32_t aY0 = smem_u32(sY + (s * 2) * TB), aY1 = aY0 + TB;
+        const uint32_t tb = tBuf + (j & 1) * 128;
+        if (!(ok = mbar_wait(&p_ready[j & 1], (j >> 1) & 1, abort_flag, err))) break;
         tc_fence_after();
         if (MODE == 0) {
-          mma_from_tmem<D>(tA0, tS, aY1, it > 0);   // dV += P^T dO
-          mma_from_tmem<D>(tA1, tDP, aY0, it > 0);  // dK += dS^T Q
+          mma_from_tmem_half<D>(tA0, tb, aY1, hh, j > 0);        // dV += P^T dO
+          mma_from_tmem_half<D>(tA1, tb + 64, aY0, hh, j > 0);   // dK += dS^T Q
         } else {
-          mma_from_tmem<D>(tA0, tDP, aY0, it > 0);  // dQ += dS K
+          mma_from_tmem_half<D>(tA0, tb + 64, aY0, hh, j > 0);   // dQ += dS K
         }
-        umma_commit(&y_empty[s]);
+        if (hh == 1) umma_commit(&y_empty[s]);
       }
       if (ok) umma_commit(acc_full);
     }
   } else {
-    // Two warps per TMEM lane quadrant: `half` 0 handles columns 0..63 of the score / dP tiles and
-    // the first half of the accumulator columns in the epilogue, `half` 1 the rest.  Both read their
-    // columns into registers, meet (bounded), and only then write P / dS over the score buffers,
-    // whose bf16 columns overlap the partner's unread fp32 columns.
+    // Two warps per TMEM lane quadrant.  A 128-column inner tile is processed as two 64-column
+    // half-tiles in alternating TMEM buffers (the MMAs of one half run under the softmax of the
+    // other); of a half-tile, `half` 0 takes columns 0..31 and `half` 1 columns 32..63, and in the
+    // epilogue the two take alternate 32-column chunks of the accumulators.  Both read their columns
+    // into registers, meet (bounded), and only then write P / dS over the score / dP buffers, whose
+    // bf16 columns overlap the partner's unread fp32 columns.
     const int quad = warp & 3, half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // row inside the owned tile
     const int x_pos = x0 + r;
@@ -516,11 +550,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
       my_dsum = live ? Dsum[idx] : 0.f;
     }
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int j = 0; j < 2 * n_iter && ok; ++j) {
+      const int it = j >> 1, hh = j & 1;
       const int g = it / n_inner, yt = y_begin + it % n_inner;
       const int y0 = yt * kTile;
       float* vbuf = vec + ((it & 1) * 8 + (warp - 2)) * 256;
-      if (MODE == 0) {
+      if (MODE == 0 && hh == 0) {
         // each warp stages its own copy of this query tile's logsumexp and Dsum vectors
         const int hq = hx * group + g;
 #pragma unroll
@@ -533,7 +568,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
         }
         __syncwarp();
       }
-      if (!(ok = mbar_wait(s_full, it & 1, abort_flag, err))) break;
+      if (!(ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, err))) break;
       tc_fence_after();
       // visibility of column c (position y0 + c) for this thread's row
       //   MODE 0: row = key, column = query: visible iff key <= query + offset
@@ -548,41 +583,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX0, const __grid_constant_
         if (p.causal) c_hi = min(c_hi, x_pos + p.offset - y0 + 1);
       }
       if (!row_live) c_hi = 0;
-      uint32_t rs[2][32], rd[2][32];
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        tmem_ld32(tS + lane_base + (half * 2 + cc) * 32, rs[cc]);
-        tmem_ld32(tDP + lane_base + (half * 2 + cc) * 32, rd[cc]);
-      }
+      // this warp's 32 columns of the half-tile: tile columns [cbase, cbase + 32)
+      const int cbase = hh * 64 + half * 32;
+      const uint32_t tb = tBuf + (j & 1) * 128 + lane_base;
+      uint32_t rs[32], rd[32], pk[16], dk[16];
+      tmem_ld32(tb + half * 32, rs);
+      tmem_ld32(tb + 64 + half * 32, rd);
       tmem_ld_wait();
-      if (!(ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], it + 1, lane, abort_flag, err))) break;
+      // P / dS (bf16 pairs) go over columns 0..31 of the score / dP buffers, which the partner warp reads
+      if (!(ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], j + 1, lane, abort_flag, err))) break;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t pk[16], dk[16];
+      for (int e = 0; e < 32; e += 2) {
+        float pv[2], dv[2];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            const float lse2 = MODE == 0 ? vbuf[col] : my_lse2;
-            const float ds = MODE == 0 ? vbuf[128 + col] : my_dsum;
-            float pr = ex2(__uint_as_float(rs[cc][e + u]) * sl2 - lse2);
-            if (col < c_lo || col >= c_hi) pr = 0.f;
-            pv[u] = pr;
-            dv[u] = pr * (__uint_as_float(rd[cc][e + u]) - ds);
-          }
-          pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
+        for (int u = 0; u < 2; ++u) {
+          const int col = cbase + e + u;
+          const float lse2 = MODE == 0 ? vbuf[col] : my_lse2;
+          const float ds = MODE == 0 ? vbuf[128 + col] : my_dsum;
+          float pr = ex2(__uint_as_float(rs[e + u]) * sl2 - lse2);
+          if (col < c_lo || col >= c_hi) pr = 0.f;
+          pv[u] = pr;
+          dv[u] = pr * (__uint_as_float(rd[e + u]) - ds);
         }
-        if (MODE == 0) tmem_st16(tS + lane_base + c * 16, pk);
-        tmem_st16(tDP + lane_base + c * 16, dk);
+        pk[e >> 1] = pack_bf16x2(pv[0], pv[1]);
+        dk[e >> 1] = pack_bf16x2(dv[0], dv[1]);
       }
+      if (MODE == 0) tmem_st16(tb + half * 16, pk);
+      tmem_st16(tb + 64 + half * 16, dk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     }
     if (ok && n_iter > 0 && mbar_wait(acc_full, 0, abort_flag, err)) {
       tc_fence_after();
