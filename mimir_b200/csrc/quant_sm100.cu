@@ -532,6 +532,42 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ kv, int 
   vc[dst] = __float2half(__bfloat162float(kv[static_cast<size_t>(b) * ld + vcol + h * D + d]));
 }
 
+// Decode-step rotary embedding and cache write in one launch: the (interleaved) pairs of the Hq query
+// heads and Hkv key heads of qkv [B][(Hq + 2 Hkv) D] are rotated in place by the row's position, the
+// rotated keys and the values go to the fp16 cache at the write position.  The arithmetic is the
+// two-kernel sequence's: rotate in fp32, round to bf16 (what attention reads for q), bf16 -> fp16 for the cache.
+__global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ pos_rows,
+                                     const float* __restrict__ freqs, __half* __restrict__ kc, __half* __restrict__ vc,
+                                     int B, int Hq, int Hkv, int D, int cap, const int* __restrict__ pos_ptr) {
+  const int half = D / 2;
+  const int n_rope = B * (Hq + Hkv) * half, n_v = B * Hkv * half;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int wpos = *pos_ptr;
+  const bool store = wpos >= 0 && wpos < cap;
+  if (idx < n_rope) {
+    const int i = idx % half, h = (idx / half) % (Hq + Hkv), b = idx / (half * (Hq + Hkv));
+    float sn, cs;
+    sincosf(static_cast<float>(pos_rows[b]) * freqs[i], &sn, &cs);
+    __nv_bfloat16* base = qkv + static_cast<size_t>(b) * ld + h * D;
+    const float x0 = __bfloat162float(base[2 * i]), x1 = __bfloat162float(base[2 * i + 1]);
+    const __nv_bfloat16 r0 = __float2bfloat16_rn(x0 * cs - x1 * sn), r1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
+    base[2 * i] = r0;
+    base[2 * i + 1] = r1;
+    if (h >= Hq && store) {
+      const size_t dst = ((static_cast<size_t>(b) * Hkv + (h - Hq)) * cap + wpos) * D + 2 * i;
+      kc[dst] = __float2half(__bfloat162float(r0));
+      kc[dst + 1] = __float2half(__bfloat162float(r1));
+    }
+  } else if (idx < n_rope + n_v && store) {
+    const int j = idx - n_rope;
+    const int i = j % half, h = (j / half) % Hkv, b = j / (half * Hkv);
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(b) * ld + (Hq + Hkv + h) * D + 2 * i;
+    const size_t dst = ((static_cast<size_t>(b) * Hkv + h) * cap + wpos) * D + 2 * i;
+    vc[dst] = __float2half(__bfloat162float(src[0]));
+    vc[dst + 1] = __float2half(__bfloat162float(src[1]));
+  }
+}
+
 // fp32 [rows][N] -> bf16
 __global__ void f32_to_bf16_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -674,6 +710,16 @@ MIMIR_API int mimir_kv_cache_write(const void* kv, int ld, int kcol, int vcol, v
   kv_cache_write_kernel<<<ceil_div(n, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(kv), ld, kcol, vcol,
                                                           static_cast<__half*>(kc), static_cast<__half*>(vc), B, Hkv,
                                                           D, cap, pos_dev);
+  count_launch();
+  return 0;
+}
+MIMIR_API int mimir_rope_kv_write(void* qkv, int ld, const int* pos_rows, const float* freqs, void* kc, void* vc, int B,
+                                  int Hq, int Hkv, int D, int cap, const int* pos_dev, cudaStream_t st) {
+  if (D % 2) return refuse("rope: head dim must be even");
+  const int n = B * (Hq + 2 * Hkv) * (D / 2);
+  rope_kv_write_kernel<<<ceil_div(n, 256), 256, 0, st>>>(static_cast<__nv_bfloat16*>(qkv), ld, pos_rows, freqs,
+                                                         static_cast<__half*>(kc), static_cast<__half*>(vc), B, Hq, Hkv, D,
+                                                         cap, pos_dev);
   count_launch();
   return 0;
 }

@@ -189,10 +189,9 @@ class TPDecoder:
     def _attention_step(self, l: int, scale: float):
         cfg, D, B = self.cfg, self.cfg.head_dim, self.B
         lib = Q._L()
-        K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
-        _native.check(lib.mimir_kv_cache_write(ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D,
-                                               ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hk, D, self.cap,
-                                               ptr(self.pos), stream_ptr()), "kv_write")
+        _native.check(lib.mimir_rope_kv_write(ptr(self.qkv), self.qkv_n, ptr(self.pos_rows), ptr(self.freqs),
+                                              ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hq, self.Hk, D, self.cap,
+                                              ptr(self.pos), stream_ptr()), "rope_kv_write")
         _native.check(lib.mimir_attn_decode(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.att), B,
                                             self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n,
                                             ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits, stream_ptr()),
@@ -222,14 +221,7 @@ class TPDecoder:
         for l, w in enumerate(self.layers):
             Q.quantize_act(self.h, self.xq, self.xs, d, mode=1, gamma=w["attn_norm"], eps=cfg.eps)
             Q.q4_gemv(w["qkv"], self.xq, self.xs, self.qkv)
-            K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
-            _native.check(lib.mimir_kv_cache_write(ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D,
-                                                   ptr(self.kc[l]), ptr(self.vc[l]), B, self.Hk, D, self.cap,
-                                                   ptr(self.pos), stream_ptr()), "kv_write")
-            _native.check(lib.mimir_attn_decode(ptr(self.qkv), ptr(self.kc[l]), ptr(self.vc[l]), ptr(self.att), B,
-                                                self.Hq, self.Hk, D, self.cap, ptr(self.len), scale, self.qkv_n,
-                                                ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits, stream_ptr()),
-                          "attn_decode")
+            self._attention_step(l, scale)
             Q.quantize_act(self.att, self.xq, self.xs, self.Hq * D, mode=0)
             self._gemv_allreduce(w["o"], self.Hq * D, self.h, self.h1, 0)
             Q.quantize_act(self.h1, self.xq, self.xs, d, mode=1, gamma=w["ffn_norm"], eps=cfg.eps)
@@ -381,10 +373,9 @@ class TPDecoder:
         full = self.logits_all.view(torch.float32).view(self.world, self.B, self.Vl)
         common = {
             "embedding": lambda: K.embedding_fwd(self.tokens, self.embed, None, self.h, 1),
-            "rope": lambda: K.rope_(self.qkv, self.pos_rows, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True),
-            "kv_write": lambda: _native.check(lib.mimir_kv_cache_write(
-                ptr(self.qkv), self.qkv_n, self.Hq * D, (self.Hq + self.Hk) * D, ptr(self.kc[0]), ptr(self.vc[0]), B,
-                self.Hk, D, self.cap, ptr(self.pos), stream_ptr()), "kv_write"),
+            "rope_kv_write": lambda: _native.check(lib.mimir_rope_kv_write(
+                ptr(self.qkv), self.qkv_n, ptr(self.pos_rows), ptr(self.freqs), ptr(self.kc[0]), ptr(self.vc[0]), B,
+                self.Hq, self.Hk, D, self.cap, ptr(self.pos), stream_ptr()), "rope_kv_write"),
             "attn_decode": lambda: _native.check(lib.mimir_attn_decode(
                 ptr(self.qkv), ptr(self.kc[0]), ptr(self.vc[0]), ptr(self.att), B, self.Hq, self.Hk, D, self.cap,
                 ptr(self.len), scale, self.qkv_n, ptr(self.attn_ws), ptr(self.attn_cnt), self.attn_splits,

@@ -226,6 +226,7 @@ class LlamaEngine:
             self.dtmp = flat[(2 * L + 1) * n:].view(M, C)
             self.rs_act = ReduceScatterGemm(M, C, self.rank, self.world, self.group)
             self.shard = torch.empty(M // self.world, C, **bf)
+            self.head_dx = torch.empty(M // self.world, C, **bf)
             self.ag_sig = SymmetricBuffer(1024 * 4, self.rank, self.world, self.group)
             self.ag_state = torch.zeros(4, dtype=torch.int32, device=dev)
         else:
@@ -241,8 +242,10 @@ class LlamaEngine:
         self.act = torch.empty(L, M, F, **bf)
         self.rstd = torch.empty(2 * L + 1, M, **f32)
         self.hf = torch.empty(M, C, **bf)
-        self.logits = torch.empty(M, cfg.padded_vocab, **bf)
-        self.loss_rows = torch.empty(M, **f32)
+        # tensor parallel: each rank computes the logits and the loss of its M / tp rows only
+        self.head_rows = M // self.world if self.mode == "tp" else M
+        self.logits = torch.empty(self.head_rows, cfg.padded_vocab, **bf)
+        self.loss_rows = torch.empty(self.head_rows, **f32)
         self.loss = torch.zeros(1, **f32)
         self.dx = torch.empty(M, C, **bf)
         self.dx2 = torch.empty(M, C, **bf)
@@ -322,21 +325,34 @@ class LlamaEngine:
             K.swiglu_fwd(self.gu[l], self.act[l])
             self._row_parallel_fwd(self.act[l], n + "wd", self.xmid[l], self.x[l + 1])
         K.rmsnorm_fwd(self.x[L], p["out_norm"], self.hf, self.rstd[2 * L], cfg.eps)
-        self._fwd(self.hf, "lm_head", self.logits)
+        self._fwd(self._head_slice(self.hf), "lm_head", self.logits)
+
+    def _head_slice(self, t):
+        """Rows of a [M, ...] tensor this rank's output head works on (all of them unless tensor parallel)."""
+        if self.mode != "tp":
+            return t
+        return t[self.rank * self.head_rows: (self.rank + 1) * self.head_rows]
 
     def loss_and_dlogits(self, grad_scale: float = 1.0) -> None:
         """Mean cross-entropy of this rank's tokens into ``self.loss``; logits become the gradient in
         place, scaled by 1 / (tokens on all ranks) so that the summed gradients are the global mean's."""
-        K.cross_entropy(self.logits, self.targets, self.loss_rows, self.logits, self.loss, self.cfg.vocab,
+        K.cross_entropy(self.logits, self._head_slice(self.targets), self.loss_rows, self.logits, self.loss, self.cfg.vocab,
                         grad_scale / (self.M * (self.world if self.mode == "fsdp" else 1) * self.dp_world), 1.0 / self.M)
+        if self.mode == "tp" and self.world > 1:
+            torch.distributed.all_reduce(self.loss, group=self.group)     # the ranks hold partial sums over their rows
 
     # -------------------------------------------------------------------- backward
     def backward(self, on_bucket_ready=None) -> None:
         cfg, p, g, L = self.cfg, self.p, self.g, self.cfg.n_layer
         Hq, Hk, D = self.Hq, self.Hk, cfg.head_dim
         dlogits = self.logits
-        self._wgrad(dlogits, self.hf, "lm_head")
-        self._dgrad(dlogits, "lm_head", self.dtmp)
+        self._wgrad(dlogits, self._head_slice(self.hf), "lm_head")
+        if self.mode == "tp" and self.world > 1:
+            torch.distributed.all_reduce(g["lm_head"], group=self.group)  # each rank saw M / tp of the rows
+            self._dgrad(dlogits, "lm_head", self.head_dx)
+            self._allgather_rows(self.head_dx, self.dtmp)
+        else:
+            self._dgrad(dlogits, "lm_head", self.dtmp)
         K.rmsnorm_bwd(self.dtmp, self.x[L], p["out_norm"], self.rstd[2 * L], None, self.dx, g["out_norm"], self.norm_scratch)
         dx, dx2 = self.dx, self.dx2
         for l in reversed(range(L)):

@@ -27,6 +27,7 @@ def _L():
             "mimir_attn_decode": [P, P, P, P, I, I, I, I, I, P, F, I, P, P, I, P],
             "mimir_kv_cache_write": [P, I, I, I, P, P, I, I, I, I, P, P],
             "mimir_f32_to_bf16": [P, P, L, P],
+            "mimir_rope_kv_write": [P, I, P, P, P, P, I, I, I, I, I, P, P],
             "mimir_q4_planar_to_bf16": [P, P, P, L, P],
             "mimir_peer_allgather": [P, PP, PP, P, P, L, I, I, I, P],
             "mimir_q4_planar_to_tiled": [P, P, P, I, I, P],

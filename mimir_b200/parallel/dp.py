@@ -78,6 +78,7 @@ class FusedDataParallel:
         self._params_arr = self.param_buf.ptr_array()
         self._sig_arr = self.sig_buf.ptr_array()
         self._bucket_index = {n: i for i, n in enumerate(self.buckets)}
+        self._last_bucket = engine.layout.buckets[0][0]   # backward finishes the buckets in reverse layout order
         if w > 1:
             dist.barrier(group=self.group)
         torch.cuda.synchronize()
@@ -96,11 +97,15 @@ class FusedDataParallel:
         b = self.buckets[name]
         e = self.engine
         lib = _native.lib()
+        # buckets that finish while backward still runs get a small grid (they share the SMs with the
+        # GEMMs); the last bucket of the step has the GPU to itself and is pure memory traffic
+        last = name == self._last_bucket
+        nblocks = 2 * torch.cuda.get_device_properties(e.device).multi_processor_count if last else self.nblocks
         rc = lib.mimir_dp_bucket(self._grads_arr, self._params_arr, self._sig_arr, ptr(self.master),
                                  ptr(self.exp_avg), ptr(self.exp_avg_sq), ptr(e.hyper), ptr(self.epoch),
                                  self.block_counters[self._bucket_index[name]:].data_ptr(), b["start"],
                                  b["count"], b["decay_n"], b["shard_off"], betas[0], betas[1], eps, wd,
-                                 self.rank, self.world, b["slot_ready"], b["slot_done"], self.nblocks,
+                                 self.rank, self.world, b["slot_ready"], b["slot_done"], nblocks,
                                  self.comm_stream.cuda_stream)
         _native.check(rc, "dp_bucket")
 

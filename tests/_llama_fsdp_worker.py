@@ -88,6 +88,8 @@ def tensor_parallel(rank, world, cfg, B, T, tok, tgt):
     grad_cos = min(grad_cos, torch.nn.functional.cosine_similarity(a2, b2, dim=0).item())
     a3, b3 = tp.g["wte"].float().flatten(), single.g["wte"].float().flatten()
     grad_cos = min(grad_cos, torch.nn.functional.cosine_similarity(a3, b3, dim=0).item())
+    a4, b4 = tp.g["lm_head"].float().flatten(), single.g["lm_head"].float().flatten()   # summed over the ranks' row shares
+    grad_cos = min(grad_cos, torch.nn.functional.cosine_similarity(a4, b4, dim=0).item())
     loss_tp, loss_single = tp.loss.item(), single.loss.item()
     tr = FusedTrainer(tp, lr=3e-3, weight_decay=0.0, use_graph=False)
     trs = FusedTrainer(single, lr=3e-3, weight_decay=0.0, use_graph=False)
