@@ -182,22 +182,22 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 
 // Sums `nparts` partial rows [nparts][width] into bf16 (optionally accumulating).
 // Sums `nparts` partial rows [nparts][width] (fp32) column-wise.  Block = 32
-// columns x 8 row lanes.  Columns [0, split) go to out0, [split, width) to out1
+// columns x 32 row lanes.  Columns [0, split) go to out0, [split, width) to out1
 // (bf16, optionally accumulating), which finishes dgamma and dbeta in one launch.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 reduce_partials_kernel(const float* __restrict__ partial, int nparts, int width, int split,
                        __nv_bfloat16* __restrict__ out0, __nv_bfloat16* __restrict__ out1, int accumulate) {
-  __shared__ float red[8][33];
+  __shared__ float red[32][33];
   const int cl = threadIdx.x & 31, rl = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
   float s = 0.f;
   if (c < width)
-    for (int p = rl; p < nparts; p += 8) s += partial[static_cast<size_t>(p) * width + c];
+    for (int p = rl; p < nparts; p += 32) s += partial[static_cast<size_t>(p) * width + c];
   red[rl][cl] = s;
   __syncthreads();
   if (rl == 0 && c < width) {
 #pragma unroll
-    for (int r = 1; r < 8; ++r) s += red[r][cl];
+    for (int r = 1; r < 32; ++r) s += red[r][cl];
     __nv_bfloat16* o = c < split ? out0 + c : out1 + (c - split);
     if (c >= split && !out1) return;
     if (accumulate) s += __bfloat162float(*o);
@@ -504,7 +504,7 @@ MIMIR_API int mimir_rmsnorm_fwd(const void* x, const void* gamma, void* y, float
 }
 
 // Number of blocks (and rows of `partial`) the backward kernels use.
-MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 8; }
+MIMIR_API int mimir_norm_bwd_blocks() { return sm_count() * 4; }
 
 // dx = dres + LN'(dy); dgamma/dbeta (bf16) written, or accumulated when accumulate != 0.
 // partial: fp32 scratch of mimir_norm_bwd_blocks() * 2 * C floats.
@@ -516,7 +516,7 @@ MIMIR_API int mimir_layernorm_bwd(const void* dy, const void* x, const void* gam
   int nb = mimir_norm_bwd_blocks();
   if (norm_bwd_dispatch<false>(dy, x, gamma, mean, rstd, dres, dx, partial, nb, rows, C, &nb, st)) return -1;
   // partial rows are [dgamma (C) | dbeta (C)]
-  reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
+  reduce_partials_kernel<<<ceil_div(2 * C, 32), 1024, 0, st>>>(partial, nb, 2 * C, C,
                                                                static_cast<__nv_bfloat16*>(dgamma),
                                                                static_cast<__nv_bfloat16*>(dbeta), accumulate);
   count_launch();
@@ -528,7 +528,7 @@ MIMIR_API int mimir_rmsnorm_bwd(const void* dy, const void* x, const void* gamma
   if (C % 8) return refuse("rmsnorm: C must be a multiple of 8");
   int nb = mimir_norm_bwd_blocks();
   if (norm_bwd_dispatch<true>(dy, x, gamma, nullptr, rstd, dres, dx, partial, nb, rows, C, &nb, st)) return -1;
-  reduce_partials_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(partial, nb, 2 * C, C,
+  reduce_partials_kernel<<<ceil_div(2 * C, 32), 1024, 0, st>>>(partial, nb, 2 * C, C,
                                                                static_cast<__nv_bfloat16*>(dgamma), nullptr,
                                                                accumulate);
   count_launch();
@@ -543,7 +543,7 @@ MIMIR_API int mimir_colsum(const void* x, int rows, int N, int ld, void* out, fl
   dim3 grid(ceil_div(N, 256), parts);
   colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld,
                                               partial);
-  reduce_partials_kernel<<<ceil_div(N, 32), 256, 0, st>>>(partial, parts, N, N,
+  reduce_partials_kernel<<<ceil_div(N, 32), 1024, 0, st>>>(partial, parts, N, N,
                                                           static_cast<__nv_bfloat16*>(out), nullptr,
                                                           accumulate);
   count_launch(2);
@@ -627,7 +627,7 @@ MIMIR_API int mimir_colsum_noalloc(const void* x, int rows, int N, int ld, void*
   const int parts = rows >= 64 * 8 ? 64 : 1;  // same split as mimir_colsum, so results agree bit for bit
   dim3 grid(ceil_div(N, 256), parts);
   colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld, scratch);
-  reduce_partials_kernel<<<ceil_div(N, 32), 256, 0, st>>>(scratch, parts, N, N,
+  reduce_partials_kernel<<<ceil_div(N, 32), 1024, 0, st>>>(scratch, parts, N, N,
                                                           static_cast<__nv_bfloat16*>(out), nullptr,
                                                           accumulate);
   count_launch(2);

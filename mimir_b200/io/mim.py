@@ -153,6 +153,40 @@ class Model:
         raw = self.section_bytes(SECTION_TRAINING)
         return _md.decode(raw) if raw else None
 
+    # -- graph runtime (reference: Model.Run / NewSession / Inputs / Outputs, io/mim/mim.go:164-330)
+    def has_graph(self) -> bool:
+        return self.section_bytes(SECTION_GRAPH) is not None
+
+    def program(self):
+        """The file's graph as a runnable program (parsed once)."""
+        if getattr(self, "_program", None) is None:
+            from . import graph as _g, graph_run as _gr
+            raw = self.section_bytes(SECTION_GRAPH)
+            if raw is None:
+                raise _g.NoGraph("the file has no graph section")
+            self._program = _gr.Program(_g.Graph.decode(raw), self.tensor)
+        return self._program
+
+    def graph(self):
+        return self.program().g
+
+    @property
+    def inputs(self):
+        """(name, dtype, dims) of every input of the main program."""
+        return [(v.name, v.dtype, list(v.dims)) for v in self.program().inputs]
+
+    @property
+    def outputs(self):
+        return [(n, v.dtype, list(v.dims)) for n, v in self.program().outputs]
+
+    def run(self, inputs: dict, cancel=None) -> dict:
+        """Computes the outputs from the inputs, keyed by name, on fresh variables."""
+        return self.program().run(inputs, cancel=cancel)
+
+    def new_session(self):
+        """A session whose variables start from their initial values, independent of other sessions."""
+        return self.program().new_session()
+
     def verify(self) -> bool:
         """Re-hashes every section against the SHA-256 in the index."""
         return _lib().mimir_mim_verify(self._h) == 0

@@ -223,8 +223,7 @@ class LayerNorm(Module):
         self.eps, self.dim = eps, dim
 
     def forward(self, x):
-        return T.core._node(lambda v, w, b: torch.nn.functional.layer_norm(v, (self.dim,), w, b, self.eps),
-                            (x, self.weight.value(), self.bias.value()), {}, "layer_norm")
+        return T.layer_norm(x, self.weight.value(), self.bias.value(), self.eps)
 
 
 class RMSNorm(Module):
@@ -235,10 +234,7 @@ class RMSNorm(Module):
         self.eps = eps
 
     def forward(self, x):
-        def run(v, w):
-            n = v.float() * torch.rsqrt(v.float().pow(2).mean(-1, keepdim=True) + self.eps)
-            return n.to(v.dtype) * w
-        return T.core._node(run, (x, self.weight.value()), {}, "rms_norm")
+        return T.rms_norm(x, self.weight.value(), self.eps)
 
 
 class GroupNorm(Module):

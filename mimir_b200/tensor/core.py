@@ -875,6 +875,28 @@ def upsample_nearest(x, scale):
     return _node(lambda v: torch.nn.functional.interpolate(v, scale_factor=scale, mode="nearest"), (x,), {}, "upsample")
 
 
+def layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
+    """Normalises over the last axis; ``weight`` / ``bias`` of that length are optional."""
+    n = x.shape[-1] if x.shape else 1
+    extra = tuple(t for t in (weight, bias) if t is not None)
+    hw, hb = weight is not None, bias is not None
+
+    def run(v, *wb):
+        w = wb[0] if hw else None
+        b = wb[1 if hw else 0] if hb else None
+        return torch.nn.functional.layer_norm(v, (n,), w, b, eps)
+    return _node(run, (x, *extra), {}, "layer_norm")
+
+
+def rms_norm(x, weight=None, eps: float = 1e-6):
+    """Root-mean-square normalisation over the last axis in fp32, rounded to the input dtype, then
+    scaled by ``weight``."""
+    def run(v, *w):
+        y = (v.float() * torch.rsqrt(v.float().pow(2).mean(-1, keepdim=True) + eps)).to(v.dtype)
+        return y * w[0] if w else y
+    return _node(run, (x,) + ((weight,) if weight is not None else ()), {}, "rms_norm")
+
+
 def from_bytes(data, shape, dtype=torch.float32, device: Device | None = None) -> Tensor:
     """A tensor over raw little-endian bytes (bytes, bytearray, memoryview, mmap) without copying when
     the buffer is writable or the target is another device (tensor.FromBytes, tensor/bytes.go)."""
@@ -923,4 +945,63 @@ def _bind_methods():
             setattr(Tensor, meth, g[fn])
 
 
+# ------------------------------------------------------------------ op tracing
+# While a trace is active every OUTERMOST call of a public op of this module is reported as
+# (name, args, kwargs, result): what the graph exporter translates.  Ops that an op calls inside
+# are not reported.  Inactive, the wrapper costs one global read per call.
+_TRACE = None
+_TRACE_DEPTH = 0
+_NOT_OPS = {"CPU", "GPU", "devices", "auto", "default_device", "set_default_device", "from_torch", "tensor",
+            "evaluate", "realize", "from_bytes", "from_bytes_func", "realize_into", "trace_ops"}
+
+
+def _traced(name, f):
+    import functools
+
+    @functools.wraps(f)
+    def g(*a, **k):
+        global _TRACE_DEPTH
+        tr = _TRACE
+        if tr is None:
+            return f(*a, **k)
+        _TRACE_DEPTH += 1
+        try:
+            out = f(*a, **k)
+        finally:
+            _TRACE_DEPTH -= 1
+        if _TRACE_DEPTH == 0:
+            tr(name, a, k, out)
+        return out
+    g._untraced = f
+    return g
+
+
+def _install_trace_hooks():
+    import types
+    g = globals()
+    for name, f in list(g.items()):
+        if name.startswith("_") or name in _NOT_OPS or not isinstance(f, types.FunctionType):
+            continue
+        g[name] = _traced(name, f)
+
+
+class trace_ops:
+    """Context manager: ``with trace_ops(callback):`` reports every outermost op call to ``callback``."""
+
+    def __init__(self, callback):
+        self.cb = callback
+
+    def __enter__(self):
+        global _TRACE, _TRACE_DEPTH
+        if _TRACE is not None:
+            raise RuntimeError("an op trace is already active")
+        _TRACE, _TRACE_DEPTH = self.cb, 0
+        return self
+
+    def __exit__(self, *a):
+        global _TRACE
+        _TRACE = None
+
+
+_install_trace_hooks()
 _bind_methods()
