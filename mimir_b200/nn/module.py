@@ -261,19 +261,41 @@ class _BatchNorm(Module):
         self.eps, self.momentum = eps, momentum
 
     def forward(self, x):
-        training = self.training
-        rm, rv = self.running_mean, self.running_var
-
-        def run(v, w, b):
-            if v.device.type == "meta":
-                return torch.empty_like(v)
-            mean = rm._data.to(v.device)
-            var = rv._data.to(v.device)
-            out = torch.nn.functional.batch_norm(v, mean, var, w, b, training, self.momentum, self.eps)
-            if training:
-                rm._data, rv._data = mean, var
-            return out
-        return T.core._node(run, (x, self.weight.value(), self.bias.value()), {}, "batch_norm")
+        """Training: batch statistics normalise, and the new running statistics (momentum average of
+        the old ones and the batch's mean / unbiased variance) are set on the buffers as recipes
+        that the output carries as effects, so a backward pass computes them in its own schedule
+        (nn/layers.go:196-243).  Evaluation: the running statistics normalise."""
+        shape = tuple(x.shape)
+        if len(shape) < 2:
+            return T.core._error_tensor(T.ErrShape(f"batch norm of {shape}, want rank 2 or more"))
+        c = shape[1]
+        axes = tuple(d for d in range(len(shape)) if d != 1)
+        bc = tuple(c if d == 1 else 1 for d in range(len(shape)))
+        per = lambda t: T.reshape(t, bc)
+        effects = ()
+        if self.training:
+            n = math.prod(shape) // max(c, 1)
+            if n < 2:
+                return T.core._error_tensor(T.ErrShape(
+                    f"batch norm in training needs more than one value per channel, got {shape}"))
+            xf = T.cast(x, torch.float32) if x.dtype != torch.float32 else x
+            mean = T.mean(xf, dim=axes)
+            d = xf - per(mean)
+            var = T.mean(d * d, dim=axes)
+            y = d / per(T.sqrt(var + self.eps))
+            m = self.momentum
+            new_mean = self.running_mean.value() * (1 - m) + T.detach(mean) * m
+            new_var = self.running_var.value() * (1 - m) + T.detach(var) * (m * n / (n - 1))
+            self.running_mean.set(new_mean)
+            self.running_var.set(new_var)
+            effects = (new_mean, new_var)
+        else:
+            xf = T.cast(x, torch.float32) if x.dtype != torch.float32 else x
+            y = (xf - per(self.running_mean.value())) / per(T.sqrt(self.running_var.value() + self.eps))
+        y = y * per(self.weight.value()) + per(self.bias.value())
+        if y.dtype != x.dtype:
+            y = T.cast(y, x.dtype)
+        return T.with_effects(y, *effects)
 
 
 class BatchNorm1d(_BatchNorm):

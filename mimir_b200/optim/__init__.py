@@ -58,6 +58,8 @@ class Optimizer:
         if self.clip_norm > 0:
             norm = self.global_norm()
             factor *= min(1.0, self.clip_norm / (norm + 1e-6))
+        from ..tensor.autograd import flush_lazy
+        flush_lazy()
         with torch.no_grad():
             for p, st in zip(self.params, self.state):
                 if p._grad is None or not p.trainable:

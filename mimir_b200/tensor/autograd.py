@@ -11,6 +11,8 @@ over the executed graph.  ``grad / vjp / jvp / jacobian / hessian / vmap`` wrap
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from . import core as C
@@ -41,6 +43,10 @@ class Param:
             # gathered value is reduce-scattered back onto the shard (nn/shard.go:74-89)
             return gather(t)
         return t
+
+    def _raw(self) -> torch.Tensor:
+        """The storage as it is, without computing a pending recipe (see ``Buffer``)."""
+        return self._data
 
     def grad(self):
         return None if self._grad is None else C.from_torch(self._grad)
@@ -105,13 +111,56 @@ class Param:
 
 
 class Buffer(Param):
-    """Non-trainable state (running statistics, caches): ``NewBuffer`` in the reference."""
+    """Non-trainable state (running statistics, caches): ``NewBuffer`` in the reference.
+
+    ``set`` accepts a lazy tensor (tensor/autograd.go:929-950): the buffer then holds the recipe and
+    takes the value when it is next read, when a backward pass computes it as an effect, or before
+    any parameter is written in place (``flush_lazy``), so the recipe never reads overwritten
+    memory."""
 
     def __init__(self, value, name: str = ""):
+        self.__dict__["_lazy"] = None
         super().__init__(value, name, trainable=False)
 
+    @property
+    def _data(self):
+        lazy = self.__dict__.get("_lazy")
+        if lazy is not None:
+            self.__dict__["_lazy"] = None
+            _LAZY.discard(self)
+            buf = self.__dict__["_buf"]
+            buf.copy_(lazy.data().to(buf.dtype))
+            self._version += 1
+        return self.__dict__["_buf"]
 
-import weakref
+    @_data.setter
+    def _data(self, v):
+        self.__dict__["_lazy"] = None
+        self.__dict__["_buf"] = v
+
+    def _raw(self) -> torch.Tensor:
+        return self.__dict__["_buf"]
+
+    def set(self, value) -> None:
+        if isinstance(value, C.Tensor) and value._err is None and value._val is None:
+            if tuple(value.shape) != tuple(self.__dict__["_buf"].shape):
+                raise E.ErrShape(f"Param.set: shape {tuple(value.shape)} != {tuple(self.__dict__['_buf'].shape)}")
+            self._data  # noqa: B018 - an older recipe is computed before it is replaced
+            self.__dict__["_lazy"] = value
+            _LAZY.add(self)
+            return
+        super().set(value)
+
+
+_LAZY = weakref.WeakSet()
+
+
+def flush_lazy() -> None:
+    """Computes every buffer that still holds a recipe; called before parameters are written in
+    place, so that a recipe never reads memory a step has overwritten."""
+    for b in list(_LAZY):
+        b._data  # noqa: B018
+
 
 _LEAF_PARAM = weakref.WeakValueDictionary()
 
@@ -130,8 +179,23 @@ def _collect_params(root: C.Tensor) -> dict:
     return out
 
 
+def _collect_effects(root: C.Tensor) -> list:
+    out, seen, stack = [], set(), [root]
+    while stack:
+        t = stack.pop()
+        if id(t) in seen:
+            continue
+        seen.add(id(t))
+        for e in t._effects:
+            if isinstance(e, C.Tensor) and e._val is None and all(e is not o for o in out):
+                out.append(e)
+        stack.extend(a for a in C._flatten(t._args) if isinstance(a, C.Tensor))
+    return out
+
+
 def backward(loss: C.Tensor, effects=()) -> None:
-    """Loss and all parameter gradients in one pass; gradients accumulate in place."""
+    """Loss, all parameter gradients and the effects the loss carries (``with_effects``) in one pass;
+    gradients accumulate in place."""
     if loss._err is not None:
         raise loss._err
     if loss.numel() != 1:
@@ -142,19 +206,23 @@ def backward(loss: C.Tensor, effects=()) -> None:
     trainable = {k: (t, p) for k, (t, p) in leaves.items() if p._trainable}
     if not trainable:
         raise E.ErrNoGrad("the loss depends on no trainable parameter")
+    carried = _collect_effects(loss)
+    for e in carried:
+        for k, v in _collect_params(e).items():
+            leaves.setdefault(k, v)
     from .memory import reserve
     reserve([loss])
     memo, inputs = {}, {}
     for k, (t, p) in leaves.items():
         C._check_leaf(t)
-        v = p._data.detach()
+        v = p._raw().detach()
         if p._trainable:
             if not v.dtype.is_floating_point:
                 raise E.ErrNotDifferentiable(f"parameter {p.name!r} has dtype {v.dtype}")
             v = inputs.setdefault(id(p), v.requires_grad_(True))
         memo[k] = v
     with torch.enable_grad():
-        (out,) = C.evaluate([loss], memo, reuse_cached=False)
+        out, *side = C.evaluate([loss] + carried, memo, reuse_cached=False)
         if not out.requires_grad:
             raise E.ErrNoGrad("the loss is not differentiable with respect to the parameters")
         params = [p for _, (t, p) in trainable.items()]
@@ -169,6 +237,9 @@ def backward(loss: C.Tensor, effects=()) -> None:
         p._data.requires_grad_(False)
     loss._val = out.detach()
     loss._fn, loss._args, loss._kw = None, (), {}
+    for e, v in zip(carried, side):
+        e._val = v.detach()
+        e._fn, e._args, e._kw = None, (), {}
     for e in effects:
         e()
 

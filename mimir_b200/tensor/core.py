@@ -102,7 +102,7 @@ class Tensor:
     """One node of the lazy graph (or a realized leaf)."""
 
     __slots__ = ("_fn", "_args", "_kw", "_val", "_err", "shape", "dtype", "device", "_stale", "_donated",
-                 "_sharding", "_opname", "__weakref__")
+                 "_sharding", "_opname", "_effects", "__weakref__")
 
     def __init__(self, fn=None, args=(), kw=None, val=None, err=None, shape=(), dtype=float32, device=None,
                  opname=""):
@@ -114,6 +114,7 @@ class Tensor:
         self._donated = False
         self._sharding = None
         self._opname = opname
+        self._effects = ()      # tensors a backward pass computes along with the gradients
 
     # ------------------------------------------------------------- properties
     @property
@@ -897,6 +898,28 @@ def rms_norm(x, weight=None, eps: float = 1e-6):
     return _node(run, (x,) + ((weight,) if weight is not None else ()), {}, "rms_norm")
 
 
+def with_effects(x, *effects):
+    """``x`` with the same values and gradients, carrying ``effects``: tensors that ``backward``
+    computes in the same schedule as the gradients whenever it runs on a result computed from the
+    returned tensor (tensor/autograd.go:753-777).  Layers use it for state a training step updates on
+    the side (the running statistics of batch normalisation), so the update costs no extra pass.
+    Gradients and the transformations ignore effects."""
+    for e in effects:
+        if isinstance(e, Tensor) and e._err is not None:
+            return _error_tensor(e._err)
+    if not effects:
+        return x
+    out = _node(lambda v: v, (x,), {}, "with_effects")
+    if out._err is None:
+        out._effects = tuple(effects)
+    return out
+
+
+def detach(x):
+    """The same values with no gradient flowing back (tensor.Detach)."""
+    return _node(lambda v: v.detach(), (x,), {}, "detach")
+
+
 def from_bytes(data, shape, dtype=torch.float32, device: Device | None = None) -> Tensor:
     """A tensor over raw little-endian bytes (bytes, bytearray, memoryview, mmap) without copying when
     the buffer is writable or the target is another device (tensor.FromBytes, tensor/bytes.go)."""
@@ -938,7 +961,7 @@ def _bind_methods():
     for n in ("mean var logsumexp argmax softmax log_softmax cumsum exp log sqrt rsqrt sin cos tanh sigmoid relu "
               "neg sign floor ceil erf silu softplus gelu clamp cast reshape permute transpose expand squeeze "
               "unsqueeze flip pad cat contiguous gather scatter_add sort argsort topk matmul maximum minimum "
-              "where one_hot").split():
+              "where one_hot with_effects detach").split():
         names[n] = n
     for meth, fn in names.items():
         if fn in g and not hasattr(Tensor, meth):
