@@ -7,6 +7,7 @@
 // nn/transformer.go:191-259 (RoPE), optim/optim.go:494-510 (AdamW rule),
 // :198-215 (global-norm clip factor), :372-392 (master weights).
 #include "common.cuh"
+#include "philox.cuh"
 #include "runtime.h"
 
 namespace mimir {
@@ -320,18 +321,6 @@ static inline unsigned blocks_for(size_t n, int per_block) {
 // (reference: backend/internal/gen/gen.go:577-610, backend/cpu/rand.go).
 // ---------------------------------------------------------------------------
 namespace mimir {
-__device__ __forceinline__ uint4 philox4x32_10(uint64_t ctr, uint64_t seed) {
-  uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32), c2 = 0, c3 = 0;
-  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-    c0 = hi1 ^ c1 ^ k0; c1 = lo1; c2 = hi0 ^ c3 ^ k1; c3 = lo0;
-    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
-  }
-  return make_uint4(c0, c1, c2, c3);
-}
 __global__ void philox_uniform_kernel(float* __restrict__ out, size_t n, uint64_t seed) {
   const size_t blk = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (blk * 4 >= n) return;

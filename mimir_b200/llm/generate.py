@@ -13,6 +13,7 @@ class Sampler:
         self.temperature, self.top_k, self.top_p, self.min_p = temperature, top_k, top_p, min_p
         self.repeat_penalty, self.repeat_last = repeat_penalty, repeat_last
         self.gen = torch.Generator().manual_seed(seed)
+        self.seed, self.draws = seed, 0
 
     def distribution(self, logits: torch.Tensor, history=()) -> torch.Tensor:
         """Probabilities [vocab] after every filter (what ``sample`` draws from)."""
@@ -40,7 +41,25 @@ class Sampler:
             p = torch.where(p >= self.min_p * p.max(), p, torch.zeros_like(p))
         return p / p.sum()
 
+    def sample_device(self, logits: torch.Tensor, history=None) -> torch.Tensor:
+        """Tokens for every row of ``logits`` ``[rows, V]`` on the GPU, drawn by the fused sampling kernel
+        (radix-select top-k, nucleus and min-p cuts, Philox draw); returns int32 ``[rows]`` on the device.
+        ``history``: optional int64 ``[rows, n]`` of recent tokens for the repetition penalty."""
+        from ..ops.sampling import sample
+        if logits.dim() == 1:
+            logits = logits[None]
+        if self.repeat_penalty != 1.0 and history is not None and history.numel():
+            logits = logits.float().clone()
+            h = history[:, -self.repeat_last:].to(logits.device)
+            v = logits.gather(1, h)
+            logits.scatter_(1, h, torch.where(v > 0, v / self.repeat_penalty, v * self.repeat_penalty))
+        self.draws += 1
+        return sample(logits, self.temperature, self.top_k, self.top_p, self.min_p, self.seed, self.draws - 1)
+
     def sample(self, logits: torch.Tensor, history=()) -> int:
+        if logits.is_cuda and logits.dim() == 1:
+            hist = torch.tensor([list(history[-self.repeat_last:])], dtype=torch.int64) if len(history) else None
+            return int(self.sample_device(logits, hist)[0])
         p = self.distribution(logits, history)
         return int(p.argmax()) if self.temperature <= 0 else int(torch.multinomial(p, 1, generator=self.gen))
 

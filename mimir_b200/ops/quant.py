@@ -117,5 +117,19 @@ def quantize_q4_0(x: torch.Tensor) -> torch.Tensor:
 
 def qmatmul_t(x: torch.Tensor, w) -> torch.Tensor:
     """``x @ dequant(w)^T`` for a ``QuantizedTensor`` weight [N, K] (OpQMatMul, tensor/quant.go:35)."""
+    if x.is_cuda and w.code in (Q8_0, Q4_0, Q4_K, Q6_K) and len(w.shape) == 2:
+        from . import quant_cuda
+        raw = w.raw if w.raw.is_cuda and w.raw.device == x.device else w.raw.to(x.device)
+        rows = x.reshape(-1, x.shape[-1])
+        if rows.shape[0] <= _QGEMV_MAX_ROWS:
+            # few rows (decode): the weight is read once in its block encoding
+            y = quant_cuda.qgemv_ggml(w.code, raw, w.shape[0], w.shape[1], rows)
+            return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
+        n = w.shape[0] * w.shape[1]
+        wd = quant_cuda.dequantize(w.code, raw, n).view(w.shape)       # many rows (prefill): dequantise on the GPU
+        return (x.float() @ wd.t()).to(x.dtype)
     wd = dequantize(w, torch.float32).to(x.device)
     return (x.float() @ wd.t()).to(x.dtype)
+
+
+_QGEMV_MAX_ROWS = 16

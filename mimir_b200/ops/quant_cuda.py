@@ -19,6 +19,7 @@ def _L():
         PP = ctypes.POINTER(ctypes.c_void_p)
         for name, args in {
             "mimir_dequant": [I, P, P, L, P],
+            "mimir_qgemv_ggml": [I, P, P, I, I, P, P, I, I, I, I, P],
             "mimir_q4_0_to_planar": [P, P, P, L, P],
             "mimir_quantize_act": [P, I, P, P, P, P, I, I, I, F, P],
             "mimir_q4_gemv": [P, P, P, P, P, I, I, I, I, I, P],
@@ -46,6 +47,22 @@ def _L():
 def dequantize(code: int, raw: torch.Tensor, n: int) -> torch.Tensor:
     out = torch.empty(n, dtype=torch.float32, device=raw.device)
     _native.check(_L().mimir_dequant(code, ptr(raw), ptr(out), n, stream_ptr()), "dequant")
+    return out
+
+
+def qgemv_ggml(code: int, raw: torch.Tensor, N: int, K: int, x: torch.Tensor, bias=None) -> torch.Tensor:
+    """``x [B, K] @ dequant(W [N, K])^T`` with ``W`` read in its ggml block encoding (Q8_0, Q4_0, Q4_K,
+    Q6_K); fp32 result ``[B, N]``.  ``x`` is fp32 or bf16, rows contiguous."""
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    x = x.contiguous()
+    if K % 8:
+        raise ValueError("qgemv: K must be a multiple of 8")
+    out = torch.empty(x.shape[0], N, dtype=torch.float32, device=x.device)
+    b = None if bias is None else bias.float().contiguous()
+    _native.check(_L().mimir_qgemv_ggml(code, ptr(raw), ptr(x), int(x.dtype == torch.float32), K,
+                                        ptr(b) if b is not None else None, ptr(out), N, N, K, x.shape[0],
+                                        stream_ptr()), "qgemv_ggml")
     return out
 
 

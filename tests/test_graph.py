@@ -428,3 +428,24 @@ def test_export_cnn(tmp_path):
     X.export(path, net, x)
     with mim.open(path) as model:
         torch.testing.assert_close(model.run({"input": x})["output"].data(), net(x).data(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_exported_model_runs_on_the_gpu(tmp_path):
+    """The interpreter computes on the device of its inputs; weights move there once."""
+    nn.manual_seed(3)
+    net = _Net()
+    idx = T.tensor(torch.tensor([[1, 5, 7, 2, 0], [3, 3, 19, 8, 4]], dtype=torch.int32))
+    path = tmp_path / "net.mim"
+    X.export(path, net, idx, input_name="tokens", output_name="y")
+    with mim.open(path) as model:
+        cpu = model.run({"tokens": idx})["y"].data()
+        s = model.new_session()
+        gpu = s.run({"tokens": idx.data().cuda()})["y"].data()
+        assert gpu.is_cuda
+        torch.testing.assert_close(gpu.cpu(), cpu, rtol=1e-4, atol=1e-5)
+    kv = _kv_cache_model().new_session()
+    out = kv.run({"rows": torch.ones(2, 3).cuda(), "pos": torch.tensor([0, 1], dtype=torch.int32).cuda()})
+    assert out["total"].data().cpu().tolist() == [[2.0, 2.0, 2.0]]
+    out = kv.run({"rows": torch.ones(1, 3).cuda(), "pos": torch.tensor([5], dtype=torch.int32).cuda()})
+    assert out["total"].data().cpu().tolist() == [[3.0, 3.0, 3.0]]
