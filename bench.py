@@ -111,6 +111,8 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--attention", default="native")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--dp-blocks", type=int, default=32,
+                    help="grid of the data-parallel bucket kernels that run beside backward")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -152,7 +154,7 @@ def main() -> int:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from mimir_b200.parallel.dp import FusedDataParallel
-        dp = FusedDataParallel(rank, world, local_rank)
+        dp = FusedDataParallel(rank, world, local_rank, nblocks=args.dp_blocks)
         flat_alloc = dp.alloc_shared
 
     cfg = GPT2Config.small()

@@ -733,16 +733,24 @@ def log_softmax(x, dim=-1):
     return _node(lambda v: torch.log_softmax(v.float(), dim).to(v.dtype), (x,), {}, "log_softmax")
 
 
-def cumsum(x, dim=-1):
-    return _node(lambda v: torch.cumsum(v, dim), (x,), {}, "cumsum")
+def _scan(opname, mode, fallback):
+    """Running sum / maximum / log-sum-exp: the native block-per-row scan for fp32 / bf16 tensors on
+    the GPU outside autograd, PyTorch otherwise."""
+    def op(x, dim=-1):
+        def run(v):
+            if v.is_cuda and not torch.is_grad_enabled() and v.dim() >= 1:
+                from ..ops import scan as native
+                if native.supported(v):
+                    return native.scan(v, mode, dim)
+            return fallback(v, dim)
+        return _node(run, (x,), {}, opname)
+    op.__name__ = opname
+    return op
 
 
-def cummax(x, dim=-1):
-    return _node(lambda v: torch.cummax(v, dim).values, (x,), {}, "cummax")
-
-
-def logcumsumexp(x, dim=-1):
-    return _node(lambda v: torch.logcumsumexp(v, dim), (x,), {}, "logcumsumexp")
+cumsum = _scan("cumsum", "sum", lambda v, d: torch.cumsum(v, d))
+cummax = _scan("cummax", "max", lambda v, d: torch.cummax(v, d).values)
+logcumsumexp = _scan("logcumsumexp", "logsumexp", lambda v, d: torch.logcumsumexp(v, d))
 
 
 def sort(x, dim=-1, descending=False):

@@ -174,3 +174,37 @@ def test_philox_kernel_matches_host_stream_bit_for_bit():
     ref = torch.where(keep.cuda(), (x.float() / 0.75).bfloat16(), torch.zeros_like(x))
     assert torch.equal(y, ref)
     assert torch.equal(K.dropout(x, 0.25, 7), y)
+
+
+@pytest.mark.parametrize("mode", ["sum", "max", "logsumexp"])
+@pytest.mark.parametrize("shape,dim,dtype", [((5, 37), -1, torch.float32), ((3, 1024), -1, torch.float32),
+                                             ((2, 5000), 1, torch.float32), ((4, 300, 6), 1, torch.float32),
+                                             ((7, 2050), -1, torch.bfloat16), ((1, 1), 0, torch.float32)])
+def test_scan_rows_against_torch(mode, shape, dim, dtype):
+    from mimir_b200.ops.scan import scan
+    torch.manual_seed(sum(shape))
+    x = torch.randn(*shape).to(dtype)
+    ref = {"sum": lambda v: torch.cumsum(v, dim), "max": lambda v: torch.cummax(v, dim).values,
+           "logsumexp": lambda v: torch.logcumsumexp(v, dim)}[mode](x.double())
+    got = scan(x.cuda(), mode, dim)
+    assert got.dtype == dtype and got.shape == x.shape
+    tol = dict(rtol=2e-2, atol=0.5) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(got.double().cpu(), ref, **tol)
+    rev = scan(x.cuda(), mode, dim, reverse=True)
+    ref_r = {"sum": lambda v: torch.cumsum(v, dim), "max": lambda v: torch.cummax(v, dim).values,
+             "logsumexp": lambda v: torch.logcumsumexp(v, dim)}[mode](x.double().flip(dim)).flip(dim)
+    torch.testing.assert_close(rev.double().cpu(), ref_r, **tol)
+
+
+def test_lazy_scans_use_the_native_kernel_on_the_gpu():
+    from mimir_b200 import tensor as T
+    x = torch.randn(6, 777)
+    for f, ref in ((T.cumsum, torch.cumsum(x, -1)), (T.cummax, torch.cummax(x, -1).values),
+                   (T.logcumsumexp, torch.logcumsumexp(x, -1))):
+        with torch.no_grad():
+            got = f(T.from_torch(x.cuda())).data()
+        torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-4)
+    inf = torch.tensor([[float("-inf"), 1.0, float("-inf"), 2.0]])
+    with torch.no_grad():
+        got = T.logcumsumexp(T.from_torch(inf.cuda())).data().cpu()
+    torch.testing.assert_close(got, torch.logcumsumexp(inf, -1))
