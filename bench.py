@@ -111,8 +111,8 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--attention", default="native")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--dp-blocks", type=int, default=32,
-                    help="grid of the data-parallel bucket kernels that run beside backward")
+    ap.add_argument("--dp-blocks", type=int, default=0,
+                    help="grid of the data-parallel bucket kernels that run beside backward (0 = two blocks per SM)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

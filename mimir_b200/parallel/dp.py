@@ -23,7 +23,7 @@ _SIG_WORDS = 4096
 
 
 class FusedDataParallel:
-    def __init__(self, rank: int, world: int, local_rank: int | None = None, nblocks: int = 32,
+    def __init__(self, rank: int, world: int, local_rank: int | None = None, nblocks: int = 0,
                  group=None):
         self.rank, self.world, self.group = rank, world, group
         self.local_rank = rank if local_rank is None else local_rank
@@ -97,10 +97,14 @@ class FusedDataParallel:
         b = self.buckets[name]
         e = self.engine
         lib = _native.lib()
-        # buckets that finish while backward still runs get a small grid (they share the SMs with the
-        # GEMMs); the last bucket of the step has the GPU to itself and is pure memory traffic
+        # Two small blocks per SM (nblocks = 0): the bucket kernel is latency-bound per thread, so a
+        # narrow grid falls behind backward and the backlog surfaces at the end of the step (GPT-2 small
+        # on 2 GPUs: 15.5 / 13.2 / 12.7 / 12.3 / 12.1 ms per step with 8 / 16 / 32 / 64 / 296 blocks);
+        # its blocks hold no shared memory and sit beside the GEMM CTAs.  The last bucket of the step
+        # has the GPU to itself and always takes the full grid.
         last = name == self._last_bucket
-        nblocks = 2 * torch.cuda.get_device_properties(e.device).multi_processor_count if last else self.nblocks
+        full = 2 * torch.cuda.get_device_properties(e.device).multi_processor_count
+        nblocks = full if last or self.nblocks <= 0 else self.nblocks
         rc = lib.mimir_dp_bucket(self._grads_arr, self._params_arr, self._sig_arr, ptr(self.master),
                                  ptr(self.exp_avg), ptr(self.exp_avg_sq), ptr(e.hyper), ptr(self.epoch),
                                  self.block_counters[self._bucket_index[name]:].data_ptr(), b["start"],
