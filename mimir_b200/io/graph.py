@@ -469,4 +469,6 @@ class Builder:
         return mim.serialize(self.tensors, metadata=metadata, graph=self.finish().encode())
 
 
-STDLIB: dict = {}   # filled by graph_run at import
+STDLIB: dict = {}   # name.vN -> implementation, filled by graph_run
+
+from . import graph_run as _graph_run  # noqa: E402,F401 - registers the standard library

@@ -136,10 +136,21 @@ def _scatter(c, data, idx, updates, axis):
         out, c.run.wrote = data, True
     else:
         out = data.clone()
-    if flat.numel() > 1 and flat.unique().numel() != flat.numel():
-        for j in range(flat.numel()):          # repeated positions: the last one wins, in order
-            out.index_copy_(axis, flat[j:j + 1], upd.narrow(axis, j, 1))
-        return out
+    n_pos = flat.numel()
+    if 1 < n_pos <= 4096:
+        # repeated positions: every copy of a position writes the slice of its LAST occurrence, so the
+        # result does not depend on the order of the writes (and nothing is read back on the host)
+        same = flat[:, None] == flat[None, :]
+        order = torch.arange(n_pos, device=flat.device)
+        winner = torch.where(same, order[None, :], order.new_zeros(())).amax(1)
+        return out.index_copy_(axis, flat, upd.index_select(axis, winner))
+    if n_pos > 1:
+        if torch.cuda.is_available() and flat.is_cuda and torch.cuda.is_current_stream_capturing():
+            raise E.ErrUnsupported("graph: a scatter of more than 4096 positions is not recorded")
+        if flat.unique().numel() != n_pos:
+            for j in range(n_pos):             # repeated positions: the last one wins, in order
+                out.index_copy_(axis, flat[j:j + 1], upd.narrow(axis, j, 1))
+            return out
     return out.index_copy_(axis, flat, upd)
 
 
@@ -698,6 +709,20 @@ class Program:
         self.outputs = [(n, g.values[i]) for n, i in zip(g.output_names, g.main.outputs)]
         if len(g.output_names) != len(g.main.outputs):
             raise G.FormatError("graph: the main program's outputs and their names differ in number")
+        self.replayable = not self._data_dependent()
+
+    def _data_dependent(self) -> bool:
+        """True when a run's kernel sequence depends on tensor values (``while`` / ``if``) or an op has to
+        look at values on the host (integer division and powers check their operands): such programs
+        are never recorded."""
+        ints = ("i8", "i16", "i32", "i64", "u8", "bool")
+        for sg in self.g.subgraphs:
+            for op in sg.ops:
+                if op.opcode in ("while", "if"):
+                    return True
+                if op.opcode in ("idiv", "imod", "pow") and any(self.g.values[i].dtype in ints for i in op.inputs):
+                    return True
+        return False
 
     def stored(self, v: G.Value, device):
         from .mim import QuantizedTensor
@@ -725,8 +750,14 @@ class Program:
         return Session(self)
 
     def run(self, inputs: dict, cancel=None) -> dict:
-        """One run on fresh variables (reference: Model.Run)."""
-        return Session(self).run(inputs, cancel=cancel)
+        """One run on fresh variables (reference: Model.Run).  A program without variables keeps one
+        session for these calls, so repeated shapes are replayed from their recording."""
+        if any(v.kind == "variable" for v in self.g.values):
+            return Session(self).run(inputs, cancel=cancel)
+        with self._lock:
+            if getattr(self, "_stateless", None) is None:
+                self._stateless = Session(self)
+        return self._stateless.run(inputs, cancel=cancel)
 
 
 def _to_torch(x):
@@ -753,11 +784,20 @@ class Session:
         self._vars: dict = {}
         self._lock = threading.Lock()
         self._broken = None
+        self._recs: dict = {}        # (device, input shapes) -> run count, False, or (graph, inputs, outputs)
+        self.replay = True           # set to False to run every pass plainly on the GPU too
 
     def reset(self) -> None:
+        """Puts the variables back to their initial values (in their buffers, which recordings keep)."""
         with self._lock:
-            self._vars = {}
             self._broken = None
+            with torch.no_grad():
+                for i, cur in self._vars.items():
+                    v = self.p.g.values[i]
+                    if v.store:
+                        cur.copy_(self.p.stored(v, cur.device))
+                    else:
+                        cur.zero_()
 
     def run(self, inputs: dict, cancel=None) -> dict:
         from ..tensor.core import from_torch
@@ -765,70 +805,123 @@ class Session:
             if self._broken is not None:
                 raise E.MimirError(f"graph: the session's variables are unreadable after a failed run "
                                    f"({self._broken}); call reset()")
-            p, g = self.p, self.p.g
-            ins = {}
-            device = None
-            for v in p.inputs:
-                if v.name not in inputs:
-                    raise E.ErrShape(f"graph: input {v.name!r} is missing")
-                t = _to_torch(inputs[v.name])
-                if t.dtype != G.DTYPES[v.dtype]:
-                    raise E.ErrDType(f"graph: input {v.name!r} is {t.dtype}, declared {v.dtype}")
-                if device is None:
-                    device = t.device
-                elif t.device != device:
-                    raise E.ErrDevice(f"graph: input {v.name!r} on {t.device}, others on {device}")
-                ins[v.name] = t.detach()
-            for name in inputs:
-                if all(v.name != name for v in p.inputs):
-                    raise E.ErrShape(f"graph: the model has no input {name!r}")
+            ins, device = self._prepare(inputs)
+            outs = None
+            if device.type == "cuda" and self.replay and cancel is None and self.p.replayable:
+                outs = self._run_recorded(ins, device)
+            if outs is None:
+                outs = self._execute(ins, device, cancel)
+            return {n: from_torch(t) for n, t in outs.items()}
+
+    def _prepare(self, inputs: dict):
+        p = self.p
+        ins = {}
+        device = None
+        for v in p.inputs:
+            if v.name not in inputs:
+                raise E.ErrShape(f"graph: input {v.name!r} is missing")
+            t = _to_torch(inputs[v.name])
+            if t.dtype != G.DTYPES[v.dtype]:
+                raise E.ErrDType(f"graph: input {v.name!r} is {t.dtype}, declared {v.dtype}")
             if device is None:
-                from ..tensor.core import default_device
-                device = default_device().torch
-            r = _Run(p, device, cancel)
-            for vi, v in zip(g.main.inputs, p.inputs):
-                r.bind(vi, tuple(ins[v.name].shape))
-                r.env[vi] = ins[v.name]
-            for i, t in p.consts_on(device).items():
-                r.env[i] = t
-            outs_set = set(g.main.outputs)
-            for i, v in enumerate(g.values):
-                if v.kind != "variable":
-                    continue
-                cur = self._vars.get(i)
-                if cur is None or cur.device != device:
-                    if cur is not None:
-                        cur = cur.to(device)
-                    elif v.store:
-                        cur = p.stored(v, device).clone()
-                    else:
-                        cur = torch.zeros(r.declared(i), dtype=G.DTYPES[v.dtype], device=device)
-                    self._vars[i] = cur
-                r.bind(i, tuple(cur.shape))
-                r.env[i] = cur
-                # the old contents may be overwritten when the variable is replaced by a value that is
-                # not also an output (a KV cache that a run writes a few rows of)
-                nxt = g.updates.get(i)
-                if nxt is not None and i not in outs_set and nxt not in outs_set:
-                    r.owned.add(i)
+                device = t.device
+            elif t.device != device:
+                raise E.ErrDevice(f"graph: input {v.name!r} on {t.device}, others on {device}")
+            ins[v.name] = t.detach()
+        for name in inputs:
+            if all(v.name != name for v in p.inputs):
+                raise E.ErrShape(f"graph: the model has no input {name!r}")
+        if device is None:
+            from ..tensor.core import default_device
+            device = default_device().torch
+        return ins, device
+
+    def _execute(self, ins: dict, device, cancel=None) -> dict:
+        """One pass over the main program.  The variables live in buffers that stay where they are for
+        the life of the session (a recorded run replays kernels that read and write those addresses):
+        a new value is copied into its variable's buffer unless the run computed it there."""
+        p, g = self.p, self.p.g
+        r = _Run(p, device, cancel)
+        for vi, v in zip(g.main.inputs, p.inputs):
+            r.bind(vi, tuple(ins[v.name].shape))
+            r.env[vi] = ins[v.name]
+        for i, t in p.consts_on(device).items():
+            r.env[i] = t
+        outs_set = set(g.main.outputs)
+        for i, v in enumerate(g.values):
+            if v.kind != "variable":
+                continue
+            cur = self._vars.get(i)
+            if cur is None or cur.device != device:
+                if cur is not None:
+                    cur = cur.to(device)
+                    self._recs.clear()        # recordings hold the old buffers
+                elif v.store:
+                    cur = p.stored(v, device).clone()
+                else:
+                    cur = torch.zeros(r.declared(i), dtype=G.DTYPES[v.dtype], device=device)
+                self._vars[i] = cur
+            r.bind(i, tuple(cur.shape))
+            r.env[i] = cur
+            # the old contents may be overwritten when the variable is replaced by a value that is
+            # not also an output (a KV cache that a run writes a few rows of)
+            nxt = g.updates.get(i)
+            if nxt is not None and i not in outs_set and nxt not in outs_set:
+                r.owned.add(i)
+        try:
+            with torch.no_grad():
+                r.body(g.main)
+                outs = {n: r._get(vi, "an output") for n, vi in zip(g.output_names, g.main.outputs)}
+                new = {var: r._get(nxt, "a variable update") for var, nxt in g.updates.items()}
+        except BaseException as exc:
+            if r.wrote:
+                self._broken = type(exc).__name__
+            raise
+        for var, t in new.items():
+            want = self._vars[var]
+            if t.shape != want.shape or t.dtype != want.dtype:
+                raise E.ErrShape(f"graph: variable {g.values[var].name!r} would change from "
+                                 f"{tuple(want.shape)} {want.dtype} to {tuple(t.shape)} {t.dtype}")
+        with torch.no_grad():
+            var_ptrs = {v.untyped_storage().data_ptr() for v in self._vars.values()}
+            # outputs and new values that live in a variable's memory are detached from it first
+            outs = {n: (t.clone() if t.untyped_storage().data_ptr() in var_ptrs else t) for n, t in outs.items()}
+            staged = {var: (None if t is self._vars[var] else
+                            t.clone() if t.untyped_storage().data_ptr() in var_ptrs else t) for var, t in new.items()}
+            for var, t in staged.items():
+                if t is not None:
+                    self._vars[var].copy_(t)
+        return outs
+
+    def _run_recorded(self, ins: dict, device):
+        """Recording and replay per input shape (reference: io/mim/replay.go:60-130).  The first run of a
+        shape is a plain pass; the second is captured into a CUDA graph over fixed input, output and
+        variable buffers; later runs copy the inputs in, replay, and copy the outputs out.  Returns None
+        when this shape is run plainly."""
+        key = (str(device), tuple((n, tuple(t.shape)) for n, t in ins.items()))
+        rec = self._recs.get(key, 0)
+        if rec is False:
+            return None
+        if isinstance(rec, int):
+            if rec < 1:
+                self._recs[key] = rec + 1
+                return None
+            static_in = {n: t.clone() for n, t in ins.items()}
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
             try:
-                with torch.no_grad():
-                    r.body(g.main)
-                    outs = {n: r._get(vi, "an output") for n, vi in zip(g.output_names, g.main.outputs)}
-                    new = {var: r._get(nxt, "a variable update") for var, nxt in g.updates.items()}
-            except BaseException as exc:
-                if r.wrote:
-                    self._broken = type(exc).__name__
-                raise
-            for var, t in new.items():
-                want = self._vars[var]
-                if t.shape != want.shape or t.dtype != want.dtype:
-                    raise E.ErrShape(f"graph: variable {g.values[var].name!r} would change from "
-                                     f"{tuple(want.shape)} {want.dtype} to {tuple(t.shape)} {t.dtype}")
-            for var, t in new.items():
-                self._vars[var] = t
-            return {n: from_torch(t.clone() if any(t is v for v in self._vars.values()) else t)
-                    for n, t in outs.items()}
+                with torch.cuda.graph(graph):
+                    static_out = self._execute(static_in, device)
+            except Exception:  # noqa: BLE001 - this shape cannot be captured: run it plainly from now on
+                self._recs[key] = False
+                torch.cuda.synchronize(device)
+                return None
+            rec = self._recs[key] = (graph, static_in, static_out)
+        graph, static_in, static_out = rec
+        for n, t in ins.items():
+            static_in[n].copy_(t)
+        graph.replay()
+        return {n: t.clone() for n, t in static_out.items()}
 
     def variable(self, name: str):
         """Current contents of a variable (a copy), or None before the first run."""

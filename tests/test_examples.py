@@ -39,3 +39,10 @@ def test_generative_examples():
 def test_gnn_example():
     import gnn
     assert gnn.main(steps=40, log=quiet) > 0.7
+
+
+def test_export_run_example():
+    import export_run
+    err, avg = export_run.main(log=quiet)
+    assert err < 1e-5
+    assert abs(avg[0].item() - (1 - 0.9 ** 3)) < 1e-6

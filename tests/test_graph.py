@@ -449,3 +449,36 @@ def test_exported_model_runs_on_the_gpu(tmp_path):
     assert out["total"].data().cpu().tolist() == [[2.0, 2.0, 2.0]]
     out = kv.run({"rows": torch.ones(1, 3).cuda(), "pos": torch.tensor([5], dtype=torch.int32).cuda()})
     assert out["total"].data().cpu().tolist() == [[3.0, 3.0, 3.0]]
+
+
+@pytest.mark.gpu
+def test_repeated_shapes_are_replayed_from_a_recording(tmp_path):
+    """Third and later runs of one input shape replay a CUDA graph; values, variables and a change of
+    shape behave as in a plain pass."""
+    nn.manual_seed(4)
+    net = _Net()
+    path = tmp_path / "net.mim"
+    idx = T.tensor(torch.randint(0, 20, (2, 5), dtype=torch.int32))
+    X.export(path, net, idx, input_name="tokens", output_name="y", dynamic={"tokens": {0: ("batch", 8)}})
+    with mim.open(path) as model:
+        s = model.new_session()
+        for trial in range(5):
+            t = torch.randint(0, 20, (2, 5), dtype=torch.int32)
+            got = s.run({"tokens": t.cuda()})["y"].data().cpu()
+            torch.testing.assert_close(got, net(T.tensor(t)).data(), rtol=1e-4, atol=1e-5)
+        assert any(isinstance(r, tuple) for r in s._recs.values())
+        t3 = torch.randint(0, 20, (3, 5), dtype=torch.int32)      # another shape: its own recording
+        torch.testing.assert_close(s.run({"tokens": t3.cuda()})["y"].data().cpu(), net(T.tensor(t3)).data(),
+                                   rtol=1e-4, atol=1e-5)
+    kv, ref = _kv_cache_model().new_session(), _kv_cache_model().new_session()
+    ref.replay = False
+    for step in range(6):
+        feed = {"rows": torch.full((1, 3), float(step + 1)), "pos": torch.tensor([step % 4], dtype=torch.int32)}
+        a = kv.run({k: v.cuda() for k, v in feed.items()})
+        b = ref.run({k: v.cuda() for k, v in feed.items()})
+        assert torch.equal(a["total"].data(), b["total"].data()) and a["steps"].item() == b["steps"].item() == 10 + step
+    assert any(isinstance(r, tuple) for r in kv._recs.values()) and not ref._recs
+    torch.testing.assert_close(kv.variable("cache").cpu(), ref.variable("cache").cpu())
+    kv.reset()
+    out = kv.run({"rows": torch.ones(1, 3).cuda(), "pos": torch.tensor([0], dtype=torch.int32).cuda()})
+    assert out["total"].data().cpu().tolist() == [[1.0, 1.0, 1.0]] and out["steps"].item() == 10
