@@ -435,7 +435,7 @@ def test_exported_model_runs_on_the_gpu(tmp_path):
     """The interpreter computes on the device of its inputs; weights move there once."""
     nn.manual_seed(3)
     net = _Net()
-    idx = T.tensor(torch.tensor([[1, 5, 7, 2, 0], [3, 3, 19, 8, 4]], dtype=torch.int32))
+    idx = T.from_torch(torch.tensor([[1, 5, 7, 2, 0], [3, 3, 19, 8, 4]], dtype=torch.int32))
     path = tmp_path / "net.mim"
     X.export(path, net, idx, input_name="tokens", output_name="y")
     with mim.open(path) as model:
@@ -458,17 +458,17 @@ def test_repeated_shapes_are_replayed_from_a_recording(tmp_path):
     nn.manual_seed(4)
     net = _Net()
     path = tmp_path / "net.mim"
-    idx = T.tensor(torch.randint(0, 20, (2, 5), dtype=torch.int32))
+    idx = T.from_torch(torch.randint(0, 20, (2, 5), dtype=torch.int32))
     X.export(path, net, idx, input_name="tokens", output_name="y", dynamic={"tokens": {0: ("batch", 8)}})
     with mim.open(path) as model:
         s = model.new_session()
         for trial in range(5):
             t = torch.randint(0, 20, (2, 5), dtype=torch.int32)
             got = s.run({"tokens": t.cuda()})["y"].data().cpu()
-            torch.testing.assert_close(got, net(T.tensor(t)).data(), rtol=1e-4, atol=1e-5)
+            torch.testing.assert_close(got, net(T.from_torch(t)).data(), rtol=1e-4, atol=1e-5)
         assert any(isinstance(r, tuple) for r in s._recs.values())
         t3 = torch.randint(0, 20, (3, 5), dtype=torch.int32)      # another shape: its own recording
-        torch.testing.assert_close(s.run({"tokens": t3.cuda()})["y"].data().cpu(), net(T.tensor(t3)).data(),
+        torch.testing.assert_close(s.run({"tokens": t3.cuda()})["y"].data().cpu(), net(T.from_torch(t3)).data(),
                                    rtol=1e-4, atol=1e-5)
     kv, ref = _kv_cache_model().new_session(), _kv_cache_model().new_session()
     ref.replay = False
