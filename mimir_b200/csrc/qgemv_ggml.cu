@@ -27,8 +27,21 @@ namespace mimir {
 
 namespace {
 
+// Every block format has an even block size and even field offsets, and rows start on even
+// addresses, so scales and 8-byte groups of quants can be read as 16-bit words.
 __device__ __forceinline__ float h2f(const uint8_t* p) {
-  return __half2float(__ushort_as_half(static_cast<uint16_t>(p[0] | (p[1] << 8))));
+  return __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(p)));
+}
+
+// eight consecutive bytes from a 2-byte aligned address
+__device__ __forceinline__ void ld_bytes8(const uint8_t* p, uint8_t out[8]) {
+  const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint16_t w = q[i];
+    out[2 * i] = static_cast<uint8_t>(w & 0xFF);
+    out[2 * i + 1] = static_cast<uint8_t>(w >> 8);
+  }
 }
 
 __device__ __forceinline__ void k4_scale_min(int j, const uint8_t* q, int& sc, int& mn) {
@@ -48,13 +61,16 @@ __device__ __forceinline__ void decode8(const uint8_t* __restrict__ row, int uni
   if constexpr (CODE == 64) {
     const uint8_t* b = row + static_cast<size_t>(unit) * 34;
     const float d = h2f(b);
+    uint8_t q[8];
+    ld_bytes8(b + 2 + off, q);
 #pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(static_cast<int8_t>(b[2 + off + t]));
+    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(static_cast<int8_t>(q[t]));
   } else if constexpr (CODE == 65) {
     const uint8_t* b = row + static_cast<size_t>(unit) * 18;
     const float d = h2f(b);
     const int sh = off < 16 ? 0 : 4;
-    const uint8_t* q = b + 2 + (off & 15);
+    uint8_t q[8];
+    ld_bytes8(b + 2 + (off & 15), q);
 #pragma unroll
     for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(((q[t] >> sh) & 0xF) - 8);
   } else if constexpr (CODE == 66) {
@@ -65,15 +81,17 @@ __device__ __forceinline__ void decode8(const uint8_t* __restrict__ row, int uni
     k4_scale_min(sub, b + 4, sc, mn);
     const float ds = d * sc, m = dmin * mn;
     const int sh = (sub & 1) ? 4 : 0;
-    const uint8_t* q = b + 16 + (sub >> 1) * 32 + off;
+    uint8_t q[8];
+    ld_bytes8(b + 16 + (sub >> 1) * 32 + off, q);
 #pragma unroll
     for (int t = 0; t < 8; ++t) v[t] = ds * static_cast<float>((q[t] >> sh) & 0xF) - m;
   } else {
     const int sb = unit >> 3, sub = unit & 7;
     const uint8_t* b = row + static_cast<size_t>(sb) * 210;
     const int half = sub >> 2, quarter = sub & 3;
-    const uint8_t* ql = b + 64 * half + ((quarter & 1) ? 32 : 0) + off;
-    const uint8_t* qh = b + 128 + 32 * half + off;
+    uint8_t ql[8], qh[8];
+    ld_bytes8(b + 64 * half + ((quarter & 1) ? 32 : 0) + off, ql);
+    ld_bytes8(b + 128 + 32 * half + off, qh);
     const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192) + 8 * half + 2 * quarter;
     const float d = h2f(b + 208);
     const int sh = (quarter & 2) ? 4 : 0;

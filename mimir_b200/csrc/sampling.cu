@@ -78,8 +78,10 @@ __device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
 template <typename T>
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, int top_k, float top_p, float min_p,
-              uint64_t seed, uint64_t draw, int* __restrict__ out_tok, float* __restrict__ out_prob) {
+              uint64_t seed, uint64_t draw, const int* __restrict__ draw_dev, int* __restrict__ out_tok,
+              float* __restrict__ out_prob) {
   extern __shared__ uint8_t smem_raw[];
+  if (draw_dev) draw = static_cast<uint64_t>(*draw_dev);   // a step counter kept on the device (graph replays)
   SampleSmem& sm = *reinterpret_cast<SampleSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row = blockIdx.x;
@@ -268,21 +270,22 @@ using namespace mimir;
 // logits: [rows, V] fp32 or bf16 with row pitch ld (elements).  out_tok: int32 [rows];
 // out_prob (optional): probability of the drawn token under the filtered distribution.
 // `draw` numbers the call (a decode step), so one seed gives an independent uniform per
-// (draw, row).
+// (draw, row); when draw_dev is not null the number is read from that device int instead, which
+// lets a captured decode step advance it between replays.
 MIMIR_API int mimir_sample(const void* logits, int is_f32, int ld, int rows, int V, float temperature, int top_k,
-                           float top_p, float min_p, unsigned long long seed, unsigned long long draw, int* out_tok,
-                           float* out_prob, cudaStream_t st) {
+                           float top_p, float min_p, unsigned long long seed, unsigned long long draw,
+                           const int* draw_dev, int* out_tok, float* out_prob, cudaStream_t st) {
   if (rows <= 0 || V <= 0) return refuse("sample: empty logits");
   if (top_p <= 0.f) top_p = 1e-30f;
   const size_t smem = sizeof(SampleSmem);
   static_assert(sizeof(SampleSmem) <= 48 * 1024, "fits the default dynamic shared memory limit");
   if (is_f32)
     sample_kernel<float><<<rows, kSampleThreads, smem, st>>>(static_cast<const float*>(logits), ld, V, temperature,
-                                                             top_k, top_p, min_p, seed, draw, out_tok, out_prob);
+                                                             top_k, top_p, min_p, seed, draw, draw_dev, out_tok, out_prob);
   else
     sample_kernel<__nv_bfloat16><<<rows, kSampleThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(logits), ld, V,
                                                                      temperature, top_k, top_p, min_p, seed, draw,
-                                                                     out_tok, out_prob);
+                                                                     draw_dev, out_tok, out_prob);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("sample launch failed");
 }

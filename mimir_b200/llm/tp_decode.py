@@ -54,11 +54,14 @@ class LlamaConfig:
 
 class TPDecoder:
     def __init__(self, cfg: LlamaConfig, rank: int, world: int, batch: int, cap: int, seed: int = 0,
-                 device=None, weights: dict | None = None, engine: str = "auto"):
+                 device=None, weights: dict | None = None, engine: str = "auto", sampler=None):
         """``engine``: "tc" runs every projection on the tensor cores (Q4_0 tiles expanded to bf16 in
         shared memory, activations rounded to Q8_0 and kept as bf16); "dp4a" is the integer
         dot-product path (one warp per weight row), whose time grows with the batch; "auto" takes
-        dp4a up to 4 rows and the tensor cores above (the measured crossover)."""
+        dp4a up to 4 rows and the tensor cores above (the measured crossover).  ``sampler`` (an
+        ``llm.generate.Sampler`` with a temperature above 0) draws the next tokens with the fused
+        sampling kernel inside the step; every rank holds the same gathered logits, seed and step
+        counter, so every rank draws the same tokens.  Without one the step is greedy."""
         if engine not in ("auto", "tc", "dp4a"):
             raise ValueError(f"unknown decode engine {engine!r}")
         if engine == "auto":
@@ -66,6 +69,7 @@ class TPDecoder:
         if engine == "tc" and (batch > 32 or cfg.d_model % 64 or (cfg.ffn // world) % 64 or (cfg.n_head // world * cfg.head_dim) % 64):
             engine = "dp4a"
         self.engine = engine
+        self.sampler = sampler if sampler is not None and sampler.temperature > 0 else None
         self.cfg, self.rank, self.world, self.B, self.cap = cfg, rank, world, batch, cap
         self.dev = torch.device(device or f"cuda:{torch.cuda.current_device()}")
         d, D = cfg.d_model, cfg.head_dim
@@ -246,8 +250,16 @@ class TPDecoder:
                                                self.logits_local.numel() * 4, self.rank, self.world, 2, stream_ptr()),
                       "allgather")
         full = self.logits_all.view(torch.float32).view(self.world, self.B, self.Vl)
-        best = full.permute(1, 0, 2).reshape(self.B, -1).argmax(-1)  # greedy sampling on the device
-        self.tokens.copy_(best)
+        flat = full.permute(1, 0, 2).reshape(self.B, -1)
+        if self.sampler is None:
+            self.tokens.copy_(flat.argmax(-1))  # greedy, on the device
+        else:
+            from ..ops.sampling import sample
+            sm = self.sampler
+            if getattr(self, "_sampled", None) is None:
+                self._sampled = torch.empty(self.B, dtype=torch.int32, device=self.dev)
+            sample(flat, sm.temperature, sm.top_k, sm.top_p, sm.min_p, sm.seed, draw_dev=self.pos, out=self._sampled)
+            self.tokens.copy_(self._sampled)
         self.pos.add_(1)
         self.len.add_(1)
         self.pos_rows.add_(1)

@@ -131,6 +131,54 @@ def bench_q4(a):
         print(json.dumps(rec), flush=True)
 
 
+def _finite_blocks(code, nblocks, dev):
+    """Random ggml blocks with small finite scales (payload bytes are arbitrary)."""
+    per = {64: 34, 65: 18, 66: 144, 67: 210}[code]
+    raw = torch.randint(0, 256, (nblocks, per), dtype=torch.uint8, device=dev)
+    d = torch.full((nblocks,), 0.01, device=dev).half().view(torch.uint8).reshape(nblocks, 2)
+    if code == 67:
+        raw[:, 208:210] = d
+    else:
+        raw[:, 0:2] = d
+        if code == 66:
+            raw[:, 2:4] = d
+    return raw.reshape(-1)
+
+
+def bench_qgemv(a):
+    """GEMV over ggml blocks read in place (Q8_0 / Q4_0 / Q4_K / Q6_K), weights streamed from HBM."""
+    from ..ops import quant_cuda as Q
+    N, K, B = a.n, a.k, a.b
+    dev = "cuda"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if a.flush else None
+    peak = _peaks().get("hbm_gbs")
+    x = torch.randn(B, K, device=dev)
+    for name, code, vals, per in (("q8_0", 64, 32, 34), ("q4_0", 65, 32, 18), ("q4_k", 66, 256, 144), ("q6_k", 67, 256, 210)):
+        if a.only and a.only != name:
+            continue
+        raw = _finite_blocks(code, N * K // vals, dev)
+        t = time_ms(lambda: Q.qgemv_ggml(code, raw, N, K, x), a.iters, flush)
+        rec = {"kernel": "qgemv_ggml_" + name, "N": N, "K": K, "B": B, "us": t * 1e3,
+               "weight_gbs": raw.numel() / t / 1e6}
+        if peak:
+            rec["frac_of_measured_hbm_copy"] = rec["weight_gbs"] / peak
+        print(json.dumps(rec), flush=True)
+
+
+def bench_sample(a):
+    """The fused sampling kernel on [rows, vocab] logits."""
+    from ..ops.sampling import sample
+    x = (torch.randn(a.rows, a.vocab, device="cuda") * 3).bfloat16()
+    out = torch.empty(a.rows, dtype=torch.int32, device="cuda")
+    for name, kw in (("greedy", dict(temperature=0.0)), ("top_k40_top_p0.95", dict(temperature=0.8, top_k=40, top_p=0.95)),
+                     ("top_p0.9", dict(temperature=1.0, top_k=0, top_p=0.9))):
+        if a.only and a.only != name:
+            continue
+        t = time_ms(lambda: sample(x, out=out, **kw), a.iters, None)
+        print(json.dumps({"kernel": "sample_" + name, "rows": a.rows, "vocab": a.vocab, "us": t * 1e3,
+                          "logits_gbs": x.numel() * 2 / t / 1e6}), flush=True)
+
+
 def bench_conv(a):
     """Implicit-GEMM convolution (forward, input gradient, weight gradient) against cuDNN through PyTorch."""
     from ..ops import conv as C
@@ -189,12 +237,22 @@ def main():
     c.add_argument("--w", type=int, default=56)
     c.add_argument("--ksize", type=int, default=3)
     c.add_argument("--only", default="")
-    for p in (g, t, q, c):
+    qg = sub.add_parser("qgemv")
+    qg.add_argument("--n", type=int, default=65536)
+    qg.add_argument("--k", type=int, default=4096)
+    qg.add_argument("--b", type=int, default=1)
+    qg.add_argument("--only", default="")
+    sp = sub.add_parser("sample")
+    sp.add_argument("--rows", type=int, default=32)
+    sp.add_argument("--vocab", type=int, default=128256)
+    sp.add_argument("--only", default="")
+    for p in (g, t, q, c, qg, sp):
         p.add_argument("--iters", type=int, default=10)
         p.add_argument("--flush", action="store_true")
         p.add_argument("--no-baseline", action="store_true")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "q4": bench_q4, "conv": bench_conv}[a.cmd](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "q4": bench_q4, "conv": bench_conv, "qgemv": bench_qgemv,
+     "sample": bench_sample}[a.cmd](a)
 
 
 if __name__ == "__main__":

@@ -87,9 +87,18 @@ def main():
     gen = dec.generate(prompt, 6).cpu().tolist()
     err = check_error_word()
     dec.close()
+    # the same prompt with the fused sampling kernel inside the step: two decoders with one seed
+    from mimir_b200.llm.generate import Sampler
+    sampled = []
+    for _ in range(2):
+        d2 = TPDecoder(cfg, rank, world, batch=B, cap=32, weights=weights, engine=os.environ.get("DECODE_ENGINE", "tc"),
+                       sampler=Sampler(temperature=1.5, top_k=50, top_p=0.95, seed=7))
+        sampled.append(d2.generate(prompt, 6).cpu().tolist())
+        err |= check_error_word()
+        d2.close()
     if world > 1:
         dist.destroy_process_group()
-    os.write(1, ("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen, "cos_prefill": cos_prefill,
+    os.write(1, ("RESULT " + json.dumps({"rank": rank, "cos": cos, "rel": rel, "err": err, "gen": gen, "sampled": sampled, "vocab": cfg.vocab, "cos_prefill": cos_prefill,
                                   "launches": int(dec.launches_per_step)}) + "\n").encode())  # one write: lines of different ranks never interleave
 
 

@@ -457,6 +457,7 @@ def test_repeated_shapes_are_replayed_from_a_recording(tmp_path):
     shape behave as in a plain pass."""
     nn.manual_seed(4)
     net = _Net()
+    net.eval()
     path = tmp_path / "net.mim"
     idx = T.from_torch(torch.randint(0, 20, (2, 5), dtype=torch.int32))
     X.export(path, net, idx, input_name="tokens", output_name="y", dynamic={"tokens": {0: ("batch", 8)}})

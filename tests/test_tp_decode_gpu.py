@@ -31,6 +31,9 @@ def test_decode_single_gpu_matches_reference(engine):
     assert r["cos"] > 0.995 and r["rel"] < 0.08, r
     assert r["cos_prefill"] > 0.995, r
     assert r["launches"] > 0
+    a, b = r["sampled"]
+    assert a == b and a != r["gen"]                      # one seed, one sequence; not the greedy one
+    assert all(0 <= t < r["vocab"] for row in a for t in row)
 
 
 @pytest.mark.parametrize("engine", ["tc", "dp4a"])
@@ -44,3 +47,4 @@ def test_decode_tp2_matches_reference_and_ranks_agree(engine):
         assert r["cos"] > 0.995 and r["rel"] < 0.08, r
         assert r["cos_prefill"] > 0.995, r
     assert res[0]["gen"] == res[1]["gen"]
+    assert res[0]["sampled"] == res[1]["sampled"] and res[0]["sampled"][0] == res[0]["sampled"][1]
