@@ -10,7 +10,8 @@ io/mim/export.go:55-105) is provided here over this package's container:
   model-defined composites name others by index) and, for sessions, **variables**: values that
   keep their contents from one run to the next (a KV cache) and take the value of another value
   of the main program when a run ends.
-* the 33 primitives have the reference's meaning: ``and`` / ``or`` are mul / max on 0-1 integers,
+* the 33 primitives the reference runs have its meaning (``shl`` / ``shr`` / ``bitcast``, which the
+  format defines and the reference's interpreter refuses, run here too): ``and`` / ``or`` are mul / max on 0-1 integers,
   ``reduce`` takes ``mode`` add | max | mul and keeps the reduced axes with size 1, ``gather`` takes
   slices along an axis at clamped positions, ``scatter`` replaces slices along an axis (the last
   of repeated positions wins), ``reshape`` / ``expand`` / ``const`` take their target from the
@@ -46,8 +47,17 @@ OPCODES = (
     "add", "mul", "max", "pow", "idiv", "imod", "and", "or", "xor", "cmplt", "cmpeq", "where",
     "reduce", "reshape", "expand", "permute", "pad", "shrink", "gather", "scatter",
     "const", "dequantize", "call", "while", "if",
+    # opcodes of the format that the reference's interpreter refuses as unsupported (io/mim/ops.go:256-258)
+    "shl", "shr", "bitcast",
 )
-assert len(OPCODES) == 33
+assert len(OPCODES) == 36
+
+# inputs, outputs of the fixed-arity opcodes (reference: the arity table, io/mim/ops.go:228-238)
+ARITY = {**{c: (1, 1) for c in ("neg", "recip", "sqrt", "exp2", "log2", "sin", "trunc", "cast", "reduce", "reshape",
+                                "expand", "permute", "pad", "shrink", "dequantize", "bitcast")},
+         **{c: (2, 1) for c in ("add", "mul", "max", "pow", "idiv", "imod", "and", "or", "xor", "cmplt", "cmpeq",
+                                "gather", "shl", "shr")},
+         "where": (3, 1), "scatter": (3, 1), "const": (0, 1)}
 
 KINDS = ("input", "weight", "const", "variable", "temp")
 
@@ -202,6 +212,14 @@ class Graph:
             for o in s.ops:
                 if o.opcode not in OPCODES:
                     raise E.ErrUnsupported(f"graph: unknown opcode {o.opcode!r}")
+                want = ARITY.get(o.opcode)
+                if want is not None and (len(o.inputs), len(o.outputs)) != want:
+                    raise FormatError(f"{o.opcode} with {len(o.inputs)} inputs and {len(o.outputs)} outputs, "
+                                      f"want {want[0]} and {want[1]}")
+                if o.opcode == "while" and len(o.inputs) != len(o.outputs):
+                    raise FormatError(f"while with {len(o.inputs)} inputs and {len(o.outputs)} outputs")
+                if o.opcode == "if" and not o.inputs:
+                    raise FormatError("if without a condition")
                 for i in list(o.inputs) + list(o.outputs):
                     if not 0 <= i < nv:
                         raise FormatError(f"{o.opcode}: value index {i} out of range")
@@ -357,6 +375,13 @@ class Builder:
     def and_(self, a, b): return self._bin("and", a, b)
     def or_(self, a, b): return self._bin("or", a, b)
     def xor(self, a, b): return self._bin("xor", a, b)
+    def shl(self, a, b): return self._bin("shl", a, b)
+    def shr(self, a, b): return self._bin("shr", a, b)
+
+    def bitcast(self, x, dtype):
+        """Reinterprets the bits as another type of the same width."""
+        return self.op("bitcast", [x], [(dtype, x.dims)], to=DTYPES[dtype_name(dtype)])[0]
+
     def cmplt(self, a, b): return self._bin("cmplt", a, b, "i32")
     def cmpeq(self, a, b): return self._bin("cmpeq", a, b, "i32")
 

@@ -10,6 +10,7 @@ recorded for autograd: a run is inference.
 from __future__ import annotations
 
 import math
+import os
 import threading
 
 import torch
@@ -210,6 +211,18 @@ def _eval_primitive(c: _Call):
         return [_pow(i[0], i[1])]
     if code in ("idiv", "imod"):
         return [_idiv(i[0], i[1], code == "imod")]
+    if code in ("shl", "shr"):
+        if _is_float(i[0].dtype) or i[0].dtype == torch.bool:
+            raise E.ErrDType(f"graph: {code} of {i[0].dtype}")
+        sh = i[1].to(i[0].dtype)
+        return [torch.bitwise_left_shift(i[0], sh) if code == "shl" else torch.bitwise_right_shift(i[0], sh)]
+    if code == "bitcast":
+        to = c.attr("to")
+        if not isinstance(to, torch.dtype) or to == torch.bool or i[0].dtype == torch.bool:
+            raise G.FormatError("bitcast without a numeric dtype to reinterpret as")
+        if torch.empty((), dtype=to).element_size() != i[0].element_size():
+            raise E.ErrDType(f"graph: bitcast from {i[0].dtype} to {to} changes the width")
+        return [i[0].contiguous().view(to)]
     if code == "xor":
         return [(i[0] != i[1]).to(i[0].dtype)]
     if code == "cmplt":
@@ -785,7 +798,8 @@ class Session:
         self._lock = threading.Lock()
         self._broken = None
         self._recs: dict = {}        # (device, input shapes) -> run count, False, or (graph, inputs, outputs)
-        self.replay = True           # set to False to run every pass plainly on the GPU too
+        # False (or MIMIR_CUDA_GRAPHS=0) runs every pass plainly on the GPU too
+        self.replay = os.environ.get("MIMIR_CUDA_GRAPHS", "1") != "0"
 
     def reset(self) -> None:
         """Puts the variables back to their initial values (in their buffers, which recordings keep)."""

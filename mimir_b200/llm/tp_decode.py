@@ -17,6 +17,8 @@ every step.  Prompts run through bf16 tcgen05 GEMMs on dequantised weights.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 import math
 from dataclasses import dataclass
@@ -274,7 +276,7 @@ class TPDecoder:
         """Runs (or replays) one decode step; no host synchronisation."""
         lib = _native.lib()
         if self.graph is None:
-            if getattr(self, "_warm", 0) < 2:
+            if getattr(self, "_warm", 0) < 2 or os.environ.get("MIMIR_CUDA_GRAPHS", "1") == "0":
                 self._warm = getattr(self, "_warm", 0) + 1
                 before = lib.mimir_launch_count()
                 self._device_step()

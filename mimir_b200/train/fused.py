@@ -10,6 +10,8 @@ memory, so replays follow any schedule.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native
@@ -20,7 +22,8 @@ class FusedTrainer:
                  weight_decay: float = 0.1, use_graph: bool = True, schedule=None, dp=None):
         self.engine = engine
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
-        self.use_graph = use_graph
+        # MIMIR_CUDA_GRAPHS=0 runs every step as plain launches (reference: backend/cuda/batch_linux.go:63)
+        self.use_graph = use_graph and os.environ.get("MIMIR_CUDA_GRAPHS", "1") != "0"
         self.schedule = schedule
         self.dp = dp  # optional parallel.dp.FusedDataParallel
         self.graph = None

@@ -83,6 +83,26 @@ def test_integer_and_logic_primitives():
     assert out["y9"].tolist() == [3, -3, 4, 0]           # float -> int rounds toward zero
 
 
+def test_shifts_and_bitcast():
+    a = torch.tensor([1, -16, 5, 1 << 20], dtype=torch.int32)
+    b = G.Builder()
+    out = one(b, [("a", "i32", [4])],
+              lambda x: [b.shl(x, 3), b.shr(x, 2), b.bitcast(b.cast(x, "f32"), "i32"),
+                         b.bitcast(b.bitcast(b.cast(x, "f32"), "i32"), "f32")], {"a": a})
+    assert out["y0"].tolist() == [8, -128, 40, 1 << 23]
+    assert out["y1"].tolist() == [0, -4, 1, 1 << 18]                 # arithmetic shift on signed integers
+    assert out["y2"].tolist() == a.float().view(torch.int32).tolist()
+    assert out["y3"].tolist() == a.float().tolist()
+    b = G.Builder()
+    with pytest.raises(E.ErrDType):
+        one(b, [("a", "i32", [4])], lambda x: b.bitcast(x, "i64"), {"a": a})
+    g = G.Graph(values=[G.Value("x", "input", "f32", [2]), G.Value("y", "temp", "f32", [2])])
+    g.main.inputs = [0]
+    g.main.ops.append(G.Op("add", [0], [1]))                         # wrong arity is refused at load
+    with pytest.raises(G.FormatError):
+        g.check()
+
+
 def test_integer_division_by_zero_is_an_error():
     b = G.Builder()
     with pytest.raises(E.ErrDivideByZero):
