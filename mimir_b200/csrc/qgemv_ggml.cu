@@ -28,79 +28,106 @@ namespace mimir {
 namespace {
 
 // Every block format has an even block size and even field offsets, and rows start on even
-// addresses, so scales and 8-byte groups of quants can be read as 16-bit words.
-__device__ __forceinline__ float h2f(const uint8_t* p) {
-  return __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t*>(p)));
-}
+// addresses, so scales and groups of quants can be read as 16-bit words.
+// The bytes one lane needs from one unit, fetched in one go so that a lane can have several units
+// in flight before it decodes the first (the kernel is bound by memory latency).
+//   Q8_0 / Q4_0: w[0] = scale (fp16), w[1..2] = 8 quant bytes
+//   Q4_K       : w[0] = d | dmin << 16, w[1..3] = the 12 scale bytes, w[4..5] = 8 quant bytes
+//   Q6_K       : w[0] = d | scale byte << 16, w[1..2] = 8 low-nibble bytes, w[3..4] = 8 high-bit bytes
+struct RawUnit {
+  uint32_t w[6];
+};
 
-// eight consecutive bytes from a 2-byte aligned address
-__device__ __forceinline__ void ld_bytes8(const uint8_t* p, uint8_t out[8]) {
+__device__ __forceinline__ uint32_t ld_u16x2(const uint8_t* p) {   // 4 bytes from a 2-byte aligned address
   const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint16_t w = q[i];
-    out[2 * i] = static_cast<uint8_t>(w & 0xFF);
-    out[2 * i + 1] = static_cast<uint8_t>(w >> 8);
-  }
+  return static_cast<uint32_t>(q[0]) | (static_cast<uint32_t>(q[1]) << 16);
 }
 
-__device__ __forceinline__ void k4_scale_min(int j, const uint8_t* q, int& sc, int& mn) {
-  if (j < 4) {
-    sc = q[j] & 63;
-    mn = q[j + 4] & 63;
-  } else {
-    sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
-    mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
-  }
-}
-
-// Eight consecutive values of unit `unit` of a row, starting at `off` (0, 8, 16, 24) inside the
-// unit.  CODE is the file's dtype code: 64 Q8_0, 65 Q4_0, 66 Q4_K, 67 Q6_K.
+// CODE is the file's dtype code: 64 Q8_0, 65 Q4_0, 66 Q4_K, 67 Q6_K.  `off` (0, 8, 16, 24) is the
+// lane's position inside the unit of 32 values.
 template <int CODE>
-__device__ __forceinline__ void decode8(const uint8_t* __restrict__ row, int unit, int off, float v[8]) {
+__device__ __forceinline__ void fetch_unit(const uint8_t* __restrict__ row, int unit, int off, RawUnit& r) {
   if constexpr (CODE == 64) {
     const uint8_t* b = row + static_cast<size_t>(unit) * 34;
-    const float d = h2f(b);
-    uint8_t q[8];
-    ld_bytes8(b + 2 + off, q);
-#pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(static_cast<int8_t>(q[t]));
+    r.w[0] = *reinterpret_cast<const uint16_t*>(b);
+    r.w[1] = ld_u16x2(b + 2 + off);
+    r.w[2] = ld_u16x2(b + 6 + off);
   } else if constexpr (CODE == 65) {
     const uint8_t* b = row + static_cast<size_t>(unit) * 18;
-    const float d = h2f(b);
-    const int sh = off < 16 ? 0 : 4;
-    uint8_t q[8];
-    ld_bytes8(b + 2 + (off & 15), q);
-#pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(((q[t] >> sh) & 0xF) - 8);
+    r.w[0] = *reinterpret_cast<const uint16_t*>(b);
+    r.w[1] = ld_u16x2(b + 2 + (off & 15));
+    r.w[2] = ld_u16x2(b + 6 + (off & 15));
   } else if constexpr (CODE == 66) {
-    const int sb = unit >> 3, sub = unit & 7;
-    const uint8_t* b = row + static_cast<size_t>(sb) * 144;
-    const float d = h2f(b), dmin = h2f(b + 2);
+    // super-blocks of 144 bytes in rows that start 16-byte aligned: 4- and 8-byte loads are aligned
+    const uint8_t* b = row + static_cast<size_t>(unit >> 3) * 144;
+    const uint32_t* h = reinterpret_cast<const uint32_t*>(b);
+    r.w[0] = h[0];
+    r.w[1] = h[1]; r.w[2] = h[2]; r.w[3] = h[3];
+    const uint2 q = *reinterpret_cast<const uint2*>(b + 16 + ((unit & 7) >> 1) * 32 + off);
+    r.w[4] = q.x; r.w[5] = q.y;
+  } else {
+    const int sub = unit & 7, half = sub >> 2, quarter = sub & 3;
+    const uint8_t* b = row + static_cast<size_t>(unit >> 3) * 210;
+    const uint32_t sc = b[192 + 8 * half + 2 * quarter + (off >> 4)];
+    r.w[0] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(b + 208)) | (sc << 16);
+    const uint8_t* ql = b + 64 * half + ((quarter & 1) ? 32 : 0) + off;
+    const uint8_t* qh = b + 128 + 32 * half + off;
+    r.w[1] = ld_u16x2(ql); r.w[2] = ld_u16x2(ql + 4);
+    r.w[3] = ld_u16x2(qh); r.w[4] = ld_u16x2(qh + 4);
+  }
+}
+
+__device__ __forceinline__ float half_bits(uint32_t lo16) {
+  return __half2float(__ushort_as_half(static_cast<uint16_t>(lo16 & 0xFFFF)));
+}
+
+__device__ __forceinline__ uint32_t byte_of(uint32_t lo, uint32_t hi, int t) {
+  return ((t < 4 ? lo : hi) >> (8 * (t & 3))) & 0xFF;
+}
+
+// Eight consecutive values of the unit from its fetched bytes.
+template <int CODE>
+__device__ __forceinline__ void decode_unit(const RawUnit& r, int unit, int off, float v[8]) {
+  if constexpr (CODE == 64) {
+    const float d = half_bits(r.w[0]);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(static_cast<int8_t>(byte_of(r.w[1], r.w[2], t)));
+  } else if constexpr (CODE == 65) {
+    const float d = half_bits(r.w[0]);
+    const int sh = off < 16 ? 0 : 4;
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+      v[t] = d * static_cast<float>(static_cast<int>((byte_of(r.w[1], r.w[2], t) >> sh) & 0xF) - 8);
+  } else if constexpr (CODE == 66) {
+    const int sub = unit & 7;
+    const float d = half_bits(r.w[0]), dmin = half_bits(r.w[0] >> 16);
+    // byte i of the 12 packed 6-bit scales / minimums, picked from the three words without an array
+    auto sbyte = [&](int i) -> int {
+      const uint32_t word = i < 4 ? r.w[1] : (i < 8 ? r.w[2] : r.w[3]);
+      return static_cast<int>((word >> (8 * (i & 3))) & 0xFF);
+    };
     int sc, mn;
-    k4_scale_min(sub, b + 4, sc, mn);
+    if (sub < 4) {
+      sc = sbyte(sub) & 63;
+      mn = sbyte(sub + 4) & 63;
+    } else {
+      sc = (sbyte(sub + 4) & 0xF) | ((sbyte(sub - 4) >> 6) << 4);
+      mn = (sbyte(sub + 4) >> 4) | ((sbyte(sub) >> 6) << 4);
+    }
     const float ds = d * sc, m = dmin * mn;
     const int sh = (sub & 1) ? 4 : 0;
-    uint8_t q[8];
-    ld_bytes8(b + 16 + (sub >> 1) * 32 + off, q);
 #pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = ds * static_cast<float>((q[t] >> sh) & 0xF) - m;
+    for (int t = 0; t < 8; ++t) v[t] = ds * static_cast<float>((byte_of(r.w[4], r.w[5], t) >> sh) & 0xF) - m;
   } else {
-    const int sb = unit >> 3, sub = unit & 7;
-    const uint8_t* b = row + static_cast<size_t>(sb) * 210;
-    const int half = sub >> 2, quarter = sub & 3;
-    uint8_t ql[8], qh[8];
-    ld_bytes8(b + 64 * half + ((quarter & 1) ? 32 : 0) + off, ql);
-    ld_bytes8(b + 128 + 32 * half + off, qh);
-    const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192) + 8 * half + 2 * quarter;
-    const float d = h2f(b + 208);
-    const int sh = (quarter & 2) ? 4 : 0;
+    const int quarter = unit & 3;
+    const float d = half_bits(r.w[0]);
     // the lane's eight values lie inside one group of 16, so they share one scale
-    const float ds = d * static_cast<float>(sc[off >> 4]);
+    const float ds = d * static_cast<float>(static_cast<int8_t>((r.w[0] >> 16) & 0xFF));
+    const int sh = (quarter & 2) ? 4 : 0;
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
-      const int lo = (ql[t] >> sh) & 0xF;
-      const int hi = (qh[t] >> (2 * quarter)) & 3;
+      const int lo = (byte_of(r.w[1], r.w[2], t) >> sh) & 0xF;
+      const int hi = (byte_of(r.w[3], r.w[4], t) >> (2 * quarter)) & 3;
       v[t] = ds * static_cast<float>((lo | (hi << 4)) - 32);
     }
   }
@@ -130,6 +157,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float x[8]) {
 }
 
 constexpr int kRowsPerPass = 4;
+constexpr int kUnitsInFlight = 4;   // units a lane fetches before it decodes the first
 constexpr int kWarpsPerBlock = 8;
 
 template <int CODE, typename XT>
@@ -146,17 +174,26 @@ qgemv_ggml_kernel(const uint8_t* __restrict__ w, const XT* __restrict__ x, int l
     float acc[kRowsPerPass];
 #pragma unroll
     for (int r = 0; r < kRowsPerPass; ++r) acc[r] = 0.f;
-    for (int u = lane >> 2; u < units; u += 8) {
-      float v[8];
-      decode8<CODE>(row, u, off, v);
-      const int k = u * 32 + off;
+    for (int u0 = lane >> 2; u0 < units; u0 += 8 * kUnitsInFlight) {
+      RawUnit raw[kUnitsInFlight];
 #pragma unroll
-      for (int r = 0; r < kRowsPerPass; ++r) {
-        if (b0 + r < B) {
-          float xv[8];
-          load8(x + static_cast<size_t>(b0 + r) * ldx + k, xv);
+      for (int j = 0; j < kUnitsInFlight; ++j)
+        if (u0 + 8 * j < units) fetch_unit<CODE>(row, u0 + 8 * j, off, raw[j]);
 #pragma unroll
-          for (int t = 0; t < 8; ++t) acc[r] = fmaf(v[t], xv[t], acc[r]);
+      for (int j = 0; j < kUnitsInFlight; ++j) {
+        const int u = u0 + 8 * j;
+        if (u >= units) break;
+        float v[8];
+        decode_unit<CODE>(raw[j], u, off, v);
+        const int k = u * 32 + off;
+#pragma unroll
+        for (int r = 0; r < kRowsPerPass; ++r) {
+          if (b0 + r < B) {
+            float xv[8];
+            load8(x + static_cast<size_t>(b0 + r) * ldx + k, xv);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) acc[r] = fmaf(v[t], xv[t], acc[r]);
+          }
         }
       }
     }
