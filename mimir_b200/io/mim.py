@@ -357,3 +357,43 @@ def apply_lora(module, adapter: "Model") -> int:
         wrapped.lora_b.set(adapter.tensor(path + ".lora_b").clone().to(wrapped.lora_b.dtype))
         done += 1
     return done
+
+
+def describe(path, out=None) -> None:
+    """Prints what a ``.mim`` file holds: version, sections with their hashes, tensors, metadata keys
+    and, when there is a graph this package can read, its inputs and outputs."""
+    import sys
+    out = out or sys.stdout
+    names = {SECTION_WEIGHTS: "weights", SECTION_METADATA: "metadata", SECTION_GRAPH: "graph",
+             SECTION_TRAINING: "training"}
+    dts = {F32: "f32", F16: "f16", BF16: "bf16", U8: "u8", Q8_0: "q8_0", Q4_0: "q4_0", Q4_K: "q4_k", Q6_K: "q6_k"}
+    with open(path) as m:
+        print(f"{path}: version {m.major}.{m.minor}, alignment {m.alignment}, hashes "
+              f"{'ok' if m.verify() else 'MISMATCH'}", file=out)
+        for s in m.sections:
+            print(f"  section {names.get(s['kind'], s['kind'])}: {s['length']} bytes, sha256 {s['sha256'].hex()[:16]}…",
+                  file=out)
+        for n in m.names():
+            dt, shape, nb = m.info(n)
+            torch_dt = _TORCH.get(dt)
+            label = dts.get(dt) or (str(torch_dt).replace("torch.", "") if torch_dt is not None else f"dtype {dt}")
+            print(f"  tensor {n}: {label} {list(shape)} ({nb} bytes)", file=out)
+        md = m.metadata
+        for k in sorted(md):
+            v = md[k]
+            text = f"[{len(v)} values]" if isinstance(v, list) and len(v) > 8 else repr(v)
+            print(f"  metadata {k} = {text}", file=out)
+        if m.has_graph():
+            try:
+                print(f"  graph inputs {m.inputs}", file=out)
+                print(f"  graph outputs {m.outputs}", file=out)
+            except Exception as exc:  # noqa: BLE001 - a graph in another encoding is reported, not fatal
+                print(f"  graph: {exc}", file=out)
+
+
+if __name__ == "__main__":
+    import sys
+    if len(sys.argv) != 2:
+        print("usage: python -m mimir_b200.io.mim <file.mim>", file=sys.stderr)
+        raise SystemExit(2)
+    describe(sys.argv[1])

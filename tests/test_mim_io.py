@@ -55,3 +55,20 @@ def test_write_read_round_trip_with_typed_metadata(tmp_path):
     data = open(path, "rb").read()
     with pytest.raises(mim.MimError):
         mim.parse(data[:-1])
+
+
+def test_describe_lists_sections_tensors_metadata_and_graph(tmp_path):
+    import io as _io
+    import torch
+    from mimir_b200 import nn
+    from mimir_b200 import tensor as T
+    from mimir_b200.io import export, mim
+    p = tmp_path / "d.mim"
+    export.export(p, nn.Sequential(nn.Linear(4, 3), nn.ReLU()), T.tensor(torch.randn(2, 4)),
+                  metadata={"general.name": "tiny"})
+    buf = _io.StringIO()
+    mim.describe(p, out=buf)
+    text = buf.getvalue()
+    for want in ("hashes ok", "section weights", "section graph", "tensor layers.0.weight: f32 [3, 4]",
+                 "metadata general.name = 'tiny'", "graph inputs [('input', 'f32', [2, 4])]"):
+        assert want in text, text
