@@ -9,9 +9,12 @@
 // Q4_0 block, or one of the eight sub-blocks of a 256-value K-quant super-block);
 // four lanes share a unit, eight values each, so a warp covers 256 values per
 // iteration and every lane's eight weights come from 8 consecutive bytes (Q6_K: 8
-// low-nibble bytes plus 8 high-bit bytes).  Up to four activation rows are held per
-// pass; larger batches loop.  fp32 accumulation, one shuffle reduction per
-// row at the end.
+// low-nibble bytes plus 8 high-bit bytes).  A lane fetches the bytes of two units before it
+// decodes the first.  Quants become floats without conversion instructions (OR into the
+// mantissa of 2^23, one subtraction that also removes the zero point); the block scale and
+// Q4_K's constant term are applied once per unit to sum(q*x) and sum(x), so a weight costs one
+// FMA per activation row.  Up to four activation rows are held per pass; larger batches loop.
+// fp32 accumulation, one shuffle reduction per row at the end.
 //
 // Replaces the reference's qmatmul kernel (backend/internal/gen/quant.go:156-209:
 // 8 outputs per block, 32 threads per output, fp32 dequant, shared-memory tree sum),
@@ -81,23 +84,36 @@ __device__ __forceinline__ float half_bits(uint32_t lo16) {
   return __half2float(__ushort_as_half(static_cast<uint16_t>(lo16 & 0xFFFF)));
 }
 
-__device__ __forceinline__ uint32_t byte_of(uint32_t lo, uint32_t hi, int t) {
-  return ((t < 4 ? lo : hi) >> (8 * (t & 3))) & 0xFF;
+// An integer field below 2^23 as a float without a conversion instruction: OR it into the mantissa
+// of 2^23 and subtract 2^23 plus the format's zero point.
+__device__ __forceinline__ float field_to_float(uint32_t field, float magic_minus_zero) {
+  return __uint_as_float(0x4B000000u | field) - magic_minus_zero;
 }
 
-// Eight consecutive values of the unit from its fetched bytes.
+// The unit's eight values as q[t] (integers held in floats, zero point already removed), a scale
+// and a constant term: value t = scale * q[t] - minus.  The product with the activations then needs
+// one FMA per value; scale and minus are applied once per unit on the sums.
 template <int CODE>
-__device__ __forceinline__ void decode_unit(const RawUnit& r, int unit, int off, float v[8]) {
+__device__ __forceinline__ void decode_unit(const RawUnit& r, int unit, int off, float q[8], float& scale,
+                                            float& minus) {
+  constexpr float kTwo23 = 8388608.f;
+  minus = 0.f;
   if constexpr (CODE == 64) {
-    const float d = half_bits(r.w[0]);
+    scale = half_bits(r.w[0]);
 #pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = d * static_cast<float>(static_cast<int8_t>(byte_of(r.w[1], r.w[2], t)));
+    for (int t = 0; t < 8; ++t) {
+      const uint32_t w = t < 4 ? r.w[1] : r.w[2];
+      // a signed byte: flip its top bit to make it unsigned, remove 128 again with the magic constant
+      q[t] = field_to_float(((w >> (8 * (t & 3))) & 0xFF) ^ 0x80, kTwo23 + 128.f);
+    }
   } else if constexpr (CODE == 65) {
-    const float d = half_bits(r.w[0]);
+    scale = half_bits(r.w[0]);
     const int sh = off < 16 ? 0 : 4;
 #pragma unroll
-    for (int t = 0; t < 8; ++t)
-      v[t] = d * static_cast<float>(static_cast<int>((byte_of(r.w[1], r.w[2], t) >> sh) & 0xF) - 8);
+    for (int t = 0; t < 8; ++t) {
+      const uint32_t w = t < 4 ? r.w[1] : r.w[2];
+      q[t] = field_to_float((w >> (8 * (t & 3) + sh)) & 0xF, kTwo23 + 8.f);
+    }
   } else if constexpr (CODE == 66) {
     const int sub = unit & 7;
     const float d = half_bits(r.w[0]), dmin = half_bits(r.w[0] >> 16);
@@ -114,21 +130,25 @@ __device__ __forceinline__ void decode_unit(const RawUnit& r, int unit, int off,
       sc = (sbyte(sub + 4) & 0xF) | ((sbyte(sub - 4) >> 6) << 4);
       mn = (sbyte(sub + 4) >> 4) | ((sbyte(sub) >> 6) << 4);
     }
-    const float ds = d * sc, m = dmin * mn;
+    scale = d * static_cast<float>(sc);
+    minus = dmin * static_cast<float>(mn);
     const int sh = (sub & 1) ? 4 : 0;
 #pragma unroll
-    for (int t = 0; t < 8; ++t) v[t] = ds * static_cast<float>((byte_of(r.w[4], r.w[5], t) >> sh) & 0xF) - m;
+    for (int t = 0; t < 8; ++t) {
+      const uint32_t w = t < 4 ? r.w[4] : r.w[5];
+      q[t] = field_to_float((w >> (8 * (t & 3) + sh)) & 0xF, kTwo23);
+    }
   } else {
     const int quarter = unit & 3;
-    const float d = half_bits(r.w[0]);
     // the lane's eight values lie inside one group of 16, so they share one scale
-    const float ds = d * static_cast<float>(static_cast<int8_t>((r.w[0] >> 16) & 0xFF));
+    scale = half_bits(r.w[0]) * static_cast<float>(static_cast<int8_t>((r.w[0] >> 16) & 0xFF));
     const int sh = (quarter & 2) ? 4 : 0;
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
-      const int lo = (byte_of(r.w[1], r.w[2], t) >> sh) & 0xF;
-      const int hi = (byte_of(r.w[3], r.w[4], t) >> (2 * quarter)) & 3;
-      v[t] = ds * static_cast<float>((lo | (hi << 4)) - 32);
+      const uint32_t wl = t < 4 ? r.w[1] : r.w[2], wh = t < 4 ? r.w[3] : r.w[4];
+      const uint32_t lo = (wl >> (8 * (t & 3) + sh)) & 0xF;
+      const uint32_t hi = (wh >> (8 * (t & 3) + 2 * quarter)) & 3;
+      q[t] = field_to_float(lo | (hi << 4), kTwo23 + 32.f);
     }
   }
 }
@@ -157,7 +177,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float x[8]) {
 }
 
 constexpr int kRowsPerPass = 4;
-constexpr int kUnitsInFlight = 4;   // units a lane fetches before it decodes the first
+constexpr int kUnitsInFlight = 2;   // units a lane fetches before it decodes the first
 constexpr int kWarpsPerBlock = 8;
 
 template <int CODE, typename XT>
@@ -183,16 +203,22 @@ qgemv_ggml_kernel(const uint8_t* __restrict__ w, const XT* __restrict__ x, int l
       for (int j = 0; j < kUnitsInFlight; ++j) {
         const int u = u0 + 8 * j;
         if (u >= units) break;
-        float v[8];
-        decode_unit<CODE>(raw[j], u, off, v);
+        float q[8], scale, minus;
+        decode_unit<CODE>(raw[j], u, off, q, scale, minus);
         const int k = u * 32 + off;
 #pragma unroll
         for (int r = 0; r < kRowsPerPass; ++r) {
           if (b0 + r < B) {
             float xv[8];
             load8(x + static_cast<size_t>(b0 + r) * ldx + k, xv);
+            float dot = 0.f, sum = 0.f;
 #pragma unroll
-            for (int t = 0; t < 8; ++t) acc[r] = fmaf(v[t], xv[t], acc[r]);
+            for (int t = 0; t < 8; ++t) {
+              dot = fmaf(q[t], xv[t], dot);
+              if constexpr (CODE == 66) sum += xv[t];     // only Q4_K has a constant term
+            }
+            acc[r] = fmaf(scale, dot, acc[r]);
+            if constexpr (CODE == 66) acc[r] = fmaf(-minus, sum, acc[r]);
           }
         }
       }

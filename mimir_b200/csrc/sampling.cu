@@ -46,6 +46,74 @@ __device__ __forceinline__ uint32_t fkey(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Calls f(index, value) for every logit of the row that belongs to this thread.  Rows that start on
+// a 16-byte boundary are read eight values per 16-byte load, four loads in flight per thread (one
+// block walks a whole row, so the bytes it keeps in flight set its speed); the order in which a
+// thread sees its values is of no consequence to any caller.
+constexpr int kLoadsInFlight = 4;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float v[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+  }
+}
+
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const __nv_bfloat16* x, int V, int tid, F f) {
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int groups = V / 8;
+    for (int g0 = tid; g0 < groups; g0 += kLoadsInFlight * kSampleThreads) {
+      uint4 u[kLoadsInFlight];
+#pragma unroll
+      for (int j = 0; j < kLoadsInFlight; ++j) {
+        const int g = g0 + j * kSampleThreads;
+        if (g < groups) u[j] = *reinterpret_cast<const uint4*>(x + g * 8);
+      }
+#pragma unroll
+      for (int j = 0; j < kLoadsInFlight; ++j) {
+        const int g = g0 + j * kSampleThreads;
+        if (g < groups) {
+          float v[8];
+          unpack8(u[j], v);
+#pragma unroll
+          for (int t = 0; t < 8; ++t) f(g * 8 + t, v[t]);
+        }
+      }
+    }
+    done = groups * 8;
+  }
+  for (int i = done + tid; i < V; i += kSampleThreads) f(i, __bfloat162float(x[i]));
+}
+
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* x, int V, int tid, F f) {
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int groups = V / 4;
+    for (int g0 = tid; g0 < groups; g0 += kLoadsInFlight * kSampleThreads) {
+      float4 u[kLoadsInFlight];
+#pragma unroll
+      for (int j = 0; j < kLoadsInFlight; ++j) {
+        const int g = g0 + j * kSampleThreads;
+        if (g < groups) u[j] = *reinterpret_cast<const float4*>(x + g * 4);
+      }
+#pragma unroll
+      for (int j = 0; j < kLoadsInFlight; ++j) {
+        const int g = g0 + j * kSampleThreads;
+        if (g < groups) {
+          f(g * 4, u[j].x); f(g * 4 + 1, u[j].y); f(g * 4 + 2, u[j].z); f(g * 4 + 3, u[j].w);
+        }
+      }
+    }
+    done = groups * 4;
+  }
+  for (int i = done + tid; i < V; i += kSampleThreads) f(i, x[i]);
+}
+
 struct SampleSmem {
   uint32_t hist[32][256];     // one histogram per warp
   float cval[kMaxCand];
@@ -54,8 +122,8 @@ struct SampleSmem {
   float red_f[32];
   int red_i[32];
   uint32_t prefix, need;
-  int n_greater, tie_base;
-  float zfull;
+  int n_greater, tie_base, n_equal;
+  float zfull, tie_val;
 };
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -76,7 +144,7 @@ __device__ __forceinline__ bool before(float va, int ia, float vb, int ib) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kSampleThreads)
+__global__ void __launch_bounds__(kSampleThreads, 1)
 sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, int top_k, float top_p, float min_p,
               uint64_t seed, uint64_t draw, const int* __restrict__ draw_dev, int* __restrict__ out_tok,
               float* __restrict__ out_prob) {
@@ -91,10 +159,9 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, in
   if (temperature <= 0.f || top_k == 1) {
     float bv = -FLT_MAX;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += kSampleThreads) {
-      const float v = ldf(x + i);
+    for_each_logit(x, V, tid, [&](int i, float v) {
       if (before(v, i, bv, bi)) { bv = v; bi = i; }
-    }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -123,10 +190,10 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, in
     __syncthreads();
     const uint32_t prefix = sm.prefix;
     const int shift = 8 * pass;
-    for (int i = tid; i < V; i += kSampleThreads) {
-      const uint32_t key = fkey(ldf(x + i));
+    for_each_logit(x, V, tid, [&](int, float v) {
+      const uint32_t key = fkey(v);
       if ((key & mask) == prefix) atomicAdd(&sm.hist[warp][(key >> shift) & 255], 1u);
-    }
+    });
     __syncthreads();
     if (tid < 256) {
       uint32_t s = 0;
@@ -153,45 +220,67 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, in
   const int n_greater_expected = k - need_ties;
 
   // ---- 2. gather: keys above the threshold in any order, equal keys in index order
-  if (tid == 0) { sm.n_greater = 0; sm.tie_base = 0; }
+  if (tid == 0) { sm.n_greater = 0; sm.tie_base = 0; sm.n_equal = 0; }
   for (int i = tid; i < kMaxCand; i += kSampleThreads) { sm.cval[i] = -FLT_MAX; sm.cidx[i] = 0x7fffffff; }
   __syncthreads();
-  for (int i = tid; i < V; i += kSampleThreads) {
-    const float v = ldf(x + i);
-    if (fkey(v) > thr) {
+  int* eq = reinterpret_cast<int*>(sm.scan);      // indices of the logits equal to the threshold (scan is free until step 4)
+  for_each_logit(x, V, tid, [&](int i, float v) {
+    const uint32_t key = fkey(v);
+    if (key > thr) {
       const int pos = atomicAdd(&sm.n_greater, 1);
       if (pos < kMaxCand) { sm.cval[pos] = v; sm.cidx[pos] = i; }
+    } else if (key == thr) {
+      const int pos = atomicAdd(&sm.n_equal, 1);
+      if (pos < kMaxCand) eq[pos] = i;
+      sm.tie_val = v;                              // every such logit has the same bits
     }
-  }
+  });
   __syncthreads();
-  for (int base = 0; base < V; base += kSampleThreads) {
-    const int taken = sm.tie_base;
-    if (taken >= need_ties) break;
-    const int i = base + tid;
-    float v = 0.f;
-    bool tie = false;
-    if (i < V) { v = ldf(x + i); tie = fkey(v) == thr; }
-    const uint32_t ballot = __ballot_sync(0xffffffffu, tie);
-    if (lane == 0) sm.red_i[warp] = __popc(ballot);
-    __syncthreads();
-    int before_me = taken;
-    for (int w = 0; w < warp; ++w) before_me += sm.red_i[w];
-    const int pos = before_me + __popc(ballot & ((1u << lane) - 1u));
-    if (tie && pos < need_ties) { sm.cval[n_greater_expected + pos] = v; sm.cidx[n_greater_expected + pos] = i; }
-    __syncthreads();
-    if (tid == 0) {
-      int t = taken;
-      for (int w = 0; w < kSampleThreads / 32; ++w) t += sm.red_i[w];
-      sm.tie_base = t;
+  const int n_equal = sm.n_equal;
+  if (n_equal <= kMaxCand) {
+    // the usual case, a handful of equal logits: each one counts the equal logits with a smaller
+    // index, and the need_ties lowest indices enter the candidate list
+    if (tid < n_equal) {
+      const int me = eq[tid];
+      int rank = 0;
+      for (int j = 0; j < n_equal; ++j) rank += eq[j] < me ? 1 : 0;
+      if (rank < need_ties) { sm.cval[n_greater_expected + rank] = sm.tie_val; sm.cidx[n_greater_expected + rank] = me; }
     }
     __syncthreads();
+  } else {
+    // more than 1024 equal logits: walk the row in index order, tile by tile, until enough are taken
+    for (int base = 0; base < V; base += kSampleThreads) {
+      const int taken = sm.tie_base;
+      if (taken >= need_ties) break;
+      const int i = base + tid;
+      float v = 0.f;
+      bool tie = false;
+      if (i < V) { v = ldf(x + i); tie = fkey(v) == thr; }
+      const uint32_t ballot = __ballot_sync(0xffffffffu, tie);
+      if (lane == 0) sm.red_i[warp] = __popc(ballot);
+      __syncthreads();
+      int before_me = taken;
+      for (int w = 0; w < warp; ++w) before_me += sm.red_i[w];
+      const int pos = before_me + __popc(ballot & ((1u << lane) - 1u));
+      if (tie && pos < need_ties) { sm.cval[n_greater_expected + pos] = v; sm.cidx[n_greater_expected + pos] = i; }
+      __syncthreads();
+      if (tid == 0) {
+        int t = taken;
+        for (int w = 0; w < kSampleThreads / 32; ++w) t += sm.red_i[w];
+        sm.tie_base = t;
+      }
+      __syncthreads();
+    }
   }
 
-  // ---- 3. bitonic sort of the 1024 slots by (value descending, index ascending)
-  for (int size = 2; size <= kMaxCand; size <<= 1) {
+  // ---- 3. bitonic sort of the first n_sort slots (the power of two that holds the k candidates;
+  //         the slots behind them are padding) by (value descending, index ascending)
+  int n_sort = 2;
+  while (n_sort < k) n_sort <<= 1;
+  for (int size = 2; size <= n_sort; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       const int other = tid ^ stride;
-      if (other > tid) {
+      if (other > tid && other < n_sort) {
         const float va = sm.cval[tid], vb = sm.cval[other];
         const int ia = sm.cidx[tid], ib = sm.cidx[other];
         const bool up = (tid & size) == 0;
@@ -207,7 +296,7 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, in
   const bool full_vocab = top_k <= 0 && V > kMaxCand;
   if (full_vocab) {
     float s = 0.f;
-    for (int i = tid; i < V; i += kSampleThreads) s += __expf((ldf(x + i) - vmax) * inv_t);
+    for_each_logit(x, V, tid, [&](int, float v) { s += __expf((v - vmax) * inv_t); });
     s = block_sum(s, sm.red_f);
     if (tid == 0) sm.zfull = s;
     __syncthreads();
