@@ -20,6 +20,14 @@ class UInt64(int):
 
 
 def decode(section: bytes) -> dict:
+    """Typed metadata section -> dict; a damaged section is a ``ValueError``."""
+    try:
+        return _decode(section)
+    except (struct.error, IndexError, UnicodeDecodeError, OverflowError, MemoryError) as exc:
+        raise ValueError(f"metadata section is damaged: {exc}") from None
+
+
+def _decode(section: bytes) -> dict:
     if len(section) < 16 or section[:4] not in (b"MIMM", b"MMFM"):
         raise ValueError("not a metadata section")
     count, pool_bytes = struct.unpack_from("<IQ", section, 4)

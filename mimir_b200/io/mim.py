@@ -101,7 +101,7 @@ class Model:
         lib.mimir_mim_info(handle, *[ctypes.byref(v) for v in vals])
         self.major, self.minor, self.alignment, nt, ns, mmf = (v.value for v in vals)
         self.legacy_magic = bool(mmf)
-        size = lib.mimir_mim_size(handle)
+        size = size_total = lib.mimir_mim_size(handle)
         base = lib.mimir_mim_base(handle)
         self._buf = (ctypes.c_uint8 * size).from_address(base)
         self._np = np.frombuffer(self._buf, dtype=np.uint8)
@@ -113,7 +113,21 @@ class Model:
             _check(lib.mimir_mim_tensor(handle, i, ctypes.byref(name), ctypes.byref(nl), ctypes.byref(dt),
                                         ctypes.byref(rank), dims, ctypes.byref(off), ctypes.byref(nb)))
             nm = ctypes.string_at(name, nl.value).decode("utf-8")
-            self._index[nm] = (dt.value, tuple(dims[d] for d in range(rank.value)), off.value, nb.value)
+            shape = tuple(dims[d] for d in range(rank.value))
+            count = math.prod(shape)
+            if dt.value in _TORCH:
+                want = count * torch.empty((), dtype=_TORCH[dt.value]).element_size()
+            elif dt.value in QUANT_BLOCK:
+                per, size = QUANT_BLOCK[dt.value]
+                want = count // per * size if count % per == 0 else -1
+            else:
+                want = nb.value       # a dtype this reader does not decode: refused when it is asked for
+            if want != nb.value or off.value + nb.value > size_total:
+                lib.mimir_mim_close(handle)
+                self._h = None
+                raise MimError(f"tensor {nm!r}: {nb.value} bytes at offset {off.value} for shape {list(shape)} "
+                               f"of dtype code {dt.value}")
+            self._index[nm] = (dt.value, shape, off.value, nb.value)
         self.sections = []
         kind, flags = ctypes.c_int(), ctypes.c_int()
         h32 = ctypes.create_string_buffer(32)
