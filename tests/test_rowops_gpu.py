@@ -64,13 +64,15 @@ def test_rmsnorm_fwd_bwd(rows, C):
     close(dg, gr.grad, 3e-2)
 
 
-def test_cross_entropy_padded_vocab():
+@pytest.mark.parametrize("rows,V,Vp", [(50, 1000, 1024), (9, 16384, 16384), (7, 32000, 32000), (5, 50257, 50304),
+                                       (3, 65536, 65536), (3, 70001, 70016), (2, 128256, 128256)])
+def test_cross_entropy_padded_vocab(rows, V, Vp):
+    """Vocabularies from 1000 to 128256 columns, padded or not, in place, out of place and loss only."""
     from mimir_b200.ops import kernels as K
     torch.manual_seed(2)
-    rows, V, Vp = 50, 1000, 1024
     logits = torch.randn(rows, Vp, device="cuda").bfloat16() * 3
     tgt = torch.randint(0, V, (rows,), device="cuda")
-    tgt[3] = -100
+    tgt[min(3, rows - 1)] = -100
     lr = logits[:, :V].float().requires_grad_(True)
     ref = F.cross_entropy(lr, tgt, ignore_index=-100, reduction="sum") / rows
     ref.backward()
@@ -80,7 +82,15 @@ def test_cross_entropy_padded_vocab():
     K.cross_entropy(work, tgt, loss_rows, work, mean, V, 1.0 / rows, 1.0 / rows)
     assert abs(mean.item() - ref.item()) < 2e-2 * abs(ref.item())
     close(work[:, :V], lr.grad, 3e-2)
-    assert work[:, V:].abs().max().item() == 0
+    if Vp > V:
+        assert work[:, V:].abs().max().item() == 0
+    # not in place, and loss only
+    out = torch.full_like(logits, 7.0)
+    K.cross_entropy(logits, tgt, loss_rows, out, mean, V, 1.0 / rows, 1.0 / rows)
+    assert torch.equal(out, work)
+    loss2 = torch.empty(rows, device="cuda")
+    K.cross_entropy(logits, tgt, loss2, None, None, V, 1.0, 1.0)
+    assert torch.equal(loss2, loss_rows)
 
 
 def test_colsum_embedding_adamw():
