@@ -466,7 +466,7 @@ norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 }
 
 // The same block-spans-the-row form, software pipelined: the packed x / dy / dres values, mean and
-// rstd of the NEXT group of R rows are requested before the current group is reduced, exchanged
+// rstd of the next TWO groups of R rows are requested before the current group is reduced, exchanged
 // through shared memory and stored, so loads stay in flight through the whole loop (the form above
 // has none in flight while it reduces and stores: it measured 16 % of DRAM peak with the long
 // scoreboard as its main stall).
@@ -499,7 +499,7 @@ norm_bwd_rows_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
   for (int j = 0; j < 8; ++j) { g[j] = 0.f; dg[j] = 0.f; db[j] = 0.f; }
   if (active) load8(gamma + c, g);
   const float invC = 1.f / C;
-  NormBwdRaw cur[R], nxt[R];
+  NormBwdRaw cur[R], nxt[R], nxt2[R];   // the current group and the two groups requested ahead of it
   auto fetch = [&](NormBwdRaw (&b)[R], int first) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -517,9 +517,10 @@ norm_bwd_rows_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
   const int step = gridDim.x * R;
   int row0 = blockIdx.x * R;
   if (row0 < rows) fetch(cur, row0);
+  if (row0 + step < rows) fetch(nxt, row0 + step);
   int parity = 0;
   for (; row0 < rows; row0 += step, parity ^= 1) {
-    if (row0 + step < rows) fetch(nxt, row0 + step);
+    if (row0 + 2 * step < rows) fetch(nxt2, row0 + 2 * step);
     float xh[R][8], d[R][8], sums[2 * R], rs[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -571,7 +572,7 @@ norm_bwd_rows_pipe_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloa
       }
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+    for (int r = 0; r < R; ++r) { cur[r] = nxt[r]; nxt[r] = nxt2[r]; }
   }
   if (active) {
     float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * C + c;
