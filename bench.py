@@ -12,6 +12,11 @@ device-timed loop (CUDA events, max over ranks); ``e2e`` is the same metric
 through ``FusedTrainer.step`` with the host->device copy of every batch from
 pinned memory and the device->host read of the loss inside the timed region.
 ``--impl reference`` reports that the reference (a Go program) cannot run here.
+``--impl baseline`` runs the same model, batch, optimizer and timing code in plain PyTorch
+(cuBLAS bf16 products, flash SDPA, fused AdamW over fp32 masters, NCCL DDP; the step captured in
+a CUDA graph on one GPU): ``baseline/torch_baselines.py``, which imports nothing of this package.
+Its measured numbers are kept in ``baseline/measured.json``; the native arm reports
+``vs_library_baseline`` against them.
 """
 from __future__ import annotations
 
@@ -92,6 +97,20 @@ class ClockSampler:
         return out
 
 
+def _against_library_baseline(world: int, value: float, e2e: float) -> dict:
+    """Ratios against the recorded run of ``--impl baseline`` on the same number of GPUs
+    (``baseline/measured.json``, written from that arm's output on the same kind of box)."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "measured.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)["gpt2_small_dp"][str(world)]
+    except (OSError, KeyError, ValueError):
+        return {"vs_library_baseline": None}
+    return {"vs_library_baseline": {"ratio": value / rec["value"], "e2e_ratio": e2e / rec["e2e"],
+                                    "baseline_tokens_per_s": rec["value"], "baseline_e2e_tokens_per_s": rec["e2e"],
+                                    "direction": "ours / baseline, higher is better"}}
+
+
 def reference_arm(args) -> int:
     print(json.dumps({
         "impl": "reference",
@@ -106,7 +125,7 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=1024)
     ap.add_argument("--attention", default="native")
@@ -141,34 +160,53 @@ def main() -> int:
     torch.cuda.set_device(local_rank)
     warmup = max(args.warmup, 3)
 
-    from mimir_b200 import _native
-    from mimir_b200.models.gpt2 import GPT2Config, GPT2Engine
-    from mimir_b200.ops._util import check_error_word
-    from mimir_b200.train import FusedTrainer
-
-    lib = _native.lib()
-    lib.mimir_set_device(local_rank)
-    dp = None
-    flat_alloc = None
+    B, T = args.micro_batch, args.seq
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        from mimir_b200.parallel.dp import FusedDataParallel
-        dp = FusedDataParallel(rank, world, local_rank, nblocks=args.dp_blocks)
-        flat_alloc = dp.alloc_shared
+    dp = None
+    if args.impl == "baseline":
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        import torch_baselines as TB
+        torch.manual_seed(0)
+        vocab = 50257
+        net = TB.GPT2().cuda().to(torch.bfloat16)
+        tr = TB.TorchTrainer(net, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, graph=not args.no_graph,
+                             ddp=world > 1, local_rank=local_rank)
+        tr.h2d_bytes_per_step, tr.d2h_bytes_per_step, tr.launches_per_step = 2 * B * T * 8, 4, 0
+        launch_count = lambda: 0          # noqa: E731 - library kernels are not counted
+        set_batch = lambda tok, tgt: tr.set_batch(tok, tgt)      # noqa: E731
+        check_error_word = lambda: 0      # noqa: E731
+    else:
+        from mimir_b200 import _native
+        from mimir_b200.models.gpt2 import GPT2Config, GPT2Engine
+        from mimir_b200.ops._util import check_error_word
+        from mimir_b200.train import FusedTrainer
 
-    cfg = GPT2Config.small()
-    B, T = args.micro_batch, args.seq
-    eng = GPT2Engine(cfg, B, T, device=f"cuda:{local_rank}", seed=0, flat_alloc=flat_alloc,
-                     attention=args.attention)
-    if dp is not None:
-        dp.attach(eng)
-    tr = FusedTrainer(eng, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, use_graph=not args.no_graph,
-                      dp=dp)
+        lib = _native.lib()
+        lib.mimir_set_device(local_rank)
+        flat_alloc = None
+        if world > 1:
+            from mimir_b200.parallel.dp import FusedDataParallel
+            dp = FusedDataParallel(rank, world, local_rank, nblocks=args.dp_blocks)
+            flat_alloc = dp.alloc_shared
+        cfg = GPT2Config.small()
+        vocab = cfg.vocab
+        eng = GPT2Engine(cfg, B, T, device=f"cuda:{local_rank}", seed=0, flat_alloc=flat_alloc,
+                         attention=args.attention)
+        if dp is not None:
+            dp.attach(eng)
+        tr = FusedTrainer(eng, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, use_graph=not args.no_graph,
+                          dp=dp)
+        launch_count = lib.mimir_launch_count
+
+        def set_batch(tok, tgt):
+            eng.tokens.copy_(tok.view(-1))
+            eng.targets.copy_(tgt.view(-1))
 
     gen = torch.Generator().manual_seed(1234 + rank)
     nbatch = 4
-    toks = [torch.randint(0, cfg.vocab, (B, T), generator=gen).pin_memory() for _ in range(nbatch)]
+    toks = [torch.randint(0, vocab, (B, T), generator=gen).pin_memory() for _ in range(nbatch)]
     tgts = [torch.roll(t, -1, 1).pin_memory() for t in toks]
 
     def barrier():
@@ -186,7 +224,7 @@ def main() -> int:
     def timed(fn):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = lib.mimir_launch_count()
+        l0 = launch_count()
         w0, t0 = time.perf_counter(), time.time()
         e0.record()
         for i in range(args.steps):
@@ -198,11 +236,10 @@ def main() -> int:
         t = torch.tensor([ms], device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item(), lib.mimir_launch_count() - l0, (t0, t1), wall
+        return t.item(), launch_count() - l0, (t0, t1), wall
 
     # device-timed loop: batch already resident, no host round trip per step
-    eng.tokens.copy_(toks[0].view(-1))
-    eng.targets.copy_(tgts[0].view(-1))
+    set_batch(toks[0], tgts[0])
     ms_dev, launches, win_dev, _ = timed(lambda i: tr.run_device_step())
     # end to end: H2D of the batch and D2H of the loss every step
     losses = []
@@ -235,8 +272,14 @@ def main() -> int:
             "launches_per_step": int(tr.launches_per_step),
             "final_loss": losses[-1] if losses else None,
             "error_word": err,
-            "impl": "ours",
+            "impl": args.impl,
         }
+        if args.impl == "baseline":
+            out["config"]["implementation"] = ("plain PyTorch: cuBLAS bf16, flash SDPA, fused AdamW over fp32 masters, "
+                                               "NCCL DDP; CUDA graph on one GPU: " + str(bool(getattr(tr, "graph", None))))
+            out["gpu_launches"] = None
+        else:
+            out.update(_against_library_baseline(world, value, e2e))
         sys.stdout.flush()
         os.write(real_stdout, (json.dumps(out) + "\n").encode())
     if world > 1:

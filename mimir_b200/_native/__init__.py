@@ -78,6 +78,8 @@ def _declare(l: ctypes.CDLL) -> None:
     sig("mimir_act_bwd", I, P, P, P, L, I, P)
     sig("mimir_swiglu_fwd", I, P, P, I, I, P)
     sig("mimir_swiglu_bwd", I, P, P, P, I, I, P)
+    sig("mimir_swiglu2_fwd", I, P, P, P, L, P)
+    sig("mimir_swiglu2_bwd", I, P, P, P, P, P, L, P)
     sig("mimir_rope", I, P, P, P, I, I, I, I, I, I, I, P)
     sig("mimir_cast_f32_bf16", I, P, P, L, F, P)
     sig("mimir_cast_bf16_f32", I, P, P, L, F, P)

@@ -150,6 +150,37 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
   st8(dgu + static_cast<size_t>(r) * 2 * F + F + c, du);
 }
 
+// The same product with gate and up in separate buffers (what two Linear layers produce).
+__global__ void swiglu2_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                   __nv_bfloat16* __restrict__ y, size_t n8) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float g[8], u[8];
+  ld8(gate + i * 8, g);
+  ld8(up + i * 8, u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) g[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  st8(y + i * 8, g);
+}
+__global__ void swiglu2_bwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                                   const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dgate,
+                                   __nv_bfloat16* __restrict__ dup, size_t n8) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float g[8], u[8], d[8], dg[8], du[8];
+  ld8(gate + i * 8, g);
+  ld8(up + i * 8, u);
+  ld8(dy + i * 8, d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float s = 1.f / (1.f + __expf(-g[j]));
+    du[j] = d[j] * g[j] * s;
+    dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+  }
+  st8(dgate + i * 8, dg);
+  st8(dup + i * 8, du);
+}
+
 // ---------------------------------------------------------------------------
 // RoPE applied in place to `nheads` heads of D dims starting at column col0 of
 // x[rows, ld].  pos[row] gives the position.  interleaved: pairs (2i, 2i+1);
@@ -407,6 +438,23 @@ MIMIR_API int mimir_swiglu_bwd(const void* gu, const void* dy, void* dgu, int ro
   swiglu_bwd_kernel<<<blocks_for(n, 256), 256, 0, st>>>(static_cast<const bf16*>(gu),
                                                         static_cast<const bf16*>(dy),
                                                         static_cast<bf16*>(dgu), rows, F);
+  count_launch();
+  return 0;
+}
+MIMIR_API int mimir_swiglu2_fwd(const void* gate, const void* up, void* y, long long n, cudaStream_t st) {
+  if (n % 8) return refuse("swiglu: n must be a multiple of 8");
+  swiglu2_fwd_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(static_cast<const bf16*>(gate),
+                                                             static_cast<const bf16*>(up), static_cast<bf16*>(y),
+                                                             static_cast<size_t>(n / 8));
+  count_launch();
+  return 0;
+}
+MIMIR_API int mimir_swiglu2_bwd(const void* gate, const void* up, const void* dy, void* dgate, void* dup,
+                                long long n, cudaStream_t st) {
+  if (n % 8) return refuse("swiglu: n must be a multiple of 8");
+  swiglu2_bwd_kernel<<<blocks_for(n / 8, 256), 256, 0, st>>>(
+      static_cast<const bf16*>(gate), static_cast<const bf16*>(up), static_cast<const bf16*>(dy),
+      static_cast<bf16*>(dgate), static_cast<bf16*>(dup), static_cast<size_t>(n / 8));
   count_launch();
   return 0;
 }

@@ -13,7 +13,16 @@ def _op(name, fn, *ts):
     return T.core._node(fn, ts, {}, name)
 
 
-def cross_entropy(logits, target): return _op("cross_entropy", lambda l, t: F.cross_entropy(l.float(), t.long()), logits, target)
+def cross_entropy(logits, target):
+    """Mean softmax cross-entropy of logits ``[N, C]`` (or ``[N, C, d1, ...]``) against integer class
+    targets.  2-D bf16 CUDA logits whose class count is a multiple of 8 run the fused native kernel (loss and d(loss)/d(logits) in one pass over the
+    logits, no fp32 copy of them); rows with a negative target are ignored there."""
+    def run(l, t):
+        if l.dim() == 2 and T.core._native_ok(l) and t.is_cuda and l.shape[-1] % 8 == 0 and l.numel():
+            from ..ops import functional as NF
+            return NF.cross_entropy(l, t)
+        return F.cross_entropy(l.float(), t.long())
+    return _op("cross_entropy", run, logits, target)
 def nll(logp, target): return _op("nll", lambda l, t: F.nll_loss(l.float(), t.long()), logp, target)
 def bce_with_logits(logits, target): return _op("bce_with_logits", lambda l, t: F.binary_cross_entropy_with_logits(l.float(), t.float()), logits, target)
 def bce(pred, target): return _op("bce", lambda p, t: F.binary_cross_entropy(p.float(), t.float()), pred, target)

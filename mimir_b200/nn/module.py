@@ -326,7 +326,8 @@ class Dropout(Module):
                 return torch.empty_like(v)
             mask = philox_uniform(tuple(v.shape), s, v.device) < keep
             return v * mask.to(v.dtype) / keep
-        return T.core._node(run, (x,), {}, "dropout")
+        run._mimir_volatile = True   # the seed changes every call: kept out of the schedule's key
+        return T.core._node(run, (x,), {}, "dropout", attrs={"kind": "unary"})
 
 
 class _Fn(Module):

@@ -111,6 +111,17 @@ def swiglu_bwd(gu, dy, dgu):
     return dgu
 
 
+def swiglu2_fwd(gate, up, out):
+    """``silu(gate) * up`` with gate and up in separate contiguous buffers."""
+    _native.check(_L().mimir_swiglu2_fwd(ptr(gate), ptr(up), ptr(out), gate.numel(), stream_ptr()), "swiglu2_fwd")
+    return out
+
+
+def swiglu2_bwd(gate, up, dy, dgate, dup):
+    _native.check(_L().mimir_swiglu2_bwd(ptr(gate), ptr(up), ptr(dy), ptr(dgate), ptr(dup), gate.numel(),
+                                         stream_ptr()), "swiglu2_bwd")
+
+
 def rope_(x2d, pos, freqs, col0, nheads, D, interleaved, inverse=False):
     rows = x2d.shape[0]
     _native.check(_L().mimir_rope(ptr(x2d), ptr(pos), ptr(freqs), rows, x2d.stride(0), col0, nheads,

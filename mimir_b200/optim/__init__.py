@@ -11,7 +11,12 @@ and exposes state under the reference's names (``exp_avg``, ``exp_avg_sq``,
 ``master``) with snapshot keys ``"<param index>.<name>"``.
 
 bf16 CUDA parameters updated by AdamW with master weights go through the fused
-native kernel (``mimir_adamw_flat``): one pass writes p, m, v and the master.
+native kernel (``mimir_adamw_flat``): at the first step the optimizer moves the
+parameters, their gradients, the fp32 masters and both moments into flat buffers
+(``FlatAdamW``), after which a step is ONE launch that writes p, m, v and the master
+(plus one sum-of-squares launch when a global-norm clip is set; the clip factor is
+computed on the device, so the step never waits for the host).  Every other rule runs
+as per-parameter PyTorch updates.
 """
 from __future__ import annotations
 
@@ -20,6 +25,87 @@ import math
 import torch
 
 from ..tensor import errors as E
+
+
+class FlatAdamW:
+    """Flat storage of an AdamW-with-master-weights optimizer over bf16 CUDA parameters.
+
+    ``param`` / ``grad`` are bf16, ``master`` / ``exp_avg`` / ``exp_avg_sq`` fp32; every parameter
+    owns a slice that starts on a multiple of 8 elements (the kernels move 16 bytes at a time) and
+    ``Param._data`` / ``Param._grad_buf`` are re-pointed at views of the slices, so the model, the
+    checkpoint code and ``backward`` keep working on the same memory.  The learning rate, the bias
+    corrections and the gradient scale reach the kernel through a 4-float device array, so a step
+    captured in a CUDA graph replays with new values (internal/sched/key.go:28-44 keeps constants
+    out of a schedule's key for the same reason)."""
+
+    def __init__(self, opt):
+        params = [p for p in opt.params if p.trainable]
+        dev = params[0]._data.device
+        offs, n = [], 0
+        for p in params:
+            offs.append(n)
+            n += (p.numel() + 7) // 8 * 8
+        self.n, self.params, self.offsets = n, params, offs
+        self.param = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        self.grad = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        self.master = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
+        # a small ring of pinned staging buffers: a buffer is rewritten only after three later
+        # steps have queued their copies, by which time its own copy has long completed
+        self._hyper_host = [torch.zeros(4).pin_memory() for _ in range(4)]
+        self._ring = 0
+        index = {id(p): i for i, p in enumerate(opt.params)}
+        for p, o in zip(params, offs):
+            k, st = p.numel(), opt.state[index[id(p)]]
+            view = lambda buf: buf.narrow(0, o, k).view(p.shape)  # noqa: E731
+            pv, mv = view(self.param), view(self.master)
+            pv.copy_(p._data)
+            mv.copy_(st["master"] if "master" in st else p._data.float())
+            for name, buf in (("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
+                if name in st:
+                    view(buf).copy_(st[name])
+                st[name] = view(buf)
+            st["master"] = mv
+            gv = view(self.grad)
+            if p._grad is not None:
+                gv.copy_(p._grad)
+                p._grad = gv
+            p._data, p._grad_buf = pv, gv
+            p._version += 1
+
+    def step(self, opt) -> None:
+        from ..ops import kernels as K
+        for p in self.params:
+            if p._grad is None:           # a parameter the loss did not reach: no stale gradient
+                p._grad_buf.zero_()
+            elif p._grad is not p._grad_buf:
+                p._grad_buf.copy_(p._grad)
+        h = opt.hyper
+        b1, b2 = h.get("beta1", 0.9), h.get("beta2", 0.999)
+        host = self._hyper_host[self._ring]
+        self._ring = (self._ring + 1) % len(self._hyper_host)
+        host[0], host[1] = opt.lr, 1.0 - b1 ** opt.steps
+        host[2], host[3] = math.sqrt(1.0 - b2 ** opt.steps), 1.0 / opt.grad_scale
+        self.hyper.copy_(host, non_blocking=True)
+        self.launch(opt)
+        for p in self.params:
+            p._version += 1
+
+    def launch(self, opt) -> None:
+        """The device work of one step (what a captured training step contains)."""
+        from ..ops import kernels as K
+        h = opt.hyper
+        clip = float(opt.clip_norm or 0.0)
+        if clip > 0:
+            self.gnorm_sq.zero_()
+            K.sumsq(self.grad, self.gnorm_sq)
+        K.adamw_flat(self.master, self.param, self.grad, self.exp_avg, self.exp_avg_sq, decay_n=self.n, lr=0.0,
+                     beta1=h.get("beta1", 0.9), beta2=h.get("beta2", 0.999), eps=h.get("eps", 1e-8),
+                     wd=opt.weight_decay, step=1, gnorm_sq=self.gnorm_sq if clip > 0 else None, clip=clip,
+                     hyper=self.hyper)
 
 
 class Optimizer:
@@ -32,28 +118,50 @@ class Optimizer:
         self.state = [dict() for _ in self.params]
         self.steps = 0
         self.grad_scale = 1.0  # gradients are divided by this (loss scaling)
+        self._flat = None      # FlatAdamW once the fused path has taken over
+
+    def _flat_eligible(self) -> bool:
+        from ..tensor import core as C
+        if self.rule is not _adamw or not self.master_weights or not C._NATIVE:
+            return False
+        ps = [p for p in self.params if p.trainable]
+        if not ps or type(self).step is not Optimizer.step:
+            return False
+        dev = ps[0]._data.device
+        return dev.type == "cuda" and all(p._data.dtype == torch.bfloat16 and p._data.device == dev
+                                          and getattr(p, "_gather", None) is None and p._sharding is None for p in ps)
 
     # -- gradient checks
     def grads_finite(self) -> bool:
         """True when every gradient is finite (optim.go:136-157); used by dynamic loss scaling."""
-        for p in self.params:
-            if p._grad is not None and not bool(torch.isfinite(p._grad).all()):
-                return False
-        return True
+        gs = [p._grad for p in self.params if p._grad is not None]
+        if not gs:
+            return True
+        if gs[0].is_cuda:       # one reduction and one host read for all gradients
+            return bool(torch.stack([torch.isfinite(g).all() for g in gs]).all())
+        return all(bool(torch.isfinite(g).all()) for g in gs)
 
     def zero_grad(self) -> None:
         for p in self.params:
             p.zero_grad()
 
     def global_norm(self) -> float:
-        sq = 0.0
-        for p in self.params:
-            if p._grad is not None:
-                sq += float(p._grad.float().pow(2).sum())
-        return math.sqrt(sq) / self.grad_scale
+        gs = [p._grad for p in self.params if p._grad is not None]
+        if not gs:
+            return 0.0
+        sq = torch.stack([g.float().pow(2).sum() for g in gs]).sum()      # one host read in all
+        return math.sqrt(float(sq)) / self.grad_scale
 
     def step(self) -> None:
         self.steps += 1
+        from ..tensor.autograd import flush_lazy
+        if self._flat is None and self._flat_eligible():
+            flush_lazy()
+            self._flat = FlatAdamW(self)
+        if self._flat is not None:
+            flush_lazy()
+            self._flat.step(self)
+            return
         factor = 1.0 / self.grad_scale
         if self.clip_norm > 0:
             norm = self.global_norm()
@@ -89,7 +197,13 @@ class Optimizer:
     def restore(self, snap: dict, steps: int | None = None) -> None:
         for key, v in snap.items():
             i, name = key.split(".", 1)
-            self.state[int(i)][name] = v.clone()
+            st = self.state[int(i)]
+            if self._flat is not None and name in st and torch.is_tensor(st[name]):
+                st[name].copy_(v)       # views of the flat buffers: written in place
+                if name == "master":
+                    self.params[int(i)]._data.copy_(v)
+            else:
+                st[name] = v.clone().to(self.params[int(i)]._data.device)
         if steps is not None:
             self.steps = steps
 
@@ -176,8 +290,16 @@ def _nadam(lr, t, w, g, st, o):
     g = _wd_coupled(g, w, o)
     mu = b1 * (1 - 0.5 * 0.96 ** (t * md))
     mu_next = b1 * (1 - 0.5 * 0.96 ** ((t + 1) * md))
-    prod = st.get("_mu_product", 1.0) * mu
-    st["_mu_product"] = prod
+    # the running product of the momentum factors is a function of the step number alone
+    # (optim/optim.go:604-609), so nothing beyond the tensors has to be checkpointed
+    cached = getattr(o, "_nadam_prod", None)      # (step, product): a cache, recomputable from t
+    if cached is not None and cached[0] == t:
+        prod = cached[1]
+    else:
+        start, prod = (cached[0], cached[1]) if cached is not None and cached[0] < t else (0, 1.0)
+        for i in range(start + 1, t + 1):
+            prod *= b1 * (1 - 0.5 * 0.96 ** (i * md))
+        o._nadam_prod = (t, prod)
     m = b1 * st.get("exp_avg", torch.zeros_like(w)) + (1 - b1) * g
     v = b2 * st.get("exp_avg_sq", torch.zeros_like(w)) + (1 - b2) * g * g
     st["exp_avg"], st["exp_avg_sq"] = m, v

@@ -26,6 +26,7 @@ class Param:
         v = value.data() if isinstance(value, C.Tensor) else torch.as_tensor(value)
         self._data = v.detach().clone()
         self._grad = None
+        self._grad_buf = None       # persistent gradient storage when an optimizer keeps flat buffers
         self._version = 0
         self.name = name
         self._trainable = trainable
@@ -65,12 +66,14 @@ class Param:
         self._data = self._data.to(device.torch)
         if self._grad is not None:
             self._grad = self._grad.to(device.torch)
+        self._grad_buf = None
         self._version += 1
         return self
 
     def cast(self, dtype) -> "Param":
         self._data = self._data.to(dtype)
         self._grad = None
+        self._grad_buf = None
         self._version += 1
         return self
 
@@ -228,11 +231,27 @@ def backward(loss: C.Tensor, effects=()) -> None:
         params = [p for _, (t, p) in trainable.items()]
         uniq = list({id(p): p for p in params}.values())
         grads = torch.autograd.grad(out, [inputs[id(p)] for p in uniq], allow_unused=True)
+    fresh_dst, fresh_src, acc_dst, acc_src = [], [], [], []
     for p, g in zip(uniq, grads):
         if g is None:
             continue
-        p._grad = g.detach() if p._grad is None else p._grad + g.detach()
-        p._data.requires_grad_(False)
+        g = g.detach()
+        buf = p._grad_buf
+        if buf is not None and buf.shape == g.shape and buf.dtype == g.dtype and buf.device == g.device:
+            # the optimizer keeps this gradient in a flat buffer: write / accumulate in place
+            if p._grad is None:
+                fresh_dst.append(buf)
+                fresh_src.append(g)
+                p._grad = buf
+            else:
+                acc_dst.append(p._grad)
+                acc_src.append(g)
+        else:
+            p._grad = g if p._grad is None else p._grad + g
+    if fresh_dst:
+        torch._foreach_copy_(fresh_dst, fresh_src)
+    if acc_dst:
+        torch._foreach_add_(acc_dst, acc_src)
     for p in uniq:
         p._data.requires_grad_(False)
     loss._val = out.detach()

@@ -102,10 +102,10 @@ class Tensor:
     """One node of the lazy graph (or a realized leaf)."""
 
     __slots__ = ("_fn", "_args", "_kw", "_val", "_err", "shape", "dtype", "device", "_stale", "_donated",
-                 "_sharding", "_opname", "_effects", "__weakref__")
+                 "_sharding", "_opname", "_effects", "_attrs", "__weakref__")
 
     def __init__(self, fn=None, args=(), kw=None, val=None, err=None, shape=(), dtype=float32, device=None,
-                 opname=""):
+                 opname="", attrs=None):
         self._fn, self._args, self._kw = fn, args, kw or {}
         self._val, self._err = val, err
         self.shape, self.dtype = tuple(shape), dtype
@@ -115,6 +115,7 @@ class Tensor:
         self._sharding = None
         self._opname = opname
         self._effects = ()      # tensors a backward pass computes along with the gradients
+        self._attrs = attrs     # op attributes the fusion planner and the layout rules read (axes, sizes)
 
     # ------------------------------------------------------------- properties
     @property
@@ -287,7 +288,7 @@ def _meta_key(fn, args, kw):
         return None
 
 
-def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None) -> Tensor:
+def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None, attrs=None) -> Tensor:
     """Records ``fn(*args, **kw)``: propagates errors, infers shape/dtype on meta tensors (the result
     of an inference is cached by structure, so a training loop pays for it once)."""
     err = _first_error(args)
@@ -312,12 +313,13 @@ def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | 
             _META_CACHE[key] = meta
     if isinstance(meta, (tuple, list)):
         outs = tuple(Tensor(fn=_pick(fn, i), args=tuple(args), kw=kw, shape=m.shape, dtype=m.dtype, device=device,
-                            opname=opname) for i, m in enumerate(meta))
+                            opname=opname, attrs=dict(attrs or {}, part=i)) for i, m in enumerate(meta))
         if _EAGER:
             for o in outs:
                 realize(o)
         return outs
-    out = Tensor(fn=fn, args=tuple(args), kw=kw, shape=meta.shape, dtype=meta.dtype, device=device, opname=opname)
+    out = Tensor(fn=fn, args=tuple(args), kw=kw, shape=meta.shape, dtype=meta.dtype, device=device, opname=opname,
+                 attrs=attrs)
     if _EAGER:
         realize(out)
     return out
@@ -347,41 +349,28 @@ def _check_leaf(t: Tensor):
 
 
 def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bool = True) -> list:
-    """Evaluates the graph below ``roots`` (iteratively, memoised); returns torch tensors."""
+    """Evaluates the graph below ``roots`` and returns torch tensors.  ``memo`` maps ``id(node)`` to a
+    value that stands in for that node (how ``backward`` substitutes differentiable leaves).  The
+    graph is planned into a program (fusion, slots, early release of intermediates) that is cached
+    by structure: see ``tensor/plan.py``."""
+    from . import plan
     memo = {} if memo is None else memo
-    for root in roots:
-        if root._err is not None:
-            raise root._err
-        stack = [root]
-        while stack:
-            t = stack[-1]
-            if id(t) in memo:
-                stack.pop()
-                continue
-            if t._fn is None or (reuse_cached and t._val is not None):
-                if t._val is None:
-                    raise E.ErrNilTensor("tensor has neither a value nor a producer")
-                _check_leaf(t)
-                memo[id(t)] = t._val
-                stack.pop()
-                continue
-            pending = [a for a in _flatten(t._args) if isinstance(a, Tensor) and id(a) not in memo]
-            if pending:
-                stack.extend(pending)
-                continue
-            vals = _map_args(t._args, lambda a: memo[id(a)])
-            try:
-                memo[id(t)] = t._fn(*vals, **t._kw)
-            except E.MimirError:
-                raise
-            except Exception as exc:  # noqa: BLE001
-                if type(exc).__module__.startswith("torch.utils.checkpoint"):
-                    raise  # control flow of activation recomputation, not a failure
-                err = E.classify(exc)
-                t._err = err
-                raise err from exc
-            stack.pop()
-    return [memo[id(r)] for r in roots]
+    roots = list(roots)
+    prog, w = plan.schedule(roots, memo, reuse_cached)
+    leaf_vals = []
+    for t in w.leaves:
+        if id(t) in memo:
+            leaf_vals.append(memo[id(t)])
+        else:
+            _check_leaf(t)
+            leaf_vals.append(t._val)
+
+    def on_error(i, err):
+        w.order[i]._err = err
+    outs = prog.run(leaf_vals, w.order, on_error)
+    for r, v in zip(roots, outs):
+        memo[id(r)] = v
+    return outs
 
 
 def realize(*tensors: Tensor) -> None:
@@ -415,6 +404,14 @@ def _creator(fn, shape, dtype, device, opname):
     return Tensor(fn=lambda: fn(shape, dtype, device.torch), shape=shape, dtype=dtype, device=device, opname=opname)
 
 
+def _volatile(t: Tensor) -> Tensor:
+    """Marks a node whose executable closes over a per-call constant (a seed): the structural key of a
+    schedule ignores the constant, and a cached program runs the executable of the current graph."""
+    if t._fn is not None:
+        t._fn._mimir_volatile = True
+    return t
+
+
 def zeros(shape, dtype=float32, device=None):
     return _creator(lambda s, d, dev: torch.zeros(s, dtype=d, device=dev), shape, dtype, device, "zeros")
 
@@ -438,12 +435,12 @@ def eye(n, dtype=float32, device=None):
 def rand(shape, seed: int = 0, dtype=float32, device=None):
     """Uniform [0,1) from the Philox4x32-10 stream of ``seed`` (same values on every device)."""
     from .random import philox_uniform
-    return _creator(lambda s, d, dev: philox_uniform(s, seed, dev).to(d), shape, dtype, device, "rand")
+    return _volatile(_creator(lambda s, d, dev: philox_uniform(s, seed, dev).to(d), shape, dtype, device, "rand"))
 
 
 def randn(shape, seed: int = 0, dtype=float32, device=None):
     from .random import philox_normal
-    return _creator(lambda s, d, dev: philox_normal(s, seed, dev).to(d), shape, dtype, device, "randn")
+    return _volatile(_creator(lambda s, d, dev: philox_normal(s, seed, dev).to(d), shape, dtype, device, "randn"))
 
 
 # ---------------------------------------------------------------------------
@@ -485,7 +482,7 @@ def _binary(opname, fn, out_bool=False):
             if x.dtype != y.dtype:
                 x, y = x.to(dt), y.to(dt)
             return fn(x, y)
-        return _node(run, (a, b), {}, opname)
+        return _node(run, (a, b), {}, opname, attrs={"kind": "binary"})
     op.__name__ = opname
     return op
 
@@ -510,9 +507,16 @@ equal = _binary("equal", torch.eq)
 mod = _binary("mod", torch.remainder)
 
 
-def _unary(opname, fn):
+def _unary(opname, fn, native_mode=None):
+    """An elementwise op of one tensor; ``native_mode`` names the activation kernel that serves
+    bf16 CUDA tensors (forward and backward) instead of the PyTorch op."""
     def op(x: Tensor, *args, **kw):
-        return _node(lambda v: fn(v, *args, **kw), (x,), {}, opname)
+        def run(v):
+            if native_mode is not None and _native_ok(v) and v.numel() % 8 == 0 and v.numel():
+                from ..ops import functional as NF
+                return NF.activation(v, native_mode)
+            return fn(v, *args, **kw)
+        return _node(run, (x,), {}, opname, attrs={"kind": "unary"})
     op.__name__ = opname
     return op
 
@@ -526,7 +530,7 @@ sin = _unary("sin", torch.sin)
 cos = _unary("cos", torch.cos)
 tanh = _unary("tanh", torch.tanh)
 sigmoid = _unary("sigmoid", torch.sigmoid)
-relu = _unary("relu", torch.relu)
+relu = _unary("relu", torch.relu, "relu")
 abs_ = _unary("abs", torch.abs)
 sign = _unary("sign", torch.sign)
 floor = _unary("floor", torch.floor)
@@ -539,7 +543,7 @@ expm1 = _unary("expm1", torch.expm1)
 lgamma = _unary("lgamma", torch.lgamma)
 digamma = _unary("digamma", torch.digamma)
 logical_not = _unary("logical_not", torch.logical_not)
-silu = _unary("silu", torch.nn.functional.silu)
+silu = _unary("silu", torch.nn.functional.silu, "silu")
 softplus = _unary("softplus", torch.nn.functional.softplus)
 
 
@@ -549,7 +553,12 @@ def trigamma(x):
 
 def gelu(x, approximate: str = "tanh"):
     """GELU; the tanh form is the default like the reference (tensor/elementwise.go:556-594)."""
-    return _node(lambda v: torch.nn.functional.gelu(v, approximate=approximate), (x,), {}, "gelu")
+    def run(v):
+        if approximate == "tanh" and _native_ok(v) and v.numel() % 8 == 0 and v.numel():
+            from ..ops import functional as NF
+            return NF.activation(v, "gelu")
+        return torch.nn.functional.gelu(v, approximate=approximate)
+    return _node(run, (x,), {}, "gelu", attrs={"kind": "unary", "approximate": approximate})
 
 
 def leaky_relu(x, slope=0.01):
@@ -567,38 +576,46 @@ def where(cond, a, b):
 
 
 def cast(x, dtype):
-    return _node(lambda v: v.to(dtype), (x,), {}, "cast")
+    return _node(lambda v: v.to(dtype), (x,), {}, "cast", attrs={"kind": "unary"})
+
+
+def _swiglu_run(g, u):
+    if g.shape == u.shape and _native_ok(g, u) and g.numel() % 8 == 0 and g.numel():
+        from ..ops import functional as NF
+        return NF.swiglu(g, u)
+    return torch.nn.functional.silu(g) * u
 
 
 def swiglu(gate, up):
-    return mul(silu(gate), up)
+    """``silu(gate) * up``: one kernel (forward and backward) for bf16 CUDA tensors."""
+    return _node(_swiglu_run, (gate, up), {}, "swiglu", attrs={"kind": "binary"})
 
 
 # ---------------------------------------------------------------------------
 # movement
 # ---------------------------------------------------------------------------
 def reshape(x, shape):
-    return _node(lambda v: v.reshape(shape), (x,), {}, "reshape")
+    return _node(lambda v: v.reshape(shape), (x,), {}, "reshape", attrs={"shape": tuple(shape)})
 
 
 def permute(x, dims):
-    return _node(lambda v: v.permute(dims), (x,), {}, "permute")
+    return _node(lambda v: v.permute(dims), (x,), {}, "permute", attrs={"dims": tuple(dims)})
 
 
 def transpose(x, a=-1, b=-2):
-    return _node(lambda v: v.transpose(a, b), (x,), {}, "transpose")
+    return _node(lambda v: v.transpose(a, b), (x,), {}, "transpose", attrs={"a": a, "b": b})
 
 
 def expand(x, shape):
-    return _node(lambda v: v.expand(shape), (x,), {}, "expand")
+    return _node(lambda v: v.expand(shape), (x,), {}, "expand", attrs={"shape": tuple(shape)})
 
 
 def squeeze(x, dim=None):
-    return _node(lambda v: v.squeeze() if dim is None else v.squeeze(dim), (x,), {}, "squeeze")
+    return _node(lambda v: v.squeeze() if dim is None else v.squeeze(dim), (x,), {}, "squeeze", attrs={"dim": dim})
 
 
 def unsqueeze(x, dim):
-    return _node(lambda v: v.unsqueeze(dim), (x,), {}, "unsqueeze")
+    return _node(lambda v: v.unsqueeze(dim), (x,), {}, "unsqueeze", attrs={"dim": dim})
 
 
 def flip(x, dims):
@@ -621,7 +638,7 @@ def shrink(x, ranges):
                 raise E.ErrIndex(f"shrink: range [{lo},{hi}) outside axis {ax} of size {v.shape[ax]}")
             v = v.narrow(ax, lo, hi - lo)
         return v
-    return _node(run, (x,), {}, "shrink")
+    return _node(run, (x,), {}, "shrink", attrs={"ranges": tuple(tuple(r) for r in ranges)})
 
 
 def getitem(x, idx):
@@ -631,7 +648,7 @@ def getitem(x, idx):
 
 
 def cat(xs, dim=0):
-    return _node(lambda vs: torch.cat(list(vs), dim), (list(xs),), {}, "cat")
+    return _node(lambda vs: torch.cat(list(vs), dim), (list(xs),), {}, "cat", attrs={"dim": dim})
 
 
 def stack(xs, dim=0):
@@ -639,11 +656,12 @@ def stack(xs, dim=0):
 
 
 def split(x, sizes, dim=0):
-    return _node(lambda v: tuple(torch.split(v, sizes, dim)), (x,), {}, "split")
+    return _node(lambda v: tuple(torch.split(v, sizes, dim)), (x,), {}, "split",
+                 attrs={"sizes": tuple(sizes) if isinstance(sizes, (list, tuple)) else sizes, "dim": dim})
 
 
 def contiguous(x):
-    return _node(lambda v: v.contiguous(), (x,), {}, "contiguous")
+    return _node(lambda v: v.contiguous(), (x,), {}, "contiguous", attrs={"kind": "unary"})
 
 
 def _check_index(i, n, opname):
@@ -654,9 +672,13 @@ def _check_index(i, n, opname):
 def gather_rows(x, index):
     """``x[index]`` along axis 0 (embedding lookup); out-of-range indices are ErrIndex."""
     def run(v, i):
+        if v.dim() == 2 and _native_ok(v) and i.is_cuda and v.shape[1] % 8 == 0 and i.numel():
+            # the kernel checks the range itself and reports through the device error word
+            from ..ops import functional as NF
+            return NF.embedding(v, i)
         _check_index(i, v.shape[0], "gather")
         return v[i.long()]
-    return _node(run, (x, index), {}, "gather")
+    return _node(run, (x, index), {}, "gather_rows")
 
 
 def gather(x, dim, index):
@@ -708,7 +730,7 @@ def _reduce(opname, fn):
             if v.dtype in _HALF:
                 v = v.float()
             return fn(v, dim, keepdim)
-        return _node(run, (x,), {}, opname)
+        return _node(run, (x,), {}, opname, attrs={"kind": "reduce", "dim": dim, "keepdim": keepdim})
     op.__name__ = opname
     return op
 
@@ -726,11 +748,11 @@ def argmax(x, dim=-1):
 
 
 def softmax(x, dim=-1):
-    return _node(lambda v: torch.softmax(v.float(), dim).to(v.dtype), (x,), {}, "softmax")
+    return _node(lambda v: torch.softmax(v.float(), dim).to(v.dtype), (x,), {}, "softmax", attrs={"dim": dim})
 
 
 def log_softmax(x, dim=-1):
-    return _node(lambda v: torch.log_softmax(v.float(), dim).to(v.dtype), (x,), {}, "log_softmax")
+    return _node(lambda v: torch.log_softmax(v.float(), dim).to(v.dtype), (x,), {}, "log_softmax", attrs={"dim": dim})
 
 
 def _scan(opname, mode, fallback):
@@ -768,21 +790,56 @@ def topk(x, k, dim=-1):
 # ---------------------------------------------------------------------------
 # products
 # ---------------------------------------------------------------------------
-def _use_native(*vals) -> bool:
-    return all(v.is_cuda and v.dtype == bfloat16 for v in vals)
+_NATIVE = os.environ.get("MIMIR_NATIVE", "1") != "0"
+
+
+def _native_ok(*vals) -> bool:
+    """True when every operand is a bf16 CUDA tensor and the native kernels are not switched off
+    (``MIMIR_NATIVE=0`` keeps the whole layer on PyTorch library kernels: the baseline mode)."""
+    return _NATIVE and all(v is not None and v.is_cuda and v.dtype == bfloat16 for v in vals)
+
+
+def set_native(on: bool) -> bool:
+    """Switches the native sm_100a dispatch of this layer on or off; returns the previous setting."""
+    global _NATIVE
+    old, _NATIVE = _NATIVE, bool(on)
+    return old
 
 
 def matmul(a, b):
-    """``a @ b`` with batch broadcasting; bf16 CUDA operands run on the tcgen05 GEMM."""
+    """``a @ b`` with batch broadcasting.  bf16 CUDA operands with a 2-D right-hand side run on the
+    tcgen05 GEMM (forward, and both gradients in backward)."""
     def run(x, y):
         if x.dtype != y.dtype:
             raise E.ErrDType(f"matmul: dtypes {x.dtype} and {y.dtype} differ")
-        if _use_native(x, y) and x.dim() == 2 and y.dim() == 2 and x.shape[0] >= 128 and y.shape[1] % 8 == 0 \
-                and x.shape[1] % 8 == 0:
-            from ..ops.gemm import gemm
-            return gemm(x.contiguous(), y.contiguous(), b_mn=True)
+        if _native_ok(x, y) and y.dim() == 2 and x.dim() >= 2 and y.shape[1] % 8 == 0 and x.shape[-1] % 8 == 0 \
+                and x.numel():
+            from ..ops import functional as NF
+            lead = x.shape[:-1]
+            x2 = x.reshape(-1, x.shape[-1])
+            out = NF.MatmulFn.apply(x2 if x2.is_contiguous() else x2.contiguous(), y if y.is_contiguous() else y.contiguous())
+            return out.view(*lead, y.shape[1])
         return x @ y
     return _node(run, (a, b), {}, "matmul")
+
+
+def _linear_run(act: int, has_bias: bool, has_res: bool):
+    """The executable of a Linear product with an optional fused GELU-tanh (``act`` 1) or residual
+    add: the native GEMM with the epilogue folded in for bf16 CUDA operands, PyTorch otherwise."""
+    def run(v, wt, *rest):
+        if v.dtype != wt.dtype:
+            raise E.ErrDType(f"linear: input {v.dtype} and weight {wt.dtype} differ")
+        b = rest[0] if has_bias else None
+        r = rest[1 if has_bias else 0] if has_res else None
+        extra = tuple(t for t in (b, r) if t is not None)
+        if _native_ok(v, wt, *extra) and wt.dim() == 2 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0 and v.numel():
+            from ..ops import functional as NF
+            return NF.linear(v, wt, b, r, act)
+        y = torch.nn.functional.linear(v, wt, b)
+        if act == 1:
+            y = torch.nn.functional.gelu(y, approximate="tanh")
+        return y + r if r is not None else y
+    return run
 
 
 def matmul_t(x, w, bias=None):
@@ -792,24 +849,16 @@ def matmul_t(x, w, bias=None):
     if isinstance(w, QuantizedTensor):
         from ..ops.quant import qmatmul_t
         return _node(lambda v: qmatmul_t(v, w), (x,), {}, "qmatmul")
-
-    def run(v, wt, *b):
-        if v.dtype != wt.dtype:
-            raise E.ErrDType(f"linear: input {v.dtype} and weight {wt.dtype} differ")
-        lead = v.shape[:-1]
-        if _use_native(v, wt) and v.numel() // v.shape[-1] >= 128 and wt.shape[0] % 8 == 0 and wt.shape[1] % 8 == 0:
-            from ..ops.gemm import gemm
-            out = gemm(v.reshape(-1, v.shape[-1]).contiguous(), wt.contiguous(), bias=b[0] if b else None)
-            return out.view(*lead, wt.shape[0])
-        return torch.nn.functional.linear(v, wt, b[0] if b else None)
     args = (x, w) + ((bias,) if bias is not None else ())
-    return _node(run, args, {}, "linear")
+    return _node(_linear_run(0, bias is not None, False), args, {}, "linear",
+                 attrs={"bias": bias is not None, "act": 0, "residual": False})
 
 
 def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
     """Fused attention over ``[B, H, T, D]`` tensors (tensor/attention.go:81-253): grouped-query
     heads when ``k``/``v`` have fewer heads, optional causal mask with offset, additive or
-    boolean mask; never materialises the score matrix on the CUDA bf16 path."""
+    boolean mask; never materialises the score matrix on the CUDA bf16 path (forward and
+    backward both run the tcgen05 kernels)."""
     args = (q, k, v) + ((mask,) if mask is not None else ())
 
     def run(qv, kv, vv, *m):
@@ -818,13 +867,9 @@ def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
         if Hq % Hk:
             raise E.ErrShape(f"attention: {Hq} query heads are not a multiple of {Hk} key heads")
         off = Tk - Tq if causal_offset is None else causal_offset
-        if not m and _use_native(qv, kv, vv) and D in (64, 128) and qv.device.type == "cuda" \
-                and not torch.is_grad_enabled():
-            from ..ops.attention import attention_fwd
-            out = torch.empty(B, Tq, Hq, D, dtype=qv.dtype, device=qv.device)
-            attention_fwd(qv.transpose(1, 2).contiguous(), kv.transpose(1, 2).contiguous(),
-                          vv.transpose(1, 2).contiguous(), out, None, causal=causal, offset=off, scale=scale)
-            return out.transpose(1, 2)
+        if not m and _native_ok(qv, kv, vv) and D in (64, 128) and kv.shape == vv.shape:
+            from ..ops import functional as NF
+            return NF.attention(qv, kv, vv, causal=causal, offset=off, scale=scale)
         if Hk != Hq:
             kv = kv.repeat_interleave(Hq // Hk, 1)
             vv = vv.repeat_interleave(Hq // Hk, 1)
@@ -839,13 +884,21 @@ def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
                 mm = torch.zeros_like(mm, dtype=qv.dtype).masked_fill(~mm, float("-inf"))
             am = mm if am is None else am + mm
         return torch.nn.functional.scaled_dot_product_attention(qv, kv, vv, attn_mask=am, scale=scale)
-    return _node(run, args, {}, "attention")
+    return _node(run, args, {}, "attention", attrs={"causal": causal, "mask": mask is not None})
 
 
 def conv2d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """2-D convolution; stride-1 bf16 CUDA convolutions run as implicit GEMMs on the tcgen05 kernels
+    (forward, input gradient and filter gradient), everything else on PyTorch."""
     args = (x, w) + ((bias,) if bias is not None else ())
-    return _node(lambda v, wt, *b: torch.nn.functional.conv2d(v, wt, b[0] if b else None, stride, padding, dilation, groups),
-                 args, {}, "conv2d")
+
+    def run(v, wt, *b):
+        if _native_ok(v, wt, *b):
+            from ..ops import functional as NF
+            if NF.conv2d_supported(v, wt, stride, padding, dilation, groups):
+                return NF.conv2d(v, wt, b[0] if b else None, padding, dilation)
+        return torch.nn.functional.conv2d(v, wt, b[0] if b else None, stride, padding, dilation, groups)
+    return _node(run, args, {}, "conv2d")
 
 
 def conv1d(x, w, bias=None, stride=1, padding=0, dilation=1, groups=1):
@@ -873,7 +926,13 @@ def conv_transpose1d(x, w, bias=None, stride=1, padding=0, output_padding=0):
 
 
 def max_pool2d(x, kernel, stride=None, padding=0):
-    return _node(lambda v: torch.nn.functional.max_pool2d(v, kernel, stride, padding), (x,), {}, "max_pool2d")
+    def run(v):
+        if _native_ok(v):
+            from ..ops import functional as NF
+            if NF.max_pool2d_supported(v, kernel, stride, padding):
+                return NF.max_pool2d(v, kernel, stride)
+        return torch.nn.functional.max_pool2d(v, kernel, stride, padding)
+    return _node(run, (x,), {}, "max_pool2d")
 
 
 def avg_pool2d(x, kernel, stride=None, padding=0):
@@ -893,17 +952,23 @@ def layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
     def run(v, *wb):
         w = wb[0] if hw else None
         b = wb[1 if hw else 0] if hb else None
+        if hw and hb and _native_ok(v, w, b) and n % 8 == 0 and n <= 8192 and v.numel():
+            from ..ops import functional as NF
+            return NF.layer_norm(v, w, b, eps)
         return torch.nn.functional.layer_norm(v, (n,), w, b, eps)
-    return _node(run, (x, *extra), {}, "layer_norm")
+    return _node(run, (x, *extra), {}, "layer_norm", attrs={"kind": "rowwise"})
 
 
 def rms_norm(x, weight=None, eps: float = 1e-6):
     """Root-mean-square normalisation over the last axis in fp32, rounded to the input dtype, then
     scaled by ``weight``."""
     def run(v, *w):
+        if w and _native_ok(v, w[0]) and v.shape[-1] % 8 == 0 and v.shape[-1] <= 8192 and v.numel():
+            from ..ops import functional as NF
+            return NF.rms_norm(v, w[0], eps)
         y = (v.float() * torch.rsqrt(v.float().pow(2).mean(-1, keepdim=True) + eps)).to(v.dtype)
         return y * w[0] if w else y
-    return _node(run, (x,) + ((weight,) if weight is not None else ()), {}, "rms_norm")
+    return _node(run, (x,) + ((weight,) if weight is not None else ()), {}, "rms_norm", attrs={"kind": "rowwise"})
 
 
 def with_effects(x, *effects):
@@ -925,7 +990,7 @@ def with_effects(x, *effects):
 
 def detach(x):
     """The same values with no gradient flowing back (tensor.Detach)."""
-    return _node(lambda v: v.detach(), (x,), {}, "detach")
+    return _node(lambda v: v.detach(), (x,), {}, "detach", attrs={"kind": "unary"})
 
 
 def from_bytes(data, shape, dtype=torch.float32, device: Device | None = None) -> Tensor:
@@ -983,7 +1048,7 @@ def _bind_methods():
 _TRACE = None
 _TRACE_DEPTH = 0
 _NOT_OPS = {"CPU", "GPU", "devices", "auto", "default_device", "set_default_device", "from_torch", "tensor",
-            "evaluate", "realize", "from_bytes", "from_bytes_func", "realize_into", "trace_ops"}
+            "evaluate", "realize", "from_bytes", "from_bytes_func", "realize_into", "trace_ops", "set_native"}
 
 
 def _traced(name, f):

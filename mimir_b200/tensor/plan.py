@@ -1,0 +1,328 @@
+"""Schedules: structural keys, the fusion planner, compiled programs and their cache.
+
+A realisation (``realize`` / ``backward``) does not interpret the lazy graph node by node.
+It walks the graph once, numbering nodes and leaves and emitting a *structural key*: the
+operations (code identity and the constants they close over), operand wiring, shapes,
+dtypes and devices, but no tensor *values*.  Graphs built by the same model code on a new
+batch have the same key, so the second step of a training loop finds a compiled
+``Program`` in the cache and runs its instruction list; only a new structure pays for
+planning (reference: internal/sched/key.go:181-231 structural key, cache.go:22-104 program
+cache of at most 64 entries, program.go:115-355 slot-based programs).
+
+Planning is where fusion happens (internal/sched/fuse.go:200-362).  Patterns folded here:
+
+* ``gelu(linear(x, w, b))``           -> one GEMM with the GELU-tanh epilogue,
+* ``linear(x, w, b) + r`` / ``r + linear``  -> one GEMM with the residual-add epilogue,
+* ``silu(g) * u``                     -> one SwiGLU kernel,
+
+each only when the inner value has no other reader, exactly the reference's "a node joins
+its consumer when all its users share one root" rule.  The fused executables fall back to
+the composed PyTorch ops when the operands are not bf16 CUDA tensors, so planning is
+device-independent and the key does not need the device capabilities.
+
+A program frees every intermediate after its last reader (the reference's pooled-buffer
+"give" events) unless autograd keeps it alive.
+"""
+from __future__ import annotations
+
+import collections
+
+import torch
+
+from . import errors as E
+
+_MAX_PROGRAMS = 64
+_CACHE: "collections.OrderedDict[tuple, Program]" = collections.OrderedDict()
+_STATS = {"compiled": 0, "hits": 0, "uncacheable": 0, "fused": 0}
+
+
+def compiled() -> int:
+    """How many programs have been planned so far (tests use it to see cache hits: sched.Compiled)."""
+    return _STATS["compiled"]
+
+
+def stats() -> dict:
+    return dict(_STATS, cached=len(_CACHE))
+
+
+def clear_cache() -> None:
+    _CACHE.clear()
+
+
+class _Ref:
+    """Operand of an instruction: the value in ``slot`` of the running program."""
+    __slots__ = ("slot",)
+
+    def __init__(self, slot):
+        self.slot = slot
+
+
+class Program:
+    """A planned schedule: ``instrs`` = (fn, operand spec, kwargs, output slot, node index);
+    ``nleaves`` leaf slots come first, ``roots`` are the slots to return, ``last_use[slot]`` is
+    the instruction after which the slot is dropped."""
+
+    __slots__ = ("instrs", "nleaves", "nslots", "roots", "drop_after", "fused")
+
+    def __init__(self, instrs, nleaves, nslots, roots, fused):
+        self.instrs, self.nleaves, self.nslots, self.roots, self.fused = instrs, nleaves, nslots, roots, fused
+        keep = set(roots)
+        last = {}
+        for i, (_, spec, _, _, _) in enumerate(instrs):
+            for s in _spec_slots(spec):
+                last[s] = i
+        self.drop_after = [[] for _ in instrs]
+        for s, i in last.items():
+            if s not in keep and s >= nleaves:
+                self.drop_after[i].append(s)
+
+    def run(self, leaf_vals, order=None, on_error=None):
+        """Runs the instructions over ``leaf_vals``.  ``order`` is the node list of the graph being
+        run: instructions whose executable is volatile take it from there."""
+        slots = list(leaf_vals) + [None] * (self.nslots - self.nleaves)
+        for i, (fn, spec, kw, out, node_idx) in enumerate(self.instrs):
+            if order is not None and getattr(fn, "_mimir_volatile", False):
+                fn = order[node_idx]._fn
+            try:
+                slots[out] = fn(*_fill(spec, slots), **kw)
+            except E.MimirError as err:
+                if on_error is not None:
+                    on_error(node_idx, err)
+                raise
+            except Exception as exc:  # noqa: BLE001 - errors are values at the API surface
+                if type(exc).__module__.startswith("torch.utils.checkpoint"):
+                    raise  # control flow of activation recomputation, not a failure
+                err = E.classify(exc)
+                if on_error is not None:
+                    on_error(node_idx, err)
+                raise err from exc
+            for s in self.drop_after[i]:
+                slots[s] = None
+        return [slots[r] for r in self.roots]
+
+
+def _spec_slots(spec):
+    for a in spec:
+        if isinstance(a, _Ref):
+            yield a.slot
+        elif isinstance(a, (list, tuple)):
+            yield from _spec_slots(a)
+
+
+def _fill(spec, slots):
+    out = []
+    for a in spec:
+        if isinstance(a, _Ref):
+            out.append(slots[a.slot])
+        elif isinstance(a, (list, tuple)):
+            out.append(type(a)(_fill(a, slots)))
+        else:
+            out.append(a)
+    return out
+
+
+def _fn_key(fn):
+    """Identity of an executable for the structural key: its code and the constants it closes over.
+    A closed-over torch tensor (a frequency table, a mask) is keyed by identity: the cached program
+    keeps the first closure alive, so the identity cannot be reused while the entry lives.  Returns
+    None when a cell holds something that cannot be keyed (a lazy tensor, a list)."""
+    from .core import Tensor
+    code = getattr(fn, "__code__", None)
+    if code is None:
+        return None
+    if getattr(fn, "_mimir_volatile", False):
+        # the closure holds a per-call constant (a dropout or sampling seed): keyed by code only,
+        # and a cached program takes this instruction's executable from the graph being run
+        # (the reference keeps Attrs.Seed and Attrs.Value out of the key the same way)
+        return (code, "volatile")
+    cells = []
+    for c in (fn.__closure__ or ()):
+        v = c.cell_contents
+        if isinstance(v, torch.Tensor):
+            cells.append(("tensor", id(v)))
+        elif isinstance(v, (Tensor, list, dict, set)):
+            return None
+        elif callable(v) and hasattr(v, "__code__"):
+            k = _fn_key(v)
+            if k is None:
+                return None
+            cells.append(k)
+        else:
+            try:
+                hash(v)
+            except TypeError:
+                return None
+            cells.append(v)
+    return (code, tuple(cells), getattr(fn, "__defaults__", None))
+
+
+def _plain_key(a):
+    if isinstance(a, (list, tuple)):
+        return tuple(_plain_key(x) for x in a)
+    if isinstance(a, torch.Tensor):
+        return ("tensor", id(a))
+    hash(a)
+    return a
+
+
+class _Walk:
+    """One pass over the unrealized graph below the roots: topological order, reader counts."""
+
+    def __init__(self, roots, memo, reuse_cached):
+        from .core import Tensor, _flatten
+        self.order, self.leaves = [], []          # interior nodes (post-order), leaf nodes
+        self.readers = collections.Counter()
+        self.index = {}                           # id(node) -> ("n", i) | ("l", i)
+        for root in roots:
+            if root._err is not None:
+                raise root._err
+            self.readers[id(root)] += 1
+            stack = [(root, False)]
+            while stack:
+                t, expanded = stack.pop()
+                if id(t) in self.index:
+                    continue
+                is_leaf = id(t) in memo or t._fn is None or (reuse_cached and t._val is not None)
+                if is_leaf:
+                    if id(t) not in memo and t._val is None:
+                        raise E.ErrNilTensor("tensor has neither a value nor a producer")
+                    self.index[id(t)] = ("l", len(self.leaves))
+                    self.leaves.append(t)
+                    continue
+                kids = [a for a in _flatten(t._args) if isinstance(a, Tensor)]
+                if expanded:
+                    self.index[id(t)] = ("n", len(self.order))
+                    self.order.append(t)
+                    continue
+                stack.append((t, True))
+                for a in kids:
+                    self.readers[id(a)] += 1
+                for a in reversed(kids):
+                    if id(a) not in self.index:
+                        stack.append((a, False))
+        # a node pushed twice before its first expansion is counted once per reader, which is
+        # what the planner wants; ``index`` makes every node appear once in ``order``
+
+
+def _single_reader(w: _Walk, t) -> bool:
+    return w.readers[id(t)] == 1 and w.index.get(id(t), ("l",))[0] == "n"
+
+
+def _plan_fusion(w: _Walk):
+    """Returns {id(consumer): (fn, args, kw, absorbed node)} for the patterns listed in the module
+    docstring.  An absorbed node is not scheduled on its own."""
+    from . import core as C
+    out, absorbed = {}, set()
+    for t in w.order:
+        op = t._opname
+        if op == "gelu" and (t._attrs or {}).get("approximate") == "tanh":
+            (x,) = t._args
+            a = x._attrs or {}
+            if isinstance(x, C.Tensor) and x._opname == "linear" and a.get("act") == 0 and not a.get("residual") \
+                    and _single_reader(w, x) and id(x) not in absorbed:
+                out[id(t)] = (C._linear_run(1, a["bias"], False), x._args, {}, x)
+                absorbed.add(id(x))
+        elif op == "add":
+            p, q = t._args
+            for lin, res in ((p, q), (q, p)):
+                a = (lin._attrs or {}) if isinstance(lin, C.Tensor) else {}
+                if isinstance(lin, C.Tensor) and isinstance(res, C.Tensor) and lin._opname == "linear" \
+                        and a.get("act") == 0 and not a.get("residual") and _single_reader(w, lin) \
+                        and id(lin) not in absorbed and tuple(res.shape) == tuple(lin.shape) == tuple(t.shape) \
+                        and res.dtype == lin.dtype == t.dtype and id(res) not in absorbed:
+                    out[id(t)] = (C._linear_run(0, a["bias"], True), tuple(lin._args) + (res,), {}, lin)
+                    absorbed.add(id(lin))
+                    break
+        elif op == "mul":
+            p, q = t._args
+            for act, up in ((p, q), (q, p)):
+                if isinstance(act, C.Tensor) and isinstance(up, C.Tensor) and act._opname == "silu" \
+                        and _single_reader(w, act) and id(act) not in absorbed \
+                        and tuple(act.shape) == tuple(up.shape) == tuple(t.shape) and act.dtype == up.dtype:
+                    out[id(t)] = (C._swiglu_run, (act._args[0], up), {}, act)
+                    absorbed.add(id(act))
+                    break
+    return out, absorbed
+
+
+def _compile(w: _Walk, roots, fusion, absorbed):
+    from .core import Tensor
+    nleaves = len(w.leaves)
+    slot_of = {id(t): i for i, t in enumerate(w.leaves)}
+    instrs, nxt = [], nleaves
+
+    def spec_of(args):
+        sp = []
+        for a in args:
+            if isinstance(a, Tensor):
+                sp.append(_Ref(slot_of[id(a)]))
+            elif isinstance(a, (list, tuple)):
+                sp.append(type(a)(spec_of(a)))
+            else:
+                sp.append(a)
+        return tuple(sp)
+
+    for i, t in enumerate(w.order):
+        if id(t) in absorbed:
+            continue
+        if id(t) in fusion:
+            fn, args, kw, _ = fusion[id(t)]
+        else:
+            fn, args, kw = t._fn, t._args, t._kw
+        slot_of[id(t)] = nxt
+        instrs.append((fn, spec_of(args), kw, nxt, i))
+        nxt += 1
+    return Program(instrs, nleaves, nxt, [slot_of[id(r)] for r in roots], len(fusion))
+
+
+def _structural_key(w: _Walk, roots):
+    """Key of the walked graph, or None when some executable cannot be keyed."""
+    from .core import Tensor
+    parts = []
+    try:
+        for t in w.leaves:
+            parts.append(("L", tuple(t.shape), t.dtype, repr(t.device)))
+        for t in w.order:
+            fk = _fn_key(t._fn)
+            if fk is None:
+                return None
+
+            def arg_key(a):
+                if isinstance(a, Tensor):
+                    return w.index[id(a)]
+                if isinstance(a, (list, tuple)):
+                    return tuple(arg_key(x) for x in a)
+                return _plain_key(a)
+            parts.append((fk, tuple(arg_key(a) for a in t._args), tuple(sorted((k, _plain_key(v)) for k, v in t._kw.items())),
+                          tuple(t.shape), t.dtype, w.readers[id(t)]))
+        parts.append(tuple(w.index[id(r)] for r in roots))
+        key = tuple(parts)
+        hash(key)
+        return key
+    except TypeError:
+        return None
+
+
+def schedule(roots, memo=None, reuse_cached=True):
+    """Plans (or finds) the program of ``roots`` and returns ``(program, walk)``; the caller runs it
+    with the leaf values of *its* graph (``walk.leaves`` in order)."""
+    memo = {} if memo is None else memo
+    w = _Walk(roots, memo, reuse_cached)
+    key = _structural_key(w, roots)
+    if key is not None:
+        prog = _CACHE.get(key)
+        if prog is not None:
+            _CACHE.move_to_end(key)
+            _STATS["hits"] += 1
+            return prog, w
+    else:
+        _STATS["uncacheable"] += 1
+    fusion, absorbed = _plan_fusion(w)
+    prog = _compile(w, roots, fusion, absorbed)
+    _STATS["compiled"] += 1
+    _STATS["fused"] += len(fusion)
+    if key is not None:
+        _CACHE[key] = prog
+        while len(_CACHE) > _MAX_PROGRAMS:
+            _CACHE.popitem(last=False)
+    return prog, w

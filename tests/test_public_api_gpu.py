@@ -1,0 +1,144 @@
+"""The public lazy tensor / nn / optim / train path on the native sm_100a kernels: a tiny GPT-2 built
+from ``nn.DecoderBlock`` trains in bf16 through ``train.fit`` and matches fp32 PyTorch in losses and in
+EVERY parameter's gradient, with no PyTorch library product / attention / normalisation / loss call."""
+import contextlib
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+F = torch.nn.functional
+
+
+@contextlib.contextmanager
+def _no_library_ops():
+    """Every PyTorch entry point the native kernels replace raises while this is active."""
+    def trap(name):
+        def f(*a, **k):
+            raise AssertionError(f"library op {name} was called on the native path")
+        return f
+    saved = []
+    for owner, name in [(F, "linear"), (F, "scaled_dot_product_attention"), (F, "layer_norm"), (F, "cross_entropy"),
+                        (F, "gelu"), (F, "embedding"), (torch, "matmul"), (torch, "mm"), (torch, "bmm"),
+                        (torch, "addmm"), (torch, "einsum"), (torch.Tensor, "__matmul__"), (torch.Tensor, "matmul")]:
+        saved.append((owner, name, getattr(owner, name)))
+        setattr(owner, name, trap(name))
+    try:
+        yield
+    finally:
+        for owner, name, fn in saved:
+            setattr(owner, name, fn)
+
+
+def _model(dtype=torch.bfloat16):
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from _tiny_gpt import TinyGPT
+    nn.manual_seed(11)
+    m = TinyGPT()
+    ref = {n: p._data.clone().float() for n, p in m.named_params()}
+    m.cast(dtype).to(T.GPU(0))
+    return m, ref
+
+
+def test_every_parameter_gets_its_gradient_from_the_native_kernels():
+    import mimir_b200.tensor as T
+    from mimir_b200 import _native
+    from mimir_b200.ops._util import check_error_word
+    from _tiny_gpt import loss_fn, torch_reference
+    m, ref = _model()
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, m.vocab, (4, 128), generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    lib = _native.lib()
+    n0 = lib.mimir_launch_count()
+    with _no_library_ops():
+        loss = loss_fn(m.vocab)(m(T.tensor(tok, device=T.GPU(0))), T.tensor(tgt, device=T.GPU(0)))
+        loss.backward()
+    assert lib.mimir_launch_count() - n0 >= 40          # the native kernels did the work
+    assert check_error_word() == 0
+    rp = {n: v.cuda().requires_grad_(True) for n, v in ref.items()}
+    # the reference starts from the bf16-rounded weights the model really has
+    with torch.no_grad():
+        for n, p in m.named_params():
+            rp[n].copy_(p._data.float())
+    rl = torch_reference(m, rp, tok.cuda(), tgt.cuda())
+    rl.backward()
+    assert abs(loss.item() - rl.item()) < 3e-2, (loss.item(), rl.item())
+    for n, p in m.named_params():
+        assert p._grad is not None, f"{n} got no gradient"
+        a, b = p._grad.float(), rp[n].grad
+        err = (a - b).norm() / (b.norm() + 1e-12)
+        assert err < 6e-2, (n, float(err))
+
+
+def test_fit_trains_in_bf16_like_fp32_pytorch():
+    import mimir_b200.tensor as T
+    from mimir_b200 import data, optim
+    from mimir_b200.ops._util import check_error_word
+    from mimir_b200.tensor import plan
+    from mimir_b200.train import fit
+    from _tiny_gpt import loss_fn, torch_reference
+    m, ref = _model()
+    g = torch.Generator().manual_seed(6)
+    tok = torch.randint(0, m.vocab, (40, 128), generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    ds = data.Tensors(tok, tgt, batch_size=4, shuffle=False)
+    opt = optim.AdamW(m.parameters(), lr=1e-3, weight_decay=0.01, master_weights=True, clip_norm=1.0)
+    losses = []
+    plan.clear_cache()
+    before = plan.compiled()
+    with _no_library_ops():
+        fit(m, opt, ds, loss=loss_fn(m.vocab), epochs=1, on_batch=lambda b: losses.append(b.loss), device=T.GPU(0))
+    assert check_error_word() == 0
+    assert opt._flat is not None, "AdamW with master weights did not take the fused flat path"
+    assert plan.compiled() - before <= 2, plan.stats()          # ten steps, one planned schedule
+    # fp32 PyTorch on the same data
+    rp = {n: torch.nn.Parameter(v.to(torch.bfloat16).float().cuda()) for n, v in ref.items()}
+    ropt = torch.optim.AdamW(rp.values(), lr=1e-3, weight_decay=0.01)
+    rlosses = []
+    for i in range(0, 40, 4):
+        ropt.zero_grad()
+        l = torch_reference(m, rp, tok[i:i + 4].cuda(), tgt[i:i + 4].cuda())
+        l.backward()
+        torch.nn.utils.clip_grad_norm_(rp.values(), 1.0)
+        ropt.step()
+        rlosses.append(l.item())
+    assert len(losses) == 10
+    for a, b in zip(losses, rlosses):
+        assert abs(a - b) < 5e-2, (losses, rlosses)
+    assert losses[-1] < losses[0]
+    for n, p in m.named_params():
+        d = (p._data.float() - rp[n].data).abs().max().item()
+        assert d < 2e-2, (n, d)
+
+
+def test_llama_block_trains_through_native_rmsnorm_swiglu_and_gqa():
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.ops._util import check_error_word
+    nn.manual_seed(3)
+    blk = nn.DecoderBlock(128, 2, hidden=256, kv_heads=1, style="llama")
+    for p in blk.parameters():
+        if p._data.dim() == 2:
+            p._data.mul_(0.3)
+    x = torch.randn(2, 128, 128) * 0.5
+    want = []
+    # fp32 CPU run of the same lazy code is the oracle
+    out = blk(T.tensor(x, device=T.CPU()))
+    T.mean(out * out).backward()
+    want = {n: p._grad.clone() for n, p in blk.named_params()}
+    lref = float(T.mean(out * out).item())
+    blk.zero_grad()
+    blk.cast(torch.bfloat16).to(T.GPU(0))
+    with _no_library_ops():
+        out = blk(T.tensor(x.to(torch.bfloat16), device=T.GPU(0)))
+        l = T.mean(out * out)
+        l.backward()
+    assert check_error_word() == 0
+    assert abs(l.item() - lref) < 3e-2 * max(1.0, abs(lref))
+    for n, p in blk.named_params():
+        assert p._grad is not None, n
+        a, b = p._grad.float().cpu(), want[n]
+        assert (a - b).norm() / (b.norm() + 1e-12) < 8e-2, n
