@@ -65,14 +65,16 @@ class MasterAdamW:
     def __init__(self, params, lr, betas, weight_decay):
         self.params = [p for p in params if p.requires_grad]
         self.master = [p.detach().float().clone().requires_grad_(True) for p in self.params]
-        self.opt = torch.optim.AdamW(self.master, lr=lr, betas=betas, weight_decay=weight_decay, fused=True)
+        self.opt = torch.optim.AdamW(self.master, lr=lr, betas=betas, weight_decay=weight_decay, fused=True,
+                                     capturable=True)
 
     def step(self, grad_scale: float = 1.0):
         grads = [p.grad for p in self.params]
         for m, g in zip(self.master, grads):
             m.grad = g.float() if grad_scale == 1.0 else g.float() * grad_scale
         self.opt.step()
-        torch._foreach_copy_(self.params, self.master)
+        with torch.no_grad():
+            torch._foreach_copy_(self.params, self.master)
         for p in self.params:
             p.grad = None
 
@@ -86,7 +88,7 @@ class TorchTrainer:
         self.net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True) \
             if ddp else model
         self.opt = MasterAdamW(model.parameters(), lr, betas, weight_decay)
-        self.graph, self.use_graph, self._warm = None, graph and not ddp, 0
+        self.graph, self.use_graph = None, graph and not ddp
         self.tok = self.tgt = None
         self.loss = torch.zeros((), device="cuda")
 
@@ -100,21 +102,22 @@ class TorchTrainer:
         if not self.use_graph:
             return self._device_step()
         if self.graph is None:
-            if self._warm < 3:
-                self._warm += 1
-                s = torch.cuda.Stream()
-                s.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(s):
+            # whole-step capture as PyTorch documents it: warm up on a side stream, then capture
+            import sys
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(3):
                     self._device_step()
-                torch.cuda.current_stream().wait_stream(s)
-                return
+            torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             try:
                 with torch.cuda.graph(g):
                     self._device_step()
                 self.graph = g
-            except Exception:  # noqa: BLE001 - a baseline that cannot be captured runs eagerly
+            except Exception as exc:  # noqa: BLE001 - a baseline that cannot be captured runs eagerly
+                sys.stderr.write(f"[baseline] CUDA graph capture failed, running eagerly: {exc}\n")
                 self.use_graph = False
                 torch.cuda.synchronize()
                 return self._device_step()

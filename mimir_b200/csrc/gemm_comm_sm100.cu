@@ -19,6 +19,11 @@
 //   slabs of its rows in fp32 and writes the bf16 result.
 //   (Reference: reduceScatter of partial sums, tensor/reshard.go:242-302.)
 //
+//   Slab reuse: a rank that has summed its slabs of call k publishes "read k" to every
+//   peer (second half of the signal pad); the epilogue of call k+1 waits (bounded) for the
+//   owner's "read k" before its first store into that owner's slab, so back-to-back calls
+//   on the same object need no host barrier and no other collective in between.
+//
 // No TMA *load* touches peer memory with any cluster-wide qualifier: remote data is
 // read with ld.relaxed.sys and written by TMA stores or st; all waits are bounded.
 #include "gemm_pair.cuh"
@@ -28,6 +33,7 @@ namespace mimir {
 constexpr int kCommRanks = 8;
 constexpr int kCommThreads = 352;  // TMA warp, MMA warp, 8 epilogue warps, gather warp
 constexpr int kCommEpiWarps = 8;
+constexpr int kCommReadFlags = 512;  // word offset of the "owner has read call k" flags in a signal pad
 
 struct CommArgs {
   // all-gather: every rank's full-size W buffer (rank r's shard is valid in buffer r)
@@ -231,6 +237,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t tempty_leader0 = map_to_cta(smem_u32(&tempty[0]), 0);
     const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty[1]), 0);
     uint32_t ti = 0, ring = 0;
+    uint32_t owner_ready = 0;  // owners whose "read" flag of the previous call this warp has seen
     uint8_t* wbuf = out_ring + (warp - 2) * 2 * 4096;
     for (int u = pair; u < units; u += npairs, ++ti) {
       int m_idx, n_idx;
@@ -245,6 +252,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // bf16 partial sub-tiles go to the staging slab of the rank that owns these rows
         const int owner = min(row0 / rpr, cm.world - 1);
         const CUtensorMap* tmo = &tmStage.m[owner];
+        if (!((owner_ready >> owner) & 1u)) {
+          // the owner must have finished summing the previous call's slabs before they are overwritten
+          if (lane == 0)
+            wait_count<true>(cm.sig[cm.rank] + kCommReadFlags + cm.slot * kCommRanks + owner, epoch, cm.wait_ns, err);
+          __syncwarp();
+          owner_ready |= 1u << owner;
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / 128; ++c) {
           uint32_t r0[32], r1[32], pk[32];
@@ -361,6 +375,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       *cm.done_count = 0;
       if (COMM == 1)
         for (int s = 0; s < cm.world; ++s) cm.shard_count[s] = 0;
+      if (COMM == 2) {
+        // every CTA of this rank has summed its part: the slabs may be overwritten by call epoch + 1
+        __threadfence_system();
+        for (int p = 0; p < cm.world; ++p)
+          st_release_sys_c(cm.sig[p] + kCommReadFlags + cm.slot * kCommRanks + cm.rank, epoch + 1);
+      }
       __threadfence();
       *cm.epoch = epoch + 1;
     }

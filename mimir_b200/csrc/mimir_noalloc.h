@@ -24,7 +24,8 @@ extern "C" {
 // nothing: no cudaMalloc, no cudaFree, no allocating library routine.
 //
 //  * N must be a multiple of 8 and at most MIMIR_COLSUM_NOALLOC_MAX_N, ld a
-//    multiple of 8; otherwise the call returns -1 and mimir_last_error() says why.
+//    multiple of 8 and at least N; otherwise the call returns -1 and
+//    mimir_last_error() says why.
 //  * The first call on each device looks up the array's device address (once,
 //    with that device current).  Make that first call outside any stream capture.
 //  * All calls on a device share the one array and it keeps the last call's

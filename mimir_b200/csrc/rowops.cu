@@ -750,12 +750,14 @@ MIMIR_API int mimir_colsum_noalloc(const void* x, int rows, int N, int ld, void*
                                    cudaStream_t st) {
   if (rows <= 0 || N <= 0) return refuse("colsum_noalloc: empty input (%d x %d)", rows, N);
   if (N % 8 || ld % 8) return refuse("colsum_noalloc: N and ld must be multiples of 8");
+  if (ld < N) return refuse("colsum_noalloc: row pitch %d is smaller than the %d columns", ld, N);
   if (N > MIMIR_COLSUM_NOALLOC_MAX_N)
     return refuse("colsum_noalloc: N = %d exceeds the built-in scratch (at most %d columns); "
                   "use mimir_colsum with your own buffer",
                   N, MIMIR_COLSUM_NOALLOC_MAX_N);
   float* scratch = mimir::colsum_scratch_for_current_device();
   if (!scratch) return -1;
+  cudaGetLastError();  // an earlier, unrelated launch error must not be reported as this call's
   const int parts = rows >= 64 * 8 ? 64 : 1;  // same split as mimir_colsum, so results agree bit for bit
   dim3 grid(ceil_div(N, 256), parts);
   colsum_partial_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows, N, ld, scratch);

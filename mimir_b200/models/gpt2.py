@@ -115,9 +115,10 @@ class GPT2Engine:
         self._init_weights(seed)
         self._alloc_activations()
         self.step_count = 0
+        self._dp = None
         self.hyper = torch.zeros(4, dtype=torch.float32, device=self.device)
-        self.hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory() if torch.cuda.is_available() \
-            else torch.zeros(4)
+        from ..ops._util import PinnedRing
+        self._hyper_ring = PinnedRing(4)
 
     # ------------------------------------------------------------------ init
     def _init_weights(self, seed: int) -> None:
@@ -276,11 +277,7 @@ class GPT2Engine:
         """Stages lr and the step's bias corrections for the device-side AdamW arguments."""
         self.step_count += 1
         t = self.step_count
-        self.hyper_host[0] = lr
-        self.hyper_host[1] = 1.0 - beta1 ** t
-        self.hyper_host[2] = math.sqrt(1.0 - beta2 ** t)
-        self.hyper_host[3] = grad_scale
-        self.hyper.copy_(self.hyper_host, non_blocking=True)
+        self._hyper_ring.stage((lr, 1.0 - beta1 ** t, math.sqrt(1.0 - beta2 ** t), grad_scale), self.hyper)
 
     def adamw(self, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1) -> None:
         """One fused launch per bucket; lr / bias corrections come from ``self.hyper``."""
@@ -293,11 +290,21 @@ class GPT2Engine:
     # --------------------------------------------------------------- helpers
     def named_parameters(self):
         cfg = self.cfg
+        if getattr(self, "_dp", None) is not None:      # masters are sharded over the ranks: gather them
+            for k, w in self._dp.state_dict().items():
+                if k.startswith("model."):
+                    name = k[len("model."):]
+                    yield name, (w[: cfg.vocab] if name == "wte" else w)
+            return
         for name, w in self.layout.views(self.master).items():
             yield name, (w[: cfg.vocab] if name == "wte" else w)
 
     def state_dict(self) -> dict:
-        """Tensors named like the reference checkpoint: model.* and optim.<i>.<state>."""
+        """Tensors named like the reference checkpoint: model.* and optim.<i>.<state>.  Under fused data
+        parallelism the optimizer state lives sharded in the ``FusedDataParallel`` object, which
+        gathers it (every rank must call)."""
+        if getattr(self, "_dp", None) is not None:
+            return self._dp.state_dict()
         out = {}
         mv = self.layout.views(self.master)
         m = self.layout.views(self.exp_avg)
@@ -309,6 +316,8 @@ class GPT2Engine:
         return out
 
     def load_state_dict(self, sd: dict) -> None:
+        if getattr(self, "_dp", None) is not None:
+            return self._dp.load_state_dict(sd)
         mv = self.layout.views(self.master)
         m = self.layout.views(self.exp_avg)
         v = self.layout.views(self.exp_avg_sq)

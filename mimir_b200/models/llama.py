@@ -111,7 +111,8 @@ class LlamaEngine:
         self._alloc_activations()
         self.step_count = 0
         self.hyper = torch.zeros(4, dtype=torch.float32, device=self.device)
-        self.hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory() if torch.cuda.is_available() else torch.zeros(4)
+        from ..ops._util import PinnedRing
+        self._hyper_ring = PinnedRing(4)
 
     # ------------------------------------------------------------------ parameters
     def _alloc_params(self, seed: int) -> None:
@@ -403,11 +404,8 @@ class LlamaEngine:
     def set_hyper(self, lr: float, beta1: float, beta2: float, grad_scale: float = 1.0) -> None:
         self.step_count += 1
         t = self.step_count
-        self.hyper_host[0] = lr
-        self.hyper_host[1] = 1.0 - beta1 ** t
-        self.hyper_host[2] = math.sqrt(1.0 - beta2 ** t)
-        self.hyper_host[3] = 1.0      # the loss gradient already carries 1 / world
-        self.hyper.copy_(self.hyper_host, non_blocking=True)
+        # grad scale 1: the loss gradient already carries 1 / world
+        self._hyper_ring.stage((lr, 1.0 - beta1 ** t, math.sqrt(1.0 - beta2 ** t), 1.0), self.hyper)
 
     def adamw(self, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1) -> None:
         """AdamW on the owned rows: decayed matrices first, then the gains (not decayed)."""

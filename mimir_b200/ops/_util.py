@@ -29,3 +29,31 @@ def check_error_word(sync: bool = True) -> int:
     if sync:
         torch.cuda.synchronize()
     return int(_native.lib().mimir_error_word(1))
+
+
+class PinnedRing:
+    """Small pinned host buffers for values a step uploads asynchronously (learning rate, bias
+    corrections).  ``stage(values, dst)`` writes the next buffer and queues the copy; a buffer is
+    reused only after the copy it fed has completed (an event per buffer), so a host that runs
+    several steps ahead of the GPU can never overwrite values a pending copy still has to read."""
+
+    def __init__(self, numel: int = 4, depth: int = 4):
+        pin = torch.cuda.is_available()
+        self.bufs = [torch.zeros(numel, dtype=torch.float32).pin_memory() if pin else torch.zeros(numel)
+                     for _ in range(depth)]
+        self.events = [None] * depth
+        self.i = 0
+
+    def stage(self, values, dst: torch.Tensor) -> None:
+        i = self.i
+        self.i = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i]
+        for k, v in enumerate(values):
+            buf[k] = v
+        dst.copy_(buf, non_blocking=True)
+        if dst.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(dst.device))
+            self.events[i] = ev

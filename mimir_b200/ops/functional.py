@@ -30,11 +30,14 @@ def _scratch(key: str, numel: int, device, dtype=torch.float32) -> torch.Tensor:
     k = (key, device.index, torch.cuda.current_stream(device).cuda_stream, dtype)
     buf = _SCRATCH.get(k)
     if buf is None or buf.numel() < numel:
+        if buf is not None:
+            _RETIRED.append(buf)      # a captured CUDA graph may still point at it: never freed
         buf = _SCRATCH[k] = torch.empty(numel, dtype=dtype, device=device)
     return buf
 
 
 _SCRATCH: dict = {}
+_RETIRED: list = []
 
 
 def _rows(t: torch.Tensor) -> torch.Tensor:

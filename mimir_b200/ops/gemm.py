@@ -20,6 +20,7 @@ GEMM_FLAGS = {
 }
 
 _workspaces: dict = {}
+_retired: list = []
 
 
 def workspace(device, nbytes: int = 128 << 20) -> torch.Tensor:
@@ -27,6 +28,8 @@ def workspace(device, nbytes: int = 128 << 20) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device())
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)       # a captured CUDA graph may still point at it: never freed
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws

@@ -38,25 +38,27 @@ class FlatAdamW:
     captured in a CUDA graph replays with new values (internal/sched/key.go:28-44 keeps constants
     out of a schedule's key for the same reason)."""
 
-    def __init__(self, opt):
+    def __init__(self, opt, alloc=None, multiple: int = 8):
+        """``alloc(numel, dtype)`` supplies the parameter and gradient buffers (peer-visible memory for
+        data parallelism); ``multiple`` pads the total length (8 x ranks there)."""
         params = [p for p in opt.params if p.trainable]
         dev = params[0]._data.device
         offs, n = [], 0
         for p in params:
             offs.append(n)
             n += (p.numel() + 7) // 8 * 8
+        n = (n + multiple - 1) // multiple * multiple
         self.n, self.params, self.offsets = n, params, offs
-        self.param = torch.zeros(n, dtype=torch.bfloat16, device=dev)
-        self.grad = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        alloc = alloc or (lambda numel, dtype: torch.zeros(numel, dtype=dtype, device=dev))
+        self.param = alloc(n, torch.bfloat16)
+        self.grad = alloc(n, torch.bfloat16)
         self.master = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
-        # a small ring of pinned staging buffers: a buffer is rewritten only after three later
-        # steps have queued their copies, by which time its own copy has long completed
-        self._hyper_host = [torch.zeros(4).pin_memory() for _ in range(4)]
-        self._ring = 0
+        from ..ops._util import PinnedRing
+        self._ring = PinnedRing(4)
         index = {id(p): i for i, p in enumerate(opt.params)}
         for p, o in zip(params, offs):
             k, st = p.numel(), opt.state[index[id(p)]]
@@ -77,20 +79,29 @@ class FlatAdamW:
             p._version += 1
 
     def step(self, opt) -> None:
-        from ..ops import kernels as K
+        self.stage(opt)
+        self.gather_grads()
+        self.launch(opt)
+        self.bump()
+
+    def stage(self, opt) -> None:
+        """Host side of a step: the learning rate, the bias corrections of step ``opt.steps`` and the
+        gradient scale go to the device array the kernel reads (an asynchronous copy from pinned memory)."""
+        h = opt.hyper
+        b1, b2 = h.get("beta1", 0.9), h.get("beta2", 0.999)
+        self._ring.stage((opt.lr, 1.0 - b1 ** opt.steps, math.sqrt(1.0 - b2 ** opt.steps), 1.0 / opt.grad_scale),
+                         self.hyper)
+
+    def gather_grads(self) -> None:
+        """Makes the flat gradient buffer current: a parameter the loss did not reach gets zeros, a
+        gradient that was produced outside its slice is copied in."""
         for p in self.params:
-            if p._grad is None:           # a parameter the loss did not reach: no stale gradient
+            if p._grad is None:
                 p._grad_buf.zero_()
             elif p._grad is not p._grad_buf:
                 p._grad_buf.copy_(p._grad)
-        h = opt.hyper
-        b1, b2 = h.get("beta1", 0.9), h.get("beta2", 0.999)
-        host = self._hyper_host[self._ring]
-        self._ring = (self._ring + 1) % len(self._hyper_host)
-        host[0], host[1] = opt.lr, 1.0 - b1 ** opt.steps
-        host[2], host[3] = math.sqrt(1.0 - b2 ** opt.steps), 1.0 / opt.grad_scale
-        self.hyper.copy_(host, non_blocking=True)
-        self.launch(opt)
+
+    def bump(self) -> None:
         for p in self.params:
             p._version += 1
 

@@ -90,7 +90,13 @@ def gemm_allgather_baseline(x, w: ShardedWeight, group=None):
 
 
 class ReduceScatterGemm:
-    """State of one reduce-scatter call site: staging slabs [world][M/world][N] and flags."""
+    """State of one reduce-scatter call site: staging slabs [world][M/world][N] and flags.
+
+    Calls on one object may follow each other directly (same stream on every rank, no host barrier
+    and no other collective in between): a rank publishes "I have summed call k" to its peers, and
+    the kernel of call k+1 waits for the owner's flag before its first store into that owner's slabs.
+    Two objects never share slabs, so calls on different objects are independent.  The ranks must
+    issue the calls of one object in the same order."""
 
     def __init__(self, M: int, N: int, rank: int, world: int, group=None, slot: int = 0):
         if M % world or (M // world) % 32:

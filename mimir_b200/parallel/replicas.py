@@ -88,6 +88,9 @@ def fit_data_parallel(model, opt, ds, loss, epochs, group, schedule=None, on_epo
     """``train.fit`` over the ranks of ``group``: every rank iterates the same batches (same seed and
     epoch) and works on its block of each."""
     from ..train.fit import EpochReport
+    from .dp import FusedFlatDataParallel, fused_flat_eligible
+    if mode == "all_reduce" and fused_flat_eligible(opt, group):
+        return _fit_fused(model, opt, ds, loss, epochs, group, schedule, on_epoch, progress)
     par = Parallel(model, group, mode)
     reports, steps = [], 0
     for epoch in range(epochs):
@@ -109,4 +112,49 @@ def fit_data_parallel(model, opt, ds, loss, epochs, group, schedule=None, on_epo
             on_epoch(rep)
         if progress is not None and group.rank == 0:
             progress.write(f"epoch {rep.epoch}/{epochs} loss={rep.loss:.4f} lr={rep.lr:.3g} steps={rep.steps} {rep.duration:.1f}s\n")
+    return reports
+
+
+def _fit_fused(model, opt, ds, loss, epochs, group, schedule, on_epoch, progress):
+    """``fit_data_parallel`` on the fused peer-memory kernel (``parallel/dp.py``): every rank runs its
+    share of each batch through the lazy layer (native kernels), then one kernel per step reduces the
+    gradients, applies AdamW to the owned slice and distributes the new parameters."""
+    from ..train.fit import EpochReport
+    from .dp import FusedFlatDataParallel
+    fused = FusedFlatDataParallel(opt, group)
+    helper = Parallel.__new__(Parallel)
+    helper.group = group
+    reports, steps = [], 0
+    try:
+        for epoch in range(epochs):
+            t0 = time.perf_counter()
+            model.train()
+            if schedule is not None:
+                opt.lr = float(schedule(epoch))
+            ds.set_epoch(epoch)
+            total, rows = 0.0, 0
+            for batch in ds.all():
+                xd = batch.x.data().to(fused.flat.param.device)
+                yd = None if batch.y is None else batch.y.data().to(xd.device)
+                lo, hi, share = helper.shard(xd)
+                value = torch.zeros(1, device=xd.device)
+                fused.begin()
+                if hi > lo:
+                    l = loss(model(T.from_torch(xd[lo:hi])), None if yd is None else T.from_torch(yd[lo:hi])) * share
+                    l.backward()
+                    value = l._val.reshape(1).float()
+                fused.step()
+                dist_value = group.all_reduce(T.from_torch(value), "sum")
+                v = float(dist_value.data()[0])
+                steps += 1
+                total += v * xd.shape[0]
+                rows += xd.shape[0]
+            rep = EpochReport(epoch + 1, total / max(rows, 1), opt.lr, steps, time.perf_counter() - t0)
+            reports.append(rep)
+            if on_epoch:
+                on_epoch(rep)
+            if progress is not None and group.rank == 0:
+                progress.write(f"epoch {rep.epoch}/{epochs} loss={rep.loss:.4f} lr={rep.lr:.3g} steps={rep.steps} {rep.duration:.1f}s\n")
+    finally:
+        fused.close()
     return reports

@@ -182,7 +182,8 @@ class Tensor:
         if self._err is not None or device == self.device:
             return self
         src = self
-        return _node(lambda v: v.to(device.torch), (src,), {}, "to", device=device)
+        # shape inference runs on meta tensors, which have no data to move
+        return _node(lambda v: v if v.device.type == "meta" else v.to(device.torch), (src,), {}, "to", device=device)
 
     def backward(self) -> None:
         from .autograd import backward
@@ -454,8 +455,20 @@ def _lift(x, like: Tensor) -> Tensor:
         dt = like.dtype
         if isinstance(x, float) and not dt.is_floating_point:
             dt = float32
-        return Tensor(val=torch.tensor(x, dtype=dt, device=like.device.torch), shape=(), dtype=dt, device=like.device)
+        # constants are immutable leaves, so one device copy per (value, dtype, device) serves every
+        # graph; a training loop then uploads nothing for them (and a step can be captured into a
+        # CUDA graph, where host-to-device copies of pageable memory are not allowed)
+        key = (type(x), x, dt, like.device)
+        val = _CONSTS.get(key)
+        if val is None:
+            if len(_CONSTS) > 4096:
+                _CONSTS.clear()
+            val = _CONSTS[key] = torch.tensor(x, dtype=dt, device=like.device.torch)
+        return Tensor(val=val, shape=(), dtype=dt, device=like.device)
     return tensor(x, device=like.device)
+
+
+_CONSTS: dict = {}
 
 
 def _binary_dtype(a: Tensor, b: Tensor, opname: str):

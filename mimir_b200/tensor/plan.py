@@ -140,6 +140,8 @@ def _fn_key(fn):
         v = c.cell_contents
         if isinstance(v, torch.Tensor):
             cells.append(("tensor", id(v)))
+        elif isinstance(v, (list, tuple)) and all(isinstance(x, (int, float, bool, str, type(None))) for x in v):
+            cells.append(tuple(v))          # a list of plain constants (split sizes, axes)
         elif isinstance(v, (Tensor, list, dict, set)):
             return None
         elif callable(v) and hasattr(v, "__code__"):

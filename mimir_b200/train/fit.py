@@ -8,7 +8,8 @@ until the estimate fits), ``loss_scale`` / ``dynamic_loss_scale`` (start 65536,
 halve on a non-finite gradient and skip the step, double after 2000 good steps,
 floor 1: train.go:194-210,536-560), ``precise_batch_norm``, ``on_epoch`` /
 ``on_batch`` callbacks and ``progress``.  A step that fails leaves no gradients
-behind (train.go:504-508).
+behind (train.go:504-508).  On a GPU, steps whose structure repeats are captured
+into a CUDA graph and replayed (``train/replay.py``).
 """
 from __future__ import annotations
 
@@ -129,6 +130,8 @@ def fit(model, opt, ds, loss=None, epochs: int = 1, eval=None, metrics=(), check
     reports, best, since_best = [], float("inf"), 0
     if memory_budget is not None:
         T.set_memory_budget(device, memory_budget)
+    from .replay import StepReplay
+    replay = StepReplay(model, opt, loss, device)     # CUDA-graph replay of whole steps where it applies
     try:
         for epoch in range(start_epoch, epochs):
             t0 = time.perf_counter()
@@ -144,6 +147,18 @@ def fit(model, opt, ds, loss=None, epochs: int = 1, eval=None, metrics=(), check
                 if micro_batch and x.shape[0] > micro_batch:
                     parts = (x.shape[0] + micro_batch - 1) // micro_batch
                 skipped, value = False, 0.0
+                if replay.enabled and parts == 1 and memory_budget is None and not dynamic_loss_scale and scale == 1.0:
+                    opt.grad_scale = 1.0
+                    lt = replay.step(x.data(), None if y is None else y.data())
+                    if lt is not None:
+                        value = float(lt.item())
+                        steps += 1
+                        good_steps += 1
+                        total += value * x.shape[0]
+                        rows += x.shape[0]
+                        if on_batch:
+                            on_batch(BatchReport(value, False, scale))
+                        continue
                 while True:
                     try:
                         value = 0.0

@@ -101,4 +101,12 @@ class FusedTrainer:
         self.run_device_step()
         self._loss_host.copy_(e.loss, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        # the error word lives in host-mapped memory: reading it costs a memory load.  A wait on a peer
+        # that ran out means this rank skipped its slice of the update, so the step must not pass
+        # silently (the word is cleared: the caller decides whether to resume from a checkpoint).
+        word = int(_native.lib().mimir_error_word(0))
+        if word:
+            from ..parallel.health import DeviceFault
+            _native.lib().mimir_error_word(1)
+            raise DeviceFault(word)
         return float(self._loss_host[0])

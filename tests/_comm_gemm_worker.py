@@ -62,6 +62,24 @@ def main():
     out = rs(at, bt, transposed=True)
     torch.cuda.synchronize()
     res["rs_tn_err"] = ((out.float() - full[rank * rpr: (rank + 1) * rpr]).abs().max() / full.abs().max()).item()
+    # ---- back-to-back calls on the same object with different inputs and NO host synchronisation or
+    # barrier in between: a rank that runs ahead must not overwrite slabs its peer is still summing
+    torch.cuda.synchronize()
+    dist.barrier()
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    ins = [(torch.randn(M2, K2, device="cuda", generator=gen).bfloat16(),
+            (torch.randn(N2, K2, device="cuda", generator=gen) * 0.1).bfloat16()) for _ in range(6)]
+    outs = []
+    for i, (ai, bi) in enumerate(ins):
+        if i in (2, 4) and rank == (i // 2) % world:
+            torch.cuda._sleep(40_000_000)          # this rank falls behind: its peers reach the next call first
+        outs.append(rs(ai, bi))
+    torch.cuda.synchronize()
+    worst = 0.0
+    for (ai, bi), o in zip(ins, outs):
+        ref = FG.gemm_reduce_scatter_baseline(ai, bi, world)
+        worst = max(worst, ((o.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-6)).item())
+    res["rs_b2b_err"] = worst
     res["err"] = check_error_word()
     dist.barrier()
     w.close()

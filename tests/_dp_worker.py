@@ -50,6 +50,24 @@ def main():
         result["single"] = [t1.step(tok, tgt) for _ in range(steps)]
         diff = (e1.params.float() - eng.params.float()).abs().max().item()
         result["max_param_diff"] = diff
+    # ---- checkpoint under data parallelism: save, one more step; fresh replica, load, same step
+    sd = {k: v.clone() for k, v in eng.state_dict().items()}
+    count = eng.step_count
+    tr.step(tok[my], tgt[my])
+    torch.cuda.synchronize()
+    after = eng.params.clone()
+    dp2 = FusedDataParallel(rank, world, local)
+    eng2 = GPT2Engine(cfg, Bl, T, device=f"cuda:{local}", seed=99, flat_alloc=dp2.alloc_shared)   # other weights
+    dp2.attach(eng2)
+    eng2.load_state_dict(sd)
+    eng2.step_count = count
+    tr2 = FusedTrainer(eng2, lr=2e-3, dp=dp2, use_graph=False)
+    tr2.step(tok[my], tgt[my])
+    torch.cuda.synchronize()
+    result["resume_identical"] = bool(torch.equal(after.view(torch.int16), eng2.params.view(torch.int16)))
+    result["ckpt_names"] = sorted(sd)[:3]
+    result["err2"] = check_error_word()
+    dp2.close()
     dp.close()
     dist.destroy_process_group()
     os.write(1, ("RESULT " + json.dumps(result) + "\n").encode())  # one write: lines of different ranks never interleave

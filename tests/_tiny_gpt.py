@@ -17,14 +17,16 @@ class TinyGPT(nn.Module):
         self.blocks = [nn.DecoderBlock(dim, heads, style="gpt2") for _ in range(layers)]
         self.lnf = nn.LayerNorm(dim)
         self.head = nn.Linear(dim, vocab, bias=False)
+        self._nn_skip_pos = None      # position ids, uploaded once
         for _, p in self.named_params():       # GPT-2 sized initial weights keep bf16 well conditioned
             if p._data.dim() == 2:
                 p._data.mul_(0.2)
 
     def forward(self, tok):
         B, Tq = tok.shape
-        pos = T.tensor(torch.arange(Tq), dtype=torch.int64, device=tok.device)
-        x = self.wte(tok) + self.wpe(pos)
+        if self._nn_skip_pos is None or self._nn_skip_pos.device != tok.device:
+            self._nn_skip_pos = T.tensor(torch.arange(self.ctx), dtype=torch.int64, device=tok.device)
+        x = self.wte(tok) + self.wpe(self._nn_skip_pos[:Tq])
         for b in self.blocks:
             x = b(x)
         return self.head(self.lnf(x))

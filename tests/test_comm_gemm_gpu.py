@@ -24,3 +24,4 @@ def test_fused_collective_gemms_two_gpus():
     for r in res:
         assert r["err"] == 0, r
         assert r["ag_err"] < 2e-2 and r["rs_err"] < 2e-2 and r["rs_tn_err"] < 2e-2, r
+        assert r["rs_b2b_err"] < 2e-2, r      # six calls in a row, no host barrier, ranks out of step

@@ -29,6 +29,8 @@ def test_dp2_matches_single_device(graph):
     for r in res:
         assert r["err"] == 0
         assert r["identical"], "replicas diverged"
+        assert r["resume_identical"], "a data-parallel checkpoint did not resume bit for bit"
+        assert r["err2"] == 0
     r0 = [r for r in res if r["rank"] == 0][0]
     for a, b in zip(r0["losses"], r0["single"]):
         assert abs(a - b) < 3e-2, (r0["losses"], r0["single"])

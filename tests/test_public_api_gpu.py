@@ -14,8 +14,10 @@ F = torch.nn.functional
 @contextlib.contextmanager
 def _no_library_ops():
     """Every PyTorch entry point the native kernels replace raises while this is active."""
-    def trap(name):
+    def trap(name, real):
         def f(*a, **k):
+            if any(torch.is_tensor(x) and x.device.type == "meta" for x in a):
+                return real(*a, **k)          # shape inference on meta tensors launches nothing
             raise AssertionError(f"library op {name} was called on the native path")
         return f
     saved = []
@@ -23,7 +25,7 @@ def _no_library_ops():
                         (F, "gelu"), (F, "embedding"), (torch, "matmul"), (torch, "mm"), (torch, "bmm"),
                         (torch, "addmm"), (torch, "einsum"), (torch.Tensor, "__matmul__"), (torch.Tensor, "matmul")]:
         saved.append((owner, name, getattr(owner, name)))
-        setattr(owner, name, trap(name))
+        setattr(owner, name, trap(name, getattr(owner, name)))
     try:
         yield
     finally:
@@ -94,6 +96,7 @@ def test_fit_trains_in_bf16_like_fp32_pytorch():
     assert check_error_word() == 0
     assert opt._flat is not None, "AdamW with master weights did not take the fused flat path"
     assert plan.compiled() - before <= 2, plan.stats()          # ten steps, one planned schedule
+    assert plan.stats()["uncacheable"] == 0
     # fp32 PyTorch on the same data
     rp = {n: torch.nn.Parameter(v.to(torch.bfloat16).float().cuda()) for n, v in ref.items()}
     ropt = torch.optim.AdamW(rp.values(), lr=1e-3, weight_decay=0.01)
@@ -112,6 +115,51 @@ def test_fit_trains_in_bf16_like_fp32_pytorch():
     for n, p in m.named_params():
         d = (p._data.float() - rp[n].data).abs().max().item()
         assert d < 2e-2, (n, d)
+
+
+def test_fit_replays_captured_steps_and_matches_the_eager_path():
+    """Steps 3.. of ``fit`` run as CUDA-graph replays; the trained weights equal those of the same run
+    with replay switched off, bit for bit (same kernels, same order)."""
+    import os
+    import mimir_b200.tensor as T
+    from mimir_b200 import _native, data, optim
+    from mimir_b200.ops._util import check_error_word
+    from mimir_b200.train import fit
+    from mimir_b200.train import replay as R
+    from _tiny_gpt import loss_fn
+    g = torch.Generator().manual_seed(8)
+    tok = torch.randint(0, 512, (48, 128), generator=g)
+    tgt = torch.roll(tok, -1, 1)
+    results = []
+    for graphs in ("1", "0"):
+        os.environ["MIMIR_CUDA_GRAPHS"] = graphs
+        m, _ = _model()
+        ds = data.Tensors(tok, tgt, batch_size=4, shuffle=False)
+        opt = optim.AdamW(m.parameters(), lr=1e-3, master_weights=True, clip_norm=1.0)
+        seen = []
+        made = []
+        orig = R.StepReplay.__init__
+
+        def spy(self, *a, **k):
+            orig(self, *a, **k)
+            made.append(self)
+        R.StepReplay.__init__ = spy
+        try:
+            fit(m, opt, ds, loss=loss_fn(m.vocab), epochs=1, schedule=lambda e: 1e-3, on_batch=lambda b: seen.append(b.loss),
+                device=T.GPU(0))
+        finally:
+            R.StepReplay.__init__ = orig
+            os.environ.pop("MIMIR_CUDA_GRAPHS", None)
+        assert check_error_word() == 0
+        results.append(([p._data.clone() for p in m.parameters()], seen, made[0], opt.steps))
+    (wa, la, ra, sa), (wb, lb, rb, sb) = results
+    assert ra.captures == 1 and ra.replays == 12 - 3, (ra.captures, ra.replays)
+    assert rb.captures == 0 and rb.replays == 0
+    assert sa == sb == 12
+    assert la == lb, (la, lb)
+    for a, b in zip(wa, wb):
+        assert torch.equal(a, b)
+    assert _native.lib().mimir_launch_count() > 0
 
 
 def test_llama_block_trains_through_native_rmsnorm_swiglu_and_gqa():
@@ -142,3 +190,29 @@ def test_llama_block_trains_through_native_rmsnorm_swiglu_and_gqa():
         assert p._grad is not None, n
         a, b = p._grad.float().cpu(), want[n]
         assert (a - b).norm() / (b.norm() + 1e-12) < 8e-2, n
+
+
+def test_fit_data_parallel_on_two_gpus_equals_one_gpu():
+    """``fit(data_parallel=)`` takes the fused reduce + AdamW + broadcast kernel; two ranks on halves of
+    every batch end where one device ends on the whole batch, replicas bit-identical, optimizer state
+    whole again after the run."""
+    import json
+    import os
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29561", os.path.join(here, "_public_dp_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-3000:]
+    res = [json.loads(l[7:]) for l in out.stdout.splitlines() if l.startswith("RESULT ")]
+    assert len(res) == 2
+    for r in res:
+        assert r["err"] == 0 and r["identical"] and r["steps"] == 8, r
+    r0 = [r for r in res if r["rank"] == 0][0]
+    for a, b in zip(r0["loss"], r0["single_loss"]):
+        assert abs(a - b) < 3e-2, r0
+    assert r0["max_param_diff"] < 1e-2 and r0["moment_diff"] < 1e-2, r0

@@ -39,14 +39,21 @@ def test_noalloc_colsum_matches_colsum_twice_in_a_row():
         want = torch.empty(N, device="cuda", dtype=torch.bfloat16)
         K.colsum(x, want, torch.empty(64 * N, device="cuda"))
         got = torch.full((N,), 7.0, device="cuda", dtype=torch.bfloat16)
-        before = torch.cuda.memory_allocated()
+        # one warm-up call (the first call on a device looks up the scratch address), then the call
+        # that is measured: the DRIVER's count of free bytes must not move, which also sees an
+        # allocation made behind torch's back
         rc = fn(x.data_ptr(), rows, N, x.stride(0), got.data_ptr(), 0, stream)
         assert rc == 0, lib.mimir_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        free_before, _ = torch.cuda.mem_get_info()
+        rc = fn(x.data_ptr(), rows, N, x.stride(0), got.data_ptr(), 0, stream)
+        assert rc == 0, lib.mimir_last_error().decode()
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before
         ref = x.float().sum(0)
         tol = 2e-2 * (ref.abs().max().item() + 1e-3)
-        assert (got.float() - want.float()).abs().max().item() <= tol
+        assert torch.equal(got, want)            # same split and order of sums as mimir_colsum: same bits
         assert (got.float() - ref).abs().max().item() <= tol
         # accumulate on top of the previous result
         rc = fn(x.data_ptr(), rows, N, x.stride(0), got.data_ptr(), 1, stream)
@@ -63,3 +70,5 @@ def test_noalloc_colsum_refuses_what_it_cannot_serve():
     assert fn(x.data_ptr(), 8, 16392, 16392, out.data_ptr(), 0, stream) == -1
     assert b"exceeds" in lib.mimir_last_error()
     assert fn(x.data_ptr(), 8, 12, 16392, out.data_ptr(), 0, stream) == -1
+    assert fn(x.data_ptr(), 8, 64, 32, out.data_ptr(), 0, stream) == -1       # row pitch below the width
+    assert b"pitch" in lib.mimir_last_error()
