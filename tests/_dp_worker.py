@@ -61,10 +61,16 @@ def main():
     dp2.attach(eng2)
     eng2.load_state_dict(sd)
     eng2.step_count = count
+    # the restore itself is exact: what the fresh replica would save equals what was saved
+    sd2 = eng2.state_dict()
+    result["restore_exact"] = all(torch.equal(sd[k], sd2[k]) for k in sd) and len(sd) == len(sd2)
     tr2 = FusedTrainer(eng2, lr=2e-3, dp=dp2, use_graph=False)
     tr2.step(tok[my], tgt[my])
     torch.cuda.synchronize()
-    result["resume_identical"] = bool(torch.equal(after.view(torch.int16), eng2.params.view(torch.int16)))
+    # the next step agrees up to the order of the embedding gradient's atomic adds (a bf16 ulp here and there)
+    d = (after.float() - eng2.params.float()).abs()
+    result["resume_max_diff"] = d.max().item()
+    result["resume_frac_diff"] = (d > 0).float().mean().item()
     result["ckpt_names"] = sorted(sd)[:3]
     result["err2"] = check_error_word()
     dp2.close()

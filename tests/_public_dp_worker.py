@@ -38,7 +38,7 @@ def main():
     reps = fit(m, opt, ds, loss=loss_fn(m.vocab), epochs=2, data_parallel=Group())
     torch.cuda.synchronize()
     res = {"rank": rank, "err": check_error_word(), "loss": [r.loss for r in reps], "steps": opt.steps}
-    mine = torch.cat([p._data.reshape(-1) for p in m.parameters()]).view(torch.int16).clone()
+    mine = torch.cat([p._data.reshape(-1) for p in m.parameters()]).view(torch.uint8).clone()
     ref = mine.clone()
     dist.broadcast(ref, 0)
     res["identical"] = bool(torch.equal(mine, ref))
