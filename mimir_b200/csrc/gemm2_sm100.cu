@@ -30,7 +30,7 @@ template <int BN, bool A_MN, bool B_MN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemm2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmPre, GemmEpi ep,
-                  int M, int N, int K, int splits, int tma_out, unsigned long long* prof, unsigned* err) {
+                  int M, int N, int K, int splits, int tma_out, unsigned* err) {
   constexpr int BNH = BN / 2;  // columns of B staged by each CTA
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BNH * kBK * 2;
@@ -120,23 +120,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0 && cta == 0) {
       uint32_t it = 0, ti = 0;
       bool ok = true;
-      // optional diagnostics of pair 0: cycles the MMA thread spent waiting
-      long long t_begin = clock64(), w_acc = 0, w_full = 0;
       for (int u = pair; u < units && ok; u += npairs, ++ti) {
         const int split = u % splits;
         const int kb0 = split * kb_per, kb1 = min(kb_total, kb0 + kb_per);
         const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
-        long long t0 = clock64();
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, err)) break;
-        w_acc += clock64() - t0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          t0 = clock64();
           if (!mbar_wait(&full[s], ph, abort_flag, err)) { ok = false; break; }
-          w_full += clock64() - t0;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sB = sA + A_BYTES;
@@ -154,12 +148,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         if (ok) umma_commit_pair(&tfull[acc], 3);
       }
-      if (prof && pair == 0) {
-        prof[0] = clock64() - t_begin;  // MMA thread: first wait to last issue
-        prof[1] = w_acc;                // ... waiting for a free accumulator
-        prof[2] = w_full;               // ... waiting for operands
-        prof[3] = ti;
-      }
     }
   } else {
     const int q = warp & 3;           // TMEM lane quadrant
@@ -168,15 +156,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t tempty_leader1 = map_to_cta(smem_u32(&tempty[1]), 0);
     uint32_t ti = 0, ring = 0;
     uint8_t* wbuf = out_ring + (warp - 2) * 2 * 4096;
-    long long e_wait = 0, e_work = 0;
     for (int u = pair; u < units; u += npairs, ++ti) {
       const int split = u % splits, tile = u / splits;
       const int n_idx = tile % n_tiles, m_idx = tile / n_tiles;
       const uint32_t acc = ti & 1, acc_ph = (ti >> 1) & 1;
-      const long long t0 = clock64();
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, err)) break;
-      const long long t1 = clock64();
-      e_wait += t1 - t0;
       tc_fence_after();
       const int row0 = m_idx * 2 * kBM + static_cast<int>(cta) * kBM + q * 32;
       const uint32_t taddr = tmem_base + acc * BN + half * (BN / 2) + (static_cast<uint32_t>(q * 32) << 16);
@@ -190,11 +174,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc ? tempty_leader1 : tempty_leader0);
-      e_work += clock64() - t1;
-    }
-    if (prof && pair == 0 && cta == 0 && warp == 2 && lane == 0) {
-      prof[4] = e_wait;  // epilogue warp: waiting for a finished accumulator
-      prof[5] = e_work;  // ... draining its share of it
     }
     if (lane == 0) bulk_wait_group_read<0>();  // the ring must outlive its last store's reads
   }
@@ -209,8 +188,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-// Device buffer of 8 counters that pair 0 fills when set (see mimir_gemm_set_profile_buffer).
-static unsigned long long* g_gemm_prof = nullptr;
 
 template <int BN, bool A_MN, bool B_MN, int STAGES>
 static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
@@ -235,8 +212,7 @@ static int launch_gemm2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   }
   const int units = ceil_div(M, 2 * kBM) * ceil_div(N, BN) * splits;
   const int pairs = units < max_pairs ? units : max_pairs;
-  kern<<<2 * pairs, kGemm2Threads, SMEM, stream>>>(tmA, tmB, tmC, tmPre, ep, M, N, K, splits, tma_out,
-                                                  g_gemm_prof, error_word_dev());
+  kern<<<2 * pairs, kGemm2Threads, SMEM, stream>>>(tmA, tmB, tmC, tmPre, ep, M, N, K, splits, tma_out, error_word_dev());
   count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : refuse("gemm2 launch failed");
 }
@@ -285,10 +261,3 @@ int launch_gemm_pair(const void* A, const void* B, int M, int N, int K, int lda,
 
 }  // namespace mimir
 
-// Diagnostics: when `buf` (device memory, 8 x uint64) is non-null the CTA-pair
-// kernel's first pair records, in SM cycles: [0] MMA-thread span, [1] its wait for a
-// free accumulator, [2] its wait for operands, [3] tiles, [4] an epilogue warp's wait for
-// a finished accumulator, [5] its drain time.  Pass null to switch off.
-MIMIR_API void mimir_gemm_set_profile_buffer(void* buf) {
-  mimir::g_gemm_prof = static_cast<unsigned long long*>(buf);
-}

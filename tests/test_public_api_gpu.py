@@ -160,8 +160,9 @@ def test_fit_replays_captured_steps_and_matches_the_eager_path():
     assert sa == sb == 12
     for x, y in zip(la, lb):
         assert abs(x - y) < 2e-3, (la, lb)
-    for a, b in zip(wa, wb):
-        assert (a.float() - b.float()).abs().max().item() < 2e-3
+    for a, b in zip(wa, wb):          # at most a couple of bf16 ulps apart
+        a, b = a.float(), b.float()
+        assert bool(((a - b).abs() <= 2.0 ** -6 * a.abs() + 1e-3).all())
     assert _native.lib().mimir_launch_count() > 0
 
 
