@@ -155,12 +155,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* v_full = k_empty + NST;
   uint64_t* v_empty = v_full + NST;
   uint64_t* s_full = v_empty + NST;
-  uint64_t* p_ready = s_full + 2;
-  uint64_t* pv_full = p_ready + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_full + 2);
+  uint64_t* p_ready = s_full + 2;   // [score buffer][key half]
+  uint64_t* pv_done = p_ready + 4;  // [key half]: one completion per tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ float xmax[2][2][kTile];   // [score buffer][half][row]: row maxima exchanged between partner warps
-  __shared__ int xseq[2][4];            // [half][quadrant]: how many exchanges that warp has published
+  __shared__ float xml[2][2][kTile];    // [m | l][half][row]: the halves' running maximum and sum, exchanged at the end
+  __shared__ int xseq[2][4];            // [half][quadrant]: rendezvous counters of the partner warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (p.Tq + kTile - 1) / kTile;
@@ -180,9 +180,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 8); mbar_init(&pv_full[i], 1);
-    }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&pv_done[i], 1); }
+    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);
     for (int i = 0; i < 8; ++i) (&xseq[0][0])[i] = 0;
     *abort_flag = 0;
     fence_mbar_init();
@@ -192,8 +191,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem;         // two 128-column score buffers
-  const uint32_t tPV = tmem + 256;  // two D-column partial-output buffers
+  const uint32_t tS = tmem;        // two 128-column score buffers
+  const uint32_t tO = tmem + 256;  // two D-column output accumulators, one per key half
 
   if (warp == 0) {
     if (lane == 0 && n_kv > 0) {
@@ -229,31 +228,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_commit(&s_full[(j + 1) & 1]);
           umma_commit(&k_empty[s]);
         }
-        const int s = j % NST;
-        if (!(ok = mbar_wait(&p_ready[j & 1], (j >> 1) & 1, abort_flag, err))) break;
+        const int s = j % NST, bi = j & 1;
         if (!(ok = mbar_wait(&v_full[s], (j / NST) & 1, abort_flag, err))) break;
-        tc_fence_after();
-        mma_from_tmem<D>(tPV + (j & 1) * D, tS + (j & 1) * 128, smem_u32(sV + s * TB), false);
-        umma_commit(&pv_full[j & 1]);
-        umma_commit(&v_empty[s]);
+        // the two key halves are independent streams: each accumulates P_half * V_half into its own
+        // accumulator as soon as its softmax warps have written P_half
+        for (int hh = 0; hh < 2 && ok; ++hh) {
+          if (!(ok = mbar_wait(&p_ready[bi * 2 + hh], (j >> 1) & 1, abort_flag, err))) break;
+          tc_fence_after();
+          mma_from_tmem_half<D>(tO + hh * D, tS + bi * 128 + hh * 64, smem_u32(sV + s * TB), hh, j > 0);
+          umma_commit(&pv_done[hh]);
+        }
+        if (ok) umma_commit(&v_empty[s]);
       }
     }
   } else {
-    // Two warps share each 32-row TMEM lane quadrant: `half` 0 owns keys 0..63 of a score tile and
-    // output columns 0..D/2, `half` 1 the rest.  Each keeps its 64 scores in registers (one pass
-    // over TMEM), the pair exchanges the running row maximum through shared memory once per tile
-    // (a 64-thread named barrier), and the two partial row sums are added at the very end.  One
-    // warp per scheduler was latency-bound; this puts two on each.
+    // Eight softmax warps: two per 32-row TMEM lane quadrant.  `half` 0 owns keys 0..63 of every key
+    // tile, `half` 1 keys 64..127, and each half is an attention of its own over its keys: own
+    // running maximum and row sum, own accumulator O_half in TMEM (P_half * V_half, accumulated by
+    // the tensor core across tiles).  The halves never talk to each other inside the loop, so they
+    // drift apart by up to one tile and the exponentials of one overlap the loads, maxima and
+    // stores of the other; their results are merged once at the end.  The accumulator is rescaled
+    // only when a row's maximum has grown by more than 2^8 since the last rescale (P stays below
+    // 2^8, harmless in bf16 / fp32), which after the first tiles almost never happens.
     const int quad = warp & 3, half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int q_pos = q0 + r;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr int DH = D / 2;
-    float m = -INFINITY, l = 0.f;
-    float o[DH];
-#pragma unroll
-    for (int d = 0; d < DH; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;   // m: the maximum the probabilities are scaled by
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int bi = j & 1;
@@ -262,99 +265,115 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = j * kTile + half * 64;
       const bool need_mask = (p.causal && kv0 + 63 > q0 + p.offset) || (kv0 + 64 > p.Tk);
       const int limit = p.causal ? min(p.Tk - 1, q_pos + p.offset) : p.Tk - 1;  // last visible key
-      const uint32_t ts = tS + bi * 128 + lane_base;
+      const uint32_t ts = tS + bi * 128 + half * 64 + lane_base;
       uint32_t s0[32], s1[32];
-      tmem_ld32(ts + half * 64, s0);
-      tmem_ld32(ts + half * 64 + 32, s1);
+      tmem_ld32(ts, s0);
+      tmem_ld32(ts + 32, s1);
       tmem_ld_wait();
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float a = __uint_as_float(s0[e]), c = __uint_as_float(s1[e]);
-        if (need_mask) {
-          if (kv0 + e > limit) a = -INFINITY;
-          if (kv0 + 32 + e > limit) c = -INFINITY;
-          s0[e] = __float_as_uint(a);
-          s1[e] = __float_as_uint(c);
+        for (int e = 0; e < 32; ++e) {
+          if (kv0 + e > limit) s0[e] = 0xff800000u;
+          if (kv0 + 32 + e > limit) s1[e] = 0xff800000u;
         }
-        mx = fmaxf(mx, fmaxf(a, c));
       }
-      xmax[bi][half][r] = mx;
-      if (!(ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], j + 1, lane, abort_flag, err))) break;
-      mx = fmaxf(m, fmaxf(mx, xmax[bi][half ^ 1][r]));
-      const float m_use = mx == -INFINITY ? 0.f : mx;
-      const float alpha = ex2((m - m_use) * sl2);
-      const float msl = m_use * sl2;
-      float rowsum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        mx0 = fmaxf(mx0, __uint_as_float(s0[e]));
+        mx1 = fmaxf(mx1, __uint_as_float(s0[e + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s1[e]));
+        mx3 = fmaxf(mx3, __uint_as_float(s1[e + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const bool grow = mx != -INFINITY && (mx - m) * sl2 > 8.f;   // also the first finite maximum (m = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? ex2((m - mx) * sl2) : 1.f;       // ex2(-inf) = 0 for the first one
+        if (grow) m = mx;
+        l *= alpha;
+        if (j > 0) {
+          // O_half *= alpha in TMEM, after the product of the previous tile has landed
+          if (!(ok = mbar_wait(&pv_done[half], (j - 1) & 1, abort_flag, err))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t rr[32];
+            tmem_ld32(tO + half * D + lane_base + c * 32, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
+            tmem_st32(tO + half * D + lane_base + c * 32, rr);
+          }
+        }
+      }
+      const float msl = (m == -INFINITY ? 0.f : m) * sl2;
+      float rs0 = 0.f, rs1 = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int e = 0; e < 32; e += 2) {
         const float p0 = ex2(__uint_as_float(s0[e]) * sl2 - msl), p1 = ex2(__uint_as_float(s0[e + 1]) * sl2 - msl);
         const float p2 = ex2(__uint_as_float(s1[e]) * sl2 - msl), p3 = ex2(__uint_as_float(s1[e + 1]) * sl2 - msl);
-        rowsum += (p0 + p1) + (p2 + p3);
+        rs0 += p0 + p1;
+        rs1 += p2 + p3;
         pk[e >> 1] = pack_bf16x2(p0, p1);
         pk[16 + (e >> 1)] = pack_bf16x2(p2, p3);
       }
-      // P (bf16 pairs) goes over columns 0..63 of the score buffer; both warps hold their scores in
-      // registers since before the barrier, so nothing unread is overwritten
-      tmem_st32(ts + half * 32, pk);
+      // P_half (bf16 pairs) goes over the first 32 columns of this half's own scores
+      tmem_st32(ts, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[bi]);
-      l = l * alpha + rowsum;
-      m = mx;
-      if (j > 0) {
-        const int pb = (j - 1) & 1;
-        if (!(ok = mbar_wait(&pv_full[pb], ((j - 1) >> 1) & 1, abort_flag, err))) break;
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld32(tPV + pb * D + lane_base + half * DH + c * 32, rr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[c * 32 + e] += __uint_as_float(rr[e]);
-        }
-      }
-#pragma unroll
-      for (int d = 0; d < DH; ++d) o[d] *= alpha;
+      if (lane == 0) mbar_arrive(&p_ready[bi * 2 + half]);
+      l += rs0 + rs1;
     }
+    // merge the halves: both products of the last tile must have landed
     if (ok && n_kv > 0) {
-      const int pb = (n_kv - 1) & 1;
-      if (mbar_wait(&pv_full[pb], ((n_kv - 1) >> 1) & 1, abort_flag, err)) {
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < DH / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld32(tPV + pb * D + lane_base + half * DH + c * 32, rr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[c * 32 + e] += __uint_as_float(rr[e]);
-        }
-      }
+      ok = mbar_wait(&pv_done[0], (n_kv - 1) & 1, abort_flag, err) &&
+           mbar_wait(&pv_done[1], (n_kv - 1) & 1, abort_flag, err);
+      tc_fence_after();
     }
-    // the row sum is the sum of the two halves' partial sums (same running maximum in both); the
-    // buffer the last tile did not use carries it
-    const int fb = n_kv & 1;
-    xmax[fb][half][r] = l;
-    if (ok) ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], n_kv + 1, lane, abort_flag, err);
-    l += xmax[fb][half ^ 1][r];
-    if (ok && q_pos < p.Tq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+    xml[0][half][r] = m;
+    xml[1][half][r] = l;
+    if (ok) ok = pair_sync(&xseq[half][quad], &xseq[half ^ 1][quad], 1, lane, abort_flag, err);
+    const float m_o = xml[0][half ^ 1][r], l_o = xml[1][half ^ 1][r];
+    const float mm = fmaxf(m, m_o);
+    const float f_me = m == -INFINITY ? 0.f : ex2((m - mm) * sl2);
+    const float f_ot = m_o == -INFINITY ? 0.f : ex2((m_o - mm) * sl2);
+    const float f0 = half == 0 ? f_me : f_ot, f1 = half == 0 ? f_ot : f_me;   // factors of O_0 and O_1
+    const float lsum = l * f_me + l_o * f_ot;
+    if (ok && n_kv > 0) {
+      // the TMEM loads are warp-wide instructions: every lane takes part, only the stores to global
+      // memory depend on whether the lane's row exists
+      const bool row_ok = q_pos < p.Tq;
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
       __nv_bfloat16* dst = O + (static_cast<size_t>(b) * p.Tq + q_pos) * p.ldo + h * D + half * DH;
 #pragma unroll
-      for (int d = 0; d < DH; d += 8) {
-        uint4 u;
-        u.x = pack_bf16x2(o[d] * inv, o[d + 1] * inv);
-        u.y = pack_bf16x2(o[d + 2] * inv, o[d + 3] * inv);
-        u.z = pack_bf16x2(o[d + 4] * inv, o[d + 5] * inv);
-        u.w = pack_bf16x2(o[d + 6] * inv, o[d + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = u;
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tO + lane_base + half * DH + c * 32, ra);
+        tmem_ld32(tO + D + lane_base + half * DH + c * 32, rb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int d = 0; d < 32; d += 8) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            v[e] = (__uint_as_float(ra[d + e]) * f0 + __uint_as_float(rb[d + e]) * f1) * inv;
+          uint4 u;
+          u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+          u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+          if (row_ok) *reinterpret_cast<uint4*>(dst + c * 32 + d) = u;
+        }
       }
-      if (LSE && half == 0)
+      if (row_ok && LSE && half == 0)
         LSE[(static_cast<size_t>(b) * p.Hq + h) * p.Tq + q_pos] =
-            l > 0.f ? (m * sl2 + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            lsum > 0.f ? (mm * sl2 + log2f(lsum)) * 0.6931471805599453f : -INFINITY;
+    } else if (ok && n_kv == 0 && q_pos < p.Tq) {
+      // no visible key at all: a zero row (the reference's zero-row rule) and -inf log-sum-exp
+      __nv_bfloat16* dst = O + (static_cast<size_t>(b) * p.Tq + q_pos) * p.ldo + h * D + half * DH;
+#pragma unroll
+      for (int d = 0; d < DH; d += 8) *reinterpret_cast<uint4*>(dst + d) = make_uint4(0, 0, 0, 0);
+      if (LSE && half == 0) LSE[(static_cast<size_t>(b) * p.Hq + h) * p.Tq + q_pos] = -INFINITY;
     }
   }
   tc_fence_before();
