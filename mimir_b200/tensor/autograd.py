@@ -34,6 +34,10 @@ class Param:
 
     # -- value access
     def value(self) -> C.Tensor:
+        if getattr(self, "_spmd", None) is not None:
+            # a parameter with a layout on a device mesh: graphs built from it are partitioned
+            from ..parallel.spmd import _param_leaf
+            return _param_leaf(self)
         t = C.from_torch(self._data)
         t._stale = (self, self._version)
         t._fn = None
@@ -205,6 +209,9 @@ def backward(loss: C.Tensor, effects=()) -> None:
         raise E.ErrShape(f"backward needs a scalar loss, got shape {loss.shape}")
     if loss._fn is None:
         raise E.ErrNoGrad("the loss does not depend on any recorded operation")
+    if C._on_mesh(loss):
+        from ..parallel import spmd
+        return spmd.backward(loss)
     leaves = _collect_params(loss)
     trainable = {k: (t, p) for k, (t, p) in leaves.items() if p._trainable}
     if not trainable:

@@ -315,15 +315,36 @@ def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | 
     if isinstance(meta, (tuple, list)):
         outs = tuple(Tensor(fn=_pick(fn, i), args=tuple(args), kw=kw, shape=m.shape, dtype=m.dtype, device=device,
                             opname=opname, attrs=dict(attrs or {}, part=i)) for i, m in enumerate(meta))
-        if _EAGER:
+        for o in outs:
+            _inherit_mesh(o, tensors)
+        if _EAGER and outs[0]._sharding is None:
             for o in outs:
                 realize(o)
         return outs
     out = Tensor(fn=fn, args=tuple(args), kw=kw, shape=meta.shape, dtype=meta.dtype, device=device, opname=opname,
                  attrs=attrs)
-    if _EAGER:
+    _inherit_mesh(out, tensors)
+    if _EAGER and out._sharding is None:
         realize(out)
     return out
+
+
+ON_MESH = "on-mesh"      # second element of ``_sharding`` for a value computed from mesh leaves (layout: by analysis)
+
+
+def _inherit_mesh(out: Tensor, operands) -> None:
+    """A value computed from tensors that live on a device mesh lives on that mesh: realising it goes
+    through the partitioner (``parallel/spmd.py``)."""
+    for t in operands:
+        sh = t._sharding
+        if sh is not None and (sh[1] is ON_MESH or type(t).__name__ == "MeshTensor"):
+            out._sharding = (sh[0], ON_MESH)
+            return
+
+
+def _on_mesh(t: Tensor) -> bool:
+    sh = t._sharding
+    return sh is not None and t._val is None and (sh[1] is ON_MESH or type(t).__name__ == "MeshTensor")
 
 
 def _pick(fn, i):
@@ -380,6 +401,9 @@ def realize(*tensors: Tensor) -> None:
     for t in tensors:
         if t._err is not None:
             raise t._err
+    if any(_on_mesh(t) for t in todo):
+        from ..parallel import spmd
+        return spmd.realize(*tensors)
     if not todo:
         for t in tensors:
             if t._fn is None:

@@ -115,10 +115,14 @@ def fit(model, opt, ds, loss=None, epochs: int = 1, eval=None, metrics=(), check
         from ..parallel.replicas import fit_data_parallel
         return fit_data_parallel(model, opt, ds, loss, epochs, data_parallel, schedule=schedule, on_epoch=on_epoch,
                                  progress=progress)
+    shard_mesh = None
     if sharded is not None:
-        from ..parallel.mesh import shard_module
-        mesh, rule = sharded
-        shard_module(model, mesh, rule)
+        # the partitioner: parameters get layouts on the mesh, every batch is placed P("data"), and the
+        # graphs built from them are analysed and lowered per rank (train/sharded.go:37-56)
+        from ..parallel import spmd
+        shard_mesh, rule = sharded
+        if getattr(model, "_mesh", None) is not shard_mesh:
+            spmd.shard_params(model, shard_mesh, rule)
     device = device or T.default_device()
     start_epoch, steps = 0, 0
     if checkpoint:
@@ -141,13 +145,21 @@ def fit(model, opt, ds, loss=None, epochs: int = 1, eval=None, metrics=(), check
             ds.set_epoch(epoch)
             total, rows = 0.0, 0
             for batch in ds.all():
-                x = batch.x.to(device)
-                y = None if batch.y is None else batch.y.to(device)
+                if shard_mesh is not None:
+                    from ..parallel import spmd
+                    from ..parallel.mesh import P
+                    spec = P("data") if "data" in shard_mesh.axes and shard_mesh.axis_size("data") > 1 else None
+                    x = spmd.place(batch.x.to(device), shard_mesh, spec)
+                    y = None if batch.y is None else spmd.place(batch.y.to(device), shard_mesh, spec)
+                else:
+                    x = batch.x.to(device)
+                    y = None if batch.y is None else batch.y.to(device)
                 parts = 1
                 if micro_batch and x.shape[0] > micro_batch:
                     parts = (x.shape[0] + micro_batch - 1) // micro_batch
                 skipped, value = False, 0.0
-                if replay.enabled and parts == 1 and memory_budget is None and not dynamic_loss_scale and scale == 1.0:
+                if replay.enabled and shard_mesh is None and parts == 1 and memory_budget is None \
+                        and not dynamic_loss_scale and scale == 1.0:
                     opt.grad_scale = 1.0
                     lt = replay.step(x.data(), None if y is None else y.data())
                     if lt is not None:
@@ -162,7 +174,7 @@ def fit(model, opt, ds, loss=None, epochs: int = 1, eval=None, metrics=(), check
                 while True:
                     try:
                         value = 0.0
-                        for xs, ys, share in _split(Batch_(x, y), parts):
+                        for xs, ys, share in ([(x, y, 1.0)] if shard_mesh is not None else _split(Batch_(x, y), parts)):
                             l = loss(model(xs), ys) * (share * scale)
                             l.backward()
                             value += l.item() / scale
