@@ -290,7 +290,7 @@ class _Exporter:
             p = pair(vals["padding"])
             d = [x.dims[0]] + list(out.shape[1:])
             return b.call1("conv2d.v1", ins, dt(), d, strides=pair(vals["stride"]), dilations=pair(vals["dilation"]),
-                           pads=[p[0], p[1], p[0], p[1]], groups=int(vals["groups"]))
+                           pads=[p[0], p[0], p[1], p[1]], groups=int(vals["groups"]))
         if name == "attention":
             q, kk, v = self.get(a[0]), self.get(a[1]), self.get(a[2])
             names = ("causal", "causal_offset", "mask", "scale")

@@ -16,10 +16,10 @@ io/mim/export.go:55-105) is provided here over this package's container:
   slices along an axis at clamped positions, ``scatter`` replaces slices along an axis (the last
   of repeated positions wins), ``reshape`` / ``expand`` / ``const`` take their target from the
   declared shape of their output.
-* the byte encoding of the section is this package's own (magic ``MB2G``, a version word and one
-  UTF-8 JSON document).  The reference keeps its encoding in a separate module
-  (``github.com/gsoultan/mimir-model``) whose source is not part of the reference tree; a graph
-  section that does not start with ``MB2G`` is reported as ``ErrUnsupported``, never guessed at.
+* two byte encodings are read: the reference's binary tables (magic ``MMFG`` / ``MIMG``; decoded by
+  ``io/mmfg.py``, so graph files written by the reference run here and give its expected
+  outputs) and this package's own (magic ``MB2G``, a version word and one UTF-8 JSON document),
+  which is what ``export`` writes.
 
 The interpreter computes with torch tensors on the device of its inputs (float composites in
 fp32, outputs cast to their declared dtypes, as the reference's stdlib does) and returns lazy

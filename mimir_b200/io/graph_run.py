@@ -45,6 +45,17 @@ class _Call:
         v = self.op.attrs.get(key, default)
         if v is None:
             return None
+        if isinstance(v, list) and any(isinstance(i, G.Sym) for i in v):
+            # a symbolic dimension in an integer list (the end of a shrink over a sequence axis):
+            # takes the size the symbol was bound to by this run's inputs
+            out = []
+            for i in v:
+                if isinstance(i, G.Sym):
+                    if i.name not in self.run.syms:
+                        raise G.FormatError(f"{self.name}: attribute {key!r} uses symbol {i.name!r} before it is known")
+                    i = self.run.syms[i.name]
+                out.append(i)
+            v = out
         if not isinstance(v, list) or any(isinstance(i, bool) or not isinstance(i, int) for i in v):
             raise G.FormatError(f"{self.name}: attribute {key!r} is not a list of integers")
         return v
@@ -57,6 +68,8 @@ class _Call:
 
     def bool(self, key, default=False) -> bool:
         v = self.op.attrs.get(key, default)
+        if isinstance(v, int) and v in (0, 1):      # the binary encoding stores flags as integers
+            return bool(v)
         if not isinstance(v, bool):
             raise G.FormatError(f"{self.name}: attribute {key!r} is not a bool")
         return v
@@ -388,16 +401,17 @@ def _conv2d(c):
     c.need(2, 3)
     stride = c.ints("strides", [1, 1])
     dil = c.ints("dilations", [1, 1])
-    pads = c.ints("pads", [0, 0, 0, 0])          # top, left, bottom, right
+    pads = c.ints("pads", [0, 0, 0, 0])          # top, bottom, left, right (io/mim/stdlib.go:208)
     groups = c.int("groups", 1)
     x, w = c.f32(0), c.f32(1)
     if len(pads) != 4 or len(stride) != 2 or len(dil) != 2:
         raise G.FormatError("conv2d: strides / dilations of 2 and pads of 4 values")
-    if pads[0] != pads[2] or pads[1] != pads[3]:
-        x = F.pad(x, [pads[1], pads[3], pads[0], pads[2]])
+    top, bottom, left, right = pads
+    if top != bottom or left != right:
+        x = F.pad(x, [left, right, top, bottom])
         pad = (0, 0)
     else:
-        pad = (pads[0], pads[1])
+        pad = (top, left)
     b = c.f32(2) if len(c.ins) > 2 else None
     return [F.conv2d(x, w, b, stride=tuple(stride), padding=pad, dilation=tuple(dil), groups=groups)]
 
@@ -835,7 +849,11 @@ class Session:
             if v.name not in inputs:
                 raise E.ErrShape(f"graph: input {v.name!r} is missing")
             t = _to_torch(inputs[v.name])
-            if t.dtype != G.DTYPES[v.dtype]:
+            want = G.DTYPES[v.dtype]
+            ints = (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8)
+            if t.dtype != want and t.dtype in ints and want in ints:
+                t = t.to(want)      # the reference has one integer type: any integer input fits an integer slot
+            if t.dtype != want:
                 raise E.ErrDType(f"graph: input {v.name!r} is {t.dtype}, declared {v.dtype}")
             if device is None:
                 device = t.device

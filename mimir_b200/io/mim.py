@@ -106,6 +106,7 @@ class Model:
         self._buf = (ctypes.c_uint8 * size).from_address(base)
         self._np = np.frombuffer(self._buf, dtype=np.uint8)
         self._index = {}
+        self._table_order = []        # tensor names in table order: graph values refer to tensors by this index
         name, nl, dt, rank = ctypes.c_char_p(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
         dims = (ctypes.c_uint64 * 8)()
         off, nb = ctypes.c_uint64(), ctypes.c_uint64()
@@ -128,6 +129,7 @@ class Model:
                 raise MimError(f"tensor {nm!r}: {nb.value} bytes at offset {off.value} for shape {list(shape)} "
                                f"of dtype code {dt.value}")
             self._index[nm] = (dt.value, shape, off.value, nb.value)
+            self._table_order.append(nm)
         self.sections = []
         kind, flags = ctypes.c_int(), ctypes.c_int()
         h32 = ctypes.create_string_buffer(32)
@@ -178,7 +180,12 @@ class Model:
             raw = self.section_bytes(SECTION_GRAPH)
             if raw is None:
                 raise _g.NoGraph("the file has no graph section")
-            self._program = _gr.Program(_g.Graph.decode(raw), self.tensor)
+            from . import mmfg as _mmfg
+            if _mmfg.is_reference_encoding(raw):       # written by the reference: its binary tables
+                graph = _mmfg.decode(raw, self._table_order)
+            else:
+                graph = _g.Graph.decode(raw)
+            self._program = _gr.Program(graph, self.tensor)
         return self._program
 
     def graph(self):

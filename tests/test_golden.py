@@ -6,8 +6,12 @@ import os
 import pytest
 import torch
 
-GOLD = "/root/reference/testdata/golden"
-pytestmark = pytest.mark.skipif(not os.path.isdir(GOLD), reason="reference golden files not mounted")
+from _refdir import reference_dir
+
+# MIMIR_GOLDEN_DIR names the directory of golden files directly, like the reference's own tests
+GOLD = os.environ.get("MIMIR_GOLDEN_DIR") or os.path.join(reference_dir() or "", "testdata", "golden")
+pytestmark = pytest.mark.skipif(not os.path.isdir(GOLD), reason="reference golden files not found "
+                                                                "(MIMIR_GOLDEN_DIR / MIMIR_REFERENCE_DIR)")
 
 
 def _open(name):

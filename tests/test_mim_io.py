@@ -5,8 +5,10 @@ import os
 import pytest
 import torch
 
-REF = "/root/reference"
-FILES = sorted(glob.glob(os.path.join(REF, "**", "*.mim"), recursive=True))
+from _refdir import reference_dir
+
+REF = reference_dir()
+FILES = sorted(glob.glob(os.path.join(REF, "**", "*.mim"), recursive=True)) if REF else []
 needs_ref = pytest.mark.skipif(not FILES, reason="reference sample files not mounted")
 
 
