@@ -19,11 +19,20 @@ from .. import _native
 
 class FusedTrainer:
     def __init__(self, engine, lr: float = 6e-4, betas=(0.9, 0.95), eps: float = 1e-8,
-                 weight_decay: float = 0.1, use_graph: bool = True, schedule=None, dp=None):
+                 weight_decay: float = 0.1, use_graph: bool = True, schedule=None, dp=None, phases=None):
+        """``phases``: a ``utils.phases.PhaseTimer``; forward / loss / backward / optimizer of every step
+        are then bracketed by CUDA events on the launching stream (and NVTX ranges when the timer was
+        made with ``nvtx=True`` or ``MIMIR_NVTX=1`` is set), and ``phases.report()`` gives device time
+        per phase, the slowest rank counting.  Phase timing needs plain launches: it switches the
+        CUDA-graph replay off."""
         self.engine = engine
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         # MIMIR_CUDA_GRAPHS=0 runs every step as plain launches (reference: backend/cuda/batch_linux.go:63)
-        self.use_graph = use_graph and os.environ.get("MIMIR_CUDA_GRAPHS", "1") != "0"
+        if phases is None and os.environ.get("MIMIR_NVTX", "") == "1":
+            from ..utils.phases import PhaseTimer
+            phases = PhaseTimer(nvtx=True)
+        self.phases = phases
+        self.use_graph = use_graph and os.environ.get("MIMIR_CUDA_GRAPHS", "1") != "0" and phases is None
         self.schedule = schedule
         self.dp = dp  # optional parallel.dp.FusedDataParallel
         self.graph = None
@@ -40,15 +49,22 @@ class FusedTrainer:
     # The device work of one step, launched on the current stream.
     def _device_step(self) -> None:
         e = self.engine
+        import contextlib
+        ph = self.phases.phase if self.phases is not None else (lambda name: contextlib.nullcontext())
         if self.dp is not None:
             self.dp.begin_step()
-        e.forward()
-        e.loss_and_dlogits()
+        with ph("forward"):
+            e.forward()
+        with ph("loss"):
+            e.loss_and_dlogits()
         if self.dp is not None:
-            self.dp.run_backward_and_update(self)
+            with ph("backward+reduce+update"):
+                self.dp.run_backward_and_update(self)
         else:
-            e.backward()
-            e.adamw(self.betas[0], self.betas[1], self.eps, self.wd)
+            with ph("backward"):
+                e.backward()
+            with ph("optimizer"):
+                e.adamw(self.betas[0], self.betas[1], self.eps, self.wd)
 
     def _current_lr(self) -> float:
         if self.schedule is None:
