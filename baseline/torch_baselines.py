@@ -310,6 +310,31 @@ class DecodeLlama:
         self.pos = p1
         return F.linear(F.rms_norm(x[:, -1], (self.C,), self.norm, 1e-5), self.head)
 
+    @torch.no_grad()
+    def step_static(self, tok, pos):
+        """One decode step with static shapes (``tok`` [B, 1] and ``pos`` a 0-d device tensor), so
+        that the whole step, NCCL all-reduces included, can be captured in a CUDA graph: the new key
+        and value are written with ``index_copy_`` and attention runs over the whole cache under a
+        mask of the positions filled so far."""
+        B = tok.shape[0]
+        x = self.emb[tok]
+        cos, sin = self.cos.index_select(0, pos.view(1)), self.sin.index_select(0, pos.view(1))
+        mask = (torch.arange(self.max_len, device=tok.device) <= pos).view(1, 1, 1, -1)
+        for l, w in enumerate(self.layers):
+            h = F.rms_norm(x, (self.C,), w["n1"], 1e-5)
+            qkv = F.linear(h, w["qkv"]).view(B, 1, self.H + 2 * self.Hk, self.D).transpose(1, 2)
+            q, k, v = qkv[:, : self.H], qkv[:, self.H: self.H + self.Hk], qkv[:, self.H + self.Hk:]
+            q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+            self.kc[l].index_copy_(2, pos.view(1), k.to(torch.float16))
+            self.vc[l].index_copy_(2, pos.view(1), v.to(torch.float16))
+            a = F.scaled_dot_product_attention(q, self.kc[l].to(torch.bfloat16), self.vc[l].to(torch.bfloat16),
+                                               attn_mask=mask, enable_gqa=self.H != self.Hk)
+            x = x + self._sum(F.linear(a.transpose(1, 2).reshape(B, 1, -1), w["o"]))
+            h = F.rms_norm(x, (self.C,), w["n2"], 1e-5)
+            g, u = F.linear(h, w["gu"]).chunk(2, -1)
+            x = x + self._sum(F.linear(F.silu(g) * u, w["down"]))
+        return F.linear(F.rms_norm(x[:, -1], (self.C,), self.norm, 1e-5), self.head)
+
     def next_token(self, logits):
         """Greedy over the vocabulary split across ranks."""
         val, idx = logits.float().max(-1)

@@ -26,6 +26,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--threads", type=int, default=0)
+    ap.add_argument("--impl", default="ours", choices=["ours", "baseline"],
+                    help="baseline = the same network and step in plain PyTorch (cuDNN / cuBLAS, or MKL on the host)")
     a = ap.parse_args()
     if a.threads:
         torch.set_num_threads(a.threads)
@@ -33,7 +35,28 @@ def main():
     x = torch.randn(a.batch, 1, 28, 28, generator=gen)
     y = torch.randint(0, 10, (a.batch,), generator=gen)
     times = []
-    if a.device == "gpu":
+    if a.impl == "baseline":
+        import sys
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "baseline"))
+        import torch_baselines as TB
+        dev = "cuda" if a.device == "gpu" else "cpu"
+        torch.manual_seed(0)
+        net = TB.MnistCNN().to(dev)
+        opt = torch.optim.AdamW(net.parameters(), lr=1e-3, weight_decay=0.01, fused=dev == "cuda")
+        xd, yd = x.to(dev), y.to(dev)
+        for i in range(a.warmup + a.steps):
+            if dev == "cuda":
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            opt.zero_grad(set_to_none=True)
+            net(xd, yd).backward()
+            opt.step()
+            if dev == "cuda":
+                torch.cuda.synchronize()
+            if i >= a.warmup:
+                times.append((time.perf_counter() - t0) * 1e3)
+        launches = 0
+    elif a.device == "gpu":
         from ..models.cnn import MnistCNN
         eng = MnistCNN(a.batch, "cuda", lr=1e-3, weight_decay=0.01)
         xd, yd = x.cuda(), y.cuda()
@@ -64,7 +87,7 @@ def main():
             if i >= a.warmup:
                 times.append((time.perf_counter() - t0) * 1e3)
         launches = 0
-    print(json.dumps({"metric": "mnist_cnn_ms_per_step", "device": a.device, "batch": a.batch, "steps": a.steps,
+    print(json.dumps({"metric": "mnist_cnn_ms_per_step", "impl": a.impl, "device": a.device, "batch": a.batch, "steps": a.steps,
                       "mean_ms": sum(times) / len(times), "median_ms": statistics.median(times), "gpu_launches": launches,
                       "threads": torch.get_num_threads(), "cpu_count": os.cpu_count(), "data": "synthetic"}))
 
