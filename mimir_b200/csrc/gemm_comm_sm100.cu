@@ -33,6 +33,7 @@ namespace mimir {
 constexpr int kCommRanks = 8;
 constexpr int kCommThreads = 352;  // TMA warp, MMA warp, 8 epilogue warps, gather warp
 constexpr int kCommEpiWarps = 8;
+constexpr int kGatherInFlight = 16;   // 16-byte peer loads a gather lane keeps in flight
 constexpr int kCommReadFlags = 512;  // word offset of the "owner has read call k" flags in a signal pad
 
 struct CommArgs {
@@ -306,13 +307,15 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int s = (cm.rank + k) % cm.world;
       const uint4* src = reinterpret_cast<const uint4*>(cm.w_full[s]) + static_cast<size_t>(s) * shard_units;
       uint4* dst = local + static_cast<size_t>(s) * shard_units;
-      for (size_t i = u0 + lane; i < u1; i += 32 * 4) {
-        uint4 v[4];
+      // NVLink round trips take microseconds: the link only fills when enough loads are in flight
+      // (148 gather warps x 32 lanes x kGatherInFlight x 16 bytes, about 1.2 MB at 16)
+      for (size_t i = u0 + lane; i < u1; i += 32 * kGatherInFlight) {
+        uint4 v[kGatherInFlight];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < kGatherInFlight; ++j)
           if (i + j * 32 < u1) v[j] = ld_peer_v4(src + i + j * 32);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < kGatherInFlight; ++j)
           if (i + j * 32 < u1) dst[i + j * 32] = v[j];
       }
       __threadfence();

@@ -56,7 +56,8 @@ class LlamaConfig:
 
 class TPDecoder:
     def __init__(self, cfg: LlamaConfig, rank: int, world: int, batch: int, cap: int, seed: int = 0,
-                 device=None, weights: dict | None = None, engine: str = "auto", sampler=None):
+                 device=None, weights: dict | None = None, engine: str = "auto", sampler=None,
+                 keep_expanded: bool = True):
         """``engine``: "tc" runs every projection on the tensor cores (Q4_0 tiles expanded to bf16 in
         shared memory, activations rounded to Q8_0 and kept as bf16); "dp4a" is the integer
         dot-product path (one warp per weight row), whose time grows with the batch; "auto" takes
@@ -66,6 +67,12 @@ class TPDecoder:
         counter, so every rank draws the same tokens.  Without one the step is greedy."""
         if engine not in ("auto", "tc", "dp4a"):
             raise ValueError(f"unknown decode engine {engine!r}")
+        # Prompt processing multiplies hundreds of tokens at once: compute bound, so it runs as bf16
+        # GEMMs on expanded weights.  ``keep_expanded`` keeps the expanded copy of every matrix after
+        # the first prompt (2 bytes per weight on top of the 4.5 bits decode reads); without it each
+        # matrix is expanded into one scratch buffer every time it is used.
+        self.keep_expanded = keep_expanded
+        self._expanded: dict = {}
         if engine == "auto":
             engine = "tc" if batch > 4 else "dp4a"
         if engine == "tc" and (batch > 32 or cfg.d_model % 64 or (cfg.ffn // world) % 64 or (cfg.n_head // world * cfg.head_dim) % 64):
@@ -332,8 +339,13 @@ class TPDecoder:
             wmax = max(self.qkv_n * d, d * self.Hq * D, 3 * self.F * d)
             wbuf = torch.empty(wmax, **bf)
 
-            def expand(w):
-                return w.to_bf16(wbuf[: w.N * w.K].view(w.N, w.K))
+            def expand(w, key=None, into=None):
+                if self.keep_expanded and key is not None:
+                    full = self._expanded.get(key)
+                    if full is None:
+                        full = self._expanded[key] = w.to_bf16(torch.empty(w.N, w.K, **bf))
+                    return full
+                return w.to_bf16((wbuf if into is None else into)[: w.N * w.K].view(w.N, w.K))
 
             def allreduce_residual(partial, resid):
                 if self.world > 1:
@@ -346,16 +358,16 @@ class TPDecoder:
             vv = q4[:, :, (self.Hq + self.Hk) * D:].unflatten(2, (self.Hk, D))
             for l, w in enumerate(self.layers):
                 K.rmsnorm_fwd(h, w["attn_norm"], x, rstd, cfg.eps)
-                gemm(x, expand(w["qkv"]), out=qkv)
+                gemm(x, expand(w["qkv"], (l, "qkv")), out=qkv)
                 K.rope_(qkv, pos, self.freqs, 0, self.Hq + self.Hk, D, interleaved=True)
                 self.kc[l][:, :, :Tm].copy_(kv.permute(0, 2, 1, 3))
                 self.vc[l][:, :, :Tm].copy_(vv.permute(0, 2, 1, 3))
                 attention_fwd(qv, kv, vv, att.view(B, Tm, self.Hq, D), lse, causal=True)
-                gemm(att, expand(w["o"]), out=part)
+                gemm(att, expand(w["o"], (l, "o")), out=part)
                 allreduce_residual(part, h)
                 K.rmsnorm_fwd(h, w["ffn_norm"], x, rstd, cfg.eps)
-                wgu = expand(w["gate_up"])
-                wd = w["down"].to_bf16(wbuf[wgu.numel(): wgu.numel() + d * self.F].view(d, self.F))
+                wgu = expand(w["gate_up"], (l, "gate_up"))
+                wd = expand(w["down"], (l, "down"), into=wbuf[2 * self.F * d:])
                 for r0 in range(0, M, chunk):
                     r1 = min(M, r0 + chunk)
                     gemm(x[r0:r1], wgu, out=gu[: r1 - r0])
