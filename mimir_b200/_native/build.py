@@ -94,6 +94,35 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+CAPI_LIB = HERE / "libmimir_capi.so"
+
+
+def build_capi(verbose: bool = False) -> Path:
+    """Builds ``libmimir_capi.so``: the C ABI over framework objects (``csrc/capi/mimir_capi.c``), a
+    plain C file that embeds the interpreter, linked against the shared libpython of this Python."""
+    import sysconfig
+    src = CSRC / "capi" / "mimir_capi.c"
+    hdr = CSRC / "capi" / "mimir_capi.h"
+    if CAPI_LIB.exists() and CAPI_LIB.stat().st_mtime >= max(src.stat().st_mtime, hdr.stat().st_mtime):
+        return CAPI_LIB
+    inc = sysconfig.get_paths()["include"]
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        raise RuntimeError("no C compiler found")
+    tmp = CAPI_LIB.with_suffix(".so.tmp")
+    cmd = [cc, "-shared", "-fPIC", "-O2", "-fvisibility=hidden", "-I", inc, "-I", str(src.parent), str(src), "-o", str(tmp),
+           f"-L{libdir}", f"-lpython{ver}", f"-Wl,-rpath,{libdir}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building the C ABI library failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, CAPI_LIB)
+    if verbose:
+        sys.stderr.write(f"[build] linked {CAPI_LIB}\n")
+    return CAPI_LIB
+
+
 def ptxas_report() -> str:
     """Concatenates the registers / spills / shared-memory lines of the last build."""
     out = []
@@ -104,5 +133,6 @@ def ptxas_report() -> str:
 
 if __name__ == "__main__":
     build(verbose=True, force="--force" in sys.argv)
+    build_capi(verbose=True)
     if "--report" in sys.argv:
         print(ptxas_report())

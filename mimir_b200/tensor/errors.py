@@ -49,6 +49,6 @@ def classify(exc: BaseException) -> MimirError:
         return ErrDType(msg)
     if "device" in low and "expected" in low:
         return ErrDevice(msg)
-    if any(k in low for k in ("shape", "size", "dimension", "broadcast", "must match", "mat1 and mat2")):
+    if any(k in low for k in ("shape", "size", "dimension", "broadcast", "must match", "mat1 and mat2", "reduction dim", " dim ")):
         return ErrShape(msg)
     return ErrInternal(msg)
