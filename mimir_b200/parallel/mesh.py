@@ -16,10 +16,12 @@ sharded layers insert:
   reduce-scatter above when the weight is sharded over the same axis).
 
 ``Mesh.traffic`` counts collectives and bytes per kind like ``Mesh.Traffic``
-(tensor/mesh.go:66-96).  Collectives use ``torch.distributed`` process groups (NCCL
-on GPUs: the baseline lowering; gloo on CPU ranks for tests); on bf16 CUDA tensors
-the all-gather + product and product + reduce-scatter pairs run as the fused
-kernels of ``parallel/fused_gemm.py``.
+(tensor/mesh.go:66-96).  Collectives here and in the per-op partitioner
+(``parallel/spmd.py``, which ``fit(sharded=...)`` uses) are ``torch.distributed``
+calls on process groups (NCCL on GPUs, gloo on CPU ranks for tests).  The fused
+all-gather + product and product + reduce-scatter kernels of
+``parallel/fused_gemm.py`` are called by the Llama engines (``models/llama.py``), not
+by these wrappers.
 """
 from __future__ import annotations
 
