@@ -870,14 +870,14 @@ def realize(*tensors: C.Tensor) -> None:
         if isinstance(t, MeshTensor) and t._val is None:      # a leaf: gather its blocks
             (o,) = lower([t], t.mesh)
             C.realize(o)
-            t._val = o._val
+            t._assign(o._val)
     if not todo:
         return
     mesh = _find_mesh(todo)
     outs = lower(todo, mesh)
     C.realize(*outs)
     for t, o in zip(todo, outs):
-        t._val = o._val
+        t._assign(o._val)
         t._fn, t._args, t._kw = None, (), {}
         t._sharding = None
 
@@ -889,7 +889,7 @@ def backward(loss: C.Tensor) -> None:
     (local_loss,) = lower([loss], mesh)
     from ..tensor.autograd import backward as plain_backward
     plain_backward(local_loss)
-    loss._val = local_loss._val
+    loss._assign(local_loss._val)
     loss._fn, loss._args, loss._kw = None, (), {}
     loss._sharding = None
 

@@ -261,10 +261,10 @@ def backward(loss: C.Tensor, effects=()) -> None:
         torch._foreach_add_(acc_dst, acc_src)
     for p in uniq:
         p._data.requires_grad_(False)
-    loss._val = out.detach()
+    loss._assign(out.detach())
     loss._fn, loss._args, loss._kw = None, (), {}
     for e, v in zip(carried, side):
-        e._val = v.detach()
+        e._assign(v.detach())
         e._fn, e._args, e._kw = None, (), {}
     for e in effects:
         e()

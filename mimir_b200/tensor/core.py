@@ -20,6 +20,7 @@ from typing import Any, Callable, Sequence
 import torch
 
 from . import errors as E
+from . import memory as _mem
 
 float32, float16, bfloat16, int32, int64, bool_ = (torch.float32, torch.float16, torch.bfloat16,
                                                     torch.int32, torch.int64, torch.bool)
@@ -102,7 +103,7 @@ class Tensor:
     """One node of the lazy graph (or a realized leaf)."""
 
     __slots__ = ("_fn", "_args", "_kw", "_val", "_err", "shape", "dtype", "device", "_stale", "_donated",
-                 "_sharding", "_opname", "_effects", "_attrs", "__weakref__")
+                 "_sharding", "_opname", "_effects", "_attrs", "_sver", "__weakref__")
 
     def __init__(self, fn=None, args=(), kw=None, val=None, err=None, shape=(), dtype=float32, device=None,
                  opname="", attrs=None):
@@ -116,6 +117,13 @@ class Tensor:
         self._opname = opname
         self._effects = ()      # tensors a backward pass computes along with the gradients
         self._attrs = attrs     # op attributes the fusion planner and the layout rules read (axes, sizes)
+        # version of the memory the value lives in (see tensor/memory.py); 0 while nothing was ever written over
+        self._sver = _mem.version_of(val) if _mem._VERSIONS and val is not None else 0
+
+    def _assign(self, val) -> None:
+        """Gives a lazy node its value (every path that realizes a tensor ends here or in ``realize``)."""
+        self._val = val
+        self._sver = _mem.version_of(val) if _mem._VERSIONS else 0
 
     # ------------------------------------------------------------- properties
     @property
@@ -364,17 +372,20 @@ def _flatten(args):
 def _check_leaf(t: Tensor):
     if t._donated:
         raise E.ErrDonated("tensor was donated to an earlier schedule")
+    if _mem._VERSIONS:
+        _mem.check_current(t)
     if t._stale is not None:
         p, version = t._stale
         if p._version != version:
             raise E.ErrOverwritten("parameter value was overwritten by a later in-place step")
 
 
-def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bool = True) -> list:
+def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bool = True, into: dict | None = None) -> list:
     """Evaluates the graph below ``roots`` and returns torch tensors.  ``memo`` maps ``id(node)`` to a
     value that stands in for that node (how ``backward`` substitutes differentiable leaves).  The
     graph is planned into a program (fusion, slots, early release of intermediates) that is cached
-    by structure: see ``tensor/plan.py``."""
+    by structure: see ``tensor/plan.py``.  ``into`` maps the position of a root to a torch tensor
+    whose memory the root is to be computed into (``realize_into``)."""
     from . import plan
     memo = {} if memo is None else memo
     roots = list(roots)
@@ -389,7 +400,11 @@ def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bo
 
     def on_error(i, err):
         w.order[i]._err = err
-    outs = prog.run(leaf_vals, w.order, on_error)
+    pool = None
+    if not torch.is_grad_enabled() and not _mem.in_transform():
+        dev = next((v.device for v in leaf_vals if torch.is_tensor(v)), None)
+        pool = _mem.pool_for(dev) if dev is not None else None
+    outs = prog.run(leaf_vals, w.order, on_error, pool=pool, into=into)
     for r, v in zip(roots, outs):
         memo[id(r)] = v
     return outs
@@ -416,6 +431,8 @@ def realize(*tensors: Tensor) -> None:
     for t, v in zip(todo, vals):
         t._val = v.detach() if torch.is_tensor(v) else v
         t._fn, t._args, t._kw = None, (), {}
+        if _mem._VERSIONS:
+            t._sver = _mem.version_of(t._val)
 
 
 # ---------------------------------------------------------------------------
@@ -505,6 +522,11 @@ def _binary_dtype(a: Tensor, b: Tensor, opname: str):
     return None, E.ErrDType(f"{opname}: dtypes {a.dtype} and {b.dtype} do not mix (cast explicitly)")
 
 
+_OUT_CAPABLE = {torch.add, torch.sub, torch.mul, torch.maximum, torch.minimum, torch.neg, torch.exp, torch.log, torch.sqrt,
+                torch.rsqrt, torch.sin, torch.cos, torch.tanh, torch.sigmoid, torch.abs, torch.sign, torch.floor, torch.ceil,
+                torch.reciprocal, torch.erf, torch.erfinv, torch.log1p, torch.expm1}
+
+
 def _binary(opname, fn, out_bool=False):
     def op(a, b):
         like = a if isinstance(a, Tensor) else b
@@ -519,6 +541,14 @@ def _binary(opname, fn, out_bool=False):
             if x.dtype != y.dtype:
                 x, y = x.to(dt), y.to(dt)
             return fn(x, y)
+        if fn in _OUT_CAPABLE:
+            # the same computation into given memory: what a program uses for pooled buffers and
+            # for a destination of ``realize_into``
+            def run_out(x, y, out):
+                if x.dtype != y.dtype:
+                    x, y = x.to(dt), y.to(dt)
+                fn(x, y, out=out)
+            run._mimir_out = run_out
         return _node(run, (a, b), {}, opname, attrs={"kind": "binary"})
     op.__name__ = opname
     return op
@@ -553,6 +583,10 @@ def _unary(opname, fn, native_mode=None):
                 from ..ops import functional as NF
                 return NF.activation(v, native_mode)
             return fn(v, *args, **kw)
+        if fn in _OUT_CAPABLE and native_mode is None and not args and not kw:
+            def run_out(v, out):
+                fn(v, out=out)
+            run._mimir_out = run_out
         return _node(run, (x,), {}, opname, attrs={"kind": "unary"})
     op.__name__ = opname
     return op
@@ -1053,14 +1087,61 @@ def from_bytes_func(fill, shape, dtype=torch.float32, device: Device | None = No
     return from_torch(t if device is None else t.to(device.torch))
 
 
-def realize_into(dst: Tensor, src: Tensor) -> Tensor:
-    """Computes ``src`` and writes it over the storage of the realized tensor ``dst`` (same shape and
-    dtype), so that holders of ``dst`` see the new value (sched.RealizeInto)."""
-    if tuple(dst.shape) != tuple(src.shape) or dst.dtype != src.dtype:
-        raise E.ErrShape(f"realize_into: {tuple(src.shape)} {src.dtype} does not fit {tuple(dst.shape)} {dst.dtype}")
-    realize(dst, src)
-    dst._val.copy_(src._val)
-    return dst
+def realize_into(dsts, srcs):
+    """Computes every tensor of ``srcs`` in ONE schedule and writes ``srcs[i]`` over the memory of the
+    realized tensor ``dsts[i]`` (same shape, dtype and device; ``None`` = new memory) where it can,
+    as an optimizer writes a parameter's new value over the old one (tensor.RealizeInto,
+    tensor/tensor.go:356-378; internal/sched/into.go:24-66).  Both may be single tensors.
+
+    Afterwards ``srcs[i]`` is realized IN the memory of ``dsts[i]``, and ``dsts[i]`` is stale, and so is
+    every tensor realized earlier that shares its memory (a view): reading one, or computing a tensor
+    built from one, raises ``ErrOverwritten``.  The value is computed straight into the destination
+    when the instruction that produces it can write into given memory (elementwise ops) and nothing
+    in the schedule reads the old values after it; otherwise it is computed into pooled memory and
+    copied over when the schedule has finished reading.  On error nothing is written."""
+    single = isinstance(srcs, Tensor)
+    dsts = [dsts] if single else list(dsts)
+    srcs = [srcs] if single else list(srcs)
+    if len(dsts) != len(srcs):
+        raise E.ErrShape(f"realize_into: {len(dsts)} destinations for {len(srcs)} tensors")
+    seen = set()
+    for d, s in zip(dsts, srcs):
+        if s._err is not None:
+            raise s._err
+        if d is None:
+            continue
+        if d._val is None:
+            raise E.ErrNilTensor("realize_into: the destination is not realized")
+        _check_leaf(d)
+        if tuple(d.shape) != tuple(s.shape) or d.dtype != s.dtype or d.device != s.device:
+            raise E.ErrShape(f"realize_into: {tuple(s.shape)} {s.dtype} on {s.device} does not fit "
+                             f"{tuple(d.shape)} {d.dtype} on {d.device}")
+        if not d._val.is_contiguous():
+            raise E.ErrUnsupported("realize_into: the destination is a strided view")
+        a = _mem._address(d._val)
+        if a in seen:
+            raise E.ErrOverwritten("realize_into: two destinations share memory")
+        seen.add(a)
+    todo = [(i, s) for i, s in enumerate(srcs) if s._val is None]
+    if any(_on_mesh(s) for _, s in todo):
+        raise E.ErrUnsupported("realize_into: tensors on a device mesh are written by the sharded step")
+    if todo:
+        from .memory import reserve
+        reserve([s for _, s in todo])
+        into = {k: dsts[i]._val for k, (i, _) in enumerate(todo) if dsts[i] is not None}
+        with torch.no_grad():
+            vals = evaluate([s for _, s in todo], into=into)
+        for (i, s), v in zip(todo, vals):
+            s._val = v.detach() if torch.is_tensor(v) else v
+            s._fn, s._args, s._kw = None, (), {}
+    for d, s in zip(dsts, srcs):
+        if d is None:
+            continue
+        if s._val.data_ptr() != d._val.data_ptr() or _mem._address(s._val) != _mem._address(d._val):
+            d._val.copy_(s._val)          # computed elsewhere (or realized before): copy, then live there
+            s._val = d._val
+        s._sver = _mem.overwrite(d._val)   # d (and older views of its memory) are stale from here on
+    return srcs[0] if single else srcs
 
 
 def _bind_methods():

@@ -91,9 +91,17 @@ class Recording:
         dests = [dests] if isinstance(dests, C.Tensor) else list(dests)
         if len(dests) != len(outs) or any(tuple(d.shape) != tuple(o.shape) or d.dtype != o.dtype for d, o in zip(dests, outs)):
             return False
-        for d, o in zip(dests, outs):
-            C.realize_into(d, o)
+        _write_into(dests, outs)
         return True
+
+
+def _write_into(dests, outs) -> None:
+    """Writes ``outs`` over the memory of ``dests`` in one schedule; the ``dests`` handles then stand
+    for the new values (``realize_into`` leaves a destination stale; here the caller keeps using it)."""
+    outs = list(outs)
+    C.realize_into(list(dests), outs)
+    for d, o in zip(dests, outs):
+        d._val, d._sver = o._val, o._sver
 
 
 def record(f, *inputs) -> Recording:
@@ -104,8 +112,7 @@ def record_into(dests, f, *inputs) -> Recording:
     """``record`` whose first run already lands in ``dests`` (tensor.RecordInto)."""
     r = Recording(f, inputs)
     dests = [dests] if isinstance(dests, C.Tensor) else list(dests)
-    for d, o in zip(dests, r.outputs):
-        C.realize_into(d, o)
+    _write_into(dests, r.outputs)
     return r
 
 

@@ -33,7 +33,7 @@ from . import errors as E
 
 _MAX_PROGRAMS = 64
 _CACHE: "collections.OrderedDict[tuple, Program]" = collections.OrderedDict()
-_STATS = {"compiled": 0, "hits": 0, "uncacheable": 0, "fused": 0}
+_STATS = {"compiled": 0, "hits": 0, "uncacheable": 0, "fused": 0, "into_direct": 0}
 
 
 def compiled() -> int:
@@ -62,29 +62,53 @@ class Program:
     ``nleaves`` leaf slots come first, ``roots`` are the slots to return, ``last_use[slot]`` is
     the instruction after which the slot is dropped."""
 
-    __slots__ = ("instrs", "nleaves", "nslots", "roots", "drop_after", "fused")
+    __slots__ = ("instrs", "nleaves", "nslots", "roots", "drop_after", "fused", "out_meta", "last_use", "writer")
 
-    def __init__(self, instrs, nleaves, nslots, roots, fused):
+    def __init__(self, instrs, nleaves, nslots, roots, fused, out_meta=None):
         self.instrs, self.nleaves, self.nslots, self.roots, self.fused = instrs, nleaves, nslots, roots, fused
+        self.out_meta = out_meta or [None] * len(instrs)     # (shape, dtype) of each instruction's result
         keep = set(roots)
         last = {}
         for i, (_, spec, _, _, _) in enumerate(instrs):
             for s in _spec_slots(spec):
                 last[s] = i
+        self.last_use = last
+        self.writer = {out: i for i, (_, _, _, out, _) in enumerate(instrs)}
         self.drop_after = [[] for _ in instrs]
         for s, i in last.items():
             if s not in keep and s >= nleaves:
                 self.drop_after[i].append(s)
 
-    def run(self, leaf_vals, order=None, on_error=None):
+    def run(self, leaf_vals, order=None, on_error=None, pool=None, into=None):
         """Runs the instructions over ``leaf_vals``.  ``order`` is the node list of the graph being
-        run: instructions whose executable is volatile take it from there."""
+        run: instructions whose executable is volatile take it from there.  ``pool`` (only without
+        autograd) serves the outputs of instructions that can write into given memory; ``into`` maps
+        a position in ``roots`` to the torch tensor that root is to be written into."""
         slots = list(leaf_vals) + [None] * (self.nslots - self.nleaves)
+        dest = self._destinations(leaf_vals, into) if into else {}
+        owner = {} if pool is not None else None     # storage address of a pooled buffer -> [buffer, live slots]
+        lives = {} if pool is not None else None     # slot -> addresses of the pooled buffers its value lives in
         for i, (fn, spec, kw, out, node_idx) in enumerate(self.instrs):
             if order is not None and getattr(fn, "_mimir_volatile", False):
                 fn = order[node_idx]._fn
             try:
-                slots[out] = fn(*_fill(spec, slots), **kw)
+                writes = getattr(fn, "_mimir_out", None) if (pool is not None or i in dest) else None
+                buf = None
+                if writes is not None and not kw and self.out_meta[i] is not None:
+                    if i in dest and self._aliased_later(slots, dest[i], i):
+                        del dest[i]       # a view of the destination's memory is still to be read: copy at the end
+                    if i in dest:
+                        buf = dest[i]
+                        _STATS["into_direct"] += 1
+                    elif pool is not None:
+                        shape, dtype = self.out_meta[i]
+                        buf = pool.take(shape, dtype, _device_of(slots, spec))
+                        owner[buf.untyped_storage().data_ptr()] = [buf, 0]
+                if buf is not None:
+                    writes(*_fill(spec, slots), out=buf)
+                    slots[out] = buf
+                else:
+                    slots[out] = fn(*_fill(spec, slots), **kw)
             except E.MimirError as err:
                 if on_error is not None:
                     on_error(node_idx, err)
@@ -96,9 +120,85 @@ class Program:
                 if on_error is not None:
                     on_error(node_idx, err)
                 raise err from exc
+            if owner:
+                # a value that lives in a pooled buffer (the output itself or a view an instruction
+                # made of one) keeps that buffer out of the pool until its slot is dropped
+                addrs = [a for a in _addresses(slots[out]) if a in owner]
+                if addrs:
+                    lives[out] = addrs
+                    for a in addrs:
+                        owner[a][1] += 1
             for s in self.drop_after[i]:
                 slots[s] = None
+                if lives and s in lives:
+                    for a in lives.pop(s):
+                        rec = owner[a]
+                        rec[1] -= 1
+                        if rec[1] == 0:
+                            pool.give(rec[0])
+                            del owner[a]
+        # buffers that a result lives in leave the pool; the rest of what is still out goes back
+        if owner:
+            kept = set()
+            for r in self.roots:
+                kept.update(lives.get(r, ()))
+            for a, rec in owner.items():
+                if a not in kept:
+                    pool.give(rec[0])
         return [slots[r] for r in self.roots]
+
+    def _aliased_later(self, slots, dst, i) -> bool:
+        """True when a value computed before instruction ``i`` lives in the memory of ``dst`` (a view an
+        earlier instruction made of a leaf) and is read after ``i``."""
+        a = dst.untyped_storage().data_ptr()
+        for s in range(self.nleaves, self.nslots):
+            v = slots[s]
+            if v is not None and self.last_use.get(s, -1) > i and any(x == a for x in _addresses(v)):
+                return True
+        return False
+
+    def _destinations(self, leaf_vals, into):
+        """instruction index -> destination tensor, for the roots that can be computed straight into
+        their destination: the producing instruction writes into given memory, and no instruction
+        after it reads a leaf that lives in the destination's memory (the producer itself may:
+        an elementwise kernel reads each element before it writes it)."""
+        out = {}
+        for k, dst in into.items():
+            slot = self.roots[k]
+            i = self.writer.get(slot)
+            if i is None or getattr(self.instrs[i][0], "_mimir_out", None) is None or self.roots.count(slot) != 1:
+                continue
+            a = dst.untyped_storage().data_ptr()
+            safe = True
+            for ls, v in enumerate(leaf_vals):
+                if torch.is_tensor(v) and v.device.type != "meta" and v.untyped_storage().data_ptr() == a:
+                    if self.last_use.get(ls, -1) > i:
+                        safe = False
+                    elif self.last_use.get(ls, -1) == i and (v.data_ptr() != dst.data_ptr() or tuple(v.shape) != tuple(dst.shape)
+                                                             or v.stride() != dst.stride()):
+                        safe = False      # the producer reads a shifted view of the memory it writes
+            if safe:
+                out[i] = dst
+        return out
+
+
+def _addresses(v):
+    if torch.is_tensor(v):
+        if v.device.type != "meta":
+            try:
+                yield v.untyped_storage().data_ptr()
+            except (NotImplementedError, RuntimeError):   # a transform's wrapper tensor
+                return
+    elif isinstance(v, (tuple, list)):
+        for x in v:
+            yield from _addresses(x)
+
+
+def _device_of(slots, spec):
+    for a in spec:
+        if isinstance(a, _Ref) and torch.is_tensor(slots[a.slot]):
+            return slots[a.slot].device
+    return torch.device("cpu")
 
 
 def _spec_slots(spec):
@@ -251,7 +351,7 @@ def _compile(w: _Walk, roots, fusion, absorbed):
     from .core import Tensor
     nleaves = len(w.leaves)
     slot_of = {id(t): i for i, t in enumerate(w.leaves)}
-    instrs, nxt = [], nleaves
+    instrs, metas, nxt = [], [], nleaves
 
     def spec_of(args):
         sp = []
@@ -273,8 +373,9 @@ def _compile(w: _Walk, roots, fusion, absorbed):
             fn, args, kw = t._fn, t._args, t._kw
         slot_of[id(t)] = nxt
         instrs.append((fn, spec_of(args), kw, nxt, i))
+        metas.append((tuple(t.shape), t.dtype))
         nxt += 1
-    return Program(instrs, nleaves, nxt, [slot_of[id(r)] for r in roots], len(fusion))
+    return Program(instrs, nleaves, nxt, [slot_of[id(r)] for r in roots], len(fusion), metas)
 
 
 def _structural_key(w: _Walk, roots):

@@ -1,0 +1,163 @@
+"""Storage versions, destinations of ``realize_into`` and the buffer pool (reference:
+internal/sched/into.go:24-66, memory.go:144-190, internal/graph/graph.go:86-115; behaviour after
+tensor/tensor.go:356-378)."""
+import pytest
+import torch
+
+import mimir_b200.tensor as T
+from mimir_b200.tensor import memory, plan
+
+
+def _stale(t):
+    with pytest.raises(T.ErrOverwritten):
+        t.data()
+
+
+def test_elementwise_update_is_computed_straight_into_its_destination():
+    p = T.tensor(torch.arange(6.0).reshape(2, 3))
+    g = T.tensor(torch.ones(2, 3))
+    mem = p.data()
+    before = plan.stats()["into_direct"]
+    new = T.realize_into(p, p - g * 0.5)                 # an optimizer's update: reads p elementwise, writes p
+    assert plan.stats()["into_direct"] == before + 1     # no temporary, no copy
+    assert new.data().data_ptr() == mem.data_ptr()
+    assert mem.tolist() == [[-0.5, 0.5, 1.5], [2.5, 3.5, 4.5]]
+    _stale(p)
+    again = T.realize_into(new, new * 2.0)               # the live handle can be written over in turn
+    assert again.data().data_ptr() == mem.data_ptr() and mem[0, 0] == -1.0
+    _stale(new)
+
+
+def test_a_destination_that_is_read_later_is_written_after_the_schedule():
+    a = T.tensor(torch.tensor([1.0, 2.0, 3.0]))
+    b = T.tensor(torch.tensor([10.0, 20.0, 30.0]))
+    ma, mb = a.data(), b.data()
+    before = plan.stats()["into_direct"]
+    na, nb = T.realize_into([a, b], [b * 2.0, a * 3.0])    # each source reads the other's destination
+    assert ma.tolist() == [20.0, 40.0, 60.0] and mb.tolist() == [3.0, 6.0, 9.0]     # old values on both sides
+    # the second product runs last, so it alone may land straight in its destination
+    assert plan.stats()["into_direct"] - before <= 1
+    assert na.data().data_ptr() == ma.data_ptr() and nb.data().data_ptr() == mb.data_ptr()
+    _stale(a)
+    _stale(b)
+
+
+def test_non_elementwise_sources_and_realized_sources_are_copied():
+    w = T.tensor(torch.eye(3) * 2.0)
+    x = T.tensor(torch.arange(9.0).reshape(3, 3))
+    dst = T.tensor(torch.zeros(3, 3))
+    mem = dst.data()
+    out = T.realize_into(dst, T.matmul(x, w))
+    assert torch.equal(mem, torch.arange(9.0).reshape(3, 3) * 2.0) and out.data().data_ptr() == mem.data_ptr()
+    ready = (x + 1.0).realize()
+    dst2 = T.tensor(torch.zeros(3, 3))
+    out2 = T.realize_into(dst2, ready)
+    assert out2 is ready and torch.equal(out2.data(), torch.arange(9.0).reshape(3, 3) + 1.0)
+    assert T.realize_into([None], [x * 1.0])[0].data().tolist() == x.data().tolist()     # no destination: new memory
+
+
+def test_views_of_overwritten_memory_are_stale_and_misfits_are_refused():
+    base = torch.arange(8.0)
+    whole = T.from_torch(base)
+    half = T.from_torch(base[4:])                          # shares the memory
+    other = T.tensor(torch.arange(8.0))                    # does not
+    T.realize_into(whole, whole + 1.0)
+    _stale(half)
+    assert other.data()[1] == 1.0
+    fresh = T.from_torch(base[4:])                         # realized after the write: current
+    assert fresh.data().tolist() == [5.0, 6.0, 7.0, 8.0]
+    with pytest.raises(T.ErrShape):
+        T.realize_into(other, T.tensor([1.0, 2.0]) * 2.0)
+    with pytest.raises(T.ErrShape):
+        T.realize_into(other, T.cast(other, T.int32) * 2)
+    both = T.from_torch(torch.zeros(4))
+    with pytest.raises(T.ErrOverwritten):
+        T.realize_into([both, T.from_torch(both.data())], [both * 2.0, both * 3.0])
+    lazy = other + 1.0
+    with pytest.raises(T.ErrNilTensor):
+        T.realize_into(lazy, other * 1.0)
+    bad = T.matmul(T.tensor(torch.ones(2, 3)), T.tensor(torch.ones(2, 3)))     # a sticky shape error
+    keep = T.tensor(torch.zeros(2, 2))
+    with pytest.raises(T.ErrShape):
+        T.realize_into(keep, bad)
+    assert keep.data().sum() == 0                          # nothing written, still current
+
+
+def test_pool_serves_elementwise_temporaries_and_replays_over_the_same_buffers():
+    memory.set_pool("cpu")
+    pool = memory.pool()
+    pool.trim()
+    x = T.tensor(torch.randn(64, 64))
+    y = T.tensor(torch.randn(64, 64))
+
+    def f(a, b):
+        return T.exp(T.tanh(a * b + a) - b).reshape((32, 128))
+
+    want = torch.exp(torch.tanh(x.data() * y.data() + x.data()) - y.data()).reshape(32, 128)
+    first = f(x, y).realize()
+    st0 = pool.stats()
+    assert torch.allclose(first.data(), want) and st0["takes"] >= 4
+    second = f(x, y).realize()
+    st1 = pool.stats()
+    assert st1["reused"] - st0["reused"] >= 3              # the temporaries of the first run serve the second
+    third = f(x, y).realize()
+    st2 = pool.stats()
+    assert st2["obtained_bytes"] - st1["obtained_bytes"] <= 64 * 64 * 4      # steady state: one result buffer per run leaves the pool
+    # results left the pool with their buffers: later runs did not write over them
+    assert torch.equal(first.data(), second.data()) and torch.equal(first.data(), third.data())
+    assert len({first.data().data_ptr(), second.data().data_ptr(), third.data().data_ptr()}) == 3
+
+
+def test_pooled_buffer_stays_out_while_a_view_of_it_is_read():
+    memory.set_pool("cpu")
+    a = T.tensor(torch.arange(12.0))
+    s = (a + 1.0).reshape((3, 4))                          # a view of a pooled buffer ...
+    t = T.permute(s, (1, 0))                               # ... and a view of that view
+    u = t * 2.0 + T.sum_(s)                                # read after the buffer's own slot has been dropped
+    want = (torch.arange(12.0) + 1).reshape(3, 4).t() * 2 + (torch.arange(12.0) + 1).sum()
+    for _ in range(3):
+        assert torch.equal((t * 2.0 + T.sum_(s)).data(), want)
+    assert torch.equal(u.data(), want)
+    parts = T.split(a * 3.0, [5, 7])                       # a tuple of views of one pooled buffer as results
+    T.realize(*parts)
+    (a * 5.0).realize()
+    (a * 7.0).realize()
+    assert parts[0].data().tolist() == [0.0, 3.0, 6.0, 9.0, 12.0] and parts[1].data()[-1] == 33.0
+
+
+def test_pool_is_not_used_under_autograd_and_can_be_turned_off():
+    from mimir_b200.tensor.autograd import Param, backward
+    memory.set_pool("cpu")
+    pool = memory.pool()
+    p = Param(torch.randn(8, 8))
+    takes = pool.stats()["takes"]
+    loss = T.sum_(T.tanh(p.value() * 2.0) * T.tanh(p.value() * 2.0))
+    backward(loss)
+    assert pool.stats()["takes"] == takes and p.grad() is not None
+    memory.set_pool("0")
+    (T.tensor(torch.ones(4)) * 2.0 + 1.0).realize()
+    assert pool.stats()["takes"] == takes and pool.stats()["buffers"] == 0
+    memory.set_pool("cpu")
+
+
+def test_a_view_made_before_the_write_and_read_after_it_keeps_the_old_values():
+    d = T.tensor(torch.arange(6.0))
+    mem = d.data()
+    v = T.reshape(d, (2, 3))
+    total, new, later = T.realize_into([None, d, None], [T.sum_(v), d * 2.0, v + 1.0])
+    assert total.item() == 15.0
+    assert later.data().tolist() == [[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]]      # computed from the old values
+    assert mem.tolist() == [0.0, 2.0, 4.0, 6.0, 8.0, 10.0] and new.data().data_ptr() == mem.data_ptr()
+
+
+def test_broadcast_operands_and_mixed_dtypes_take_the_pool_path_correctly():
+    memory.set_pool("cpu")
+    a = T.tensor(torch.randn(4, 1, 8))
+    b = T.tensor(torch.randn(5, 1))
+    h = T.cast(T.tensor(torch.randn(4, 5, 8)), T.bfloat16)
+    want = (a.data() * b.data() + h.data().float()).abs().neg()
+    for _ in range(3):
+        got = T.neg(T.abs_(a * b + h)).data()
+        assert got.dtype == torch.float32 and torch.equal(got, want)
+    small = T.tensor(torch.randn(3)) + 1                    # a Python scalar operand
+    assert small.data().shape == (3,)

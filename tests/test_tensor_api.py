@@ -102,8 +102,18 @@ def test_bytes_round_trip_realize_into_and_record_into():
     assert z.data().tolist() == y.data().tolist()
     dst = T.tensor([[0.0, 0.0], [0.0, 0.0]])
     held = dst.data()
-    T.realize_into(dst, x * 2.0)
+    view = T.from_torch(held[0])                                          # a view of the same memory, realized earlier
+    built = dst + 1.0                                                     # built from the old value, not computed yet
+    new = T.realize_into(dst, x * 2.0)
     assert held.tolist() == [[2.0, 4.0], [6.0, 8.0]]                      # same storage, new value
+    assert new.data().data_ptr() == held.data_ptr() and new.data().tolist() == held.tolist()
+    for stale in (dst, view, built):                                      # the destination, its views and what was built on it
+        try:
+            stale.data()
+            raise AssertionError("a stale tensor was read")
+        except T.ErrOverwritten:
+            pass
+    assert (new + 1.0).data().tolist() == [[3.0, 5.0], [7.0, 9.0]]
     out = T.tensor([0.0, 0.0])
     rec = T.record_into(out, lambda a: a + 1.0, T.tensor([1.0, 2.0]))
     assert out.data().tolist() == [2.0, 3.0]
