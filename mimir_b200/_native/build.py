@@ -1,5 +1,6 @@
 """Builds the native library in-tree: every ``csrc/*.cu`` / ``*.cpp`` is compiled
-for sm_100a and linked into ``mimir_b200/_native/libmimir_b200.so``.
+for sm_100a (``*.cc``: host-only CPU kernels, by the host compiler) and linked into
+``mimir_b200/_native/libmimir_b200.so``.
 
 The library has a plain C ABI (no Python or torch headers), so it compiles in
 seconds, loads through ``ctypes`` here and through ``purego`` from Go, and the
@@ -51,15 +52,22 @@ def _compile(src: Path, verbose: bool) -> Path:
     dig = _digest(src)
     if obj.exists() and stamp.exists() and stamp.read_text() == dig:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
-    if src.suffix == ".cpp":
-        cmd.insert(1, "-x")
-        cmd.insert(2, "cu")
+    if src.suffix == ".cc":
+        # host-only sources (CPU kernels with per-function ISA targets) go straight to the host compiler
+        cxx = shutil.which("g++") or shutil.which("c++")
+        if cxx is None:
+            raise RuntimeError("no C++ compiler found")
+        cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        if src.suffix == ".cpp":
+            cmd.insert(1, "-x")
+            cmd.insert(2, "cu")
     res = subprocess.run(cmd, capture_output=True, text=True)
     log = OBJ / (src.name + ".log")
     log.write_text(res.stdout + res.stderr)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stdout}\n{res.stderr}")
+        raise RuntimeError(f"compiling {src.name} failed:\n{res.stdout}\n{res.stderr}")
     if verbose:
         sys.stderr.write(f"[build] {src.name}\n")
     stamp.write_text(dig)
@@ -67,7 +75,7 @@ def _compile(src: Path, verbose: bool) -> Path:
 
 
 def sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp"))
+    return sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp")) + sorted(CSRC.glob("*.cc"))
 
 
 def build(verbose: bool = False, force: bool = False) -> Path:

@@ -128,8 +128,18 @@ def qmatmul_t(x: torch.Tensor, w) -> torch.Tensor:
         n = w.shape[0] * w.shape[1]
         wd = quant_cuda.dequantize(w.code, raw, n).view(w.shape)       # many rows (prefill): dequantise on the GPU
         return (x.float() @ wd.t()).to(x.dtype)
+    if x.device.type == "cpu" and w.raw.device.type == "cpu" and w.code in (Q8_0, Q4_0, Q4_K, Q6_K) and len(w.shape) == 2 \
+            and not torch.is_grad_enabled() and x.numel() // max(x.shape[-1], 1) <= _QGEMV_MAX_ROWS \
+            and w.shape[1] % BLOCK[w.code][0] == 0:
+        # few rows on the host (decode): the native kernel reads the weight once in its block
+        # encoding; CPU_MODE picks float activations ("exact") or int8 blocks with VNNI ("int8" / "auto")
+        from . import quant_cpu
+        raw = w.raw if w.raw.is_contiguous() else w.raw.contiguous()
+        y = quant_cpu.qgemv(w.code, raw.reshape(-1), w.shape[0], w.shape[1], x, CPU_MODE)
+        return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
     wd = dequantize(w, torch.float32).to(x.device)
     return (x.float() @ wd.t()).to(x.dtype)
 
 
 _QGEMV_MAX_ROWS = 16
+CPU_MODE = "exact"      # the lazy layer's product keeps the meaning x @ dequant(W)^T; decoders ask for "auto"

@@ -1,0 +1,55 @@
+"""CPU products with block-quantized weights read in place (``csrc/cpu_quant.cc``): the host path of
+decoding, where the reference keeps its weights quantized too (backend/cpu/quant.go,
+llm/decode.go:79-160).  ``mode``: ``"exact"`` multiplies float activations with weights decoded value
+by value (exactly ``x @ dequant(W)^T`` up to float summation order); ``"int8"`` rounds the
+activation rows to 32-value int8 blocks and uses VNNI dot products (the CPU must have AVX-512 VNNI);
+``"auto"`` takes int8 where the CPU has it."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+
+_MODES = {"exact": 0, "int8": 1, "auto": -1}
+MAX_ROWS = 8
+
+
+def _lib():
+    lib = _native.lib()
+    if not getattr(lib, "_cpuq_bound", False):
+        c = ctypes
+        lib.mimir_cpu_qgemv.argtypes = [c.c_int, c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_int, c.c_void_p, c.c_int, c.c_void_p]
+        lib.mimir_cpu_qgemv_has_int8.restype = c.c_int
+        lib.mimir_cpu_set_threads.argtypes = [c.c_int]
+        lib._cpuq_bound = True
+    return lib
+
+
+def has_int8() -> bool:
+    return bool(_lib().mimir_cpu_qgemv_has_int8())
+
+
+def set_threads(n: int) -> int:
+    """Threads of the next products (0 = one per hardware thread); returns the previous setting."""
+    return _lib().mimir_cpu_set_threads(int(n))
+
+
+def qgemv(code: int, raw: torch.Tensor, n: int, k: int, x: torch.Tensor, mode: str = "auto") -> torch.Tensor:
+    """``x [B, K] @ W^T`` -> fp32 ``[B, N]`` for a weight of ``n`` rows of ``k`` values stored as ggml
+    blocks of ``code`` in the uint8 tensor ``raw``; up to 8 rows per call (more are chunked)."""
+    if raw.device.type != "cpu" or raw.dtype != torch.uint8 or not raw.is_contiguous():
+        raise ValueError("qgemv: the weight must be a contiguous uint8 CPU tensor")
+    rows = x.reshape(-1, x.shape[-1]).float().contiguous()
+    if rows.shape[1] != k:
+        raise ValueError(f"qgemv: activations of {rows.shape[1]} columns for a weight of {k}")
+    out = torch.empty(rows.shape[0], n, dtype=torch.float32)
+    lib = _lib()
+    for b0 in range(0, rows.shape[0], MAX_ROWS):
+        xb = rows[b0:b0 + MAX_ROWS]
+        yb = out[b0:b0 + MAX_ROWS]
+        rc = lib.mimir_cpu_qgemv(code, raw.data_ptr(), n, k, xb.data_ptr(), xb.shape[0], yb.data_ptr(), _MODES[mode], None)
+        if rc:
+            raise ValueError(f"qgemv: unsupported arguments (code {code}, N {n}, K {k}, mode {mode})")
+    return out
