@@ -124,6 +124,36 @@ def mapped(path: str, x: str = "x", y: str | None = "y", batch_size=32, shuffle=
 
 
 # -------------------------------------------------------------------- synthetic
+class _SyntheticShard(Source):
+    """Rows generated as they are read: features uniform in [-1, 1), target 1 where a fixed direction
+    of the feature space is positive (separable), every chunk a function of (seed, shard, chunk) only."""
+
+    def __init__(self, rows: int, features: int, seed: int, shard: int, chunk: int = 65536):
+        self.rows, self.features, self.seed, self.shard, self.chunk = rows, features, seed, shard, chunk
+        g = torch.Generator().manual_seed(seed * 2654435761 % (1 << 62))
+        self.w = torch.randn(features, generator=g)
+
+    def read(self):
+        done, c = 0, 0
+        while done < self.rows:
+            n = min(self.chunk, self.rows - done)
+            g = torch.Generator().manual_seed((self.seed * 1000003 + self.shard) * 1000003 + c)
+            x = torch.rand(n, self.features, generator=g) * 2.0 - 1.0
+            yield x, (x @ self.w > 0).long()
+            done += n
+            c += 1
+
+
+def synthetic(rows: int, features: int = 32, shards: int = 1, seed: int = 0, batch_size: int = 32, **kw) -> Stream:
+    """A stream of ``rows`` generated rows over ``shards`` shards in constant memory, for scale tests
+    and benchmarks (datasets.Synthetic, data/datasets/synthetic.go): nothing is stored, so the row
+    count is free; the same seed gives the same rows."""
+    rows, features, shards = max(int(rows), 0), max(int(features), 1), max(int(shards), 1)
+    per, extra = divmod(rows, shards)
+    srcs = [_SyntheticShard(per + (1 if i < extra else 0), features, seed, i) for i in range(shards)]
+    return Stream([s for s in srcs if s.rows], batch_size=batch_size, **kw)
+
+
 def synthetic_classification(rows=1024, features=16, classes=4, batch_size=32, seed=0, noise=0.5) -> Tensors:
     g = torch.Generator().manual_seed(seed)
     centers = torch.randn(classes, features, generator=g) * 2

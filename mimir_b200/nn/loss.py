@@ -62,7 +62,13 @@ def cross_entropy(logits, target):
             from ..ops import functional as NF
             return NF.cross_entropy(l, t)
         return F.cross_entropy(l.float(), t.long())
-    return _core._node(run, (logits, target), {}, "cross_entropy")
+    # a scalar float32 result whenever the operands fit; a misfit goes through the inference and
+    # comes back as a sticky error
+    known = None
+    if logits._err is None and target._err is None and len(logits.shape) >= 2 and logits.dtype.is_floating_point \
+            and not target.dtype.is_floating_point and tuple(target.shape) == tuple(logits.shape[:1]) + tuple(logits.shape[2:]):
+        known = ((), T.float32)
+    return _core._node(run, (logits, target), {}, "cross_entropy", known=known)
 
 
 def nll(logp, target):

@@ -280,6 +280,7 @@ def _meta_key(fn, args, kw):
     captured by the closure, a list argument): that inference is simply not cached."""
     try:
         cells = tuple(c.cell_contents for c in (fn.__closure__ or ()))
+        cells = tuple(() if isinstance(c, (list, dict, tuple)) and not c else c for c in cells)   # empty containers are constants
         for c in cells:
             if isinstance(c, (torch.Tensor, Tensor, list, dict)):
                 return None
@@ -297,9 +298,11 @@ def _meta_key(fn, args, kw):
         return None
 
 
-def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None, attrs=None) -> Tensor:
+def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | None = None, attrs=None, known=None) -> Tensor:
     """Records ``fn(*args, **kw)``: propagates errors, infers shape/dtype on meta tensors (the result
-    of an inference is cached by structure, so a training loop pays for it once)."""
+    of an inference is cached by structure, so a training loop pays for it once).  ``known`` =
+    (shape, dtype) skips the inference for ops whose result type is plain (elementwise ops of one
+    floating tensor)."""
     err = _first_error(args)
     if err is not None:
         return _error_tensor(err)
@@ -309,6 +312,12 @@ def _node(fn: Callable, args: Sequence, kw: dict, opname: str, device: Device | 
         for t in tensors:
             if t.device != device:
                 return _error_tensor(E.ErrDevice(f"{opname}: operands on {device} and {t.device}"))
+    if known is not None:
+        out = Tensor(fn=fn, args=tuple(args), kw=kw, shape=known[0], dtype=known[1], device=device, opname=opname, attrs=attrs)
+        _inherit_mesh(out, tensors)
+        if _EAGER and out._sharding is None:
+            realize(out)
+        return out
     key = _meta_key(fn, args, kw)
     meta = _META_CACHE.get(key) if key is not None else None
     if meta is None:
@@ -527,6 +536,20 @@ _OUT_CAPABLE = {torch.add, torch.sub, torch.mul, torch.maximum, torch.minimum, t
                 torch.reciprocal, torch.erf, torch.erfinv, torch.log1p, torch.expm1}
 
 
+def _broadcast(p, q):
+    """Broadcast of two shapes, or None when they do not fit."""
+    if p == q:
+        return tuple(p)
+    n = max(len(p), len(q))
+    p, q = (1,) * (n - len(p)) + tuple(p), (1,) * (n - len(q)) + tuple(q)
+    out = []
+    for x, y in zip(p, q):
+        if x != y and x != 1 and y != 1:
+            return None
+        out.append(y if x == 1 else x)
+    return tuple(out)
+
+
 def _binary(opname, fn, out_bool=False):
     def op(a, b):
         like = a if isinstance(a, Tensor) else b
@@ -549,7 +572,12 @@ def _binary(opname, fn, out_bool=False):
                     x, y = x.to(dt), y.to(dt)
                 fn(x, y, out=out)
             run._mimir_out = run_out
-        return _node(run, (a, b), {}, opname, attrs={"kind": "binary"})
+        # the result type of an elementwise op of two tensors is their broadcast shape in the common
+        # dtype (comparisons: bool); shapes that do not broadcast go through the inference and come
+        # back as a sticky error
+        shape = _broadcast(a.shape, b.shape)
+        known = None if shape is None else (shape, torch.bool if opname in ("less", "equal") else dt)
+        return _node(run, (a, b), {}, opname, attrs={"kind": "binary"}, known=known)
     op.__name__ = opname
     return op
 
@@ -574,7 +602,7 @@ equal = _binary("equal", torch.eq)
 mod = _binary("mod", torch.remainder)
 
 
-def _unary(opname, fn, native_mode=None):
+def _unary(opname, fn, native_mode=None, same_type=True):
     """An elementwise op of one tensor; ``native_mode`` names the activation kernel that serves
     bf16 CUDA tensors (forward and backward) instead of the PyTorch op."""
     def op(x: Tensor, *args, **kw):
@@ -587,7 +615,10 @@ def _unary(opname, fn, native_mode=None):
             def run_out(v, out):
                 fn(v, out=out)
             run._mimir_out = run_out
-        return _node(run, (x,), {}, opname, attrs={"kind": "unary"})
+        # an elementwise op of a floating tensor keeps its shape and dtype: no inference needed
+        known = (x.shape, x.dtype) if same_type and isinstance(x, Tensor) and x._err is None and x.dtype.is_floating_point \
+            and not args and not kw else None
+        return _node(run, (x,), {}, opname, attrs={"kind": "unary"}, known=known)
     op.__name__ = opname
     return op
 
@@ -613,7 +644,7 @@ log1p = _unary("log1p", torch.log1p)
 expm1 = _unary("expm1", torch.expm1)
 lgamma = _unary("lgamma", torch.lgamma)
 digamma = _unary("digamma", torch.digamma)
-logical_not = _unary("logical_not", torch.logical_not)
+logical_not = _unary("logical_not", torch.logical_not, same_type=False)
 silu = _unary("silu", torch.nn.functional.silu, "silu")
 softplus = _unary("softplus", torch.nn.functional.softplus)
 
@@ -921,8 +952,16 @@ def matmul_t(x, w, bias=None):
         from ..ops.quant import qmatmul_t
         return _node(lambda v: qmatmul_t(v, w), (x,), {}, "qmatmul")
     args = (x, w) + ((bias,) if bias is not None else ())
+    # the plain case has a plain result type; anything else (a mismatch, mixed dtypes) goes through
+    # the inference, which turns it into a sticky error or a promotion
+    known = None
+    if isinstance(x, Tensor) and isinstance(w, Tensor) and x._err is None and w._err is None and len(w.shape) == 2 \
+            and len(x.shape) >= 1 and x.shape[-1] == w.shape[1] and x.dtype == w.dtype and x.dtype.is_floating_point \
+            and (bias is None or (isinstance(bias, Tensor) and bias._err is None and tuple(bias.shape) == (w.shape[0],)
+                                  and bias.dtype == x.dtype)):
+        known = (tuple(x.shape[:-1]) + (w.shape[0],), x.dtype)
     return _node(_linear_run(0, bias is not None, False), args, {}, "linear",
-                 attrs={"bias": bias is not None, "act": 0, "residual": False})
+                 attrs={"bias": bias is not None, "act": 0, "residual": False}, known=known)
 
 
 def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
