@@ -273,6 +273,30 @@ MIM_API int mimir_mim_tensor(void* h, int i, const char** name, int* name_len, i
   return 0;
 }
 
+// The whole tensor table in one call (a file of 20 000 tensors is indexed in a millisecond instead of
+// 20 000 calls): meta[i * 12 + {0: dtype, 1: rank, 2..9: dims, 10: absolute file offset, 11: bytes}],
+// name_end[i] = end of name i in the concatenated `names` (name i starts where name i - 1 ends).
+// With meta == nullptr returns the number of bytes `names` needs.
+MIM_API long long mimir_mim_table(void* h, uint64_t* meta, uint32_t* name_end, char* names, long long names_cap) {
+  MimFile* f = static_cast<MimFile*>(h);
+  long long total = 0;
+  for (const TensorRow& t : f->tensors) total += static_cast<long long>(t.name.size());
+  if (!meta) return total;
+  if (names_cap < total) return fail("mim: name buffer too small");
+  long long pos = 0;
+  for (size_t i = 0; i < f->tensors.size(); ++i) {
+    const TensorRow& t = f->tensors[i];
+    uint64_t* m = meta + i * 12;
+    m[0] = t.dtype; m[1] = t.rank;
+    for (int d = 0; d < 8; ++d) m[2 + d] = t.dims[d];
+    m[10] = f->data_off + t.off; m[11] = t.len;
+    memcpy(names + pos, t.name.data(), t.name.size());
+    pos += static_cast<long long>(t.name.size());
+    name_end[i] = static_cast<uint32_t>(pos);
+  }
+  return total;
+}
+
 MIM_API int mimir_mim_section(void* h, int i, int* kind, int* flags, uint64_t* off, uint64_t* len,
                               uint8_t* hash32) {
   MimFile* f = static_cast<MimFile*>(h);

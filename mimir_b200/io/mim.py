@@ -68,6 +68,8 @@ def _lib():
         lib.mimir_mim_tensor.argtypes = [vp, c.c_int, c.POINTER(c.c_char_p), c.POINTER(c.c_int),
                                          c.POINTER(c.c_int), c.POINTER(c.c_int), c.POINTER(c.c_uint64),
                                          c.POINTER(c.c_uint64), c.POINTER(c.c_uint64)]
+        lib.mimir_mim_table.argtypes = [vp, vp, vp, c.c_char_p, c.c_longlong]
+        lib.mimir_mim_table.restype = c.c_longlong
         lib.mimir_mim_section.argtypes = [vp, c.c_int, c.POINTER(c.c_int), c.POINTER(c.c_int),
                                           c.POINTER(c.c_uint64), c.POINTER(c.c_uint64), c.c_char_p]
         lib.mimir_mim_verify.argtypes = [vp]
@@ -107,29 +109,47 @@ class Model:
         self._np = np.frombuffer(self._buf, dtype=np.uint8)
         self._index = {}
         self._table_order = []        # tensor names in table order: graph values refer to tensors by this index
-        name, nl, dt, rank = ctypes.c_char_p(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-        dims = (ctypes.c_uint64 * 8)()
         off, nb = ctypes.c_uint64(), ctypes.c_uint64()
-        for i in range(nt):
-            _check(lib.mimir_mim_tensor(handle, i, ctypes.byref(name), ctypes.byref(nl), ctypes.byref(dt),
-                                        ctypes.byref(rank), dims, ctypes.byref(off), ctypes.byref(nb)))
-            nm = ctypes.string_at(name, nl.value).decode("utf-8")
-            shape = tuple(dims[d] for d in range(rank.value))
-            count = math.prod(shape)
-            if dt.value in _TORCH:
-                want = count * torch.empty((), dtype=_TORCH[dt.value]).element_size()
-            elif dt.value in QUANT_BLOCK:
-                per, size = QUANT_BLOCK[dt.value]
-                want = count // per * size if count % per == 0 else -1
-            else:
-                want = nb.value       # a dtype this reader does not decode: refused when it is asked for
-            if want != nb.value or off.value + nb.value > size_total:
+        if nt:
+            # the whole table in one call, checked with array arithmetic: a file of 20 000 tensors opens in milliseconds
+            need = lib.mimir_mim_table(handle, None, None, None, 0)
+            meta = np.zeros((nt, 12), dtype=np.uint64)
+            ends = np.zeros(nt, dtype=np.uint32)
+            blob = ctypes.create_string_buffer(max(int(need), 1))
+            if lib.mimir_mim_table(handle, meta.ctypes.data, ends.ctypes.data, blob, int(need)) < 0:
+                _check(-1)
+            raw = blob.raw[:need]
+            dts, ranks = meta[:, 0].astype(np.int64), meta[:, 1].astype(np.int64)
+            dims = meta[:, 2:10].astype(np.int64)
+            live = np.arange(8)[None, :] < ranks[:, None]
+            counts = np.where(live, dims, 1).prod(1)
+            want = meta[:, 11].astype(np.int64).copy()          # dtypes this reader does not decode: refused when asked for
+            for code, tdt in _TORCH.items():
+                sel = dts == code
+                if sel.any():
+                    want[sel] = counts[sel] * torch.empty((), dtype=tdt).element_size()
+            for code, (per, bsize) in QUANT_BLOCK.items():
+                sel = dts == code
+                if sel.any():
+                    want[sel] = np.where(counts[sel] % per == 0, counts[sel] // per * bsize, -1)
+            offs, lens = meta[:, 10].astype(np.int64), meta[:, 11].astype(np.int64)
+            bad = np.nonzero((want != lens) | (offs + lens > size_total) | (offs < 0) | (lens < 0))[0]
+            starts = np.concatenate([[0], ends[:-1]]).tolist()
+            ends_l, dts_l, ranks_l, dims_l, offs_l, lens_l = ends.tolist(), dts.tolist(), ranks.tolist(), dims.tolist(), offs.tolist(), lens.tolist()
+            if bad.size:
+                i = int(bad[0])
+                nm = raw[starts[i]:ends_l[i]].decode("utf-8", "replace")
                 lib.mimir_mim_close(handle)
                 self._h = None
-                raise MimError(f"tensor {nm!r}: {nb.value} bytes at offset {off.value} for shape {list(shape)} "
-                               f"of dtype code {dt.value}")
-            self._index[nm] = (dt.value, shape, off.value, nb.value)
-            self._table_order.append(nm)
+                raise MimError(f"tensor {nm!r}: {lens_l[i]} bytes at offset {offs_l[i]} for shape {dims_l[i][:ranks_l[i]]} "
+                               f"of dtype code {dts_l[i]}")
+            text = raw.decode("utf-8")
+            if len(text) == len(raw):                             # ASCII names: byte offsets are character offsets
+                order = [text[a:b] for a, b in zip(starts, ends_l)]
+            else:
+                order = [raw[a:b].decode("utf-8") for a, b in zip(starts, ends_l)]
+            self._table_order = order
+            self._index = {nm: (dts_l[i], tuple(dims_l[i][:ranks_l[i]]), offs_l[i], lens_l[i]) for i, nm in enumerate(order)}
         self.sections = []
         kind, flags = ctypes.c_int(), ctypes.c_int()
         h32 = ctypes.create_string_buffer(32)

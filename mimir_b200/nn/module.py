@@ -279,11 +279,30 @@ class _BatchNorm(Module):
                 return T.core._error_tensor(T.ErrShape(
                     f"batch norm in training needs more than one value per channel, got {shape}"))
             xf = T.cast(x, torch.float32) if x.dtype != torch.float32 else x
+            m = self.momentum
+            if x._sharding is None:
+                # one fused normalisation (and one fused backward) instead of eight elementwise passes;
+                # the batch statistics for the running averages come from one more pass without autograd
+                eps, dt = self.eps, x.dtype
+
+                def bn(v, w, b):
+                    return torch.nn.functional.batch_norm(v, None, None, w.to(v.dtype), b.to(v.dtype), True, 0.0, eps).to(dt)
+
+                def stats(v):
+                    var, mean = torch.var_mean(v.detach(), dim=axes, unbiased=False)
+                    return torch.stack([mean, var])
+                y = T.core._node(bn, (xf, self.weight.value(), self.bias.value()), {}, "batch_norm", known=(shape, x.dtype))
+                mv = T.detach(T.core._node(stats, (xf,), {}, "batch_stats", known=((2, c), torch.float32)))
+                new_mean = self.running_mean.value() * (1 - m) + mv[0] * m
+                new_var = self.running_var.value() * (1 - m) + mv[1] * (m * n / (n - 1))
+                self.running_mean.set(new_mean)
+                self.running_var.set(new_var)
+                return T.with_effects(y, new_mean, new_var)
+            # on a device mesh the statistics are built from reductions the partitioner can split
             mean = T.mean(xf, dim=axes)
             d = xf - per(mean)
             var = T.mean(d * d, dim=axes)
             y = d / per(T.sqrt(var + self.eps))
-            m = self.momentum
             new_mean = self.running_mean.value() * (1 - m) + T.detach(mean) * m
             new_var = self.running_var.value() * (1 - m) + T.detach(var) * (m * n / (n - 1))
             self.running_mean.set(new_mean)

@@ -179,6 +179,8 @@ class Optimizer:
             factor *= min(1.0, self.clip_norm / (norm + 1e-6))
         from ..tensor.autograd import flush_lazy
         flush_lazy()
+        if self.rule in (_adam, _adamw) and self._foreach_adam(factor):
+            return
         with torch.no_grad():
             for p, st in zip(self.params, self.state):
                 if p._grad is None or not p.trainable:
@@ -195,6 +197,50 @@ class Optimizer:
                     st["master"] = new_w
                 p._data.copy_(new_w.to(p.dtype))
                 p._version += 1
+
+    def _foreach_adam(self, factor: float) -> bool:
+        """Adam / AdamW over all float32 / float64 parameters at once, in place: the same update as
+        the rule (optim.go:455-520), as seven multi-tensor operations instead of a dozen temporaries
+        per parameter.  False when some parameter needs the general path (half precision, master
+        weights, mixed devices)."""
+        ws, gs, ms, vs, ps = [], [], [], [], []
+        for p, st in zip(self.params, self.state):
+            if p._grad is None or not p.trainable:
+                continue
+            w, g = p._data, p._grad
+            if w.dtype not in (torch.float32, torch.float64) or g.dtype != w.dtype or g.device != w.device or "master" in st:
+                return False
+            ws.append(w)
+            gs.append(g)
+            ps.append((p, st))
+        if not ws:
+            return True
+        for (p, st), w in zip(ps, ws):
+            if "exp_avg" not in st:
+                st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(w), torch.zeros_like(w)
+            ms.append(st["exp_avg"])
+            vs.append(st["exp_avg_sq"])
+        h, t, lr = self.hyper, self.steps, self.lr
+        b1, b2, eps = h.get("beta1", 0.9), h.get("beta2", 0.999), h.get("eps", 1e-8)
+        with torch.no_grad():
+            if factor != 1.0:
+                gs = torch._foreach_mul(gs, factor)
+            if self.rule is _adamw:
+                if self.weight_decay:
+                    torch._foreach_mul_(ws, 1 - lr * self.weight_decay)
+            elif self.weight_decay:
+                gs = torch._foreach_add(gs, ws, alpha=self.weight_decay)
+            torch._foreach_mul_(ms, b1)
+            torch._foreach_add_(ms, gs, alpha=1 - b1)
+            torch._foreach_mul_(vs, b2)
+            torch._foreach_addcmul_(vs, gs, gs, value=1 - b2)
+            den = torch._foreach_sqrt(vs)
+            torch._foreach_div_(den, math.sqrt(1 - b2 ** t))
+            torch._foreach_add_(den, eps)
+            torch._foreach_addcdiv_(ws, ms, den, value=-(lr / (1 - b1 ** t)))
+        for p, _ in ps:
+            p._version += 1
+        return True
 
     # -- checkpointing
     def snapshot(self) -> dict:

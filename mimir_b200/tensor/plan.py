@@ -242,6 +242,9 @@ def _fn_key(fn):
             cells.append(("tensor", id(v)))
         elif isinstance(v, (list, tuple)) and all(isinstance(x, (int, float, bool, str, type(None))) for x in v):
             cells.append(tuple(v))          # a list of plain constants (split sizes, axes)
+        elif isinstance(v, dict) and all(isinstance(k, str) and isinstance(x, (int, float, bool, str, type(None)))
+                                         for k, x in v.items()):
+            cells.append(tuple(sorted(v.items())))          # keyword constants of an elementwise op ({} most of the time)
         elif isinstance(v, (Tensor, list, dict, set)):
             return None
         elif callable(v) and hasattr(v, "__code__"):
