@@ -204,6 +204,9 @@ struct File {
   std::vector<int64_t> offsets;    // byte arrays: count + 1
   std::vector<uint8_t> nulls;      // count, 1 = null
   int64_t r_null_count = 0;
+  // destinations of a fixed-width decode given by the caller (else the vectors above)
+  uint8_t* ext_values = nullptr;
+  uint8_t* ext_nulls = nullptr;
   // scratch
   std::vector<uint8_t> page, dict_bytes;
   std::vector<int64_t> dict_offsets;
@@ -728,6 +731,8 @@ struct Decoder {
   int64_t dict_count = 0;
   int64_t filled = 0;    // rows decoded so far
   std::vector<int64_t> tmp64, tmp64b;
+  uint8_t* out = nullptr;      // fixed-width values: rows x width
+  uint8_t* nul = nullptr;      // rows, 1 = null
 
   Decoder(File& f_, const Column& c, const Chunk& k, int64_t r)
       : f(f_), col(c), ch(k), rows(r), width(width_of(c.type, c.type_length)), bytes_like(c.type == P_BYTE_ARRAY) {}
@@ -738,12 +743,18 @@ struct Decoder {
     if (rows < 0 || rows > (int64_t{1} << 31) || rows > (int64_t{1} << 24) + ch.total_compressed * 4096)
       PQ_FAIL(kFormat, "row group declares more rows than its bytes could hold");
     try {
-      f.nulls.assign(rows, 0);
+      if (f.ext_nulls) { nul = f.ext_nulls; memset(nul, 0, static_cast<size_t>(rows)); }
+      else { f.nulls.assign(rows, 0); nul = f.nulls.data(); }
       if (bytes_like) {
         f.offsets.assign(rows + 1, 0);
         f.values.clear();
+      } else if (f.ext_values) {
+        out = f.ext_values;
+        memset(out, 0, static_cast<size_t>(rows) * width);
+        f.offsets.clear();
       } else {
         f.values.assign(static_cast<size_t>(rows) * width, 0);
+        out = f.values.data();
         f.offsets.clear();
       }
     } catch (const std::bad_alloc&) {
@@ -799,7 +810,7 @@ struct Decoder {
       for (int64_t k = 0; k < n; ++k) {
         const int64_t row = filled + k;
         if (defined && !defined[k]) {
-          f.nulls[row] = 1;
+          nul[row] = 1;
           ++f.r_null_count;
           if (bytes_like) f.offsets[row + 1] = static_cast<int64_t>(f.values.size());
           continue;
@@ -815,11 +826,11 @@ struct Decoder {
         });
       } else if (col.type == P_BOOLEAN) {
         const uint8_t* q = c.take((present + 7) / 8);
-        for_rows([&](int64_t row, int64_t v) { f.values[row] = (q[v >> 3] >> (v & 7)) & 1; });
+        for_rows([&](int64_t row, int64_t v) { out[row] = (q[v >> 3] >> (v & 7)) & 1; });
       } else {
         const uint8_t* q = c.take(static_cast<size_t>(present) * width);
-        if (!defined) memcpy(f.values.data() + static_cast<size_t>(filled) * width, q, static_cast<size_t>(present) * width);
-        else for_rows([&](int64_t row, int64_t v) { memcpy(f.values.data() + row * width, q + v * width, width); });
+        if (!defined) memcpy(out + static_cast<size_t>(filled) * width, q, static_cast<size_t>(present) * width);
+        else for_rows([&](int64_t row, int64_t v) { memcpy(out + row * width, q + v * width, width); });
       }
     } else if (enc == 2 || enc == 8) {   // dictionary indices
       if (!have_dict) PQ_FAIL(kFormat, "dictionary-encoded page without a dictionary");
@@ -837,7 +848,7 @@ struct Decoder {
         });
       } else {
         for_rows([&](int64_t row, int64_t v) {
-          memcpy(f.values.data() + row * width, f.dict_bytes.data() + static_cast<size_t>(f.idx[v]) * width, width);
+          memcpy(out + row * width, f.dict_bytes.data() + static_cast<size_t>(f.idx[v]) * width, width);
         });
       }
     } else if (enc == 3) {   // RLE booleans: 4-byte length, then runs of width 1
@@ -848,15 +859,15 @@ struct Decoder {
       f.idx.resize(present);
       Hybrid h{sub, 1};
       h.read(f.idx.data(), present);
-      for_rows([&](int64_t row, int64_t v) { f.values[row] = static_cast<uint8_t>(f.idx[v]); });
+      for_rows([&](int64_t row, int64_t v) { out[row] = static_cast<uint8_t>(f.idx[v]); });
     } else if (enc == 5) {   // DELTA_BINARY_PACKED
       if (col.type != P_INT32 && col.type != P_INT64) PQ_FAIL(kUnsupported, "DELTA_BINARY_PACKED values of a column that is not an integer");
       delta_decode(c, tmp64, present);
       if (static_cast<int64_t>(tmp64.size()) != present) PQ_FAIL(kFormat, "delta stream with a different count than the page");
       if (col.type == P_INT32)
-        for_rows([&](int64_t row, int64_t v) { const int32_t x = static_cast<int32_t>(tmp64[v]); memcpy(f.values.data() + row * 4, &x, 4); });
+        for_rows([&](int64_t row, int64_t v) { const int32_t x = static_cast<int32_t>(tmp64[v]); memcpy(out + row * 4, &x, 4); });
       else
-        for_rows([&](int64_t row, int64_t v) { memcpy(f.values.data() + row * 8, &tmp64[v], 8); });
+        for_rows([&](int64_t row, int64_t v) { memcpy(out + row * 8, &tmp64[v], 8); });
     } else if (enc == 6) {   // DELTA_LENGTH_BYTE_ARRAY
       if (!bytes_like) PQ_FAIL(kUnsupported, "DELTA_LENGTH_BYTE_ARRAY values of a column that is not BYTE_ARRAY");
       delta_decode(c, tmp64, present);
@@ -881,7 +892,7 @@ struct Decoder {
         if (bytes_like) put_bytes(row, reinterpret_cast<const uint8_t*>(cur.data()), cur.size());
         else {
           if (static_cast<int>(cur.size()) != width) PQ_FAIL(kFormat, "fixed-length value of another length");
-          memcpy(f.values.data() + row * width, cur.data(), width);
+          memcpy(out + row * width, cur.data(), width);
         }
         prev.swap(cur);
       });
@@ -889,7 +900,7 @@ struct Decoder {
       if (bytes_like || col.type == P_BOOLEAN) PQ_FAIL(kUnsupported, "BYTE_STREAM_SPLIT values of a column without a fixed width");
       const uint8_t* q = c.take(static_cast<size_t>(present) * width);
       for_rows([&](int64_t row, int64_t v) {
-        uint8_t* d = f.values.data() + row * width;
+        uint8_t* d = out + row * width;
         for (int b = 0; b < width; ++b) d[b] = q[static_cast<size_t>(b) * present + v];
       });
     } else {
@@ -1114,6 +1125,30 @@ MIMIR_API int mimir_pq_decode(void* h, int group, int column) {
     Decoder d(*f, c, k, f->groups[group].rows);
     d.run();
   });
+}
+
+// Decodes a fixed-width column straight into the caller's memory: `values` holds rows x width bytes
+// (booleans one byte each), `nulls` rows bytes (may be null for a required column: then nulls are not
+// reported).  Returns the status; *null_count gets the number of nulls.
+MIMIR_API int mimir_pq_decode_into(void* h, int group, int column, void* values, long long value_bytes,
+                                   unsigned char* nulls, long long* null_count) {
+  File* f = static_cast<File*>(h);
+  const int rc = guard(f, [&] {
+    if (group < 0 || group >= static_cast<int>(f->groups.size())) PQ_FAIL(kArgument, "no such row group");
+    if (column < 0 || column >= static_cast<int>(f->cols.size())) PQ_FAIL(kArgument, "no such column");
+    const Column& c = f->cols[column];
+    const int w = width_of(c.type, c.type_length);
+    if (c.type == P_BYTE_ARRAY || w <= 0) PQ_FAIL(kArgument, "column without a fixed width");
+    if (value_bytes != f->groups[group].rows * w) PQ_FAIL(kArgument, "destination of another size than the column chunk");
+    f->ext_values = static_cast<uint8_t*>(values);
+    f->ext_nulls = nulls;
+  });
+  if (rc != kOk) return rc;
+  const int rc2 = mimir_pq_decode(h, group, column);
+  f->ext_values = nullptr;
+  f->ext_nulls = nullptr;
+  *null_count = f->r_null_count;
+  return rc2;
 }
 
 // Pointers into the handle's buffers, valid until the next decode or close.

@@ -76,6 +76,7 @@ def _bind(lib):
     lib.mimir_pq_result.argtypes = [c.c_void_p, c.POINTER(c.c_int), c.POINTER(c.c_longlong), c.POINTER(c.c_void_p),
                                     c.POINTER(c.c_longlong), c.POINTER(c.c_void_p), c.POINTER(c.c_void_p),
                                     c.POINTER(c.c_longlong)]
+    lib.mimir_pq_decode_into.argtypes = [c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_longlong, c.c_void_p, c.POINTER(c.c_longlong)]
     lib._pq_bound = True
     return lib
 
@@ -177,6 +178,9 @@ class File:
         FIXED_LEN_BYTE_ARRAY (nulls hold ``None``); ``nulls`` is a bool tensor, or ``None`` for a
         required column."""
         ci = self._index[column] if isinstance(column, str) else int(column)
+        col = self._cols[ci] if 0 <= ci < len(self._cols) else None
+        if col is not None and col.type in _NP and not col.nested:
+            return self._read_fixed(int(group), ci, col)
         rc = self._lib.mimir_pq_decode(self._h, int(group), ci)
         if rc:
             _raise(rc, (self._lib.mimir_pq_last_error(self._h) or b"").decode("utf-8", "replace"))
@@ -206,6 +210,23 @@ class File:
             mask = null_t.tolist()
             items = [None if m else v for v, m in zip(items, mask)]
         return items, null_t
+
+    def _read_fixed(self, group: int, ci: int, col, out: torch.Tensor | None = None):
+        """A numeric / boolean column chunk decoded straight into a tensor (``out``: a contiguous
+        destination of the chunk's length and the column's dtype)."""
+        n = self.row_group_rows(group)
+        np_dt = _NP[col.type]
+        if out is None:
+            out = torch.from_numpy(np.empty(n, dtype=np_dt))
+        nulls = torch.empty(n, dtype=torch.uint8) if col.nullable else None
+        nc = ctypes.c_longlong()
+        rc = self._lib.mimir_pq_decode_into(self._h, group, ci, out.data_ptr(), n * out.element_size(),
+                                            nulls.data_ptr() if nulls is not None else None, ctypes.byref(nc))
+        if rc:
+            _raise(rc, (self._lib.mimir_pq_last_error(self._h) or b"").decode("utf-8", "replace"))
+        if nulls is not None:
+            nulls = nulls.bool() if nc.value else torch.zeros(n, dtype=torch.bool)
+        return (out.bool() if col.type == BOOLEAN else out), nulls
 
     def read(self, columns=None, row_group: int | None = None) -> dict:
         """Column name -> tensor (numeric / bool; nulls of float columns become NaN) or list
@@ -238,7 +259,26 @@ class File:
             yield self.read(columns, g)
 
     def matrix(self, features, label=None, row_group: int | None = None, dtype=torch.float32):
-        cols = self.read(list(features) + ([label] if label else []), row_group)
+        """``(X [rows, features], y)`` of one row group or the whole file.  Feature columns whose file
+        type already is ``dtype`` and that hold no nulls are decoded straight into the rows of one
+        ``[features, rows]`` buffer, of which ``X`` is the transposed view."""
+        features = list(features)
+        if row_group is not None:
+            fast = {torch.float32: FLOAT, torch.float64: DOUBLE, torch.int32: INT32, torch.int64: INT64}.get(dtype)
+            infos = [self._cols[self._index[f]] for f in features]
+            if fast is not None and all(c.type == fast and not c.nested for c in infos):
+                n = self.row_group_rows(row_group)
+                buf = torch.empty(len(features), n, dtype=dtype)
+                for k, f in enumerate(features):
+                    _, nulls = self._read_fixed(row_group, self._index[f], infos[k], buf[k])
+                    if nulls is not None and bool(nulls.any()):
+                        if not dtype.is_floating_point:
+                            break
+                        buf[k].masked_fill_(nulls, float("nan"))
+                else:
+                    y = self.read([label], row_group)[label] if label else None
+                    return buf.t(), y
+        cols = self.read(features + ([label] if label else []), row_group)
         X = torch.stack([cols[f].to(dtype) for f in features], 1)
         return X, (cols[label] if label else None)
 
