@@ -145,9 +145,9 @@ class CPUDecoder:
         self.len = 0
 
     def _rope(self, x: torch.Tensor, pos: int) -> torch.Tensor:
-        """``x [B, H, D]`` rotated for position ``pos``."""
+        """``x [B, T, H, D]`` rotated for positions ``pos .. pos + T - 1``."""
         d = self.cfg.rope_dim
-        ang = pos * self.inv_freq
+        ang = (torch.arange(pos, pos + x.shape[1], dtype=torch.float32)[:, None] * self.inv_freq[None])[None, :, None, :]
         cos, sin = ang.cos(), ang.sin()
         rot, rest = x[..., :d], x[..., d:]
         if self.interleaved:
@@ -161,27 +161,38 @@ class CPUDecoder:
     def _norm(self, x: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
         return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * g
 
-    @torch.no_grad()
-    def step(self, tokens: torch.Tensor) -> torch.Tensor:
-        """One token per sequence: ``tokens [B]`` -> logits ``[B, vocab]``; the cache grows by one.
-        The small tensor ops between the products run on the calling thread: PyTorch's own thread
-        pool would compete with the product workers for the same cores."""
+    def _own_thread(self, fn, *a):
+        """Runs ``fn`` with PyTorch's thread pool set to one thread: the small tensor ops between the
+        products run on the calling thread, because PyTorch's workers would compete with the product
+        workers for the same cores."""
         if not self.own_threads:
-            return self._step(tokens)
+            return fn(*a)
         had = torch.get_num_threads()
         torch.set_num_threads(1)
         try:
-            return self._step(tokens)
+            return fn(*a)
         finally:
             torch.set_num_threads(had)
 
-    def _step(self, tokens: torch.Tensor) -> torch.Tensor:
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """One token per sequence: ``tokens [B]`` -> logits ``[B, vocab]``; the cache grows by one."""
+        return self._own_thread(self._forward, tokens.reshape(self.batch, 1))
+
+    def _forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        """``tokens [B, T]`` at positions ``len .. len + T - 1`` -> logits of the last one ``[B, vocab]``.
+        The products see ``B * T`` activation rows, eight per pass over a weight matrix."""
         c, B, pos = self.cfg, self.batch, self.len
-        if pos >= self.cap:
-            raise IndexError(f"KV cache overflow: {pos} + 1 > {self.cap}")
+        Tn = tokens.shape[1]
+        if pos + Tn > self.cap:
+            raise IndexError(f"KV cache overflow: {pos} + {Tn} > {self.cap}")
         H, Hk, D = c.heads, c.kv_heads, c.head_dim
-        x = self.embed.rows(tokens.reshape(-1).long())
+        x = self.embed.rows(tokens.reshape(-1).long())                       # [B * T, embed]
         scale = 1.0 / math.sqrt(D)
+        mask = None
+        if Tn > 1:
+            i, j = torch.arange(Tn)[:, None], torch.arange(pos + Tn)[None]
+            mask = torch.zeros(Tn, pos + Tn).masked_fill(j > i + pos, float("-inf"))
         for li, l in enumerate(self.layers):
             h = self._norm(x, l["attn_norm"])
             if l["qkv"] is not None:
@@ -191,14 +202,17 @@ class CPUDecoder:
             if l["qkv_bias"] is not None:
                 qkv = qkv + l["qkv_bias"]
             q, k, v = qkv.split([H * D, Hk * D, Hk * D], 1)
-            q = self._rope(q.view(B, H, D), pos)
-            k = self._rope(k.view(B, Hk, D), pos)
-            self.kc[li, :, :, pos] = k
-            self.vc[li, :, :, pos] = v.view(B, Hk, D)
-            keys, vals = self.kc[li, :, :, : pos + 1], self.vc[li, :, :, : pos + 1]        # [B, Hk, T, D]
-            qg = q.view(B, Hk, H // Hk, D)
-            att = torch.softmax(torch.matmul(qg, keys.transpose(-1, -2)) * scale, -1)          # [B, Hk, G, T]
-            o = torch.matmul(att, vals).reshape(B, H * D)
+            q = self._rope(q.view(B, Tn, H, D), pos)
+            k = self._rope(k.view(B, Tn, Hk, D), pos)
+            self.kc[li, :, :, pos: pos + Tn] = k.transpose(1, 2)
+            self.vc[li, :, :, pos: pos + Tn] = v.view(B, Tn, Hk, D).transpose(1, 2)
+            keys, vals = self.kc[li, :, :, : pos + Tn], self.vc[li, :, :, : pos + Tn]     # [B, Hk, S, D]
+            qg = q.permute(0, 2, 1, 3).reshape(B, Hk, (H // Hk) * Tn, D)                # the heads of a group side by side
+            att = torch.matmul(qg, keys.transpose(-1, -2)) * scale                       # [B, Hk, G * T, S]
+            if mask is not None:
+                att = att.view(B, Hk, H // Hk, Tn, pos + Tn) + mask
+            att = torch.softmax(att, -1).view(B, Hk, (H // Hk) * Tn, pos + Tn)
+            o = torch.matmul(att, vals).view(B, H, Tn, D).permute(0, 2, 1, 3).reshape(B * Tn, H * D)
             x = x + l["o"].mul(o, self.mode)
             h = self._norm(x, l["ffn_norm"])
             if l["gate_up"] is not None:
@@ -206,15 +220,17 @@ class CPUDecoder:
             else:
                 g, u = l["gate"].mul(h, self.mode), l["up"].mul(h, self.mode)
             x = x + l["down"].mul(torch.nn.functional.silu(g) * u, self.mode)
-        self.len = pos + 1
-        return self.head.mul(self._norm(x, self.out_norm), self.mode)
+        self.len = pos + Tn
+        last = x.view(B, Tn, -1)[:, -1]
+        return self.head.mul(self._norm(last, self.out_norm), self.mode)
 
     @torch.no_grad()
-    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
-        """Feeds ``prompt [B, T]`` token by token; returns the logits after the last one."""
+    def prefill(self, prompt: torch.Tensor, chunk: int = 32) -> torch.Tensor:
+        """Feeds ``prompt [B, T]`` in chunks of ``chunk`` positions (each weight matrix is read once per
+        eight activation rows, not once per token); returns the logits after the last token."""
         logits = None
-        for t in range(prompt.shape[1]):
-            logits = self.step(prompt[:, t])
+        for t0 in range(0, prompt.shape[1], chunk):
+            logits = self._own_thread(self._forward, prompt[:, t0: t0 + chunk])
         return logits
 
     @torch.no_grad()

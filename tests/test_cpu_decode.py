@@ -31,7 +31,10 @@ def test_float_weights_exact_mode_equals_the_model_with_caches(arch):
         assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), t
     assert dec.len == 7
     dec.reset()
-    assert torch.allclose(dec.prefill(toks), want, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(dec.prefill(toks), want, atol=2e-4, rtol=1e-4)              # all positions in one pass
+    dec.reset()
+    assert torch.allclose(dec.prefill(toks, chunk=3), want, atol=2e-4, rtol=1e-4)     # chunks of 3, 3 and 1 positions
+    assert dec.len == 7
 
 
 def _quantized_file(tmp_path, m):
