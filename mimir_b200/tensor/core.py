@@ -181,9 +181,17 @@ class Tensor:
         return getattr(self, "_sharding", None)
 
     def donate(self) -> "Tensor":
-        """Marks a realized leaf whose memory the next schedule may reuse
-        (internal/sched/donate.go:49); using it afterwards is ErrDonated."""
-        self._donated = True
+        """Marks a realized tensor whose owner is done with it once the NEXT schedule that reads it has
+        run, as a batch of inputs that a training step reads once (tensor.Donate, tensor/tensor.go:420-452;
+        internal/sched/donate.go:26-60).  That schedule may read it like any other tensor; after its
+        last reader the memory goes back to the pool (so later instructions of the same schedule take it
+        for their results), and from the moment the schedule runs the tensor is stale: reading it, or
+        computing a tensor built from it, raises ``ErrDonated``.  Read everything you need of it in
+        that one schedule, or donate a copy.  A schedule refused before it starts (the memory budget)
+        leaves the tensor alone.  A tensor that is not computed yet is left alone, and so is every
+        tensor when operations are evaluated as they are built (``MIMIR_EAGER=1``)."""
+        if self._val is not None and self._fn is None and not _EAGER:
+            self._donated = True
         return self
 
     def to(self, device: Device) -> "Tensor":
@@ -378,8 +386,11 @@ def _flatten(args):
             yield a
 
 
+_TAKEN = 2      # value of ``Tensor._donated`` once a schedule has consumed the donation
+
+
 def _check_leaf(t: Tensor):
-    if t._donated:
+    if t._donated == _TAKEN:
         raise E.ErrDonated("tensor was donated to an earlier schedule")
     if _mem._VERSIONS:
         _mem.check_current(t)
@@ -413,7 +424,14 @@ def evaluate(roots: Sequence[Tensor], memo: dict | None = None, reuse_cached: bo
     if not torch.is_grad_enabled() and not _mem.in_transform():
         dev = next((v.device for v in leaf_vals if torch.is_tensor(v)), None)
         pool = _mem.pool_for(dev) if dev is not None else None
-    outs = prog.run(leaf_vals, w.order, on_error, pool=pool, into=into)
+    # donated leaves: this schedule is their last reader; their handles are stale from here on, whether
+    # the schedule succeeds or not (it has started)
+    donated = [i for i, t in enumerate(w.leaves) if t._donated is True and id(t) not in memo]
+    for i in donated:
+        t = w.leaves[i]
+        t._donated = _TAKEN
+        t._val = None
+    outs = prog.run(leaf_vals, w.order, on_error, pool=pool, into=into, donated=donated)
     for r, v in zip(roots, outs):
         memo[id(r)] = v
     return outs

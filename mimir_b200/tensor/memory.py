@@ -16,8 +16,8 @@ the source of the write, which now lives in that memory, is current.  Versions a
 address and only for storages that were ever written over: a program that never calls
 ``realize_into`` pays one empty-dict test per leaf.
 
-**Pool** (internal/sched/memory.go:144-190): free lists of buffers keyed by (device, dtype, element
-count).  A program running without autograd takes the outputs of its elementwise instructions from
+**Pool** (internal/sched/memory.go:144-190, :252-304): free lists of buffers keyed by (device, dtype, element
+count); a buffer that no schedule has taken for 16 schedules is released.  A program running without autograd takes the outputs of its elementwise instructions from
 the pool and gives each buffer back when the last value that lives in it (the output itself or a
 view some later instruction made of it) has been dropped, most recently freed first, so a replayed
 schedule runs over the same buffers every time.  A buffer that a result takes away leaves the pool.
@@ -128,8 +128,11 @@ def check_current(t) -> None:
 class Pool:
     """Free lists of buffers keyed by (device, dtype, element count)."""
 
+    AGE_OUT = 16           # a buffer no schedule has asked for in this many schedules goes back to the allocator
+
     def __init__(self, limit_bytes: int = 1 << 30):
-        self.free: dict = {}
+        self.free: dict = {}   # key -> [(buffer, schedule it was freed in), ...], most recently freed last
+        self.clock = 0
         self.limit = limit_bytes
         self.held = 0          # bytes on the free lists
         self.obtained = 0      # bytes asked from the allocator
@@ -144,7 +147,7 @@ class Pool:
         lst = self.free.get(key)
         self.taken += 1
         if lst:
-            buf = lst.pop()
+            buf, _ = lst.pop()
             self.held -= buf.numel() * buf.element_size()
             self.reused += 1
             return buf.view(shape)
@@ -157,7 +160,23 @@ class Pool:
         if self.held + nbytes > self.limit:
             return             # over the limit: the allocator gets it back
         self.held += nbytes
-        self.free.setdefault((buf.device, buf.dtype, buf.numel()), []).append(buf.reshape(-1))
+        self.free.setdefault((buf.device, buf.dtype, buf.numel()), []).append((buf.reshape(-1), self.clock))
+
+    def tick(self) -> None:
+        """Called once per schedule: buffers freed more than ``AGE_OUT`` schedules ago are released."""
+        self.clock += 1
+        if self.clock % self.AGE_OUT or not self.free:
+            return
+        old = self.clock - self.AGE_OUT
+        for key in list(self.free):
+            lst = self.free[key]
+            keep = [(b, t) for b, t in lst if t >= old]
+            if len(keep) != len(lst):
+                self.held -= sum(b.numel() * b.element_size() for b, t in lst if t < old)
+                if keep:
+                    self.free[key] = keep
+                else:
+                    del self.free[key]
 
     def trim(self) -> None:
         self.free.clear()

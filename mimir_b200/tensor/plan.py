@@ -79,13 +79,21 @@ class Program:
             if s not in keep and s >= nleaves:
                 self.drop_after[i].append(s)
 
-    def run(self, leaf_vals, order=None, on_error=None, pool=None, into=None):
+    def run(self, leaf_vals, order=None, on_error=None, pool=None, into=None, donated=()):
         """Runs the instructions over ``leaf_vals``.  ``order`` is the node list of the graph being
         run: instructions whose executable is volatile take it from there.  ``pool`` (only without
         autograd) serves the outputs of instructions that can write into given memory; ``into`` maps
         a position in ``roots`` to the torch tensor that root is to be written into."""
         slots = list(leaf_vals) + [None] * (self.nslots - self.nleaves)
         dest = self._destinations(leaf_vals, into) if into else {}
+        # a donated leaf is dropped after its last reader; its memory goes to the pool when the tensor
+        # owns all of it (not a view, not a mapped file) and no result of this schedule lives in it
+        drop_leaf = {}
+        for s in donated:
+            if s not in self.roots:
+                drop_leaf.setdefault(self.last_use.get(s, -1), []).append(s)
+        if pool is not None:
+            pool.tick()
         owner = {} if pool is not None else None     # storage address of a pooled buffer -> [buffer, live slots]
         lives = {} if pool is not None else None     # slot -> addresses of the pooled buffers its value lives in
         for i, (fn, spec, kw, out, node_idx) in enumerate(self.instrs):
@@ -128,6 +136,11 @@ class Program:
                     lives[out] = addrs
                     for a in addrs:
                         owner[a][1] += 1
+            for s in drop_leaf.get(i, ()):
+                v, slots[s] = slots[s], None
+                if pool is not None and torch.is_tensor(v) and _sole_owner(v) and not self._lives_on(slots, v):
+                    pool.give(v)
+                del v
             for s in self.drop_after[i]:
                 slots[s] = None
                 if lives and s in lives:
@@ -146,6 +159,12 @@ class Program:
                 if a not in kept:
                     pool.give(rec[0])
         return [slots[r] for r in self.roots]
+
+    def _lives_on(self, slots, v) -> bool:
+        """True when a value still held by the running program lives in the memory of ``v`` (a view some
+        instruction made of it)."""
+        a = v.untyped_storage().data_ptr()
+        return any(x is not None and any(y == a for y in _addresses(x)) for x in slots)
 
     def _aliased_later(self, slots, dst, i) -> bool:
         """True when a value computed before instruction ``i`` lives in the memory of ``dst`` (a view an
@@ -180,6 +199,24 @@ class Program:
             if safe:
                 out[i] = dst
         return out
+
+
+def _sole_owner(v) -> bool:
+    """True when nothing but the running schedule can reach the memory of ``v``: the tensor spans its
+    whole storage, no other tensor shares that storage (a view, a detached twin the caller kept) and
+    no other Python reference to ``v`` exists besides the schedule's own (the caller's list of leaf
+    values, this frame and the probe).  Memory the tensor does not own alone is never taken."""
+    import sys
+    if v.device.type == "meta" or not v.is_contiguous() or not v.numel():
+        return False
+    st = v.untyped_storage()
+    if st.nbytes() != v.numel() * v.element_size():
+        return False
+    try:
+        shared = torch._C._storage_Use_Count(st._cdata) > 2      # the tensor and this probe
+    except Exception:  # noqa: BLE001 - without the counter, assume it is shared
+        return False
+    return not shared and sys.getrefcount(v) <= 4      # the leaf-value list, the two frames, the probe
 
 
 def _addresses(v):
@@ -290,6 +327,8 @@ class _Walk:
                 is_leaf = id(t) in memo or t._fn is None or (reuse_cached and t._val is not None)
                 if is_leaf:
                     if id(t) not in memo and t._val is None:
+                        if t._donated == 2:
+                            raise E.ErrDonated("tensor was donated to an earlier schedule")
                         raise E.ErrNilTensor("tensor has neither a value nor a producer")
                     self.index[id(t)] = ("l", len(self.leaves))
                     self.leaves.append(t)
@@ -387,7 +426,7 @@ def _structural_key(w: _Walk, roots):
     parts = []
     try:
         for t in w.leaves:
-            parts.append(("L", tuple(t.shape), t.dtype, repr(t.device)))
+            parts.append(("L", tuple(t.shape), t.dtype, repr(t.device), t._donated is True))   # a step that donates its batch has a program of its own
         for t in w.order:
             fk = _fn_key(t._fn)
             if fk is None:

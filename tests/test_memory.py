@@ -161,3 +161,62 @@ def test_broadcast_operands_and_mixed_dtypes_take_the_pool_path_correctly():
         assert got.dtype == torch.float32 and torch.equal(got, want)
     small = T.tensor(torch.randn(3)) + 1                    # a Python scalar operand
     assert small.data().shape == (3,)
+
+
+def test_donated_batch_is_read_once_and_its_memory_serves_the_same_schedule():
+    memory.set_pool("cpu")
+    pool = memory.pool()
+    pool.trim()
+    w = T.tensor(torch.randn(64, 64))
+
+    def step(batch):
+        return T.sum_(T.tanh(batch * 2.0 + 1.0) * 3.0)
+
+    want = float(torch.sum(torch.tanh(torch.ones(64, 64) * 2.0 + 1.0) * 3.0))
+    kept = T.tensor(torch.ones(64, 64))
+    assert abs(step(kept).item() - want) < 1e-3
+    base = pool.stats()
+    for _ in range(3):
+        batch = T.tensor(torch.ones(64, 64)).donate()       # the tensor owns its memory: nobody else holds it
+        out = step(batch)
+        assert abs(out.item() - want) < 1e-3
+        with pytest.raises(T.ErrDonated):
+            (batch + 1.0).data()
+    after = pool.stats()
+    assert after["obtained_bytes"] == base["obtained_bytes"]        # the donated batches fed the pool: nothing new was asked for
+    assert plan.stats()["cached"] >= 2                              # the donating step has a program of its own
+    # memory somebody else can reach is never taken
+    mine = torch.ones(64, 64)
+    shared = T.from_torch(mine).donate()
+    assert abs(step(shared).item() - want) < 1e-3
+    for _ in range(4):
+        step(T.tensor(torch.zeros(64, 64))).item()
+    assert float(mine.sum()) == 64 * 64                               # still the caller's values
+    with pytest.raises(T.ErrDonated):
+        shared.data()
+    # a tensor that is not computed yet is left alone; a refused schedule leaves its batch alone
+    lazy = (w + 1.0).donate()
+    assert lazy.data().shape == (64, 64) and lazy.data().shape == (64, 64)
+    cpu = T.CPU()
+    T.set_memory_budget(cpu, 1024)
+    try:
+        b = T.tensor(torch.ones(64, 64)).donate()
+        with pytest.raises(T.ErrMemoryBudget):
+            step(b).item()
+    finally:
+        T.set_memory_budget(cpu, None)
+    assert abs(step(b).item() - want) < 1e-3                          # it was not consumed by the refused schedule
+
+
+def test_unused_buffers_age_out_of_the_pool():
+    memory.set_pool("cpu")
+    pool = memory.pool()
+    pool.trim()
+    big = T.tensor(torch.randn(256, 256))
+    (T.exp(big * 2.0) + 1.0).realize()
+    assert pool.stats()["held_bytes"] >= 256 * 256 * 4          # a temporary of that size waits for reuse
+    small = T.tensor(torch.randn(8))
+    for _ in range(2 * pool.AGE_OUT + 1):
+        (small * 2.0 + 1.0).realize()                           # schedules that never ask for it
+    assert all(k[2] != 256 * 256 for k in pool.free)           # released
+    assert pool.stats()["held_bytes"] < 256 * 256 * 4

@@ -72,8 +72,11 @@ def test_transforms_scan_record_trace_budget():
     finally:
         T.set_memory_budget(cpu, None)
     d = T.ones((2,), device=cpu).realize().donate()
-    with pytest.raises(T.ErrDonated):
+    assert (d + 1).data().tolist() == [2.0, 2.0]          # the next schedule that reads it may
+    with pytest.raises(T.ErrDonated):                     # from then on it is stale
         (d + 1).data()
+    with pytest.raises(T.ErrDonated):
+        d.data()
 
 
 def test_custom_func_and_checkpoint_gradients():
