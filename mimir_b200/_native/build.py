@@ -92,7 +92,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         return LIB
     tmp = LIB.with_suffix(".so.tmp")
     cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs),
-           "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-lpthread", "-ldl"]
+           "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC", "-lpthread", "-ldl", "-lmvec", "-lm"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

@@ -12,8 +12,8 @@
 //     x . dequant(W) and is what the int8 path is tested against.
 // Rows of W are split over a small pool of worker threads that lives as long as the library.
 // Plain C ABI; compiled by the host compiler (no CUDA in this file).
-#include <immintrin.h>
-#include <pthread.h>
+#include "cpu_pool.h"
+
 
 #include <atomic>
 #include <condition_variable>
@@ -303,75 +303,16 @@ void quantize_row(const float* x, int K, int8_t* q, float* d, float* ds, float* 
 // ---------------------------------------------------------------------------
 // worker pool
 // ---------------------------------------------------------------------------
-// Workers spin briefly on the job counter before they sleep, so the back-to-back products of a
-// decode step are picked up in well under a microsecond; after some tens of microseconds without work they block
-// on a condition variable and cost nothing.
-class Pool {
- public:
-  explicit Pool(int n) {
-    for (int i = 1; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
-  }
-  ~Pool() {
-    {
-      std::lock_guard<std::mutex> lk(m_);
-      quit_.store(true);
-    }
-    cv_.notify_all();
-    for (auto& t : workers_) t.join();
-  }
-  int size() const { return static_cast<int>(workers_.size()) + 1; }
-  // runs fn(part, parts) on every thread (the caller is part 0) and returns when all are done
-  void run(const std::function<void(int, int)>& fn) {
-    const int parts = size();
-    if (parts == 1) { fn(0, 1); return; }
-    fn_ = &fn;
-    pending_.store(parts - 1, std::memory_order_relaxed);
-    {
-      std::lock_guard<std::mutex> lk(m_);        // pairs with the sleepers' predicate check
-      epoch_.fetch_add(1, std::memory_order_release);
-    }
-    if (sleepers_.load(std::memory_order_acquire) > 0) cv_.notify_all();
-    fn(0, parts);
-    for (int spins = 0; pending_.load(std::memory_order_acquire) != 0; ++spins) {
-      if (spins < 20000) _mm_pause();
-      else std::this_thread::yield();
-    }
-  }
+}  // namespace
 
- private:
-  void loop(int id) {
-    uint64_t seen = 0;
-    for (;;) {
-      int spins = 0;
-      while (epoch_.load(std::memory_order_acquire) == seen && !quit_.load(std::memory_order_relaxed)) {
-        if (++spins < 1500) { _mm_pause(); continue; }
-        std::unique_lock<std::mutex> lk(m_);
-        sleepers_.fetch_add(1, std::memory_order_release);
-        cv_.wait(lk, [&] { return quit_.load() || epoch_.load(std::memory_order_acquire) != seen; });
-        sleepers_.fetch_sub(1, std::memory_order_release);
-      }
-      if (quit_.load(std::memory_order_relaxed)) return;
-      seen = epoch_.load(std::memory_order_acquire);
-      (*fn_)(id, size());
-      pending_.fetch_sub(1, std::memory_order_release);
-    }
-  }
-  std::vector<std::thread> workers_;
-  std::mutex m_;
-  std::condition_variable cv_;
-  const std::function<void(int, int)>* fn_ = nullptr;
-  std::atomic<int> pending_{0};
-  std::atomic<int> sleepers_{0};
-  std::atomic<uint64_t> epoch_{0};
-  std::atomic<bool> quit_{false};
-};
+namespace mimir_cpu {
 
-std::mutex g_pool_mutex;
-Pool* g_pool = nullptr;
-int g_threads = 0;
+static std::mutex g_pool_mutex;
+static Pool* g_pool = nullptr;
+static int g_threads = 0;
 
 // after fork() the child has none of the worker threads: it starts a pool of its own on first use
-void forget_pool_in_child() { g_pool = nullptr; new (&g_pool_mutex) std::mutex(); }
+static void forget_pool_in_child() { g_pool = nullptr; new (&g_pool_mutex) std::mutex(); }
 
 Pool& pool() {
   static const bool hooked = (pthread_atfork(nullptr, nullptr, forget_pool_in_child), true);
@@ -385,6 +326,22 @@ Pool& pool() {
   return *g_pool;
 }
 
+std::mutex& pool_mutex() { return g_pool_mutex; }
+
+int set_threads(int n) {
+  std::lock_guard<std::mutex> lk(g_pool_mutex);
+  const int old = g_threads;
+  g_threads = n < 0 ? 0 : n;
+  if (g_pool) { delete g_pool; g_pool = nullptr; }
+  return old;
+}
+
+}  // namespace mimir_cpu
+
+namespace {
+
+using mimir_cpu::pool;
+
 bool has_vnni() {
   static const bool ok = __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512vl") &&
                          __builtin_cpu_supports("avx512bw") && __builtin_cpu_supports("avx2");
@@ -397,13 +354,7 @@ bool has_vnni() {
 MIMIR_CPU_API int mimir_cpu_qgemv_has_int8() { return has_vnni() ? 1 : 0; }
 
 // Number of threads of the next products (0 = one per hardware thread).  Returns the previous setting.
-MIMIR_CPU_API int mimir_cpu_set_threads(int n) {
-  std::lock_guard<std::mutex> lk(g_pool_mutex);
-  const int old = g_threads;
-  g_threads = n < 0 ? 0 : n;
-  if (g_pool) { delete g_pool; g_pool = nullptr; }
-  return old;
-}
+MIMIR_CPU_API int mimir_cpu_set_threads(int n) { return mimir_cpu::set_threads(n); }
 
 // y [B][N] (fp32) = x [B][K] (fp32) . W^T, W = N rows of K values in ggml blocks of `code`.
 // mode 0: exact; 1: int8 activations; -1: int8 when the CPU has it.  scratch: B * (K + 4 * K / 32 * 4 + 64) bytes
@@ -415,8 +366,8 @@ MIMIR_CPU_API int mimir_cpu_qgemv(int code, const void* w, int N, int K, const f
   if (K <= 0 || K % vals) return -1;
   const bool int8 = mode == 1 || (mode == -1 && has_vnni());
   if (int8 && !has_vnni()) return -1;
-  std::lock_guard<std::mutex> lk(g_pool_mutex);
-  Pool& p = pool();
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& p = pool();
   const uint8_t* wb = static_cast<const uint8_t*>(w);
   // rows are handed out in chunks from a shared counter, so a thread that is held up (a busy core, a
   // hyper-thread sibling) takes fewer chunks instead of holding everyone back

@@ -636,7 +636,7 @@ def _unary(opname, fn, native_mode=None, same_type=True):
         # an elementwise op of a floating tensor keeps its shape and dtype: no inference needed
         known = (x.shape, x.dtype) if same_type and isinstance(x, Tensor) and x._err is None and x.dtype.is_floating_point \
             and not args and not kw else None
-        return _node(run, (x,), {}, opname, attrs={"kind": "unary"}, known=known)
+        return _node(run, (x,), {}, opname, attrs={"kind": "unary", "plain": not args and not kw}, known=known)
     op.__name__ = opname
     return op
 

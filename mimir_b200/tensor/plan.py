@@ -26,6 +26,7 @@ A program frees every intermediate after its last reader (the reference's pooled
 from __future__ import annotations
 
 import collections
+import os
 
 import torch
 
@@ -377,7 +378,8 @@ def _plan_fusion(w: _Walk):
                     out[id(t)] = (C._linear_run(0, a["bias"], True), tuple(lin._args) + (res,), {}, lin)
                     absorbed.add(id(lin))
                     break
-        elif op == "mul":
+        elif op == "mul" and not (getattr(t.device, "kind", "") == "cpu" and t.dtype == torch.float32):
+            # (float32 on the CPU: the elementwise fusion below takes the whole chain)
             p, q = t._args
             for act, up in ((p, q), (q, p)):
                 if isinstance(act, C.Tensor) and isinstance(up, C.Tensor) and act._opname == "silu" \
@@ -386,7 +388,107 @@ def _plan_fusion(w: _Walk):
                     out[id(t)] = (C._swiglu_run, (act._args[0], up), {}, act)
                     absorbed.add(id(act))
                     break
+    _fuse_elementwise(w, out, absorbed)
     return out, absorbed
+
+
+_MAX_CHAIN = 48       # instructions of one fused elementwise program
+_MAX_INPUTS = 16
+
+
+def _elementwise_name(t):
+    """Name of the fusable elementwise op of node ``t`` (float32 on the CPU, plain arguments), or None."""
+    from ..ops import fused_cpu as FC
+    a = t._attrs or {}
+    op = t._opname
+    if op not in FC.OPS or t.dtype != torch.float32 or getattr(t.device, "kind", "") != "cpu" or t._sharding is not None:
+        return None
+    if a.get("kind") not in ("unary", "binary"):
+        return None
+    if a.get("kind") == "unary" and not a.get("plain", op == "gelu"):
+        return None
+    if op == "gelu" and a.get("approximate") != "tanh":
+        return None
+    return op
+
+
+_FUSE_ELEMENTWISE = os.environ.get("MIMIR_FUSE", "1") not in ("0", "off", "false")
+
+
+def set_elementwise_fusion(on: bool) -> bool:
+    """Turns the fusion of elementwise chains on or off (``MIMIR_FUSE=0`` at start-up); returns the
+    previous setting.  Cached programs are dropped, since they were planned under the other setting."""
+    global _FUSE_ELEMENTWISE
+    old, _FUSE_ELEMENTWISE = _FUSE_ELEMENTWISE, bool(on)
+    clear_cache()
+    return old
+
+
+def _fuse_elementwise(w: _Walk, out, absorbed) -> None:
+    """Chains (trees) of elementwise float32 CPU ops whose intermediate values have one reader become
+    one fused program each: the root keeps its place in the schedule, the others are absorbed."""
+    if not _FUSE_ELEMENTWISE:
+        return
+    from . import core as C
+    from ..ops import fused_cpu as FC
+    clusters = {}                      # id(root) -> members in topological order
+    for t in w.order:
+        if id(t) in absorbed or id(t) in out:
+            continue
+        name = _elementwise_name(t)
+        if name is None:
+            continue
+        operands = [a for a in t._args if isinstance(a, C.Tensor)]
+        if len(operands) != len(t._args) or not operands:
+            continue
+        n = t.numel()
+        if any(a.dtype != torch.float32 or (tuple(a.shape) != tuple(t.shape) and a.numel() != 1) for a in operands):
+            continue
+        if n == 1 and any(tuple(a.shape) != tuple(t.shape) for a in operands):
+            continue
+        members = []
+        for a in operands:
+            sub = clusters.get(id(a))
+            if sub is not None and _single_reader(w, a) and tuple(a.shape) == tuple(t.shape) \
+                    and len(members) + len(sub) < _MAX_CHAIN:
+                members += [m for m in sub if all(m is not x for x in members)]
+                del clusters[id(a)]
+        clusters[id(t)] = members + [t]
+    by_id = {id(t): t for t in w.order}
+    for root_id, members in clusters.items():
+        if len(members) < 2:
+            continue
+        root = by_id[root_id]
+        inside = {id(m): k for k, m in enumerate(members)}
+        inputs, index = [], {}
+        for m in members:
+            for a in m._args:
+                if id(a) not in inside and id(a) not in index:
+                    index[id(a)] = len(inputs)
+                    inputs.append(a)
+        if len(inputs) > _MAX_INPUTS:
+            continue
+        n_in = len(inputs)
+        reg = lambda a: n_in + inside[id(a)] if id(a) in inside else index[id(a)]   # noqa: E731
+        instrs = []
+        for m in members:
+            ops = [reg(a) for a in m._args]
+            instrs.append((m._opname, ops[0], ops[1] if len(ops) > 1 else None))
+        prog = FC.Fused(instrs, n_in, root.shape)
+        fn = _fused_executable(prog)
+        out[root_id] = (fn, tuple(inputs), {}, None)
+        for m in members[:-1]:
+            absorbed.add(id(m))
+
+
+def _fused_executable(prog):
+    def run(*vals):
+        return prog(*vals)
+
+    def run_out(*vals, out):
+        prog.into(*vals, out=out)
+    run._mimir_out = run_out
+    return run
 
 
 def _compile(w: _Walk, roots, fusion, absorbed):

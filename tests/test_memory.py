@@ -13,7 +13,7 @@ def _stale(t):
         t.data()
 
 
-def test_elementwise_update_is_computed_straight_into_its_destination():
+def test_elementwise_update_is_computed_straight_into_its_destination(unfused):
     p = T.tensor(torch.arange(6.0).reshape(2, 3))
     g = T.tensor(torch.ones(2, 3))
     mem = p.data()
@@ -28,7 +28,7 @@ def test_elementwise_update_is_computed_straight_into_its_destination():
     _stale(new)
 
 
-def test_a_destination_that_is_read_later_is_written_after_the_schedule():
+def test_a_destination_that_is_read_later_is_written_after_the_schedule(unfused):
     a = T.tensor(torch.tensor([1.0, 2.0, 3.0]))
     b = T.tensor(torch.tensor([10.0, 20.0, 30.0]))
     ma, mb = a.data(), b.data()
@@ -83,7 +83,16 @@ def test_views_of_overwritten_memory_are_stale_and_misfits_are_refused():
     assert keep.data().sum() == 0                          # nothing written, still current
 
 
-def test_pool_serves_elementwise_temporaries_and_replays_over_the_same_buffers():
+@pytest.fixture
+def unfused():
+    """The pool tests watch the temporaries of single elementwise instructions, so the planner must not
+    fold their chains into one program."""
+    old = plan.set_elementwise_fusion(False)
+    yield
+    plan.set_elementwise_fusion(old)
+
+
+def test_pool_serves_elementwise_temporaries_and_replays_over_the_same_buffers(unfused):
     memory.set_pool("cpu")
     pool = memory.pool()
     pool.trim()
@@ -108,7 +117,7 @@ def test_pool_serves_elementwise_temporaries_and_replays_over_the_same_buffers()
     assert len({first.data().data_ptr(), second.data().data_ptr(), third.data().data_ptr()}) == 3
 
 
-def test_pooled_buffer_stays_out_while_a_view_of_it_is_read():
+def test_pooled_buffer_stays_out_while_a_view_of_it_is_read(unfused):
     memory.set_pool("cpu")
     a = T.tensor(torch.arange(12.0))
     s = (a + 1.0).reshape((3, 4))                          # a view of a pooled buffer ...
@@ -150,7 +159,7 @@ def test_a_view_made_before_the_write_and_read_after_it_keeps_the_old_values():
     assert mem.tolist() == [0.0, 2.0, 4.0, 6.0, 8.0, 10.0] and new.data().data_ptr() == mem.data_ptr()
 
 
-def test_broadcast_operands_and_mixed_dtypes_take_the_pool_path_correctly():
+def test_broadcast_operands_and_mixed_dtypes_take_the_pool_path_correctly(unfused):
     memory.set_pool("cpu")
     a = T.tensor(torch.randn(4, 1, 8))
     b = T.tensor(torch.randn(5, 1))
@@ -163,7 +172,7 @@ def test_broadcast_operands_and_mixed_dtypes_take_the_pool_path_correctly():
     assert small.data().shape == (3,)
 
 
-def test_donated_batch_is_read_once_and_its_memory_serves_the_same_schedule():
+def test_donated_batch_is_read_once_and_its_memory_serves_the_same_schedule(unfused):
     memory.set_pool("cpu")
     pool = memory.pool()
     pool.trim()
@@ -208,7 +217,7 @@ def test_donated_batch_is_read_once_and_its_memory_serves_the_same_schedule():
     assert abs(step(b).item() - want) < 1e-3                          # it was not consumed by the refused schedule
 
 
-def test_unused_buffers_age_out_of_the_pool():
+def test_unused_buffers_age_out_of_the_pool(unfused):
     memory.set_pool("cpu")
     pool = memory.pool()
     pool.trim()
@@ -220,3 +229,54 @@ def test_unused_buffers_age_out_of_the_pool():
         (small * 2.0 + 1.0).realize()                           # schedules that never ask for it
     assert all(k[2] != 256 * 256 for k in pool.free)           # released
     assert pool.stats()["held_bytes"] < 256 * 256 * 4
+
+
+def test_elementwise_chains_run_as_one_fused_program_on_the_cpu():
+    """internal/sched/fuse.go:200-362: a chain of elementwise ops is one kernel; here one native program
+    over cache-sized blocks, with the composed PyTorch ops as the path under autograd."""
+    from mimir_b200.tensor.autograd import Param, backward
+    plan.set_elementwise_fusion(True)
+    torch.manual_seed(0)
+    a, b = torch.randn(300, 77), torch.rand(300, 77) + 0.5
+    x, y = T.tensor(a), T.tensor(b)
+    before = plan.stats()["fused"]
+
+    def f(p, q):
+        u = T.tanh(p * q + 1.5) - T.sqrt(q)
+        return T.maximum(T.exp(u) * 0.25, T.abs_(p)) / (T.softplus(q) + T.sigmoid(p)) + T.gelu(p) * T.silu(q)
+
+    def ref(p, q):
+        F = torch.nn.functional
+        u = torch.tanh(p * q + 1.5) - torch.sqrt(q)
+        return torch.maximum(torch.exp(u) * 0.25, torch.abs(p)) / (F.softplus(q) + torch.sigmoid(p)) + F.gelu(p, approximate="tanh") * F.silu(q)
+    got = f(x, y).data()
+    assert plan.stats()["fused"] - before == 1                       # the whole expression is one program
+    assert torch.allclose(got, ref(a, b), rtol=2e-6, atol=2e-6)
+    assert torch.equal(f(x, y).data(), got)                          # cached program, same result
+    # NaNs and signed zeros go through like the single ops
+    s = torch.tensor([float("nan"), -0.0, 0.0, -3.0, 2.0, float("inf")] * 100)
+    st = T.tensor(s)
+    out = (T.relu(st) + T.sign(st) * 2.0 + T.minimum(st, 1.0)).data()
+    want = torch.relu(s) + torch.sign(s) * 2.0 + torch.minimum(s, torch.tensor(1.0))
+    assert torch.equal(torch.isnan(out), torch.isnan(want)) and torch.equal(out[~torch.isnan(out)], want[~torch.isnan(want)])
+    # under autograd the same program runs as composed ops and gives gradients
+    p = Param(a.clone())
+    loss = T.sum_(f(p.value(), y))
+    backward(loss)
+    ar = a.clone().requires_grad_(True)
+    ref(ar, b).sum().backward()
+    assert torch.allclose(p.grad().data(), ar.grad, rtol=1e-4, atol=1e-5)
+    # a value with two readers is not folded away; other dtypes and strided operands stay on PyTorch
+    h = T.exp(x * 0.5)
+    both = (h + 1.0).data(), (h * 2.0).data()
+    assert torch.allclose(both[0], torch.exp(a * 0.5) + 1.0) and torch.allclose(both[1], torch.exp(a * 0.5) * 2.0)
+    xd = T.tensor(a.double())
+    assert (T.exp(xd * 0.5) + 1.0).data().dtype == torch.float64
+    xt = T.from_torch(a.t())
+    assert torch.allclose((T.exp(xt * 0.5) + 1.0).data(), torch.exp(a.t() * 0.5) + 1.0)
+    # into a destination: the fused program writes straight into it
+    dst = T.tensor(torch.zeros(300, 77))
+    mem = dst.data()
+    before = plan.stats()["into_direct"]
+    T.realize_into(dst, T.tanh(x * 2.0) + y)
+    assert plan.stats()["into_direct"] == before + 1 and torch.allclose(mem, torch.tanh(a * 2.0) + b, atol=1e-6)
