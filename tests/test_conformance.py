@@ -1,5 +1,5 @@
 """The shared case table (``mimir_b200/utils/conformance.py``) against its float64 oracle files: on
-the CPU in float32 and bfloat16, and in float32 on the GPU (reference: the same kerneltest cases on
+the CPU in float32 and bfloat16; the GPU pass is ``tests/test_zy_conformance_gpu.py`` (reference: the same kerneltest cases on
 every backend, backend/internal/kerneltest/kerneltest.go:58-120; oracle files as tools/golden/gen.py
 writes them)."""
 import os
@@ -55,14 +55,3 @@ def test_a_wrong_kernel_is_caught_by_the_row_bound(golden, monkeypatch):
     monkeypatch.setattr(case, "run", off_by_one_row)
     bad = conf.check(golden, only={"matmul_2d"})
     assert len(bad) == 1 and "matmul_2d/out" in bad[0]
-
-
-@pytest.mark.gpu
-def test_gpu_float32_is_conformant(golden):
-    import mimir_b200.tensor as T
-    old = torch.backends.cudnn.allow_tf32
-    torch.backends.cudnn.allow_tf32 = False                 # float32 convolutions in full precision, like the oracle
-    try:
-        assert conf.check(golden, device=T.GPU(0)) == []
-    finally:
-        torch.backends.cudnn.allow_tf32 = old
