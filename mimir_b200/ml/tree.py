@@ -16,7 +16,35 @@ def _bin(X, bins=255):
     qs = torch.linspace(0, 1, bins + 1)[1:-1]
     edges = torch.quantile(X, qs.to(X.device), dim=0).t().contiguous()  # [F, bins-1]
     B = torch.searchsorted(edges, X.t().contiguous()).t().contiguous()
-    return B.to(torch.int64), edges
+    # one byte per value when the bins allow it: the native histogram pass reads the rows as they are
+    return B.to(torch.uint8 if bins <= 256 else torch.int64), edges
+
+
+def _histogram(B, idx, g, h, bins):
+    """Sums of g, sums of h and counts per (feature, bin) over the rows ``idx``: ``[3, F, bins]`` float64.
+    uint8 bins on the CPU take the native multi-threaded pass (``csrc/cpu_hist.cc``)."""
+    F = B.shape[1]
+    if B.dtype == torch.uint8 and B.device.type == "cpu" and B.is_contiguous() and bins <= 256:
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_hist_bound", False):
+            lib.mimir_cpu_hist.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+            lib._hist_bound = True
+        out = torch.empty(3, F, bins, dtype=torch.float64)
+        idx = idx.contiguous()
+        g32 = g if g.dtype == torch.float32 and g.is_contiguous() else g.float().contiguous()
+        h32 = h if h.dtype == torch.float32 and h.is_contiguous() else h.float().contiguous()
+        rc = lib.mimir_cpu_hist(B.data_ptr(), F, idx.data_ptr(), idx.numel(), g32.data_ptr(), h32.data_ptr(), bins, out.data_ptr())
+        if rc == 0:
+            return out
+    Bi = B[idx].long()
+    flat = (Bi + torch.arange(F, device=B.device) * bins).reshape(-1)
+    hg = torch.bincount(flat, weights=g[idx].double().repeat_interleave(F), minlength=F * bins)
+    hh = torch.bincount(flat, weights=h[idx].double().repeat_interleave(F), minlength=F * bins)
+    hc = torch.bincount(flat, minlength=F * bins).double()
+    return torch.stack([hg, hh, hc]).view(3, F, bins)
 
 
 class _Tree:
@@ -32,11 +60,53 @@ class _Tree:
         n, F = B.shape
         self.importance = torch.zeros(F)
         self.nodes = []
+        if g.dtype != torch.float64:
+            g, h = g.float().contiguous(), h.float().contiguous()
+        if B.dtype == torch.uint8 and B.device.type == "cpu" and B.is_contiguous() and self.bins <= 256 and g.dtype == torch.float32 \
+                and self._grow_native(B, g, h):
+            return self
         self._grow(B, g, h, torch.arange(n, device=B.device), 0)
         return self
 
-    def _grow(self, B, g, h, idx, depth):
-        G, H = g[idx].sum(), h[idx].sum()
+    def _grow_native(self, B, g, h) -> bool:
+        """The whole tree grown by ``csrc/cpu_hist.cc`` (histograms over the worker pool, the larger
+        child's histogram by subtraction, rows partitioned in place).  Feature subsets per node are drawn
+        from a seed taken from this tree's generator."""
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_tree_bound", False):
+            c = ctypes
+            lib.mimir_cpu_grow_tree.argtypes = [c.c_void_p, c.c_int, c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                                c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_ulonglong, c.c_void_p, c.c_int, c.c_void_p]
+            lib._tree_bound = True
+        n, F = B.shape
+        k = 0
+        seed = 0
+        if self.colsample < 1.0:
+            k = max(1, int(F * self.colsample))
+            seed = int(torch.randint(0, 2 ** 62, (1,), generator=self.gen))
+        max_nodes = int(min(2 ** (self.max_depth + 1) - 1, 2 * n + 1))
+        nodes = torch.empty(max_nodes, 5, dtype=torch.float64)
+        imp = torch.zeros(F, dtype=torch.float64)
+        idx = torch.arange(n, dtype=torch.int64)
+        cnt = lib.mimir_cpu_grow_tree(B.data_ptr(), F, idx.data_ptr(), n, g.data_ptr(), h.data_ptr(), self.bins, self.max_depth,
+                                      max(int(self.min_leaf), 1) if self.min_leaf >= 1 else 0, float(self.min_gain), float(self.l2), k, seed,
+                                      nodes.data_ptr(), max_nodes, imp.data_ptr())
+        if cnt <= 0:
+            return False
+        rows = nodes[:cnt]
+        self.nodes = [[int(r[0]), int(r[1]), int(r[2]), int(r[3]), float(r[4])] for r in rows.tolist()]
+        self.importance = imp.float()
+        return True
+
+    def _grow(self, B, g, h, idx, depth, hist=None):
+        """``hist``: this node's histogram when the parent already has it (a child's histogram is the
+        parent's minus its sibling's, so only the smaller child is ever counted)."""
+        if hist is not None:
+            G, H = hist[0, 0].sum().to(g.dtype), hist[1, 0].sum().to(g.dtype)      # every row falls in some bin of feature 0
+        else:
+            G, H = g[idx].sum(), h[idx].sum()
         node = len(self.nodes)
         self.nodes.append([-1, 0, -1, -1, float(-G / (H + self.l2))])
         if depth >= self.max_depth or idx.numel() < 2 * self.min_leaf:
@@ -46,11 +116,10 @@ class _Tree:
         if self.colsample < 1.0:
             k = max(1, int(F * self.colsample))
             feats = torch.randperm(F, generator=self.gen)[:k]
-        Bi = B[idx][:, feats]
-        flat = Bi + torch.arange(feats.numel(), device=B.device) * self.bins
-        hg = torch.bincount(flat.reshape(-1), weights=g[idx].repeat_interleave(feats.numel()), minlength=feats.numel() * self.bins)
-        hh = torch.bincount(flat.reshape(-1), weights=h[idx].repeat_interleave(feats.numel()), minlength=feats.numel() * self.bins)
-        hc = torch.bincount(flat.reshape(-1), minlength=feats.numel() * self.bins)
+        if hist is None:
+            hist = _histogram(B, idx, g, h, self.bins)
+        sel = hist[:, feats].to(g.dtype if g.dtype == torch.float64 else torch.float32)
+        hg, hh, hc = sel[0].reshape(-1), sel[1].reshape(-1), hist[2, feats].reshape(-1).long()
         GL = hg.view(-1, self.bins).cumsum(1)
         HL = hh.view(-1, self.bins).cumsum(1)
         CL = hc.view(-1, self.bins).cumsum(1)
@@ -65,11 +134,32 @@ class _Tree:
         self.importance[f] += bg
         go_left = B[idx, f] <= b
         self.nodes[node][0], self.nodes[node][1] = f, b
-        self.nodes[node][2] = self._grow(B, g, h, idx[go_left], depth + 1)
-        self.nodes[node][3] = self._grow(B, g, h, idx[~go_left], depth + 1)
+        li, ri = idx[go_left], idx[~go_left]
+        lh = rh = None
+        if depth + 1 < self.max_depth and min(li.numel(), ri.numel()) >= 2 * self.min_leaf:
+            if li.numel() <= ri.numel():
+                lh = _histogram(B, li, g, h, self.bins)
+                rh = hist - lh
+            else:
+                rh = _histogram(B, ri, g, h, self.bins)
+                lh = hist - rh
+        self.nodes[node][2] = self._grow(B, g, h, li, depth + 1, lh)
+        self.nodes[node][3] = self._grow(B, g, h, ri, depth + 1, rh)
         return node
 
     def predict_binned(self, B):
+        if B.dtype == torch.uint8 and B.device.type == "cpu" and B.is_contiguous() and self.nodes:
+            import ctypes
+            from .. import _native
+            lib = _native.lib()
+            if not getattr(lib, "_predict_bound", False):
+                lib.mimir_cpu_tree_predict.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int,
+                                                       ctypes.c_void_p]
+                lib._predict_bound = True
+            tbl = torch.tensor(self.nodes, dtype=torch.float64)
+            out = torch.empty(B.shape[0])
+            if lib.mimir_cpu_tree_predict(B.data_ptr(), B.shape[1], B.shape[0], tbl.data_ptr(), tbl.shape[0], out.data_ptr()) == 0:
+                return out
         out = torch.zeros(B.shape[0])
         node = torch.zeros(B.shape[0], dtype=torch.int64)
         active = torch.ones(B.shape[0], dtype=torch.bool)

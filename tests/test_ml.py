@@ -119,3 +119,28 @@ def test_gmm_ward_fista_kernel_svm():
     assert (svm.classify(P) == lab).float().mean() > 0.98
     lin = ml.KernelSVM(c=1.0, kernel="linear").fit(X[:150], (X[:150] @ wt > 0).long())
     assert (lin.classify(X[:150]) == (X[:150] @ wt > 0).long()).float().mean() > 0.95
+
+
+def test_native_tree_growth_equals_the_reference_path():
+    """The tree grown by the native code (histograms over the worker pool, sibling subtraction, in-place
+    row partition) against the same learner on the PyTorch path (bins as int64)."""
+    from mimir_b200.ml import tree as TR
+    torch.manual_seed(3)
+    X = torch.randn(3000, 9)
+    y = X[:, 0] * 2 - X[:, 4] + (X[:, 2] > 0.3).float() * 3 + 0.1 * torch.randn(3000)
+    B, _ = TR._bin(X, 64)
+    assert B.dtype == torch.uint8
+    g, h = (0.0 - y), torch.ones(3000)
+    fast = TR._Tree(5, 3, 0.0, 1.0, 64).fit(B, g, h)
+    slow = TR._Tree(5, 3, 0.0, 1.0, 64).fit(B.long(), g, h)            # int64 bins: the PyTorch path
+    assert len(fast.nodes) == len(slow.nodes) > 20
+    for a, b in zip(fast.nodes, slow.nodes):
+        assert a[:4] == b[:4] and abs(a[4] - b[4]) < 1e-4 * max(1.0, abs(b[4])), (a, b)
+    assert torch.allclose(fast.predict_binned(B), slow.predict_binned(B.long()), atol=1e-4)
+    assert torch.allclose(fast.importance, slow.importance, rtol=1e-3, atol=1e-3)
+    # feature sampling per node: deterministic for a seed, and it does restrict the features
+    g1 = torch.Generator().manual_seed(5)
+    g2 = torch.Generator().manual_seed(5)
+    t1 = TR._Tree(4, 1, 0.0, 1.0, 64, colsample=0.3, gen=g1).fit(B, g, h)
+    t2 = TR._Tree(4, 1, 0.0, 1.0, 64, colsample=0.3, gen=g2).fit(B, g, h)
+    assert t1.nodes == t2.nodes and t1.nodes != fast.nodes
