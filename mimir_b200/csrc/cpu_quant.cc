@@ -4,10 +4,11 @@
 // weights quantized and multiplies block by block).
 //
 // Two paths, chosen once at run time from the CPU's features:
-//   * int8: the activation rows are rounded to 32-value blocks (float scale, int8 values, block sum),
-//     and every weight block is multiplied with its activation block by 256-bit VNNI dot products
-//     (vpdpbusd: unsigned weight codes x signed activations), the offsets (-8, -32, the K-quant
-//     minima) folded in through the activation block sums;
+//   * int8: the activation rows are rounded to int8 (one float scale per 32 values for Q8_0 / Q4_0
+//     weights, one per 256 for the K-quants, whose super-blocks are then summed in integers: dot
+//     products times their 6-bit or int8 sub-block scales), and every weight block is multiplied with
+//     its activation block by 256-bit VNNI dot products (vpdpbusd: unsigned weight codes x signed
+//     activations), the offsets (-8, -32, the K-quant minima) folded in through the block sums;
 //   * exact: float activations, weights decoded value by value (any x86-64).  It computes exactly
 //     x . dequant(W) and is what the int8 path is tested against.
 // Rows of W are split over a small pool of worker threads that lives as long as the library.
@@ -143,11 +144,13 @@ void rows_exact(int code, const uint8_t* w, int K, const float* x, int B, float*
 // ---------------------------------------------------------------------------
 // int8 path
 // ---------------------------------------------------------------------------
-struct ActQ {            // one activation row rounded to 32-value blocks
+struct ActQ {            // one activation row rounded to int8
   const int8_t* q;       // K values
-  const float* d;        // K / 32 scales
+  const float* d;        // K / 32 scales (one per 32 values for Q8_0 / Q4_0 weights; the K-quants share
+                         // one per 256 values, repeated, so that a super-block is summed in integers)
   const float* ds;       // K / 32: scale x sum of the block's values
-  const float* ds16;     // K / 16: scale x sum of each half block (Q6_K has a scale per 16 values)
+  const int32_t* isum;   // K / 32: sum of the block's int8 values
+  const int32_t* isum16; // K / 16: sum of each half block (Q6_K has a scale per 16 values)
 };
 
 #define VNNI __attribute__((target("avx2,fma,avx512f,avx512bw,avx512vl,avx512vnni")))
@@ -196,46 +199,52 @@ VNNI void rows_int8_t(int code, const uint8_t* w, int K, const ActQ* act, float*
         }
       }
     } else if (code == Q4_K) {
-      // two accumulators per activation row, so consecutive sub-block pairs do not wait for each other
-      __m256 acc2[B];
-      _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) acc2[b] = _mm256_setzero_ps();
+      // a super-block is summed in integers: dot products x 6-bit scales, one float multiply at its end
       for (int sb = 0; sb < K / 256; ++sb) {
         const uint8_t* p = row + static_cast<size_t>(sb) * 144;
         const float d = ld_half(p), dmin = ld_half(p + 2);
-        // the eight 6-bit scales and minima of the super-block, unpacked once
-        float fs[8], fm[8];
+        int sc[8], mn[8];
         {
           const uint8_t* q = p + 4;
           for (int j = 0; j < 4; ++j) {
-            fs[j] = d * (q[j] & 63);
-            fm[j] = dmin * (q[j + 4] & 63);
-            fs[j + 4] = d * ((q[j + 8] & 0xF) | ((q[j] >> 6) << 4));
-            fm[j + 4] = dmin * ((q[j + 8] >> 4) | ((q[j + 4] >> 6) << 4));
+            sc[j] = q[j] & 63;
+            mn[j] = q[j + 4] & 63;
+            sc[j + 4] = (q[j + 8] & 0xF) | ((q[j] >> 6) << 4);
+            mn[j + 4] = (q[j + 8] >> 4) | ((q[j + 4] >> 6) << 4);
           }
         }
+        __m256i acci[B];
+        _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) acci[b] = _mm256_setzero_si256();
+        const int b0 = sb * 8;
         for (int pr = 0; pr < 4; ++pr) {
           const __m256i raw = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(p + 16 + 32 * pr));
           const __m256i lo = _mm256_and_si256(raw, low4);
           const __m256i hi = _mm256_and_si256(_mm256_srli_epi16(raw, 4), low4);
-          const int b0 = sb * 8 + 2 * pr;                          // activation blocks of the two sub-blocks
+          const __m256i s0 = _mm256_set1_epi32(sc[2 * pr]), s1 = _mm256_set1_epi32(sc[2 * pr + 1]);
           _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) {
-            const __m256i qa0 = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(act[b].q + b0 * 32));
-            const __m256i qa1 = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(act[b].q + b0 * 32 + 32));
-            const __m256i d0 = _mm256_dpbusd_epi32(_mm256_setzero_si256(), lo, qa0);
-            const __m256i d1 = _mm256_dpbusd_epi32(_mm256_setzero_si256(), hi, qa1);
-            acc[b] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(d0), _mm256_set1_ps(fs[2 * pr] * act[b].d[b0]), acc[b]);
-            acc2[b] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(d1), _mm256_set1_ps(fs[2 * pr + 1] * act[b].d[b0 + 1]), acc2[b]);
-            off[b] += fm[2 * pr] * act[b].ds[b0] + fm[2 * pr + 1] * act[b].ds[b0 + 1];
+            const int8_t* qa = act[b].q + (b0 + 2 * pr) * 32;
+            const __m256i d0 = _mm256_dpbusd_epi32(_mm256_setzero_si256(), lo, _mm256_loadu_si256(reinterpret_cast<const __m256i*>(qa)));
+            const __m256i d1 = _mm256_dpbusd_epi32(_mm256_setzero_si256(), hi, _mm256_loadu_si256(reinterpret_cast<const __m256i*>(qa + 32)));
+            acci[b] = _mm256_add_epi32(acci[b], _mm256_add_epi32(_mm256_mullo_epi32(d0, s0), _mm256_mullo_epi32(d1, s1)));
           }
         }
+        _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) {
+          const float da = act[b].d[b0];
+          acc[b] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(acci[b]), _mm256_set1_ps(d * da), acc[b]);
+          int ms = 0;
+          for (int j = 0; j < 8; ++j) ms += mn[j] * act[b].isum[b0 + j];
+          off[b] += dmin * da * static_cast<float>(ms);
+        }
       }
-      _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) acc[b] = _mm256_add_ps(acc[b], acc2[b]);
-    } else {  // Q6_K
+    } else {  // Q6_K: 6-bit codes with an offset of 32 and an int8 scale per 16 values
       const __m256i two = _mm256_set1_epi8(3);
       for (int sb = 0; sb < K / 256; ++sb) {
         const uint8_t* p = row + static_cast<size_t>(sb) * 210;
         const int8_t* sc = reinterpret_cast<const int8_t*>(p + 192);
         const float d = ld_half(p + 208);
+        __m256i acci[B];
+        int ioff[B];
+        _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) { acci[b] = _mm256_setzero_si256(); ioff[b] = 0; }
         for (int h = 0; h < 2; ++h) {
           const __m256i l0 = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(p + 64 * h));
           const __m256i l1 = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(p + 64 * h + 32));
@@ -250,15 +259,20 @@ VNNI void rows_int8_t(int code, const uint8_t* w, int K, const ActQ* act, float*
                                  _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(hq, 6), two), 4));
           for (int g = 0; g < 4; ++g) {
             const int ab = sb * 8 + h * 4 + g;                     // activation block of these 32 values
-            const float sa = d * sc[8 * h + 2 * g], sb2 = d * sc[8 * h + 2 * g + 1];   // a scale per 16 values
-            const __m256 scale = _mm256_set_ps(sb2, sb2, sb2, sb2, sa, sa, sa, sa);
+            const int sa = sc[8 * h + 2 * g], sb2 = sc[8 * h + 2 * g + 1];   // a scale per 16 values
+            const __m256i scale = _mm256_set_epi32(sb2, sb2, sb2, sb2, sa, sa, sa, sa);
             _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) {
               const __m256i qa = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(act[b].q + ab * 32));
               const __m256i dot = _mm256_dpbusd_epi32(_mm256_setzero_si256(), q[g], qa);
-              acc[b] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(dot), _mm256_mul_ps(scale, _mm256_set1_ps(act[b].d[ab])), acc[b]);
-              off[b] += 32.f * (sa * act[b].ds16[2 * ab] + sb2 * act[b].ds16[2 * ab + 1]);   // codes carry an offset of 32
+              acci[b] = _mm256_add_epi32(acci[b], _mm256_mullo_epi32(dot, scale));
+              ioff[b] += sa * act[b].isum16[2 * ab] + sb2 * act[b].isum16[2 * ab + 1];   // codes carry an offset of 32
             }
           }
+        }
+        _Pragma("GCC unroll 8") for (int b = 0; b < B; ++b) {
+          const float f = d * act[b].d[sb * 8];
+          acc[b] = _mm256_fmadd_ps(_mm256_cvtepi32_ps(acci[b]), _mm256_set1_ps(f), acc[b]);
+          off[b] += 32.f * f * static_cast<float>(ioff[b]);
         }
       }
     }
@@ -281,22 +295,26 @@ VNNI void rows_int8(int code, const uint8_t* w, int K, const ActQ* act, int B, f
 }
 
 // rounds one row of K floats to 32-value blocks
-void quantize_row(const float* x, int K, int8_t* q, float* d, float* ds, float* ds16) {
-  for (int blk = 0; blk < K / 32; ++blk) {
-    const float* xb = x + blk * 32;
+// group: values sharing one scale (32, or 256 for the K-quants)
+void quantize_row(const float* x, int K, int group, int8_t* q, float* d, float* ds, int32_t* isum, int32_t* isum16) {
+  for (int g0 = 0; g0 < K; g0 += group) {
     float amax = 0.f;
-    for (int i = 0; i < 32; ++i) amax = std::fmax(amax, std::fabs(xb[i]));
+    for (int i = 0; i < group; ++i) amax = std::fmax(amax, std::fabs(x[g0 + i]));
     const float scale = amax / 127.f, inv = scale > 0.f ? 1.f / scale : 0.f;
-    int s0 = 0, s1 = 0;
-    for (int i = 0; i < 32; ++i) {
-      const int v = static_cast<int>(std::nearbyint(xb[i] * inv));
-      q[blk * 32 + i] = static_cast<int8_t>(v);
-      (i < 16 ? s0 : s1) += v;
+    for (int blk = g0 / 32; blk < (g0 + group) / 32; ++blk) {
+      const float* xb = x + blk * 32;
+      int s0 = 0, s1 = 0;
+      for (int i = 0; i < 32; ++i) {
+        const int v = static_cast<int>(std::nearbyint(xb[i] * inv));
+        q[blk * 32 + i] = static_cast<int8_t>(v);
+        (i < 16 ? s0 : s1) += v;
+      }
+      d[blk] = scale;
+      ds[blk] = scale * static_cast<float>(s0 + s1);
+      isum[blk] = s0 + s1;
+      isum16[2 * blk] = s0;
+      isum16[2 * blk + 1] = s1;
     }
-    d[blk] = scale;
-    ds[blk] = scale * static_cast<float>(s0 + s1);
-    ds16[2 * blk] = scale * static_cast<float>(s0);
-    ds16[2 * blk + 1] = scale * static_cast<float>(s1);
   }
 }
 
@@ -357,7 +375,7 @@ MIMIR_CPU_API int mimir_cpu_qgemv_has_int8() { return has_vnni() ? 1 : 0; }
 MIMIR_CPU_API int mimir_cpu_set_threads(int n) { return mimir_cpu::set_threads(n); }
 
 // y [B][N] (fp32) = x [B][K] (fp32) . W^T, W = N rows of K values in ggml blocks of `code`.
-// mode 0: exact; 1: int8 activations; -1: int8 when the CPU has it.  scratch: B * (K + 4 * K / 32 * 4 + 64) bytes
+// mode 0: exact; 1: int8 activations; -1: int8 when the CPU has it.  scratch: B * (K + 5 * K / 32 * 4 + 64) bytes
 // or null (allocated per call).  Returns 0, or -1 for a bad argument.
 MIMIR_CPU_API int mimir_cpu_qgemv(int code, const void* w, int N, int K, const float* x, int B, float* y, int mode,
                                   void* scratch) {
@@ -381,7 +399,7 @@ MIMIR_CPU_API int mimir_cpu_qgemv(int code, const void* w, int N, int K, const f
     return 0;
   }
   const int nb = K / 32;
-  const size_t per_row = static_cast<size_t>(K) + static_cast<size_t>(nb) * 4 * 4 + 64;
+  const size_t per_row = static_cast<size_t>(K) + static_cast<size_t>(nb) * 5 * 4 + 64;
   std::vector<uint8_t> own;
   uint8_t* s = static_cast<uint8_t*>(scratch);
   if (!s) { own.resize(per_row * B); s = own.data(); }
@@ -390,8 +408,9 @@ MIMIR_CPU_API int mimir_cpu_qgemv(int code, const void* w, int N, int K, const f
     uint8_t* base = s + per_row * b;
     int8_t* q = reinterpret_cast<int8_t*>(base);
     float* f = reinterpret_cast<float*>(base + ((static_cast<size_t>(K) + 63) / 64) * 64);
-    act[b] = ActQ{q, f, f + nb, f + 2 * nb};
-    quantize_row(x + static_cast<size_t>(b) * K, K, q, f, f + nb, f + 2 * nb);
+    int32_t* is = reinterpret_cast<int32_t*>(f + 2 * nb);
+    act[b] = ActQ{q, f, f + nb, is, is + nb};
+    quantize_row(x + static_cast<size_t>(b) * K, K, vals == 256 ? 256 : 32, q, f, f + nb, is, is + nb);
   }
   p.run([&](int, int) {
     for (int n0 = next.fetch_add(chunk); n0 < N; n0 = next.fetch_add(chunk))

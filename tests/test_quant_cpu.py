@@ -46,7 +46,8 @@ def test_int8_product_stays_within_the_rounding_of_the_activations(code):
     want = x.double() @ w.t()
     got = quant_cpu.qgemv(code, raw, n, k, x, "int8").double()
     # the oracle of the int8 path: the same product with the activations rounded to int8 blocks
-    xb = x.reshape(5, k // 32, 32)
+    group = 256 if code in (Q.Q4_K, Q.Q6_K) else 32            # the K-quants share one activation scale per super-block
+    xb = x.reshape(5, k // group, group)
     d = xb.abs().amax(-1, keepdim=True) / 127
     xq = (torch.round(xb / d.clamp_min(1e-30)) * d).reshape(5, k).double()
     rounded = xq @ w.t()
