@@ -69,8 +69,46 @@ class Tensors(Dataset):
             yield Batch(T.from_torch(self.x[idx]), None if self.y is None else T.from_torch(self.y[idx]))
 
 
-def statistics(x):
-    """Per-feature mean and standard deviation (data.Statistics)."""
+def _merge_moments(a, b):
+    """Chan's pairwise update of (count, mean, sum of squared deviations)."""
+    (na, ma, sa), (nb, mb, sb) = a, b
+    if na == 0:
+        return b
+    if nb == 0:
+        return a
+    n = na + nb
+    delta = mb - ma
+    return n, ma + delta * (nb / n), sa + sb + delta * delta * (na * nb / n)
+
+
+def statistics(x, workers: int = 4):
+    """Per-feature mean and standard deviation (data.Statistics, README "Scale").  A tensor is
+    reduced directly; a ``Stream`` (or a list of ``Source`` shards) is read ONCE, its shards in
+    parallel, with the moments of the chunks merged pairwise, so a data set of any size needs the
+    memory of a few chunks."""
+    if isinstance(x, Stream) or (isinstance(x, (list, tuple)) and x and isinstance(x[0], Source)):
+        import concurrent.futures
+        sources = x.sources if isinstance(x, Stream) else list(x)
+
+        def one(src):
+            acc = (0, None, None)
+            for cx, _ in src.read():
+                c = cx.double().reshape(cx.shape[0], -1) if cx.dim() != 2 else cx.double()
+                if not c.shape[0]:
+                    continue
+                m = c.mean(0)
+                acc = _merge_moments(acc, (c.shape[0], m, ((c - m) ** 2).sum(0)))
+            return acc
+        with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, workers)) as ex:
+            parts = list(ex.map(one, sources))
+        total = (0, None, None)
+        for part in parts:                      # merged in shard order: the result does not depend on timing
+            total = _merge_moments(total, part)
+        n, mean, ss = total
+        if not n:
+            raise ValueError("statistics of an empty source")
+        std = (ss / max(n - 1, 1)).sqrt().clamp_min(1e-8)
+        return mean.float(), std.float()
     v = x.data() if isinstance(x, T.Tensor) else torch.as_tensor(x)
     v = v.float()
     dims = tuple(d for d in range(v.dim()) if d != 1) if v.dim() > 2 else (0,)
@@ -96,16 +134,26 @@ class Stream(Dataset):
     """Batches from shards with a background prefetch thread and an optional shuffle buffer."""
 
     def __init__(self, sources, batch_size: int = 32, prefetch: int = 4, shuffle_buffer: int = 0, seed: int = 0,
-                 in_order: bool = True, drop_last: bool = False):
+                 in_order: bool = True, drop_last: bool = False, normalize=None, class_targets: bool = False):
+        """``normalize``: ``(mean, std)`` per feature, as ``statistics`` returns them, applied to every
+        chunk as it is read; ``class_targets``: labels become integer class indices (data.Normalize,
+        data.ClassTargets)."""
         self.sources, self.batch_size, self.prefetch = list(sources), batch_size, prefetch
         self.shuffle_buffer, self.seed, self.epoch, self.drop_last = shuffle_buffer, seed, 0, drop_last
+        self.normalize, self.class_targets = normalize, class_targets
 
     def set_epoch(self, epoch: int) -> None:
         self.epoch = epoch
 
     def _chunks(self):
         for s in self.sources:
-            yield from s.read()
+            for x, y in s.read():
+                if self.normalize is not None:
+                    mean, std = self.normalize
+                    x = (x.float() - mean) / std
+                if self.class_targets and y is not None:
+                    y = y.long()
+                yield x, y
 
     def _rows(self):
         g = torch.Generator().manual_seed(self.seed * 7919 + self.epoch)

@@ -95,22 +95,32 @@ def csv_shards(pattern: str, label=-1, header=True, batch_size=32, chunk=4096, *
 
 # --------------------------------------------------------------------- Parquet
 class _ParquetShard(Source):
-    def __init__(self, path, features, label):
+    def __init__(self, path, features, label, classes=None):
         self.path, self.features, self.label = path, features, label
+        self.classes = {c: i for i, c in enumerate(classes)} if classes else None
 
     def read(self):
         from ..io import parquet
         f = parquet.File(self.path)
         feats = self.features or [c for c in f.columns if c != self.label]
         for g in range(f.row_groups):
-            yield f.matrix(feats, self.label, g)
+            X, y = f.matrix(feats, self.label, g)
+            if self.classes is not None and isinstance(y, list):
+                try:
+                    y = torch.tensor([self.classes[v] for v in y], dtype=torch.int64)
+                except KeyError as e:
+                    raise ValueError(f"{self.path}: label {e.args[0]!r} is not one of {list(self.classes)}") from None
+            yield X, y
 
 
-def parquet_shards(pattern: str, features=None, label: str | None = None, batch_size=32, **kw) -> Stream:
-    paths = sorted(glob.glob(pattern))
+def parquet_shards(pattern, features=None, label: str | None = None, batch_size=32, classes=None, **kw) -> Stream:
+    """A stream over the row groups of Parquet files (a glob pattern or a list of paths), decoded by
+    the native reader.  ``classes``: the names a string label column may hold, mapped to 0, 1, ...
+    (datasets.ParquetShards with datasets.Classes)."""
+    paths = sorted(glob.glob(pattern)) if isinstance(pattern, str) else list(pattern)
     if not paths:
         raise FileNotFoundError(f"no files match {pattern!r}")
-    return Stream([_ParquetShard(p, features, label) for p in paths], batch_size=batch_size, **kw)
+    return Stream([_ParquetShard(p, features, label, classes) for p in paths], batch_size=batch_size, **kw)
 
 
 # ------------------------------------------------------------------ .mim mapped

@@ -1,6 +1,8 @@
 """Dataset readers and the Parquet reader (reference: data/datasets/*_test.go, io/parquet/*_test.go)."""
 import os
 
+import pytest
+
 import torch
 
 from mimir_b200.data import datasets
@@ -60,3 +62,38 @@ def test_mapped_and_synthetic(tmp_path):
     b0 = next(iter(t))
     assert b0.x.shape == (4, 16) and b0.y.shape == (4, 16)
     assert datasets.synthetic_regression(rows=10, batch_size=5).rows() == 10
+
+
+def test_streamed_statistics_normalize_and_named_classes(tmp_path):
+    """README "Scale": statistics in one parallel pass over the shards, applied as the stream is read;
+    a string label column mapped through its class names."""
+    from mimir_b200 import data
+    torch.manual_seed(0)
+    paths, Xs = [], []
+    for k in range(3):
+        n = 500 + 37 * k
+        X = torch.randn(n, 4) * torch.tensor([1.0, 5.0, 0.1, 2.0]) + torch.tensor([0.0, 10.0, -3.0, 1.0])
+        Xs.append(X)
+        p = os.path.join(tmp_path, f"s{k}.parquet")
+        parquet.write(p, {"a": X[:, 0], "b": X[:, 1], "c": X[:, 2], "d": X[:, 3],
+                          "label": ["yes" if v > 0 else "no" for v in X[:, 0].tolist()]}, row_group_size=200)
+        paths.append(p)
+    allX = torch.cat(Xs)
+    src = datasets.parquet_shards(paths, ["a", "b", "c", "d"], "label", classes=("no", "yes"), batch_size=128)
+    mean, std = data.statistics(src)
+    assert torch.allclose(mean, allX.mean(0), atol=1e-4) and torch.allclose(std, allX.std(0), rtol=1e-4)
+    st = datasets.parquet_shards(paths, ["a", "b", "c", "d"], "label", classes=("no", "yes"), batch_size=128,
+                                 normalize=(mean, std), class_targets=True, shuffle_buffer=256, seed=3)
+    xs, ys = [], []
+    for b in st:
+        xs.append(b.x.data())
+        ys.append(b.y.data())
+    Xn, Y = torch.cat(xs), torch.cat(ys)
+    assert Xn.shape == allX.shape and Y.dtype == torch.int64
+    assert torch.allclose(Xn.mean(0), torch.zeros(4), atol=1e-3) and torch.allclose(Xn.std(0), torch.ones(4), atol=1e-3)
+    assert int(Y.sum()) == int((allX[:, 0] > 0).sum())
+    assert torch.equal(Y, (Xn[:, 0] * std[0] + mean[0] > 0).long())                 # labels stayed with their rows through the shuffle
+    with pytest.raises(ValueError, match="maybe"):
+        p = os.path.join(tmp_path, "bad.parquet")
+        parquet.write(p, {"a": torch.zeros(2), "label": ["yes", "maybe"]})
+        list(datasets.parquet_shards(p, ["a"], "label", classes=("no", "yes")))
