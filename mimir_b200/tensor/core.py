@@ -896,15 +896,28 @@ logcumsumexp = _scan("logcumsumexp", "logsumexp", lambda v, d: torch.logcumsumex
 
 
 def sort(x, dim=-1, descending=False):
-    return _node(lambda v: tuple(torch.sort(v, dim, descending)), (x,), {}, "sort")
+    """``(values, indices)``, stable: equal values keep their order (tensor/sort.go)."""
+    return _node(lambda v: tuple(torch.sort(v, dim=dim, descending=descending, stable=True)), (x,), {}, "sort")
 
 
 def argsort(x, dim=-1, descending=False):
-    return _node(lambda v: torch.argsort(v, dim, descending).to(int32), (x,), {}, "argsort")
+    return _node(lambda v: torch.argsort(v, dim=dim, descending=descending, stable=True).to(int32), (x,), {}, "argsort")
 
 
-def topk(x, k, dim=-1):
-    return _node(lambda v: tuple(torch.topk(v, k, dim)), (x,), {}, "topk")
+def topk(x, k, dim=-1, largest=True):
+    """``(values, indices)`` of the ``k`` largest (or smallest) entries along ``dim``, in order."""
+    return _node(lambda v: tuple(torch.topk(v, k, dim, largest=largest)), (x,), {}, "topk")
+
+
+def cummax_indices(x, dim=-1):
+    """Position of the running maximum along ``dim``; of equal values (or after a NaN) the latest one."""
+    return _node(lambda v: torch.cummax(v, dim).indices.to(int32), (x,), {}, "cummax_indices")
+
+
+def windows(x, axis, size, step=1):
+    """Sliding windows of ``size`` values every ``step`` along ``axis``, as a new last axis
+    (tensor.Unfold over one axis: ``[..., n, ...] -> [..., (n - size) // step + 1, ..., size]``)."""
+    return _node(lambda v: v.unfold(axis, size, step), (x,), {}, "windows", attrs={"axis": axis, "size": size, "step": step})
 
 
 # ---------------------------------------------------------------------------

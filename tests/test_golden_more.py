@@ -1,0 +1,177 @@
+"""More of the reference's committed float64 oracle files (testdata/golden/*.mim; the cases and their
+meaning are in tools/golden/gen.py): gradients of the tensor ops, scans, sorting, Fourier transforms,
+linear algebra and the rest of the forward cases."""
+import math
+import os
+
+import pytest
+import torch
+
+from _refdir import reference_dir
+
+GOLD = os.environ.get("MIMIR_GOLDEN_DIR") or os.path.join(reference_dir() or "", "testdata", "golden")
+pytestmark = pytest.mark.skipif(not os.path.isdir(GOLD), reason="reference golden files not found")
+
+
+def _open(name):
+    from mimir_b200.io import mim
+    return mim.open(os.path.join(GOLD, name + ".mim"))
+
+
+def _inputs(m, case):
+    ins, i = [], 0
+    while f"{case}/in{i}" in m:
+        ins.append(m.tensor(f"{case}/in{i}").clone())
+        i += 1
+    return ins
+
+
+def _run_case(m, case, fn, tol=2e-5, int_inputs=()):
+    """Forward value and, where the file has them, the gradients of sum(out * gout) with respect to
+    every input that has a ``grad<i>`` entry."""
+    import mimir_b200.tensor as T
+    from mimir_b200.tensor.autograd import Param, backward
+    ins = _inputs(m, case)
+    want = m.tensor(f"{case}/out")
+    diff = [i for i in range(len(ins)) if f"{case}/grad{i}" in m]
+    params, args = {}, []
+    for i, x in enumerate(ins):
+        if i in diff:
+            params[i] = Param(x.clone())
+            args.append(params[i].value())
+        else:
+            args.append(T.tensor(x, dtype=x.dtype, device=T.CPU()))
+    out = fn(*args)
+    assert out.err is None, (case, out.err)
+    if diff:
+        gout = T.tensor(m.tensor(f"{case}/gout").clone(), device=T.CPU())
+        backward(T.sum_(out * T.reshape(gout, tuple(out.shape))))
+    got = out.data()
+    assert tuple(got.shape) == tuple(want.shape) or got.numel() == want.numel(), (case, got.shape, want.shape)
+    scale = max(1.0, float(want.float().abs().max())) if want.numel() else 1.0
+    assert torch.allclose(got.reshape(want.shape).float(), want.float(), rtol=tol, atol=tol * scale), case
+    for i in diff:
+        g, wg = params[i].grad(), m.tensor(f"{case}/grad{i}")
+        assert g is not None, f"{case}: no gradient for input {i}"
+        gs = max(1.0, float(wg.abs().max()))
+        assert torch.allclose(g.data().float(), wg, rtol=tol * 5, atol=tol * 5 * gs), f"{case}/grad{i}"
+
+
+def test_gradients_of_tensor_ops():
+    import mimir_b200.tensor as T
+    G = {
+        "exp": T.exp, "log": T.log, "sin": T.sin, "sqrt": T.sqrt, "recip": T.recip, "sigmoid": T.sigmoid, "tanh": T.tanh,
+        "gelu": T.gelu, "silu": T.silu, "relu": T.relu, "abs": T.abs_,
+        "add": T.add, "sub": T.sub, "mul": T.mul, "div": T.div, "maximum": T.maximum, "minimum": T.minimum,
+        "where": lambda c, x, y: T.where(T.logical_not(T.equal(c, 0.0)), x, y),
+        "sum_axes02": lambda x: T.sum_(x, (0, 2)), "max_axis2": lambda x: T.max_(x, 2), "mean_last": lambda x: T.mean(x, -1),
+        "var_axis1": lambda x: T.var(x, 1), "softmax_axis1": lambda x: T.softmax(x, 1), "log_softmax": lambda x: T.log_softmax(x, -1),
+        "permute_reshape": lambda x: T.reshape(T.permute(x, (2, 0, 1)), (4, 6)),
+        "expand": lambda x: T.expand(x, (2, 3, 4)),
+        "pad": lambda x: T.pad(x, ((1, 0), (2, 1)), -1.0),
+        "shrink_flip_add": lambda x: T.flip(T.shrink(x, ((1, 4), (2, 6))), (0,)) + T.shrink(x, ((0, 3), (0, 4))),
+        "unfold_overlap": lambda x: T.windows(x, 1, 4, 2), "unfold_gapped": lambda x: T.windows(x, 1, 2, 3),
+        "cat": lambda x, y: T.cat([x, y], 1),
+        "matmul_batched": T.matmul, "matmul_vec_mat": T.matmul,
+        "gather": lambda x, i: T.gather(x, 1, i),
+        "scatter_add": lambda x, i, s: T.scatter_add(x, 0, i, s),
+        "conv2d": lambda x, w, b: T.conv2d(x, w, b, padding=1),
+        "conv2d_grouped": lambda x, w: T.conv2d(x, w, None, stride=2, padding=1, dilation=2, groups=2),
+        "max_pool2d": lambda x: T.max_pool2d(x, 2), "max_pool2d_padded": lambda x: T.max_pool2d(x, 3, 2, 1),
+        "avg_pool2d": lambda x: T.avg_pool2d(x, 3, 1, 1),
+        "layer_norm": lambda x, g, b: T.layer_norm(x, g, b, 1e-5),
+        "attention": lambda q, k, v: T.matmul(T.softmax(T.matmul(q, T.transpose(k, -1, -2)) * (1 / math.sqrt(8)), -1), v),
+        "mlp": lambda x, w1, b1, w2, b2: T.log_softmax(T.matmul(T.gelu(T.matmul(x, w1) + b1), w2) + b2, -1),
+    }
+    with _open("grads") as m:
+        cases = sorted({n.split("/")[0] for n in m.names()})
+        assert sorted(G) == cases, sorted(set(cases) ^ set(G))
+        for case in cases:
+            _run_case(m, case, G[case])
+
+
+def test_scans():
+    import mimir_b200.tensor as T
+    S = {
+        "cumsum_axis1": lambda x: T.cumsum(x, 1), "cumsum_last": lambda x: T.cumsum(x, -1), "cumsum_int": lambda x: T.cumsum(x, 1),
+        "cummax_axis1": lambda x: T.cummax(x, 1), "cummax_axis0": lambda x: T.cummax(x, 0),
+        "cummax_indices": lambda x: T.cummax_indices(x, 1),
+        "logcumsumexp_last": lambda x: T.logcumsumexp(x, -1), "logcumsumexp_large": lambda x: T.logcumsumexp(x, 0),
+    }
+    with _open("scan") as m:
+        assert sorted(S) == sorted({n.split("/")[0] for n in m.names()})
+        for case, fn in S.items():
+            _run_case(m, case, fn)
+
+
+def test_sorting_fourier_and_linear_algebra():
+    import mimir_b200.tensor as T
+    eye = lambda x: T.tensor(torch.eye(x.shape[-1]))  # noqa: E731
+    shift = lambda x, by: x + eye(x) * float(by)  # noqa: E731
+    spd = lambda x, by: T.matmul(x, T.transpose(x, -1, -2)) + eye(x) * float(by)  # noqa: E731
+    flat = lambda *ts: T.cat([T.reshape(t, (-1,)) for t in ts], 0)  # noqa: E731
+
+    def svd_parts(x):
+        u, s, vh = T.svd(x)
+        return flat(s, u * u, vh * vh)
+
+    def eigh_parts(x):
+        w, v = T.eigh(x + T.transpose(x, -1, -2))
+        return flat(w, v * v)
+    L = {
+        "sort_values": lambda x: T.sort(x, 1)[0], "sort_descending_indices": lambda x: T.cast(T.sort(x, 1, True)[1], T.int32),
+        "argsort_axis0": lambda x: T.argsort(x, 0), "topk_values": lambda x: T.topk(x, 3, 1)[0],
+        "topk_smallest_indices": lambda x: T.cast(T.topk(x, 2, 0, largest=False)[1], T.int32),
+        "fft": lambda x: T.fft(x, 1), "fft_bluestein": lambda x: T.fft(x, 0), "ifft": lambda x: T.ifft(x, -1),
+        "rfft": lambda x: T.rfft(x, -1), "irfft": lambda x: T.irfft(x, -1, 8), "irfft_odd_padded": lambda x: T.irfft(x, 0, 9),
+        "cholesky": lambda x: T.cholesky(spd(x, 2)),
+        "solve": lambda a, b: T.solve(shift(a, 3), b), "solve_vector": lambda a, b: T.solve(shift(a, 3), b),
+        "triangular_solve_lower": lambda a, b: T.triangular_solve(shift(a, 3), b, upper=False),
+        "triangular_solve_upper": lambda a, b: T.triangular_solve(shift(a, 3), b, upper=True),
+        "inv": lambda x: T.inv(shift(x, 3)), "det": lambda x: T.det(shift(x, 1)),
+        "slogdet_sign": lambda x: T.slogdet(x)[0], "slogdet_logabsdet": lambda x: T.slogdet(x)[1],
+        "qr_tall": lambda x: flat(*T.qr(x)), "qr_wide": lambda x: flat(*T.qr(x)),
+        "svd_tall": svd_parts, "svd_wide": svd_parts, "eigh": eigh_parts,
+    }
+    with _open("linalg") as m:
+        assert sorted(L) == sorted({n.split("/")[0] for n in m.names()})
+        for case, fn in L.items():
+            _run_case(m, case, fn, tol=1e-4)
+    # what the decompositions promise beyond the oracle values
+    a = T.tensor(torch.randn(3, 5, 4))
+    q, r = T.qr(a)
+    assert torch.allclose(T.matmul(q, r).data(), a.data(), atol=1e-5)
+    with pytest.raises(T.ErrSingular):
+        T.cholesky(T.tensor(torch.tensor([[1.0, 2.0], [2.0, 1.0]]))).data()
+    assert isinstance(T.inv(T.tensor(torch.ones(2, 3))).err, T.ErrShape)
+    assert isinstance(T.fft(T.tensor(torch.ones(4, 3))).err, T.ErrShape)
+
+
+def test_remaining_forward_cases():
+    import mimir_b200.tensor as T
+    O = {
+        "cast_f2i": lambda x: T.cast(x, T.int32), "cast_i2f": lambda x: T.cast(x, T.float32),
+        "equal": T.equal, "less": T.less, "greater": T.greater, "exp2": T.exp2, "log2": T.log2, "fmod": T.fmod, "fmod_int": T.fmod,
+        "expand": lambda x: T.expand(x, (2, 3, 4)), "flip": lambda x: T.flip(x, (0, 1)),
+        "gather": lambda x, i: T.gather(x, 1, i), "scatter_add": lambda x, i, s: T.scatter_add(x, 0, i, s),
+        "layer_norm": lambda x, g, b: T.layer_norm(x, g, b, 1e-5),
+        "attention": lambda q, k, v: T.matmul(T.softmax(T.matmul(q, T.transpose(k, -1, -2)) * (1 / math.sqrt(8)), -1), v),
+        "matmul_mat_vec": T.matmul, "matmul_vec_mat": T.matmul, "matmul_transposed": lambda x, y: T.matmul(T.transpose(x, 0, 1), y),
+        "mlp": lambda x, w1, b1, w2, b2: T.log_softmax(T.matmul(T.gelu(T.matmul(x, w1) + b1), w2) + b2, -1),
+        "pad": lambda x: T.pad(x, ((1, 0), (2, 1)), -1.0), "permute_reshape": lambda x: T.reshape(T.permute(x, (2, 0, 1)), (4, 6)),
+        "shrink": lambda x: T.shrink(x, ((1, 4), (2, 6))),
+        "shrink_flip_add": lambda x: T.flip(T.shrink(x, ((1, 4), (2, 6))), (0,)) + T.shrink(x, ((0, 3), (0, 4))),
+        "sum_int": lambda x: T.sum_(x, 1),
+    }
+    with _open("ops") as m:
+        have = {n.split("/")[0] for n in m.names()}
+        for case, fn in O.items():
+            assert case in have, case
+            ins = _inputs(m, case)
+            want = m.tensor(f"{case}/out")
+            got = fn(*[T.tensor(x, dtype=x.dtype, device=T.CPU()) for x in ins]).data()
+            assert tuple(got.shape) == tuple(want.shape), (case, got.shape, want.shape)
+            if want.dtype.is_floating_point:
+                assert torch.allclose(got.float(), want, rtol=2e-5, atol=2e-6 * max(1.0, float(want.abs().max()))), case
+            else:
+                assert torch.equal(got.to(want.dtype), want), case
