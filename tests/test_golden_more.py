@@ -175,3 +175,53 @@ def test_remaining_forward_cases():
                 assert torch.allclose(got.float(), want, rtol=2e-5, atol=2e-6 * max(1.0, float(want.abs().max()))), case
             else:
                 assert torch.equal(got.to(want.dtype), want), case
+
+
+RNN_CASES = {
+    # name: (kind, input size, hidden size, layers, bidirectional, batch_first, relu, bias)
+    "rnn_tanh": ("rnn", 3, 4, 1, False, False, False, True),
+    "rnn_relu_2layer_bidir": ("rnn", 3, 4, 2, True, False, True, True),
+    "lstm": ("lstm", 3, 4, 1, False, False, False, True),
+    "lstm_2layer_bidir": ("lstm", 3, 4, 2, True, False, False, True),
+    "lstm_batch_first_unbiased": ("lstm", 3, 4, 1, False, True, False, False),
+    "lstm_unbatched": ("lstm", 3, 4, 1, False, False, False, True),
+    "gru": ("gru", 3, 4, 1, False, False, False, True),
+    "gru_2layer_bidir_batch_first": ("gru", 3, 4, 2, True, True, False, True),
+}
+
+
+def test_recurrent_layers():
+    """rnn.mim: outputs, final states and the gradients of every input, initial state and weight, for
+    stacked / bidirectional / batch-first / unbiased / unbatched layers with PyTorch's weight layout."""
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.tensor.autograd import Param, backward
+    with _open("rnn") as m:
+        assert sorted(RNN_CASES) == sorted({n.split("/")[0] for n in m.names()})
+        for case, (kind, n_in, hidden, layers, bidir, batch_first, relu, bias) in RNN_CASES.items():
+            ins = _inputs(m, case)
+            ns = 2 if kind == "lstm" else 1
+            kw = dict(bidirectional=bidir, batch_first=batch_first, bias=bias)
+            layer = {"rnn": lambda: nn.RNN(n_in, hidden, layers, relu=relu, **kw), "lstm": lambda: nn.LSTM(n_in, hidden, layers, **kw),
+                     "gru": lambda: nn.GRU(n_in, hidden, layers, **kw)}[kind]()
+            weights = ins[1 + ns:]
+            per = 4 if bias else 2
+            order = []
+            for k in range(layers * (2 if bidir else 1)):
+                order += [layer.w_ih[k], layer.w_hh[k]] + ([layer.b_ih[k], layer.b_hh[k]] if bias else [])
+            assert len(order) == len(weights) and per * len(layer.w_ih) == len(weights)
+            for p, w in zip(order, weights):
+                assert tuple(p.shape) == tuple(w.shape), case
+                p.set(w.clone())
+            x = Param(ins[0].clone())
+            states = [Param(s.clone()) for s in ins[1:1 + ns]]
+            res = layer.run(x.value(), *[s.value() for s in states])
+            joined = T.cat([T.reshape(r, (-1,)) for r in res], 0)
+            gout = T.tensor(m.tensor(f"{case}/gout").clone(), device=T.CPU())
+            backward(T.sum_(joined * gout))
+            assert torch.allclose(joined.data(), m.tensor(f"{case}/out"), rtol=2e-5, atol=2e-6), case
+            assert torch.allclose(res[0].data(), m.tensor(f"{case}/output"), rtol=2e-5, atol=2e-6), case
+            assert torch.allclose(res[1].data(), m.tensor(f"{case}/h_n"), rtol=2e-5, atol=2e-6), case
+            for i, p in enumerate([x] + states + order):
+                want = m.tensor(f"{case}/grad{i}")
+                assert torch.allclose(p.grad().data(), want, rtol=1e-4, atol=1e-5), f"{case}/grad{i}"

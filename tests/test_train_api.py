@@ -57,7 +57,7 @@ def test_layers_run_and_cache_matches_full_sequence():
     cache = nn.KVCache(2, 2, 16, 8)
     step = [blk(T.tensor(x[:, i:i + 1], device=T.CPU()), cache).data() for i in range(5)]
     assert torch.allclose(torch.cat(step, 1), full, atol=1e-5)
-    out, h = nn.LSTM(8, 16, 2)(T.tensor(torch.randn(3, 7, 8), device=T.CPU()))
+    out, h = nn.LSTM(8, 16, 2, batch_first=True)(T.tensor(torch.randn(3, 7, 8), device=T.CPU()))
     assert out.shape == (3, 7, 16) and h.shape == (2, 3, 16)
     g = nn.Graph(4, [0, 1, 2], [1, 2, 3])
     assert nn.GATConv(8, 4, 2)(T.tensor(torch.randn(4, 8), device=T.CPU()), g).data().shape == (4, 8)
