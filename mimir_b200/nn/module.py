@@ -227,11 +227,13 @@ class LayerNorm(Module):
 
 
 class RMSNorm(Module):
-    """Normalises in fp32, rounds to the input dtype, then scales (nn/transformer.go:28-61)."""
+    """Normalises in fp32, rounds to the input dtype, then scales (nn/transformer.go:28-61).  Without
+    an ``eps`` it is float32's machine epsilon (2^-23), the reference's and PyTorch's default; Llama
+    models pass 1e-5 or 1e-6."""
 
-    def __init__(self, dim: int, eps: float = 1e-6, dtype=torch.float32):
+    def __init__(self, dim: int, eps: float | None = None, dtype=torch.float32):
         self.weight = Param(torch.ones(dim, dtype=dtype), "weight")
-        self.eps = eps
+        self.eps = 2.0 ** -23 if eps is None else eps
 
     def forward(self, x):
         return T.rms_norm(x, self.weight.value(), self.eps)

@@ -13,13 +13,13 @@ import torch
 
 from .. import tensor as T
 from ..tensor.autograd import Param
-from .module import LayerNorm, Linear, Module, RMSNorm
+from .module import Dropout, LayerNorm, Linear, Module, RMSNorm, uniform_init
 
 
 class RotaryEmbedding:
     """Rotary position embedding with optional Llama-3 frequency scaling (nn/transformer.go:110,191-259)."""
 
-    def __init__(self, dim: int, base: float = 10000.0, interleaved: bool = True, scaling: dict | None = None):
+    def __init__(self, dim: int, base: float = 10000.0, interleaved: bool = False, scaling: dict | None = None):
         self.dim, self.base, self.interleaved = dim, base, interleaved
         inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
         if scaling:
@@ -35,9 +35,13 @@ class RotaryEmbedding:
                                   torch.where(wl < old / hi, inv, (1 - smooth) * inv / factor + smooth * inv))
         self.inv_freq = inv.float()
 
-    def apply(self, x, positions):
-        """``x`` [B, H, T, D]; ``positions`` an int tensor [T] (lazy or torch)."""
+    def apply(self, x, positions=0):
+        """``x`` [B, H, T, D]; ``positions`` an int tensor [T] (lazy or torch), or the position of the
+        first row (the reference's ``Apply(x, offset)``).  The default pairs column i with column
+        i + dim/2 (GPT-NeoX, Hugging Face Llama); ``interleaved`` pairs (2i, 2i+1) (GPT-J, Meta's Llama)."""
         inv, inter, d = self.inv_freq, self.interleaved, self.dim
+        if isinstance(positions, int):
+            positions = torch.arange(positions, positions + x.shape[-2], dtype=torch.int32)
         pos = positions if isinstance(positions, T.Tensor) else T.tensor(positions, dtype=torch.int32, device=x.device)
 
         def run(v, p):
@@ -133,26 +137,58 @@ class SelfAttention(Module):
 
 
 class MultiheadAttention(Module):
-    """Separate query / key / value inputs (cross attention)."""
+    """Attention over separate query / key / value inputs ``[B, T, dim]`` with the three input
+    projections stored as one ``in_proj_weight [3 dim, dim]`` (rows: query, key, value) and
+    ``in_proj_bias [3 dim]``, then ``out_proj`` (nn/transformer_layers.go: MultiheadAttention).  When
+    the three inputs are one tensor the projection is a single product."""
 
     def __init__(self, dim: int, heads: int, bias: bool = True, dtype=torch.float32):
-        self.heads, self.head_dim = heads, dim // heads
-        self.q, self.k, self.v, self.out = (Linear(dim, dim, bias, dtype) for _ in range(4))
+        if dim % heads:
+            raise ValueError(f"MultiheadAttention: {dim} features do not split into {heads} heads")
+        self.dim, self.heads, self.head_dim = dim, heads, dim // heads
+        bound = math.sqrt(6.0 / (dim + 3 * dim))            # Xavier uniform over the fused matrix
+        self.in_proj_weight = Param(uniform_init((3 * dim, dim), bound, dtype), "in_proj_weight")
+        self.in_proj_bias = Param(torch.zeros(3 * dim, dtype=dtype), "in_proj_bias") if bias else None
+        self.out_proj = Linear(dim, dim, bias, dtype)
 
-    def forward(self, query, key, value, mask=None, causal=False):
+    def _project(self, query, key, value):
+        w = self.in_proj_weight.value()
+        b = self.in_proj_bias.value() if self.in_proj_bias is not None else None
+        E = self.dim
+        if query is key and key is value:
+            return T.split(T.matmul_t(query, w, b), [E, E, E], dim=-1)
+        out = []
+        for i, x in enumerate((query, key, value)):
+            wi = T.shrink(w, ((i * E, (i + 1) * E), (0, E)))
+            bi = T.shrink(b, ((i * E, (i + 1) * E),)) if b is not None else None
+            out.append(T.matmul_t(x, wi, bi))
+        return out
+
+    def forward(self, query, key=None, value=None, mask=None, causal=False):
+        key = query if key is None else key
+        value = key if value is None else value
         B, Tq, C = query.shape
         Tk = key.shape[1]
+        q, k, v = self._project(query, key, value)
         sp = lambda t, n: T.permute(T.reshape(t, (B, n, self.heads, self.head_dim)), (0, 2, 1, 3))  # noqa: E731
-        o = T.attention(sp(self.q(query), Tq), sp(self.k(key), Tk), sp(self.v(value), Tk), causal=causal, mask=mask)
-        return self.out(T.reshape(T.permute(o, (0, 2, 1, 3)), (B, Tq, C)))
+        o = T.attention(sp(q, Tq), sp(k, Tk), sp(v, Tk), causal=causal, mask=mask)
+        return self.out_proj(T.reshape(T.permute(o, (0, 2, 1, 3)), (B, Tq, C)))
+
+
+_ACTIVATIONS = {"gelu": lambda x: T.gelu(x), "gelu_exact": lambda x: T.gelu(x, "none"), "relu": lambda x: T.relu(x),
+                "silu": lambda x: T.silu(x), "tanh": lambda x: T.tanh(x)}
 
 
 class MLP(Module):
-    def __init__(self, dim: int, hidden: int, bias: bool = True, dtype=torch.float32):
+    """``down(act(up(x)))``; ``activation`` is a name ("gelu", the tanh form; "gelu_exact"; "relu"; "silu";
+    "tanh") or a function of one tensor."""
+
+    def __init__(self, dim: int, hidden: int, bias: bool = True, dtype=torch.float32, activation="gelu"):
         self.up, self.down = Linear(dim, hidden, bias, dtype), Linear(hidden, dim, bias, dtype)
+        self.act = _ACTIVATIONS[activation] if isinstance(activation, str) else activation
 
     def forward(self, x):
-        return self.down(T.gelu(self.up(x)))
+        return self.down(self.act(self.up(x)))
 
 
 class GatedMLP(Module):
@@ -183,13 +219,23 @@ class DecoderBlock(Module):
 
 
 class TransformerEncoderLayer(Module):
-    """Post-norm encoder layer (BERT style)."""
+    """Self-attention and a two-layer feed-forward, each with a residual and a LayerNorm
+    (nn/transformer_layers.go: NewTransformerEncoderLayer).  The defaults are the reference's and
+    PyTorch's: ReLU, LayerNorm epsilon 1e-5, dropout 0.1 (active only while training), the norm after
+    each residual; ``norm_first`` moves it in front of each sub-layer, ``activation`` names another
+    function.  The attention's projections are one ``attn.qkv`` matrix ``[3 dim, dim]`` (rows: query,
+    key, value)."""
 
-    def __init__(self, dim: int, heads: int, hidden: int, eps: float = 1e-12, dtype=torch.float32):
+    def __init__(self, dim: int, heads: int, hidden: int, eps: float = 1e-5, dtype=torch.float32,
+                 activation="relu", dropout: float = 0.1, norm_first: bool = False):
         self.attn = SelfAttention(dim, heads, causal=False, dtype=dtype)
         self.norm1, self.norm2 = LayerNorm(dim, eps, dtype), LayerNorm(dim, eps, dtype)
-        self.mlp = MLP(dim, hidden, True, dtype)
+        self.mlp = MLP(dim, hidden, True, dtype, activation)
+        self.drop1, self.drop2, self.norm_first = Dropout(dropout), Dropout(dropout), norm_first
 
     def forward(self, x, mask=None):
-        x = self.norm1(x + self.attn(x, mask=mask))
-        return self.norm2(x + self.mlp(x))
+        if self.norm_first:
+            x = x + self.drop1(self.attn(self.norm1(x), mask=mask))
+            return x + self.drop2(self.mlp(self.norm2(x)))
+        x = self.norm1(x + self.drop1(self.attn(x, mask=mask)))
+        return self.norm2(x + self.drop2(self.mlp(x)))

@@ -997,8 +997,9 @@ def matmul_t(x, w, bias=None):
 
 def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
     """Fused attention over ``[B, H, T, D]`` tensors (tensor/attention.go:81-253): grouped-query
-    heads when ``k``/``v`` have fewer heads, optional causal mask with offset, additive or
-    boolean mask; never materialises the score matrix on the CUDA bf16 path (forward and
+    heads when ``k``/``v`` have fewer heads, optional causal mask (query i sees keys j <= i +
+    ``causal_offset``; 0 by default, so the first query sees the first key alone; a decoding step
+    over a cache of Tk - Tq keys passes that many), additive or boolean mask; never materialises the score matrix on the CUDA bf16 path (forward and
     backward both run the tcgen05 kernels)."""
     args = (q, k, v) + ((mask,) if mask is not None else ())
 
@@ -1007,7 +1008,7 @@ def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
         Hk, Tk = kv.shape[1], kv.shape[2]
         if Hq % Hk:
             raise E.ErrShape(f"attention: {Hq} query heads are not a multiple of {Hk} key heads")
-        off = Tk - Tq if causal_offset is None else causal_offset
+        off = 0 if causal_offset is None else causal_offset
         if not m and _native_ok(qv, kv, vv) and D in (64, 128) and kv.shape == vv.shape:
             from ..ops import functional as NF
             return NF.attention(qv, kv, vv, causal=causal, offset=off, scale=scale)

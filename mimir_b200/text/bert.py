@@ -37,7 +37,7 @@ class Bert(nn.Module):
             e.weight.set(nn.normal_init(tuple(e.weight.shape), 0.02))
         self.norm = nn.LayerNorm(cfg.dim, cfg.eps)
         self.drop = nn.Dropout(cfg.dropout)
-        self.layers = [nn.TransformerEncoderLayer(cfg.dim, cfg.heads, cfg.hidden, cfg.eps) for _ in range(cfg.layers)]
+        self.layers = [nn.TransformerEncoderLayer(cfg.dim, cfg.heads, cfg.hidden, cfg.eps, activation="gelu", dropout=0.0) for _ in range(cfg.layers)]
         self.pooler = nn.Linear(cfg.dim, cfg.dim)
 
     def forward(self, ids, type_ids=None, attention_mask=None):

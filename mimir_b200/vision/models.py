@@ -114,7 +114,7 @@ class ViT(nn.Module):
         n = (image // patch) ** 2
         self.cls = T.Param(torch.zeros(1, 1, dim), "cls")
         self.pos = T.Param(nn.normal_init((1, n + 1, dim), 0.02), "pos")
-        self.layers = [nn.TransformerEncoderLayer(dim, heads, mlp) for _ in range(depth)]
+        self.layers = [nn.TransformerEncoderLayer(dim, heads, mlp, eps=1e-12, activation="gelu", dropout=0.0) for _ in range(depth)]
         self.norm = nn.LayerNorm(dim)
         self.head = nn.Linear(dim, classes)
 

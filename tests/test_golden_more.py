@@ -225,3 +225,169 @@ def test_recurrent_layers():
             for i, p in enumerate([x] + states + order):
                 want = m.tensor(f"{case}/grad{i}")
                 assert torch.allclose(p.grad().data(), want, rtol=1e-4, atol=1e-5), f"{case}/grad{i}"
+
+
+def _run_module(m, case, fn, tol=2e-5):
+    """``fn(ins)`` builds the layer from the case's inputs and returns the output with a map from
+    input index to the ``Param`` whose gradient the file holds as ``grad<i>``."""
+    import mimir_b200.tensor as T
+    from mimir_b200.tensor.autograd import backward
+    ins = _inputs(m, case)
+    want = m.tensor(f"{case}/out")
+    out, graders = fn(ins)
+    assert out.err is None, (case, out.err)
+    gout = T.tensor(m.tensor(f"{case}/gout").clone(), device=T.CPU())
+    backward(T.sum_(out * T.reshape(gout, tuple(out.shape))))
+    got = out.data()
+    scale = max(1.0, float(want.abs().max()))
+    assert torch.allclose(got.reshape(want.shape).float(), want.float(), rtol=tol, atol=tol * scale), case
+    checked = 0
+    for i in range(len(ins)):
+        if f"{case}/grad{i}" not in m:
+            continue
+        assert i in graders, f"{case}: input {i} has a gradient in the file and no parameter here"
+        g, wg = graders[i].grad(), m.tensor(f"{case}/grad{i}")
+        assert g is not None, f"{case}: no gradient for input {i}"
+        gs = max(1.0, float(wg.abs().max()))
+        assert torch.allclose(g.data().float().reshape(wg.shape), wg, rtol=tol * 5, atol=tol * 5 * gs), f"{case}/grad{i}"
+        checked += 1
+    assert checked, case
+    return got
+
+
+def _set(params, values):
+    assert len(params) == len(values)
+    for p, v in zip(params, values):
+        p.set(v)
+    return {i + 1: p for i, p in enumerate(params)}
+
+
+def test_attention_layers_and_blocks():
+    """The cases of attention.mim that go through layers: rotary embeddings, RMS norm, masked and
+    multi-head attention, the GPT-2 and Llama decoder blocks and the encoder layer, with the gradient
+    of every parameter."""
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.tensor.autograd import Param
+    with _open("attention") as m:
+        _run_case(m, "sdpa_bool_mask", lambda q, k, v, keep: T.attention(q, k, v, mask=T.logical_not(T.equal(keep, 0.0))))
+        _run_case(m, "sdpa_mask", lambda q, k, v, mask: T.attention(q, k, v, mask=mask))
+        for case, kw in {"sdpa": {}, "sdpa_causal": dict(causal=True), "sdpa_gqa": dict(causal=True, causal_offset=2),
+                         "sdpa_causal_offset": dict(causal=True, causal_offset=4), "sdpa_scale": dict(scale=0.3)}.items():
+            _run_case(m, case, lambda q, k, v, kw=kw: T.attention(q, k, v, **kw))
+        _run_case(m, "rms_norm", lambda x, w: T.rms_norm(x, w, 1e-6))
+
+        def rms_default(ins):
+            layer = nn.RMSNorm(6)
+            x = Param(ins[0])
+            g = _set([layer.weight], ins[1:])
+            return layer(x.value()), {0: x, **g}
+        _run_module(m, "rms_norm_default_eps", rms_default)
+
+        _run_case(m, "rope_neox", lambda x: nn.RotaryEmbedding(8, 10000.0).apply(x, 3))
+        _run_case(m, "rope_interleaved", lambda x: nn.RotaryEmbedding(8, 10000.0, interleaved=True).apply(x, 3))
+        scaling = dict(type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_context=64)
+        _run_case(m, "rope_partial_scaled", lambda x: nn.RotaryEmbedding(8, 10000.0, scaling=scaling).apply(x, 2))
+
+        def mha(ins):
+            layer = nn.MultiheadAttention(8, 2)
+            x = Param(ins[0])
+            xv = x.value()
+            ps = [layer.in_proj_weight, layer.in_proj_bias, layer.out_proj.weight, layer.out_proj.bias]
+            g = _set(ps, ins[1:])
+            return layer(xv, xv, xv), {0: x, **g}
+        _run_module(m, "multihead_attention", mha)
+
+        def mha_causal(ins):
+            layer = nn.MultiheadAttention(8, 4)
+            q, k, v = (Param(t) for t in ins[:3])
+            ps = [layer.in_proj_weight, layer.in_proj_bias, layer.out_proj.weight, layer.out_proj.bias]
+            g = {i + 3: p for i, p in enumerate(ps)}
+            for p, val in zip(ps, ins[3:]):
+                p.set(val)
+            return layer(q.value(), k.value(), v.value(), causal=True), {0: q, 1: k, 2: v, **g}
+        _run_module(m, "multihead_attention_causal", mha_causal)
+
+        def gpt2(ins):
+            b = nn.DecoderBlock(8, 2, style="gpt2")
+            x = Param(ins[0])
+            ps = [b.norm1.weight, b.norm1.bias, b.attn.qkv.weight, b.attn.qkv.bias, b.attn.out.weight, b.attn.out.bias,
+                  b.norm2.weight, b.norm2.bias, b.mlp.up.weight, b.mlp.up.bias, b.mlp.down.weight, b.mlp.down.bias]
+            g = _set(ps, ins[1:])
+            return b(x.value()), {0: x, **g}
+        _run_module(m, "decoder_block_gpt2", gpt2)
+
+        def llama(ins):
+            b = nn.DecoderBlock(16, 4, hidden=24, kv_heads=2, style="llama", rope=nn.RotaryEmbedding(4, 10000.0))
+            x = Param(ins[0])
+            ps = [b.norm1.weight, b.attn.qkv.weight, b.attn.out.weight, b.norm2.weight,
+                  b.mlp.gate.weight, b.mlp.up.weight, b.mlp.down.weight]
+            g = _set(ps, ins[1:])
+            return b(x.value()), {0: x, **g}
+        _run_module(m, "decoder_block_llama", llama)
+
+        def encoder(ins):
+            l = nn.TransformerEncoderLayer(8, 2, 16).eval()
+            x = Param(ins[0])
+            ps = [l.attn.qkv.weight, l.attn.qkv.bias, l.attn.out.weight, l.attn.out.bias, l.mlp.up.weight, l.mlp.up.bias,
+                  l.mlp.down.weight, l.mlp.down.bias, l.norm1.weight, l.norm1.bias, l.norm2.weight, l.norm2.bias]
+            g = _set(ps, ins[1:])
+            return l(x.value()), {0: x, **g}
+        _run_module(m, "transformer_encoder_layer", encoder)
+
+
+def test_layers_of_nn_mim():
+    """linear, layer norm, batch norm (with its running statistics), embedding and cross-entropy over
+    an extra axis, with gradients."""
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.nn import loss as L
+    from mimir_b200.tensor.autograd import Param
+    with _open("nn") as m:
+        def linear(ins):
+            layer = nn.Linear(6, 3)
+            x = Param(ins[0])
+            g = _set([layer.weight, layer.bias], ins[1:])
+            return layer(x.value()), {0: x, **g}
+        _run_module(m, "linear", linear)
+
+        def layer_norm(ins):
+            layer = nn.LayerNorm(8)
+            x = Param(ins[0])
+            g = _set([layer.weight, layer.bias], ins[1:])
+            return layer(x.value()), {0: x, **g}
+        _run_module(m, "layer_norm", layer_norm)
+
+        for case, cls, ch in (("batch_norm1d", nn.BatchNorm1d, 5), ("batch_norm2d", nn.BatchNorm2d, 3)):
+            holder = {}
+
+            def bn(ins, cls=cls, ch=ch, holder=holder):
+                layer = holder["layer"] = cls(ch)
+                x = Param(ins[0])
+                g = _set([layer.weight, layer.bias], ins[1:])
+                return layer(x.value()), {0: x, **g}
+            _run_module(m, case, bn)
+            layer = holder["layer"]
+            for name in ("running_mean", "running_var"):
+                got, want = getattr(layer, name).value().data(), m.tensor(f"{case}/{name}")
+                assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), (case, name)
+
+        def bn_eval(ins):
+            layer = nn.BatchNorm2d(3).eval()
+            layer.running_mean.set(ins[1])
+            layer.running_var.set(ins[2])
+            x = Param(ins[0])
+            layer.weight.set(ins[3])
+            layer.bias.set(ins[4])
+            return layer(x.value()), {0: x, 3: layer.weight, 4: layer.bias}
+        _run_module(m, "batch_norm_eval", bn_eval)
+
+        def embedding(ins):
+            layer = nn.Embedding(5, 4)
+            layer.weight.set(ins[1])
+            return layer(T.tensor(ins[0], dtype=ins[0].dtype, device=T.CPU())), {1: layer.weight}
+        _run_module(m, "embedding", embedding)
+
+        for case, fn in {"cross_entropy_kdim": L.cross_entropy, "cross_entropy": L.cross_entropy, "nll": L.nll,
+                         "mse": L.mse, "l1": L.l1, "huber": L.huber, "bce_with_logits": L.bce_with_logits}.items():
+            _run_case(m, case, fn)
