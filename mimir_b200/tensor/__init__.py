@@ -6,6 +6,7 @@ from .autograd import Param, Buffer, backward, gradients, grad, vjp, jvp, jacobi
 from .loop import scan, record, record_into, Recording, trace, TracedGraph  # noqa: F401
 from .memory import set_memory_budget, memory_budget, memory_of  # noqa: F401
 from .random import philox_uniform, philox_normal, splitmix64  # noqa: F401
+from .pattern import Pattern, segment  # noqa: F401
 from .linalg import (exp2, log2, greater, fmod, fft, ifft, rfft, irfft, cholesky, triangular_solve, solve, inv, det,  # noqa: F401
                      slogdet, qr, svd, eigh, rand_gamma, rand_poisson)
 from . import group  # noqa: F401,E402

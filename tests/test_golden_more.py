@@ -391,3 +391,50 @@ def test_layers_of_nn_mim():
         for case, fn in {"cross_entropy_kdim": L.cross_entropy, "cross_entropy": L.cross_entropy, "nll": L.nll,
                          "mse": L.mse, "l1": L.l1, "huber": L.huber, "bce_with_logits": L.bce_with_logits}.items():
             _run_case(m, case, fn)
+
+
+def test_graph_layers():
+    """gnn.mim: aggregation of edge messages, the softmax over incoming edges, and the GCN / GraphSAGE /
+    GAT convolutions with the gradient of every parameter."""
+    import mimir_b200.tensor as T
+    from mimir_b200 import nn
+    from mimir_b200.tensor.autograd import Param
+    with _open("gnn") as m:
+        nodes = m.tensor("gcn/in0").shape[0]
+
+        def graph(ei):
+            return nn.Graph.from_edge_index(nodes, ei)
+
+        for reduce in ("sum", "mean", "max"):
+            def agg(ins, reduce=reduce):
+                msg = Param(ins[0])
+                return getattr(graph(ins[1]), reduce)(msg.value()), {0: msg}
+            _run_module(m, f"aggregate_{reduce}", agg)
+
+        def edge_softmax(ins):
+            s = Param(ins[0])
+            return graph(ins[1]).softmax(s.value()), {0: s}
+        _run_module(m, "edge_softmax", edge_softmax)
+
+        def gcn(ins):
+            c = nn.GCNConv(5, 4)
+            x = Param(ins[0])
+            c.weight.set(ins[2]); c.bias.set(ins[3])
+            return c.convolve(graph(ins[1]), x.value()), {0: x, 2: c.weight, 3: c.bias}
+        _run_module(m, "gcn", gcn)
+
+        def sage(ins):
+            c = nn.SAGEConv(5, 4)
+            x = Param(ins[0])
+            c.neighbors.weight.set(ins[2]); c.neighbors.bias.set(ins[3]); c.root.weight.set(ins[4])
+            return c.convolve(graph(ins[1]), x.value()), {0: x, 2: c.neighbors.weight, 3: c.neighbors.bias, 4: c.root.weight}
+        _run_module(m, "sage", sage)
+
+        for case, mean_heads in (("gat_concat", False), ("gat_mean", True)):
+            def gat(ins, mean_heads=mean_heads):
+                c = nn.GATConv(5, 3, heads=2, mean_heads=mean_heads)
+                x = Param(ins[0])
+                for p, v in zip((c.weight, c.att_src, c.att_dst, c.bias), ins[2:]):
+                    p.set(v)
+                return c.convolve(graph(ins[1]), x.value()), {0: x, 2: c.weight, 3: c.att_src, 4: c.att_dst, 5: c.bias}
+            _run_module(m, case, gat)
