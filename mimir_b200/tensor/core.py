@@ -568,6 +568,9 @@ def _broadcast(p, q):
     return tuple(out)
 
 
+_BOOL_RESULT = ("less", "equal", "logical_and", "logical_or")
+
+
 def _binary(opname, fn, out_bool=False):
     def op(a, b):
         like = a if isinstance(a, Tensor) else b
@@ -594,7 +597,7 @@ def _binary(opname, fn, out_bool=False):
         # dtype (comparisons: bool); shapes that do not broadcast go through the inference and come
         # back as a sticky error
         shape = _broadcast(a.shape, b.shape)
-        known = None if shape is None else (shape, torch.bool if opname in ("less", "equal") else dt)
+        known = None if shape is None else (shape, torch.bool if opname in _BOOL_RESULT else dt)
         return _node(run, (a, b), {}, opname, attrs={"kind": "binary"}, known=known)
     op.__name__ = opname
     return op
@@ -618,6 +621,8 @@ pow_ = _binary("pow", torch.pow)
 less = _binary("less", torch.lt)
 equal = _binary("equal", torch.eq)
 mod = _binary("mod", torch.remainder)
+logical_and = _binary("logical_and", torch.logical_and)     # non-zero counts as true, like the comparisons' results
+logical_or = _binary("logical_or", torch.logical_or)
 
 
 def _unary(opname, fn, native_mode=None, same_type=True):

@@ -438,3 +438,60 @@ def test_graph_layers():
                     p.set(v)
                 return c.convolve(graph(ins[1]), x.value()), {0: x, 2: c.weight, 3: c.att_src, 4: c.att_dst, 5: c.bias}
             _run_module(m, case, gat)
+
+
+def test_distributions_and_special_functions():
+    """distributions.mim: log-probabilities, entropies, variances, CDFs and KL divergences of the eleven
+    families, and the special functions under them, with the gradient of every float input."""
+    import mimir_b200.tensor as T
+    from mimir_b200 import distributions as D
+    two = lambda cls: (lambda a, b, c, d: D.kl(cls(a, b), cls(c, d)))  # noqa: E731
+    one = lambda make: (lambda a, b: D.kl(make(a), make(b)))  # noqa: E731
+    cases = {
+        "normal_log_prob": lambda m, s, x: D.Normal(m, s).log_prob(x),
+        "normal_entropy": lambda m, s: D.Normal(m, s).entropy(),
+        "normal_cdf": lambda m, s, x: D.Normal(m, s).cdf(x),
+        "normal_icdf": lambda m, s, p: D.Normal(m, s).icdf(p),
+        "normal_kl": two(D.Normal),
+        "mvn_log_prob": lambda m, l, x: D.MultivariateNormal(m, scale_tril=l).log_prob(x),
+        "mvn_entropy": lambda m, l: D.MultivariateNormal(m, scale_tril=l).entropy(),
+        "mvn_variance": lambda m, l: D.MultivariateNormal(m, scale_tril=l).variance(),
+        "mvn_kl": lambda a, b, c, d: D.kl(D.MultivariateNormal(a, scale_tril=b), D.MultivariateNormal(c, scale_tril=d)),
+        "bernoulli_log_prob": lambda l, x: D.Bernoulli(logits=l).log_prob(x),
+        "bernoulli_probs_log_prob": lambda p, x: D.Bernoulli(probs=p).log_prob(x),
+        "bernoulli_entropy": lambda l: D.Bernoulli(logits=l).entropy(),
+        "bernoulli_kl": one(lambda p: D.Bernoulli(probs=p)),
+        "categorical_log_prob": lambda l, x: D.Categorical(logits=l).log_prob(x),
+        "categorical_probs_log_prob": lambda p, x: D.Categorical(probs=p).log_prob(x),
+        "categorical_entropy": lambda l: D.Categorical(logits=l).entropy(),
+        "categorical_kl": one(lambda l: D.Categorical(logits=l)),
+        "uniform_log_prob": lambda lo, hi, x: D.Uniform(lo, hi).log_prob(x),
+        "uniform_entropy": lambda lo, hi: D.Uniform(lo, hi).entropy(),
+        "uniform_kl": two(D.Uniform),
+        "exponential_log_prob": lambda r, x: D.Exponential(r).log_prob(x),
+        "exponential_entropy": lambda r: D.Exponential(r).entropy(),
+        "exponential_kl": one(D.Exponential),
+        "laplace_log_prob": lambda m, s, x: D.Laplace(m, s).log_prob(x),
+        "laplace_entropy": lambda m, s: D.Laplace(m, s).entropy(),
+        "laplace_kl": two(D.Laplace),
+        "gamma_log_prob": lambda a, b, x: D.Gamma(a, b).log_prob(x),
+        "gamma_entropy": lambda a, b: D.Gamma(a, b).entropy(),
+        "gamma_kl": two(D.Gamma),
+        "beta_log_prob": lambda a, b, x: D.Beta(a, b).log_prob(x),
+        "beta_entropy": lambda a, b: D.Beta(a, b).entropy(),
+        "beta_kl": two(D.Beta),
+        "dirichlet_log_prob": lambda a, x: D.Dirichlet(a).log_prob(x),
+        "dirichlet_entropy": lambda a: D.Dirichlet(a).entropy(),
+        "dirichlet_variance": lambda a: D.Dirichlet(a).variance(),
+        "dirichlet_kl": one(D.Dirichlet),
+        "poisson_log_prob": lambda r, k: D.Poisson(r).log_prob(k),
+        "poisson_entropy": lambda r: D.Poisson(r).entropy(),
+        "poisson_kl": one(D.Poisson),
+        "special_digamma": T.digamma, "special_erf": T.erf, "special_erfinv": T.erfinv, "special_expm1": T.expm1,
+        "special_lgamma": T.lgamma, "special_lgamma_negative": T.lgamma, "special_log1p": T.log1p,
+    }
+    with _open("distributions") as m:
+        names = {n.split("/")[0] for n in m.names()}
+        assert names == set(cases), names ^ set(cases)
+        for case, fn in cases.items():
+            _run_case(m, case, fn, tol=5e-5)
