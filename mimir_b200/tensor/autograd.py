@@ -309,42 +309,59 @@ def _untrace(t: C.Tensor):
     return v
 
 
+def _value(x):
+    """The torch value a transform starts from.  Inside another transform (a gradient under ``jvp`` or
+    ``vmap``) the value is that transform's tracer and must keep its tangent or batch level, so it is
+    not detached."""
+    from .memory import in_transform
+    return _untrace(x) if in_transform() else x.data()
+
+
 def grad(f, argnums=0):
     """``grad(f)(x...)`` = gradient of the scalar ``f`` (tensor.Grad)."""
     def run(*xs):
-        vals = [x.data() for x in xs]
+        vals = [_value(x) for x in xs]
         out = torch.func.grad(_wrap_fn(f), argnums=argnums)(*vals)
         return tuple(C.from_torch(o) for o in out) if isinstance(out, tuple) else C.from_torch(out)
     return run
 
 
-def vjp(f, *xs):
-    out, pull = torch.func.vjp(_wrap_fn(f), *[x.data() for x in xs])
+def _lift_out(o):
+    """torch results (one tensor or a tuple of them) as lazy tensors."""
+    return tuple(C.from_torch(v) for v in o) if isinstance(o, (tuple, list)) else C.from_torch(o)
 
-    def pullback(ct):
-        res = pull(ct.data())
+
+def vjp(f, *xs):
+    """``f(x...)`` (one tensor or a tuple) and the function from cotangents of the outputs to the
+    gradients of the inputs (tensor.VJP)."""
+    out, pull = torch.func.vjp(_wrap_fn(f), *[_value(x) for x in xs])
+
+    def pullback(*ct):
+        res = pull(tuple(_value(c) for c in ct) if isinstance(out, tuple) else _value(ct[0]))
         return tuple(C.from_torch(r) for r in res)
-    return C.from_torch(out), pullback
+    return _lift_out(out), pullback
 
 
 def jvp(f, xs, tangents):
-    out, tan = torch.func.jvp(_wrap_fn(f), tuple(x.data() for x in xs), tuple(t.data() for t in tangents))
-    return C.from_torch(out), C.from_torch(tan)
+    """``f(x...)`` and its derivative along ``tangents`` (tensor.JVP); ``f`` may return a tuple, as
+    ``grad(g)`` of several arguments does, which makes ``jvp(grad(g), x, v)`` a Hessian-vector product."""
+    out, tan = torch.func.jvp(_wrap_fn(f), tuple(_value(x) for x in xs), tuple(_value(t) for t in tangents))
+    return _lift_out(out), _lift_out(tan)
 
 
 def jacobian(f, x):
-    return C.from_torch(torch.func.jacrev(_wrap_fn(f))(x.data()))
+    return C.from_torch(torch.func.jacrev(_wrap_fn(f))(_value(x)))
 
 
 def hessian(f, x):
-    return C.from_torch(torch.func.hessian(_wrap_fn(f))(x.data()))
+    return C.from_torch(torch.func.hessian(_wrap_fn(f))(_value(x)))
 
 
 def vmap(f, in_axes=0, out_axes=0):
     """Vectorises ``f`` over an axis (tensor.VMap with InAxes / OutAxes)."""
     def run(*xs):
         try:
-            out = torch.func.vmap(_wrap_fn(f), in_dims=in_axes, out_dims=out_axes)(*[x.data() for x in xs])
+            out = torch.func.vmap(_wrap_fn(f), in_dims=in_axes, out_dims=out_axes)(*[_value(x) for x in xs])
         except RuntimeError as exc:
             raise E.ErrNotBatchable(str(exc)) from exc
         return tuple(C.from_torch(o) for o in out) if isinstance(out, tuple) else C.from_torch(out)

@@ -790,6 +790,9 @@ def contiguous(x):
 
 
 def _check_index(i, n, opname):
+    # a batched index (under vmap) cannot be read on the host; the torch op checks the bounds itself there
+    if torch._C._functorch.is_functorch_wrapped_tensor(i):
+        return
     if i.device.type != "meta" and i.numel() and (int(i.min()) < 0 or int(i.max()) >= n):
         raise E.ErrIndex(f"{opname}: index outside [0, {n})")
 
@@ -1030,6 +1033,11 @@ def attention(q, k, v, causal=False, causal_offset=None, mask=None, scale=None):
             if mm.dtype == torch.bool:
                 mm = torch.zeros_like(mm, dtype=qv.dtype).masked_fill(~mm, float("-inf"))
             am = mm if am is None else am + mm
+        if _mem.in_transform():
+            # the fused library kernel has no forward-mode derivative: under jvp / vmap / nested
+            # gradients the scores are written out in ops that have every rule
+            s = torch.matmul(qv, kv.transpose(-1, -2)) * (scale if scale is not None else 1.0 / math.sqrt(D))
+            return torch.matmul(torch.softmax(s if am is None else s + am, -1), vv)
         return torch.nn.functional.scaled_dot_product_attention(qv, kv, vv, attn_mask=am, scale=scale)
     return _node(run, args, {}, "attention", attrs={"causal": causal, "mask": mask is not None})
 

@@ -495,3 +495,81 @@ def test_distributions_and_special_functions():
         assert names == set(cases), names ^ set(cases)
         for case, fn in cases.items():
             _run_case(m, case, fn, tol=5e-5)
+
+
+def test_function_transforms():
+    """transforms.mim: Hessian-vector products (a forward derivative of a gradient), forward derivatives,
+    Jacobians, a Hessian and per-example gradients (a gradient mapped over the batch)."""
+    import mimir_b200.tensor as T
+    from mimir_b200.tensor import autograd as A
+
+    def mlp_energy(x, w1, b1, w2):
+        y = T.matmul(T.tanh(T.matmul(x, w1) + b1), w2)
+        return T.sum_(y * y) * 0.25
+
+    def xent(x, w, y):
+        return T.neg(T.mean(T.gather(T.log_softmax(T.matmul(x, w), -1), 1, T.unsqueeze(y, 1))))
+
+    def conv_pool(x, w, b, g):
+        y = T.max_pool2d(T.conv2d(x, w, b, padding=1), 2)
+        return T.sum_(y * y * g)
+
+    def per_example(x, y, w1, b1, w2):
+        logits = T.matmul(T.relu(T.matmul(x, w1) + b1), w2)
+        return T.neg(T.squeeze(T.gather(T.log_softmax(logits, -1), 0, T.unsqueeze(y, 0)), 0))
+
+    cases = {
+        "hvp_mlp": ("hvp", [0, 1, 2, 3], mlp_energy),
+        "hvp_cross_entropy": ("hvp", [0, 1], xent),
+        "hvp_attention_causal": ("hvp", [0, 1, 2], lambda q, k, v, w: T.sum_(T.attention(q, k, v, causal=True, causal_offset=2) * w)),
+        "hvp_conv_pool": ("hvp", [0, 1, 2], conv_pool),
+        "hvp_logcumsumexp": ("hvp", [0], lambda x, g: T.sum_(T.logcumsumexp(x, -1) * g)),
+        "jvp_mlp": ("jvp", [0, 1, 2], lambda x, w, b: T.tanh(T.matmul(x, w) + b)),
+        "jvp_attention_gqa": ("jvp", [0, 1, 2], lambda q, k, v: T.attention(q, k, v)),
+        "jvp_softmax_cumsum": ("jvp", [0], lambda x: T.cumsum(T.softmax(x, -1), 0)),
+        "jvp_conv_avg_pool": ("jvp", [0, 1], lambda x, w: T.avg_pool2d(T.conv2d(x, w, None, padding=1), 2)),
+        "jacobian_softmax": ("jac", [0], lambda x, w: T.softmax(T.matmul(x, w), -1)),
+        "jacobian_rows": ("jac", [0], lambda x, w: T.sum_(T.tanh(T.matmul(x, w)), 0)),
+        "hessian_logsumexp": ("hess", [0], lambda x, w: T.log(T.sum_(T.exp(T.matmul(T.sin(x), w))))),
+        "per_example_mlp": ("perex", [2, 3, 4], per_example),
+    }
+
+    def close(got, want, what):
+        got = got.data() if hasattr(got, "data") and callable(got.data) else got
+        assert torch.allclose(got.float().reshape(want.shape), want, rtol=1e-4, atol=1e-5), what
+
+    with _open("transforms") as m:
+        assert {n.split("/")[0] for n in m.names()} == set(cases)
+        for case, (kind, diff, f) in cases.items():
+            ins = [T.tensor(x, dtype=x.dtype, device=T.CPU()) for x in _inputs(m, case)]
+
+            def partial(*x, f=f, ins=ins, diff=diff):
+                args = list(ins)
+                for k, i in enumerate(diff):
+                    args[i] = x[k]
+                return f(*args)
+            x = [ins[i] for i in diff]
+            if kind != "perex":
+                close(partial(*x), m.tensor(f"{case}/out"), case)
+            if kind == "hvp":
+                v = [T.tensor(m.tensor(f"{case}/vec{i}").clone()) for i in diff]
+                _, hv = A.jvp(A.grad(partial, argnums=tuple(range(len(diff)))), x, v)
+                for k, i in enumerate(diff):
+                    close(hv[k], m.tensor(f"{case}/hvp{i}"), f"{case}/hvp{i}")
+            elif kind == "jvp":
+                v = [T.tensor(m.tensor(f"{case}/tan{i}").clone()) for i in diff]
+                y, tan = A.jvp(partial, x, v)
+                close(y, m.tensor(f"{case}/out"), case)
+                close(tan, m.tensor(f"{case}/jvp"), f"{case}/jvp")
+            elif kind == "jac":
+                close(A.jacobian(partial, x[0]), m.tensor(f"{case}/jac"), f"{case}/jac")
+            elif kind == "hess":
+                close(A.hessian(partial, x[0]), m.tensor(f"{case}/hess"), f"{case}/hess")
+            else:
+                def one(ex_x, ex_y, f=f, x=x):
+                    loss = lambda *p: f(ex_x, ex_y, *p)  # noqa: E731
+                    return (loss(*x),) + tuple(A.grad(loss, argnums=(0, 1, 2))(*x))
+                got = A.vmap(one)(ins[0], ins[1])
+                close(got[0], m.tensor(f"{case}/out"), case)
+                for k, i in enumerate(diff):
+                    close(got[1 + k], m.tensor(f"{case}/pergrad{i}"), f"{case}/pergrad{i}")
