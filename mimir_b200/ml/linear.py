@@ -178,3 +178,192 @@ class KernelSVM:
 
     def classify(self, X):
         return (self.decision(X) > 0).long()
+
+
+# ---------------------------------------------------------------------------------------------
+# Fitted linear models over a table (reference: linear/linear.go, linear/fit.go, linear/lbfgs.go)
+# ---------------------------------------------------------------------------------------------
+from .base import CLASSIFICATION, REGRESSION, Model, Standard, as_rows, count_classes  # noqa: E402
+
+
+class Linear(Model):
+    """For each output a weight per feature and a bias, in the features' own units, passed through
+    ``link`` ("identity", "sigmoid" for two classes, "softmax" for more).  ``predict`` returns one value
+    per row for regression and ``classes`` probabilities per row for classification."""
+
+    FIELDS = ("task", "features", "classes", "weights", "bias", "link", "fill")
+
+    def weight(self, o: int, j: int) -> float:
+        return float(self.weights[o, j])
+
+    def decision(self, X) -> torch.Tensor:
+        X = as_rows(X, self.features)
+        X = torch.where(torch.isnan(X), self.fill.to(X), X) if torch.isnan(X).any() else X
+        return X @ self.weights.t().to(X) + self.bias.to(X)
+
+    def predict(self, X) -> torch.Tensor:
+        z = self.decision(X)
+        if self.link == "identity":
+            return z[:, 0]
+        if self.link == "sigmoid":
+            p = torch.sigmoid(z[:, 0])
+            return torch.stack([1 - p, p], 1)
+        return torch.softmax(z, 1)
+
+    def module(self):
+        from .modules import LinearModule
+        return LinearModule.of(self)
+
+
+def _unscale(w_std, b_std, std: Standard):
+    """Weights of standardized features as weights of the features themselves."""
+    w = w_std / std.scale.double()
+    return w.float(), (b_std - w @ std.mean.double()).float()
+
+
+def regression(d, l1: float = 0.0, l2: float = 0.0, max_iter: int = 1000, tol: float = 1e-6) -> Linear:
+    """Least squares with optional lasso (``l1``) and ridge (``l2``) penalties on standardized features:
+    ``1/(2n) |y - Xw - b|^2 + l1 |w|_1 + l2/2 |w|^2``.  Without ``l1`` the normal equations are solved
+    directly; with it, coordinate descent runs on the Gram matrix until a pass changes no weight by more
+    than ``tol``."""
+    d.check(REGRESSION)
+    if l1 < 0 or l2 < 0 or max_iter < 1 or tol < 0:
+        raise ValueError("penalties, passes and tolerance must not be negative")
+    std = Standard.fit(d.X)
+    Z = std.apply(d.X).double()
+    y = d.Y.double()
+    n, F = Z.shape
+    ym = y.mean()
+    G, c = Z.t() @ Z / n, Z.t() @ (y - ym) / n
+    if l1 == 0:
+        A = G + l2 * torch.eye(F, dtype=torch.double)
+        w = torch.linalg.lstsq(A, c.unsqueeze(1)).solution[:, 0] if l2 == 0 else torch.linalg.solve(A, c)
+    else:
+        w = torch.zeros(F, dtype=torch.double)
+        diag = G.diagonal()
+        for _ in range(max_iter):
+            moved = 0.0
+            for j in range(F):
+                if diag[j] <= 0:
+                    continue
+                rho = float(c[j] - G[j] @ w + diag[j] * w[j])
+                new = (abs(rho) - l1) / float(diag[j] + l2)
+                new = 0.0 if new <= 0 else (new if rho > 0 else -new)
+                moved = max(moved, abs(new - float(w[j])))
+                w[j] = new
+            if moved <= tol:
+                break
+    wt, b = _unscale(w.unsqueeze(0), ym.unsqueeze(0), std)
+    m = Linear()
+    m.task, m.features, m.classes, m.weights, m.bias, m.link, m.fill = REGRESSION, F, 0, wt, b, "identity", std.mean
+    return m
+
+
+def _lbfgs(f, x0, max_iter, tol, history=10):
+    """Limited-memory BFGS with a backtracking Armijo line search; ``f(x) -> (value, gradient)``.  Stops
+    once no part of the gradient exceeds ``tol``."""
+    x = x0.clone()
+    fx, g = f(x)
+    S, Y = [], []
+    for _ in range(max_iter):
+        if float(g.abs().max()) <= tol:
+            break
+        q = g.clone()
+        alphas = []
+        for s, yv in zip(reversed(S), reversed(Y)):
+            a = (s @ q) / (yv @ s)
+            alphas.append(a)
+            q -= a * yv
+        if S:
+            q *= (S[-1] @ Y[-1]) / (Y[-1] @ Y[-1])
+        for (s, yv), a in zip(zip(S, Y), reversed(alphas)):
+            q += (a - (yv @ q) / (yv @ s)) * s
+        p = -q
+        slope = float(g @ p)
+        if slope >= 0:                      # not a descent direction: restart from the gradient
+            p, slope, S, Y = -g, -float(g @ g), [], []
+        step, ok = 1.0 if S else min(1.0, 1.0 / max(float(g.norm()), 1e-12)), False
+        for _ in range(40):
+            xn = x + step * p
+            fn, gn = f(xn)
+            if float(fn) <= float(fx) + 1e-4 * step * slope:
+                ok = True
+                break
+            step *= 0.5
+        if not ok:
+            break
+        s, yv = xn - x, gn - g
+        if float(s @ yv) > 1e-12:
+            S.append(s)
+            Y.append(yv)
+            if len(S) > history:
+                S.pop(0)
+                Y.pop(0)
+        x, fx, g = xn, fn, gn
+    return x
+
+
+def logistic_fit(d, l1: float = 0.0, l2: float | None = None, classes: int = 0, max_iter: int = 1000,
+                 tol: float = 1e-6) -> Linear:
+    """Logistic (two classes) or softmax regression on standardized features.  ``l2`` defaults to one over
+    the number of rows (the penalty of scikit-learn's ``C = 1``).  Without ``l1`` the loss is minimised by
+    L-BFGS until no part of the gradient exceeds ``tol``; with it by accelerated proximal gradient steps
+    whose soft threshold drives the weights of unhelpful features to exactly zero."""
+    d.check(CLASSIFICATION)
+    K = count_classes(d.Y, classes)
+    if K < 2:
+        raise ValueError("logistic regression needs at least two classes")
+    std = Standard.fit(d.X)
+    Z = std.apply(d.X).double()
+    n, F = Z.shape
+    l2 = 1.0 / n if l2 is None else l2
+    if l1 < 0 or l2 < 0:
+        raise ValueError("penalties must not be negative")
+    outs = 1 if K == 2 else K
+    y = d.Y.long()
+    onehot = torch.nn.functional.one_hot(y, K).double()
+
+    def smooth(theta):
+        W, b = theta[:outs * F].reshape(outs, F), theta[outs * F:]
+        z = Z @ W.t() + b
+        if outs == 1:
+            t = onehot[:, 1]
+            loss = (torch.clamp(z[:, 0], min=0) - z[:, 0] * t + torch.log1p(torch.exp(-z[:, 0].abs()))).mean()
+            r = (torch.sigmoid(z[:, 0]) - t).unsqueeze(1)
+        else:
+            lp = torch.log_softmax(z, 1)
+            loss = -(lp * onehot).sum(1).mean()
+            r = lp.exp() - onehot
+        gW = r.t() @ Z / n + l2 * W
+        return loss + 0.5 * l2 * (W * W).sum(), torch.cat([gW.reshape(-1), r.mean(0)])
+
+    theta = torch.zeros(outs * F + outs, dtype=torch.double)
+    if l1 == 0:
+        theta = _lbfgs(smooth, theta, max_iter, tol)
+    else:
+        # FISTA with backtracking on the smooth part; the bias is not penalised
+        mask = torch.cat([torch.ones(outs * F), torch.zeros(outs)]).double()
+        L, t, zk = 1.0, 1.0, theta.clone()
+        for _ in range(max_iter):
+            fz, gz = smooth(zk)
+            while True:
+                u = zk - gz / L
+                new = torch.where(mask > 0, torch.sign(u) * torch.clamp(u.abs() - l1 / L, min=0), u)
+                diff = new - zk
+                if float(smooth(new)[0]) <= float(fz + gz @ diff + 0.5 * L * (diff @ diff)) + 1e-12:
+                    break
+                L *= 2.0
+            t_new = (1 + (1 + 4 * t * t) ** 0.5) / 2
+            zk = new + (t - 1) / t_new * (new - theta)
+            moved = float((new - theta).abs().max())
+            theta, t = new, t_new
+            if moved <= tol:
+                break
+    W, b = theta[:outs * F].reshape(outs, F), theta[outs * F:]
+    scale = std.scale.double()
+    Wu = W / scale
+    m = Linear()
+    m.task, m.features, m.classes = CLASSIFICATION, F, K
+    m.weights, m.bias = Wu.float(), (b - Wu @ std.mean.double()).float()
+    m.link, m.fill = ("sigmoid" if outs == 1 else "softmax"), std.mean
+    return m

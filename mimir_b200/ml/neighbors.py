@@ -201,3 +201,75 @@ def ward(X, k):
         label[label == label[j]] = label[i]
     _, out = torch.unique(label, return_inverse=True)
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# k nearest neighbours over a table (reference: neighbors/neighbors.go)
+# ---------------------------------------------------------------------------------------------
+from .base import CLASSIFICATION, REGRESSION, Model, Standard, as_rows, as_task, count_classes  # noqa: E402
+
+EUCLIDEAN, MANHATTAN, COSINE = "euclidean", "manhattan", "cosine"
+METRICS = (EUCLIDEAN, MANHATTAN, COSINE)
+
+
+def distances(metric: str, Q: torch.Tensor, R: torch.Tensor) -> torch.Tensor:
+    """``[queries, rows]`` distances: Euclidean and cosine are one matrix product plus norms; Manhattan
+    sums absolute differences in blocks of queries."""
+    if metric == EUCLIDEAN:
+        return pairwise_sq(Q, R).clamp_min(0).sqrt()
+    if metric == COSINE:
+        qn = Q / Q.norm(dim=1, keepdim=True).clamp_min(1e-12)
+        rn = R / R.norm(dim=1, keepdim=True).clamp_min(1e-12)
+        return (1.0 - qn @ rn.t()).clamp_min(0)
+    if metric == MANHATTAN:
+        block = max(1, (1 << 24) // max(R.numel(), 1))
+        return torch.cat([(Q[i:i + block, None, :] - R[None]).abs().sum(-1) for i in range(0, Q.shape[0], block)]) \
+            if Q.shape[0] else torch.zeros(0, R.shape[0])
+    raise ValueError(f"unknown metric {metric!r}: want one of {METRICS}")
+
+
+class Neighbors(Model):
+    """The kept rows (standardized unless ``raw``) and their answers.  ``predict`` gives ``classes``
+    probabilities per row (the neighbours' votes, weighted by inverse distance with ``by_distance``) or
+    the neighbours' mean answer for regression."""
+
+    FIELDS = ("task", "features", "classes", "k", "by_distance", "metric", "rows", "answers", "standard")
+
+    def neighbors(self, X):
+        """For each row of ``X`` its ``k`` nearest kept rows: ``(index [q, k], distance [q, k])``, nearest first."""
+        Q = self.standard.apply(as_rows(X, self.features))
+        dist = distances(self.metric, Q, self.rows)
+        d, i = torch.topk(dist, min(self.k, self.rows.shape[0]), dim=1, largest=False)
+        return i, d
+
+    def predict(self, X) -> torch.Tensor:
+        i, d = self.neighbors(X)
+        if self.by_distance:
+            w = 1.0 / d.clamp_min(1e-12)
+            exact = d <= 1e-12                    # a row at distance zero answers alone, with its twins
+            w = torch.where(exact.any(1, keepdim=True), exact.float(), w)
+        else:
+            w = torch.ones_like(d)
+        ans = self.answers[i]
+        if self.task is REGRESSION:
+            return (w * ans.float()).sum(1) / w.sum(1)
+        votes = torch.zeros(i.shape[0], self.classes).scatter_add_(1, ans.long(), w)
+        return votes / votes.sum(1, keepdim=True)
+
+    def module(self):
+        from .modules import NeighborsModule
+        return NeighborsModule.of(self)
+
+
+def fit(d, task, k: int = 5, by_distance: bool = False, metric: str = EUCLIDEAN, raw: bool = False, classes: int = 0) -> Neighbors:
+    task = as_task(task)
+    d.check(task)
+    if k < 1 or metric not in METRICS:
+        raise ValueError(f"neighbors: k must be at least 1 and the metric one of {METRICS}")
+    m = Neighbors()
+    m.task, m.features, m.k, m.by_distance, m.metric = task, d.n_features, int(k), bool(by_distance), metric
+    m.standard = Standard.fit(d.X, raw=raw)
+    m.rows = m.standard.apply(d.X)
+    m.classes = count_classes(d.Y, classes) if task is CLASSIFICATION else 0
+    m.answers = d.Y.long() if task is CLASSIFICATION else d.Y.float()
+    return m

@@ -220,6 +220,11 @@ class Model:
         imp = sum(t.importance for t in trees)
         return imp / imp.sum().clamp_min(1e-12)
 
+    def module(self):
+        """This ensemble as an ``nn.Module`` that walks every tree in tensor ops (``ml/modules.py``)."""
+        from .modules import TreeModule
+        return TreeModule.of(self)
+
     def to_json(self) -> str:
         def enc(t):
             return t.nodes
@@ -243,13 +248,23 @@ class Model:
 
 
 def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=1, min_gain=0.0, l2=1.0, bins=255,
-                      subsample=1.0, colsample=1.0, classes=0, seed=0, validation=None, progress=None) -> Model:
-    """Second-order boosting: squared error (classes=0), logistic (2) or softmax (>2)."""
+                      subsample=1.0, colsample=1.0, classes=0, seed=0, validation=None, patience=10, progress=None) -> Model:
+    """Second-order boosting: squared error (classes=0), logistic (2) or softmax (>2).  ``subsample`` draws
+    that share of the rows for each tree and ``colsample`` that share of the features for each node.
+    ``validation`` (a table, or ``(X, y)``) is scored after every round (squared error or log loss): boosting
+    stops once ``patience`` rounds in a row have not improved it, and the model keeps the best round's trees
+    (tree/boost.go: Validation)."""
     X, y = torch.as_tensor(X).float(), torch.as_tensor(y)
     gen = torch.Generator().manual_seed(seed)
     B, edges = _bin(X, bins)
     n = X.shape[0]
     out_trees = []
+    held = None
+    if validation is not None:
+        Xv, yv = (validation.X, validation.Y) if hasattr(validation, "X") else validation
+        Xv, yv = torch.as_tensor(Xv).float(), torch.as_tensor(yv)
+        Bv = torch.searchsorted(edges, Xv.t().contiguous()).t().contiguous()
+        held = dict(B=Bv, y=yv, best=math.inf, at=0, bad=0)
     if classes > 2:
         base = torch.zeros(classes)
         F = torch.zeros(n, classes)
@@ -258,6 +273,8 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
         yf = y.float()
         base = float(yf.mean()) if classes == 0 else float(torch.logit(yf.mean().clamp(1e-6, 1 - 1e-6)))
         F = torch.full((n,), base)
+    if held is not None:
+        held["F"] = base.clone().repeat(held["B"].shape[0], 1) if classes > 2 else torch.full((held["B"].shape[0],), base)
     for it in range(trees):
         rows = torch.arange(n) if subsample >= 1.0 else torch.randperm(n, generator=gen)[: max(1, int(n * subsample))]
         if classes > 2:
@@ -267,6 +284,8 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
                 g, h = (p[:, k] - oh[:, k]), (p[:, k] * (1 - p[:, k])).clamp_min(1e-6)
                 t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B[rows], g[rows], h[rows])
                 F[:, k] += learning_rate * t.predict_binned(B)
+                if held is not None:
+                    held["F"][:, k] += learning_rate * t.predict_binned(held["B"])
                 round_trees.append(t)
             out_trees.append(round_trees)
         else:
@@ -277,10 +296,29 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
                 g, h = F - yf, torch.ones(n)
             t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B[rows], g[rows], h[rows])
             F += learning_rate * t.predict_binned(B)
+            if held is not None:
+                held["F"] += learning_rate * t.predict_binned(held["B"])
             out_trees.append(t)
         if progress is not None and (it + 1) % 10 == 0:
             progress.write(f"tree {it + 1}/{trees}\n")
-    return Model(out_trees, edges, learning_rate, base, classes, "gbdt")
+        if held is not None:
+            if classes > 2:
+                loss = float(torch.nn.functional.cross_entropy(held["F"], held["y"].long()))
+            elif classes == 2:
+                loss = float(torch.nn.functional.binary_cross_entropy_with_logits(held["F"], held["y"].float()))
+            else:
+                loss = float(((held["F"] - held["y"].float()) ** 2).mean())
+            if loss < held["best"] - 1e-12:
+                held["best"], held["at"], held["bad"] = loss, it + 1, 0
+            else:
+                held["bad"] += 1
+                if held["bad"] >= max(int(patience), 1):
+                    break
+    if held is not None and held["at"] > 0:
+        out_trees = out_trees[:held["at"]]
+    m = Model(out_trees, edges, learning_rate, base, classes, "gbdt")
+    m.validation_loss = held["best"] if held is not None else None
+    return m
 
 
 def decision_tree(X, y, max_depth=8, min_leaf=1, classes=0, **kw) -> Model:

@@ -59,17 +59,8 @@ def test_neighbors_cluster_decomp():
     assert p.transform(X).shape == (400, 2) and p.variance[0] >= p.variance[1]
 
 
-def test_forecast_recommend_rules_automl():
-    hw = ml.HoltWinters(period=4).fit([1, 2, 3, 4] * 6)
-    assert torch.allclose(hw.forecast(4), torch.tensor([1.0, 2, 3, 4]), atol=1e-4)
-    assert torch.allclose(ml.autoregressive(torch.arange(20.0), 2)(3), torch.tensor([20.0, 21, 22]), atol=1e-3)
-    als = ml.ALS(5, 6, factors=2, l2=0.01, iters=20).fit([0, 0, 1, 2, 3, 4], [0, 1, 1, 2, 3, 4], [5, 3, 4, 1, 2, 5.0])
-    assert abs(float(als.predict(torch.tensor([0]), torch.tensor([0]))) - 5) < 0.1
-    _, rules = ml.apriori([["a", "b"], ["a", "b", "c"], ["a"], ["b", "c"]], 0.4, 0.6)
-    assert rules[0][0] == {"c"} and rules[0][1] == {"b"} and rules[0][3] == 1.0
+def test_splits_and_scaler():
     X, y, _ = _reg()
-    name, model, board = ml.automl(X[:200], y[:200], folds=2)
-    assert name == "ridge" and board["ridge"] > 0.99
     tr, te = ml.split(ml.Data(X, y), 0.25)
     assert len(tr) == 300 and len(te) == 100
     sc = ml.fit_scaler(X)

@@ -1,0 +1,319 @@
+"""The table-level models: what each recovers on data whose answer is known, options, missing values,
+JSON round trips, errors, and that a model's ``nn.Module`` answers as its ``predict`` does (the
+categories of the reference's tests under linear/, svm/, neighbors/, bayes/, cluster/, decompose/,
+forecast/, recommend/, rules/, automl/ and tabular/)."""
+import math
+
+import pytest
+import torch
+
+import mimir_b200.tensor as T
+from mimir_b200 import ml
+from mimir_b200.ml import automl, bayes, cluster, decompose, forecast, linear, neighbors, recommend, rules, svm, tree
+from mimir_b200.ml.tabular import Data, cross_validate
+
+
+def blobs(n=150, d=4, gap=1.5, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    X = torch.cat([torch.randn(n, d, generator=g) + gap, torch.randn(n, d, generator=g) - gap])
+    return X, (torch.arange(2 * n) >= n).long()
+
+
+def three(seed=1):
+    g = torch.Generator().manual_seed(seed)
+    C = torch.cat([torch.randn(80, 2, generator=g) * 0.5 + torch.tensor([4.0, 0.0]), torch.randn(80, 2, generator=g) * 0.5 - torch.tensor([4.0, 0.0]),
+                   torch.randn(80, 2, generator=g) * 0.5 + torch.tensor([0.0, 5.0])])
+    return C, torch.arange(3).repeat_interleave(80)
+
+
+def pure(assign, truth, k=3):
+    return all(len(set(assign[truth == j].tolist())) == 1 for j in range(k)) and len(set(assign.tolist())) == k
+
+
+def module_matches(model, Q, soft=True, tol=1e-4):
+    out = model.module()(T.tensor(Q)).data()
+    want = model.predict(Q)
+    got = torch.softmax(out, 1) if soft else out[:, 0]
+    return float((got - want).abs().max()) < tol
+
+
+# ------------------------------------------------------------------ tabular
+def test_table_checks_splits_and_cross_validation():
+    X, y = blobs(20)
+    d = Data(X, y)
+    d.check("classification")
+    assert d.rows == 40 and d.classes() == 2 and d.n_features == 4
+    assert Data(X.reshape(-1).tolist(), y, n_features=4).rows == 40
+    tr, te = d.split(0.25, seed=3)
+    both = torch.cat([tr.X, te.X])
+    assert len(te) == 10 and len(tr) == 30 and torch.equal(both.sort(0).values, X.sort(0).values)      # every row exactly once
+    seen = []
+    scores = cross_validate(lambda t: len(t), lambda m, h: seen.append(h.X) or m, d, folds=4)
+    assert scores == [30.0] * 4 and torch.equal(torch.cat(seen).sort(0).values, X.sort(0).values)
+    with pytest.raises(ValueError):
+        Data(X, y.float() + 0.5).check("classification")
+    with pytest.raises(ValueError):
+        Data(X, y[:3]).check("regression")
+    with pytest.raises(ValueError):
+        Data(torch.zeros(0, 3), torch.zeros(0)).check()
+    with pytest.raises(ValueError):
+        cross_validate(None, None, d, folds=1)
+
+
+# ------------------------------------------------------------------ linear
+def test_least_squares_ridge_and_lasso():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(400, 6, generator=g) * torch.tensor([1, 5, 0.1, 2, 1, 1.0]) + 3
+    w = torch.tensor([2.0, -1, 0, 0, 0.5, 0])
+    y = X @ w + 1 + 0.01 * torch.randn(400, generator=g)
+    m = linear.regression(Data(X, y))
+    assert torch.allclose(m.weights[0], w, atol=0.02) and abs(float(m.bias) - 1) < 0.05 and abs(m.weight(0, 1) + 1) < 0.02
+    # ridge against its closed form on standardized features
+    l2 = 0.5
+    mu, sd = X.double().mean(0), X.double().std(0, unbiased=False)
+    Z = (X.double() - mu) / sd
+    ws = torch.linalg.solve(Z.t() @ Z / 400 + l2 * torch.eye(6, dtype=torch.double), Z.t() @ (y.double() - y.double().mean()) / 400)
+    assert torch.allclose(linear.regression(Data(X, y), l2=l2).weights[0].double(), ws / sd, atol=1e-5)
+    lasso = linear.regression(Data(X, y), l1=0.05)
+    assert (lasso.weights[0][[2, 3, 5]] == 0).all() and (lasso.weights[0][[0, 1, 4]].abs() > 0.3).all()
+
+
+def test_logistic_recovers_log_odds_classes_and_sparsity():
+    g = torch.Generator().manual_seed(1)
+    X = torch.randn(4000, 3, generator=g)
+    w = torch.tensor([1.5, -2.0, 0.0])
+    yc = (torch.rand(4000, generator=g) < torch.sigmoid(X @ w + 0.5)).long()
+    m = linear.logistic_fit(Data(X, yc), l2=1e-6)
+    assert torch.allclose(m.weights[0], w, atol=0.15) and abs(float(m.bias) - 0.5) < 0.15
+    p = m.predict(X[:5])
+    assert p.shape == (5, 2) and torch.allclose(p.sum(1), torch.ones(5))
+    C, truth = three()
+    m3 = linear.logistic_fit(Data(C, truth))
+    assert (m3.classify(C) == truth).float().mean() > 0.99 and m3.predict(C).shape == (240, 3)
+    sparse = linear.logistic_fit(Data(X, yc), l1=0.05)
+    assert sparse.weights[0, 2] == 0 and sparse.weights[0, 0] > 0.5 and sparse.weights[0, 1] < -0.5
+    assert module_matches(m, X[:9]) and module_matches(m3, C[::20]) and module_matches(linear.regression(Data(X, X @ w)), X[:9], soft=False)
+
+
+def test_missing_and_constant_features_json_and_bad_input():
+    X, y = blobs()
+    X = torch.cat([X, torch.full((300, 1), 7.0)], 1)            # a constant feature
+    Xn = X.clone()
+    Xn[::5, 0] = math.nan
+    m = linear.logistic_fit(Data(Xn, y))
+    assert (m.classify(Xn) == y).float().mean() > 0.97 and m.weights[0, 4] == 0 and torch.isfinite(m.predict(Xn)).all()
+    again = linear.Linear.from_json(m.to_json())
+    assert torch.equal(again.predict(Xn), m.predict(Xn))
+    with pytest.raises(ValueError):
+        linear.Linear.from_json(svm.fit(Data(X, y), "classification", kernel="linear").to_json())
+    with pytest.raises(ValueError):
+        linear.regression(Data(X, y.float()), l1=-1)
+    with pytest.raises(ValueError):
+        linear.logistic_fit(Data(X, torch.zeros(300)))
+
+
+# ------------------------------------------------------------------ svm
+def test_kernels_separate_rings_and_linear_separates_blobs():
+    g = torch.Generator().manual_seed(0)
+    r = torch.cat([torch.rand(150, generator=g), 2 + torch.rand(150, generator=g)])
+    th = torch.rand(300, generator=g) * 2 * math.pi
+    P, lab = torch.stack([r * th.cos(), r * th.sin()], 1), (torch.arange(300) >= 150).long()
+    for kernel, kw in (("rbf", {}), ("polynomial", dict(coef0=1.0, degree=2))):
+        m = svm.fit(Data(P, lab), "classification", kernel=kernel, c=10.0, **kw)
+        assert (m.classify(P) == lab).float().mean() > 0.98 and 0 < m.support_vectors() < 150
+        assert module_matches(m, P[::17], tol=1e-3)
+    assert (svm.fit(Data(P, lab), "classification", kernel="linear").classify(P) == lab).float().mean() < 0.8     # no line splits rings
+    X, y = blobs(2000, 5)
+    lin = svm.fit(Data(X, y), "classification", kernel="linear")
+    assert (lin.classify(X) == y).float().mean() > 0.99 and lin.support_vectors() == 0 and module_matches(lin, X[::333], tol=1e-3)
+    C, truth = three()
+    m3 = svm.fit(Data(C, truth), "classification")
+    p = m3.predict(C)
+    assert (p.argmax(1) == truth).float().mean() > 0.99 and torch.allclose(p.sum(1), torch.ones(240), atol=1e-5)
+    assert module_matches(m3, C[::20], tol=1e-3)
+    assert torch.allclose(svm.SVM.from_json(m3.to_json()).predict(C), p)
+
+
+def test_support_vector_regression_and_bad_options():
+    x = torch.linspace(-3, 3, 200)[:, None]
+    y = torch.sin(x[:, 0]) * 2 + 5
+    m = svm.fit(Data(x, y), "regression", c=10.0, epsilon=0.05)
+    assert float(((m.predict(x) - y) ** 2).mean().sqrt()) < 0.15 and m.support_vectors() < 60
+    assert module_matches(m, x[::20], soft=False, tol=1e-3)
+    for bad in (dict(c=0), dict(kernel="wavelet"), dict(gamma=-1.0), dict(epsilon=-0.1)):
+        with pytest.raises(ValueError):
+            svm.fit(Data(x, y), "regression", **bad)
+
+
+# ------------------------------------------------------------------ neighbours and naive Bayes
+def test_neighbours_classify_regress_and_list():
+    X, y = blobs()
+    m = neighbors.fit(Data(X, y), "classification", k=7, by_distance=True)
+    assert (m.classify(X) == y).all()                                        # each row is its own nearest neighbour
+    idx, dist = m.neighbors(X[:3])
+    assert idx[:, 0].tolist() == [0, 1, 2] and float(dist[:, 0].max()) < 1e-3 and (dist[:, 1:] >= dist[:, :-1]).all()
+    for metric in neighbors.METRICS:
+        mm = neighbors.fit(Data(X, y), "classification", metric=metric, raw=metric == "manhattan")
+        assert (mm.classify(X) == y).float().mean() > 0.97 and module_matches(mm, X[::31])
+    r = neighbors.fit(Data(X, X[:, 0] * 2), "regression", k=3)
+    assert float(((r.predict(X) - X[:, 0] * 2) ** 2).mean()) < 0.3 and module_matches(r, X[::31], soft=False)
+    assert module_matches(m, X[::31])
+    with pytest.raises(ValueError):
+        neighbors.fit(Data(X, y), "classification", k=0)
+    with pytest.raises(ValueError):
+        neighbors.fit(Data(X, y), "classification", metric="chebyshev")
+
+
+def test_naive_bayes_kinds_priors_and_missing_values():
+    X, y = blobs()
+    g = bayes.gaussian(Data(X, y))
+    assert (g.classify(X) == y).float().mean() > 0.98 and module_matches(g, X[::31])
+    Xn = X[:4].clone()
+    Xn[0, 1] = math.nan                                                      # left out of the row's likelihood
+    keep = [0, 2, 3]
+    sub = bayes.gaussian(Data(X[:, keep], y))
+    assert torch.allclose(g.log_likelihood(Xn)[0], sub.log_likelihood(X[:1][:, keep])[0], atol=1e-9)
+    gen = torch.Generator().manual_seed(0)
+    counts = torch.poisson(torch.cat([torch.tensor([[5.0, 1, 1]]).repeat(100, 1), torch.tensor([[1.0, 1, 5]]).repeat(100, 1)]), generator=gen)
+    yc = (torch.arange(200) >= 100).long()
+    mn, bn = bayes.multinomial(Data(counts, yc)), bayes.bernoulli(Data(counts, yc), binarize=2.5)
+    assert (mn.classify(counts) == yc).float().mean() > 0.9 and (bn.classify(counts) == yc).float().mean() > 0.85
+    assert module_matches(mn, counts[::13]) and module_matches(bn, counts[::13])
+    skew = bayes.gaussian(Data(X, y), priors=[0.999, 0.001])
+    assert (skew.classify(X) == 0).sum() >= (g.classify(X) == 0).sum()
+    assert torch.allclose(bayes.NaiveBayes.from_json(mn.to_json()).predict(counts), mn.predict(counts))
+    with pytest.raises(ValueError):
+        bayes.multinomial(Data(-counts, yc))
+    with pytest.raises(ValueError):
+        bayes.gaussian(Data(X, y), priors=[0.5, 0.2])
+
+
+# ------------------------------------------------------------------ cluster, decompose
+def test_groupings_find_the_blobs():
+    C, truth = three()
+    km = cluster.kmeans_fit(C, 3)
+    assert pure(km.assign(C), truth) and km.predict(C).sum(1).eq(1).all() and cluster.silhouette(km, C) > 0.7
+    mx = cluster.gaussian_mixture(C, 3)
+    assert pure(mx.assign(C), truth) and torch.allclose(mx.weights, torch.full((3,), 1 / 3), atol=1e-3)
+    assert float(mx.log_density(torch.tensor([[20.0, 20.0]]))) < float(mx.log_density(C[:1])) - 100
+    assert torch.equal(km.module()(T.tensor(C)).data().argmax(1), km.assign(C)) and module_matches(mx, C[::20])
+    db = cluster.dbscan_fit(torch.cat([C, torch.tensor([[40.0, 40.0]])]), 0.3)
+    assert db.groups == 3 and db.labels[-1] == cluster.NOISE and pure(db.labels[:-1], truth)
+    assert db.assign(torch.tensor([[4.0, 0.0], [30.0, 30.0]])).tolist() == [int(db.labels[0]), cluster.NOISE]
+    ag = cluster.agglomerative(C, 3)
+    h = ag.heights()
+    assert pure(ag.cut(3), truth) and (h[1:] >= h[:-1]).all() and h[-2] > 20 * h[-3]       # two big jumps: three groups
+    assert ag.cut(0).unique().tolist() == [0] and pure(ag.assign(C), truth) and ag.cut(240).unique().numel() == 240
+    assert cluster.silhouette(ag.centers(C, 2), C) < cluster.silhouette(ag, C)
+    for model, cls in ((km, cluster.Means), (mx, cluster.Mixture), (db, cluster.Density), (ag, cluster.Linkage)):
+        again = cls.from_json(model.to_json())
+        assert torch.equal(again.assign(C), model.assign(C))
+    for bad in (lambda: cluster.kmeans_fit(C, 0), lambda: cluster.kmeans_fit(C, 500), lambda: cluster.dbscan_fit(C, -1.0),
+                lambda: cluster.agglomerative(C, 0), lambda: cluster.kmeans_fit(torch.zeros(0, 2), 1)):
+        with pytest.raises(ValueError):
+            bad()
+
+
+def test_pca_finds_the_shared_direction():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(300, 1, generator=g) @ torch.tensor([[1.0, 2, 0.5]]) + 0.1 * torch.randn(300, 3, generator=g)
+    p = decompose.pca_fit(X, 2)
+    assert p.k == 2 and p.ratio[0] > 0.95 and torch.allclose(p.directions[0].abs(), torch.full((3,), 3 ** -0.5), atol=0.02)
+    assert sorted(p.ranked(0)) == [0, 1, 2] and abs(float(p.directions[0] @ p.directions[1])) < 1e-5
+    full = decompose.pca_fit(X, 3)
+    assert torch.allclose(full.inverse(full.transform(X)), X, atol=1e-4)
+    wide = decompose.pca_fit(torch.randn(5, 12, generator=g), 3)                 # more features than rows
+    assert wide.transform(torch.randn(2, 12)).shape == (2, 3)
+    with pytest.raises(ValueError):
+        decompose.pca_fit(X, 4)
+
+
+# ------------------------------------------------------------------ forecast, recommend, rules, automl
+def test_forecast_learns_the_week_with_gaps():
+    g = torch.Generator().manual_seed(0)
+    week = torch.tensor([5.0, 6, 7, 8, 9, 3, 2])
+    series = [week.repeat(20) * s + 0.1 * s * torch.randn(140, generator=g) for s in (1.0, 10.0, 300.0)]
+    series[0][30:33] = math.nan
+    m = forecast.fit(series, season=7, trees=80)
+    f = m.forecast(series[1][:133], 7)
+    assert float((f - week * 10).abs().max()) < 2.0 and m.features == 18
+    row, scale = m.rows(series[1][:133])
+    assert row.shape == (18,) and abs(float(m.trees.predict(row[None])[0]) * scale - float(f[0])) < 1e-4
+    assert torch.allclose(forecast.Forecaster.from_json(m.to_json()).forecast(series[1][:133], 3), f[:3])
+    s = forecast.smooth(week.repeat(10) + torch.arange(70) * 0.1, season=7)
+    assert torch.allclose(s.forecast(7), week + 7.0 + torch.arange(7) * 0.1, atol=0.2)
+    with pytest.raises(ValueError):
+        forecast.fit([torch.arange(5.0)])
+    with pytest.raises(ValueError):
+        forecast.smooth([1.0, 2.0], season=7)
+
+
+def test_recommendations_beat_popularity_and_ratings_predict():
+    g = torch.Generator().manual_seed(0)
+    events = []
+    for u in range(40):
+        for i in (range(0, 10) if u % 2 == 0 else range(10, 20)):
+            if torch.rand(1, generator=g) < 0.6:
+                events.append((u, i, 1.0))
+    held = [(u, i, 1.0) for u in range(0, 40, 2) for i in range(10) if (u, i, 1.0) not in events][:20]
+    m = recommend.fit(40, 20, events, factors=4, iterations=10)
+    assert m.hit_rate(events, held, 5) >= 0.8                                   # popularity alone would name the other taste half the time
+    seen = [i for u, i, _ in events if u == 0]
+    top = m.recommend(0, 3, seen)
+    assert all(i < 10 and i not in seen for i in top) and all(i < 10 for i in m.similar(0, 3))
+    assert m.score(0, top[0]) > m.score(0, 15)
+    pairs = torch.tensor([[0, 1], [3, 12]])
+    out = m.module()(T.tensor(pairs)).data()[:, 0]
+    assert torch.allclose(out, torch.tensor([m.score(0, 1), m.score(3, 12)]), atol=1e-6)
+    r = recommend.fit(3, 3, [(0, 0, 5), (0, 1, 3), (1, 0, 4), (1, 1, 2), (2, 1, 1), (2, 2, 5)], factors=2, ratings=True, l2=0.01, iterations=30)
+    assert abs(r.score(0, 0) - 5) < 0.1 and abs(r.score(1, 1) - 2) < 0.1
+    for bad in ([(0, 99, 1.0)], [(0, 0, -1.0)], []):
+        with pytest.raises(ValueError):
+            recommend.fit(3, 3, bad)
+
+
+def test_rules_find_what_goes_together():
+    baskets = [["bread", "butter"], ["bread", "butter", "jam"], ["bread"], ["butter", "jam"], ["bread", "butter"], ["tea"]]
+    out = rules.mine(baskets, 0.3, 0.6)
+    first = out[0]
+    assert first.if_ == ("jam",) and first.then == ("butter",) and first.confidence == 1.0 and abs(first.lift - 1.5) < 1e-9
+    assert all(a.lift >= b.lift for a, b in zip(out, out[1:])) and len(rules.mine(baskets, 0.3, 0.6, top=1)) == 1
+    assert not any("tea" in r.if_ + r.then for r in out)
+    with pytest.raises(ValueError):
+        rules.mine([], 0.3)
+    with pytest.raises(ValueError):
+        rules.mine(baskets, 0.0)
+
+
+def test_search_picks_what_fits():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(300, 5, generator=g)
+    y = X @ torch.tensor([1.0, -2, 0.5, 0, 0]) + 0.01 * torch.randn(300, generator=g)
+    told = []
+    r = automl.search(Data(X, y), "regression", trials=5, folds=2, progress=lambda a, b: told.append((a, b)))
+    assert r.candidate.family == automl.LINEAR and r.score < 0.05 and told[-1] == (5, 5) and len(r.trials) == 5
+    assert float(((r.best.predict(X) - y) ** 2).mean()) < 0.01
+    step = (X[:, 0] * X[:, 1] > 0).long()                                     # no line splits it
+    rc = automl.search(Data(X, step), "classification", trials=6, folds=2, families=(automl.BOOST, automl.LINEAR))
+    assert rc.candidate.family == automl.BOOST and {t.candidate.family for t in rc.trials} == {automl.BOOST, automl.LINEAR}
+    assert (rc.best.classify(X) == step).float().mean() > 0.95 and str(rc.candidate).startswith("boost(")
+    quick = automl.search(Data(X, y), "regression", trials=12, budget=0.0)
+    assert len(quick.trials) == 1
+    with pytest.raises(ValueError):
+        automl.search(Data(X, y), "regression", families=("oracle",))
+
+
+def test_boosting_stops_when_a_validation_table_stops_improving():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(600, 5, generator=g)
+    y = torch.sin(X[:, 0]) * 2 + X[:, 1] + 0.3 * torch.randn(600, generator=g)
+    m = tree.gradient_boosting(X[:400], y[:400], trees=300, max_depth=4, validation=(X[400:], y[400:]), patience=5)
+    assert len(m.trees) < 150 and abs(m.validation_loss - float(((m.predict(X[400:]) - y[400:]) ** 2).mean())) < 1e-5
+    out = m.module()(T.tensor(X[:7])).data()[:, 0]
+    assert torch.allclose(out, m.predict(X[:7]), atol=1e-5)
+    y3 = torch.bucketize(X[:, 0].contiguous(), torch.tensor([-0.5, 0.5]))
+    m3 = tree.gradient_boosting(X, y3, trees=8, max_depth=3, classes=3)
+    assert torch.allclose(torch.softmax(m3.module()(T.tensor(X[:7])).data(), 1), m3.predict(X[:7]), atol=1e-6)
+    empty = type(m3.module()).empty(m3.module().shape)
+    empty.load_state_dict(m3.module().state_dict())
+    assert torch.equal(empty(T.tensor(X[:7])).data(), m3.module()(T.tensor(X[:7])).data())
