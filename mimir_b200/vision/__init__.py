@@ -1,5 +1,8 @@
-"""Vision models and box utilities (reference: vision/): ResNet-18/34/50, MobileNetV2, ViT,
-U-Net, CenterNet, IoU / NMS / average precision."""
-from .models import (CenterNet, MobileNetV2, ResNet, UNet, ViT, centernet_decode, centernet_loss, resnet18,
-                     resnet34, resnet50)
-from .boxes import average_precision, box_iou, nms
+"""Vision models and box utilities (reference: vision/): ResNet-18/34/50, MobileNetV2 and ViT behind one
+features / head interface with options for channels, small pictures, width and dropout; a CenterNet
+``Detector`` over any ``Backbone`` with targets, loss and decoding; U-Net; box IoU, NMS, GIoU loss,
+mean average precision and mean IoU."""
+from .models import (Backbone, CenterNet, DetectionTargets, Detector, Head, MobileNetV2, PictureModel, ResNet, UNet, ViT,  # noqa: F401
+                     centernet_decode, centernet_loss, resnet18, resnet34, resnet50, tiny_backbone)
+from .boxes import (Detection, average_precision, box_iou, giou_loss, iou, mean_average_precision, mean_iou, nms,  # noqa: F401
+                    nms_detections)

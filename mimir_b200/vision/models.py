@@ -18,6 +18,39 @@ def _conv_bn(cin, cout, k, stride=1, padding=None, groups=1, act=True):
     return nn.Sequential(*layers)
 
 
+class Head(nn.Module):
+    """A classifier: dropout (while training), then a linear layer."""
+
+    def __init__(self, width: int, classes: int, dropout: float = 0.0):
+        self.drop = nn.Dropout(dropout) if dropout > 0 else None
+        self.linear = nn.Linear(width, classes)
+
+    def forward(self, x):
+        return self.linear(self.drop(x) if self.drop is not None else x)
+
+
+class PictureModel(nn.Module):
+    """A picture network split into what it sees and what it says (vision/vision.go: Model):
+    ``features`` reads a batch of pictures into one vector each and ``head`` turns that into logits.
+    Transfer learning keeps the features and swaps the head: ``set_head`` starts a new one for other
+    classes, and ``head_parameters`` alone are what an optimizer is given to fit only the head."""
+
+    width = 0
+    _nn_skip_dropout = 0.0
+
+    def features(self, x):
+        raise NotImplementedError
+
+    def forward(self, x):
+        return self.head(self.features(x))
+
+    def set_head(self, classes: int) -> None:
+        self.head = Head(self.width, classes, self._nn_skip_dropout)
+
+    def head_parameters(self) -> list:
+        return self.head.parameters()
+
+
 class BasicBlock(nn.Module):
     expansion = 1
 
@@ -45,10 +78,16 @@ class Bottleneck(nn.Module):
         return T.relu(y + (self.down(x) if self.down is not None else x))
 
 
-class ResNet(nn.Module):
-    def __init__(self, block, depths, classes=1000, in_channels=3, width=64):
-        self.stem = _conv_bn(in_channels, width, 7, 2, 3)
-        self.pool = nn.MaxPool2d(3, 2, 1)
+class ResNet(PictureModel):
+    """``small`` fits the model to 32 to 64 pixel pictures (CIFAR): the first layer keeps the size where
+    it otherwise shrinks a 224-pixel photo fourfold.  ``width`` is the first stage's channels (64 times
+    a multiplier, e.g. 32 for a model a quarter the size); ``dropout`` acts on the features before the head."""
+
+    def __init__(self, block, depths, classes=1000, in_channels=3, width=64, small=False, dropout=0.0):
+        width = max(8, int(round(width)))
+        self.stem = _conv_bn(in_channels, width, 3, 1, 1) if small else _conv_bn(in_channels, width, 7, 2, 3)
+        self.pool = None if small else nn.MaxPool2d(3, 2, 1)
+        self._nn_skip_small, self._nn_skip_dropout = small, dropout
         blocks, cin = [], width
         for i, n in enumerate(depths):
             planes = width * 2 ** i
@@ -56,17 +95,25 @@ class ResNet(nn.Module):
                 blocks.append(block(cin, planes, 2 if (j == 0 and i > 0) else 1))
                 cin = planes * block.expansion
         self.blocks = blocks
-        self.head = nn.Linear(cin, classes)
-        self.features = cin
+        self.width = cin
+        self.head = Head(cin, classes, dropout)
 
     def forward_features(self, x):
-        x = self.pool(self.stem(x))
+        """The last feature map, before the average and head: 32 times smaller than the picture (8 when small)."""
+        x = self.stem(x)
+        if self.pool is not None:
+            x = self.pool(x)
         for b in self.blocks:
             x = b(x)
         return x
 
-    def forward(self, x):
-        return self.head(T.mean(self.forward_features(x), dim=(2, 3)))
+    def features(self, x):
+        return T.mean(self.forward_features(x), dim=(2, 3))
+
+    def backbone(self) -> "Backbone":
+        """This network's feature maps as a detector's backbone; the weights are shared, so a ResNet taught to
+        classify starts a detector that already sees."""
+        return Backbone(self.forward_features, self.width, 8 if self._nn_skip_small else 32, self)
 
 
 def resnet18(classes=1000, **kw): return ResNet(BasicBlock, (2, 2, 2, 2), classes, **kw)
@@ -88,44 +135,50 @@ class InvertedResidual(nn.Module):
         return x + self.body(x) if self.skip else self.body(x)
 
 
-class MobileNetV2(nn.Module):
+class MobileNetV2(PictureModel):
     CFG = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
 
-    def __init__(self, classes=1000, width=1.0, in_channels=3):
+    def __init__(self, classes=1000, width=1.0, in_channels=3, small=False, dropout=0.2):
         c = lambda v: max(8, int(v * width + 4) // 8 * 8)
-        layers, cin = [_conv_bn(in_channels, c(32), 3, 2)], c(32)
-        for t, ch, n, s in self.CFG:
+        layers, cin = [_conv_bn(in_channels, c(32), 3, 1 if small else 2)], c(32)
+        for k, (t, ch, n, s) in enumerate(self.CFG):
+            if small and k == 1:
+                s = 1                                           # small pictures keep their size one stage longer
             for i in range(n):
                 layers.append(InvertedResidual(cin, c(ch), s if i == 0 else 1, t))
                 cin = c(ch)
         layers.append(_conv_bn(cin, c(1280), 1))
         self.body = nn.Sequential(*layers)
-        self.head = nn.Linear(c(1280), classes)
+        self.width, self._nn_skip_dropout = c(1280), dropout
+        self.head = Head(self.width, classes, dropout)
 
-    def forward(self, x):
-        return self.head(T.mean(self.body(x), dim=(2, 3)))
+    def features(self, x):
+        return T.mean(self.body(x), dim=(2, 3))
 
 
-class ViT(nn.Module):
+class ViT(PictureModel):
     """Patch embedding by a strided convolution, class token, learned positions, transformer encoder layers."""
 
-    def __init__(self, image=224, patch=16, dim=768, depth=12, heads=12, mlp=3072, classes=1000, in_channels=3):
+    def __init__(self, image=224, patch=16, dim=768, depth=12, heads=12, mlp=3072, classes=1000, in_channels=3, dropout=0.0):
+        if image % patch or dim % heads:
+            raise ValueError(f"ViT: pictures of {image} pixels in patches of {patch}, or {dim} features over {heads} heads")
         self.patch = nn.Conv2d(in_channels, dim, patch, patch)
+        self.width, self._nn_skip_dropout = dim, dropout
         n = (image // patch) ** 2
         self.cls = T.Param(torch.zeros(1, 1, dim), "cls")
         self.pos = T.Param(nn.normal_init((1, n + 1, dim), 0.02), "pos")
         self.layers = [nn.TransformerEncoderLayer(dim, heads, mlp, eps=1e-12, activation="gelu", dropout=0.0) for _ in range(depth)]
         self.norm = nn.LayerNorm(dim)
-        self.head = nn.Linear(dim, classes)
+        self.head = Head(dim, classes, dropout)
 
-    def forward(self, x):
+    def features(self, x):
         p = self.patch(x)                                       # [B, dim, h, w]
         B, dim = p.shape[0], p.shape[1]
         tok = T.transpose(T.reshape(p, (B, dim, -1)), 1, 2)     # [B, n, dim]
         tok = T.cat([T.expand(self.cls.value(), (B, 1, dim)), tok], 1) + self.pos.value()
         for l in self.layers:
             tok = l(tok)
-        return self.head(self.norm(tok)[:, 0])
+        return self.norm(tok)[:, 0]
 
 
 class UNet(nn.Module):
@@ -157,7 +210,7 @@ class CenterNet(nn.Module):
 
     def __init__(self, classes=80, backbone=None, head_width=64):
         self.backbone = backbone or resnet18()
-        cin, ups = self.backbone.features, []
+        cin, ups = self.backbone.width, []
         for c in (256, 128, 64):
             ups += [nn.ConvTranspose2d(cin, c, 4, 2, 1, bias=False), nn.BatchNorm2d(c), nn.ReLU()]
             cin = c
@@ -200,3 +253,133 @@ def centernet_decode(heat: torch.Tensor, size: torch.Tensor, offset: torch.Tenso
     w, h = gather(size, 0), gather(size, 1)
     boxes = torch.stack([cx - w / 2, cy - h / 2, cx + w / 2, cy + h / 2], -1) * stride
     return boxes, scores, cls
+
+
+# ---------------------------------------------------------------------------------------------
+# Detection as points (reference: vision/detect.go)
+# ---------------------------------------------------------------------------------------------
+class Backbone(nn.Module):
+    """Reads pictures into feature maps for a ``Detector``: ``[N, C, H, W] -> [N, channels, H/stride, W/stride]``."""
+
+    def __init__(self, fn, channels: int, stride: int, owner=None):
+        self._nn_skip_fn, self.channels, self.stride = fn, channels, stride
+        self.owner = owner                      # the module whose weights ``fn`` runs (kept so they are saved and trained)
+
+    def forward(self, x):
+        return self._nn_skip_fn(x)
+
+
+def tiny_backbone(in_channels: int, width: int) -> Backbone:
+    """Four convolutions from ``in_channels`` to ``2 * width`` channels, four times smaller than the picture:
+    a backbone that learns in seconds, for small pictures and few kinds of thing."""
+    body = nn.Sequential(_conv_bn(in_channels, width, 3, 1), _conv_bn(width, width, 3, 2), _conv_bn(width, 2 * width, 3, 2),
+                         _conv_bn(2 * width, 2 * width, 3, 1))
+    return Backbone(body, 2 * width, 4, body)
+
+
+DETECTOR_STRIDE = 4
+
+
+class DetectionTargets:
+    """What a detector should give for a batch of pictures, on its grid: ``heat [N, classes, h, w]`` (a
+    Gaussian bump around every true centre, 1 at the centre), ``size`` and ``offset [N, 2, h, w]`` and
+    ``mask [N, h, w]`` (1 at the centres)."""
+
+    def __init__(self, heat, size, offset, mask):
+        self.heat, self.size, self.offset, self.mask = heat, size, offset, mask
+
+
+def _gaussian_radius(h: float, w: float, min_overlap: float = 0.7) -> float:
+    """How far a corner may move with the box still overlapping the true one by ``min_overlap`` (CenterNet)."""
+    a1, b1, c1 = 1.0, h + w, w * h * (1 - min_overlap) / (1 + min_overlap)
+    r1 = (b1 - math.sqrt(max(b1 * b1 - 4 * a1 * c1, 0.0))) / 2
+    a2, b2, c2 = 4.0, 2 * (h + w), (1 - min_overlap) * w * h
+    r2 = (b2 - math.sqrt(max(b2 * b2 - 4 * a2 * c2, 0.0))) / (2 * a2)
+    a3, b3, c3 = 4 * min_overlap, -2 * min_overlap * (h + w), (min_overlap - 1) * w * h
+    r3 = (b3 + math.sqrt(max(b3 * b3 - 4 * a3 * c3, 0.0))) / (2 * a3)
+    return max(0.0, min(r1, r2, r3))
+
+
+class Detector(nn.Module):
+    """Finds things in pictures as CenterNet does ("objects as points"): on a grid four times smaller than
+    the picture it scores, for each kind of thing, how likely each cell holds a thing's centre, and says how
+    wide and tall that thing is and where in the cell its centre lies.  The peaks of the scores are the
+    things found, so it needs no anchors and no NMS.  ``forward`` maps ``[N, C, H, W]`` to
+    ``[N, classes + 4, H/4, W/4]``: centre logits per class, then width, height, x and y offset in grid cells.
+    A backbone coarser than the grid is grown to it by transposed convolutions."""
+
+    def __init__(self, classes: int, backbone: Backbone, head_width: int = 64):
+        if classes < 1 or backbone.stride < DETECTOR_STRIDE or backbone.stride & (backbone.stride - 1):
+            raise ValueError(f"detector: {classes} classes on a backbone of stride {backbone.stride} (want a power of two, at least 4)")
+        self.classes, self.backbone = classes, backbone
+        cin, ups, stride, c = backbone.channels, [], backbone.stride, 256
+        while stride > DETECTOR_STRIDE:
+            ups += [nn.ConvTranspose2d(cin, c, 4, 2, 1, bias=False), nn.BatchNorm2d(c), nn.ReLU()]
+            cin, c, stride = c, max(c // 2, 64), stride // 2
+        self.up = nn.Sequential(*ups) if ups else None
+        self.neck = nn.Sequential(nn.Conv2d(cin, head_width, 3, padding=1), nn.ReLU())
+        self.out = nn.Conv2d(head_width, classes + 4, 1)
+        bias = torch.zeros(classes + 4)
+        bias[:classes] = -2.19                              # centres are rare: start the scores near 0.1
+        self.out.bias.set(bias)
+
+    def forward(self, x):
+        f = self.backbone(x)
+        if self.up is not None:
+            f = self.up(f)
+        return self.out(self.neck(f))
+
+    def targets(self, truth, h: int, w: int) -> DetectionTargets:
+        """``truth[i]``: the true things of picture i as ``(class, x1, y1, x2, y2)`` in pixels, for pictures of
+        height ``h`` and width ``w``."""
+        if h % DETECTOR_STRIDE or w % DETECTOR_STRIDE:
+            raise ValueError(f"detector: pictures of {h} x {w}, want multiples of {DETECTOR_STRIDE}")
+        gh, gw, n = h // DETECTOR_STRIDE, w // DETECTOR_STRIDE, len(truth)
+        heat = torch.zeros(n, self.classes, gh, gw)
+        size, offset, mask = torch.zeros(n, 2, gh, gw), torch.zeros(n, 2, gh, gw), torch.zeros(n, gh, gw)
+        ys, xs = torch.arange(gh, dtype=torch.float32)[:, None], torch.arange(gw, dtype=torch.float32)[None]
+        for i, things in enumerate(truth):
+            for cls, x1, y1, x2, y2 in things:
+                if not 0 <= int(cls) < self.classes:
+                    raise ValueError(f"detector: class {cls} of {self.classes}")
+                bw, bh = (x2 - x1) / DETECTOR_STRIDE, (y2 - y1) / DETECTOR_STRIDE
+                if bw <= 0 or bh <= 0:
+                    continue
+                cx, cy = (x1 + x2) / 2 / DETECTOR_STRIDE, (y1 + y2) / 2 / DETECTOR_STRIDE
+                ix, iy = min(max(int(cx), 0), gw - 1), min(max(int(cy), 0), gh - 1)
+                sigma = (2 * int(_gaussian_radius(math.ceil(bh), math.ceil(bw))) + 1) / 6.0     # a bump of diameter 2 r + 1
+                bump = torch.exp(-((xs - ix) ** 2 + (ys - iy) ** 2) / (2 * sigma * sigma))
+                heat[i, int(cls)] = torch.maximum(heat[i, int(cls)], bump)
+                size[i, :, iy, ix] = torch.tensor([bw, bh])
+                offset[i, :, iy, ix] = torch.tensor([cx - ix, cy - iy])
+                mask[i, iy, ix] = 1.0
+        return DetectionTargets(heat, size, offset, mask)
+
+    def _parts(self, out):
+        n, _, gh, gw = out.shape
+        c = self.classes
+        cut = lambda lo, hi: T.shrink(out, ((0, n), (lo, hi), (0, gh), (0, gw)))  # noqa: E731
+        return cut(0, c), cut(c, c + 2), cut(c + 2, c + 4)
+
+    def loss(self, out, t: DetectionTargets):
+        """The penalty-reduced focal loss of the centre scores, plus a tenth of the L1 error of the sizes and
+        the L1 error of the offsets at the centres."""
+        heat, size, offset = self._parts(out)
+        dev = out.device
+        return centernet_loss(heat, size, offset, T.tensor(t.heat, device=dev), T.tensor(t.size, device=dev),
+                              T.tensor(t.offset, device=dev), T.tensor(t.mask, device=dev))
+
+    def detect(self, out, threshold: float = 0.3, top: int = 100) -> list:
+        """The things found in each picture: the peaks of the centre scores (cells whose 3x3 neighbourhood
+        holds no higher score), up to ``top`` a picture scoring at least ``threshold``, best first, as
+        ``Detection(cls, score, (x1, y1, x2, y2))`` with boxes in pixels."""
+        from .boxes import Detection
+        v = out.data().float().cpu()
+        c = self.classes
+        boxes, scores, cls = centernet_decode(v[:, :c], v[:, c:c + 2], v[:, c + 2:], k=top, stride=DETECTOR_STRIDE)
+        found = []
+        for b in range(v.shape[0]):
+            keep = scores[b] >= threshold
+            found.append([Detection(int(k), float(s), tuple(float(z) for z in bx))
+                          for k, s, bx in zip(cls[b][keep], scores[b][keep], boxes[b][keep])])
+        return found
