@@ -26,6 +26,22 @@ class BertConfig:
     def tiny(vocab=128):
         return BertConfig(vocab=vocab, dim=32, layers=2, heads=2, hidden=64, max_positions=64)
 
+    @staticmethod
+    def base(vocab=30522):
+        """Devlin et al.'s BERT-base: 768 numbers, 12 layers of 12 heads, 512 tokens."""
+        return BertConfig(vocab=vocab)
+
+    @staticmethod
+    def mini(vocab=30522):
+        """Turc et al.'s BERT-mini: 256 numbers in 4 layers of 4 heads."""
+        return BertConfig(vocab=vocab, dim=256, layers=4, heads=4, hidden=1024)
+
+    @staticmethod
+    def small(vocab=30522):
+        """Turc et al.'s BERT-tiny: 128 numbers in 2 layers of 2 heads; small enough to teach from scratch on a
+        few thousand texts."""
+        return BertConfig(vocab=vocab, dim=128, layers=2, heads=2, hidden=512)
+
 
 class Bert(nn.Module):
     def __init__(self, cfg: BertConfig):
@@ -74,3 +90,41 @@ class BertForSequenceClassification(nn.Module):
 
     def forward(self, ids, type_ids=None, attention_mask=None):
         return self.head(self.drop(self.bert(ids, type_ids, attention_mask)[1]))
+
+
+class TextClassifier(nn.Module):
+    """A BERT that reads token ids ``[B, S]`` and says a class (text/bert.go: BERT): ``encode`` gives each
+    token's vector, ``features`` the pooled [CLS] vector, ``forward`` the logits.  Padding (``pad_id``) is
+    hidden from attention.  ``set_head`` / ``head_parameters`` serve transfer learning."""
+
+    def __init__(self, cfg: BertConfig, classes: int, pad_id: int = 0):
+        if cfg.dim % cfg.heads:
+            raise ValueError(f"BERT: {cfg.dim} features over {cfg.heads} heads")
+        self.bert, self.drop, self.head = Bert(cfg), nn.Dropout(cfg.dropout), nn.Linear(cfg.dim, classes)
+        self.width, self.pad_id = cfg.dim, pad_id
+
+    def _ids(self, x):
+        x = x if isinstance(x, T.Tensor) else T.tensor(torch.as_tensor(x))
+        return T.cast(x, torch.int64) if x.dtype != torch.int64 else x
+
+    def _run(self, x):
+        ids = self._ids(x)
+        if ids.shape[1] > self.bert.cfg.max_positions:
+            raise ValueError(f"BERT: {ids.shape[1]} tokens, the model reads {self.bert.cfg.max_positions}")
+        visible = T.logical_not(T.equal(ids, T.tensor(torch.tensor(self.pad_id), device=ids.device)))
+        return self.bert(ids, attention_mask=visible)
+
+    def encode(self, x):
+        return self._run(x)[0]
+
+    def features(self, x):
+        return self._run(x)[1]
+
+    def forward(self, x):
+        return self.head(self.drop(self.features(x)))
+
+    def set_head(self, classes: int) -> None:
+        self.head = nn.Linear(self.width, classes)
+
+    def head_parameters(self) -> list:
+        return self.head.parameters()

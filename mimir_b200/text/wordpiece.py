@@ -10,8 +10,37 @@ class WordPiece:
     def __init__(self, vocab, lower: bool = True, unk="[UNK]", cls="[CLS]", sep="[SEP]", pad="[PAD]", mask="[MASK]",
                  max_chars: int = 100):
         self.tokens = list(vocab)
+        have = set(self.tokens)
+        for special in (pad, unk, cls, sep, mask):          # the special tokens a vocabulary lacks are added at the end
+            if special not in have:
+                self.tokens.append(special)
+                have.add(special)
         self.ids = {t: i for i, t in enumerate(self.tokens)}
         self.lower, self.unk, self.cls, self.sep, self.pad, self.mask, self.max_chars = lower, unk, cls, sep, pad, mask, max_chars
+
+    # -- the vocabulary
+    @property
+    def size(self) -> int:
+        return len(self.tokens)
+
+    def vocab(self) -> list:
+        """The tokens in id order, to save and read back."""
+        return list(self.tokens)
+
+    def id(self, token: str) -> int:
+        return self.ids.get(token, self.ids[self.unk])
+
+    def token(self, i: int) -> str:
+        return self.tokens[i] if 0 <= i < len(self.tokens) else self.unk
+
+    @property
+    def pad_id(self) -> int:
+        return self.ids[self.pad]
+
+    def encode_ids(self, text: str, length: int) -> list:
+        """The ids of [CLS], the text's tokens and [SEP], cut or padded with [PAD] to ``length``: one input
+        row of a BERT."""
+        return self.encode(text, max_len=length)[0]
 
     @staticmethod
     def from_file(path: str, **kw) -> "WordPiece":
@@ -103,3 +132,42 @@ class WordPiece:
             else:
                 words.append(t)
         return " ".join(words)
+
+
+def build_vocab(texts, size: int, lower: bool = True) -> list:
+    """A vocabulary of at most ``size`` tokens for a BERT taught from scratch on ``texts``: the special
+    tokens, every character the texts hold (alone and as a word piece), then the most common words and the
+    most common word endings until ``size`` is reached.  Every word of the texts is then read whole or in
+    pieces and none is [UNK]."""
+    basic = WordPiece([], lower=lower)
+    words: dict = {}
+    for t in texts:
+        for w in basic.basic(t):
+            words[w] = words.get(w, 0) + 1
+    out = list(basic.tokens)
+    seen = set(out)
+
+    def add(tok):
+        if tok not in seen and len(out) < size:
+            out.append(tok)
+            seen.add(tok)
+    chars = sorted({c for w in words for c in w})
+    for c in chars:
+        add(c)
+    for c in chars:
+        add("##" + c)
+    endings: dict = {}
+    for w, n in words.items():
+        for k in range(1, len(w)):
+            e = "##" + w[k:]
+            endings[e] = endings.get(e, 0) + n
+    by_count = lambda d: [k for k, _ in sorted(d.items(), key=lambda kv: (-kv[1], kv[0]))]  # noqa: E731
+    ws, es = by_count({w: n for w, n in words.items() if len(w) > 1}), by_count({e: n for e, n in endings.items() if len(e) > 3})
+    for i in range(max(len(ws), len(es))):                 # words and endings in turn, the most common first
+        if i < len(ws):
+            add(ws[i])
+        if i < len(es):
+            add(es[i])
+        if len(out) >= size:
+            break
+    return out
