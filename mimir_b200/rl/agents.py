@@ -60,6 +60,13 @@ class DQN:
             return self.rng.randrange(self.actions)
         return int(self.q(T.tensor([obs])).data().argmax())
 
+    def greedy(self, obs) -> int:
+        return self.act(obs, greedy=True)
+
+    def values(self, obs) -> list:
+        """The value of each action in ``obs``."""
+        return self.q(T.tensor([obs])).data()[0].tolist()
+
     def observe(self, obs, action, reward, nxt, done):
         self.buf.add(obs, action, reward, nxt, float(done))
         self.steps += 1
@@ -116,10 +123,21 @@ class PPO:
         a = int(torch.multinomial(probs, 1, generator=self.gen))
         return a, float(torch.log(probs[a])), value
 
+    def probabilities(self, obs) -> list:
+        """How likely the policy is to take each action in ``obs``."""
+        return torch.softmax(self.pi(T.tensor([obs])).data()[0], 0).tolist()
+
+    def greedy(self, obs) -> int:
+        return int(self.pi(T.tensor([obs])).data()[0].argmax())
+
     def update(self, obs, actions, logps, rewards, values, dones, last_value):
+        """One rollout of one environment: advantages by GAE, then ``update_from``."""
         adv, ret = gae(rewards, values, dones, last_value, self.gamma, self.lam)
-        obs, actions = torch.tensor(obs, dtype=torch.float32), torch.tensor(actions)
-        old, adv, ret = torch.tensor(logps), torch.tensor(adv), torch.tensor(ret)
+        return self.update_from(torch.tensor(obs, dtype=torch.float32), torch.tensor(actions), torch.tensor(logps),
+                                torch.tensor(adv), torch.tensor(ret))
+
+    def update_from(self, obs, actions, old, adv, ret):
+        """``epochs`` passes of minibatches over steps whose advantages and returns are given (tensors)."""
         adv = (adv - adv.mean()) / (adv.std() + 1e-8)
         stats = {}
         for _ in range(self.epochs):
