@@ -6,3 +6,11 @@ from .transformer import (RotaryEmbedding, KVCache, SelfAttention, MultiheadAtte
 from .rnn import RNN, LSTM, GRU  # noqa: F401
 from .gnn import Graph, GCNConv, SAGEConv, GATConv  # noqa: F401
 from . import loss  # noqa: F401
+
+LoRA = LoRALinear          # the reference's name for the adapter layer
+
+
+def LogSoftmax(dim=-1):
+    from .module import _Fn
+    from .. import tensor as _T
+    return _Fn(lambda x: _T.log_softmax(x, dim))
