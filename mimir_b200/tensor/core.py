@@ -1218,6 +1218,9 @@ def realize_into(dsts, srcs):
         for (i, s), v in zip(todo, vals):
             s._val = v.detach() if torch.is_tensor(v) else v
             s._fn, s._args, s._kw = None, (), {}
+            if _mem._VERSIONS:
+                # fresh memory may sit at an address that an older, overwritten storage had
+                s._sver = _mem.version_of(s._val)
     for d, s in zip(dsts, srcs):
         if d is None:
             continue
