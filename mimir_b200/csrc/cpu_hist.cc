@@ -56,48 +56,49 @@ MIMIR_CPU_API int mimir_cpu_hist(const uint8_t* bins, int F, const int64_t* idx,
 // ---------------------------------------------------------------------------
 namespace {
 
-struct Hist {
-  std::vector<double> v;   // [3][F][nbins]
+// One (feature, bin) cell: the sums of gradients and hessians and the count of the rows that fall in it, side
+// by side, so a row's update of a feature touches one cache line instead of three.
+struct Cell {
+  double g, h, c;
 };
 
-void build_hist(const uint8_t* bins, int F, const int64_t* idx, long long n, const float* g, const float* h, int nbins,
-                mimir_cpu::Pool& pool, std::vector<double>& partial, double* out) {
+struct Hist {
+  std::vector<Cell> v;   // [F][nbins]
+};
+
+// The histogram of the rows idx[0 .. n) over bins held one COLUMN per feature (colbins [F][total]): a
+// feature's pass streams the node's gradients, gathered once into row order (og / oh), and touches only that
+// feature's cells, which stay in the first-level cache.  Workers share the features, so nothing is cleared,
+// summed or ordered afterwards and the result is the same for any number of workers.
+void build_hist(const uint8_t* colbins, long long total, int F, const int64_t* idx, long long n, const float* g, const float* h,
+                int nbins, mimir_cpu::Pool& pool, std::vector<float>& og, std::vector<float>& oh, Cell* out) {
   const size_t cells = static_cast<size_t>(F) * nbins;
-  memset(out, 0, sizeof(double) * 3 * cells);
-  const int parts = n < 8192 ? 1 : pool.size();
-  if (parts == 1) {
-    double *hg = out, *hh = out + cells, *hc = out + 2 * cells;
+  memset(static_cast<void*>(out), 0, sizeof(Cell) * cells);
+  if (static_cast<long long>(og.size()) < n) { og.resize(n); oh.resize(n); }
+  for (long long k = 0; k < n; ++k) { og[k] = g[idx[k]]; oh[k] = h[idx[k]]; }
+  auto feature = [&](int f) {
+    const uint8_t* col = colbins + static_cast<size_t>(f) * total;
+    Cell* c = out + static_cast<size_t>(f) * nbins;
     for (long long k = 0; k < n; ++k) {
-      const long long r = idx[k];
-      const uint8_t* row = bins + static_cast<size_t>(r) * F;
-      const double gv = g[r], hv = h[r];
-      for (int f = 0; f < F; ++f) {
-        const size_t c = static_cast<size_t>(f) * nbins + row[f];
-        hg[c] += gv; hh[c] += hv; hc[c] += 1.0;
-      }
+      Cell& cell = c[col[idx[k]]];
+      cell.g += og[k];
+      cell.h += oh[k];
+      cell.c += 1.0;
     }
+  };
+  const int workers = pool.size();
+  if (n * F < 65536 || workers == 1 || F < 2) {
+    for (int f = 0; f < F; ++f) feature(f);
     return;
   }
-  partial.assign(static_cast<size_t>(parts) * 3 * cells, 0.0);
+  // half the workers take features: a feature's pass is bound by the latency of its own additions, which a
+  // second hardware thread on the same core only slows down
+  const int takers = workers > 2 ? workers / 2 : workers;
+  std::atomic<int> next{0};
   pool.run([&](int part, int) {
-    if (part >= parts) return;
-    const long long per = (n + parts - 1) / parts, r0 = part * per, r1 = r0 + per < n ? r0 + per : n;
-    double* hg = partial.data() + static_cast<size_t>(part) * 3 * cells;
-    double *hh = hg + cells, *hc = hh + cells;
-    for (long long k = r0; k < r1; ++k) {
-      const long long r = idx[k];
-      const uint8_t* row = bins + static_cast<size_t>(r) * F;
-      const double gv = g[r], hv = h[r];
-      for (int f = 0; f < F; ++f) {
-        const size_t c = static_cast<size_t>(f) * nbins + row[f];
-        hg[c] += gv; hh[c] += hv; hc[c] += 1.0;
-      }
-    }
+    if (part >= takers) return;
+    for (int f = next.fetch_add(1); f < F; f = next.fetch_add(1)) feature(f);
   });
-  for (int p = 0; p < parts; ++p) {
-    const double* src = partial.data() + static_cast<size_t>(p) * 3 * cells;
-    for (size_t c = 0; c < 3 * cells; ++c) out[c] += src[c];
-  }
 }
 
 inline uint64_t splitmix(uint64_t& s) {
@@ -109,19 +110,19 @@ inline uint64_t splitmix(uint64_t& s) {
 
 }  // namespace
 
-// Grows a tree over the rows idx[0 .. n) (idx is reordered in place).  colsample_k: features tried per node
+// Grows a tree over the rows idx[0 .. n) (idx is reordered in place); bins are held one column per feature.  colsample_k: features tried per node
 // (0 = all), drawn from `seed`.  nodes: double [max_nodes][5] = feature (-1: leaf), bin, left, right, value;
 // importance: double [F], gains added per split feature.  Returns the number of nodes, or -1.
-MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, long long n, const float* g, const float* h,
-                                      int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
-                                      unsigned long long seed, double* nodes, int max_nodes, double* importance) {
+static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, long long n, const float* g, const float* h,
+                     int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
+                     unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out) {
   if (F < 1 || nbins < 1 || nbins > 256 || n < 1 || max_nodes < 1 || max_depth < 0) return -1;
   std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
   mimir_cpu::Pool& pool = mimir_cpu::pool();
   const size_t cells = static_cast<size_t>(F) * nbins;
   struct Item { long long lo, hi; int depth, node; Hist* hist; double G, H; };   // hist == nullptr: a leaf, sums given
   std::vector<Item> stack;
-  std::vector<double> partial;
+  std::vector<float> og, oh;
   std::vector<int64_t> scratch(n);
   std::vector<int> feats(F);
   uint64_t rng = seed;
@@ -131,8 +132,8 @@ MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, 
     nd[0] = -1; nd[1] = 0; nd[2] = -1; nd[3] = -1; nd[4] = value;
     return n_nodes++;
   };
-  Hist* root = new Hist{std::vector<double>(3 * cells)};
-  build_hist(bins, F, idx, n, g, h, nbins, pool, partial, root->v.data());
+  Hist* root = new Hist{std::vector<Cell>(cells)};
+  build_hist(bins, total, F, idx, n, g, h, nbins, pool, og, oh, root->v.data());
   stack.push_back({0, n, 0, -1, root, 0, 0});
   // the parent's child slots are patched when a child gets its number; children are numbered in
   // depth-first order, left before right, like a recursive builder numbers them
@@ -145,18 +146,24 @@ MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, 
     const Patch pt = patch.back();
     patch.pop_back();
     double G = it.G, H = it.H;
-    const double* hg = it.hist ? it.hist->v.data() : nullptr;
-    const double *hh = hg + cells, *hc = hh + cells;
+    const Cell* hc = it.hist ? it.hist->v.data() : nullptr;
     if (it.hist) {
       G = H = 0;
-      for (int b = 0; b < nbins; ++b) { G += hg[b]; H += hh[b]; }
+      for (int b = 0; b < nbins; ++b) { G += hc[b].g; H += hc[b].h; }      // every row falls in some bin of feature 0
     }
     if (n_nodes >= max_nodes) { delete it.hist; return -1; }
     const int node = new_node(-G / (H + l2));
     if (pt.parent >= 0) nodes[static_cast<size_t>(pt.parent) * 5 + 2 + pt.side] = node;
     const long long cnt = it.hi - it.lo;
-    if (!it.hist) continue;
-    if (it.depth >= max_depth || cnt < 2 * min_leaf) { delete it.hist; continue; }
+    // a node that stays a leaf tells its rows their value (when the caller wants the tree's answers for the
+    // rows it was grown on, which saves a pass over the tree afterwards)
+    auto settle = [&]() {
+      if (!leaf_out) return;
+      const float v = static_cast<float>(-G / (H + l2));
+      for (long long k = it.lo; k < it.hi; ++k) leaf_out[idx[k]] = v;
+    };
+    if (!it.hist) { settle(); continue; }
+    if (it.depth >= max_depth || cnt < 2 * min_leaf) { delete it.hist; settle(); continue; }
     // features tried at this node
     int nf = F;
     for (int f = 0; f < F; ++f) feats[f] = f;
@@ -174,8 +181,8 @@ MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, 
       const int f = feats[q];
       double GL = 0, HL = 0, CL = 0;
       for (int b = 0; b < nbins; ++b) {
-        const size_t c = static_cast<size_t>(f) * nbins + b;
-        GL += hg[c]; HL += hh[c]; CL += hc[c];
+        const Cell& cell = hc[static_cast<size_t>(f) * nbins + b];
+        GL += cell.g; HL += cell.h; CL += cell.c;
         const double CR = static_cast<double>(cnt) - CL;
         if (CL < static_cast<double>(min_leaf) || CR < static_cast<double>(min_leaf)) continue;
         const double GR = G - GL, HR = H - HL;
@@ -183,31 +190,69 @@ MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, 
         if (gain > best_gain) { best_gain = gain; best_f = f; best_b = b; best_GL = GL; best_HL = HL; }
       }
     }
-    if (best_f < 0 || !(best_gain > min_gain)) { delete it.hist; continue; }
+    if (best_f < 0 || !(best_gain > min_gain)) { delete it.hist; settle(); continue; }
     importance[best_f] += best_gain;
     nodes[static_cast<size_t>(node) * 5] = best_f;
     nodes[static_cast<size_t>(node) * 5 + 1] = best_b;
-    // stable partition of the rows: left rows first, both sides in their old order
+    // stable partition of the rows: left rows first, both sides in their old order.  Large nodes are cut
+    // into one chunk per worker: each counts its left rows, then writes both kinds at the places the counts
+    // before it give (the same order as a serial pass).
     long long nl = 0, nr = 0;
-    for (long long k = it.lo; k < it.hi; ++k) {
-      const int64_t r = idx[k];
-      if (bins[static_cast<size_t>(r) * F + best_f] <= best_b) idx[it.lo + nl++] = r;
-      else scratch[nr++] = r;
+    const uint8_t* col = bins + static_cast<size_t>(best_f) * total;
+    const long long cnt_rows = it.hi - it.lo;
+    const int chunks = cnt_rows < 32768 ? 1 : pool.size();
+    if (chunks == 1) {
+      for (long long k = it.lo; k < it.hi; ++k) {
+        const int64_t r = idx[k];
+        const bool left = col[r] <= best_b;
+        idx[it.lo + nl] = r;           // both stores are made and one of the two cursors moves: no branch to mispredict
+        scratch[nr] = r;
+        nl += left;
+        nr += !left;
+      }
+      memcpy(idx + it.lo + nl, scratch.data(), sizeof(int64_t) * nr);
+    } else {
+      std::vector<long long> lefts(chunks + 1, 0);
+      const long long per = (cnt_rows + chunks - 1) / chunks;
+      pool.run([&](int part, int) {
+        if (part >= chunks) return;
+        const long long a = it.lo + part * per, b = a + per < it.hi ? a + per : it.hi;
+        long long c = 0;
+        for (long long k = a; k < b; ++k) c += col[idx[k]] <= best_b;
+        lefts[part + 1] = c;
+      });
+      for (int p = 0; p < chunks; ++p) lefts[p + 1] += lefts[p];
+      nl = lefts[chunks];
+      nr = cnt_rows - nl;
+      pool.run([&](int part, int) {
+        if (part >= chunks) return;
+        const long long a = it.lo + part * per, b = a + per < it.hi ? a + per : it.hi;
+        if (a >= b) return;
+        long long wl = lefts[part], wr = nl + (a - it.lo) - lefts[part];       // rights before this chunk = rows before - lefts before
+        for (long long k = a; k < b; ++k) {
+          const int64_t r = idx[k];
+          if (col[r] <= best_b) scratch[wl++] = r;
+          else scratch[wr++] = r;
+        }
+      });
+      memcpy(idx + it.lo, scratch.data(), sizeof(int64_t) * cnt_rows);
     }
-    memcpy(idx + it.lo + nl, scratch.data(), sizeof(int64_t) * nr);
     const long long mid = it.lo + nl;
     Hist *lh = nullptr, *rh = nullptr;
     if (it.depth + 1 < max_depth) {
       // children that may split again need histograms: the smaller one is counted, the larger one is
       // the parent's minus it
-      lh = new Hist{std::vector<double>(3 * cells)};
+      lh = new Hist{std::vector<Cell>(cells)};
       rh = it.hist;
+      auto subtract = [&]() {
+        for (size_t c = 0; c < cells; ++c) { rh->v[c].g -= lh->v[c].g; rh->v[c].h -= lh->v[c].h; rh->v[c].c -= lh->v[c].c; }
+      };
       if (nl <= nr) {
-        build_hist(bins, F, idx + it.lo, nl, g, h, nbins, pool, partial, lh->v.data());
-        for (size_t c = 0; c < 3 * cells; ++c) rh->v[c] -= lh->v[c];
+        build_hist(bins, total, F, idx + it.lo, nl, g, h, nbins, pool, og, oh, lh->v.data());
+        subtract();
       } else {
-        build_hist(bins, F, idx + mid, nr, g, h, nbins, pool, partial, lh->v.data());
-        for (size_t c = 0; c < 3 * cells; ++c) rh->v[c] -= lh->v[c];
+        build_hist(bins, total, F, idx + mid, nr, g, h, nbins, pool, og, oh, lh->v.data());
+        subtract();
         Hist* t = lh; lh = rh; rh = t;  // lh = left (larger, by subtraction), rh = right (counted)
       }
     } else {
@@ -220,6 +265,19 @@ MIMIR_CPU_API int mimir_cpu_grow_tree(const uint8_t* bins, int F, int64_t* idx, 
     patch.push_back({node, 0});
   }
   return n_nodes;
+}
+
+// bins: one COLUMN per feature, uint8 [F][total]; idx [n] holds row numbers in [0, total).
+// leaf_out (float [total], may be null) receives the value of the leaf each grown-on row reached.
+MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long total, int F, int64_t* idx, long long n, const float* g,
+                                              const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2,
+                                              int colsample_k, unsigned long long seed, double* nodes, int max_nodes,
+                                              double* importance, float* leaf_out) {
+  if (total < 1) return -1;
+  for (long long k = 0; k < n; ++k)
+    if (idx[k] < 0 || idx[k] >= total) return -1;
+  return grow_tree(colbins, total, F, idx, n, g, h, nbins, max_depth, min_leaf, min_gain, l2, colsample_k, seed, nodes, max_nodes,
+                   importance, leaf_out);
 }
 
 // out[r] = value of the leaf row r of `bins` (uint8 [n][F]) reaches in the tree `nodes` (double [n_nodes][5]).

@@ -32,6 +32,19 @@ class Pool {
     for (auto& t : workers_) t.join();
   }
   int size() const { return static_cast<int>(workers_.size()) + 1; }
+  // While a Hot object lives the workers keep spinning between jobs instead of going to sleep: for a
+  // caller that hands over many short jobs with serial work of its own in between (a tree grower), where
+  // waking a sleeper would cost more than the job.
+  class Hot {
+   public:
+    explicit Hot(Pool& p) : p_(p) { p_.hot_.fetch_add(1, std::memory_order_relaxed); }
+    ~Hot() { p_.hot_.fetch_sub(1, std::memory_order_relaxed); }
+    Hot(const Hot&) = delete;
+    Hot& operator=(const Hot&) = delete;
+
+   private:
+    Pool& p_;
+  };
   // runs fn(part, parts) on every thread (the caller is part 0) and returns when all are done
   void run(const std::function<void(int, int)>& fn) {
     const int parts = size();
@@ -56,7 +69,7 @@ class Pool {
     for (;;) {
       int spins = 0;
       while (epoch_.load(std::memory_order_acquire) == seen && !quit_.load(std::memory_order_relaxed)) {
-        if (++spins < 1500) { _mm_pause(); continue; }
+        if (++spins < 1500 || hot_.load(std::memory_order_relaxed) > 0) { _mm_pause(); continue; }
         std::unique_lock<std::mutex> lk(m_);
         sleepers_.fetch_add(1, std::memory_order_release);
         cv_.wait(lk, [&] { return quit_.load() || epoch_.load(std::memory_order_acquire) != seen; });
@@ -74,6 +87,7 @@ class Pool {
   const std::function<void(int, int)>* fn_ = nullptr;
   std::atomic<int> pending_{0};
   std::atomic<int> sleepers_{0};
+  std::atomic<int> hot_{0};
   std::atomic<uint64_t> epoch_{0};
   std::atomic<bool> quit_{false};
 };

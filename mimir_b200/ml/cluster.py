@@ -16,7 +16,8 @@ NOISE = -1
 
 
 def _sq(A, B):
-    return ((A * A).sum(1, keepdim=True) - 2.0 * (A @ B.t()) + (B * B).sum(1)[None]).clamp_min(0)
+    from .neighbors import pairwise_sq
+    return pairwise_sq(A, B).clamp_min_(0)
 
 
 def _table(X, features, what):
@@ -48,27 +49,51 @@ class Means(Model):
         return GroupsModule.of(self)
 
 
-def _plus_plus(Z, k, g):
-    pool = Z if Z.shape[0] <= 100_000 else Z[torch.randperm(Z.shape[0], generator=g)[:100_000]]
-    centers = pool[torch.randint(0, pool.shape[0], (1,), generator=g)]
-    d = _sq(pool, centers)[:, 0]
+def _extend(Z):
+    """Rows as ``[z, |z|^2, 1]``: their squared distances to centers are then one product with ``_centers_ext``."""
+    z2 = (Z * Z).sum(1, keepdim=True)
+    return torch.cat([Z, z2, torch.ones_like(z2)], 1)
+
+
+def _to_centers(Zx, C):
+    """``[rows, k]`` squared distances of extended rows to the centers ``C``."""
+    Cx = torch.cat([C * -2.0, torch.ones(C.shape[0], 1, dtype=C.dtype), (C * C).sum(1, keepdim=True)], 1)
+    return (Zx @ Cx.t()).clamp_min_(0)
+
+
+def _draw(weights, g):
+    """One index with a chance in proportion to ``weights`` (a cumulative sum and a binary search)."""
+    cum = torch.cumsum(weights.double(), 0)
+    total = float(cum[-1])
+    if not total > 0:
+        return int(torch.randint(0, weights.numel(), (1,), generator=g))
+    u = torch.rand(1, generator=g, dtype=torch.double) * total
+    return min(int(torch.searchsorted(cum, u)), weights.numel() - 1)
+
+
+def _plus_plus(Z, Zx, k, g):
+    if Z.shape[0] > 100_000:
+        pick = torch.randperm(Z.shape[0], generator=g)[:100_000]
+        Z, Zx = Z[pick], Zx[pick]
+    centers = Z[int(torch.randint(0, Z.shape[0], (1,), generator=g))][None]
+    d = _to_centers(Zx, centers)[:, 0]
     for _ in range(1, k):
-        total = float(d.sum())
-        pick = torch.multinomial(d / total, 1, generator=g) if total > 0 else torch.randint(0, pool.shape[0], (1,), generator=g)
-        centers = torch.cat([centers, pool[pick]])
-        d = torch.minimum(d, _sq(pool, pool[pick])[:, 0])
+        nxt = Z[_draw(d, g)][None]
+        centers = torch.cat([centers, nxt])
+        d = torch.minimum(d, _to_centers(Zx, nxt)[:, 0])
     return centers
 
 
-def _lloyd(Z, centers, max_iter, tol):
+def _lloyd(Z, Zx, centers, max_iter, tol):
     k = centers.shape[0]
     for _ in range(max_iter):
-        d = _sq(Z, centers)
+        d = _to_centers(Zx, centers)
         a = d.argmin(1)
-        new = torch.zeros_like(centers).index_add_(0, a, Z)
-        cnt = torch.bincount(a, minlength=k)
+        onehot = torch.zeros(Z.shape[0], k, dtype=Z.dtype)
+        onehot.scatter_(1, a[:, None], 1.0)
+        cnt = onehot.sum(0)
+        new = (onehot.t() @ Z) / cnt.clamp_min(1)[:, None]         # the sums of each group's rows as one product
         empty = cnt == 0
-        new = new / cnt.clamp_min(1)[:, None]
         if empty.any():
             # a center that lost every row restarts at the row farthest from its center
             far = d.min(1).values.topk(int(empty.sum())).indices
@@ -77,7 +102,7 @@ def _lloyd(Z, centers, max_iter, tol):
         centers = new
         if moved <= tol:
             break
-    d = _sq(Z, centers)
+    d = _to_centers(Zx, centers)
     return centers, float(d.min(1).values.sum())
 
 
@@ -90,9 +115,10 @@ def kmeans_fit(X, k: int, features: int | None = None, inits: int = 4, max_iter:
     std = Standard.fit(X)
     Z = std.apply(X)
     g = torch.Generator().manual_seed(seed)
+    Zx = _extend(Z)
     best = None
     for _ in range(inits):
-        centers, inertia = _lloyd(Z, _plus_plus(Z, k, g), max_iter, tol)
+        centers, inertia = _lloyd(Z, Zx, _plus_plus(Z, Zx, k, g), max_iter, tol)
         if best is None or inertia < best[1]:
             best = (centers, inertia)
     m = Means()

@@ -221,6 +221,22 @@ def _unscale(w_std, b_std, std: Standard):
     return w.float(), (b_std - w @ std.mean.double()).float()
 
 
+def _native_cd(G, c, l1, l2, tol, max_iter, w) -> bool:
+    """Coordinate descent on the Gram matrix in native code; False when the library is missing."""
+    import ctypes
+    from .. import _native
+    if not _native.available():
+        return False
+    lib = _native.lib()
+    if not getattr(lib, "_cd_bound", False):
+        lib.mimir_cpu_elastic_cd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_double, ctypes.c_double,
+                                             ctypes.c_double, ctypes.c_int, ctypes.c_void_p]
+        lib.mimir_cpu_elastic_cd.restype = ctypes.c_int
+        lib._cd_bound = True
+    Gc, cc = G.contiguous(), c.contiguous()
+    return lib.mimir_cpu_elastic_cd(Gc.data_ptr(), cc.data_ptr(), Gc.shape[0], float(l1), float(l2), float(tol), int(max_iter), w.data_ptr()) >= 0
+
+
 def regression(d, l1: float = 0.0, l2: float = 0.0, max_iter: int = 1000, tol: float = 1e-6) -> Linear:
     """Least squares with optional lasso (``l1``) and ridge (``l2``) penalties on standardized features:
     ``1/(2n) |y - Xw - b|^2 + l1 |w|_1 + l2/2 |w|^2``.  Without ``l1`` the normal equations are solved
@@ -241,7 +257,7 @@ def regression(d, l1: float = 0.0, l2: float = 0.0, max_iter: int = 1000, tol: f
     else:
         w = torch.zeros(F, dtype=torch.double)
         diag = G.diagonal()
-        for _ in range(max_iter):
+        for _ in range(0 if _native_cd(G, c, l1, l2, tol, max_iter, w) else max_iter):
             moved = 0.0
             for j in range(F):
                 if diag[j] <= 0:

@@ -7,7 +7,12 @@ import torch
 
 
 def pairwise_sq(A, B):
-    return (A * A).sum(1, keepdim=True) - 2 * A @ B.t() + (B * B).sum(1)[None]
+    """Squared Euclidean distances ``[rows of A, rows of B]`` as ONE matrix product: the rows are extended to
+    ``[a, |a|^2, 1]`` and ``[-2 b, 1, |b|^2]``, so the result is written once instead of being built from
+    three full-size temporaries."""
+    a2, b2 = (A * A).sum(1, keepdim=True), (B * B).sum(1, keepdim=True)
+    one_a, one_b = torch.ones_like(a2), torch.ones_like(b2)
+    return torch.cat([A, a2, one_a], 1) @ torch.cat([B * -2.0, one_b, b2], 1).t()
 
 
 class KNN:
@@ -228,6 +233,27 @@ def distances(metric: str, Q: torch.Tensor, R: torch.Tensor) -> torch.Tensor:
     raise ValueError(f"unknown metric {metric!r}: want one of {METRICS}")
 
 
+def _smallest(D, k: int, group: int = 64):
+    """The ``k`` smallest of each row of ``D`` with their columns, smallest first.  Wide rows are searched in
+    two steps: the minimum of every group of 64 columns (one vectorised pass), then only the ``k`` groups
+    with the smallest minima, which must hold the ``k`` smallest values (the k-th smallest value cannot
+    exceed the k-th smallest group minimum)."""
+    q, n = D.shape
+    if n <= 8192 or k * group >= n:
+        return torch.topk(D, k, dim=1, largest=False)
+    full = n // group * group
+    mins = D[:, :full].reshape(q, -1, group).amin(2)
+    tail = D[:, full:]
+    groups = torch.topk(mins, k, dim=1, largest=False).indices                    # [q, k]
+    cols = (groups[:, :, None] * group + torch.arange(group)[None, None]).reshape(q, -1)
+    cand, cand_cols = D.gather(1, cols), cols
+    if tail.shape[1]:
+        cand = torch.cat([cand, tail], 1)
+        cand_cols = torch.cat([cols, torch.arange(full, n).expand(q, -1)], 1)
+    d, j = torch.topk(cand, k, dim=1, largest=False)
+    return d, cand_cols.gather(1, j)
+
+
 class Neighbors(Model):
     """The kept rows (standardized unless ``raw``) and their answers.  ``predict`` gives ``classes``
     probabilities per row (the neighbours' votes, weighted by inverse distance with ``by_distance``) or
@@ -238,9 +264,39 @@ class Neighbors(Model):
     def neighbors(self, X):
         """For each row of ``X`` its ``k`` nearest kept rows: ``(index [q, k], distance [q, k])``, nearest first."""
         Q = self.standard.apply(as_rows(X, self.features))
-        dist = distances(self.metric, Q, self.rows)
-        d, i = torch.topk(dist, min(self.k, self.rows.shape[0]), dim=1, largest=False)
-        return i, d
+        k = min(self.k, self.rows.shape[0])
+        # tiles of 256 queries by 4096 kept rows stay in cache: each tile is one small matrix product and gives
+        # its k nearest; the candidates of a query block are merged at the end.  Euclidean neighbours are
+        # chosen on squared distances and only the chosen take a square root.
+        n = self.rows.shape[0]
+        qb, rb = 256, (4096 if n > 32768 else max(n, 1))
+        ext = None
+        if self.metric == EUCLIDEAN:
+            ext = getattr(self, "_ext", None)
+            if ext is None or ext.shape[0] != n:
+                r2 = (self.rows * self.rows).sum(1, keepdim=True)
+                ext = self._ext = torch.cat([self.rows * -2.0, torch.ones_like(r2), r2], 1).contiguous()
+        ds, ids = [], []
+        for s in range(0, Q.shape[0], qb):
+            q = Q[s:s + qb]
+            if ext is not None:
+                q2 = (q * q).sum(1, keepdim=True)
+                q = torch.cat([q, q2, torch.ones_like(q2)], 1)
+            cd, ci = [], []
+            for r in range(0, n, rb):
+                tile = q @ ext[r:r + rb].t() if ext is not None else distances(self.metric, q, self.rows[r:r + rb])
+                d, i = _smallest(tile, min(k, tile.shape[1]))
+                cd.append(d)
+                ci.append(i + r)
+            d, i = torch.cat(cd, 1), torch.cat(ci, 1)
+            if d.shape[1] > k:
+                d, j = torch.topk(d, k, dim=1, largest=False)
+                i = i.gather(1, j)
+            ds.append(d.clamp_min(0).sqrt() if ext is not None else d)
+            ids.append(i)
+        if not ds:
+            return torch.zeros(0, k, dtype=torch.long), torch.zeros(0, k)
+        return torch.cat(ids), torch.cat(ds)
 
     def predict(self, X) -> torch.Tensor:
         i, d = self.neighbors(X)

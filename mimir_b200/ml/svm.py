@@ -46,16 +46,18 @@ class _Rows:
         self.Z, self.args = Z, (kind, gamma, coef0, degree)
         n = Z.shape[0]
         self.full = None
-        if n * n * 8 <= cache_mb * (1 << 20):
-            self.full = kernel_matrix(kind, Z, Z, gamma, coef0, degree)
+        if n * n * 4 <= cache_mb * (1 << 20):
+            # single precision holds twice the rows and is what the native solver reads
+            Zf = Z.float()
+            self.full = kernel_matrix(kind, Zf, Zf, gamma, coef0, degree)
         self.cap = max(2, int(cache_mb * (1 << 20) // max(8 * n, 1)))
         self.cache: dict = {}
-        self.diag = self.full.diagonal().clone() if self.full is not None else \
+        self.diag = self.full.diagonal().double() if self.full is not None else \
             torch.stack([kernel_matrix(kind, Z[i:i + 1], Z[i:i + 1], gamma, coef0, degree)[0, 0] for i in range(n)])
 
     def row(self, i: int):
         if self.full is not None:
-            return self.full[i]
+            return self.full[i].double()
         r = self.cache.pop(i, None)
         if r is None:
             kind, gamma, coef0, degree = self.args
@@ -72,6 +74,8 @@ def _smo(rows: _Rows, idx, y, p, c, tol, max_iter):
     l = y.numel()
     a = torch.zeros(l, dtype=torch.double)
     G = p.clone()
+    if rows.full is not None and _native_smo(rows, idx, y, c, tol, max_iter, a, G):
+        return a, _bias(a, G, y, c)
     diag = rows.diag[idx]
     tau = 1e-12
     for _ in range(max_iter):
@@ -101,17 +105,37 @@ def _smo(rows: _Rows, idx, y, p, c, tol, max_iter):
         a[i] += y[i] * step
         a[j] -= y[j] * step
         G += (step * y) * (Ki - Kj)
+    return a, _bias(a, G, y, c)
+
+
+def _bias(a, G, y, c) -> float:
+    """``-y_t G_t`` at a free multiplier (their mean), or the midpoint of the violating pair's bounds."""
     score = -y * G
     free = (a > 1e-12 * c) & (a < c * (1 - 1e-12))
     if free.any():
-        bias = float(score[free].mean())
-    else:
-        up = ((y > 0) & (a < c)) | ((y < 0) & (a > 0))
-        low = ((y > 0) & (a > 0)) | ((y < 0) & (a < c))
-        hi = float(score[up].max()) if up.any() else 0.0
-        lo = float(score[low].min()) if low.any() else hi
-        bias = 0.5 * (hi + lo)
-    return a, bias
+        return float(score[free].mean())
+    up = ((y > 0) & (a < c)) | ((y < 0) & (a > 0))
+    low = ((y > 0) & (a > 0)) | ((y < 0) & (a < c))
+    hi = float(score[up].max()) if up.any() else 0.0
+    lo = float(score[low].min()) if low.any() else hi
+    return 0.5 * (hi + lo)
+
+
+def _native_smo(rows, idx, y, c, tol, max_iter, a, G) -> bool:
+    """The solver's loop in native code over the kernel matrix in memory; False when the library is missing."""
+    from .. import _native
+    if not _native.available():
+        return False
+    lib = _native.lib()
+    if not getattr(lib, "_smo_bound", False):
+        lib.mimir_cpu_svm_smo.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong,
+                                          ctypes.c_double, ctypes.c_double, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p]
+        lib.mimir_cpu_svm_smo.restype = ctypes.c_longlong
+        lib._smo_bound = True
+    K32 = rows.full
+    idx64, yd = idx.to(torch.int64).contiguous(), y.double().contiguous()
+    return lib.mimir_cpu_svm_smo(K32.data_ptr(), K32.shape[0], idx64.data_ptr(), yd.data_ptr(), yd.numel(), float(c), float(tol),
+                                 int(max_iter), a.data_ptr(), G.data_ptr()) >= 0
 
 
 def _dcd(Z, y, c, tol, max_iter, seed):
@@ -275,7 +299,7 @@ def fit(d, task, c: float = 1.0, kernel: str = RBF, gamma: float | None = None, 
             biases.append(b)
             f = None
         if f is None:
-            f = torch.stack([rows.row(i) for i in range(n)]) @ beta + b if rows.full is None else rows.full @ beta + b
+            f = torch.stack([rows.row(i) for i in range(n)]) @ beta + b if rows.full is None else (rows.full @ beta.float()).double() + b
         platt.append(_platt(f, y))
     if kernel == LINEAR:
         m.support, m.coef = torch.zeros(0, F, dtype=torch.double), torch.stack(coefs)

@@ -14,10 +14,28 @@ import torch
 def _bin(X, bins=255):
     X = X.float()
     qs = torch.linspace(0, 1, bins + 1)[1:-1]
-    edges = torch.quantile(X, qs.to(X.device), dim=0).t().contiguous()  # [F, bins-1]
+    # the bin edges come from at most 65,536 rows (evenly spaced ones): enough for 255 quantiles, and the sort
+    # of every column is the most expensive step of a fit on a large table
+    S = X if X.shape[0] <= 65536 else X[torch.linspace(0, X.shape[0] - 1, 65536).long()]
+    edges = torch.quantile(S, qs.to(X.device), dim=0).t().contiguous()  # [F, bins-1]
     B = torch.searchsorted(edges, X.t().contiguous()).t().contiguous()
     # one byte per value when the bins allow it: the native histogram pass reads the rows as they are
     return B.to(torch.uint8 if bins <= 256 else torch.int64), edges
+
+
+_COLUMNS: dict = {}
+
+
+def _columns(B):
+    """``B`` with one column per feature in memory (``[F, n]`` contiguous), which is what the native grower
+    reads; kept for the latest table so the trees of one ensemble share it."""
+    key = (B.data_ptr(), tuple(B.shape), B._version)
+    hit = _COLUMNS.get("last")
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    cols = B.t().contiguous()
+    _COLUMNS["last"] = (key, cols, B)          # B is kept alive so its address cannot be reused under the key
+    return cols
 
 
 def _histogram(B, idx, g, h, bins):
@@ -56,19 +74,22 @@ class _Tree:
         self.nodes = []  # (feature, bin, left, right, value)
         self.importance = None
 
-    def fit(self, B, g, h):
+    def fit(self, B, g, h, rows=None):
+        """Grows the tree on the rows ``rows`` of ``B`` (all of them when None); ``g`` and ``h`` are indexed by
+        row number.  After a native fit on all rows ``self.answers`` holds the tree's value for each row."""
         n, F = B.shape
         self.importance = torch.zeros(F)
         self.nodes = []
+        self.answers = None
         if g.dtype != torch.float64:
             g, h = g.float().contiguous(), h.float().contiguous()
         if B.dtype == torch.uint8 and B.device.type == "cpu" and B.is_contiguous() and self.bins <= 256 and g.dtype == torch.float32 \
-                and self._grow_native(B, g, h):
+                and self._grow_native(B, g, h, rows):
             return self
-        self._grow(B, g, h, torch.arange(n, device=B.device), 0)
+        self._grow(B, g, h, torch.arange(n, device=B.device) if rows is None else rows.to(B.device), 0)
         return self
 
-    def _grow_native(self, B, g, h) -> bool:
+    def _grow_native(self, B, g, h, rows=None) -> bool:
         """The whole tree grown by ``csrc/cpu_hist.cc`` (histograms over the worker pool, the larger
         child's histogram by subtraction, rows partitioned in place).  Feature subsets per node are drawn
         from a seed taken from this tree's generator."""
@@ -77,10 +98,12 @@ class _Tree:
         lib = _native.lib()
         if not getattr(lib, "_tree_bound", False):
             c = ctypes
-            lib.mimir_cpu_grow_tree.argtypes = [c.c_void_p, c.c_int, c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
-                                                c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_ulonglong, c.c_void_p, c.c_int, c.c_void_p]
+            lib.mimir_cpu_grow_tree_answers.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
+                                                        c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_ulonglong, c.c_void_p, c.c_int,
+                                                        c.c_void_p, c.c_void_p]
             lib._tree_bound = True
-        n, F = B.shape
+        total, F = B.shape
+        n = total if rows is None else int(rows.numel())
         k = 0
         seed = 0
         if self.colsample < 1.0:
@@ -89,12 +112,16 @@ class _Tree:
         max_nodes = int(min(2 ** (self.max_depth + 1) - 1, 2 * n + 1))
         nodes = torch.empty(max_nodes, 5, dtype=torch.float64)
         imp = torch.zeros(F, dtype=torch.float64)
-        idx = torch.arange(n, dtype=torch.int64)
-        cnt = lib.mimir_cpu_grow_tree(B.data_ptr(), F, idx.data_ptr(), n, g.data_ptr(), h.data_ptr(), self.bins, self.max_depth,
-                                      max(int(self.min_leaf), 1) if self.min_leaf >= 1 else 0, float(self.min_gain), float(self.l2), k, seed,
-                                      nodes.data_ptr(), max_nodes, imp.data_ptr())
+        idx = torch.arange(n, dtype=torch.int64) if rows is None else rows.to(torch.int64).clone()
+        answers = torch.empty(total) if rows is None else None
+        cols = _columns(B)
+        cnt = lib.mimir_cpu_grow_tree_answers(cols.data_ptr(), total, F, idx.data_ptr(), n, g.data_ptr(), h.data_ptr(), self.bins, self.max_depth,
+                                              max(int(self.min_leaf), 1) if self.min_leaf >= 1 else 0, float(self.min_gain), float(self.l2),
+                                              k, seed, nodes.data_ptr(), max_nodes, imp.data_ptr(),
+                                              answers.data_ptr() if answers is not None else None)
         if cnt <= 0:
             return False
+        self.answers = answers
         rows = nodes[:cnt]
         self.nodes = [[int(r[0]), int(r[1]), int(r[2]), int(r[3]), float(r[4])] for r in rows.tolist()]
         self.importance = imp.float()
@@ -276,14 +303,14 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
     if held is not None:
         held["F"] = base.clone().repeat(held["B"].shape[0], 1) if classes > 2 else torch.full((held["B"].shape[0],), base)
     for it in range(trees):
-        rows = torch.arange(n) if subsample >= 1.0 else torch.randperm(n, generator=gen)[: max(1, int(n * subsample))]
+        rows = None if subsample >= 1.0 else torch.randperm(n, generator=gen)[: max(1, int(n * subsample))]
         if classes > 2:
             p = torch.softmax(F, 1)
             round_trees = []
             for k in range(classes):
                 g, h = (p[:, k] - oh[:, k]), (p[:, k] * (1 - p[:, k])).clamp_min(1e-6)
-                t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B[rows], g[rows], h[rows])
-                F[:, k] += learning_rate * t.predict_binned(B)
+                t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B, g, h, rows)
+                F[:, k] += learning_rate * (t.answers if t.answers is not None else t.predict_binned(B))
                 if held is not None:
                     held["F"][:, k] += learning_rate * t.predict_binned(held["B"])
                 round_trees.append(t)
@@ -294,8 +321,8 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
                 g, h = p - yf, (p * (1 - p)).clamp_min(1e-6)
             else:
                 g, h = F - yf, torch.ones(n)
-            t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B[rows], g[rows], h[rows])
-            F += learning_rate * t.predict_binned(B)
+            t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B, g, h, rows)
+            F += learning_rate * (t.answers if t.answers is not None else t.predict_binned(B))
             if held is not None:
                 held["F"] += learning_rate * t.predict_binned(held["B"])
             out_trees.append(t)

@@ -75,7 +75,7 @@ def main(argv=None):
                        lambda m: float(m.score(Xn[half:], ycn[half:]))),
         "rbf_svm_4k": (lambda: svm.fit(ml.Data(X[:4000], y_cls[:4000]), "classification"), lambda m: acc(m.classify(X[half:half + 4000]), y_cls[half:half + 4000]),
                        lambda: sk.svm.SVC(probability=False).fit(Xn[:4000], ycn[:4000]), lambda m: float(m.score(Xn[half:half + 4000], ycn[half:half + 4000]))),
-        "boosting": (lambda: tree.gradient_boosting(X[:half], y_cls[:half], trees=50, max_depth=6, classes=2),
+        "boosting": (lambda: tree.gradient_boosting(X[:half], y_cls[:half], trees=50, max_depth=6, classes=2, min_leaf=20, l2=0.0),
                      lambda m: acc(m.classify(X[half:]), y_cls[half:]),
                      lambda: sk.ensemble.HistGradientBoostingClassifier(max_iter=50, max_depth=6, early_stopping=False).fit(Xn[:half], ycn[:half]),
                      lambda m: float(m.score(Xn[half:], ycn[half:]))),
