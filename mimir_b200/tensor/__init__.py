@@ -8,7 +8,7 @@ from .memory import set_memory_budget, memory_budget, memory_of  # noqa: F401
 from .random import philox_uniform, philox_normal, splitmix64  # noqa: F401
 from .pattern import Pattern, segment  # noqa: F401
 from .linalg import (exp2, log2, greater, fmod, fft, ifft, rfft, irfft, cholesky, triangular_solve, solve, inv, det,  # noqa: F401
-                     slogdet, qr, svd, eigh, rand_gamma, rand_poisson)
+                     slogdet, qr, svd, eigh, rand_gamma, rand_poisson, from_slice, scalar, flatten)
 from . import group  # noqa: F401,E402
 from .group import Group, cpus  # noqa: F401,E402
 from .core import from_bytes, from_bytes_func, realize_into  # noqa: F401,E402

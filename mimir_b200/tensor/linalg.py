@@ -170,3 +170,26 @@ def rand_poisson(rate, seed: int = 0):
         g = torch.Generator(device=r.device).manual_seed(int(seed) & ((1 << 62) - 1))
         return torch.poisson(r.float(), generator=g).to(r.dtype)
     return C._volatile(_node(run, (rate,), {}, "rand_poisson"))
+
+
+def from_slice(values, *shape, dtype=None, device=None):
+    """A tensor of ``shape`` from a flat list of numbers (tensor.FromSlice); floats are float32, whole numbers int32."""
+    v = torch.as_tensor(values)
+    if dtype is None:
+        dtype = torch.float32 if v.dtype.is_floating_point else (torch.bool if v.dtype == torch.bool else torch.int32)
+    v = v.to(dtype)
+    if shape and int(torch.tensor(shape).prod()) != v.numel():
+        return C._error_tensor(E.ErrShape(f"from_slice: {v.numel()} values for shape {tuple(shape)}"))
+    return C.tensor(v.reshape(tuple(shape)) if shape else v, dtype=dtype, device=device)
+
+
+def scalar(value, dtype=None, device=None):
+    """A tensor of no dimensions (tensor.Scalar)."""
+    return from_slice(value, dtype=dtype, device=device)
+
+
+def flatten(x, start: int = 1):
+    """Every axis from ``start`` on as one (tensor.Flatten): ``[N, C, H, W] -> [N, C*H*W]`` by default."""
+    s = tuple(x.shape)
+    start = start if start >= 0 else len(s) + start
+    return C.reshape(x, s[:start] + (-1,))

@@ -181,6 +181,16 @@ class ViT(PictureModel):
         return self.norm(tok)[:, 0]
 
 
+def vit_b16(classes=1000, **kw):
+    """ViT-B/16: 224-pixel pictures in 16-pixel patches, 768 features, 12 layers of 12 heads."""
+    return ViT(224, 16, 768, 12, 12, 3072, classes, **kw)
+
+
+def vit_tiny(classes=1000, image=224, patch=16, **kw):
+    """ViT-Ti: 192 features, 12 layers of 3 heads."""
+    return ViT(image, patch, 192, 12, 3, 768, classes, **kw)
+
+
 class UNet(nn.Module):
     def __init__(self, in_channels=3, classes=1, width=32, depth=4):
         def block(a, b):
