@@ -50,40 +50,12 @@ class Result:
     task: object
 
 
-class _Probabilities:
-    """Gives every family one ``predict``: ``[rows, classes]`` probabilities, or ``[rows]`` values."""
-
-    def __init__(self, model, classes, kind):
-        self.model, self.classes, self.kind = model, classes, kind
-
-    def predict(self, X):
-        p = self.model.predict(X)
-        if self.classes and p.dim() == 1:                       # a two-class tree ensemble answers P(class 1)
-            p = torch.stack([1 - p, p], 1)
-        return p
-
-    def classify(self, X):
-        p = self.predict(X)
-        return p.argmax(1) if p.dim() == 2 else p
-
-
 def _fitter(c: Candidate, task, classes, seed):
     s = c.settings
     if c.family == BOOST:
-        return lambda d: _Probabilities(tree.gradient_boosting(d.X, d.Y, classes=classes, seed=seed, **s), classes, BOOST)
+        return lambda d: tree.boosting(d, task, classes=classes, seed=seed, **s)
     if c.family == FOREST:
-        if classes:
-            # a forest of probability trees: one regression forest per class on its indicator
-            def fit(d):
-                forests = [tree.random_forest(d.X, (d.Y == k).float(), seed=seed + k, **s) for k in range(classes)]
-
-                class _F:
-                    def predict(self, X):
-                        p = torch.stack([f.predict(X) for f in forests], 1).clamp_min(0)
-                        return p / p.sum(1, keepdim=True).clamp_min(1e-12)
-                return _Probabilities(_F(), classes, FOREST)
-            return fit
-        return lambda d: _Probabilities(tree.random_forest(d.X, d.Y, seed=seed, **s), 0, FOREST)
+        return lambda d: tree.forest(d, task, classes=classes, seed=seed, **s)
     if c.family == LINEAR:
         return (lambda d: linear.logistic_fit(d, classes=classes, **s)) if classes else (lambda d: linear.regression(d, **s))
     if c.family == SVM:

@@ -429,3 +429,81 @@ def isolation_forest(X, trees=100, samples=256, seed=0) -> IsolationForestModel:
         grow(rows, 0)
         forest.append(nodes)
     return IsolationForestModel(forest, samples)
+
+
+# ---------------------------------------------------------------------------------------------
+# Table-level entry points (reference: tree/boost.go, tree/forest.go, tree/tree.go, tree/options.go)
+# ---------------------------------------------------------------------------------------------
+class Ensemble:
+    """Trees fitted to a table for a task: ``predict`` gives ``classes`` probabilities per row for
+    classification and one value per row for regression, whatever the kind of ensemble underneath (boosted
+    rounds, or one forest per class).  ``importance()`` is each feature's share of the total gain."""
+
+    def __init__(self, task, classes: int, models: list, kind: str):
+        self.task, self.classes, self.models, self.kind = task, classes, models, kind
+
+    def predict(self, X):
+        X = torch.as_tensor(X).float()
+        if not self.classes:
+            return self.models[0].predict(X)
+        if self.kind == "forest":
+            p = torch.stack([m.predict(X) for m in self.models], 1).clamp_min(0)
+            return p / p.sum(1, keepdim=True).clamp_min(1e-12)
+        p = self.models[0].predict(X)
+        return torch.stack([1 - p, p], 1) if p.dim() == 1 else p
+
+    def classify(self, X):
+        p = self.predict(X)
+        return p.argmax(1) if p.dim() == 2 else p
+
+    def importance(self):
+        imp = sum(m.importance() for m in self.models)
+        return imp / imp.sum().clamp_min(1e-12)
+
+    def module(self):
+        """The ensemble as an ``nn.Module`` (boosted trees and single trees; a forest of several classes is
+        served one class at a time by its members' modules)."""
+        if len(self.models) != 1:
+            raise ValueError("a forest of several classes has one module per class: use models[k].module()")
+        return self.models[0].module()
+
+    def to_json(self) -> str:
+        return json.dumps({"task": str(self.task), "classes": self.classes, "kind": self.kind,
+                           "models": [json.loads(m.to_json()) for m in self.models]})
+
+    @staticmethod
+    def from_json(s: str) -> "Ensemble":
+        from .base import as_task
+        d = json.loads(s)
+        return Ensemble(as_task(d["task"]), d["classes"], [Model.from_json(json.dumps(m)) for m in d["models"]], d["kind"])
+
+
+def _table(d, task, classes):
+    from .base import CLASSIFICATION, as_task, count_classes
+    task = as_task(task)
+    d.check(task)
+    return task, (count_classes(d.Y, classes) if task is CLASSIFICATION else 0)
+
+
+def boosting(d, task, classes: int = 0, **options) -> Ensemble:
+    """Gradient boosting on a table: squared error for regression, logistic loss for two classes, softmax for
+    more.  Options are ``gradient_boosting``'s (``trees``, ``learning_rate``, ``max_depth``, ``min_leaf``,
+    ``min_gain``, ``l2``, ``subsample``, ``colsample``, ``bins``, ``seed``, ``validation`` with ``patience``)."""
+    task, k = _table(d, task, classes)
+    return Ensemble(task, k, [gradient_boosting(d.X, d.Y, classes=k, **options)], "boost")
+
+
+def forest(d, task, classes: int = 0, **options) -> Ensemble:
+    """A random forest on a table; for classification one regression forest per class on its indicator, whose
+    averaged leaves are the class's probability."""
+    task, k = _table(d, task, classes)
+    seed = options.pop("seed", 0)
+    if not k:
+        return Ensemble(task, 0, [random_forest(d.X, d.Y, seed=seed, **options)], "forest")
+    return Ensemble(task, k, [random_forest(d.X, (d.Y == c).float(), seed=seed + c, **options) for c in range(k)], "forest")
+
+
+def single(d, task, classes: int = 0, **options) -> Ensemble:
+    """One decision tree on a table."""
+    task, k = _table(d, task, classes)
+    return Ensemble(task, k, [decision_tree(d.X, d.Y, classes=k, **options)], "tree")

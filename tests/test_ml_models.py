@@ -317,3 +317,23 @@ def test_boosting_stops_when_a_validation_table_stops_improving():
     empty = type(m3.module()).empty(m3.module().shape)
     empty.load_state_dict(m3.module().state_dict())
     assert torch.equal(empty(T.tensor(X[:7])).data(), m3.module()(T.tensor(X[:7])).data())
+
+
+def test_table_level_trees_answer_with_probabilities_and_round_trip():
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(400, 5, generator=g)
+    y3 = torch.bucketize(X[:, 0].contiguous(), torch.tensor([-0.5, 0.5]))
+    yr = X[:, 0] * 2 + X[:, 1]
+    for make, kw in ((tree.boosting, dict(trees=15)), (tree.forest, dict(trees=15)), (tree.single, {})):
+        m = make(Data(X, y3), "classification", **kw)
+        p = m.predict(X)
+        assert p.shape == (400, 3) and torch.allclose(p.sum(1), torch.ones(400), atol=1e-5)
+        assert (m.classify(X) == y3).float().mean() > 0.95 and int(m.importance().argmax()) == 0
+        assert torch.allclose(tree.Ensemble.from_json(m.to_json()).predict(X), p)
+        r = make(Data(X, yr), "regression", **kw)
+        assert r.predict(X).shape == (400,) and float(((r.predict(X) - yr) ** 2).mean()) < 0.5
+    two = tree.boosting(Data(X, (X[:, 1] > 0).long()), "classification", trees=10, max_depth=3)
+    assert two.predict(X).shape == (400, 2)
+    assert torch.allclose(torch.softmax(two.module()(T.tensor(X[:5])).data(), 1), two.predict(X[:5]), atol=1e-6)
+    with pytest.raises(ValueError):
+        tree.boosting(Data(X, yr), "classification")
