@@ -3,7 +3,11 @@ MNIST MLP, MNIST CNN, ResNet-18 at 224 x 224, a deep tabular MLP; one step = for
 backward, AdamW update) through this package's public API, next to the same step in plain PyTorch
 on the same box.
 
-    python -m mimir_b200.utils.bench_cpu [--only mlp,cnn,deep,resnet18] [--steps 10] [--threads 0]
+    python -m mimir_b200.utils.bench_cpu [--only mlp,cnn,deep,resnet18,gcn] [--steps 10] [--threads 0]
+
+``gcn`` is a two-layer graph convolution over a random graph of 100,000 nodes and 1,000,000 edges (64 -> 64 -> 8
+features): this package's ``nn.GCNConv`` (segment kernel over sorted entries) against the same layer written
+on ``torch.sparse`` CSR products, the faster of PyTorch's two ways to aggregate neighbours.
 
 One JSON line per model: best and median milliseconds of both arms (synthetic inputs, random-init
 weights of the same shapes).
@@ -80,6 +84,41 @@ MODELS = {
 }
 
 
+def _gcn_case(steps, warmup):
+    g = torch.Generator().manual_seed(0)
+    n, e, f, hidden, classes = 100_000, 1_000_000, 64, 64, 8
+    src, dst = torch.randint(0, n, (e,), generator=g), torch.randint(0, n, (e,), generator=g)
+    x, y = torch.randn(n, f, generator=g), torch.randint(0, classes, (n,), generator=g)
+    nn.manual_seed(0)
+    graph = nn.Graph(n, src, dst)
+    l1, l2 = nn.GCNConv(f, hidden), nn.GCNConv(hidden, classes)
+    opt = optim.AdamW(l1.parameters() + l2.parameters(), lr=1e-3, weight_decay=0.01)
+    xt, yt = T.from_torch(x), T.from_torch(y)
+
+    def ours_step():
+        L.cross_entropy(l2.convolve(graph, T.relu(l1.convolve(graph, xt))), yt).backward()
+        opt.step()
+        opt.zero_grad()
+    ob, om = _time(ours_step, steps, warmup)
+    # the same layer on torch.sparse: self loops (existing ones dropped), D^-1/2 A D^-1/2 as one CSR matrix
+    keep = src != dst
+    loop = torch.arange(n)
+    s2, d2 = torch.cat([src[keep], loop]), torch.cat([dst[keep], loop])
+    dinv = torch.bincount(d2, minlength=n).float().clamp_min(1).rsqrt()
+    adj = torch.sparse_coo_tensor(torch.stack([d2, s2]), dinv[d2] * dinv[s2], (n, n)).coalesce().to_sparse_csr()
+    torch.manual_seed(0)
+    w1, w2 = torch.nn.Linear(f, hidden), torch.nn.Linear(hidden, classes)
+    topt = torch.optim.AdamW(list(w1.parameters()) + list(w2.parameters()), lr=1e-3, weight_decay=0.01)
+
+    def torch_step():
+        topt.zero_grad(set_to_none=True)
+        h = torch.relu(adj @ (x @ w1.weight.t()) + w1.bias)
+        torch.nn.functional.cross_entropy(adj @ (h @ w2.weight.t()) + w2.bias, y).backward()
+        topt.step()
+    tb, tm = _time(torch_step, steps, warmup)
+    return n, ob, om, tb, tm
+
+
 def _time(step, steps, warmup):
     times = []
     for i in range(warmup + steps):
@@ -101,6 +140,12 @@ def main(argv=None) -> int:
         torch.set_num_threads(a.threads)
     T.set_default_device(T.CPU())
     for name in a.only.split(","):
+        if name == "gcn":
+            n, ob, om, tb, tm = _gcn_case(max(3, a.steps // 2), a.warmup)
+            print(json.dumps({"metric": "cpu_train_step_ms", "model": "gcn", "batch": n, "ours_best_ms": round(ob, 2),
+                              "ours_median_ms": round(om, 2), "pytorch_best_ms": round(tb, 2), "pytorch_median_ms": round(tm, 2),
+                              "ours_over_pytorch": round(om / tm, 3), "threads": torch.get_num_threads(), "data": "synthetic"}), flush=True)
+            continue
         m = MODELS[name]
         g = torch.Generator().manual_seed(0)
         x = torch.randn(*m["shape"], generator=g)
