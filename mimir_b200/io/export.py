@@ -141,6 +141,10 @@ class _Exporter:
             x = self.get(a[0])
             approx = k.get("approximate", a[1] if len(a) > 1 else "tanh")
             return b.call1("gelu_tanh.v1" if approx == "tanh" else "gelu_erf.v1", [x], dt(), dims(x))
+        if name in ("abs_", "abs"):
+            x = self.get(a[0])
+            neg = b.op("neg", [x], [(x.dtype, dims(x))])[0]
+            return b.op("max", [x, neg], [(x.dtype, dims(x))])[0]
         if name == "leaky_relu":
             x = self.get(a[0])
             slope = k.get("slope", a[1] if len(a) > 1 else 0.01)
@@ -179,6 +183,19 @@ class _Exporter:
                 y = self._cast(y, x.dtype)
             r = b.op("cmplt" if name == "less" else "cmpeq", [x, y], [("i32", dims(x, y))])[0]
             return r
+        if name in ("logical_and", "logical_or"):
+            # truth values are the i32 0 / 1 that comparisons give; any other operand is first compared with zero
+            def truth(v):
+                t = self.get(v)
+                if t.dtype == "i32":
+                    return t
+                isz = b.op("cmpeq", [t, b.const(0, t.dtype, [])], [("i32", dims(t))])[0]
+                self.sizes[isz.index] = self.sizes[t.index]
+                r = b.op("cmpeq", [isz, b.const(0, "i32", [])], [("i32", dims(t))])[0]
+                self.sizes[r.index] = self.sizes[t.index]
+                return r
+            x, y = truth(a[0]), truth(a[1])
+            return b.op("and" if name == "logical_and" else "or", [x, y], [("i32", dims(x, y))])[0]
         if name == "logical_not":
             x = self.get(a[0])
             return b.op("cmpeq", [x, b.const(0, x.dtype, [])], [("i32", dims(x))])[0]
@@ -316,7 +333,8 @@ class _Exporter:
             axis = int(k.get("dim", a[2] if len(a) > 2 else -1))
             d = x.dims[:]
             d[axis % len(d)] = kk
-            return b.call("top_k.v1", [x], [(x.dtype, d), ("i64", d)], k=kk, axis=axis)
+            largest = bool(k.get("largest", a[3] if len(a) > 3 else True))
+            return b.call("top_k.v1", [x], [(x.dtype, d), ("i64", d)], k=kk, axis=axis, largest=largest)
         if name in ("zeros", "ones", "full"):
             value = 0 if name == "zeros" else 1 if name == "ones" else k.get("value", a[1] if len(a) > 1 else 0)
             return b.const(value, dt(), list(out.shape))
@@ -328,11 +346,25 @@ class _Exporter:
         return r
 
     def _reshape_dims(self, x, out):
-        """Carries a leading symbolic axis through a reshape that keeps that axis' size."""
+        """Carries symbolic axes through a reshape that keeps them whole: an axis of the operand whose traced
+        size reappears at the same offset (the product of the sizes before it) in the result stays symbolic
+        there, wherever it lands (``[batch, F] -> [1, batch, F]`` as well as ``[batch, a, b] -> [batch, a * b]``)."""
         d = list(out.shape)
-        sx = self.sizes.get(x.index, ())
-        if x.dims and d and isinstance(x.dims[0], G.Sym) and sx and sx[0] == d[0]:
-            d[0] = x.dims[0]
+        sx = tuple(self.sizes.get(x.index, ()))
+        if len(sx) != len(x.dims):
+            return d
+        before = 1
+        for i, dim in enumerate(x.dims):
+            if isinstance(dim, G.Sym):
+                acc = 1
+                for j, size in enumerate(d):
+                    if acc == before and size == sx[i] and not isinstance(d[j], G.Sym):
+                        d[j] = dim
+                        break
+                    acc *= size if isinstance(size, int) else 1
+                    if acc > before:
+                        break
+            before *= sx[i]
         return d
 
     def _getitem(self, x, idx, out):

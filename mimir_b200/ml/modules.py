@@ -165,7 +165,8 @@ class NeighborsModule(_Tables):
             w = T.where(T.less(any_exact * 0.0, any_exact), exact, T.recip(T.maximum(near, 1e-12)))
         else:
             w = near * 0.0 + 1.0
-        ans = T.reshape(T.gather_rows(self.answers.value(), T.reshape(idx, (-1,))), (idx.shape[0], k, -1))
+        width = self.answers.value().shape[1]
+        ans = T.reshape(T.gather_rows(self.answers.value(), idx), (-1, k, width))
         votes = T.sum_(ans * T.unsqueeze(w, -1), 1) / T.sum_(w, 1, keepdim=True)
         return _log_probs(votes) if self.classes else votes
 
@@ -302,16 +303,30 @@ class TreeModule(_Tables):
         return mod
 
     def forward(self, x):
-        n, trees = x.shape[0], self.feature.value().shape[0]
-        pos = T.zeros((trees, n), dtype=torch.int64, device=x.device)
-        feat, thr, left, right = (b.value() for b in (self.feature, self.threshold, self.left, self.right))
+        """Only operations of the exported graph vocabulary are used (a table lookup is a row gather of the
+        flattened table at ``tree * nodes + node``; a row's value of a node's feature is picked by comparing the
+        feature number with 0..F-1), so the module exports like a network."""
+        feat, thr, left, right, value = (b.value() for b in (self.feature, self.threshold, self.left, self.right, self.value))
+        trees, nodes = feat.shape
+        features = x.shape[1]
+        dev = x.device
+        flat = lambda t: T.reshape(t, (trees * nodes,))  # noqa: E731
+        base = T.tensor(torch.arange(trees, dtype=torch.int64)[:, None] * nodes, device=dev)          # [trees, 1]
+        which = T.tensor(torch.arange(features, dtype=torch.int64).reshape(1, 1, features), device=dev)
+        xb = T.unsqueeze(x, 0)                                                                        # [1, n, F]
+        # every row starts at the root of every tree: node 0
+        zero_col = T.cast(T.unsqueeze(T.sum_(T.where(T.equal(x, x), x, 0.0), 1), 0) * 0.0, torch.int64)  # [1, n] zeros, batch-sized
+        pos = base * 0 + zero_col                                                                     # [trees, n]
         for _ in range(self.depth):
-            f = T.gather(feat, 1, pos)                                          # [trees, n]
-            xv = T.transpose(T.gather(x, 1, T.transpose(f, 0, 1)), 0, 1)        # the row's value of the node's feature
-            go_left = T.logical_not(T.less(T.gather(thr, 1, pos), xv))          # x <= threshold; a missing value goes right
-            pos = T.where(go_left, T.gather(left, 1, pos), T.gather(right, 1, pos))
-        leaf = T.gather(self.value.value(), 1, pos)                             # [trees, n]
-        per_out = T.sum_(T.reshape(leaf, (trees // self.outputs, self.outputs, n)), 0)       # rounds add up per output
+            at = pos + base
+            f = T.gather_rows(flat(feat), at)                                                         # [trees, n]
+            picked = T.where(T.equal(T.unsqueeze(f, -1), which), xb, 0.0)                             # [trees, n, F]
+            xv = T.sum_(picked, -1)
+            missing = T.logical_not(T.equal(xv, xv))
+            go_left = T.logical_and(T.logical_not(T.less(T.gather_rows(flat(thr), at), xv)), T.logical_not(missing))
+            pos = T.where(go_left, T.gather_rows(flat(left), at), T.gather_rows(flat(right), at))
+        leaf = T.gather_rows(flat(value), pos + base)                                                 # [trees, n]
+        per_out = T.sum_(T.reshape(leaf, (trees // self.outputs, self.outputs, -1)), 0)               # rounds add up per output
         out = T.transpose(per_out, 0, 1) * self.scale + self.base.value()
         if self.classes == 2 and self.outputs == 1 and not getattr(self, "_nn_skip_forest", False):
             return T.cat([out * 0.0, out], 1)

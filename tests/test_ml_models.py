@@ -337,3 +337,38 @@ def test_table_level_trees_answer_with_probabilities_and_round_trip():
     assert torch.allclose(torch.softmax(two.module()(T.tensor(X[:5])).data(), 1), two.predict(X[:5]), atol=1e-6)
     with pytest.raises(ValueError):
         tree.boosting(Data(X, yr), "classification")
+
+
+def test_modules_save_load_and_export_like_networks(tmp_path):
+    """A fitted model's module keeps its tables in a .mim file, loads into an empty module of the same shape,
+    and exports as a graph that the interpreter runs on another batch size (missing values included)."""
+    import os
+    from mimir_b200.io import export, mim
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(300, 5, generator=g)
+    y, y3 = (X[:, 0] > 0).long(), torch.bucketize(X[:, 1].contiguous(), torch.tensor([-0.5, 0.5]))
+    d = Data(X, y)
+    Q = torch.randn(7, 5, generator=g)
+    Q[0, 0] = math.nan
+    models = {
+        "logistic": linear.logistic_fit(d), "svm": svm.fit(d, "classification"), "bayes": bayes.gaussian(d),
+        "knn": neighbors.fit(d, "classification", by_distance=True), "knn_manhattan": neighbors.fit(Data(X, X[:, 0]), "regression", metric="manhattan"),
+        "kmeans": cluster.kmeans_fit(X, 3), "mixture": cluster.gaussian_mixture(X, 2),
+        "boost2": tree.gradient_boosting(X, y, trees=5, max_depth=3, classes=2), "boost3": tree.gradient_boosting(X, y3, trees=4, max_depth=3, classes=3),
+        "forest": tree.random_forest(X, X[:, 0] * 2, trees=5, max_depth=4),
+    }
+    for name, model in models.items():
+        mod = model.module()
+        want = mod(T.tensor(Q)).data()
+        assert torch.isfinite(want).all(), name
+        path = os.path.join(tmp_path, name + ".mim")
+        mim.save(path, mod)
+        fresh = type(mod).empty(mod.shape)
+        with mim.open(path) as f:
+            fresh.load_state_dict(f.load())
+        assert torch.equal(fresh(T.tensor(Q)).data(), want), name
+        graph = os.path.join(tmp_path, name + "-graph.mim")
+        export.export(graph, mod, X[:4], input_name="x", output_name="y", dynamic={"x": {0: ("batch", 64)}})
+        with mim.open(graph) as f:
+            got = f.run({"x": Q})["y"].data()
+        assert torch.allclose(got, want, rtol=1e-4, atol=1e-4), (name, float((got - want).abs().max()))
