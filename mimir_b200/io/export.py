@@ -338,6 +338,14 @@ class _Exporter:
         if name in ("zeros", "ones", "full"):
             value = 0 if name == "zeros" else 1 if name == "ones" else k.get("value", a[1] if len(a) > 1 else 0)
             return b.const(value, dt(), list(out.shape))
+        from .export_decompose import REWRITES
+        rewrite = REWRITES.get(name)
+        if rewrite is not None:
+            # rebuilt from ops that have translations; the trace is live, so the rebuild is recorded as it runs
+            res = rewrite(*a, **k)
+            if isinstance(res, (tuple, list)):
+                return [self.get(r) for r in res]
+            return self.get(res)
         raise E.ErrUnsupported(f"export: op {name!r} has no translation into the graph vocabulary")
 
     def _cast(self, x, dtype):

@@ -246,8 +246,20 @@ class GroupNorm(Module):
         self.groups, self.eps = groups, eps
 
     def forward(self, x):
-        return T.core._node(lambda v, w, b: torch.nn.functional.group_norm(v, self.groups, w, b, self.eps),
-                            (x, self.weight.value(), self.bias.value()), {}, "group_norm")
+        """Mean and variance over each group of channels (and all positions) of each example, in tensor ops:
+        ``[N, C, ...] -> [N, groups, -1]``, normalised over the last axis, back, then scaled per channel."""
+        shape = tuple(x.shape)
+        n, c = shape[0], shape[1]
+        if c % self.groups:
+            return T.core._error_tensor(T.ErrShape(f"group norm of {c} channels in {self.groups} groups"))
+        g = T.reshape(x, (n, self.groups, -1))
+        g = T.cast(g, torch.float32) if g.dtype != torch.float32 else g
+        mean = T.mean(g, dim=2, keepdim=True)
+        d = g - mean
+        y = d / T.sqrt(T.mean(d * d, dim=2, keepdim=True) + self.eps)
+        per = (1, c) + (1,) * (len(shape) - 2)
+        y = T.reshape(y, shape) * T.reshape(self.weight.value(), per) + T.reshape(self.bias.value(), per)
+        return T.cast(y, x.dtype) if y.dtype != x.dtype else y
 
 
 class _BatchNorm(Module):

@@ -20,7 +20,9 @@ _node = C._node
 # ------------------------------------------------------------------ elementwise
 exp2 = C._unary("exp2", torch.exp2)
 log2 = C._unary("log2", torch.log2)
-greater = C._binary("greater", torch.gt)
+def greater(a, b):
+    """``a > b`` elementwise (tensor.Greater): ``less`` with the operands swapped, so it traces and exports as one."""
+    return C.less(b, a)
 fmod = C._binary("fmod", torch.fmod)
 
 
