@@ -252,6 +252,11 @@ def windows(x, axis, size, step=1):
     return T.permute(g, order)
 
 
+def arange(n, dtype=torch.int32, device=None):
+    """A range of a fixed length is a constant of the graph."""
+    return C.tensor(torch.arange(n, dtype=dtype), device=device)
+
+
 def with_effects(x, *effects):
     return x
 
@@ -262,4 +267,4 @@ def greater(a, b):
 
 REWRITES = {f.__name__: f for f in (clamp, softplus, log1p, expm1, sign, floor, ceil, var, logsumexp, flip, stack, split, one_hot,
                                     argmax, gather, max_pool2d, avg_pool2d, upsample_nearest, conv1d, conv_transpose2d,
-                                    conv_transpose1d, with_effects, greater, windows)}
+                                    conv_transpose1d, with_effects, greater, windows, arange)}

@@ -56,6 +56,8 @@ class _Recurrent(Module):
             ws += [self.w_ih[k].value(), self.w_hh[k].value()]
             if self.bias:
                 ws += [self.b_ih[k].value(), self.b_hh[k].value()]
+        if T.core._TRACE is not None:
+            return self._run_in_ops(x, init)          # an exporter is listening: the recurrence as separate ops
         cell, batch_first, n_init = self.cell, self.batch_first, len(init)
 
         def fn(v, *rest):
@@ -105,6 +107,48 @@ class _Recurrent(Module):
             return (out,) + finals
         return T.core._node(fn, (x, *init, *ws), {}, type(self).__name__.lower())
 
+    def _run_in_ops(self, x, init):
+        """The same recurrence unrolled in public tensor ops (one product, one cell per step), which is what a
+        graph exporter can translate.  Batched input only."""
+        ns, dirs, nl, hid = self.states, 2 if self.bidirectional else 1, self.layers, self.hidden
+        if len(x.shape) != 3:
+            return tuple(T.core._error_tensor(T.ErrShape("recurrent layer: export needs batched input [T, B, C] or [B, T, C]"))
+                         for _ in range(1 + ns))
+        seq = T.transpose(x, 0, 1) if self.batch_first else x
+        steps, batch = seq.shape[0], seq.shape[1]
+        hs, cs = [], []
+        for l in range(nl):
+            outs = []
+            for d in range(dirs):
+                k = l * dirs + d
+                wi, wh = self.w_ih[k].value(), self.w_hh[k].value()
+                bi, bh = (self.b_ih[k].value(), self.b_hh[k].value()) if self.bias else (None, None)
+                if init:
+                    h = T.reshape(T.shrink(init[0], ((k, k + 1), (0, batch), (0, hid))), (batch, hid))
+                    c = T.reshape(T.shrink(init[1], ((k, k + 1), (0, batch), (0, hid))), (batch, hid)) if ns == 2 else None
+                else:
+                    # zeros shaped by the batch of the input, so a dynamic batch stays dynamic
+                    first = T.reshape(T.shrink(seq, ((0, 1), (0, batch), (0, 1))), (batch, 1))
+                    zero = T.expand(first * 0.0, (batch, hid))
+                    h, c = zero, (zero if ns == 2 else None)
+                gi_all = T.matmul_t(seq, wi, bi)                                  # the input products of every step at once
+                ys = [None] * steps
+                for t in (range(steps - 1, -1, -1) if d else range(steps)):
+                    gi = T.reshape(T.shrink(gi_all, ((t, t + 1), (0, batch), (0, gi_all.shape[2]))), (batch, gi_all.shape[2]))
+                    h, c = self.cell_ops(gi, T.matmul_t(h, wh, bh), h, c)
+                    ys[t] = h
+                outs.append(T.stack(ys, 0))
+                hs.append(h)
+                cs.append(c)
+            seq = outs[0] if dirs == 1 else T.cat(outs, -1)
+        out = T.transpose(seq, 0, 1) if self.batch_first else seq
+        finals = (T.stack(hs, 0),) if ns == 1 else (T.stack(hs, 0), T.stack(cs, 0))
+        return (out,) + finals
+
+    def cell_ops(self, gi, gh, h, c):
+        """``cell`` in lazy tensor ops."""
+        raise NotImplementedError
+
     def forward(self, x, *init):
         """The outputs and the final hidden state (``run`` also gives an LSTM's final cell state)."""
         res = self.run(x, *init)
@@ -122,6 +166,9 @@ class RNN(_Recurrent):
     def cell(self, gi, gh, h, c):
         return (torch.relu(gi + gh) if self.relu else torch.tanh(gi + gh)), c
 
+    def cell_ops(self, gi, gh, h, c):
+        return (T.relu(gi + gh) if self.relu else T.tanh(gi + gh)), c
+
 
 class LSTM(_Recurrent):
     gates = 4
@@ -131,6 +178,12 @@ class LSTM(_Recurrent):
         i, f, g, o = (gi + gh).chunk(4, -1)
         c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
         return torch.sigmoid(o) * torch.tanh(c), c
+
+    def cell_ops(self, gi, gh, h, c):
+        H = self.hidden
+        i, f, g, o = T.split(gi + gh, [H, H, H, H], -1)
+        c = T.sigmoid(f) * c + T.sigmoid(i) * T.tanh(g)
+        return T.sigmoid(o) * T.tanh(c), c
 
 
 class GRU(_Recurrent):
@@ -142,3 +195,11 @@ class GRU(_Recurrent):
         r, z = torch.sigmoid(ir + hr), torch.sigmoid(iz + hz)
         n = torch.tanh(inn + r * hn)
         return (1 - z) * n + z * h, c
+
+    def cell_ops(self, gi, gh, h, c):
+        H = self.hidden
+        ir, iz, inn = T.split(gi, [H, H, H], -1)
+        hr, hz, hn = T.split(gh, [H, H, H], -1)
+        r, z = T.sigmoid(ir + hr), T.sigmoid(iz + hz)
+        n = T.tanh(inn + r * hn)
+        return (1.0 - z) * n + z * h, c

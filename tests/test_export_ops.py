@@ -84,3 +84,28 @@ def test_whole_models_export_and_agree():
         got = mim.parse(buf.getvalue()).run({"input": x})["output"].data()
         want = net(T.tensor(x)).data()
         assert torch.allclose(got, want, rtol=1e-4, atol=1e-5), (name, float((got - want).abs().max()))
+
+
+def test_recurrent_layers_and_text_classifier_export():
+    from mimir_b200 import text
+    nn.manual_seed(0)
+    g = torch.Generator().manual_seed(0)
+    for name, net, x in (("lstm", nn.LSTM(5, 8, layers=2, batch_first=True), torch.randn(2, 6, 5, generator=g)),
+                         ("gru", nn.GRU(5, 8, bidirectional=True), torch.randn(6, 2, 5, generator=g)),
+                         ("rnn", nn.RNN(5, 8, relu=True, bias=False), torch.randn(6, 2, 5, generator=g))):
+        f = lambda a, net=net: net(a)[0]  # noqa: E731
+        buf = io.BytesIO()
+        X.export_func(buf, f, [T.tensor(x)], input_names=["input"], output_names=["output"], module=net)
+        got = mim.parse(buf.getvalue()).run({"input": x})["output"].data()
+        assert torch.allclose(got, f(T.tensor(x)).data(), atol=1e-5), name
+    ids = torch.randint(1, 50, (2, 12), generator=g)
+    ids[0, 8:] = 0
+    cfg = text.BertConfig(vocab=50, dim=32, layers=1, heads=2, hidden=64, max_positions=16, dropout=0.0)
+    clf = text.TextClassifier(cfg, 3, pad_id=0).eval()
+    buf = io.BytesIO()
+    X.export(buf, clf, ids)
+    other = ids.clone()
+    other[1, 5:] = 0                                                  # the padding mask is computed in the graph, not baked in
+    for batch in (ids, other):
+        got = mim.parse(buf.getvalue()).run({"input": batch})["output"].data()
+        assert torch.allclose(got, clf(T.tensor(batch)).data(), atol=1e-5)
