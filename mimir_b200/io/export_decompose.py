@@ -257,6 +257,11 @@ def arange(n, dtype=torch.int32, device=None):
     return C.tensor(torch.arange(n, dtype=dtype), device=device)
 
 
+def detach(x):
+    """A graph has no gradients to cut."""
+    return x
+
+
 def with_effects(x, *effects):
     return x
 
@@ -267,4 +272,4 @@ def greater(a, b):
 
 REWRITES = {f.__name__: f for f in (clamp, softplus, log1p, expm1, sign, floor, ceil, var, logsumexp, flip, stack, split, one_hot,
                                     argmax, gather, max_pool2d, avg_pool2d, upsample_nearest, conv1d, conv_transpose2d,
-                                    conv_transpose1d, with_effects, greater, windows, arange)}
+                                    conv_transpose1d, with_effects, greater, windows, arange, detach)}

@@ -164,11 +164,36 @@ def _apply(spec: _Spec, x, what: str):
     if not shape or shape[0] != spec.n_in:
         return C._error_tensor(E.ErrShape(f"pattern: {what} wants {spec.n_in} rows, got shape {shape}"))
 
+    if C._TRACE is not None:
+        return _as_dense_product(spec, x)
+
     def run(v):
         if v.device.type == "meta":
             return torch.empty((spec.n_out,) + tuple(v.shape[1:]), dtype=v.dtype, device="meta")
         return _SegmentSum.apply(v, spec)
     return C._node(run, (x,), {}, "segment", known=((spec.n_out,) + shape[1:], x.dtype))
+
+
+DENSE_EXPORT_CELLS = 1 << 24
+
+
+def _as_dense_product(spec: _Spec, x):
+    """While a graph exporter listens, a segment sum is written as the product by its 0 / 1 / count matrix (a
+    constant of the graph), which the graph vocabulary has a word for.  Meant for graphs small enough to hold
+    that matrix: ``DENSE_EXPORT_CELLS`` cells at most."""
+    n_out, n_in = spec.n_out, spec.n_in
+    if n_out * n_in > DENSE_EXPORT_CELLS:
+        return C._error_tensor(E.ErrUnsupported(f"export: a sparse pattern of {n_out} x {n_in} is too large to export as a dense matrix"))
+    offsets, lst, _ = spec.lists(torch.device("cpu"))
+    rows = torch.repeat_interleave(torch.arange(n_out), (offsets[1:] - offsets[:-1]).long())
+    dense = torch.zeros(n_out, n_in)
+    dense.index_put_((rows, lst.long()[:rows.numel()]), torch.ones(rows.numel()), accumulate=True)
+    shape = tuple(x.shape)
+    flat = C.reshape(x, (shape[0], -1)) if len(shape) != 2 else x
+    wide = C.cast(flat, torch.float32) if flat.dtype != torch.float32 else flat
+    y = C.matmul(C.tensor(dense, device=x.device), wide)
+    y = C.cast(y, x.dtype) if y.dtype != x.dtype else y
+    return C.reshape(y, (n_out,) + shape[1:]) if len(shape) != 2 else y
 
 
 class Pattern:
@@ -266,7 +291,17 @@ class Pattern:
                 return torch.empty((spec.n_out,) + tuple(v.shape[1:]), dtype=v.dtype, device="meta")
             offsets, lst, _ = spec.lists(v.device)
             return _segment_raw(v.detach(), offsets, lst, MAX)
-        best = C.detach(C._node(top, (C.detach(x),), {}, "segment_max", known=((self.rows,) + shape[1:], x.dtype)))
+        if C._TRACE is not None:
+            # an exporter listens: the maximum over a row's entries from the dense 0 / 1 matrix (small graphs)
+            if self.rows * self.cols > DENSE_EXPORT_CELLS:
+                return C._error_tensor(E.ErrUnsupported(f"export: a sparse pattern of {self.rows} x {self.cols} is too large to export as a dense matrix"))
+            has = C.tensor((self.dense() > 0).float().reshape((self.rows, self.cols) + (1,) * (len(shape) - 1)), device=x.device)
+            cand = C.where(C.less(0.0, has), C.unsqueeze(x, 0), -float("inf"))
+            top_rows = C.max_(cand, 1)
+            deg = C.tensor(self._by.lists["degrees"].reshape((self.rows,) + (1,) * (len(shape) - 1)), device=x.device)
+            best = C.where(C.less(0.0, deg), top_rows, 0.0)
+        else:
+            best = C.detach(C._node(top, (C.detach(x),), {}, "segment_max", known=((self.rows,) + shape[1:], x.dtype)))
         # the maximum again as a sum over the entries that hold it, divided by their number: the same
         # value, and a linear map of x whose derivatives share a tie evenly
         picked = self.at_cols(x)

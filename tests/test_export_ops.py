@@ -109,3 +109,31 @@ def test_recurrent_layers_and_text_classifier_export():
     for batch in (ids, other):
         got = mim.parse(buf.getvalue()).run({"input": batch})["output"].data()
         assert torch.allclose(got, clf(T.tensor(batch)).data(), atol=1e-5)
+
+
+def test_graph_layers_export_over_a_small_graph():
+    """While an exporter listens, sparse patterns become products by their dense 0 / 1 matrices (constants of
+    the graph), so GCN, GraphSAGE and GAT export with their graph baked in; a graph too large for that is refused."""
+    from mimir_b200.tensor import pattern
+    nn.manual_seed(0)
+    g = torch.Generator().manual_seed(0)
+    n = 30
+    src, dst = torch.randint(0, n, (90,), generator=g), torch.randint(0, n, (90,), generator=g)
+    dst[dst == 7] = 8                                               # node 7 has no incoming edge
+    graph = nn.Graph(n, src, dst)
+    x = torch.randn(n, 6, generator=g)
+    layers = {"gcn": nn.GCNConv(6, 4), "sage": nn.SAGEConv(6, 4), "gat": nn.GATConv(6, 3, heads=2)}
+    fns = {k: (lambda a, l=l: l.convolve(graph, a)) for k, l in layers.items()}
+    fns["max"] = lambda a: graph.max(graph.source(a))
+    for name, f in fns.items():
+        buf = io.BytesIO()
+        X.export_func(buf, f, [T.tensor(x)], input_names=["x"], output_names=["y"], module=layers.get(name))
+        got = mim.parse(buf.getvalue()).run({"x": x})["y"].data()
+        assert torch.allclose(got, f(T.tensor(x)).data(), atol=1e-5), name
+    old = pattern.DENSE_EXPORT_CELLS
+    pattern.DENSE_EXPORT_CELLS = 100
+    try:
+        with pytest.raises(T.ErrUnsupported):
+            X.export_func(io.BytesIO(), fns["gcn"], [T.tensor(x)])
+    finally:
+        pattern.DENSE_EXPORT_CELLS = old
