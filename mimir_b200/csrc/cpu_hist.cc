@@ -58,8 +58,8 @@ namespace {
 
 // One (feature, bin) cell: the sums of gradients and hessians and the count of the rows that fall in it, side
 // by side, so a row's update of a feature touches one cache line instead of three.
-struct Cell {
-  double g, h, c;
+struct alignas(32) Cell {
+  double g, h, c, pad;     // four doubles: one 256-bit load, add and store per update
 };
 
 inline uint64_t mix(uint64_t z) {
@@ -80,6 +80,31 @@ struct Grow {
   std::vector<Cell> hist;          // empty for a node that cannot split (depth limit): its sums are given
   bool counted = false;            // its histogram is counted from its rows (the smaller child); else parent - sibling
 };
+
+// One feature's pass over the rows idx[lo .. hi): the cell of each row's bin takes (gradient, hessian, 1).
+// With AVX2 the three additions are one 256-bit add on the padded cell.
+__attribute__((target("avx2"))) void count_cells_avx2(const uint8_t* col, const int64_t* idx, const float* og, const float* oh,
+                                                       long long lo, long long hi, Cell* c) {
+  for (long long k = lo; k < hi; ++k) {
+    double* cell = reinterpret_cast<double*>(c + col[idx[k]]);
+    const __m256d inc = _mm256_set_pd(0.0, 1.0, static_cast<double>(oh[k]), static_cast<double>(og[k]));
+    _mm256_store_pd(cell, _mm256_add_pd(_mm256_load_pd(cell), inc));
+  }
+}
+
+void count_cells(const uint8_t* col, const int64_t* idx, const float* og, const float* oh, long long lo, long long hi, Cell* c) {
+  static const bool avx2 = __builtin_cpu_supports("avx2");
+  if (avx2) {
+    count_cells_avx2(col, idx, og, oh, lo, hi, c);
+    return;
+  }
+  for (long long k = lo; k < hi; ++k) {
+    Cell& cell = c[col[idx[k]]];
+    cell.g += og[k];
+    cell.h += oh[k];
+    cell.c += 1.0;
+  }
+}
 
 // runs fn(i) for i in [0, count) on the pool, items handed out one by one; serial when there is little to share
 template <class Fn>
@@ -128,21 +153,13 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
       for (long long k = a; k < b; ++k) { og[k] = g[idx[k]]; oh[k] = h[idx[k]]; }
     });
   };
-  auto count_feature = [&](Grow& nd, int f) {
-    const uint8_t* col = bins + static_cast<size_t>(f) * total;
-    Cell* c = nd.hist.data() + static_cast<size_t>(f) * nbins;
-    for (long long k = nd.lo; k < nd.hi; ++k) {
-      Cell& cell = c[col[idx[k]]];
-      cell.g += og[k];
-      cell.h += oh[k];
-      cell.c += 1.0;
-    }
-  };
+  auto count_feature = [&](Grow& nd, int f) { count_cells(bins + static_cast<size_t>(f) * total, idx, og.data(), oh.data(), nd.lo, nd.hi,
+                                                          nd.hist.data() + static_cast<size_t>(f) * nbins); };
 
   all.emplace_back();
   all[0].lo = 0;
   all[0].hi = n;
-  all[0].hist.assign(cells, Cell{0, 0, 0});
+  all[0].hist.assign(cells, Cell{0, 0, 0, 0});
   gather(0, n);
   for_each(pool, F, wide, [&](long long f) { count_feature(all[0], static_cast<int>(f)); });
   {
@@ -290,7 +307,7 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
       if (nd.depth + 1 >= max_depth) { std::vector<Cell>().swap(nd.hist); continue; }     // the children are leaves: sums are given
       Grow &l = all[nd.left], &r = all[nd.right];
       Grow& small = (l.hi - l.lo) <= (r.hi - r.lo) ? l : r;
-      small.hist.assign(cells, Cell{0, 0, 0});
+      small.hist.assign(cells, Cell{0, 0, 0, 0});
       small.counted = true;
       counted.push_back(&small == &l ? nd.left : nd.right);
       parents_of.push_back(id);
