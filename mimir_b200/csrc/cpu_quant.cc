@@ -418,3 +418,39 @@ MIMIR_CPU_API int mimir_cpu_qgemv(int code, const void* w, int N, int K, const f
   });
   return 0;
 }
+
+// out [N][K] (bfloat16, round to nearest even) = the values of W, N rows of K values in ggml blocks of `code`.
+// For prompts: many activation rows amortise one expansion of the matrix, and the product then runs as a
+// bfloat16 matrix product (on the matrix units where the CPU has them).  Returns 0, or -1 for a bad argument.
+MIMIR_CPU_API int mimir_cpu_dequant_bf16(int code, const void* w, int N, int K, uint16_t* out) {
+  if (code < Q8_0 || code > Q6_K || N < 0) return -1;
+  const int vals = (code == Q8_0 || code == Q4_0) ? 32 : 256;
+  if (K <= 0 || K % vals) return -1;
+  const size_t bb = code == Q8_0 ? 34 : code == Q4_0 ? 18 : code == Q4_K ? 144 : 210;
+  const size_t rb = row_bytes(code, K);
+  const uint8_t* wb = static_cast<const uint8_t*>(w);
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& p = pool();
+  const int chunk = 16;
+  std::atomic<int> next{0};
+  p.run([&](int, int) {
+    float tmp[256];
+    for (int n0 = next.fetch_add(chunk); n0 < N; n0 = next.fetch_add(chunk)) {
+      const int n1 = n0 + chunk < N ? n0 + chunk : N;
+      for (int n = n0; n < n1; ++n) {
+        const uint8_t* row = wb + static_cast<size_t>(n) * rb;
+        uint16_t* o = out + static_cast<size_t>(n) * K;
+        for (int k0 = 0; k0 < K; k0 += vals) {
+          decode_block(code, row + static_cast<size_t>(k0 / vals) * bb, tmp);
+          for (int i = 0; i < vals; ++i) {
+            uint32_t u;
+            memcpy(&u, &tmp[i], 4);
+            u += 0x7FFFu + ((u >> 16) & 1u);          // round to nearest, ties to even (the values are finite)
+            o[k0 + i] = static_cast<uint16_t>(u >> 16);
+          }
+        }
+      }
+    }
+  });
+  return 0;
+}

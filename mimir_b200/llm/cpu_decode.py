@@ -17,12 +17,26 @@ from __future__ import annotations
 
 import math
 
+import threading
+
 import torch
 
 from ..io import mim
 from ..ops import quant as Q
 from ..ops import quant_cpu
 from .model import Config
+
+
+WIDE_ROWS = 32            # activation rows from which a product expands the weight and runs in bfloat16
+_LOCAL = threading.local()
+
+
+def _scratch(values: int) -> torch.Tensor:
+    """This thread's bfloat16 buffer of at least ``values`` elements (it only grows)."""
+    buf = getattr(_LOCAL, "buf", None)
+    if buf is None or buf.numel() < values:
+        buf = _LOCAL.buf = torch.empty(values, dtype=torch.bfloat16)
+    return buf
 
 
 class _Mat:
@@ -55,9 +69,15 @@ class _Mat:
         return Q.dequantize_raw(self.code, raw, idx.numel() * self.k).view(idx.numel(), self.k)
 
     def mul(self, x: torch.Tensor, mode: str) -> torch.Tensor:
-        """``x [B, K] -> [B, N]``."""
+        """``x [B, K] -> [B, N]``.  A few rows (decoding) multiply the blocks as they are; a prompt's many rows
+        (``WIDE_ROWS`` or more, unless ``mode`` is "exact") expand the matrix to bfloat16 once into a scratch
+        buffer and run one bfloat16 matrix product, which the CPU's matrix units serve: the expansion is paid
+        once per chunk of the prompt instead of the blocks being unpacked again for every eight rows."""
         if self.code == 0:
             return x @ self.data.t()
+        if x.shape[0] >= WIDE_ROWS and mode != "exact":
+            w = quant_cpu.dequant_bf16(self.code, self.data, self.n, self.k, _scratch(self.n * self.k))
+            return (x.to(torch.bfloat16) @ w.t()).float()
         return quant_cpu.qgemv(self.code, self.data, self.n, self.k, x, mode)
 
     @staticmethod
@@ -225,12 +245,17 @@ class CPUDecoder:
         return self.head.mul(self._norm(last, self.out_norm), self.mode)
 
     @torch.no_grad()
-    def prefill(self, prompt: torch.Tensor, chunk: int = 32) -> torch.Tensor:
-        """Feeds ``prompt [B, T]`` in chunks of ``chunk`` positions (each weight matrix is read once per
-        eight activation rows, not once per token); returns the logits after the last token."""
+    def prefill(self, prompt: torch.Tensor, chunk: int = 256) -> torch.Tensor:
+        """Feeds ``prompt [B, T]`` in chunks of ``chunk`` positions (a chunk of 32 rows or more expands each
+        weight matrix once and multiplies in bfloat16; smaller ones read the blocks once per eight rows);
+        returns the logits after the last token."""
         logits = None
         for t0 in range(0, prompt.shape[1], chunk):
-            logits = self._own_thread(self._forward, prompt[:, t0: t0 + chunk])
+            part = prompt[:, t0: t0 + chunk]
+            if part.shape[0] * part.shape[1] >= WIDE_ROWS and self.mode != "exact":
+                logits = self._forward(part)          # wide products are PyTorch's: they need its threads
+            else:
+                logits = self._own_thread(self._forward, part)
         return logits
 
     @torch.no_grad()

@@ -53,3 +53,24 @@ def qgemv(code: int, raw: torch.Tensor, n: int, k: int, x: torch.Tensor, mode: s
         if rc:
             raise ValueError(f"qgemv: unsupported arguments (code {code}, N {n}, K {k}, mode {mode})")
     return out
+
+
+def dequant_bf16(code: int, raw: torch.Tensor, n: int, k: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The weight's values as a bfloat16 ``[n, k]`` tensor (written into ``out`` when given: one scratch
+    buffer serves every matrix of a model), expanded by the worker pool."""
+    if raw.device.type != "cpu" or raw.dtype != torch.uint8 or not raw.is_contiguous():
+        raise ValueError("dequant_bf16: the weight must be a contiguous uint8 CPU tensor")
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.bfloat16)
+    elif out.dtype != torch.bfloat16 or out.numel() < n * k or not out.is_contiguous():
+        raise ValueError("dequant_bf16: the scratch buffer must be contiguous bfloat16 of at least n * k values")
+    lib = _lib()
+    if not getattr(lib, "_dequant_bound", False):
+        import ctypes
+        lib.mimir_cpu_dequant_bf16.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        lib.mimir_cpu_dequant_bf16.restype = ctypes.c_int
+        lib._dequant_bound = True
+    view = out.reshape(-1)[: n * k].view(n, k)
+    if lib.mimir_cpu_dequant_bf16(int(code), raw.data_ptr(), n, k, view.data_ptr()) != 0:
+        raise ValueError(f"dequant_bf16: bad arguments (code {code}, {n} x {k})")
+    return view

@@ -129,3 +129,24 @@ def test_reference_q4_k_m_sample_prompt_logits_and_greedy_steps(mode, tol):
         if tol is not None:
             assert int(logits.argmax()) == want, i
         logits = dec.step(torch.tensor([want]))[0]
+
+
+def test_a_long_prompt_runs_on_expanded_weights_and_agrees_with_the_exact_products(tmp_path):
+    """Chunks of 32 activation rows or more expand each quantized matrix to bfloat16 once and multiply there;
+    the logits stay within bfloat16's precision of the exact products, and shorter chunks are untouched."""
+    m = _model()
+    path = _quantized_file(tmp_path, m)
+    exact = llm.CPUDecoder.load(path, cap=48, mode="exact", float_as="f32")
+    fast = llm.CPUDecoder.load(path, cap=48, mode="auto", float_as="f32")
+    toks = torch.randint(0, 96, (1, 40), generator=torch.Generator().manual_seed(0))
+    want = exact.prefill(toks)
+    got = fast.prefill(toks)                                     # one chunk of 40 rows: the expanded path
+    assert fast.len == 40 and float((got - want).abs().max()) < 3e-2 * float(want.abs().max())
+    assert got.argmax(-1).equal(want.argmax(-1))
+    nxt = want.argmax(-1)
+    assert float((fast.step(nxt) - exact.step(nxt)).abs().max()) < 3e-2 * float(want.abs().max())     # the cache it filled decodes on
+    w = quant_cpu.dequant_bf16(Q.Q8_0, fast.layers[0]["o"].data, fast.layers[0]["o"].n, fast.layers[0]["o"].k)
+    full = Q.dequantize_raw(Q.Q8_0, fast.layers[0]["o"].data, w.numel()).view(w.shape)
+    assert torch.equal(w, full.bfloat16())                       # round to nearest even, bit for bit
+    with pytest.raises(ValueError):
+        quant_cpu.dequant_bf16(Q.Q8_0, fast.layers[0]["o"].data, 4, 4, torch.empty(3, dtype=torch.bfloat16))
