@@ -95,9 +95,10 @@ class _Mat:
 
 class CPUDecoder:
     def __init__(self, cfg: Config, tensors: dict, batch: int = 1, cap: int | None = None, mode: str = "auto",
-                 float_as: str = "q8_0", rope_freqs: torch.Tensor | None = None):
+                 float_as: str = "q8_0", rope_freqs: torch.Tensor | None = None, fused_layers: bool = True):
         """``tensors``: file names (``token_embd.weight``, ``blk.N.attn_q.weight`` ...) -> float tensors
-        or ``QuantizedTensor``s."""
+        or ``QuantizedTensor``s.  ``fused_layers=False`` keeps single-token steps on the tensor-op path that
+        prompts use (the native layer routine is checked against it)."""
         if mode not in ("auto", "int8", "exact"):
             raise ValueError("mode is 'auto', 'int8' or 'exact'")
         self.cfg, self.batch, self.cap = cfg, batch, cap or cfg.context
@@ -133,6 +134,10 @@ class CPUDecoder:
         self.kc = torch.zeros(c.layers, batch, c.kv_heads, self.cap, c.head_dim)
         self.vc = torch.zeros_like(self.kc)
         self.len = 0
+        # one native call per layer when every product reads blocks and the q / k / v and gate / up rows are fused
+        self.fused_layers = fused_layers and self.own_threads and batch <= quant_cpu.MAX_ROWS and all(
+            l["qkv"] is not None and l["gate_up"] is not None for l in self.layers)
+        self._args = None
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -197,7 +202,42 @@ class CPUDecoder:
     @torch.no_grad()
     def step(self, tokens: torch.Tensor) -> torch.Tensor:
         """One token per sequence: ``tokens [B]`` -> logits ``[B, vocab]``; the cache grows by one."""
+        if self.fused_layers:
+            return self._step_native(tokens.reshape(self.batch))
         return self._own_thread(self._forward, tokens.reshape(self.batch, 1))
+
+    def _layer_args(self):
+        """The argument block of each layer (addresses of weights and caches do not change between steps)."""
+        if self._args is None:
+            c, B = self.cfg, self.batch
+            self._x = torch.empty(B, c.embed)
+            self._work = torch.empty(quant_cpu.decode_scratch(B, c.embed, c.heads, c.kv_heads, c.head_dim, c.hidden, self.cap))
+            self._args = []
+            for li, l in enumerate(self.layers):
+                a = quant_cpu.DecodeLayer(
+                    B=B, E=c.embed, H=c.heads, Hk=c.kv_heads, D=c.head_dim, hidden=c.hidden, rope_dim=c.rope_dim,
+                    interleaved=int(self.interleaved), pos=0, cap=self.cap, mode=quant_cpu._MODES[self.mode],
+                    qkv_code=l["qkv"].code, o_code=l["o"].code, gate_up_code=l["gate_up"].code, down_code=l["down"].code,
+                    eps=float(c.eps), attn_norm=l["attn_norm"].data_ptr(), ffn_norm=l["ffn_norm"].data_ptr(),
+                    qkv_bias=l["qkv_bias"].data_ptr() if l["qkv_bias"] is not None else None,
+                    inv_freq=self.inv_freq.data_ptr(), qkv=l["qkv"].data.data_ptr(), o=l["o"].data.data_ptr(),
+                    gate_up=l["gate_up"].data.data_ptr(), down=l["down"].data.data_ptr(),
+                    k_cache=self.kc[li].data_ptr(), v_cache=self.vc[li].data_ptr(), x=self._x.data_ptr(),
+                    scratch=self._work.data_ptr())
+                self._args.append(a)
+        return self._args
+
+    def _step_native(self, tokens: torch.Tensor) -> torch.Tensor:
+        pos = self.len
+        if pos + 1 > self.cap:
+            raise IndexError(f"KV cache overflow: {pos} + 1 > {self.cap}")
+        args = self._layer_args()
+        self._x.copy_(self.embed.rows(tokens.long()))
+        for a in args:
+            a.pos = pos
+            quant_cpu.decode_layer(a)
+        self.len = pos + 1
+        return self.head.mul(self._own_thread(self._norm, self._x, self.out_norm), self.mode)
 
     def _forward(self, tokens: torch.Tensor) -> torch.Tensor:
         """``tokens [B, T]`` at positions ``len .. len + T - 1`` -> logits of the last one ``[B, vocab]``.

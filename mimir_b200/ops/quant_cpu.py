@@ -74,3 +74,33 @@ def dequant_bf16(code: int, raw: torch.Tensor, n: int, k: int, out: torch.Tensor
     if lib.mimir_cpu_dequant_bf16(int(code), raw.data_ptr(), n, k, view.data_ptr()) != 0:
         raise ValueError(f"dequant_bf16: bad arguments (code {code}, {n} x {k})")
     return view
+
+
+class DecodeLayer(ctypes.Structure):
+    """The argument block of ``mimir_cpu_decode_layer`` (``csrc/cpu_decode.cc``): one decoder layer for one
+    new token per sequence.  The caller keeps every tensor whose address it holds alive."""
+
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "B", "E", "H", "Hk", "D", "hidden", "rope_dim", "interleaved", "pos", "cap", "mode", "qkv_code", "o_code",
+        "gate_up_code", "down_code", "pad_")] + [("eps", ctypes.c_float), ("pad2_", ctypes.c_float)] + [
+        (n, ctypes.c_void_p) for n in ("attn_norm", "ffn_norm", "qkv_bias", "inv_freq", "qkv", "o", "gate_up", "down",
+                                       "k_cache", "v_cache", "x", "scratch")]
+
+
+def decode_scratch(B: int, E: int, H: int, Hk: int, D: int, hidden: int, cap: int) -> int:
+    """Floats of scratch one ``decode_layer`` call needs."""
+    lib = _lib()
+    lib.mimir_cpu_decode_scratch.restype = ctypes.c_longlong
+    lib.mimir_cpu_decode_scratch.argtypes = [ctypes.c_int] * 7
+    return int(lib.mimir_cpu_decode_scratch(B, E, H, Hk, D, hidden, cap))
+
+
+def decode_layer(args: DecodeLayer) -> None:
+    """Runs one layer in place on ``args.x`` and appends the new key and value rows at ``args.pos``."""
+    lib = _lib()
+    if not getattr(lib, "_decode_bound", False):
+        lib.mimir_cpu_decode_layer.argtypes = [ctypes.POINTER(DecodeLayer)]
+        lib.mimir_cpu_decode_layer.restype = ctypes.c_int
+        lib._decode_bound = True
+    if lib.mimir_cpu_decode_layer(ctypes.byref(args)) != 0:
+        raise ValueError("decode_layer: bad arguments")

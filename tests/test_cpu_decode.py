@@ -150,3 +150,29 @@ def test_a_long_prompt_runs_on_expanded_weights_and_agrees_with_the_exact_produc
     assert torch.equal(w, full.bfloat16())                       # round to nearest even, bit for bit
     with pytest.raises(ValueError):
         quant_cpu.dequant_bf16(Q.Q8_0, fast.layers[0]["o"].data, 4, 4, torch.empty(3, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("arch", ["llama", "qwen2"])
+@pytest.mark.parametrize("mode", ["exact", "int8"])
+def test_the_native_layer_routine_equals_the_tensor_op_path(tmp_path, arch, mode):
+    """Single-token steps over block-encoded weights run one native call per layer (normalisations, rotary
+    positions, cache append, attention, SwiGLU and residuals included); the tensor-op path that prompts use is
+    its oracle, for both rotary orders, with and without projection biases, and after a chunked prompt."""
+    if mode == "int8" and not quant_cpu.has_int8():
+        pytest.skip("no VNNI on this CPU")
+    m = _model(arch)
+    path = _quantized_file(tmp_path, m)
+    fused = llm.CPUDecoder.load(path, batch=2, cap=24, mode=mode, float_as="f32")
+    plain = llm.CPUDecoder.load(path, batch=2, cap=24, mode=mode, float_as="f32", fused_layers=False)
+    assert fused.fused_layers and not plain.fused_layers
+    assert (fused.layers[0]["qkv_bias"] is not None) == (arch == "qwen2")
+    toks = torch.randint(0, 96, (2, 12), generator=torch.Generator().manual_seed(3))
+    fused.prefill(toks[:, :5]), plain.prefill(toks[:, :5])
+    for t in range(5, 12):
+        got, want = fused.step(toks[:, t]), plain.step(toks[:, t])
+        assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), t
+    assert fused.len == plain.len == 12
+    assert torch.allclose(fused.kc, plain.kc, atol=1e-5) and torch.allclose(fused.vc, plain.vc, atol=1e-5)
+    with pytest.raises(IndexError):
+        for _ in range(13):
+            fused.step(toks[:, 0])
