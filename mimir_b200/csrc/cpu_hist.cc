@@ -6,7 +6,10 @@
 // [3][F][nbins] = sums of g, sums of h, counts.  Rows are split evenly over the worker threads, each
 // adds into a histogram of its own, and the partial histograms are summed in thread order, so the
 // result does not depend on timing.
+#include <cmath>
+#include <cstdint>
 #include <cstring>
+#include <new>
 
 #include "cpu_pool.h"
 
@@ -68,6 +71,24 @@ inline uint64_t mix(uint64_t z) {
   return z ^ (z >> 31);
 }
 
+// A node's histogram: cells that are NOT zeroed when they are made (the pass that counts a feature clears that
+// feature's cells first, on the worker that counts it).
+struct Hist {
+  Cell* p = nullptr;
+  Hist() = default;
+  Hist(const Hist&) = delete;
+  Hist& operator=(const Hist&) = delete;
+  Hist(Hist&& o) noexcept : p(o.p) { o.p = nullptr; }
+  Hist& operator=(Hist&& o) noexcept { if (this != &o) { release(); p = o.p; o.p = nullptr; } return *this; }
+  ~Hist() { release(); }
+  void make(size_t cells) { release(); p = static_cast<Cell*>(::operator new(cells * sizeof(Cell), std::align_val_t(32))); }
+  void release() { if (p) ::operator delete(p, std::align_val_t(32)); p = nullptr; }
+  bool empty() const { return p == nullptr; }
+  Cell* data() { return p; }
+  const Cell* data() const { return p; }
+  Cell& operator[](size_t i) { return p[i]; }
+};
+
 // A node while the tree grows, level by level.
 struct Grow {
   long long lo = 0, hi = 0;        // its rows are idx[lo .. hi)
@@ -77,32 +98,56 @@ struct Grow {
   int feature = -1, bin = 0;
   double G = 0, H = 0, gain = 0, GL = 0, HL = 0;
   long long nl = 0;                // rows that go left
-  std::vector<Cell> hist;          // empty for a node that cannot split (depth limit): its sums are given
+  Hist hist;                       // empty for a node that cannot split (depth limit): its sums are given
   bool counted = false;            // its histogram is counted from its rows (the smaller child); else parent - sibling
 };
 
-// One feature's pass over the rows idx[lo .. hi): the cell of each row's bin takes (gradient, hessian, 1).
-// With AVX2 the three additions are one 256-bit add on the padded cell.
-__attribute__((target("avx2"))) void count_cells_avx2(const uint8_t* col, const int64_t* idx, const float* og, const float* oh,
-                                                       long long lo, long long hi, Cell* c) {
-  for (long long k = lo; k < hi; ++k) {
-    double* cell = reinterpret_cast<double*>(c + col[idx[k]]);
-    const __m256d inc = _mm256_set_pd(0.0, 1.0, static_cast<double>(oh[k]), static_cast<double>(og[k]));
-    _mm256_store_pd(cell, _mm256_add_pd(_mm256_load_pd(cell), inc));
-  }
-}
-
-void count_cells(const uint8_t* col, const int64_t* idx, const float* og, const float* oh, long long lo, long long hi, Cell* c) {
-  static const bool avx2 = __builtin_cpu_supports("avx2");
-  if (avx2) {
-    count_cells_avx2(col, idx, og, oh, lo, hi, c);
+// One pass over the rows idx[lo .. hi) for one feature or for two at once: the cell of each row's bin takes
+// (gradient, hessian, 1).  gh holds the two numbers of a row side by side, in row order.  Two features per pass
+// halve the reads of the row numbers and the gradients, which is what a large node's pass waits for.  With AVX2
+// the three additions are one 256-bit add on the padded cell.
+__attribute__((target("avx2"))) void count_cells_avx2(const uint8_t* col, const uint8_t* col2, const int32_t* idx, const float* gh,
+                                                       long long lo, long long hi, Cell* c, Cell* c2) {
+  const __m256d one = _mm256_set_pd(0.0, 1.0, 0.0, 0.0);
+  if (col2 == nullptr) {
+    for (long long k = lo; k < hi; ++k) {
+      double* cell = reinterpret_cast<double*>(c + col[idx[k]]);
+      const __m128 pair = _mm_castpd_ps(_mm_load_sd(reinterpret_cast<const double*>(gh + 2 * k)));
+      const __m256d inc = _mm256_add_pd(_mm256_insertf128_pd(_mm256_setzero_pd(), _mm_cvtps_pd(pair), 0), one);
+      _mm256_store_pd(cell, _mm256_add_pd(_mm256_load_pd(cell), inc));
+    }
     return;
   }
   for (long long k = lo; k < hi; ++k) {
-    Cell& cell = c[col[idx[k]]];
-    cell.g += og[k];
-    cell.h += oh[k];
+    const int32_t r = idx[k];
+    double* cell = reinterpret_cast<double*>(c + col[r]);
+    double* cell2 = reinterpret_cast<double*>(c2 + col2[r]);
+    const __m128 pair = _mm_castpd_ps(_mm_load_sd(reinterpret_cast<const double*>(gh + 2 * k)));
+    const __m256d inc = _mm256_add_pd(_mm256_insertf128_pd(_mm256_setzero_pd(), _mm_cvtps_pd(pair), 0), one);
+    _mm256_store_pd(cell, _mm256_add_pd(_mm256_load_pd(cell), inc));
+    _mm256_store_pd(cell2, _mm256_add_pd(_mm256_load_pd(cell2), inc));
+  }
+}
+
+void count_cells(const uint8_t* col, const uint8_t* col2, const int32_t* idx, const float* gh, long long lo, long long hi, Cell* c,
+                 Cell* c2) {
+  static const bool avx2 = __builtin_cpu_supports("avx2");
+  if (avx2) {
+    count_cells_avx2(col, col2, idx, gh, lo, hi, c, c2);
+    return;
+  }
+  for (long long k = lo; k < hi; ++k) {
+    const int32_t r = idx[k];
+    Cell& cell = c[col[r]];
+    cell.g += gh[2 * k];
+    cell.h += gh[2 * k + 1];
     cell.c += 1.0;
+    if (col2) {
+      Cell& other = c2[col2[r]];
+      other.g += gh[2 * k];
+      other.h += gh[2 * k + 1];
+      other.c += 1.0;
+    }
   }
 }
 
@@ -130,38 +175,45 @@ void for_each(mimir_cpu::Pool& pool, long long count, bool parallel, const Fn& f
 // The tree grows one LEVEL at a time, so the pool is entered a few times per level instead of a few times per
 // node: (1) every node of the level finds its best split, (2) the rows of the splitting nodes are partitioned,
 // (3) the gradients are gathered into row order once for the whole level, (4) the histograms of the smaller
-// children are counted, one (child, feature) pass per task, each pass touching one feature's cells only,
+// children are counted, one (child, feature pair) pass per task, each pass touching its two features' cells only,
 // (5) the larger children take the parent's histogram minus the sibling's.  Every sum is made by one worker in
 // row order, so the tree does not depend on the number of workers.
-static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, long long n, const float* g, const float* h,
-                     int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
+// The caller holds the pool's lock.
+static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total, int F, int32_t* idx, long long n, const float* g,
+                     const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
                      unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out) {
   if (F < 1 || nbins < 1 || nbins > 256 || n < 1 || max_nodes < 1 || max_depth < 0) return -1;
-  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
-  mimir_cpu::Pool& pool = mimir_cpu::pool();
   const size_t cells = static_cast<size_t>(F) * nbins;
   std::vector<Grow> all;
   all.reserve(static_cast<size_t>(max_nodes < 4096 ? max_nodes : 4096));
-  std::vector<float> og(n), oh(n);
-  std::vector<int64_t> scratch(n);
+  std::vector<float> gh(2 * static_cast<size_t>(n));       // (gradient, hessian) of the rows in the order of idx
+  std::vector<int32_t> scratch(n);
   const bool wide = n * static_cast<long long>(F) >= 65536;      // enough work to share at all
 
   auto gather = [&](long long lo, long long hi) {
     const long long chunk = 16384, count = (hi - lo + chunk - 1) / chunk;
     for_each(pool, count, wide, [&](long long c) {
       const long long a = lo + c * chunk, b = a + chunk < hi ? a + chunk : hi;
-      for (long long k = a; k < b; ++k) { og[k] = g[idx[k]]; oh[k] = h[idx[k]]; }
+      for (long long k = a; k < b; ++k) { gh[2 * k] = g[idx[k]]; gh[2 * k + 1] = h[idx[k]]; }
     });
   };
-  auto count_feature = [&](Grow& nd, int f) { count_cells(bins + static_cast<size_t>(f) * total, idx, og.data(), oh.data(), nd.lo, nd.hi,
-                                                          nd.hist.data() + static_cast<size_t>(f) * nbins); };
+  // features 2 q and 2 q + 1 (the last pair of an odd count is one feature) of a node, cleared and counted
+  const int pairs = (F + 1) / 2;
+  auto count_pair = [&](Grow& nd, int q) {
+    const int f = 2 * q;
+    const bool two = f + 1 < F;
+    Cell* c = nd.hist.data() + static_cast<size_t>(f) * nbins;
+    memset(static_cast<void*>(c), 0, sizeof(Cell) * nbins * (two ? 2 : 1));
+    count_cells(bins + static_cast<size_t>(f) * total, two ? bins + static_cast<size_t>(f + 1) * total : nullptr, idx, gh.data(), nd.lo,
+                nd.hi, c, c + nbins);
+  };
 
   all.emplace_back();
   all[0].lo = 0;
   all[0].hi = n;
-  all[0].hist.assign(cells, Cell{0, 0, 0, 0});
+  all[0].hist.make(cells);
   gather(0, n);
-  for_each(pool, F, wide, [&](long long f) { count_feature(all[0], static_cast<int>(f)); });
+  for_each(pool, pairs, wide, [&](long long q) { count_pair(all[0], static_cast<int>(q)); });
   {
     double G = 0, H = 0;
     for (int b = 0; b < nbins; ++b) { G += all[0].hist[b].g; H += all[0].hist[b].h; }      // every row falls in some bin of feature 0
@@ -217,11 +269,12 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
     next_level.clear();
     for (int id : level) {
       if (all[id].feature < 0) {
-        std::vector<Cell>().swap(all[id].hist);          // a leaf: its histogram is not needed again
+        all[id].hist.release();          // a leaf: its histogram is not needed again
         continue;
       }
       if (static_cast<int>(all.size()) + 2 > max_nodes) return -1;
-      const Grow p = Grow{all[id].lo, all[id].hi, all[id].depth, all[id].path};
+      Grow p;
+      p.lo = all[id].lo; p.hi = all[id].hi; p.depth = all[id].depth; p.path = all[id].path;
       const long long mid = p.lo + all[id].nl;
       Grow l, r;
       l.lo = p.lo; l.hi = mid; r.lo = mid; r.hi = p.hi;
@@ -240,25 +293,30 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
     // cut into chunks (counted, then written at the places the counts before them give); many nodes go one per task.
     const long long parents = static_cast<long long>(next_level.size());
     const int workers = pool.size();
+    auto split_rows = [&](Grow& nd) {
+      const uint8_t* col = bins + static_cast<size_t>(nd.feature) * total;
+      long long nl = 0, nr = 0;
+      for (long long k = nd.lo; k < nd.hi; ++k) {
+        const int32_t r = idx[k];
+        const bool left = col[r] <= nd.bin;
+        idx[nd.lo + nl] = r;          // both stores are made and one cursor moves: no branch to mispredict
+        scratch[nd.lo + nr] = r;
+        nl += left;
+        nr += !left;
+      }
+      memcpy(idx + nd.lo + nl, scratch.data() + nd.lo, sizeof(int32_t) * nr);
+    };
     if (wide && parents < workers) {
+      std::vector<int> small_ones;
+      for (int id : next_level)
+        if (all[id].hi - all[id].lo < 32768) small_ones.push_back(id);
+      for_each(pool, static_cast<long long>(small_ones.size()), true, [&](long long i) { split_rows(all[small_ones[i]]); });
       for (int id : next_level) {
         Grow& nd = all[id];
         const uint8_t* col = bins + static_cast<size_t>(nd.feature) * total;
         const long long rows = nd.hi - nd.lo;
-        const int chunks = rows < 32768 ? 1 : workers;
-        if (chunks == 1) {
-          long long nl = 0, nr = 0;
-          for (long long k = nd.lo; k < nd.hi; ++k) {
-            const int64_t r = idx[k];
-            const bool left = col[r] <= nd.bin;
-            idx[nd.lo + nl] = r;          // both stores are made and one cursor moves: no branch to mispredict
-            scratch[nd.lo + nr] = r;
-            nl += left;
-            nr += !left;
-          }
-          memcpy(idx + nd.lo + nl, scratch.data() + nd.lo, sizeof(int64_t) * nr);
-          continue;
-        }
+        if (rows < 32768) continue;
+        const int chunks = workers;
         std::vector<long long> lefts(chunks + 1, 0);
         const long long per = (rows + chunks - 1) / chunks;
         for_each(pool, chunks, true, [&](long long part) {
@@ -273,28 +331,18 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
           const long long a = nd.lo + part * per, b = a + per < nd.hi ? a + per : nd.hi;
           long long wl = nd.lo + lefts[part], wr = nd.lo + nl + (a - nd.lo) - lefts[part];
           for (long long k = a; k < b; ++k) {
-            const int64_t r = idx[k];
+            const int32_t r = idx[k];
             if (col[r] <= nd.bin) scratch[wl++] = r;
             else scratch[wr++] = r;
           }
         });
-        memcpy(idx + nd.lo, scratch.data() + nd.lo, sizeof(int64_t) * rows);
+        for_each(pool, chunks, true, [&](long long part) {
+          const long long a = nd.lo + part * per, b = a + per < nd.hi ? a + per : nd.hi;
+          if (b > a) memcpy(idx + a, scratch.data() + a, sizeof(int32_t) * (b - a));
+        });
       }
     } else {
-      for_each(pool, parents, wide, [&](long long pi) {
-        Grow& nd = all[next_level[pi]];
-        const uint8_t* col = bins + static_cast<size_t>(nd.feature) * total;
-        long long nl = 0, nr = 0;
-        for (long long k = nd.lo; k < nd.hi; ++k) {
-          const int64_t r = idx[k];
-          const bool left = col[r] <= nd.bin;
-          idx[nd.lo + nl] = r;
-          scratch[nd.lo + nr] = r;
-          nl += left;
-          nr += !left;
-        }
-        memcpy(idx + nd.lo + nl, scratch.data() + nd.lo, sizeof(int64_t) * nr);
-      });
+      for_each(pool, parents, wide, [&](long long pi) { split_rows(all[next_level[pi]]); });
     }
     // children that may split again need histograms: the smaller one is counted, the larger one is the
     // parent's minus it
@@ -304,10 +352,10 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
       Grow& nd = all[id];
       children.push_back(nd.left);
       children.push_back(nd.right);
-      if (nd.depth + 1 >= max_depth) { std::vector<Cell>().swap(nd.hist); continue; }     // the children are leaves: sums are given
+      if (nd.depth + 1 >= max_depth) { nd.hist.release(); continue; }     // the children are leaves: sums are given
       Grow &l = all[nd.left], &r = all[nd.right];
       Grow& small = (l.hi - l.lo) <= (r.hi - r.lo) ? l : r;
-      small.hist.assign(cells, Cell{0, 0, 0, 0});
+      small.hist.make(cells);
       small.counted = true;
       counted.push_back(&small == &l ? nd.left : nd.right);
       parents_of.push_back(id);
@@ -319,12 +367,12 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
         for (int c : counted)
           for (long long a = all[c].lo; a < all[c].hi; a += 16384) pieces.emplace_back(a, a + 16384 < all[c].hi ? a + 16384 : all[c].hi);
         for_each(pool, static_cast<long long>(pieces.size()), wide, [&](long long i) {
-          for (long long k = pieces[i].first; k < pieces[i].second; ++k) { og[k] = g[idx[k]]; oh[k] = h[idx[k]]; }
+          for (long long k = pieces[i].first; k < pieces[i].second; ++k) { gh[2 * k] = g[idx[k]]; gh[2 * k + 1] = h[idx[k]]; }
         });
       }
-      // (4) one (child, feature) pass per task
-      const long long tasks = static_cast<long long>(counted.size()) * F;
-      for_each(pool, tasks, wide, [&](long long t) { count_feature(all[counted[t / F]], static_cast<int>(t % F)); });
+      // (4) one (child, feature pair) pass per task
+      const long long tasks = static_cast<long long>(counted.size()) * pairs;
+      for_each(pool, tasks, wide, [&](long long t) { count_pair(all[counted[t / pairs]], static_cast<int>(t % pairs)); });
       // (5) the sibling takes what is left of the parent's histogram
       for_each(pool, static_cast<long long>(counted.size()), wide && counted.size() >= 4, [&](long long i) {
         Grow& parent = all[parents_of[i]];
@@ -339,6 +387,7 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
   // numbered depth first, left before right, like a recursive builder numbers them
   int n_nodes = 0;
   std::vector<std::pair<int, int>> stack;      // (node in the list, slot of the parent to patch or -1)
+  std::vector<int> leaves;
   stack.emplace_back(0, -1);
   while (!stack.empty()) {
     const auto [id, slot] = stack.back();
@@ -353,11 +402,16 @@ static int grow_tree(const uint8_t* bins, long long total, int F, int64_t* idx, 
       stack.emplace_back(nd.right, n_nodes * 5 + 3);      // right is pushed first so that left is numbered first
       stack.emplace_back(nd.left, n_nodes * 5 + 2);
     } else if (leaf_out) {
-      const float v = static_cast<float>(value);
-      for (long long k = nd.lo; k < nd.hi; ++k) leaf_out[idx[k]] = v;
+      leaves.push_back(id);
     }
     ++n_nodes;
   }
+  // every row's answer: the leaves share the workers (a row belongs to one leaf, so no two tasks write one place)
+  for_each(pool, static_cast<long long>(leaves.size()), wide, [&](long long i) {
+    const Grow& nd = all[leaves[i]];
+    const float v = static_cast<float>(-nd.G / (nd.H + l2));
+    for (long long k = nd.lo; k < nd.hi; ++k) leaf_out[idx[k]] = v;
+  });
   return n_nodes;
 }
 
@@ -367,11 +421,65 @@ MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long 
                                               const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2,
                                               int colsample_k, unsigned long long seed, double* nodes, int max_nodes,
                                               double* importance, float* leaf_out) {
-  if (total < 1) return -1;
-  for (long long k = 0; k < n; ++k)
+  if (total < 1 || total > INT32_MAX || n < 1) return -1;
+  std::vector<int32_t> rows(n);          // row numbers as 32-bit values: half the bytes every pass reads
+  for (long long k = 0; k < n; ++k) {
     if (idx[k] < 0 || idx[k] >= total) return -1;
-  return grow_tree(colbins, total, F, idx, n, g, h, nbins, max_depth, min_leaf, min_gain, l2, colsample_k, seed, nodes, max_nodes,
-                   importance, leaf_out);
+    rows[k] = static_cast<int32_t>(idx[k]);
+  }
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  const int cnt = grow_tree(mimir_cpu::pool(), colbins, total, F, rows.data(), n, g, h, nbins, max_depth, min_leaf, min_gain, l2,
+                            colsample_k, seed, nodes, max_nodes, importance, leaf_out);
+  for (long long k = 0; k < n; ++k) idx[k] = rows[k];
+  return cnt;
+}
+
+// `rounds` rounds of second-order boosting over all rows, without returning to the caller between trees: the
+// workers stay awake from one tree to the next, and a round's gradients and score update are two passes here
+// instead of a dozen tensor operations.  kind 0: squared error (g = score - y, h = 1); kind 1: logistic
+// (p = sigmoid(score), g = p - y, h = max(p (1 - p), 1e-6)).  score [total] (float) is updated in place by
+// lr * (the leaf each row reached).  seeds [rounds]: the feature-draw seed of each tree (read when colsample_k > 0).
+// nodes: double [rounds][max_nodes][5]; counts: int [rounds]; importance: double [rounds][F] (zeroed here).
+// Returns the number of rounds done (all of them), or -1.
+MIMIR_CPU_API int mimir_cpu_boost(const uint8_t* colbins, long long total, int F, const float* y, float* score, int kind, int rounds,
+                                  double lr, int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
+                                  const unsigned long long* seeds, double* nodes, int max_nodes, int* counts, double* importance) {
+  if (total < 1 || total > INT32_MAX || rounds < 0 || (kind != 0 && kind != 1)) return -1;
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  std::vector<float> g(total), h(total), leaf(total);
+  std::vector<int32_t> idx(total);
+  const long long chunk = 8192, chunks = (total + chunk - 1) / chunk;
+  const bool wide = total >= 4 * chunk;
+  const float step = static_cast<float>(lr);
+  for (int r = 0; r < rounds; ++r) {
+    for_each(pool, chunks, wide, [&](long long c) {
+      const long long a = c * chunk, b = a + chunk < total ? a + chunk : total;
+      for (long long k = a; k < b; ++k) idx[k] = static_cast<int32_t>(k);
+      if (kind == 0) {
+        for (long long k = a; k < b; ++k) { g[k] = score[k] - y[k]; h[k] = 1.0f; }
+      } else {
+        for (long long k = a; k < b; ++k) {
+          const float p = 1.0f / (1.0f + std::exp(-score[k]));
+          const float hh = p * (1.0f - p);
+          g[k] = p - y[k];
+          h[k] = hh < 1e-6f ? 1e-6f : hh;
+        }
+      }
+    });
+    double* imp = importance + static_cast<size_t>(r) * F;
+    for (int f = 0; f < F; ++f) imp[f] = 0;
+    const int cnt = grow_tree(pool, colbins, total, F, idx.data(), total, g.data(), h.data(), nbins, max_depth, min_leaf, min_gain, l2,
+                              colsample_k, seeds ? seeds[r] : 0ull, nodes + static_cast<size_t>(r) * max_nodes * 5, max_nodes, imp,
+                              leaf.data());
+    if (cnt <= 0) return -1;
+    counts[r] = cnt;
+    for_each(pool, chunks, wide, [&](long long c) {
+      const long long a = c * chunk, b = a + chunk < total ? a + chunk : total;
+      for (long long k = a; k < b; ++k) score[k] += step * leaf[k];
+    });
+  }
+  return rounds;
 }
 
 // out[r] = value of the leaf row r of `bins` (uint8 [n][F]) reaches in the tree `nodes` (double [n_nodes][5]).
@@ -402,4 +510,123 @@ MIMIR_CPU_API int mimir_cpu_tree_predict(const uint8_t* bins, int F, long long n
   if (n < 16384) work(0, 1);
   else pool.run(work);
   return bad.load() ? -1 : 0;
+}
+
+namespace {
+
+// the number of edges below x (NaN: n_edges): the first edge that is not below x, found without a branch the
+// processor has to guess
+inline int bin_of(const float* e, int n_edges, float x) {
+  if (!(x == x) || n_edges == 0) return n_edges;
+  const float* base = e;
+  int len = n_edges;
+  while (len > 1) {
+    const int half = len / 2;
+    base += base[half - 1] < x ? half : 0;
+    len -= half;
+  }
+  return static_cast<int>(base - e) + (base[0] < x ? 1 : 0);
+}
+
+// sixteen values of one feature at a time: the same halving search in every lane, the probes fetched by a gather
+__attribute__((target("avx512f,avx512bw"))) void bins_avx512(const float* e, int n_edges, const float* x, long long count, uint8_t* out) {
+  long long k = 0;
+  if (n_edges > 0) {
+    for (; k + 16 <= count; k += 16) {
+      const __m512 v = _mm512_loadu_ps(x + k);
+      __m512i base = _mm512_setzero_si512();
+      int len = n_edges;
+      while (len > 1) {
+        const int half = len / 2;
+        const __m512 probe = _mm512_i32gather_ps(_mm512_add_epi32(base, _mm512_set1_epi32(half - 1)), e, 4);
+        base = _mm512_mask_add_epi32(base, _mm512_cmp_ps_mask(probe, v, _CMP_LT_OQ), base, _mm512_set1_epi32(half));
+        len -= half;
+      }
+      const __m512 probe = _mm512_i32gather_ps(base, e, 4);
+      base = _mm512_mask_add_epi32(base, _mm512_cmp_ps_mask(probe, v, _CMP_LT_OQ), base, _mm512_set1_epi32(1));
+      base = _mm512_mask_mov_epi32(base, _mm512_cmp_ps_mask(v, v, _CMP_UNORD_Q), _mm512_set1_epi32(n_edges));
+      _mm_storeu_si128(reinterpret_cast<__m128i*>(out + k), _mm512_cvtepi32_epi8(base));
+    }
+  }
+  for (; k < count; ++k) out[k] = static_cast<uint8_t>(bin_of(e, n_edges, x[k]));
+}
+
+}  // namespace
+
+// Bins a table: X float [n][F] (row-major); edges float [F][n_edges], ascending per feature.  The bin of a value
+// is the number of its feature's edges below it (NaN: n_edges, after every edge).  Written twice: rows uint8
+// [n][F] (what prediction walks) and cols uint8 [F][n] (what the grower reads); either may be null.
+// n_edges <= 255.  Chunks of rows share the workers; a chunk is turned to one column per feature first, so the
+// search runs over sixteen neighbouring values of a feature at a time where the CPU has AVX-512.
+MIMIR_CPU_API int mimir_cpu_bin_table(const float* X, long long n, int F, const float* edges, int n_edges, uint8_t* rows, uint8_t* cols) {
+  if (n < 0 || F < 1 || n_edges < 0 || n_edges > 255) return -1;
+  static const bool wide_lanes = __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw");
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  const long long chunk = 2048, chunks = (n + chunk - 1) / chunk;
+  for_each(pool, chunks, n * F >= 65536, [&](long long c) {
+    const long long a = c * chunk, b = a + chunk < n ? a + chunk : n, m = b - a;
+    std::vector<float> xs(static_cast<size_t>(F) * m);
+    std::vector<uint8_t> bs(static_cast<size_t>(F) * m);
+    for (long long r = 0; r < m; ++r)
+      for (int f = 0; f < F; ++f) xs[static_cast<size_t>(f) * m + r] = X[static_cast<size_t>(a + r) * F + f];
+    for (int f = 0; f < F; ++f) {
+      const float* e = edges + static_cast<size_t>(f) * n_edges;
+      const float* x = xs.data() + static_cast<size_t>(f) * m;
+      uint8_t* o = bs.data() + static_cast<size_t>(f) * m;
+      if (wide_lanes) bins_avx512(e, n_edges, x, m, o);
+      else
+        for (long long r = 0; r < m; ++r) o[r] = static_cast<uint8_t>(bin_of(e, n_edges, x[r]));
+      if (cols) memcpy(cols + static_cast<size_t>(f) * n + a, o, m);
+    }
+    if (rows)
+      for (long long r = 0; r < m; ++r)
+        for (int f = 0; f < F; ++f) rows[static_cast<size_t>(a + r) * F + f] = bs[static_cast<size_t>(f) * m + r];
+  });
+  return 0;
+}
+
+// out[r] = the sum over `trees` trees of the value of the leaf row r of `bins` (uint8 [n][F]) reaches.  The
+// trees' node tables lie one after another in `nodes` (double [.][5], child numbers relative to the tree's
+// first node); tree t owns nodes offsets[t] .. offsets[t + 1].  Sums are made in tree order in double.
+MIMIR_CPU_API int mimir_cpu_trees_predict(const uint8_t* bins, int F, long long n, const double* nodes, const long long* offsets, int trees,
+                                          float* out) {
+  if (F < 1 || n < 0 || trees < 0) return -1;
+  // the tables in a form a walk reads quickly, checked once: a child comes after its parent (so every walk
+  // ends) and lies inside its tree, a feature inside the row
+  struct Step { int32_t feature, bin, child[2]; double value; };
+  std::vector<Step> steps(trees > 0 ? static_cast<size_t>(offsets[trees] - offsets[0]) : 0);
+  for (int t = 0; t < trees; ++t) {
+    const long long lo = offsets[t], count = offsets[t + 1] - lo;
+    if (count <= 0 || lo - offsets[0] < 0) return -1;
+    for (long long i = 0; i < count; ++i) {
+      const double* nd = nodes + static_cast<size_t>(lo + i) * 5;
+      Step& s = steps[static_cast<size_t>(lo - offsets[0] + i)];
+      s.feature = static_cast<int32_t>(nd[0]);
+      s.bin = static_cast<int32_t>(nd[1]);
+      s.child[0] = static_cast<int32_t>(nd[2]);
+      s.child[1] = static_cast<int32_t>(nd[3]);
+      s.value = nd[4];
+      if (s.feature >= F) return -1;
+      if (s.feature >= 0 && (s.child[0] <= i || s.child[0] >= count || s.child[1] <= i || s.child[1] >= count)) return -1;
+    }
+  }
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  const long long chunk = 1024, chunks = (n + chunk - 1) / chunk;
+  for_each(pool, chunks, n * trees >= 65536, [&](long long c) {
+    const long long a = c * chunk, b = a + chunk < n ? a + chunk : n;
+    std::vector<double> sum(b - a, 0.0);
+    for (int t = 0; t < trees; ++t) {
+      const Step* tree = steps.data() + (offsets[t] - offsets[0]);
+      for (long long r = a; r < b; ++r) {
+        const uint8_t* row = bins + static_cast<size_t>(r) * F;
+        const Step* s = tree;
+        while (s->feature >= 0) s = tree + s->child[row[s->feature] > s->bin];
+        sum[r - a] += s->value;
+      }
+    }
+    for (long long r = a; r < b; ++r) out[r] = static_cast<float>(sum[r - a]);
+  });
+  return 0;
 }

@@ -1,8 +1,9 @@
 """Histogram-based trees (reference: tree/): DecisionTree, RandomForest, GradientBoosting,
 IsolationForest.  Features are binned into at most 255 bins once; split search works on
 per-node gradient / hessian histograms (the reference accelerates the same histograms
-with AVX2 assembly, tree/hist_amd64.go; here they are ``torch.bincount`` calls, which run
-on the GPU when the data lives there)."""
+with AVX2 assembly, tree/hist_amd64.go; on the host the binning, the trees and whole boosting
+loops are native code, ``csrc/cpu_hist.cc``; elsewhere the histograms are ``torch.bincount``
+calls, which run on the GPU when the data lives there)."""
 from __future__ import annotations
 
 import json
@@ -18,9 +19,35 @@ def _bin(X, bins=255):
     # of every column is the most expensive step of a fit on a large table
     S = X if X.shape[0] <= 65536 else X[torch.linspace(0, X.shape[0] - 1, 65536).long()]
     edges = torch.quantile(S, qs.to(X.device), dim=0).t().contiguous()  # [F, bins-1]
+    if bins <= 256 and X.device.type == "cpu":
+        # one byte per value, written by rows (what prediction walks) and by columns (what the grower reads)
+        B, cols = bin_table(X, edges, columns=True)
+        _COLUMNS["last"] = ((B.data_ptr(), tuple(B.shape), B._version), cols, B)
+        return B, edges
     B = torch.searchsorted(edges, X.t().contiguous()).t().contiguous()
-    # one byte per value when the bins allow it: the native histogram pass reads the rows as they are
     return B.to(torch.uint8 if bins <= 256 else torch.int64), edges
+
+
+def bin_table(X, edges, columns=False):
+    """The bin of every value of ``X [n, F]``: the number of its feature's ``edges [F, bins - 1]`` below it, as
+    uint8 ``[n, F]`` (``torch.searchsorted`` per feature, done by ``mimir_cpu_bin_table`` over the worker pool).
+    ``columns=True`` also returns the same table held one column per feature, ``[F, n]``."""
+    import ctypes
+    from .. import _native
+    X, edges = X.float().contiguous(), edges.float().contiguous()
+    n, F = X.shape
+    if edges.shape[0] != F or edges.shape[1] > 255:
+        raise ValueError(f"edges of shape {tuple(edges.shape)} for {F} features")
+    lib = _native.lib()
+    if not getattr(lib, "_bin_bound", False):
+        lib.mimir_cpu_bin_table.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                            ctypes.c_void_p]
+        lib._bin_bound = True
+    B = torch.empty(n, F, dtype=torch.uint8)
+    cols = torch.empty(F, n, dtype=torch.uint8) if columns else None
+    if lib.mimir_cpu_bin_table(X.data_ptr(), n, F, edges.data_ptr(), edges.shape[1], B.data_ptr(), cols.data_ptr() if columns else None) != 0:
+        raise ValueError("bin_table: bad arguments")
+    return (B, cols) if columns else B
 
 
 _COLUMNS: dict = {}
@@ -214,21 +241,43 @@ class Model:
         self.trees, self.edges, self.lr, self.base, self.classes, self.kind = trees, edges, lr, base, classes, kind
 
     def _binned(self, X):
-        return torch.searchsorted(self.edges, torch.as_tensor(X).float().t().contiguous()).t().contiguous()
+        X = torch.as_tensor(X).float()
+        if X.device.type == "cpu" and self.edges.shape[1] <= 255:
+            return bin_table(X, self.edges)
+        return torch.searchsorted(self.edges, X.t().contiguous()).t().contiguous()
+
+    @staticmethod
+    def _sum_of(trees, B):
+        """The sum of the trees' values for every row of ``B``: one native pass over all trees for byte bins
+        on the host (``mimir_cpu_trees_predict``), else tree by tree."""
+        if B.dtype == torch.uint8 and B.device.type == "cpu" and B.is_contiguous() and trees and all(t.nodes for t in trees):
+            import ctypes
+            from .. import _native
+            lib = _native.lib()
+            if not getattr(lib, "_trees_bound", False):
+                lib.mimir_cpu_trees_predict.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p,
+                                                        ctypes.c_int, ctypes.c_void_p]
+                lib._trees_bound = True
+            tbl = torch.tensor([q for t in trees for q in t.nodes], dtype=torch.float64)
+            offsets = torch.tensor([0] + [len(t.nodes) for t in trees], dtype=torch.int64).cumsum(0).contiguous()
+            out = torch.empty(B.shape[0])
+            if lib.mimir_cpu_trees_predict(B.data_ptr(), B.shape[1], B.shape[0], tbl.data_ptr(), offsets.data_ptr(), len(trees),
+                                           out.data_ptr()) == 0:
+                return out
+        out = torch.zeros(B.shape[0])
+        for t in trees:
+            out += t.predict_binned(B)
+        return out
 
     def raw(self, X):
         B = self._binned(X)
         if self.classes > 2:
             out = self.base.clone().repeat(B.shape[0], 1)
-            for round_trees in self.trees:
-                for k, t in enumerate(round_trees):
-                    out[:, k] += self.lr * t.predict_binned(B)
+            for k in range(self.classes):
+                out[:, k] += self.lr * self._sum_of([r[k] for r in self.trees], B)
             return out
-        out = torch.full((B.shape[0],), float(self.base))
         scale = self.lr if self.kind == "gbdt" else 1.0 / max(len(self.trees), 1)
-        for t in self.trees:
-            out += scale * t.predict_binned(B)
-        return out
+        return float(self.base) + scale * self._sum_of(self.trees, B)
 
     def predict(self, X):
         r = self.raw(X)
@@ -274,13 +323,53 @@ class Model:
         return Model(trees, torch.tensor(d["edges"]), d["lr"], base, d["classes"], d["kind"])
 
 
+def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, l2, bins, colsample, gen):
+    """``rounds`` trees grown one after another by ``mimir_cpu_boost`` (``csrc/cpu_hist.cc``) on all rows of ``B``;
+    ``score`` is updated in place.  Feature-draw seeds come from ``gen`` in the order the per-tree loop draws them."""
+    import ctypes
+    from .. import _native
+    lib = _native.lib()
+    if not getattr(lib, "_boost_bound", False):
+        c = ctypes
+        lib.mimir_cpu_boost.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_double, c.c_int, c.c_int,
+                                        c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p]
+        lib._boost_bound = True
+    total, F = B.shape
+    k, seeds = 0, None
+    if colsample < 1.0:
+        k = max(1, int(F * colsample))
+        seeds = torch.tensor([int(torch.randint(0, 2 ** 62, (1,), generator=gen)) for _ in range(rounds)], dtype=torch.int64)
+    max_nodes = int(min(2 ** (max_depth + 1) - 1, 2 * total + 1))
+    nodes = torch.empty(rounds, max_nodes, 5, dtype=torch.float64)
+    counts = torch.zeros(rounds, dtype=torch.int32)
+    imp = torch.empty(rounds, F, dtype=torch.float64)
+    cols = _columns(B)
+    y = y.float().contiguous()
+    done = lib.mimir_cpu_boost(cols.data_ptr(), total, F, y.data_ptr(), score.data_ptr(), kind, rounds, float(lr), bins, max_depth,
+                               max(int(min_leaf), 1) if min_leaf >= 1 else 0, float(min_gain), float(l2), k,
+                               seeds.data_ptr() if seeds is not None else None, nodes.data_ptr(), max_nodes, counts.data_ptr(), imp.data_ptr())
+    if done != rounds:
+        raise RuntimeError("boosting: the native grower refused its arguments")
+    out = []
+    for r in range(rounds):
+        t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen)
+        t.nodes = [[int(q[0]), int(q[1]), int(q[2]), int(q[3]), float(q[4])] for q in nodes[r, : int(counts[r])].tolist()]
+        t.importance = imp[r].float()
+        t.answers = None
+        out.append(t)
+    return out
+
+
 def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=1, min_gain=0.0, l2=1.0, bins=255,
-                      subsample=1.0, colsample=1.0, classes=0, seed=0, validation=None, patience=10, progress=None) -> Model:
+                      subsample=1.0, colsample=1.0, classes=0, seed=0, validation=None, patience=10, progress=None,
+                      native_rounds=True) -> Model:
     """Second-order boosting: squared error (classes=0), logistic (2) or softmax (>2).  ``subsample`` draws
     that share of the rows for each tree and ``colsample`` that share of the features for each node.
     ``validation`` (a table, or ``(X, y)``) is scored after every round (squared error or log loss): boosting
     stops once ``patience`` rounds in a row have not improved it, and the model keeps the best round's trees
-    (tree/boost.go: Validation)."""
+    (tree/boost.go: Validation).  Without row sampling and validation, regression and two-class boosting run all
+    their rounds in one native call; ``native_rounds=False`` keeps the per-round loop (the same trees up to the
+    rounding of the sigmoid)."""
     X, y = torch.as_tensor(X).float(), torch.as_tensor(y)
     gen = torch.Generator().manual_seed(seed)
     B, edges = _bin(X, bins)
@@ -302,6 +391,15 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
         F = torch.full((n,), base)
     if held is not None:
         held["F"] = base.clone().repeat(held["B"].shape[0], 1) if classes > 2 else torch.full((held["B"].shape[0],), base)
+    if native_rounds and classes <= 2 and subsample >= 1.0 and held is None and B.dtype == torch.uint8 and B.device.type == "cpu" and bins <= 256:
+        # every round in native code (``mimir_cpu_boost``): the loop below is its oracle
+        span = 10 if progress is not None else trees
+        for it in range(0, trees, span):
+            out_trees += _boost_native(B, yf, F, 0 if classes == 0 else 1, min(span, trees - it), learning_rate, max_depth, min_leaf,
+                                       min_gain, l2, bins, colsample, gen)
+            if progress is not None and len(out_trees) % 10 == 0:
+                progress.write(f"tree {len(out_trees)}/{trees}\n")
+        trees = 0
     for it in range(trees):
         rows = None if subsample >= 1.0 else torch.randperm(n, generator=gen)[: max(1, int(n * subsample))]
         if classes > 2:

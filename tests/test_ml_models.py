@@ -372,3 +372,64 @@ def test_modules_save_load_and_export_like_networks(tmp_path):
         with mim.open(graph) as f:
             got = f.run({"x": Q})["y"].data()
         assert torch.allclose(got, want, rtol=1e-4, atol=1e-4), (name, float((got - want).abs().max()))
+
+
+@pytest.mark.parametrize("kw", [dict(classes=2), dict(classes=0), dict(classes=2, colsample=0.5)])
+def test_boosting_rounds_in_one_native_call_grow_the_trees_of_the_per_round_loop(kw):
+    """Regression and two-class boosting without row sampling or validation run every round inside one native
+    call; the per-round loop is the oracle: the same splits in every tree, leaf values within float rounding
+    (the native sigmoid and PyTorch's differ in the last bit), the same importances."""
+    from mimir_b200.ml import tree
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(6000, 8, generator=g)
+    score = X[:, 0] * 2 + X[:, 1] * X[:, 2] + 0.1 * torch.randn(6000, generator=g)
+    y = (score > 0).long() if kw["classes"] else score
+    a = tree.gradient_boosting(X, y, trees=12, max_depth=4, min_leaf=5, seed=3, **kw)
+    b = tree.gradient_boosting(X, y, trees=12, max_depth=4, min_leaf=5, seed=3, native_rounds=False, **kw)
+    assert len(a.trees) == len(b.trees) == 12
+    for ta, tb in zip(a.trees, b.trees):
+        assert [q[:4] for q in ta.nodes] == [q[:4] for q in tb.nodes]
+        assert max(abs(p[4] - q[4]) for p, q in zip(ta.nodes, tb.nodes)) < 1e-5
+    assert float((a.raw(X) - b.raw(X)).abs().max()) < 1e-4
+    assert torch.allclose(a.importance(), b.importance(), atol=1e-5)
+    lines = []
+
+    class Sink:
+        def write(self, s):
+            lines.append(s)
+    tree.gradient_boosting(X, y, trees=20, max_depth=3, progress=Sink(), **kw)
+    assert lines == ["tree 10/20\n", "tree 20/20\n"]
+
+
+def test_native_binning_and_ensemble_prediction_agree_with_the_tensor_ops():
+    """``bin_table`` is ``torch.searchsorted`` per feature (NaN after every edge, infinities, repeated edges),
+    by rows and by columns; the one-pass ensemble prediction is the sum of the trees walked one by one, for two
+    classes, several classes and forests; a table that is not a tree is refused, not walked."""
+    from mimir_b200.ml import tree
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(5003, 7, generator=g)
+    X[::11, 2] = float("nan")
+    X[5, 1], X[6, 1] = float("inf"), -float("inf")
+    edges = torch.quantile(torch.randn(4096, 7, generator=g), torch.linspace(0, 1, 256)[1:-1], dim=0).t().contiguous()
+    edges[3, 100:110] = edges[3, 100]
+    B, C = tree.bin_table(X, edges, columns=True)
+    assert B.dtype == torch.uint8 and torch.equal(B.long(), torch.searchsorted(edges, X.t().contiguous()).t())
+    assert torch.equal(B.t(), C)
+    assert torch.equal(tree.bin_table(X, edges[:, :0]), torch.zeros(5003, 7, dtype=torch.uint8))
+    Xc = torch.nan_to_num(X, nan=0.0, posinf=3.0, neginf=-3.0)
+    y3 = (Xc[:, 0] > 0.5).long() + (Xc[:, 1] > 0).long()
+    for m in (tree.gradient_boosting(Xc, (y3 > 0).long(), trees=8, max_depth=4, classes=2),
+              tree.gradient_boosting(Xc, y3, trees=5, max_depth=3, classes=3),
+              tree.random_forest(Xc, Xc[:, 0] * Xc[:, 1], trees=6, max_depth=5)):
+        Bm = m._binned(X)
+        groups = [[r[k] for r in m.trees] for k in range(3)] if m.classes > 2 else [m.trees]
+        for trees in groups:
+            want = sum(t.predict_binned(Bm).double() for t in trees)
+            assert torch.allclose(tree.Model._sum_of(trees, Bm).double(), want, atol=1e-5)
+        assert m.raw(X).shape[0] == 5003
+    t0 = m.trees[0]
+    good = t0.nodes
+    t0.nodes = [[0, 3, 0, 0, 0.0]] + [list(q) for q in good[1:]]      # a node that is its own child
+    lib_answer = tree.Model._sum_of(m.trees, Bm)                        # falls back to the walks with a step limit
+    assert torch.isfinite(lib_answer).all()
+    t0.nodes = good
