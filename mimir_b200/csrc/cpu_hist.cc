@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <memory>
 #include <new>
 
 #include "cpu_pool.h"
@@ -98,6 +99,7 @@ struct Grow {
   int feature = -1, bin = 0;
   double G = 0, H = 0, gain = 0, GL = 0, HL = 0;
   long long nl = 0;                // rows that go left
+  std::vector<int> feats;          // the features drawn for this node (empty: all of them)
   Hist hist;                       // empty for a node that cannot split (depth limit): its sums are given
   bool counted = false;            // its histogram is counted from its rows (the smaller child); else parent - sibling
 };
@@ -178,33 +180,55 @@ void for_each(mimir_cpu::Pool& pool, long long count, bool parallel, const Fn& f
 // children are counted, one (child, feature pair) pass per task, each pass touching its two features' cells only,
 // (5) the larger children take the parent's histogram minus the sibling's.  Every sum is made by one worker in
 // row order, so the tree does not depend on the number of workers.
-// The caller holds the pool's lock.
+// The caller holds the pool's lock, or passes serial = true: then nothing is handed to the pool and several
+// trees may grow at once, one per worker (a forest).
 static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total, int F, int32_t* idx, long long n, const float* g,
                      const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
-                     unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out) {
+                     unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out, bool serial = false) {
   if (F < 1 || nbins < 1 || nbins > 256 || n < 1 || max_nodes < 1 || max_depth < 0) return -1;
-  const size_t cells = static_cast<size_t>(F) * nbins;
+  // With few features drawn per node (at most half of them, as forests do) a node counts the features it drew
+  // and nothing else, and both children are counted: cheaper than counting every feature for the smaller child
+  // and subtracting whole histograms, which small nodes deep in a tree cannot pay for.
+  const bool sampled = colsample_k > 0 && colsample_k < F;
+  const bool direct = sampled && colsample_k * 2 <= F;
+  const int held = direct ? colsample_k : F;                       // features a node's histogram holds
+  const size_t cells = static_cast<size_t>(held) * nbins;
+  auto draw = [&](Grow& nd) {
+    nd.feats.resize(F);
+    for (int f = 0; f < F; ++f) nd.feats[f] = f;
+    uint64_t rng = mix(seed ^ (nd.path * 0x9E3779B97F4A7C15ull));
+    for (int k = 0; k < colsample_k; ++k) {
+      rng = mix(rng + 0x9E3779B97F4A7C15ull);
+      const int j = k + static_cast<int>(rng % static_cast<uint64_t>(F - k));
+      const int t = nd.feats[k]; nd.feats[k] = nd.feats[j]; nd.feats[j] = t;
+    }
+    nd.feats.resize(colsample_k);
+  };
   std::vector<Grow> all;
   all.reserve(static_cast<size_t>(max_nodes < 4096 ? max_nodes : 4096));
   std::vector<float> gh(2 * static_cast<size_t>(n));       // (gradient, hessian) of the rows in the order of idx
   std::vector<int32_t> scratch(n);
-  const bool wide = n * static_cast<long long>(F) >= 65536;      // enough work to share at all
+  const bool wide = !serial && n * static_cast<long long>(F) >= 65536;      // enough work to share at all
+  // the workers stay awake while a shared tree grows, so even its small steps are worth handing out
+  std::unique_ptr<mimir_cpu::Pool::Awake> awake(wide ? new mimir_cpu::Pool::Awake(pool) : nullptr);
+  auto busy = [&](long long work) { return wide && work > 0; };
 
   auto gather = [&](long long lo, long long hi) {
     const long long chunk = 16384, count = (hi - lo + chunk - 1) / chunk;
-    for_each(pool, count, wide, [&](long long c) {
+    for_each(pool, count, busy(hi - lo), [&](long long c) {
       const long long a = lo + c * chunk, b = a + chunk < hi ? a + chunk : hi;
       for (long long k = a; k < b; ++k) { gh[2 * k] = g[idx[k]]; gh[2 * k + 1] = h[idx[k]]; }
     });
   };
-  // features 2 q and 2 q + 1 (the last pair of an odd count is one feature) of a node, cleared and counted
-  const int pairs = (F + 1) / 2;
+  // held features 2 q and 2 q + 1 (the last pair of an odd count is one feature) of a node, cleared and counted
+  const int pairs = (held + 1) / 2;
   auto count_pair = [&](Grow& nd, int q) {
-    const int f = 2 * q;
-    const bool two = f + 1 < F;
-    Cell* c = nd.hist.data() + static_cast<size_t>(f) * nbins;
+    const int j = 2 * q;
+    const bool two = j + 1 < held;
+    const int f = direct ? nd.feats[j] : j, f2 = !two ? 0 : direct ? nd.feats[j + 1] : j + 1;
+    Cell* c = nd.hist.data() + static_cast<size_t>(j) * nbins;
     memset(static_cast<void*>(c), 0, sizeof(Cell) * nbins * (two ? 2 : 1));
-    count_cells(bins + static_cast<size_t>(f) * total, two ? bins + static_cast<size_t>(f + 1) * total : nullptr, idx, gh.data(), nd.lo,
+    count_cells(bins + static_cast<size_t>(f) * total, two ? bins + static_cast<size_t>(f2) * total : nullptr, idx, gh.data(), nd.lo,
                 nd.hi, c, c + nbins);
   };
 
@@ -212,41 +236,33 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
   all[0].lo = 0;
   all[0].hi = n;
   all[0].hist.make(cells);
+  if (direct) draw(all[0]);
   gather(0, n);
-  for_each(pool, pairs, wide, [&](long long q) { count_pair(all[0], static_cast<int>(q)); });
+  for_each(pool, pairs, busy(n * held), [&](long long q) { count_pair(all[0], static_cast<int>(q)); });
   {
     double G = 0, H = 0;
-    for (int b = 0; b < nbins; ++b) { G += all[0].hist[b].g; H += all[0].hist[b].h; }      // every row falls in some bin of feature 0
+    for (int b = 0; b < nbins; ++b) { G += all[0].hist[b].g; H += all[0].hist[b].h; }      // every row falls in some bin of the first held feature
     all[0].G = G;
     all[0].H = H;
   }
   std::vector<int> level{0}, next_level;
   while (!level.empty()) {
     // (1) the best split of every node of the level that may split
-    for_each(pool, static_cast<long long>(level.size()), wide && level.size() >= 4, [&](long long li) {
+    for_each(pool, static_cast<long long>(level.size()), level.size() >= 4 && busy(static_cast<long long>(level.size()) * held * nbins / 4), [&](long long li) {
       Grow& nd = all[level[li]];
       const long long cnt = nd.hi - nd.lo;
       if (nd.hist.empty() || nd.depth >= max_depth || cnt < 2 * min_leaf) return;
-      std::vector<int> feats(F);
-      int nf = F;
-      for (int f = 0; f < F; ++f) feats[f] = f;
-      if (colsample_k > 0 && colsample_k < F) {
-        uint64_t rng = mix(seed ^ (nd.path * 0x9E3779B97F4A7C15ull));
-        for (int k = 0; k < colsample_k; ++k) {
-          rng = mix(rng + 0x9E3779B97F4A7C15ull);
-          const int j = k + static_cast<int>(rng % static_cast<uint64_t>(F - k));
-          const int t = feats[k]; feats[k] = feats[j]; feats[j] = t;
-        }
-        nf = colsample_k;
-      }
+      if (sampled && !direct) draw(nd);
+      const int nf = sampled ? colsample_k : F;
       const double parent_score = nd.G * nd.G / (nd.H + l2);
       double best_gain = -1, best_GL = 0, best_HL = 0, best_CL = 0;
       int best_f = -1, best_b = 0;
       for (int q = 0; q < nf; ++q) {
-        const int f = feats[q];
-        const Cell* hc = nd.hist.data() + static_cast<size_t>(f) * nbins;
+        const int f = sampled ? nd.feats[q] : q;
+        const Cell* hc = nd.hist.data() + static_cast<size_t>(direct ? q : f) * nbins;
         double GL = 0, HL = 0, CL = 0;
         for (int b = 0; b < nbins; ++b) {
+          if (hc[b].c == 0) continue;          // no row here: the same cut as the bin before
           GL += hc[b].g; HL += hc[b].h; CL += hc[b].c;
           const double CR = static_cast<double>(cnt) - CL;
           if (CL < static_cast<double>(min_leaf) || CR < static_cast<double>(min_leaf)) continue;
@@ -292,7 +308,9 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
     // (2) the rows of each splitting node: left rows first, both sides in their old order.  Few, large nodes are
     // cut into chunks (counted, then written at the places the counts before them give); many nodes go one per task.
     const long long parents = static_cast<long long>(next_level.size());
-    const int workers = pool.size();
+    const int workers = serial ? 1 : pool.size();
+    long long level_rows = 0;
+    for (int id : next_level) level_rows += all[id].hi - all[id].lo;
     auto split_rows = [&](Grow& nd) {
       const uint8_t* col = bins + static_cast<size_t>(nd.feature) * total;
       long long nl = 0, nr = 0;
@@ -310,7 +328,9 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
       std::vector<int> small_ones;
       for (int id : next_level)
         if (all[id].hi - all[id].lo < 32768) small_ones.push_back(id);
-      for_each(pool, static_cast<long long>(small_ones.size()), true, [&](long long i) { split_rows(all[small_ones[i]]); });
+      long long small_rows = 0;
+      for (int id : small_ones) small_rows += all[id].hi - all[id].lo;
+      for_each(pool, static_cast<long long>(small_ones.size()), busy(small_rows), [&](long long i) { split_rows(all[small_ones[i]]); });
       for (int id : next_level) {
         Grow& nd = all[id];
         const uint8_t* col = bins + static_cast<size_t>(nd.feature) * total;
@@ -342,7 +362,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
         });
       }
     } else {
-      for_each(pool, parents, wide, [&](long long pi) { split_rows(all[next_level[pi]]); });
+      for_each(pool, parents, busy(level_rows), [&](long long pi) { split_rows(all[next_level[pi]]); });
     }
     // children that may split again need histograms: the smaller one is counted, the larger one is the
     // parent's minus it
@@ -354,6 +374,18 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
       children.push_back(nd.right);
       if (nd.depth + 1 >= max_depth) { nd.hist.release(); continue; }     // the children are leaves: sums are given
       Grow &l = all[nd.left], &r = all[nd.right];
+      if (direct) {
+        nd.hist.release();
+        for (int child : {nd.left, nd.right}) {
+          Grow& ch = all[child];
+          if (ch.hi - ch.lo < 2 * min_leaf || ch.hi - ch.lo < 2) continue;      // it cannot split: no histogram
+          ch.hist.make(cells);
+          ch.counted = true;
+          draw(ch);
+          counted.push_back(child);
+        }
+        continue;
+      }
       Grow& small = (l.hi - l.lo) <= (r.hi - r.lo) ? l : r;
       small.hist.make(cells);
       small.counted = true;
@@ -362,19 +394,22 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
     }
     if (!counted.empty()) {
       // (3) gradients in row order for the rows that will be counted: chunks of every counted child, one run
+      long long counted_rows = 0;
       {
         std::vector<std::pair<long long, long long>> pieces;
-        for (int c : counted)
+        for (int c : counted) {
+          counted_rows += all[c].hi - all[c].lo;
           for (long long a = all[c].lo; a < all[c].hi; a += 16384) pieces.emplace_back(a, a + 16384 < all[c].hi ? a + 16384 : all[c].hi);
-        for_each(pool, static_cast<long long>(pieces.size()), wide, [&](long long i) {
+        }
+        for_each(pool, static_cast<long long>(pieces.size()), busy(counted_rows), [&](long long i) {
           for (long long k = pieces[i].first; k < pieces[i].second; ++k) { gh[2 * k] = g[idx[k]]; gh[2 * k + 1] = h[idx[k]]; }
         });
       }
       // (4) one (child, feature pair) pass per task
       const long long tasks = static_cast<long long>(counted.size()) * pairs;
-      for_each(pool, tasks, wide, [&](long long t) { count_pair(all[counted[t / pairs]], static_cast<int>(t % pairs)); });
+      for_each(pool, tasks, busy(counted_rows * held), [&](long long t) { count_pair(all[counted[t / pairs]], static_cast<int>(t % pairs)); });
       // (5) the sibling takes what is left of the parent's histogram
-      for_each(pool, static_cast<long long>(counted.size()), wide && counted.size() >= 4, [&](long long i) {
+      for_each(pool, static_cast<long long>(parents_of.size()), parents_of.size() >= 4 && busy(static_cast<long long>(parents_of.size() * cells)), [&](long long i) {
         Grow& parent = all[parents_of[i]];
         Grow& small = all[counted[i]];
         Grow& big = all[counted[i] == parent.left ? parent.right : parent.left];
@@ -407,7 +442,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
     ++n_nodes;
   }
   // every row's answer: the leaves share the workers (a row belongs to one leaf, so no two tasks write one place)
-  for_each(pool, static_cast<long long>(leaves.size()), wide, [&](long long i) {
+  for_each(pool, static_cast<long long>(leaves.size()), busy(n), [&](long long i) {
     const Grow& nd = all[leaves[i]];
     const float v = static_cast<float>(-nd.G / (nd.H + l2));
     for (long long k = nd.lo; k < nd.hi; ++k) leaf_out[idx[k]] = v;
@@ -434,6 +469,36 @@ MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long 
   return cnt;
 }
 
+// A forest: `trees` trees, each grown on its own list of rows (rows int64 [trees][n], numbers in [0, total),
+// repeats allowed: bootstrap samples) with the gradients g, h [total] shared by all.  The trees share the workers,
+// one whole tree per task, each grown serially: small nodes deep in a tree have too little work to split among
+// threads, whole trees do.  seeds [trees]: the feature-draw seed of each tree.  nodes: double
+// [trees][max_nodes][5]; counts: int [trees]; importance: double [trees][F] (zeroed here).  Returns 0 or -1.
+MIMIR_CPU_API int mimir_cpu_grow_forest(const uint8_t* colbins, long long total, int F, const int64_t* rows, long long n, int trees,
+                                        const float* g, const float* h, int nbins, int max_depth, long long min_leaf, double min_gain,
+                                        double l2, int colsample_k, const unsigned long long* seeds, double* nodes, int max_nodes,
+                                        int* counts, double* importance) {
+  if (total < 1 || total > INT32_MAX || n < 1 || trees < 0) return -1;
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  std::atomic<int> bad{0};
+  for_each(pool, trees, trees > 1, [&](long long t) {
+    std::vector<int32_t> idx(n);
+    const int64_t* mine = rows + static_cast<size_t>(t) * n;
+    for (long long k = 0; k < n; ++k) {
+      if (mine[k] < 0 || mine[k] >= total) { bad.store(1); return; }
+      idx[k] = static_cast<int32_t>(mine[k]);
+    }
+    double* imp = importance + static_cast<size_t>(t) * F;
+    for (int f = 0; f < F; ++f) imp[f] = 0;
+    const int cnt = grow_tree(pool, colbins, total, F, idx.data(), n, g, h, nbins, max_depth, min_leaf, min_gain, l2, colsample_k,
+                              seeds ? seeds[t] : 0ull, nodes + static_cast<size_t>(t) * max_nodes * 5, max_nodes, imp, nullptr, true);
+    if (cnt <= 0) { bad.store(1); return; }
+    counts[t] = cnt;
+  });
+  return bad.load() ? -1 : 0;
+}
+
 // `rounds` rounds of second-order boosting over all rows, without returning to the caller between trees: the
 // workers stay awake from one tree to the next, and a round's gradients and score update are two passes here
 // instead of a dozen tensor operations.  kind 0: squared error (g = score - y, h = 1); kind 1: logistic
@@ -447,6 +512,7 @@ MIMIR_CPU_API int mimir_cpu_boost(const uint8_t* colbins, long long total, int F
   if (total < 1 || total > INT32_MAX || rounds < 0 || (kind != 0 && kind != 1)) return -1;
   std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
   mimir_cpu::Pool& pool = mimir_cpu::pool();
+  mimir_cpu::Pool::Awake awake(pool);
   std::vector<float> g(total), h(total), leaf(total);
   std::vector<int32_t> idx(total);
   const long long chunk = 8192, chunks = (total + chunk - 1) / chunk;

@@ -32,6 +32,18 @@ class Pool {
     for (auto& t : workers_) t.join();
   }
   int size() const { return static_cast<int>(workers_.size()) + 1; }
+  // While one of these lives the workers do not go to sleep between jobs: for a native routine that hands the
+  // pool many short jobs with short serial steps between them (a tree, a boosting loop), where a sleeping
+  // worker would miss most of the jobs.  Only for the length of one native call: the workers spin meanwhile.
+  class Awake {
+   public:
+    explicit Awake(Pool& p) : p_(p) { p_.awake_.fetch_add(1, std::memory_order_relaxed); }
+    ~Awake() { p_.awake_.fetch_sub(1, std::memory_order_relaxed); }
+    Awake(const Awake&) = delete;
+    Awake& operator=(const Awake&) = delete;
+   private:
+    Pool& p_;
+  };
   // Runs fn(part, parts) on the caller and on whichever workers turn up before the caller has finished: for
   // jobs whose pieces are handed out from a shared counter, so that any subset of the threads completes
   // them.  Unlike run() it never waits for a sleeping worker to wake: on a busy or virtual machine that wait
@@ -83,7 +95,7 @@ class Pool {
     for (;;) {
       int spins = 0;
       while (epoch_.load(std::memory_order_acquire) == seen && !quit_.load(std::memory_order_relaxed)) {
-        if (++spins < 1500) { _mm_pause(); continue; }
+        if (++spins < 1500 || awake_.load(std::memory_order_relaxed) > 0) { _mm_pause(); continue; }
         std::unique_lock<std::mutex> lk(m_);
         sleepers_.fetch_add(1, std::memory_order_release);
         cv_.wait(lk, [&] { return quit_.load() || epoch_.load(std::memory_order_acquire) != seen; });
@@ -110,6 +122,7 @@ class Pool {
   std::atomic<int> pending_{0};
   std::atomic<int> sleepers_{0};
   std::atomic<int> active_{0};
+  std::atomic<int> awake_{0};
   std::atomic<uint64_t> closed_{0};
   std::atomic<uint64_t> epoch_{0};
   std::atomic<bool> quit_{false};

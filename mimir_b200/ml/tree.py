@@ -451,14 +451,62 @@ def decision_tree(X, y, max_depth=8, min_leaf=1, classes=0, **kw) -> Model:
                              classes=classes, **kw)
 
 
-def random_forest(X, y, trees=100, max_depth=10, min_leaf=1, colsample=None, bootstrap=True, classes=0, seed=0, bins=255) -> Model:
-    """Bagged trees on bootstrap samples with per-node feature sampling; averages the trees."""
+def _forest_native(B, rows, g, h, seeds, max_depth, min_leaf, bins, colsample, gen):
+    """One tree per row of ``rows [trees, n]`` (row numbers of ``B``, repeats allowed), grown side by side."""
+    import ctypes
+    from .. import _native
+    lib = _native.lib()
+    if not getattr(lib, "_forest_bound", False):
+        c = ctypes
+        lib.mimir_cpu_grow_forest.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int,
+                                              c.c_int, c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p,
+                                              c.c_void_p]
+        lib._forest_bound = True
+    total, F = B.shape
+    count, n = rows.shape
+    k = max(1, int(F * colsample)) if colsample < 1.0 else 0
+    max_nodes = int(min(2 ** (max_depth + 1) - 1, 2 * n + 1))
+    nodes = torch.empty(count, max_nodes, 5, dtype=torch.float64)
+    counts = torch.zeros(count, dtype=torch.int32)
+    imp = torch.empty(count, F, dtype=torch.float64)
+    rows = rows.to(torch.int64).contiguous()
+    seed_t = torch.tensor(seeds, dtype=torch.int64)
+    cols = _columns(B)
+    rc = lib.mimir_cpu_grow_forest(cols.data_ptr(), total, F, rows.data_ptr(), n, count, g.data_ptr(), h.data_ptr(), bins, max_depth,
+                                   max(int(min_leaf), 1) if min_leaf >= 1 else 0, 0.0, 0.0, k, seed_t.data_ptr(), nodes.data_ptr(), max_nodes,
+                                   counts.data_ptr(), imp.data_ptr())
+    if rc != 0:
+        raise RuntimeError("forest: the native grower refused its arguments")
+    out = []
+    for r in range(count):
+        t = _Tree(max_depth, min_leaf, 0.0, 0.0, bins, colsample, gen)
+        t.nodes = [[int(q[0]), int(q[1]), int(q[2]), int(q[3]), float(q[4])] for q in nodes[r, : int(counts[r])].tolist()]
+        t.importance = imp[r].float()
+        t.answers = None
+        out.append(t)
+    return out
+
+
+def random_forest(X, y, trees=100, max_depth=10, min_leaf=1, colsample=None, bootstrap=True, classes=0, seed=0, bins=255,
+                  native_trees=True) -> Model:
+    """Bagged trees on bootstrap samples with per-node feature sampling; averages the trees.  On the host the
+    trees grow side by side in native code; ``native_trees=False`` grows them one by one (the same trees)."""
     X, y = torch.as_tensor(X).float(), torch.as_tensor(y).float()
     gen = torch.Generator().manual_seed(seed)
     B, edges = _bin(X, bins)
     n, F = X.shape
     colsample = colsample or (math.sqrt(F) / F if classes else 1.0 / 3 if F >= 3 else 1.0)
     out = []
+    if native_trees and B.dtype == torch.uint8 and B.device.type == "cpu" and bins <= 256:
+        # the trees of a chunk grow side by side in native code, one whole tree per worker (``mimir_cpu_grow_forest``)
+        g, h = (-y).contiguous(), torch.ones(n)
+        for t0 in range(0, trees, 32):
+            rows, seeds = [], []
+            for _ in range(min(32, trees - t0)):         # the draws in the order the per-tree loop makes them
+                rows.append(torch.randint(0, n, (n,), generator=gen) if bootstrap else torch.arange(n))
+                seeds.append(int(torch.randint(0, 2 ** 62, (1,), generator=gen)) if colsample < 1.0 else 0)
+            out += _forest_native(B, torch.stack(rows), g, h, seeds, max_depth, min_leaf, bins, colsample, gen)
+        trees = 0
     for _ in range(trees):
         rows = torch.randint(0, n, (n,), generator=gen) if bootstrap else torch.arange(n)
         t = _Tree(max_depth, min_leaf, 0.0, 0.0, bins, colsample, gen).fit(B[rows], -y[rows], torch.ones(n))

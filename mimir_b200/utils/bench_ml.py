@@ -79,6 +79,10 @@ def main(argv=None):
                      lambda m: acc(m.classify(X[half:]), y_cls[half:]),
                      lambda: sk.ensemble.HistGradientBoostingClassifier(max_iter=50, max_depth=6, early_stopping=False).fit(Xn[:half], ycn[:half]),
                      lambda m: float(m.score(Xn[half:], ycn[half:]))),
+        "forest": (lambda: tree.random_forest(X[:half], y_cls[:half], trees=50, max_depth=10, classes=2),
+                   lambda m: acc((m.raw(X[half:]) > 0.5).long(), y_cls[half:]),
+                   lambda: sk.ensemble.RandomForestClassifier(50, max_depth=10, n_jobs=-1).fit(Xn[:half], ycn[:half]),
+                   lambda m: float(m.score(Xn[half:], ycn[half:]))),
         "kmeans": (lambda: cluster.kmeans_fit(blobs, 8, inits=4), lambda m: m.inertia / a.rows,
                    lambda: sk.cluster.KMeans(8, n_init=4, random_state=0).fit(sklearn.preprocessing.scale(bn)), lambda m: float(m.inertia_) / a.rows),
         "knn_predict": (lambda: neighbors.fit(d_cls, "classification").classify(X[half:half + 2000]), lambda p: acc(p, y_cls[half:half + 2000]),

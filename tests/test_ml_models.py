@@ -433,3 +433,20 @@ def test_native_binning_and_ensemble_prediction_agree_with_the_tensor_ops():
     lib_answer = tree.Model._sum_of(m.trees, Bm)                        # falls back to the walks with a step limit
     assert torch.isfinite(lib_answer).all()
     t0.nodes = good
+
+
+def test_forest_trees_grown_side_by_side_are_the_trees_grown_one_by_one():
+    """A forest's trees grow in one native call, whole trees sharing the workers; growing them one at a time
+    from the same generator gives the same trees, with and without bootstrap samples."""
+    from mimir_b200.ml import tree
+    g = torch.Generator().manual_seed(2)
+    X = torch.randn(3000, 9, generator=g)
+    y = X[:, 0] * X[:, 1] + X[:, 2]
+    for kw in (dict(), dict(bootstrap=False), dict(colsample=0.8), dict(classes=2)):
+        yy = (y > 0).float() if kw.get("classes") else y
+        a = tree.random_forest(X, yy, trees=7, max_depth=6, seed=4, **kw)
+        b = tree.random_forest(X, yy, trees=7, max_depth=6, seed=4, native_trees=False, **kw)
+        assert [t.nodes for t in a.trees] == [t.nodes for t in b.trees], kw
+        assert torch.allclose(a.importance(), b.importance(), atol=1e-6)
+    r2 = 1 - ((a.raw(X) - yy) ** 2).sum() / ((yy - yy.mean()) ** 2).sum()
+    assert float(r2) > 0.5
