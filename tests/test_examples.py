@@ -46,3 +46,10 @@ def test_export_run_example():
     err, avg = export_run.main(log=quiet)
     assert err < 1e-5
     assert abs(avg[0].item() - (1 - 0.9 ** 3)) < 1e-6
+
+
+def test_tabular_example():
+    import tabular
+    a_boost, a_lin, a_auto, agree, err = tabular.main(rows=1500, budget=10.0, log=quiet)
+    assert a_boost > 0.85 > a_lin            # the answer is an interaction of two features
+    assert a_auto > 0.85 and agree > 0.98 and err < 1e-4
