@@ -184,22 +184,32 @@ void for_each(mimir_cpu::Pool& pool, long long count, bool parallel, const Fn& f
 // trees may grow at once, one per worker (a forest).
 static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total, int F, int32_t* idx, long long n, const float* g,
                      const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
-                     unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out, bool serial = false) {
+                     unsigned long long seed, double* nodes, int max_nodes, double* importance, float* leaf_out, bool serial,
+                     double min_weight, const int32_t* allowed, int n_allowed) {
   if (F < 1 || nbins < 1 || nbins > 256 || n < 1 || max_nodes < 1 || max_depth < 0) return -1;
+  // `allowed` (ascending feature numbers, or null for all) is what this tree may split on: below, features are
+  // counted, drawn and compared by their place u in that list, and feat(u) is the feature itself
+  if (allowed) {
+    if (n_allowed < 1) return -1;
+    for (int u = 0; u < n_allowed; ++u)
+      if (allowed[u] < 0 || allowed[u] >= F || (u > 0 && allowed[u] <= allowed[u - 1])) return -1;
+  }
+  const int Fu = allowed ? n_allowed : F;
+  auto feat = [&](int u) { return allowed ? static_cast<int>(allowed[u]) : u; };
   // With few features drawn per node (at most half of them, as forests do) a node counts the features it drew
   // and nothing else, and both children are counted: cheaper than counting every feature for the smaller child
   // and subtracting whole histograms, which small nodes deep in a tree cannot pay for.
-  const bool sampled = colsample_k > 0 && colsample_k < F;
-  const bool direct = sampled && colsample_k * 2 <= F;
-  const int held = direct ? colsample_k : F;                       // features a node's histogram holds
+  const bool sampled = colsample_k > 0 && colsample_k < Fu;
+  const bool direct = sampled && colsample_k * 2 <= Fu;
+  const int held = direct ? colsample_k : Fu;                      // features a node's histogram holds
   const size_t cells = static_cast<size_t>(held) * nbins;
   auto draw = [&](Grow& nd) {
-    nd.feats.resize(F);
-    for (int f = 0; f < F; ++f) nd.feats[f] = f;
+    nd.feats.resize(Fu);
+    for (int f = 0; f < Fu; ++f) nd.feats[f] = f;
     uint64_t rng = mix(seed ^ (nd.path * 0x9E3779B97F4A7C15ull));
     for (int k = 0; k < colsample_k; ++k) {
       rng = mix(rng + 0x9E3779B97F4A7C15ull);
-      const int j = k + static_cast<int>(rng % static_cast<uint64_t>(F - k));
+      const int j = k + static_cast<int>(rng % static_cast<uint64_t>(Fu - k));
       const int t = nd.feats[k]; nd.feats[k] = nd.feats[j]; nd.feats[j] = t;
     }
     nd.feats.resize(colsample_k);
@@ -208,7 +218,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
   all.reserve(static_cast<size_t>(max_nodes < 4096 ? max_nodes : 4096));
   std::vector<float> gh(2 * static_cast<size_t>(n));       // (gradient, hessian) of the rows in the order of idx
   std::vector<int32_t> scratch(n);
-  const bool wide = !serial && n * static_cast<long long>(F) >= 65536;      // enough work to share at all
+  const bool wide = !serial && n * static_cast<long long>(Fu) >= 65536;      // enough work to share at all
   // the workers stay awake while a shared tree grows, so even its small steps are worth handing out
   std::unique_ptr<mimir_cpu::Pool::Awake> awake(wide ? new mimir_cpu::Pool::Awake(pool) : nullptr);
   auto busy = [&](long long work) { return wide && work > 0; };
@@ -225,7 +235,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
   auto count_pair = [&](Grow& nd, int q) {
     const int j = 2 * q;
     const bool two = j + 1 < held;
-    const int f = direct ? nd.feats[j] : j, f2 = !two ? 0 : direct ? nd.feats[j + 1] : j + 1;
+    const int f = feat(direct ? nd.feats[j] : j), f2 = !two ? 0 : feat(direct ? nd.feats[j + 1] : j + 1);
     Cell* c = nd.hist.data() + static_cast<size_t>(j) * nbins;
     memset(static_cast<void*>(c), 0, sizeof(Cell) * nbins * (two ? 2 : 1));
     count_cells(bins + static_cast<size_t>(f) * total, two ? bins + static_cast<size_t>(f2) * total : nullptr, idx, gh.data(), nd.lo,
@@ -253,7 +263,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
       const long long cnt = nd.hi - nd.lo;
       if (nd.hist.empty() || nd.depth >= max_depth || cnt < 2 * min_leaf) return;
       if (sampled && !direct) draw(nd);
-      const int nf = sampled ? colsample_k : F;
+      const int nf = sampled ? colsample_k : Fu;
       const double parent_score = nd.G * nd.G / (nd.H + l2);
       double best_gain = -1, best_GL = 0, best_HL = 0, best_CL = 0;
       int best_f = -1, best_b = 0;
@@ -267,6 +277,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
           const double CR = static_cast<double>(cnt) - CL;
           if (CL < static_cast<double>(min_leaf) || CR < static_cast<double>(min_leaf)) continue;
           const double GR = nd.G - GL, HR = nd.H - HL;
+          if (HL < min_weight || HR < min_weight) continue;
           const double gain = GL * GL / (HL + l2) + GR * GR / (HR + l2) - parent_score;
           if (gain > best_gain || (gain == best_gain && best_f >= 0 && f < best_f)) {
             best_gain = gain; best_f = f; best_b = b; best_GL = GL; best_HL = HL; best_CL = CL;
@@ -274,7 +285,7 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
         }
       }
       if (best_f < 0 || !(best_gain > min_gain)) return;
-      nd.feature = best_f;
+      nd.feature = feat(best_f);
       nd.bin = best_b;
       nd.gain = best_gain;
       nd.GL = best_GL;
@@ -452,10 +463,13 @@ static int grow_tree(mimir_cpu::Pool& pool, const uint8_t* bins, long long total
 
 // bins: one COLUMN per feature, uint8 [F][total]; idx [n] holds row numbers in [0, total).
 // leaf_out (float [total], may be null) receives the value of the leaf each grown-on row reached.
+// min_weight: the smallest sum of hessians a child may hold; allowed [n_allowed]: the features (ascending) the
+// tree may split on, or null for all.
 MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long total, int F, int64_t* idx, long long n, const float* g,
                                               const float* h, int nbins, int max_depth, long long min_leaf, double min_gain, double l2,
                                               int colsample_k, unsigned long long seed, double* nodes, int max_nodes,
-                                              double* importance, float* leaf_out) {
+                                              double* importance, float* leaf_out, double min_weight, const int32_t* allowed,
+                                              int n_allowed) {
   if (total < 1 || total > INT32_MAX || n < 1) return -1;
   std::vector<int32_t> rows(n);          // row numbers as 32-bit values: half the bytes every pass reads
   for (long long k = 0; k < n; ++k) {
@@ -464,7 +478,7 @@ MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long 
   }
   std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
   const int cnt = grow_tree(mimir_cpu::pool(), colbins, total, F, rows.data(), n, g, h, nbins, max_depth, min_leaf, min_gain, l2,
-                            colsample_k, seed, nodes, max_nodes, importance, leaf_out);
+                            colsample_k, seed, nodes, max_nodes, importance, leaf_out, false, min_weight, allowed, n_allowed);
   for (long long k = 0; k < n; ++k) idx[k] = rows[k];
   return cnt;
 }
@@ -473,11 +487,12 @@ MIMIR_CPU_API int mimir_cpu_grow_tree_answers(const uint8_t* colbins, long long 
 // repeats allowed: bootstrap samples) with the gradients g, h [total] shared by all.  The trees share the workers,
 // one whole tree per task, each grown serially: small nodes deep in a tree have too little work to split among
 // threads, whole trees do.  seeds [trees]: the feature-draw seed of each tree.  nodes: double
-// [trees][max_nodes][5]; counts: int [trees]; importance: double [trees][F] (zeroed here).  Returns 0 or -1.
+// [trees][max_nodes][5]; counts: int [trees]; importance: double [trees][F] (zeroed here).  min_weight, allowed
+// [trees][n_allowed]: as in mimir_cpu_boost.  Returns 0 or -1.
 MIMIR_CPU_API int mimir_cpu_grow_forest(const uint8_t* colbins, long long total, int F, const int64_t* rows, long long n, int trees,
                                         const float* g, const float* h, int nbins, int max_depth, long long min_leaf, double min_gain,
                                         double l2, int colsample_k, const unsigned long long* seeds, double* nodes, int max_nodes,
-                                        int* counts, double* importance) {
+                                        int* counts, double* importance, double min_weight, const int32_t* allowed, int n_allowed) {
   if (total < 1 || total > INT32_MAX || n < 1 || trees < 0) return -1;
   std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
   mimir_cpu::Pool& pool = mimir_cpu::pool();
@@ -492,7 +507,8 @@ MIMIR_CPU_API int mimir_cpu_grow_forest(const uint8_t* colbins, long long total,
     double* imp = importance + static_cast<size_t>(t) * F;
     for (int f = 0; f < F; ++f) imp[f] = 0;
     const int cnt = grow_tree(pool, colbins, total, F, idx.data(), n, g, h, nbins, max_depth, min_leaf, min_gain, l2, colsample_k,
-                              seeds ? seeds[t] : 0ull, nodes + static_cast<size_t>(t) * max_nodes * 5, max_nodes, imp, nullptr, true);
+                              seeds ? seeds[t] : 0ull, nodes + static_cast<size_t>(t) * max_nodes * 5, max_nodes, imp, nullptr, true,
+                              min_weight, allowed ? allowed + static_cast<size_t>(t) * n_allowed : nullptr, n_allowed);
     if (cnt <= 0) { bad.store(1); return; }
     counts[t] = cnt;
   });
@@ -505,10 +521,12 @@ MIMIR_CPU_API int mimir_cpu_grow_forest(const uint8_t* colbins, long long total,
 // (p = sigmoid(score), g = p - y, h = max(p (1 - p), 1e-6)).  score [total] (float) is updated in place by
 // lr * (the leaf each row reached).  seeds [rounds]: the feature-draw seed of each tree (read when colsample_k > 0).
 // nodes: double [rounds][max_nodes][5]; counts: int [rounds]; importance: double [rounds][F] (zeroed here).
-// Returns the number of rounds done (all of them), or -1.
+// min_weight: the smallest sum of hessians a child may hold; allowed: int32 [rounds][n_allowed], the features
+// (ascending) each round's tree may split on, or null for all.  Returns the number of rounds done (all), or -1.
 MIMIR_CPU_API int mimir_cpu_boost(const uint8_t* colbins, long long total, int F, const float* y, float* score, int kind, int rounds,
                                   double lr, int nbins, int max_depth, long long min_leaf, double min_gain, double l2, int colsample_k,
-                                  const unsigned long long* seeds, double* nodes, int max_nodes, int* counts, double* importance) {
+                                  const unsigned long long* seeds, double* nodes, int max_nodes, int* counts, double* importance,
+                                  double min_weight, const int32_t* allowed, int n_allowed) {
   if (total < 1 || total > INT32_MAX || rounds < 0 || (kind != 0 && kind != 1)) return -1;
   std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
   mimir_cpu::Pool& pool = mimir_cpu::pool();
@@ -537,7 +555,7 @@ MIMIR_CPU_API int mimir_cpu_boost(const uint8_t* colbins, long long total, int F
     for (int f = 0; f < F; ++f) imp[f] = 0;
     const int cnt = grow_tree(pool, colbins, total, F, idx.data(), total, g.data(), h.data(), nbins, max_depth, min_leaf, min_gain, l2,
                               colsample_k, seeds ? seeds[r] : 0ull, nodes + static_cast<size_t>(r) * max_nodes * 5, max_nodes, imp,
-                              leaf.data());
+                              leaf.data(), false, min_weight, allowed ? allowed + static_cast<size_t>(r) * n_allowed : nullptr, n_allowed);
     if (cnt <= 0) return -1;
     counts[r] = cnt;
     for_each(pool, chunks, wide, [&](long long c) {

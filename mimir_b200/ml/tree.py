@@ -95,9 +95,13 @@ def _histogram(B, idx, g, h, bins):
 class _Tree:
     """Regression tree on gradients/hessians (second-order gain with L2)."""
 
-    def __init__(self, max_depth=6, min_leaf=1, min_gain=0.0, l2=1.0, bins=255, colsample=1.0, gen=None):
+    def __init__(self, max_depth=6, min_leaf=1, min_gain=0.0, l2=1.0, bins=255, colsample=1.0, gen=None, min_weight=0.0, allowed=None):
+        """``colsample``: the share of the features drawn afresh at every node; ``allowed``: the features (ascending
+        numbers) this tree may split on at all, None for every one; ``min_weight``: the smallest sum of hessians a
+        child may hold."""
         self.max_depth, self.min_leaf, self.min_gain, self.l2, self.bins = max_depth, min_leaf, min_gain, l2, bins
-        self.colsample, self.gen = colsample, gen
+        self.colsample, self.gen, self.min_weight = colsample, gen, float(min_weight)
+        self.allowed = None if allowed is None else torch.as_tensor(allowed, dtype=torch.int32).contiguous()
         self.nodes = []  # (feature, bin, left, right, value)
         self.importance = None
 
@@ -127,14 +131,15 @@ class _Tree:
             c = ctypes
             lib.mimir_cpu_grow_tree_answers.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_longlong, c.c_void_p, c.c_void_p, c.c_int, c.c_int,
                                                         c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_ulonglong, c.c_void_p, c.c_int,
-                                                        c.c_void_p, c.c_void_p]
+                                                        c.c_void_p, c.c_void_p, c.c_double, c.c_void_p, c.c_int]
             lib._tree_bound = True
         total, F = B.shape
         n = total if rows is None else int(rows.numel())
         k = 0
         seed = 0
+        universe = F if self.allowed is None else int(self.allowed.numel())
         if self.colsample < 1.0:
-            k = max(1, int(F * self.colsample))
+            k = max(1, int(universe * self.colsample))
             seed = int(torch.randint(0, 2 ** 62, (1,), generator=self.gen))
         max_nodes = int(min(2 ** (self.max_depth + 1) - 1, 2 * n + 1))
         nodes = torch.empty(max_nodes, 5, dtype=torch.float64)
@@ -145,7 +150,8 @@ class _Tree:
         cnt = lib.mimir_cpu_grow_tree_answers(cols.data_ptr(), total, F, idx.data_ptr(), n, g.data_ptr(), h.data_ptr(), self.bins, self.max_depth,
                                               max(int(self.min_leaf), 1) if self.min_leaf >= 1 else 0, float(self.min_gain), float(self.l2),
                                               k, seed, nodes.data_ptr(), max_nodes, imp.data_ptr(),
-                                              answers.data_ptr() if answers is not None else None)
+                                              answers.data_ptr() if answers is not None else None, self.min_weight,
+                                              self.allowed.data_ptr() if self.allowed is not None else None, universe)
         if cnt <= 0:
             return False
         self.answers = answers
@@ -165,11 +171,10 @@ class _Tree:
         self.nodes.append([-1, 0, -1, -1, float(-G / (H + self.l2))])
         if depth >= self.max_depth or idx.numel() < 2 * self.min_leaf:
             return node
-        F = B.shape[1]
-        feats = torch.arange(F)
+        feats = torch.arange(B.shape[1]) if self.allowed is None else self.allowed.long()
         if self.colsample < 1.0:
-            k = max(1, int(F * self.colsample))
-            feats = torch.randperm(F, generator=self.gen)[:k]
+            k = max(1, int(feats.numel() * self.colsample))
+            feats = feats[torch.randperm(feats.numel(), generator=self.gen)[:k]]
         if hist is None:
             hist = _histogram(B, idx, g, h, self.bins)
         sel = hist[:, feats].to(g.dtype if g.dtype == torch.float64 else torch.float32)
@@ -179,7 +184,7 @@ class _Tree:
         CL = hc.view(-1, self.bins).cumsum(1)
         GR, HR, CR = G - GL, H - HL, idx.numel() - CL
         gain = GL ** 2 / (HL + self.l2) + GR ** 2 / (HR + self.l2) - G ** 2 / (H + self.l2)
-        gain[(CL < self.min_leaf) | (CR < self.min_leaf)] = -1
+        gain[(CL < self.min_leaf) | (CR < self.min_leaf) | (HL < self.min_weight) | (HR < self.min_weight)] = -1
         best = int(gain.argmax())
         bg = float(gain.reshape(-1)[best])
         if bg <= self.min_gain:
@@ -323,7 +328,7 @@ class Model:
         return Model(trees, torch.tensor(d["edges"]), d["lr"], base, d["classes"], d["kind"])
 
 
-def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, l2, bins, colsample, gen):
+def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight=0.0, per_tree=1.0):
     """``rounds`` trees grown one after another by ``mimir_cpu_boost`` (``csrc/cpu_hist.cc``) on all rows of ``B``;
     ``score`` is updated in place.  Feature-draw seeds come from ``gen`` in the order the per-tree loop draws them."""
     import ctypes
@@ -332,13 +337,22 @@ def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, 
     if not getattr(lib, "_boost_bound", False):
         c = ctypes
         lib.mimir_cpu_boost.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_double, c.c_int, c.c_int,
-                                        c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p]
+                                        c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p,
+                                        c.c_double, c.c_void_p, c.c_int]
         lib._boost_bound = True
     total, F = B.shape
-    k, seeds = 0, None
-    if colsample < 1.0:
-        k = max(1, int(F * colsample))
-        seeds = torch.tensor([int(torch.randint(0, 2 ** 62, (1,), generator=gen)) for _ in range(rounds)], dtype=torch.int64)
+    k, seeds, allowed = 0, None, None
+    universe = F if per_tree >= 1.0 else max(1, int(F * per_tree))
+    if colsample < 1.0 or per_tree < 1.0:
+        # the draws of each round in the order the per-round loop makes them: the tree's features, then its seed
+        k = max(1, int(universe * colsample)) if colsample < 1.0 else 0
+        lists, seeds = [], []
+        for _ in range(rounds):
+            if per_tree < 1.0:
+                lists.append(_draw_features(F, per_tree, gen))
+            seeds.append(int(torch.randint(0, 2 ** 62, (1,), generator=gen)) if colsample < 1.0 else 0)
+        seeds = torch.tensor(seeds, dtype=torch.int64)
+        allowed = torch.stack(lists).contiguous() if lists else None
     max_nodes = int(min(2 ** (max_depth + 1) - 1, 2 * total + 1))
     nodes = torch.empty(rounds, max_nodes, 5, dtype=torch.float64)
     counts = torch.zeros(rounds, dtype=torch.int32)
@@ -347,12 +361,13 @@ def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, 
     y = y.float().contiguous()
     done = lib.mimir_cpu_boost(cols.data_ptr(), total, F, y.data_ptr(), score.data_ptr(), kind, rounds, float(lr), bins, max_depth,
                                max(int(min_leaf), 1) if min_leaf >= 1 else 0, float(min_gain), float(l2), k,
-                               seeds.data_ptr() if seeds is not None else None, nodes.data_ptr(), max_nodes, counts.data_ptr(), imp.data_ptr())
+                               seeds.data_ptr() if seeds is not None else None, nodes.data_ptr(), max_nodes, counts.data_ptr(), imp.data_ptr(),
+                               float(min_weight), allowed.data_ptr() if allowed is not None else None, universe)
     if done != rounds:
         raise RuntimeError("boosting: the native grower refused its arguments")
     out = []
     for r in range(rounds):
-        t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen)
+        t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, None if allowed is None else allowed[r])
         t.nodes = [[int(q[0]), int(q[1]), int(q[2]), int(q[3]), float(q[4])] for q in nodes[r, : int(counts[r])].tolist()]
         t.importance = imp[r].float()
         t.answers = None
@@ -360,11 +375,20 @@ def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, 
     return out
 
 
+def _draw_features(F, share, gen):
+    """The features one tree may split on: ``share`` of all, drawn without repeats, ascending (None: all)."""
+    if share >= 1.0:
+        return None
+    return torch.randperm(F, generator=gen)[: max(1, int(F * share))].sort().values.to(torch.int32).contiguous()
+
+
 def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=1, min_gain=0.0, l2=1.0, bins=255,
                       subsample=1.0, colsample=1.0, classes=0, seed=0, validation=None, patience=10, progress=None,
-                      native_rounds=True) -> Model:
+                      native_rounds=True, min_weight=0.0, per_tree=1.0) -> Model:
     """Second-order boosting: squared error (classes=0), logistic (2) or softmax (>2).  ``subsample`` draws
-    that share of the rows for each tree and ``colsample`` that share of the features for each node.
+    that share of the rows for each tree, ``per_tree`` that share of the features for each tree (tree/options.go:
+    ColSample) and ``colsample`` that share of a tree's features afresh at every node; ``min_weight`` is the
+    smallest sum of hessians a child may hold (XGBoost's min_child_weight; tree/options.go: MinWeight).
     ``validation`` (a table, or ``(X, y)``) is scored after every round (squared error or log loss): boosting
     stops once ``patience`` rounds in a row have not improved it, and the model keeps the best round's trees
     (tree/boost.go: Validation).  Without row sampling and validation, regression and two-class boosting run all
@@ -396,18 +420,19 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
         span = 10 if progress is not None else trees
         for it in range(0, trees, span):
             out_trees += _boost_native(B, yf, F, 0 if classes == 0 else 1, min(span, trees - it), learning_rate, max_depth, min_leaf,
-                                       min_gain, l2, bins, colsample, gen)
+                                       min_gain, l2, bins, colsample, gen, min_weight, per_tree)
             if progress is not None and len(out_trees) % 10 == 0:
                 progress.write(f"tree {len(out_trees)}/{trees}\n")
         trees = 0
     for it in range(trees):
         rows = None if subsample >= 1.0 else torch.randperm(n, generator=gen)[: max(1, int(n * subsample))]
+        allowed = _draw_features(X.shape[1], per_tree, gen)
         if classes > 2:
             p = torch.softmax(F, 1)
             round_trees = []
             for k in range(classes):
                 g, h = (p[:, k] - oh[:, k]), (p[:, k] * (1 - p[:, k])).clamp_min(1e-6)
-                t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B, g, h, rows)
+                t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, allowed).fit(B, g, h, rows)
                 F[:, k] += learning_rate * (t.answers if t.answers is not None else t.predict_binned(B))
                 if held is not None:
                     held["F"][:, k] += learning_rate * t.predict_binned(held["B"])
@@ -419,7 +444,7 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
                 g, h = p - yf, (p * (1 - p)).clamp_min(1e-6)
             else:
                 g, h = F - yf, torch.ones(n)
-            t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen).fit(B, g, h, rows)
+            t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, allowed).fit(B, g, h, rows)
             F += learning_rate * (t.answers if t.answers is not None else t.predict_binned(B))
             if held is not None:
                 held["F"] += learning_rate * t.predict_binned(held["B"])
@@ -460,7 +485,7 @@ def _forest_native(B, rows, g, h, seeds, max_depth, min_leaf, bins, colsample, g
         c = ctypes
         lib.mimir_cpu_grow_forest.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int,
                                               c.c_int, c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p,
-                                              c.c_void_p]
+                                              c.c_void_p, c.c_double, c.c_void_p, c.c_int]
         lib._forest_bound = True
     total, F = B.shape
     count, n = rows.shape
@@ -474,7 +499,7 @@ def _forest_native(B, rows, g, h, seeds, max_depth, min_leaf, bins, colsample, g
     cols = _columns(B)
     rc = lib.mimir_cpu_grow_forest(cols.data_ptr(), total, F, rows.data_ptr(), n, count, g.data_ptr(), h.data_ptr(), bins, max_depth,
                                    max(int(min_leaf), 1) if min_leaf >= 1 else 0, 0.0, 0.0, k, seed_t.data_ptr(), nodes.data_ptr(), max_nodes,
-                                   counts.data_ptr(), imp.data_ptr())
+                                   counts.data_ptr(), imp.data_ptr(), 0.0, None, 0)
     if rc != 0:
         raise RuntimeError("forest: the native grower refused its arguments")
     out = []
@@ -488,13 +513,19 @@ def _forest_native(B, rows, g, h, seeds, max_depth, min_leaf, bins, colsample, g
 
 
 def random_forest(X, y, trees=100, max_depth=10, min_leaf=1, colsample=None, bootstrap=True, classes=0, seed=0, bins=255,
-                  native_trees=True) -> Model:
-    """Bagged trees on bootstrap samples with per-node feature sampling; averages the trees.  On the host the
-    trees grow side by side in native code; ``native_trees=False`` grows them one by one (the same trees)."""
+                  native_trees=True, per_node=None) -> Model:
+    """Bagged trees on bootstrap samples with per-node feature sampling; averages the trees.  ``per_node``
+    features are drawn at each node (tree/options.go: PerNode), or the share ``colsample`` of them; by default the
+    square root of the features for classification and a third for regression.  On the host the trees grow side
+    by side in native code; ``native_trees=False`` grows them one by one (the same trees)."""
     X, y = torch.as_tensor(X).float(), torch.as_tensor(y).float()
     gen = torch.Generator().manual_seed(seed)
     B, edges = _bin(X, bins)
     n, F = X.shape
+    if per_node is not None:
+        if not 1 <= int(per_node) <= F:
+            raise ValueError(f"per_node {per_node} of {F} features")
+        colsample = (int(per_node) + 0.5) / F if per_node < F else 1.0
     colsample = colsample or (math.sqrt(F) / F if classes else 1.0 / 3 if F >= 3 else 1.0)
     out = []
     if native_trees and B.dtype == torch.uint8 and B.device.type == "cpu" and bins <= 256:
@@ -631,12 +662,32 @@ def _table(d, task, classes):
     return task, (count_classes(d.Y, classes) if task is CLASSIFICATION else 0)
 
 
+class _workers:
+    """``with _workers(n):`` the native tree code uses ``n`` threads inside (None: as many as it has now;
+    tree/options.go: Workers)."""
+
+    def __init__(self, n):
+        self.n, self.had = n, None
+
+    def __enter__(self):
+        if self.n is not None:
+            from ..ops import quant_cpu
+            self.had = quant_cpu.set_threads(int(self.n))
+
+    def __exit__(self, *exc):
+        if self.n is not None:
+            from ..ops import quant_cpu
+            quant_cpu.set_threads(self.had)
+
+
 def boosting(d, task, classes: int = 0, **options) -> Ensemble:
     """Gradient boosting on a table: squared error for regression, logistic loss for two classes, softmax for
     more.  Options are ``gradient_boosting``'s (``trees``, ``learning_rate``, ``max_depth``, ``min_leaf``,
-    ``min_gain``, ``l2``, ``subsample``, ``colsample``, ``bins``, ``seed``, ``validation`` with ``patience``)."""
+    ``min_gain``, ``min_weight``, ``l2``, ``subsample``, ``per_tree``, ``colsample``, ``bins``, ``seed``, ``validation``
+    with ``patience``), and ``workers``: the threads the native code uses."""
     task, k = _table(d, task, classes)
-    return Ensemble(task, k, [gradient_boosting(d.X, d.Y, classes=k, **options)], "boost")
+    with _workers(options.pop("workers", None)):
+        return Ensemble(task, k, [gradient_boosting(d.X, d.Y, classes=k, **options)], "boost")
 
 
 def forest(d, task, classes: int = 0, **options) -> Ensemble:
@@ -644,9 +695,10 @@ def forest(d, task, classes: int = 0, **options) -> Ensemble:
     averaged leaves are the class's probability."""
     task, k = _table(d, task, classes)
     seed = options.pop("seed", 0)
-    if not k:
-        return Ensemble(task, 0, [random_forest(d.X, d.Y, seed=seed, **options)], "forest")
-    return Ensemble(task, k, [random_forest(d.X, (d.Y == c).float(), seed=seed + c, **options) for c in range(k)], "forest")
+    with _workers(options.pop("workers", None)):
+        if not k:
+            return Ensemble(task, 0, [random_forest(d.X, d.Y, seed=seed, **options)], "forest")
+        return Ensemble(task, k, [random_forest(d.X, (d.Y == c).float(), seed=seed + c, **options) for c in range(k)], "forest")
 
 
 def single(d, task, classes: int = 0, **options) -> Ensemble:

@@ -450,3 +450,36 @@ def test_forest_trees_grown_side_by_side_are_the_trees_grown_one_by_one():
         assert torch.allclose(a.importance(), b.importance(), atol=1e-6)
     r2 = 1 - ((a.raw(X) - yy) ** 2).sum() / ((yy - yy.mean()) ** 2).sum()
     assert float(r2) > 0.5
+
+
+def test_tree_options_features_per_tree_features_per_node_smallest_child_weight_and_workers():
+    """The reference's options: a share of the features per boosted tree, a count of features per forest node,
+    the smallest hessian sum of a child, the number of threads (tree/options.go: ColSample, PerNode, MinWeight,
+    Workers).  The native rounds and the per-round loop agree under each."""
+    from mimir_b200.ml import tree
+    from mimir_b200.ops import quant_cpu
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(3000, 10, generator=g)
+    y = (X[:, 0] * X[:, 1] + X[:, 2] > 0).long()
+    for kw in (dict(per_tree=0.5), dict(per_tree=0.5, colsample=0.6), dict(min_weight=5.0)):
+        a = tree.gradient_boosting(X, y, trees=8, max_depth=4, classes=2, seed=1, **kw)
+        b = tree.gradient_boosting(X, y, trees=8, max_depth=4, classes=2, seed=1, native_rounds=False, **kw)
+        for ta, tb in zip(a.trees, b.trees):
+            assert [q[:4] for q in ta.nodes] == [q[:4] for q in tb.nodes], kw
+            if "per_tree" in kw:
+                assert ta.allowed.numel() == 5 and {q[0] for q in ta.nodes if q[0] >= 0} <= set(ta.allowed.tolist())
+        if "per_tree" in kw:
+            assert len({tuple(t.allowed.tolist()) for t in a.trees}) > 1        # drawn afresh for each tree
+    one = tree.gradient_boosting(X, y, trees=1, max_depth=8, classes=2, min_weight=5.0)
+    leaf = one.trees[0].predict_binned(one._binned(X))
+    assert min(int((leaf == v).sum()) for v in leaf.unique()) >= 20                # a hessian is at most 1/4
+    f = tree.random_forest(X, y.float(), trees=4, max_depth=5, per_node=3)
+    assert all(max(1, int(10 * t.colsample)) == 3 for t in f.trees)
+    with pytest.raises(ValueError):
+        tree.random_forest(X, y.float(), trees=1, per_node=11)
+    had = quant_cpu.set_threads(0)
+    quant_cpu.set_threads(had)
+    e1 = tree.boosting(ml.Data(X, y), "classification", trees=5, workers=1)
+    e4 = tree.boosting(ml.Data(X, y), "classification", trees=5, workers=4)
+    assert torch.equal(e1.predict(X), e4.predict(X))                               # the trees do not depend on the threads
+    assert quant_cpu.set_threads(had) == had                                       # and the setting is put back
