@@ -714,3 +714,51 @@ MIMIR_CPU_API int mimir_cpu_trees_predict(const uint8_t* bins, int F, long long 
   });
   return 0;
 }
+
+// Isolation trees: out[r] = the sum over `trees` trees of (the number of cuts row r of X (float [n][F]) passes
+// before it reaches a leaf + that leaf's `extra`).  Node tables as in mimir_cpu_trees_predict, but a node is
+// (feature, threshold, left, right, extra) and a row goes left when its value is below the threshold (a NaN
+// goes right).  Returns 0, or -1 for a table that is not a tree.
+MIMIR_CPU_API int mimir_cpu_paths_sum(const float* X, int F, long long n, const double* nodes, const long long* offsets, int trees,
+                                      float* out) {
+  if (F < 1 || n < 0 || trees < 0) return -1;
+  struct Cut { int32_t feature, child[2]; float threshold; double extra; };
+  std::vector<Cut> cuts(trees > 0 ? static_cast<size_t>(offsets[trees] - offsets[0]) : 0);
+  for (int t = 0; t < trees; ++t) {
+    const long long lo = offsets[t], count = offsets[t + 1] - lo;
+    if (count <= 0 || lo - offsets[0] < 0) return -1;
+    for (long long i = 0; i < count; ++i) {
+      const double* nd = nodes + static_cast<size_t>(lo + i) * 5;
+      Cut& c = cuts[static_cast<size_t>(lo - offsets[0] + i)];
+      c.feature = static_cast<int32_t>(nd[0]);
+      c.threshold = static_cast<float>(nd[1]);
+      c.child[0] = static_cast<int32_t>(nd[2]);
+      c.child[1] = static_cast<int32_t>(nd[3]);
+      c.extra = nd[4];
+      if (c.feature >= F) return -1;
+      if (c.feature >= 0 && (c.child[0] <= i || c.child[0] >= count || c.child[1] <= i || c.child[1] >= count)) return -1;
+    }
+  }
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  const long long chunk = 1024, chunks = (n + chunk - 1) / chunk;
+  for_each(pool, chunks, n * trees >= 65536, [&](long long c) {
+    const long long a = c * chunk, b = a + chunk < n ? a + chunk : n;
+    std::vector<double> sum(b - a, 0.0);
+    for (int t = 0; t < trees; ++t) {
+      const Cut* tree = cuts.data() + (offsets[t] - offsets[0]);
+      for (long long r = a; r < b; ++r) {
+        const float* row = X + static_cast<size_t>(r) * F;
+        const Cut* s = tree;
+        int depth = 0;
+        while (s->feature >= 0) {
+          s = tree + s->child[row[s->feature] < s->threshold ? 0 : 1];
+          ++depth;
+        }
+        sum[r - a] += depth + s->extra;
+      }
+    }
+    for (long long r = a; r < b; ++r) out[r] = static_cast<float>(sum[r - a]);
+  });
+  return 0;
+}

@@ -554,11 +554,35 @@ class IsolationForestModel:
     def score(self, X):
         """Anomaly score in (0, 1): higher = more isolated."""
         X = torch.as_tensor(X).float()
-        depth = torch.zeros(X.shape[0])
-        for t in self.trees:
-            depth += self._path(t, X)
+        depth = self._paths_native(X) if X.device.type == "cpu" and self.trees else None
+        if depth is None:
+            depth = torch.zeros(X.shape[0])
+            for t in self.trees:
+                depth += self._path(t, X)
         c = 2 * (math.log(self.sample - 1) + 0.5772156649) - 2 * (self.sample - 1) / self.sample if self.sample > 2 else 1.0
         return torch.pow(2.0, -(depth / len(self.trees)) / c)
+
+    @staticmethod
+    def _extra(size):
+        """The expected further depth of a leaf that still holds ``size`` rows."""
+        return 2 * (math.log(size - 1) + 0.5772156649) - 2 * (size - 1) / size if size > 2 else (1.0 if size == 2 else 0.0)
+
+    def _paths_native(self, X):
+        """The summed path lengths of every row over all trees in one native pass (``mimir_cpu_paths_sum``), or
+        None when the library refuses the tables."""
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_paths_bound", False):
+            lib.mimir_cpu_paths_sum.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                                ctypes.c_void_p]
+            lib._paths_bound = True
+        tbl = torch.tensor([[q[0], q[1], q[2], q[3], self._extra(q[4]) if q[0] < 0 else 0.0] for t in self.trees for q in t], dtype=torch.float64)
+        offsets = torch.tensor([0] + [len(t) for t in self.trees], dtype=torch.int64).cumsum(0).contiguous()
+        X = X.contiguous()
+        out = torch.empty(X.shape[0])
+        rc = lib.mimir_cpu_paths_sum(X.data_ptr(), X.shape[1], X.shape[0], tbl.data_ptr(), offsets.data_ptr(), len(self.trees), out.data_ptr())
+        return out if rc == 0 else None
 
     @staticmethod
     def _path(tree, X):
@@ -568,8 +592,7 @@ class IsolationForestModel:
             node, idx, d = stack.pop()
             f, thr, l, r, size = tree[node]
             if f < 0 or idx.numel() == 0:
-                extra = 2 * (math.log(size - 1) + 0.5772156649) - 2 * (size - 1) / size if size > 2 else (1.0 if size == 2 else 0.0)
-                out[idx] = d + extra
+                out[idx] = d + IsolationForestModel._extra(size)
                 continue
             left = X[idx, f] < thr
             stack.append((l, idx[left], d + 1))

@@ -483,3 +483,16 @@ def test_tree_options_features_per_tree_features_per_node_smallest_child_weight_
     e4 = tree.boosting(ml.Data(X, y), "classification", trees=5, workers=4)
     assert torch.equal(e1.predict(X), e4.predict(X))                               # the trees do not depend on the threads
     assert quant_cpu.set_threads(had) == had                                       # and the setting is put back
+
+
+def test_isolation_scores_in_one_native_pass_equal_the_tree_by_tree_walk():
+    from mimir_b200.ml import tree
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(3000, 6, generator=g)
+    X[:20] += 6
+    X[40, 2] = float("nan")                                           # goes right at every cut on feature 2, in both walks
+    m = tree.isolation_forest(X, trees=30, samples=128)
+    walked = sum(m._path(t, X).double() for t in m.trees)
+    assert torch.allclose(m._paths_native(X).double(), walked, atol=1e-3)
+    s = m.score(X)
+    assert float(s[:20].mean()) > float(s[100:].mean()) + 0.1
