@@ -211,15 +211,37 @@ class Density(Model):
         return torch.where(d <= self.eps * self.eps, self.core_labels[i], torch.full_like(i, NOISE))
 
 
-def dbscan_fit(X, eps: float, features: int | None = None, min_rows: int = 5) -> Density:
-    """Neighbours are found block by block of rows against the table (a GEMM each); groups grow from each
-    unvisited core by repeated frontier expansion.  ``eps`` is in standardized units."""
+def dbscan_fit(X, eps: float, features: int | None = None, min_rows: int = 5, native: bool = True) -> Density:
+    """``eps`` is in standardized units.  On the host the search is native code: rows are compared tile by tile,
+    cores within reach of one another are joined as they are met, and nothing but the table is held in memory.
+    ``native=False`` (and other devices) finds neighbours block by block of rows against the table (a GEMM each)
+    and grows groups from each unvisited core by repeated frontier expansion: the same groups, the same numbers."""
     X = _table(X, features, "dbscan")
     if eps <= 0 or min_rows < 1:
         raise ValueError("dbscan: eps must be positive and min_rows at least 1")
     std = Standard.fit(X)
     Z = std.apply(X)
     n = Z.shape[0]
+    if native and Z.device.type == "cpu" and n < 2 ** 31:
+        # the whole search in native code: no list of neighbours is kept (``mimir_cpu_dbscan``)
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_dbscan_bound", False):
+            lib.mimir_cpu_dbscan.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p,
+                                             ctypes.c_void_p]
+            lib.mimir_cpu_dbscan.restype = ctypes.c_longlong
+            lib._dbscan_bound = True
+        Zc = Z.float().contiguous()
+        labels = torch.empty(n, dtype=torch.long)
+        core8 = torch.empty(n, dtype=torch.uint8)
+        if lib.mimir_cpu_dbscan(Zc.data_ptr(), n, Zc.shape[1], float(eps) * float(eps), int(min_rows), labels.data_ptr(), core8.data_ptr()) < 0:
+            raise ValueError("dbscan: the native search refused its arguments")
+        core = core8.bool()
+        m = Density()
+        m.features, m.eps, m.min_rows, m.labels, m.standard = X.shape[1], float(eps), int(min_rows), labels, std
+        m.cores, m.core_labels = Z[core], labels[core]
+        return m
     block = max(1, (1 << 25) // max(n, 1))
     near = []                                    # per row: indices within eps
     for s in range(0, n, block):
@@ -301,16 +323,32 @@ class Linkage(Model):
         return self.means.assign(X)
 
 
-def agglomerative(X, k: int, features: int | None = None) -> Linkage:
-    """Ward's minimum-variance hierarchy by the nearest-neighbour chain algorithm: time and memory grow
-    with the square of the rows.  The distance between clusters A and B is
-    ``|A||B| / (|A| + |B|) |mean_A - mean_B|^2``, kept up to date by the Lance-Williams update."""
+def agglomerative(X, k: int, features: int | None = None, native: bool = True) -> Linkage:
+    """Ward's minimum-variance hierarchy by the nearest-neighbour chain algorithm.  The distance between clusters
+    A and B is ``|A||B| / (|A| + |B|) |mean_A - mean_B|^2``.  On the host the chain runs in native code straight
+    from the clusters' means: time grows with the square of the rows, memory with the rows.  ``native=False`` (and
+    other devices) keeps an n x n matrix up to date by the Lance-Williams update: the same hierarchy up to
+    rounding."""
     X = _table(X, features, "agglomerative")
     n = X.shape[0]
     if k < 1 or k > n:
         raise ValueError(f"agglomerative: {k} groups of {n} rows")
     std = Standard.fit(X)
     Z = std.apply(X).double()
+    if native and Z.device.type == "cpu":
+        # the chain in native code over the clusters' means, with no distance matrix (``mimir_cpu_ward_means``)
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_ward_bound", False):
+            lib.mimir_cpu_ward_means.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+            lib._ward_bound = True
+        Zc = Z.contiguous()
+        pairs = torch.empty(max(n - 1, 0), 2, dtype=torch.long)
+        hs = torch.empty(max(n - 1, 0), dtype=torch.double)
+        if lib.mimir_cpu_ward_means(Zc.data_ptr(), n, Zc.shape[1], pairs.data_ptr(), hs.data_ptr()) != 0:
+            raise ValueError("agglomerative: the native chain refused its arguments")
+        return _linkage(X, std, k, [tuple(p) for p in pairs.tolist()], hs.tolist())
     D = 0.5 * _sq(Z, Z)                               # Ward distance between single rows
     D.fill_diagonal_(math.inf)
     size = torch.ones(n, dtype=torch.double)
@@ -343,6 +381,12 @@ def agglomerative(X, k: int, features: int | None = None) -> Linkage:
         alive[b] = False
         size[a] = sa + sb
         name[a] = n + step
+    return _linkage(X, std, k, merges, heights)
+
+
+def _linkage(X, std, k, merges, heights) -> Linkage:
+    """The hierarchy from the merges in the order the chain found them."""
+    n = X.shape[0]
     order = sorted(range(n - 1), key=lambda i: heights[i])
     # reducible linkage: the chain finds merges out of height order; renumber them rising
     remap = {}

@@ -85,6 +85,13 @@ def main(argv=None):
                    lambda m: float(m.score(Xn[half:], ycn[half:]))),
         "kmeans": (lambda: cluster.kmeans_fit(blobs, 8, inits=4), lambda m: m.inertia / a.rows,
                    lambda: sk.cluster.KMeans(8, n_init=4, random_state=0).fit(sklearn.preprocessing.scale(bn)), lambda m: float(m.inertia_) / a.rows),
+        "dbscan_10k": (lambda: cluster.dbscan_fit(blobs[:10000], eps=3.0, min_rows=5), lambda m: float(m.groups),
+                       lambda: sk.cluster.DBSCAN(eps=3.0, min_samples=5).fit(sklearn.preprocessing.scale(bn[:10000])),
+                       lambda m: float(m.labels_.max() + 1)),
+        "ward_5k": (lambda: cluster.agglomerative(blobs[:5000], 8), lambda m: m.means.inertia / 5000,
+                    lambda: sk.cluster.AgglomerativeClustering(8).fit(sklearn.preprocessing.scale(bn[:5000])),
+                    lambda m: float(sum(((sklearn.preprocessing.scale(bn[:5000])[m.labels_ == c] - sklearn.preprocessing.scale(bn[:5000])[m.labels_ == c].mean(0)) ** 2).sum()
+                                        for c in range(8))) / 5000),
         "knn_predict": (lambda: neighbors.fit(d_cls, "classification").classify(X[half:half + 2000]), lambda p: acc(p, y_cls[half:half + 2000]),
                         lambda: sk.neighbors.KNeighborsClassifier(5, algorithm="brute").fit(Xn[:half], ycn[:half]).predict(Xn[half:half + 2000]),
                         lambda p: float((torch.as_tensor(p) == y_cls[half:half + 2000]).float().mean())),

@@ -496,3 +496,28 @@ def test_isolation_scores_in_one_native_pass_equal_the_tree_by_tree_walk():
     assert torch.allclose(m._paths_native(X).double(), walked, atol=1e-3)
     s = m.score(X)
     assert float(s[:20].mean()) > float(s[100:].mean()) + 0.1
+
+
+def test_native_density_groups_and_ward_chain_equal_the_tensor_op_paths():
+    """DBSCAN on the host joins cores concurrently without keeping neighbour lists, Ward's chain runs from the
+    clusters' means without a distance matrix; the tensor-op paths (neighbour lists and frontier growth; an
+    n x n matrix under the Lance-Williams update) are their oracles: the same labels, noise and borders included,
+    and the same merges at the same heights."""
+    g = torch.Generator().manual_seed(4)
+    centers = torch.randn(5, 4, generator=g) * 3
+    X = centers[torch.randint(0, 5, (1500,), generator=g)] + 0.6 * torch.randn(1500, 4, generator=g)
+    noise = borders = 0
+    for eps, rows in ((0.25, 6), (0.4, 8), (0.6, 30)):
+        a = cluster.dbscan_fit(X, eps=eps, min_rows=rows)
+        b = cluster.dbscan_fit(X, eps=eps, min_rows=rows, native=False)
+        assert torch.equal(a.labels, b.labels) and torch.equal(a.core_labels, b.core_labels) and a.groups == b.groups
+        assert torch.equal(a.assign(X[:50]), b.assign(X[:50])) and a.groups >= 1
+        noise += int((a.labels < 0).sum())
+        borders += int((a.labels >= 0).sum()) - int(a.cores.shape[0])
+    assert noise > 0 and borders > 0                                         # every kind of row was compared
+    w = cluster.agglomerative(X[:700], 5)
+    v = cluster.agglomerative(X[:700], 5, native=False)
+    assert torch.equal(w.merges, v.merges) and torch.allclose(w.merge_heights, v.merge_heights, rtol=1e-9, atol=1e-9)
+    assert torch.equal(w.cut(5), v.cut(5)) and torch.equal(w.cut(40), v.cut(40))
+    one = cluster.agglomerative(X[:1], 1)
+    assert one.merges.shape == (0, 2)
