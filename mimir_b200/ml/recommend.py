@@ -49,7 +49,7 @@ class Factors(Model):
         return FactorsModule.of(self)
 
 
-def _solve_side(A, B, idx_rows, idx_cols, conf, target, l2, implicit):
+def _solve_side(A, B, idx_rows, idx_cols, conf, target, l2, implicit, native=True):
     """Sets each row of ``A`` to the least-squares fit against the fixed ``B`` of what it has events with.
     Implicit: (B'B + B_u'(C_u - I)B_u + l2 I) x = B_u' C_u p_u with one shared B'B."""
     k = B.shape[1]
@@ -58,6 +58,26 @@ def _solve_side(A, B, idx_rows, idx_cols, conf, target, l2, implicit):
     rows, cols, conf, target = idx_rows[order], idx_cols[order], conf[order], target[order]
     counts = torch.bincount(rows, minlength=A.shape[0])
     BtB = B.t() @ B if implicit else None
+    if native and A.device.type == "cpu" and A.dtype == torch.double and A.is_contiguous():
+        # each row's normal equations built and solved (Cholesky) by the worker that owns the row (``mimir_cpu_als_side``)
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_als_bound", False):
+            lib.mimir_cpu_als_side.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p,
+                                               ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_double]
+            lib._als_bound = True
+        start = torch.zeros(A.shape[0] + 1, dtype=torch.long)
+        start[1:] = counts.cumsum(0)
+        Bc = B.contiguous()
+        w = (conf - (1.0 if implicit else 0.0)).double().contiguous()
+        t = (conf * target).double().contiguous()
+        cols = cols.contiguous()
+        base = BtB.contiguous() if implicit else None
+        if lib.mimir_cpu_als_side(A.data_ptr(), A.shape[0], Bc.data_ptr(), Bc.shape[0], k, start.data_ptr(), cols.data_ptr(), w.data_ptr(),
+                                  t.data_ptr(), base.data_ptr() if base is not None else None, float(l2)) != 0:
+            raise ValueError("recommend: the native solver refused its arguments")
+        return
     # outer products of the event rows, summed per row of A
     Bc = B[cols]
     outer = torch.zeros(A.shape[0], k, k, dtype=B.dtype).index_add_(0, rows, (conf - (1.0 if implicit else 0.0))[:, None, None] * Bc[:, :, None] * Bc[:, None, :])

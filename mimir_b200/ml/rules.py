@@ -6,6 +6,8 @@ from __future__ import annotations
 import itertools
 from dataclasses import dataclass
 
+import torch
+
 
 @dataclass
 class Rule:
@@ -33,24 +35,44 @@ def mine(baskets, min_support: float = 0.01, min_confidence: float = 0.5, max_it
             count[k] = count.get(k, 0) + 1
     frequent = {k: c for k, c in count.items() if c >= need}
     support = dict(frequent)
-    level = sorted(frequent)
+    level = sorted(frequent, key=lambda t: tuple(map(str, t)))
+    # the baskets as a 0 / 1 table over the frequent items: the baskets that hold a set are counted by matrix
+    # products (the columns of a set's first items multiplied together, times the table), not basket by basket
+    column = {k[0]: j for j, k in enumerate(level)}
+    table = torch.zeros(n, max(len(level), 1))
+    held = [(r, column[x]) for r, b in enumerate(sets) for x in b if x in column]
+    if held:
+        at = torch.tensor(held, dtype=torch.long)
+        table[at[:, 0], at[:, 1]] = 1.0
     size = 1
     while level and size < max_items:
         size += 1
-        cands = set()
-        for a, b in itertools.combinations(level, 2):
-            if a[:-1] == b[:-1]:
-                c = tuple(sorted(set(a) | set(b), key=str))
-                if len(c) == size and all(tuple(s) in frequent for s in itertools.combinations(c, size - 1)):
-                    cands.add(c)
-        count = {c: 0 for c in cands}
-        members = {c: frozenset(c) for c in cands}
-        for b in sets:
-            if len(b) < size:
-                continue
-            for c, fs in members.items():
-                if fs <= b:
-                    count[c] += 1
+        # candidates: two frequent sets that share all but their last item, every smaller subset frequent
+        groups: dict = {}
+        for c in level:
+            groups.setdefault(c[:-1], []).append(c[-1])
+        cands = []
+        for prefix, lasts in groups.items():
+            for x, y in itertools.combinations(lasts, 2):
+                c = prefix + (x, y)
+                if size == 2 or all(tuple(sub) in frequent for sub in itertools.combinations(c, size - 1)):
+                    cands.append(c)
+        count = {}
+        by_prefix: dict = {}
+        for c in cands:
+            by_prefix.setdefault(c[:-1], []).append(c[-1])
+        prefixes = list(by_prefix)
+        for p0 in range(0, len(prefixes), 1024):
+            part = prefixes[p0: p0 + 1024]
+            cols = torch.tensor([[column[x] for x in pre] for pre in part], dtype=torch.long)       # [prefixes, size - 1]
+            both = table[:, cols[:, 0]]
+            for j in range(1, size - 1):
+                both = both * table[:, cols[:, j]]
+            counts = both.t() @ table                                                              # [prefixes, items]
+            for r, pre in enumerate(part):
+                row = counts[r]
+                for last in by_prefix[pre]:
+                    count[pre + (last,)] = int(round(float(row[column[last]])))
         frequent = {c: v for c, v in count.items() if v >= need}
         support.update(frequent)
         level = sorted(frequent, key=lambda t: tuple(map(str, t)))

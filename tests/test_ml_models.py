@@ -521,3 +521,32 @@ def test_native_density_groups_and_ward_chain_equal_the_tensor_op_paths():
     assert torch.equal(w.cut(5), v.cut(5)) and torch.equal(w.cut(40), v.cut(40))
     one = cluster.agglomerative(X[:1], 1)
     assert one.merges.shape == (0, 2)
+
+
+def test_native_least_squares_side_and_rules_counted_by_matrix_products():
+    """One side of alternating least squares solved row by row in native code equals the batched tensor solve,
+    with and without the shared B'B of implicit feedback and for rows without events; item sets counted by matrix
+    products give the counts of a basket-by-basket count, with item names whose text order is not their numeric
+    order and sets of up to four items."""
+    import itertools
+    g = torch.Generator().manual_seed(0)
+    U, I, E, k = 120, 90, 2500, 6
+    u, i = torch.randint(0, U - 5, (E,), generator=g), torch.randint(0, I, (E,), generator=g)      # the last five rows have no events
+    for implicit in (True, False):
+        A1 = torch.randn(U, k, generator=g, dtype=torch.double)
+        A2, B = A1.clone(), torch.randn(I, k, generator=g, dtype=torch.double)
+        conf, target = 1 + 10 * torch.rand(E, generator=g, dtype=torch.double), torch.rand(E, generator=g, dtype=torch.double)
+        recommend._solve_side(A1, B, u, i, conf, target, 0.1, implicit)
+        recommend._solve_side(A2, B, u, i, conf, target, 0.1, implicit, native=False)
+        assert torch.allclose(A1, A2, atol=1e-10) and float(A1[-5:].abs().max()) == 0.0
+    baskets = [torch.randint(0, 120, (5,), generator=g).tolist() + [7, 100][: int(r % 3 == 0) * 2] for r in range(1500)]
+    found = rules.mine(baskets, min_support=0.004, min_confidence=0.0, max_items=4)
+    sets = [frozenset(b) for b in baskets]
+    assert found and max(len(r.if_) + len(r.then) for r in found) >= 3
+    for r in found[:40] + found[-40:]:
+        both = sum(1 for b in sets if set(r.if_) | set(r.then) <= b)
+        first = sum(1 for b in sets if set(r.if_) <= b)
+        assert abs(r.support - both / len(sets)) < 1e-12 and abs(r.confidence - both / first) < 1e-12
+    pairs = {frozenset(r.if_ + r.then) for r in found if len(r.if_) + len(r.then) == 2}
+    want = {frozenset(p) for p in itertools.combinations(range(120), 2) if sum(1 for b in sets if set(p) <= b) >= 0.004 * len(sets)}
+    assert pairs == want
