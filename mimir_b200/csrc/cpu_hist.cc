@@ -596,6 +596,69 @@ MIMIR_CPU_API int mimir_cpu_tree_predict(const uint8_t* bins, int F, long long n
   return bad.load() ? -1 : 0;
 }
 
+// Softmax boosting over `classes` classes: as mimir_cpu_boost, but a round computes every row's class
+// probabilities once from score [total][classes] and then grows one tree per class on
+// g = p_c - (y == c), h = max(p_c (1 - p_c), 1e-6); the scores move after each tree, the probabilities of the round
+// do not.  y: int64 [total] in [0, classes).  seeds [rounds][classes]; allowed [rounds][n_allowed] (one list per
+// round, shared by its trees) or null.  nodes: double [rounds * classes][max_nodes][5]; counts: int
+// [rounds * classes]; importance: double [rounds * classes][F].  Returns the rounds done, or -1.
+MIMIR_CPU_API int mimir_cpu_boost_classes(const uint8_t* colbins, long long total, int F, const int64_t* y, float* score, int classes,
+                                          int rounds, double lr, int nbins, int max_depth, long long min_leaf, double min_gain, double l2,
+                                          int colsample_k, const unsigned long long* seeds, double* nodes, int max_nodes, int* counts,
+                                          double* importance, double min_weight, const int32_t* allowed, int n_allowed) {
+  if (total < 1 || total > INT32_MAX || rounds < 0 || classes < 2 || classes > 4096) return -1;
+  for (long long k = 0; k < total; ++k)
+    if (y[k] < 0 || y[k] >= classes) return -1;
+  std::lock_guard<std::mutex> lk(mimir_cpu::pool_mutex());
+  mimir_cpu::Pool& pool = mimir_cpu::pool();
+  mimir_cpu::Pool::Awake awake(pool);
+  std::vector<float> p(static_cast<size_t>(total) * classes), g(total), h(total), leaf(total);
+  std::vector<int32_t> idx(total);
+  const long long chunk = 4096, chunks = (total + chunk - 1) / chunk;
+  const bool wide = total >= 4 * chunk;
+  const float step = static_cast<float>(lr);
+  for (int r = 0; r < rounds; ++r) {
+    for_each(pool, chunks, wide, [&](long long c) {
+      const long long a = c * chunk, b = a + chunk < total ? a + chunk : total;
+      for (long long k = a; k < b; ++k) {
+        const float* s = score + static_cast<size_t>(k) * classes;
+        float* q = p.data() + static_cast<size_t>(k) * classes;
+        float top = s[0];
+        for (int c2 = 1; c2 < classes; ++c2) top = s[c2] > top ? s[c2] : top;
+        float sum = 0.f;
+        for (int c2 = 0; c2 < classes; ++c2) { q[c2] = std::exp(s[c2] - top); sum += q[c2]; }
+        const float inv = 1.0f / sum;
+        for (int c2 = 0; c2 < classes; ++c2) q[c2] *= inv;
+      }
+    });
+    for (int cls = 0; cls < classes; ++cls) {
+      const size_t t = static_cast<size_t>(r) * classes + cls;
+      for_each(pool, chunks, wide, [&](long long c) {
+        const long long a = c * chunk, b = a + chunk < total ? a + chunk : total;
+        for (long long k = a; k < b; ++k) {
+          const float pk = p[static_cast<size_t>(k) * classes + cls];
+          const float hh = pk * (1.0f - pk);
+          idx[k] = static_cast<int32_t>(k);
+          g[k] = pk - (y[k] == cls ? 1.0f : 0.0f);
+          h[k] = hh < 1e-6f ? 1e-6f : hh;
+        }
+      });
+      double* imp = importance + t * F;
+      for (int f = 0; f < F; ++f) imp[f] = 0;
+      const int cnt = grow_tree(pool, colbins, total, F, idx.data(), total, g.data(), h.data(), nbins, max_depth, min_leaf, min_gain, l2,
+                                colsample_k, seeds ? seeds[t] : 0ull, nodes + t * max_nodes * 5, max_nodes, imp, leaf.data(), false,
+                                min_weight, allowed ? allowed + static_cast<size_t>(r) * n_allowed : nullptr, n_allowed);
+      if (cnt <= 0) return -1;
+      counts[t] = cnt;
+      for_each(pool, chunks, wide, [&](long long c) {
+        const long long a = c * chunk, b = a + chunk < total ? a + chunk : total;
+        for (long long k = a; k < b; ++k) score[static_cast<size_t>(k) * classes + cls] += step * leaf[k];
+      });
+    }
+  }
+  return rounds;
+}
+
 namespace {
 
 // the number of edges below x (NaN: n_edges): the first edge that is not below x, found without a branch the

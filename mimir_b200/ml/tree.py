@@ -328,9 +328,12 @@ class Model:
         return Model(trees, torch.tensor(d["edges"]), d["lr"], base, d["classes"], d["kind"])
 
 
-def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight=0.0, per_tree=1.0):
-    """``rounds`` trees grown one after another by ``mimir_cpu_boost`` (``csrc/cpu_hist.cc``) on all rows of ``B``;
-    ``score`` is updated in place.  Feature-draw seeds come from ``gen`` in the order the per-tree loop draws them."""
+def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight=0.0, per_tree=1.0,
+                  classes=0):
+    """``rounds`` rounds grown one after another by ``mimir_cpu_boost`` (``csrc/cpu_hist.cc``) on all rows of ``B``,
+    or, with ``classes`` above two, by ``mimir_cpu_boost_classes`` (one tree per class and round; the result is a
+    list of rounds, each a list of trees).  ``score`` is updated in place.  Feature lists and feature-draw seeds
+    come from ``gen`` in the order the per-round loop draws them."""
     import ctypes
     from .. import _native
     lib = _native.lib()
@@ -339,8 +342,12 @@ def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, 
         lib.mimir_cpu_boost.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_double, c.c_int, c.c_int,
                                         c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p,
                                         c.c_double, c.c_void_p, c.c_int]
+        lib.mimir_cpu_boost_classes.argtypes = [c.c_void_p, c.c_longlong, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_double, c.c_int,
+                                                c.c_int, c.c_longlong, c.c_double, c.c_double, c.c_int, c.c_void_p, c.c_void_p, c.c_int, c.c_void_p,
+                                                c.c_void_p, c.c_double, c.c_void_p, c.c_int]
         lib._boost_bound = True
     total, F = B.shape
+    per_round = classes if classes > 2 else 1
     k, seeds, allowed = 0, None, None
     universe = F if per_tree >= 1.0 else max(1, int(F * per_tree))
     if colsample < 1.0 or per_tree < 1.0:
@@ -350,29 +357,36 @@ def _boost_native(B, y, score, kind, rounds, lr, max_depth, min_leaf, min_gain, 
         for _ in range(rounds):
             if per_tree < 1.0:
                 lists.append(_draw_features(F, per_tree, gen))
-            seeds.append(int(torch.randint(0, 2 ** 62, (1,), generator=gen)) if colsample < 1.0 else 0)
+            seeds += [int(torch.randint(0, 2 ** 62, (1,), generator=gen)) if colsample < 1.0 else 0 for _ in range(per_round)]
         seeds = torch.tensor(seeds, dtype=torch.int64)
         allowed = torch.stack(lists).contiguous() if lists else None
     max_nodes = int(min(2 ** (max_depth + 1) - 1, 2 * total + 1))
-    nodes = torch.empty(rounds, max_nodes, 5, dtype=torch.float64)
-    counts = torch.zeros(rounds, dtype=torch.int32)
-    imp = torch.empty(rounds, F, dtype=torch.float64)
+    grown = rounds * per_round
+    nodes = torch.empty(grown, max_nodes, 5, dtype=torch.float64)
+    counts = torch.zeros(grown, dtype=torch.int32)
+    imp = torch.empty(grown, F, dtype=torch.float64)
     cols = _columns(B)
-    y = y.float().contiguous()
-    done = lib.mimir_cpu_boost(cols.data_ptr(), total, F, y.data_ptr(), score.data_ptr(), kind, rounds, float(lr), bins, max_depth,
-                               max(int(min_leaf), 1) if min_leaf >= 1 else 0, float(min_gain), float(l2), k,
-                               seeds.data_ptr() if seeds is not None else None, nodes.data_ptr(), max_nodes, counts.data_ptr(), imp.data_ptr(),
-                               float(min_weight), allowed.data_ptr() if allowed is not None else None, universe)
+    tail = (float(lr), bins, max_depth, max(int(min_leaf), 1) if min_leaf >= 1 else 0, float(min_gain), float(l2), k,
+            seeds.data_ptr() if seeds is not None else None, nodes.data_ptr(), max_nodes, counts.data_ptr(), imp.data_ptr(),
+            float(min_weight), allowed.data_ptr() if allowed is not None else None, universe)
+    if classes > 2:
+        y = y.long().contiguous()
+        if not score.is_contiguous() or tuple(score.shape) != (total, classes):
+            raise ValueError("boosting: scores must be a contiguous [rows, classes] table")
+        done = lib.mimir_cpu_boost_classes(cols.data_ptr(), total, F, y.data_ptr(), score.data_ptr(), classes, rounds, *tail)
+    else:
+        y = y.float().contiguous()
+        done = lib.mimir_cpu_boost(cols.data_ptr(), total, F, y.data_ptr(), score.data_ptr(), kind, rounds, *tail)
     if done != rounds:
         raise RuntimeError("boosting: the native grower refused its arguments")
     out = []
-    for r in range(rounds):
-        t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, None if allowed is None else allowed[r])
+    for r in range(grown):
+        t = _Tree(max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, None if allowed is None else allowed[r // per_round])
         t.nodes = [[int(q[0]), int(q[1]), int(q[2]), int(q[3]), float(q[4])] for q in nodes[r, : int(counts[r])].tolist()]
         t.importance = imp[r].float()
         t.answers = None
         out.append(t)
-    return out
+    return out if per_round == 1 else [out[r: r + per_round] for r in range(0, grown, per_round)]
 
 
 def _draw_features(F, share, gen):
@@ -391,8 +405,8 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
     smallest sum of hessians a child may hold (XGBoost's min_child_weight; tree/options.go: MinWeight).
     ``validation`` (a table, or ``(X, y)``) is scored after every round (squared error or log loss): boosting
     stops once ``patience`` rounds in a row have not improved it, and the model keeps the best round's trees
-    (tree/boost.go: Validation).  Without row sampling and validation, regression and two-class boosting run all
-    their rounds in one native call; ``native_rounds=False`` keeps the per-round loop (the same trees up to the
+    (tree/boost.go: Validation).  Without row sampling and validation every round runs inside one native
+    call; ``native_rounds=False`` keeps the per-round loop (the same trees up to the
     rounding of the sigmoid)."""
     X, y = torch.as_tensor(X).float(), torch.as_tensor(y)
     gen = torch.Generator().manual_seed(seed)
@@ -415,12 +429,12 @@ def gradient_boosting(X, y, trees=100, learning_rate=0.1, max_depth=6, min_leaf=
         F = torch.full((n,), base)
     if held is not None:
         held["F"] = base.clone().repeat(held["B"].shape[0], 1) if classes > 2 else torch.full((held["B"].shape[0],), base)
-    if native_rounds and classes <= 2 and subsample >= 1.0 and held is None and B.dtype == torch.uint8 and B.device.type == "cpu" and bins <= 256:
+    if native_rounds and subsample >= 1.0 and held is None and B.dtype == torch.uint8 and B.device.type == "cpu" and bins <= 256:
         # every round in native code (``mimir_cpu_boost``): the loop below is its oracle
         span = 10 if progress is not None else trees
         for it in range(0, trees, span):
-            out_trees += _boost_native(B, yf, F, 0 if classes == 0 else 1, min(span, trees - it), learning_rate, max_depth, min_leaf,
-                                       min_gain, l2, bins, colsample, gen, min_weight, per_tree)
+            out_trees += _boost_native(B, y if classes > 2 else yf, F, 0 if classes == 0 else 1, min(span, trees - it), learning_rate,
+                                       max_depth, min_leaf, min_gain, l2, bins, colsample, gen, min_weight, per_tree, classes)
             if progress is not None and len(out_trees) % 10 == 0:
                 progress.write(f"tree {len(out_trees)}/{trees}\n")
         trees = 0

@@ -550,3 +550,21 @@ def test_native_least_squares_side_and_rules_counted_by_matrix_products():
     pairs = {frozenset(r.if_ + r.then) for r in found if len(r.if_) + len(r.then) == 2}
     want = {frozenset(p) for p in itertools.combinations(range(120), 2) if sum(1 for b in sets if set(p) <= b) >= 0.004 * len(sets)}
     assert pairs == want
+
+
+def test_softmax_boosting_rounds_in_one_native_call_grow_the_trees_of_the_per_round_loop():
+    from mimir_b200.ml import tree
+    g = torch.Generator().manual_seed(8)
+    centers = torch.randn(4, 6, generator=g) * 2
+    y = torch.randint(0, 4, (2500,), generator=g)
+    X = centers[y] + torch.randn(2500, 6, generator=g)
+    for kw in (dict(), dict(colsample=0.6, per_tree=0.7), dict(min_weight=2.0)):
+        a = tree.gradient_boosting(X, y, trees=6, max_depth=4, classes=4, seed=2, **kw)
+        b = tree.gradient_boosting(X, y, trees=6, max_depth=4, classes=4, seed=2, native_rounds=False, **kw)
+        assert len(a.trees) == len(b.trees) == 6 and all(len(r) == 4 for r in a.trees)
+        for ra, rb in zip(a.trees, b.trees):
+            for ta, tb in zip(ra, rb):
+                assert [q[:4] for q in ta.nodes] == [q[:4] for q in tb.nodes], kw
+        assert float((a.raw(X) - b.raw(X)).abs().max()) < 1e-4
+        assert torch.allclose(a.importance(), b.importance(), atol=1e-5)
+    assert float((a.classify(X) == y).float().mean()) > 0.8
