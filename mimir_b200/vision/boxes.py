@@ -14,7 +14,24 @@ def box_iou(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def nms(boxes: torch.Tensor, scores: torch.Tensor, threshold: float = 0.5) -> torch.Tensor:
-    order = scores.argsort(descending=True)
+    """The boxes kept by greedy suppression, best first.  On the host each box is compared with the boxes kept
+    so far in native code (``mimir_cpu_nms``); elsewhere against a full table of overlaps."""
+    order = scores.argsort(descending=True, stable=True)
+    if boxes.device.type == "cpu" and scores.device.type == "cpu":
+        import ctypes
+        from .. import _native
+        lib = _native.lib()
+        if not getattr(lib, "_nms_bound", False):
+            lib.mimir_cpu_nms.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p]
+            lib.mimir_cpu_nms.restype = ctypes.c_longlong
+            lib._nms_bound = True
+        b = boxes.float().reshape(-1, 4).contiguous()
+        order = order.contiguous()
+        keep = torch.empty(b.shape[0], dtype=torch.long)
+        count = lib.mimir_cpu_nms(b.data_ptr(), order.data_ptr(), b.shape[0], float(threshold), keep.data_ptr())
+        if count < 0:
+            raise ValueError("nms: boxes and scores do not match")
+        return keep[:count].clone()
     iou = box_iou(boxes[order], boxes[order])
     keep, dead = [], torch.zeros(len(order), dtype=torch.bool)
     for i in range(len(order)):

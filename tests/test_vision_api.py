@@ -98,3 +98,23 @@ def test_box_scores_and_losses():
     assert p.grad().data()[1].abs().sum() > 0 and p.grad().data()[0].abs().sum() < 1e-6
     pred, truth = torch.tensor([0, 0, 1, 1, 2, 2]), torch.tensor([0, 1, 1, 1, 2, 0])
     assert abs(vision.mean_iou(pred, truth, 4) - (1 / 3 + 2 / 3 + 1 / 2) / 3) < 1e-9
+
+
+def test_native_suppression_keeps_the_boxes_of_the_overlap_table():
+    """Greedy suppression on the host compares each box with the boxes kept so far; a full table of overlaps
+    visited in the same order is its oracle, ties in score included."""
+    import torch
+    from mimir_b200.vision import boxes as VB
+    g = torch.Generator().manual_seed(0)
+    for n in (0, 1, 400):
+        b = torch.rand(n, 4, generator=g) * 100
+        b[:, 2:] = b[:, :2] + 10 + torch.rand(n, 2, generator=g) * 30
+        s = (torch.rand(n, generator=g) * 20).round() / 20                     # repeated scores
+        order = s.argsort(descending=True, stable=True)
+        iou = VB.box_iou(b[order], b[order])
+        keep, dead = [], torch.zeros(n, dtype=torch.bool)
+        for i in range(n):
+            if not dead[i]:
+                keep.append(int(order[i]))
+                dead |= iou[i] > 0.4
+        assert VB.nms(b, s, 0.4).tolist() == keep
