@@ -57,14 +57,54 @@ def mnist(directory: str, train: bool = True, batch_size: int = 128, shuffle: bo
 
 
 # ------------------------------------------------------------------------- CSV
+def _read_csv_native(path: str, header: bool):
+    """``(names, table)`` of a CSV file of plain numbers parsed by ``mimir_cpu_csv_parse`` (pieces of the file
+    in parallel), or None when the file needs the general reader (quotes, a field that is not a number, ragged
+    lines)."""
+    import ctypes
+
+    import numpy as np
+
+    from .. import _native
+    with open(path, "rb") as f:
+        first = f.readline()
+    if not first.strip() or b'"' in first:
+        return None
+    names = next(_csv.reader([first.decode("utf-8", "replace").rstrip("\r\n")]))
+    raw = np.fromfile(path, dtype=np.uint8)
+    skip = len(first) if header else 0
+    if not header:
+        names = [f"c{i}" for i in range(len(names))]
+    if (raw[skip:] == ord('"')).any():
+        return None
+    lib = _native.lib()
+    if not getattr(lib, "_csv_bound", False):
+        lib.mimir_cpu_csv_lines.argtypes = [ctypes.c_void_p, ctypes.c_longlong]
+        lib.mimir_cpu_csv_lines.restype = ctypes.c_longlong
+        lib.mimir_cpu_csv_parse.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong]
+        lib.mimir_cpu_csv_parse.restype = ctypes.c_longlong
+        lib._csv_bound = True
+    at, size = raw.ctypes.data + skip, int(raw.size) - skip
+    rows = lib.mimir_cpu_csv_lines(at, size)
+    table = torch.empty(max(rows, 0), len(names), dtype=torch.float64)
+    if rows < 0 or lib.mimir_cpu_csv_parse(at, size, len(names), table.data_ptr(), rows) != rows:
+        return None
+    return names, table
+
+
 def read_csv(path: str, label: str | int | None = -1, header: bool = True, dtype=torch.float32):
     """Numeric CSV -> ``(X, y, feature_names)``; ``label`` names or indexes the target column (None: no target)."""
-    with open(path, newline="") as f:
-        rows = list(_csv.reader(f))
-    names = rows[0] if header else [f"c{i}" for i in range(len(rows[0]))]
-    body = rows[1:] if header else rows
+    data = names = None
+    fast = _read_csv_native(path, header)
+    if fast is not None:
+        names, data = fast
+    else:
+        with open(path, newline="") as f:
+            rows = list(_csv.reader(f))
+        names = rows[0] if header else [f"c{i}" for i in range(len(rows[0]))]
+        body = rows[1:] if header else rows
+        data = torch.tensor([[float(v) if v != "" else float("nan") for v in r] for r in body], dtype=torch.float64)
     li = None if label is None else (names.index(label) if isinstance(label, str) else label % len(names))
-    data = torch.tensor([[float(v) if v != "" else float("nan") for v in r] for r in body], dtype=torch.float64)
     if li is None:
         return data.to(dtype), None, names
     keep = [i for i in range(len(names)) if i != li]

@@ -97,3 +97,37 @@ def test_streamed_statistics_normalize_and_named_classes(tmp_path):
         p = os.path.join(tmp_path, "bad.parquet")
         parquet.write(p, {"a": torch.zeros(2), "label": ["yes", "maybe"]})
         list(datasets.parquet_shards(p, ["a"], "label", classes=("no", "yes")))
+
+
+def test_native_csv_reader_equals_the_general_one(tmp_path):
+    """Plain numeric files are parsed in native code, pieces of the file in parallel; the general reader is the
+    oracle (and the fallback for quoted or non-numeric fields): empty fields, blank lines, CRLF, signs, exponents,
+    a last line without a line end, and a file large enough to be cut into pieces."""
+    import numpy as np
+    from mimir_b200.data import datasets
+    small = tmp_path / "s.csv"
+    small.write_text("a,b,c\r\n1,,3\r\n\r\n+4.5, 5e-1 ,nan\r\n7,8,9")
+    X, y, names = datasets.read_csv(str(small))
+    assert names == ["a", "b"] and X.shape == (3, 2) and torch.isnan(X[0, 1]) and torch.isnan(y[1])
+    assert X[1].tolist() == [4.5, 0.5] and y.tolist()[::2] == [3.0, 9.0]
+    big = tmp_path / "b.csv"
+    table = np.random.default_rng(0).standard_normal((30000, 9))
+    np.savetxt(big, table, delimiter=",", header=",".join(f"c{i}" for i in range(9)), comments="", fmt="%.9g")
+    assert big.stat().st_size > (1 << 20)
+    Xn, yn, _ = datasets.read_csv(str(big), label="c3")
+    native = datasets._read_csv_native
+    try:
+        datasets._read_csv_native = lambda *a: None
+        Xg, yg, _ = datasets.read_csv(str(big), label="c3")
+    finally:
+        datasets._read_csv_native = native
+    assert torch.equal(Xn, Xg) and torch.equal(yn, yg) and Xn.shape == (30000, 8)
+    quoted = tmp_path / "q.csv"
+    quoted.write_text('a,b\n1,"2"\n')
+    assert datasets._read_csv_native(str(quoted), True) is None and datasets.read_csv(str(quoted))[1].tolist() == [2.0]
+    ragged = tmp_path / "r.csv"
+    ragged.write_text("a,b\n1,2\n3\n")
+    assert datasets._read_csv_native(str(ragged), True) is None
+    bare = tmp_path / "n.csv"
+    bare.write_text("1,2\n3,4\n")
+    assert datasets.read_csv(str(bare), header=False)[0].tolist() == [[1.0], [3.0]]
