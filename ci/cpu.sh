@@ -5,3 +5,7 @@ set -euo pipefail
 cd "$(dirname "$0")/.."
 python -c "import __graft_entry__ as g; g.build()"
 python -m pytest tests -x -q -m "not gpu"
+# classical models against scikit-learn on this machine, where it is installed: none may take twice its time
+if python -c "import sklearn" 2>/dev/null; then
+  python -m mimir_b200.utils.bench_ml --rows 20000 --gate 2
+fi

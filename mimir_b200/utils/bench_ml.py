@@ -4,7 +4,8 @@
 
 Prints one JSON line per model: fit seconds here and in scikit-learn (the best of ``--repeat`` runs, after
 one warm-up) and a quality figure of each (accuracy, R^2, inertia ratio), so a speed-up that costs quality
-shows.  scikit-learn is optional: without it only this library's figures are printed."""
+shows.  ``--gate 2`` makes it a check: the exit code is 1 when some model takes more than twice scikit-learn's
+time.  scikit-learn is optional: without it only this library's figures are printed."""
 from __future__ import annotations
 
 import argparse
@@ -42,6 +43,7 @@ def main(argv=None):
     ap.add_argument("--rows", type=int, default=20000)
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--only", nargs="*", default=None)
+    ap.add_argument("--gate", type=float, default=0.0, help="exit 1 when a model takes more than this many times scikit-learn's time")
     a = ap.parse_args(argv)
     from .. import ml
     from ..ml import cluster, decompose, linear, neighbors, svm, tree
@@ -100,6 +102,7 @@ def main(argv=None):
     }
     if sk is not None:
         import sklearn.preprocessing  # noqa: F401
+    slow = []
     for name, (ours, q_ours, theirs, q_theirs) in cases.items():
         if a.only and name not in a.only:
             continue
@@ -108,7 +111,11 @@ def main(argv=None):
         if sk is not None:
             t2, m2 = _best(theirs, a.repeat)
             line.update(sklearn_seconds=round(t2, 4), sklearn_quality=round(q_theirs(m2), 4), speedup=round(t2 / t, 2))
+            if a.gate > 0 and t > a.gate * t2:
+                slow.append(name)
         print(json.dumps(line), flush=True)
+    if slow:
+        raise SystemExit(f"slower than {a.gate} x scikit-learn: {', '.join(slow)}")
 
 
 if __name__ == "__main__":
